@@ -1,0 +1,195 @@
+"""Python launchers for the tcgen05 GEMM (``csrc/cuda/gemm_sm100.cu``).
+
+Conventions: ``a`` holds the A operand either as ``[M, K]`` (K contiguous, ``a_mn=False``) or as
+``[K, M]`` (``a_mn=True``); ``b`` holds B either as ``[N, K]`` (the ``[out, in]`` weight layout of the
+reference, core/ops_cpu_dense.cpp:199-201) or as ``[K, N]`` (``b_mn=True``).  Operands are fp16 or
+bf16, accumulation is fp32, the output dtype is chosen by the caller.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+EPI_STORE, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2
+
+
+def _check_operand(t, name):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with unit inner stride")
+    if t.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError(f"{name} must be fp16 or bf16")
+    if t.data_ptr() % 16 or (t.stride(0) * 2) % 16:
+        raise ValueError(f"{name} must be 16-byte aligned with a row pitch that is a multiple of 16 bytes")
+
+
+def _launch(args: _lib.GemmArgs):
+    rc = _lib.lib().gb_gemm(ctypes.byref(args), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_gemm")
+
+
+def _base_args(a, b, M, N, K, a_mn, b_mn, out, block_n):
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    if a.dtype != b.dtype:
+        raise ValueError("operand dtypes differ")
+    g = _lib.GemmArgs()
+    g.A, g.B = a.data_ptr(), b.data_ptr()
+    g.M, g.N, g.K = M, N, K
+    g.a_rows, g.a_cols, g.lda = a.shape[0], a.shape[1], a.stride(0)
+    g.b_rows, g.b_cols, g.ldb = b.shape[0], b.shape[1], b.stride(0)
+    g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
+    g.is_bf16 = int(a.dtype == torch.bfloat16)
+    g.out_dtype = _lib.DT_CODE[out.dtype]
+    g.block_n = block_n
+    g.out = out.data_ptr()
+    g.ldo = out.stride(-2)
+    g.status = _lib.status_word(a.device).data_ptr()
+    return g
+
+
+def pick_block_n(M, N):
+    """Smaller N tiles when the problem would otherwise leave most of the 148 SMs idle."""
+    tiles128 = ((M + 127) // 128) * ((N + 127) // 128)
+    if tiles128 < 100 and N % 64 == 0:
+        return 64
+    return 128
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, addend=None, block_n=0):
+    """``out = A @ B^T (+ addend)``; ``addend`` is fp32 and may alias an fp32 ``out`` (accumulate)."""
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"reduction dims differ: {K} vs {Kb}")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    if not block_n:
+        block_n = pick_block_n(M, N)
+    g = _base_args(a, b, M, N, K, a_mn, b_mn, out, block_n)
+    g.epilogue = EPI_STORE
+    if addend is not None:
+        if addend.dtype != torch.float32:
+            raise ValueError("addend must be fp32")
+        g.addend, g.ld_add = addend.data_ptr(), addend.stride(0)
+    _launch(g)
+    return out
+
+
+def gemm_swiglu(a, w_gu, *, act_out=None, gu_out=None, tile_expert=None, num_m_tiles=None, group_rows=0):
+    """Fused ``[gate|up]`` projection + SwiGLU.
+
+    ``w_gu`` stores gate and up rows interleaved in blocks of 64 (``g0..g63,u0..u63,g64..``) so that one
+    128-column accumulator tile holds matching gate/up columns; ``gu_out`` (optional, same interleaved
+    column order) keeps the pre-activations for backward, ``act_out[m, j] = silu(g_j) * u_j``.
+    With ``tile_expert``/``num_m_tiles`` the rows are expert-sorted and ``w_gu`` stacks ``group_rows`` rows per expert.
+    """
+    M, K = a.shape
+    N = group_rows if group_rows else w_gu.shape[0]
+    if N % 128:
+        raise ValueError("2*E must be a multiple of 128")
+    if act_out is None:
+        act_out = torch.empty(M, N // 2, dtype=a.dtype, device=a.device)
+    g = _base_args(a, w_gu, M, N, K, False, False, act_out, 128)
+    g.epilogue = EPI_SWIGLU_FWD
+    if gu_out is not None:
+        g.aux_out, g.ld_aux = gu_out.data_ptr(), gu_out.stride(0)
+    if tile_expert is not None:
+        g.mode = 1
+        g.tile_expert, g.num_m_tiles = tile_expert.data_ptr(), num_m_tiles.data_ptr()
+        g.b_group_rows = group_rows
+    _launch(g)
+    return act_out
+
+
+def gemm_swiglu_bwd(dy, w_down, gu, *, dgu_out=None, b_mn=True, tile_expert=None, num_m_tiles=None, group_rows=0,
+                    n=None):
+    """``d_act = dy @ W_down`` fused with the SwiGLU derivative: writes interleaved ``(dg, du)``.
+
+    ``w_down`` is the stored ``[d, E]`` matrix (``[ne*d, E]`` when grouped), i.e. B in ``[K, N]`` layout.
+    """
+    M, K = dy.shape
+    N = n if n is not None else (w_down.shape[1] if b_mn else w_down.shape[0])
+    if dgu_out is None:
+        dgu_out = torch.empty(M, 2 * N, dtype=dy.dtype, device=dy.device)
+    g = _base_args(dy, w_down, M, N, K, False, b_mn, dgu_out, 128 if N % 128 == 0 else 64)
+    g.epilogue = EPI_SWIGLU_BWD
+    g.aux_in, g.ld_aux = gu.data_ptr(), gu.stride(0)
+    if tile_expert is not None:
+        g.mode = 1
+        g.tile_expert, g.num_m_tiles = tile_expert.data_ptr(), num_m_tiles.data_ptr()
+        g.b_group_rows = group_rows
+    _launch(g)
+    return dgu_out
+
+
+def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_rows, out=None, out_dtype=None,
+                      block_n=0):
+    """Expert-sorted rows: every 128-row tile of ``a`` multiplies the weight block of ``tile_expert[tile]``.
+
+    ``b`` stacks the per-expert matrices along its rows: ``group_rows`` stored rows per expert.
+    """
+    M, K = a.shape
+    if out is None:
+        out = torch.empty(M, n, dtype=out_dtype or a.dtype, device=a.device)
+    if not block_n:
+        block_n = 128
+    g = _base_args(a, b, M, n, K, False, b_mn, out, block_n)
+    g.epilogue = EPI_STORE
+    g.mode = 1
+    g.tile_expert, g.num_m_tiles = tile_expert.data_ptr(), num_m_tiles.data_ptr()
+    g.b_group_rows = group_rows
+    _launch(g)
+    return out
+
+
+def gemm_grouped_reduce(a, b, seg_offsets, groups, out, *, accumulate=True, block_n=0):
+    """Per-expert weight gradient: ``out[g] (+)= a[rows_g]^T @ b[rows_g]`` with ``rows_g`` given by the padded
+    offsets ``seg_offsets[g] .. seg_offsets[g+1]`` (device int32, multiples of 128; pad rows must be zero).
+    ``a`` is ``[rows, M]``, ``b`` is ``[rows, N]``, ``out`` is fp32 ``[groups, M, N]``.
+    """
+    M, N = a.shape[1], b.shape[1]
+    if out.dtype != torch.float32 or out.shape != (groups, M, N) or not out.is_contiguous():
+        raise ValueError("out must be contiguous fp32 [groups, M, N]")
+    if not block_n:
+        block_n = 128
+    g = _base_args(a, b, M, N, 0, True, True, out, block_n)
+    g.epilogue = EPI_STORE
+    g.mode = 2
+    g.seg_offsets = seg_offsets.data_ptr()
+    g.groups = groups
+    g.out_group_stride = M * N
+    g.ldo = N
+    if accumulate:
+        g.addend, g.ld_add = out.data_ptr(), N
+    _launch(g)
+    return out
+
+
+def interleave_gate_up(gate, up, block=64):
+    """``[.., E, d]`` gate and up -> ``[.., 2E, d]`` with rows interleaved in blocks of ``block``."""
+    *lead, E, d = gate.shape
+    g = gate.reshape(*lead, E // block, 1, block, d)
+    u = up.reshape(*lead, E // block, 1, block, d)
+    return torch.cat([g, u], dim=-3).reshape(*lead, 2 * E, d)
+
+
+def deinterleave_gate_up(gu, block=64):
+    """Inverse of :func:`interleave_gate_up` along the second-to-last dim."""
+    *lead, E2, d = gu.shape
+    v = gu.reshape(*lead, E2 // (2 * block), 2, block, d)
+    return v[..., 0, :, :].reshape(*lead, E2 // 2, d), v[..., 1, :, :].reshape(*lead, E2 // 2, d)
+
+
+def interleave_cols(g, u, block=64):
+    """Column version for activations: ``[M, E]`` x2 -> ``[M, 2E]`` interleaved in blocks of 64."""
+    M, E = g.shape
+    return torch.stack([g.reshape(M, E // block, block), u.reshape(M, E // block, block)], dim=2).reshape(M, 2 * E)
+
+
+def deinterleave_cols(gu, block=64):
+    M, E2 = gu.shape
+    v = gu.reshape(M, E2 // (2 * block), 2, block)
+    return v[:, :, 0, :].reshape(M, E2 // 2), v[:, :, 1, :].reshape(M, E2 // 2)

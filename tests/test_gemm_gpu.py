@@ -1,0 +1,160 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 reference of the same product."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from ghassan_b200.ops import gemm as G, _lib
+    return G, _lib
+
+
+def _close(got, ref, tol=2e-2):
+    got = got.float()
+    ref = ref.float()
+    err = (got - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    return err / scale, err / scale < tol
+
+
+def _rand(*shape, dtype=torch.float16, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * 0.5).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 200, 320), (128, 64, 64), (1024, 768, 512)])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_dense_kmajor(dtype, M, N, K, bn):
+    G, L = _ops()
+    a = _rand(M, K, dtype=dtype, seed=1)
+    b = _rand(N, K, dtype=dtype, seed=2)
+    out = G.gemm(a, b, block_n=bn)
+    L.check_status(what="gemm")
+    rel, ok = _close(out, a.float() @ b.float().t())
+    assert ok, rel
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("bn", [64, 128])
+def test_operand_majors(a_mn, b_mn, bn):
+    G, L = _ops()
+    M, N, K = 384, 320, 448
+    A = _rand(M, K, seed=3)
+    B = _rand(N, K, seed=4)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=bn, out_dtype=torch.float32)
+    L.check_status(what="gemm")
+    rel, ok = _close(out, A.float() @ B.float().t(), tol=5e-3)
+    assert ok, rel
+
+
+def test_fp32_accumulate_and_residual():
+    G, L = _ops()
+    M, N, K = 256, 192, 128
+    a, b = _rand(M, K, seed=5), _rand(N, K, seed=6)
+    acc = torch.randn(M, N, device="cuda")
+    ref = acc + a.float() @ b.float().t()
+    G.gemm(a, b, out=acc, addend=acc)
+    L.check_status(what="gemm")
+    rel, ok = _close(acc, ref, tol=5e-3)
+    assert ok, rel
+    res = torch.randn(M, N, device="cuda")
+    out = G.gemm(a, b, out_dtype=torch.float32, addend=res)
+    rel, ok = _close(out, res + a.float() @ b.float().t(), tol=5e-3)
+    assert ok, rel
+
+
+def test_swiglu_forward_backward_epilogues():
+    G, L = _ops()
+    M, d, E = 200, 256, 192
+    x = _rand(M, d, seed=7)
+    wg, wu = _rand(E, d, seed=8) * 0.2, _rand(E, d, seed=9) * 0.2
+    wgu = G.interleave_gate_up(wg, wu).contiguous()
+    gu = torch.zeros(M, 2 * E, dtype=torch.float16, device="cuda")
+    act = G.gemm_swiglu(x, wgu, gu_out=gu)
+    L.check_status(what="swiglu fwd")
+    g_ref = x.float() @ wg.float().t()
+    u_ref = x.float() @ wu.float().t()
+    a_ref = torch.nn.functional.silu(g_ref) * u_ref
+    g_got, u_got = G.deinterleave_cols(gu)
+    assert _close(g_got, g_ref)[1] and _close(u_got, u_ref)[1]
+    rel, ok = _close(act, a_ref)
+    assert ok, rel
+    # backward: d_act = dy @ W_down ; (dg, du) from saved (g, u)
+    wd = _rand(d, E, seed=10) * 0.2
+    dy = _rand(M, d, seed=11)
+    dgu = G.gemm_swiglu_bwd(dy, wd, gu)
+    L.check_status(what="swiglu bwd")
+    dact = dy.float() @ wd.float()
+    gf, uf = g_got.float(), u_got.float()
+    sg = torch.sigmoid(gf)
+    dg_ref = dact * uf * (sg * (1 + gf * (1 - sg)))
+    du_ref = dact * gf * sg
+    dg, du = G.deinterleave_cols(dgu)
+    assert _close(dg, dg_ref)[1], _close(dg, dg_ref)[0]
+    assert _close(du, du_ref)[1], _close(du, du_ref)[0]
+
+
+def _make_groups(counts):
+    """Padded (128) segment offsets, tile->expert map and live tile count for the given row counts."""
+    offs = [0]
+    tiles = []
+    for e, c in enumerate(counts):
+        pad = (c + 127) // 128 * 128
+        tiles += [e] * (pad // 128)
+        offs.append(offs[-1] + pad)
+    return offs, tiles
+
+
+def test_grouped_rows_and_grouped_reduce():
+    G, L = _ops()
+    counts = [130, 0, 5, 256, 77]
+    ne, d, E = len(counts), 192, 128
+    offs, tiles = _make_groups(counts)
+    rows = offs[-1]
+    x = torch.zeros(rows, d, dtype=torch.float16, device="cuda")
+    for e, c in enumerate(counts):
+        x[offs[e]:offs[e] + c] = _rand(c, d, seed=20 + e) if c else x[0:0]
+    w = _rand(ne * E, d, seed=30) * 0.3            # K-major stacked [ne*E, d]
+    tile_expert = torch.tensor(tiles + [0] * 4, dtype=torch.int32, device="cuda")
+    ntiles = torch.tensor([len(tiles)], dtype=torch.int32, device="cuda")
+    y = G.gemm_grouped_rows(x, w, tile_expert, ntiles, n=E, group_rows=E, out_dtype=torch.float32)
+    L.check_status(what="grouped rows")
+    for e, c in enumerate(counts):
+        if c:
+            ref = x[offs[e]:offs[e] + c].float() @ w[e * E:(e + 1) * E].float().t()
+            rel, ok = _close(y[offs[e]:offs[e] + c], ref, tol=5e-3)
+            assert ok, (e, rel)
+    # N-major stacked B: dgrad dx = y16 @ W_e  with W_e stored [E, d] = [K, N]
+    y16 = torch.zeros(rows, E, dtype=torch.float16, device="cuda")
+    for e, c in enumerate(counts):
+        if c:
+            y16[offs[e]:offs[e] + c] = _rand(c, E, seed=40 + e)
+    dx = G.gemm_grouped_rows(y16, w, tile_expert, ntiles, n=d, b_mn=True, group_rows=E, out_dtype=torch.float32)
+    L.check_status(what="grouped rows N-major")
+    for e, c in enumerate(counts):
+        if c:
+            ref = y16[offs[e]:offs[e] + c].float() @ w[e * E:(e + 1) * E].float()
+            rel, ok = _close(dx[offs[e]:offs[e] + c], ref, tol=5e-3)
+            assert ok, (e, rel)
+    # wgrad: dW_e = y16_e^T @ x_e, accumulated into fp32
+    seg = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    dw = torch.ones(ne, E, d, dtype=torch.float32, device="cuda")
+    G.gemm_grouped_reduce(y16, x, seg, ne, dw, accumulate=True)
+    L.check_status(what="grouped reduce")
+    for e, c in enumerate(counts):
+        ref = 1.0 + y16[offs[e]:offs[e] + c].float().t() @ x[offs[e]:offs[e] + c].float()
+        rel, ok = _close(dw[e], ref, tol=5e-3)
+        assert ok, (e, rel)
+
+
+def test_large_gemm_matches():
+    G, L = _ops()
+    a, b = _rand(4096, 1024, seed=50), _rand(2048, 1024, seed=51)
+    out = G.gemm(a, b, out_dtype=torch.float32)
+    L.check_status(what="gemm")
+    rel, ok = _close(out, a.float() @ b.float().t(), tol=5e-3)
+    assert ok, rel
