@@ -1,0 +1,436 @@
+// Memory-bound model kernels: embedding gather/scatter, RMSNorm forward/backward (with the residual
+// stream kept in fp32 and 16-bit GEMM operands produced in the same pass), QK-norm + RoPE forward/backward.
+// They replace k_embed_*, k_rmsnorm_*, k_rope_freq, k_split_qkv and the add/copy kernels of the reference
+// (cuda/kernels.cu:327-692): the split of the fused QKV output, the per-head norm and the rotation are one
+// pass, residual adds live in GEMM epilogues, and weight-gradient column sums are two-stage and deterministic.
+#include "sm100_common.cuh"
+#include "gb_api.h"
+
+namespace gb {
+
+template <typename T> struct Vec8 { uint4 v; };
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  uint4 q = *reinterpret_cast<const uint4*>(p);
+  float2 a = Cvt<T>::unpack2(q.x), b = Cvt<T>::unpack2(q.y), c = Cvt<T>::unpack2(q.z), d = Cvt<T>::unpack2(q.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
+  uint4 q;
+  q.x = Cvt<T>::pack2(f[0], f[1]); q.y = Cvt<T>::pack2(f[2], f[3]);
+  q.z = Cvt<T>::pack2(f[4], f[5]); q.w = Cvt<T>::pack2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = q;
+}
+
+// ------------------------------------------------------------------------------------------ embedding
+__global__ void embed_fwd_kernel(const int* __restrict__ ids, const float* __restrict__ table, float* __restrict__ out,
+                                 int n_tok, int d, int vocab) {
+  const int t = blockIdx.x;
+  if (t >= n_tok) return;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const float4* src = reinterpret_cast<const float4*>(table + (size_t)id * d);
+  float4* dst = reinterpret_cast<float4*>(out + (size_t)t * d);
+  for (int i = threadIdx.x; i < d / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// dtable[ids[t]] += dx[t]  (fp32 atomics; rows of distinct ids never collide)
+__global__ void embed_bwd_kernel(const int* __restrict__ ids, const float* __restrict__ dx, float* __restrict__ dtable,
+                                 int n_tok, int d, int vocab) {
+  const int t = blockIdx.x;
+  if (t >= n_tok) return;
+  const int id = ids[t];
+  if (id < 0 || id >= vocab) return;
+  const float* src = dx + (size_t)t * d;
+  float* dst = dtable + (size_t)id * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[i]);
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm
+// One warp per row.  y16 = x * inv * w (16-bit), rrms[row] = inv;  inv = 0 when it is not finite.
+template <typename T>
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                                   float* __restrict__ rrms, int rows, int d, float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * d);
+  float ss = 0.f;
+  for (int i = lane; i < d / 4; i += 32) {
+    float4 v = xr[i];
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  float inv = rsqrtf(ss / (float)d + eps);
+  if (!isfinite(inv)) inv = 0.f;
+  if (lane == 0 && rrms) rrms[row] = inv;
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  T* yr = y + (size_t)row * d;
+  for (int i = lane; i < d / 4; i += 32) {
+    float4 v = xr[i], g = wr[i];
+    uint2 o;
+    o.x = Cvt<T>::pack2(v.x * inv * g.x, v.y * inv * g.y);
+    o.y = Cvt<T>::pack2(v.z * inv * g.z, v.w * inv * g.w);
+    *reinterpret_cast<uint2*>(yr + 4 * i) = o;
+  }
+}
+
+// dx_out = dres + g*w*inv - x*inv^3/d * sum(g*w*x);  optional 16-bit copy of dx_out.
+// Also writes this block's column partials of dw (sum over its rows of g*x*inv) to part[blockIdx.x, :].
+template <typename T>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ g, const float* __restrict__ x, const float* __restrict__ w,
+                                   const float* __restrict__ rrms, const float* __restrict__ dres,
+                                   float* __restrict__ dx_out, T* __restrict__ dx16, float* __restrict__ part,
+                                   int rows, int d, int rows_per_block) {
+  extern __shared__ float sm_dw_all[];  // [nwarps][d]: every warp sums its own rows, lanes own distinct columns
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < d * nwarps; i += blockDim.x) sm_dw_all[i] = 0.f;
+  __syncthreads();
+  float* sm_dw = sm_dw_all + (size_t)warp * d;
+  const int row0 = blockIdx.x * rows_per_block;
+  const int row1 = min(rows, row0 + rows_per_block);
+  for (int row = row0 + warp; row < row1; row += nwarps) {
+    const float inv = rrms[row];
+    const float* xr = x + (size_t)row * d;
+    const T* gr = g + (size_t)row * d;
+    float dot = 0.f;
+    for (int i = lane * 4; i < d; i += 128) {
+      float4 xv = *reinterpret_cast<const float4*>(xr + i);
+      float4 wv = *reinterpret_cast<const float4*>(w + i);
+      uint2 gq = *reinterpret_cast<const uint2*>(gr + i);
+      float2 g01 = Cvt<T>::unpack2(gq.x), g23 = Cvt<T>::unpack2(gq.y);
+      dot += g01.x * wv.x * xv.x + g01.y * wv.y * xv.y + g23.x * wv.z * xv.z + g23.y * wv.w * xv.w;
+    }
+    dot = warp_sum(dot);
+    const float coef = inv * inv * inv * dot / (float)d;
+    for (int i = lane * 4; i < d; i += 128) {
+      float4 xv = *reinterpret_cast<const float4*>(xr + i);
+      float4 wv = *reinterpret_cast<const float4*>(w + i);
+      uint2 gq = *reinterpret_cast<const uint2*>(gr + i);
+      float2 g01 = Cvt<T>::unpack2(gq.x), g23 = Cvt<T>::unpack2(gq.y);
+      float4 r = dres ? *reinterpret_cast<const float4*>(dres + (size_t)row * d + i) : make_float4(0, 0, 0, 0);
+      float4 o;
+      o.x = r.x + g01.x * wv.x * inv - xv.x * coef;
+      o.y = r.y + g01.y * wv.y * inv - xv.y * coef;
+      o.z = r.z + g23.x * wv.z * inv - xv.z * coef;
+      o.w = r.w + g23.y * wv.w * inv - xv.w * coef;
+      *reinterpret_cast<float4*>(dx_out + (size_t)row * d + i) = o;
+      if (dx16) {
+        uint2 q;
+        q.x = Cvt<T>::pack2(o.x, o.y);
+        q.y = Cvt<T>::pack2(o.z, o.w);
+        *reinterpret_cast<uint2*>(dx16 + (size_t)row * d + i) = q;
+      }
+      sm_dw[i + 0] += g01.x * xv.x * inv;
+      sm_dw[i + 1] += g01.y * xv.y * inv;
+      sm_dw[i + 2] += g23.x * xv.z * inv;
+      sm_dw[i + 3] += g23.y * xv.w * inv;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float s = 0.f;
+    for (int wv = 0; wv < nwarps; ++wv) s += sm_dw_all[(size_t)wv * d + i];
+    part[(size_t)blockIdx.x * d + i] = s;
+  }
+}
+
+// dw[c] += sum_b part[b, c]
+__global__ void colsum_finalize_kernel(const float* __restrict__ part, float* __restrict__ dw, int nblocks, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * d + c];
+  dw[c] += s;
+}
+
+// ------------------------------------------------------------------------------------------ QK-norm + RoPE
+// qkv: [N, ld_in] fused GEMM output (q heads, then k heads, then v heads).  One warp per (token, head) for the
+// q and k heads: optional RMSNorm over head_dim with a shared [hd] weight, then rotation by the cached
+// cos/sin of the row position.  rope_type 0 rotates (2i, 2i+1), 1 rotates (i, i + hd/2).
+template <typename T, int HD>
+__global__ void qk_norm_rope_fwd_kernel(const T* __restrict__ qkv, int ld_in, T* __restrict__ out, int ld_out,
+                                        const float* __restrict__ qw, const float* __restrict__ kw,
+                                        const float* __restrict__ cs, const int* __restrict__ pos, int n_tok, int H,
+                                        int KV, float eps, int rope_type) {
+  constexpr int PAIRS = HD / 2;
+  constexpr int PPL = (PAIRS + 31) / 32;  // pairs per lane
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = H + KV;
+  if (gw >= n_tok * heads) return;
+  const int t = gw / heads, h = gw - t * heads;
+  const T* src = qkv + (size_t)t * ld_in + (size_t)h * HD;
+  T* dst = out + (size_t)t * ld_out + (size_t)h * HD;
+  const float* w = (h < H) ? qw : kw;
+  float a[PPL], b[PPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PPL; ++k) {
+    const int p = lane + 32 * k;
+    if (p < PAIRS) {
+      const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+      a[k] = Cvt<T>::to_f(src[i0]);
+      b[k] = Cvt<T>::to_f(src[i1]);
+      ss += a[k] * a[k] + b[k] * b[k];
+    }
+  }
+  float inv = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)HD + eps);
+    if (!isfinite(inv)) inv = 0.f;
+  }
+  const float* csr = cs + (size_t)pos[t] * HD;  // [pos][PAIRS cos | PAIRS sin]
+#pragma unroll
+  for (int k = 0; k < PPL; ++k) {
+    const int p = lane + 32 * k;
+    if (p < PAIRS) {
+      const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+      float x0 = a[k], x1 = b[k];
+      if (w) { x0 *= inv * w[i0]; x1 *= inv * w[i1]; }
+      const float c = csr[p], s = csr[PAIRS + p];
+      dst[i0] = Cvt<T>::from_f(x0 * c - x1 * s);
+      dst[i1] = Cvt<T>::from_f(x0 * s + x1 * c);
+    }
+  }
+}
+
+// Backward: dq_r/dk_r (grads after rotation) -> grads of the raw projections, written into dqkv (q and k parts).
+// Per-block partials of the norm-weight grads go to part_q / part_k ([gridDim.x, HD]).
+template <typename T, int HD>
+__global__ void qk_norm_rope_bwd_kernel(const T* __restrict__ dout, int ld_dout, const T* __restrict__ qkv, int ld_in,
+                                        T* __restrict__ dqkv, int ld_dqkv, const float* __restrict__ qw,
+                                        const float* __restrict__ kw, const float* __restrict__ cs,
+                                        const int* __restrict__ pos, float* __restrict__ part_q,
+                                        float* __restrict__ part_k, int n_tok, int H, int KV, float eps, int rope_type,
+                                        int items_per_block) {
+  constexpr int PAIRS = HD / 2;
+  constexpr int PPL = (PAIRS + 31) / 32;
+  __shared__ float s_dwq_all[8][HD], s_dwk_all[8][HD];  // launched with 8 warps; each warp sums its own items
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < 8 * HD; i += blockDim.x) { (&s_dwq_all[0][0])[i] = 0.f; (&s_dwk_all[0][0])[i] = 0.f; }
+  __syncthreads();
+  float* s_dwq = s_dwq_all[warp];
+  float* s_dwk = s_dwk_all[warp];
+  const int heads = H + KV;
+  const int total = n_tok * heads;
+  const int it0 = blockIdx.x * items_per_block, it1 = min(total, it0 + items_per_block);
+  for (int item = it0 + warp; item < it1; item += nwarps) {
+    const int t = item / heads, h = item - t * heads;
+    const T* gsrc = dout + (size_t)t * ld_dout + (size_t)h * HD;
+    const T* raw = qkv + (size_t)t * ld_in + (size_t)h * HD;
+    T* dst = dqkv + (size_t)t * ld_dqkv + (size_t)h * HD;
+    const float* w = (h < H) ? qw : kw;
+    float* sdw = (h < H) ? s_dwq : s_dwk;
+    const float* csr = cs + (size_t)pos[t] * HD;
+    float g0[PPL], g1[PPL], x0[PPL], x1[PPL];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < PPL; ++k) {
+      const int p = lane + 32 * k;
+      if (p < PAIRS) {
+        const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+        const float c = csr[p], s = csr[PAIRS + p];
+        const float d0 = Cvt<T>::to_f(gsrc[i0]), d1 = Cvt<T>::to_f(gsrc[i1]);
+        g0[k] = d0 * c + d1 * s;    // inverse rotation
+        g1[k] = -d0 * s + d1 * c;
+        if (w) {
+          x0[k] = Cvt<T>::to_f(raw[i0]);
+          x1[k] = Cvt<T>::to_f(raw[i1]);
+          ss += x0[k] * x0[k] + x1[k] * x1[k];
+          dot += g0[k] * w[i0] * x0[k] + g1[k] * w[i1] * x1[k];
+        }
+      }
+    }
+    if (!w) {
+#pragma unroll
+      for (int k = 0; k < PPL; ++k) {
+        const int p = lane + 32 * k;
+        if (p < PAIRS) {
+          const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+          dst[i0] = Cvt<T>::from_f(g0[k]);
+          dst[i1] = Cvt<T>::from_f(g1[k]);
+        }
+      }
+      continue;
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    float inv = rsqrtf(ss / (float)HD + eps);
+    if (!isfinite(inv)) inv = 0.f;
+    const float coef = inv * inv * inv * dot / (float)HD;
+#pragma unroll
+    for (int k = 0; k < PPL; ++k) {
+      const int p = lane + 32 * k;
+      if (p < PAIRS) {
+        const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+        dst[i0] = Cvt<T>::from_f(g0[k] * w[i0] * inv - x0[k] * coef);
+        dst[i1] = Cvt<T>::from_f(g1[k] * w[i1] * inv - x1[k] * coef);
+        sdw[i0] += g0[k] * x0[k] * inv;
+        sdw[i1] += g1[k] * x1[k] * inv;
+      }
+    }
+  }
+  __syncthreads();
+  if (part_q)
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+      float sq = 0.f, sk = 0.f;
+      for (int wv = 0; wv < nwarps; ++wv) { sq += s_dwq_all[wv][i]; sk += s_dwk_all[wv][i]; }
+      part_q[(size_t)blockIdx.x * HD + i] = sq;
+      part_k[(size_t)blockIdx.x * HD + i] = sk;
+    }
+}
+
+// ------------------------------------------------------------------------------------------ casts / fills
+template <typename T>
+__global__ void cast_f32_to_16_kernel(const float* __restrict__ src, T* __restrict__ dst, long long n) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (; i + 8 <= n; i += stride) {
+    float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + 4);
+    float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    store8<T>(dst + i, f);
+  }
+  if (i < n && i + 8 > n)
+    for (long long j = i; j < n; ++j) dst[j] = Cvt<T>::from_f(src[j]);
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+#define GB_LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+
+extern "C" int gb_embed_fwd(const int* ids, const float* table, float* out, int n_tok, int d, int vocab, cudaStream_t st) {
+  if (d % 4) return -1;
+  embed_fwd_kernel<<<n_tok, 128, 0, st>>>(ids, table, out, n_tok, d, vocab);
+  return GB_LAUNCH_OK();
+}
+extern "C" int gb_embed_bwd(const int* ids, const float* dx, float* dtable, int n_tok, int d, int vocab, cudaStream_t st) {
+  embed_bwd_kernel<<<n_tok, 128, 0, st>>>(ids, dx, dtable, n_tok, d, vocab);
+  return GB_LAUNCH_OK();
+}
+
+extern "C" int gb_rmsnorm_fwd(const float* x, const float* w, void* y, float* rrms, int rows, int d, float eps, int is_bf16,
+                              cudaStream_t st) {
+  if (d % 4) return -1;
+  const int wpb = 8;
+  dim3 grid((rows + wpb - 1) / wpb);
+  if (is_bf16) rmsnorm_fwd_kernel<__nv_bfloat16><<<grid, wpb * 32, 0, st>>>(x, w, (__nv_bfloat16*)y, rrms, rows, d, eps);
+  else rmsnorm_fwd_kernel<__half><<<grid, wpb * 32, 0, st>>>(x, w, (__half*)y, rrms, rows, d, eps);
+  return GB_LAUNCH_OK();
+}
+
+// Number of row blocks (and rows of the partial buffer) gb_rmsnorm_bwd uses for `rows`.
+extern "C" int gb_rmsnorm_bwd_blocks(int rows) {
+  int b = (rows + 63) / 64;
+  return b > 592 ? 592 : (b < 1 ? 1 : b);
+}
+
+// dw (fp32 [d]) is accumulated (+=).  `part` must hold gb_rmsnorm_bwd_blocks(rows) * d floats.
+// Column sums are formed per warp, then per block, then block by block in index order: the result is
+// bit-reproducible from run to run.
+extern "C" int gb_rmsnorm_bwd(const void* g, const float* x, const float* w, const float* rrms, const float* dres,
+                              float* dx_out, void* dx16, float* part, float* dw, int rows, int d, int is_bf16,
+                              cudaStream_t st) {
+  if (d % 4) return -1;
+  const int nb = gb_rmsnorm_bwd_blocks(rows);
+  const int rpb = (rows + nb - 1) / nb;
+  int wpb = 12288 / d;
+  wpb = wpb > 8 ? 8 : wpb;
+  if (wpb < 1) return -1;
+  const size_t smem = (size_t)d * wpb * sizeof(float);
+  const int threads = wpb * 32;
+  if (is_bf16)
+    rmsnorm_bwd_kernel<__nv_bfloat16><<<nb, threads, smem, st>>>((const __nv_bfloat16*)g, x, w, rrms, dres, dx_out,
+                                                             (__nv_bfloat16*)dx16, part, rows, d, rpb);
+  else
+    rmsnorm_bwd_kernel<__half><<<nb, threads, smem, st>>>((const __half*)g, x, w, rrms, dres, dx_out, (__half*)dx16, part,
+                                                      rows, d, rpb);
+  if (dw) colsum_finalize_kernel<<<(d + 255) / 256, 256, 0, st>>>(part, dw, nb, d);
+  return GB_LAUNCH_OK();
+}
+
+extern "C" int gb_qk_rope_blocks(int n_items) {
+  int b = (n_items + 255) / 256;
+  return b > 592 ? 592 : (b < 1 ? 1 : b);
+}
+
+template <typename T>
+static int qk_fwd_t(const void* qkv, int ld_in, void* out, int ld_out, const float* qw, const float* kw, const float* cs,
+                    const int* pos, int n_tok, int H, int KV, int hd, float eps, int rope_type, cudaStream_t st) {
+  const int items = n_tok * (H + KV);
+  const int wpb = 8;
+  dim3 grid((items + wpb - 1) / wpb);
+#define GB_QK_FWD(HD) \
+  qk_norm_rope_fwd_kernel<T, HD><<<grid, wpb * 32, 0, st>>>((const T*)qkv, ld_in, (T*)out, ld_out, qw, kw, cs, pos, n_tok, H, KV, eps, rope_type)
+  switch (hd) {
+    case 32: GB_QK_FWD(32); break;
+    case 64: GB_QK_FWD(64); break;
+    case 96: GB_QK_FWD(96); break;
+    case 128: GB_QK_FWD(128); break;
+    case 256: GB_QK_FWD(256); break;
+    default: return -1;
+  }
+#undef GB_QK_FWD
+  return GB_LAUNCH_OK();
+}
+
+extern "C" int gb_qk_norm_rope_fwd(const void* qkv, int ld_in, void* out, int ld_out, const float* qw, const float* kw,
+                                   const float* cos_sin, const int* pos, int n_tok, int H, int KV, int hd, float eps,
+                                   int rope_type, int is_bf16, cudaStream_t st) {
+  return is_bf16 ? qk_fwd_t<__nv_bfloat16>(qkv, ld_in, out, ld_out, qw, kw, cos_sin, pos, n_tok, H, KV, hd, eps, rope_type, st)
+                 : qk_fwd_t<__half>(qkv, ld_in, out, ld_out, qw, kw, cos_sin, pos, n_tok, H, KV, hd, eps, rope_type, st);
+}
+
+template <typename T>
+static int qk_bwd_t(const void* dout, int ld_dout, const void* qkv, int ld_in, void* dqkv, int ld_dqkv, const float* qw,
+                    const float* kw, const float* cs, const int* pos, float* part, float* dqw, float* dkw, int n_tok,
+                    int H, int KV, int hd, float eps, int rope_type, cudaStream_t st) {
+  const int items = n_tok * (H + KV);
+  const int nb = gb_qk_rope_blocks(items);
+  const int ipb = (items + nb - 1) / nb;
+  float* pq = part;
+  float* pk = part ? part + (size_t)nb * hd : nullptr;
+#define GB_QK_BWD(HD)                                                                                                 \
+  qk_norm_rope_bwd_kernel<T, HD><<<nb, 256, 0, st>>>((const T*)dout, ld_dout, (const T*)qkv, ld_in, (T*)dqkv, ld_dqkv, \
+                                                     qw, kw, cs, pos, pq, pk, n_tok, H, KV, eps, rope_type, ipb)
+  switch (hd) {
+    case 32: GB_QK_BWD(32); break;
+    case 64: GB_QK_BWD(64); break;
+    case 96: GB_QK_BWD(96); break;
+    case 128: GB_QK_BWD(128); break;
+    case 256: GB_QK_BWD(256); break;
+    default: return -1;
+  }
+#undef GB_QK_BWD
+  if (qw && part && dqw) {
+    colsum_finalize_kernel<<<1, 256, 0, st>>>(pq, dqw, nb, hd);
+    colsum_finalize_kernel<<<1, 256, 0, st>>>(pk, dkw, nb, hd);
+  }
+  return GB_LAUNCH_OK();
+}
+
+// part: 2 * gb_qk_rope_blocks(n_tok*(H+KV)) * hd floats; dqw/dkw ([hd], fp32) are accumulated.
+extern "C" int gb_qk_norm_rope_bwd(const void* dout, int ld_dout, const void* qkv, int ld_in, void* dqkv, int ld_dqkv,
+                                   const float* qw, const float* kw, const float* cos_sin, const int* pos, float* part,
+                                   float* dqw, float* dkw, int n_tok, int H, int KV, int hd, float eps, int rope_type,
+                                   int is_bf16, cudaStream_t st) {
+  return is_bf16 ? qk_bwd_t<__nv_bfloat16>(dout, ld_dout, qkv, ld_in, dqkv, ld_dqkv, qw, kw, cos_sin, pos, part, dqw, dkw,
+                                           n_tok, H, KV, hd, eps, rope_type, st)
+                 : qk_bwd_t<__half>(dout, ld_dout, qkv, ld_in, dqkv, ld_dqkv, qw, kw, cos_sin, pos, part, dqw, dkw, n_tok,
+                                    H, KV, hd, eps, rope_type, st);
+}
+
+extern "C" int gb_cast_f32_to_16(const float* src, void* dst, long long n, int is_bf16, cudaStream_t st) {
+  if (n <= 0) return 0;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  if (is_bf16) cast_f32_to_16_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(src, (__nv_bfloat16*)dst, n);
+  else cast_f32_to_16_kernel<__half><<<(int)blocks, 256, 0, st>>>(src, (__half*)dst, n);
+  return GB_LAUNCH_OK();
+}

@@ -1,0 +1,474 @@
+// Mixture-of-experts routing and data movement around the grouped tcgen05 GEMMs.
+//
+//   route    : router logits (fp32 weights) + jitter hash + softmax + bias-on-selection top-k (ties -> lowest
+//              index) + renormalised combine weights + per-block expert histograms       (one warp per token)
+//   group    : device-side scan -> 128-row padded expert segments, tile->expert map, stable (token-order) row
+//              positions, expert-sorted 16-bit copy of the activations; no host synchronisation anywhere
+//   combine  : out = resid + shared(x) + sum_k w_k * y_k   gathered per token (deterministic, no atomics)
+//   backward : weighted scatter of d(out) into sorted order, per-slot <d(out), y_k> for the router gradient,
+//              softmax-Jacobian with top-k renormalisation (+ aux-loss term, + jitter), d(router weights)
+// The semantics are the reference's (core/ops_cpu_moe.cpp:182-379, cuda/moe.cu:113-258, 601-970); the
+// structure is not: the reference syncs the host once per layer per pass to read group offsets and loops
+// over experts with one cuBLAS call each.
+#include "sm100_common.cuh"
+#include "gb_api.h"
+
+namespace gb {
+
+constexpr int BLK_TOK = 256;   // tokens per routing block
+constexpr int MAX_NE = 64;
+constexpr int MAX_K = 8;
+
+__device__ __forceinline__ float jitter_u(long long t, int e, unsigned long long seed) {
+  unsigned long long h = (unsigned long long)t * 0x9E3779B97F4A7C15ULL;
+  h ^= (unsigned long long)e * 0xC2B2AE3D27D4EB4FULL;
+  h ^= (seed + 0x9E3779B97F4A7C15ULL);
+  h ^= h >> 33; h *= 0xff51afd7ed558ccdULL;
+  h ^= h >> 33; h *= 0xc4ceb9fe1a85ec53ULL;
+  h ^= h >> 33;
+  return (float)((h >> 40) & 0xFFFFFF) / (float)(1 << 24) - 0.5f;
+}
+
+// (value, index) arg-max over the warp; equal values keep the lower index
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
+  __shared__ int s_hist[MAX_NE + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ne = a.ne, K = a.top_k, d = a.d;
+  for (int i = threadIdx.x; i <= ne; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const int t0 = blockIdx.x * BLK_TOK;
+  const int t1 = min(a.n_tok, t0 + BLK_TOK);
+  const T* x16 = reinterpret_cast<const T*>(a.x16);
+  for (int t = t0 + warp; t < t1; t += 8) {
+    const T* xr = x16 + (size_t)t * d;
+    // lane holds the logits of experts `lane` and `lane + 32`
+    float l0 = -INFINITY, l1 = -INFINITY;
+    for (int e = 0; e < ne; ++e) {
+      const float* wr = a.router_w + (size_t)e * d;
+      float s = 0.f;
+      for (int i = lane * 2; i < d; i += 64) {
+        const float2 xv = Cvt<T>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
+        const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+        s += xv.x * wv.x + xv.y * wv.y;
+      }
+      s = warp_sum(s);
+      if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, a.jitter_seed);
+      if (e == lane) l0 = s;
+      if (e == lane + 32) l1 = s;
+    }
+    const float mx = warp_max(fmaxf(l0, l1));
+    const float e0 = lane < ne ? __expf(l0 - mx) : 0.f;
+    const float e1 = lane + 32 < ne ? __expf(l1 - mx) : 0.f;
+    const float inv = 1.f / warp_sum(e0 + e1);
+    const float p0 = e0 * inv, p1 = e1 * inv;
+    if (lane < ne) a.probs[(size_t)t * ne + lane] = p0;
+    if (lane + 32 < ne) a.probs[(size_t)t * ne + lane + 32] = p1;
+    float s0 = lane < ne ? p0 + (a.bias ? a.bias[lane] : 0.f) : -INFINITY;
+    float s1 = lane + 32 < ne ? p1 + (a.bias ? a.bias[lane + 32] : 0.f) : -INFINITY;
+    float psel[MAX_K];
+    int esel[MAX_K];
+    float psum = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAX_K; ++k) {
+      if (k < K) {
+        float bv = s0; int bi = lane;
+        if (s1 > bv) { bv = s1; bi = lane + 32; }
+        if (bv == -INFINITY) bi = 1 << 20;   // exhausted lanes never win a tie
+        warp_argmax(bv, bi);
+        esel[k] = bi;
+        const float pw = __shfl_sync(0xffffffffu, bi < 32 ? p0 : p1, bi & 31);
+        psel[k] = pw;
+        psum += pw;
+        if (bi == lane) s0 = -INFINITY;
+        if (bi == lane + 32) s1 = -INFINITY;
+      }
+    }
+    const float invs = psum > 1e-8f ? 1.f / psum : 0.f;
+    if (lane == 0) {
+#pragma unroll
+      for (int k = 0; k < MAX_K; ++k)
+        if (k < K) {
+          a.idx[(size_t)t * K + k] = esel[k];
+          a.w[(size_t)t * K + k] = psel[k] * invs;
+          atomicAdd(&s_hist[esel[k]], 1);
+        }
+      if (a.shared) atomicAdd(&s_hist[ne], 1);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= ne; i += blockDim.x) a.block_hist[(size_t)blockIdx.x * (ne + 1) + i] = s_hist[i];
+}
+
+// Single block.  Totals, padded offsets, per-block bases, tile map, balance statistics.
+__global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks) {
+  __shared__ int s_total[MAX_NE + 1];
+  __shared__ int s_off[MAX_NE + 2];
+  const int ne1 = a.ne + (a.shared ? 1 : 0);
+  const int stride = a.ne + 1;
+  const int e = threadIdx.x;
+  if (e < ne1) {
+    int run = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+      const int c = a.block_hist[(size_t)b * stride + e];
+      a.block_base[(size_t)b * stride + e] = run;   // relative for now
+      run += c;
+    }
+    s_total[e] = run;
+    a.block_base[(size_t)n_blocks * stride + e] = run;  // last row: totals
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int i = 0; i < ne1; ++i) {
+      s_off[i] = off;
+      off += (s_total[i] + 127) / 128 * 128;
+    }
+    s_off[ne1] = off;
+    for (int i = 0; i <= ne1; ++i) a.seg_offsets[i] = s_off[i];
+    if (!a.shared) a.seg_offsets[a.ne + 1] = off;
+    a.num_tiles[0] = off / 128;
+  }
+  __syncthreads();
+  if (e < ne1) {
+    for (int b = 0; b < n_blocks; ++b) a.block_base[(size_t)b * stride + e] += s_off[e];
+    for (int tle = s_off[e] / 128; tle < s_off[e + 1] / 128; ++tle) a.tile_expert[tle] = e;
+  }
+  if (e < a.ne) {
+    if (a.counts) a.counts[e] += (float)s_total[e];
+    if (a.f_frac) a.f_frac[e] = (float)s_total[e] / (float)((long long)a.n_tok * a.top_k);
+  }
+}
+
+// mean_t probs[t, e] -> aux_m[e]; one block per expert, fixed-order tree reduction
+__global__ void moe_colmean_kernel(const float* __restrict__ probs, float* __restrict__ out, int n_tok, int ne) {
+  __shared__ float s[256];
+  const int e = blockIdx.x;
+  float acc = 0.f;
+  for (int t = threadIdx.x; t < n_tok; t += 256) acc += probs[(size_t)t * ne + e];
+  s[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[e] = s[0] / (float)n_tok;
+}
+
+// Row positions (stable: token order inside every expert) and the expert-sorted copy.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_pack_kernel(const gb_moe_args a) {
+  __shared__ int s_idx[BLK_TOK * MAX_K];
+  __shared__ int s_pos[BLK_TOK * (MAX_K + 1)];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
+  const int t0 = blockIdx.x * BLK_TOK;
+  const int nt = min(a.n_tok, t0 + BLK_TOK) - t0;
+  for (int i = threadIdx.x; i < nt * K; i += blockDim.x) s_idx[i] = a.idx[(size_t)t0 * K + i];
+  __syncthreads();
+  const int* base = a.block_base + (size_t)blockIdx.x * (ne + 1);
+  for (int e = warp; e < ne; e += 8) {
+    int run = base[e];
+    for (int c = 0; c < nt; c += 32) {
+      const int tl = c + lane;
+      int k_hit = -1;
+      if (tl < nt)
+        for (int k = 0; k < K; ++k)
+          if (s_idx[tl * K + k] == e) k_hit = k;
+      const unsigned bal = __ballot_sync(0xffffffffu, k_hit >= 0);
+      if (k_hit >= 0) s_pos[tl * S + k_hit] = run + __popc(bal & ((1u << lane) - 1));
+      run += __popc(bal);
+    }
+  }
+  if (a.shared)
+    for (int tl = threadIdx.x; tl < nt; tl += blockDim.x) s_pos[tl * S + K] = base[ne] + tl;
+  __syncthreads();
+  for (int i = threadIdx.x; i < nt * S; i += blockDim.x) a.slot_pos[(size_t)t0 * S + i] = s_pos[i];
+  const T* x16 = reinterpret_cast<const T*>(a.x16);
+  T* xp = reinterpret_cast<T*>(a.x_perm);
+  const int vec = d / 8;
+  for (int tl = warp; tl < nt; tl += 8) {
+    const uint4* src = reinterpret_cast<const uint4*>(x16 + (size_t)(t0 + tl) * d);
+    for (int i = lane; i < vec; i += 32) {
+      const uint4 v = src[i];
+      for (int s = 0; s < S; ++s) reinterpret_cast<uint4*>(xp + (size_t)s_pos[tl * S + s] * d)[i] = v;
+    }
+  }
+}
+
+// zero rows [seg_off[e] + total[e], seg_off[e+1]) of a sorted 16-bit buffer
+template <typename T>
+__global__ void moe_zero_pads_kernel(T* __restrict__ buf, const int* __restrict__ seg_offsets,
+                                     const int* __restrict__ totals, int d) {
+  const int e = blockIdx.x;
+  const int r0 = seg_offsets[e] + totals[e], r1 = seg_offsets[e + 1];
+  const int vec = d / 8;
+  for (int i = threadIdx.x; i < (r1 - r0) * vec; i += blockDim.x)
+    reinterpret_cast<uint4*>(buf + (size_t)r0 * d)[i] = make_uint4(0, 0, 0, 0);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const gb_moe_args a) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= a.n_tok) return;
+  const int K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
+  const T* y = reinterpret_cast<const T*>(a.y_perm);
+  int pos[MAX_K + 1];
+  float w[MAX_K + 1];
+#pragma unroll
+  for (int s = 0; s <= MAX_K; ++s)
+    if (s < S) {
+      pos[s] = a.slot_pos[(size_t)t * S + s];
+      w[s] = s < K ? a.w[(size_t)t * K + s] : 1.f;
+    }
+  for (int i = lane * 8; i < d; i += 256) {
+    float acc[8];
+    if (a.resid) {
+      const float4 r0 = *reinterpret_cast<const float4*>(a.resid + (size_t)t * d + i);
+      const float4 r1 = *reinterpret_cast<const float4*>(a.resid + (size_t)t * d + i + 4);
+      acc[0] = r0.x; acc[1] = r0.y; acc[2] = r0.z; acc[3] = r0.w; acc[4] = r1.x; acc[5] = r1.y; acc[6] = r1.z; acc[7] = r1.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+#pragma unroll
+    for (int s = 0; s <= MAX_K; ++s)
+      if (s < S) {
+        const uint4 q = *reinterpret_cast<const uint4*>(y + (size_t)pos[s] * d + i);
+        const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+        acc[0] += w[s] * v0.x; acc[1] += w[s] * v0.y; acc[2] += w[s] * v1.x; acc[3] += w[s] * v1.y;
+        acc[4] += w[s] * v2.x; acc[5] += w[s] * v2.y; acc[6] += w[s] * v3.x; acc[7] += w[s] * v3.y;
+      }
+    *reinterpret_cast<float4*>(a.out + (size_t)t * d + i) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(a.out + (size_t)t * d + i + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
+// dy_perm[pos(t,k)] = w_k * dout[t]; dy_perm[pos(t,shared)] = dout[t]; gdot[t,k] = <dout[t], y_perm[pos(t,k)]>
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const gb_moe_args a) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= a.n_tok) return;
+  const int K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
+  const T* y = reinterpret_cast<const T*>(a.y_perm);
+  T* dy = reinterpret_cast<T*>(a.dy_perm);
+  int pos[MAX_K + 1];
+  float w[MAX_K + 1], dot[MAX_K];
+#pragma unroll
+  for (int s = 0; s <= MAX_K; ++s)
+    if (s < S) {
+      pos[s] = a.slot_pos[(size_t)t * S + s];
+      w[s] = s < K ? a.w[(size_t)t * K + s] : 1.f;
+    }
+#pragma unroll
+  for (int k = 0; k < MAX_K; ++k) dot[k] = 0.f;
+  for (int i = lane * 8; i < d; i += 256) {
+    const float4 g0 = *reinterpret_cast<const float4*>(a.dout + (size_t)t * d + i);
+    const float4 g1 = *reinterpret_cast<const float4*>(a.dout + (size_t)t * d + i + 4);
+    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+    for (int s = 0; s <= MAX_K; ++s)
+      if (s < S) {
+        if (s < K) {
+          const uint4 q = *reinterpret_cast<const uint4*>(y + (size_t)pos[s] * d + i);
+          const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+          dot[s] += g[0] * v0.x + g[1] * v0.y + g[2] * v1.x + g[3] * v1.y + g[4] * v2.x + g[5] * v2.y + g[6] * v3.x + g[7] * v3.y;
+        }
+        uint4 o;
+        o.x = Cvt<T>::pack2(w[s] * g[0], w[s] * g[1]); o.y = Cvt<T>::pack2(w[s] * g[2], w[s] * g[3]);
+        o.z = Cvt<T>::pack2(w[s] * g[4], w[s] * g[5]); o.w = Cvt<T>::pack2(w[s] * g[6], w[s] * g[7]);
+        *reinterpret_cast<uint4*>(dy + (size_t)pos[s] * d + i) = o;
+      }
+  }
+#pragma unroll
+  for (int k = 0; k < MAX_K; ++k)
+    if (k < K) {
+      const float s = warp_sum(dot[k]);
+      if (lane == 0) a.gdot[(size_t)t * K + k] = s;
+    }
+}
+
+// Per token: sum the sorted-order input gradients of its slots, add the router path, write 16-bit dx and the
+// router-logit gradients (into `part`, [n_tok, ne]).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= a.n_tok) return;
+  const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
+  // ---- router-logit gradient (lane e and e+32 hold expert e / e+32)
+  const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
+  const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
+  float dp0 = 0.f, dp1 = 0.f;
+  if (a.f_frac && a.aux_coef != 0.f) {
+    if (lane < ne) dp0 = a.aux_coef * a.f_frac[lane];
+    if (lane + 32 < ne) dp1 = a.aux_coef * a.f_frac[lane + 32];
+  }
+  float ssum = 0.f, gbar = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int e = a.idx[(size_t)t * K + k];
+    const float pe = a.probs[(size_t)t * ne + e];
+    ssum += pe;
+    gbar += a.gdot[(size_t)t * K + k] * a.w[(size_t)t * K + k];
+  }
+  if (ssum > 1e-8f) {
+    const float invs = 1.f / ssum;
+    for (int k = 0; k < K; ++k) {
+      const int e = a.idx[(size_t)t * K + k];
+      const float v = (a.gdot[(size_t)t * K + k] - gbar) * invs;
+      if (e == lane) dp0 += v;
+      if (e == lane + 32) dp1 += v;
+    }
+  }
+  const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
+  float dl0 = p0 * (dp0 - pdp), dl1 = p1 * (dp1 - pdp);
+  if (a.use_jitter) {
+    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane, a.jitter_seed);
+    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane + 32, a.jitter_seed);
+  }
+  if (lane < ne) a.part[(size_t)t * ne + lane] = dl0;
+  if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1;
+  // ---- input gradient
+  const T* dxp = reinterpret_cast<const T*>(a.dx_perm);
+  T* dx = reinterpret_cast<T*>(a.dx16);
+  int pos[MAX_K + 1];
+#pragma unroll
+  for (int s = 0; s <= MAX_K; ++s)
+    if (s < S) pos[s] = a.slot_pos[(size_t)t * S + s];
+  for (int i = lane * 8; i < d; i += 256) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int s = 0; s <= MAX_K; ++s)
+      if (s < S) {
+        const uint4 q = *reinterpret_cast<const uint4*>(dxp + (size_t)pos[s] * d + i);
+        const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+        acc[0] += v0.x; acc[1] += v0.y; acc[2] += v1.x; acc[3] += v1.y; acc[4] += v2.x; acc[5] += v2.y; acc[6] += v3.x; acc[7] += v3.y;
+      }
+    for (int e = 0; e < ne; ++e) {
+      const float dl = __shfl_sync(0xffffffffu, e < 32 ? dl0 : dl1, e & 31);
+      const float4 w0 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i);
+      const float4 w1 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i + 4);
+      acc[0] += dl * w0.x; acc[1] += dl * w0.y; acc[2] += dl * w0.z; acc[3] += dl * w0.w;
+      acc[4] += dl * w1.x; acc[5] += dl * w1.y; acc[6] += dl * w1.z; acc[7] += dl * w1.w;
+    }
+    uint4 o;
+    o.x = Cvt<T>::pack2(acc[0], acc[1]); o.y = Cvt<T>::pack2(acc[2], acc[3]);
+    o.z = Cvt<T>::pack2(acc[4], acc[5]); o.w = Cvt<T>::pack2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(dx + (size_t)t * d + i) = o;
+  }
+}
+
+// d_router_w[e, c] += sum_t dlogit[t, e] * x16[t, c]   (sequential over t per thread: deterministic)
+template <typename T>
+__global__ void moe_router_wgrad_kernel(const float* __restrict__ dlogit, const T* __restrict__ x16,
+                                        float* __restrict__ dw, int n_tok, int ne, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int e = blockIdx.y;
+  if (c >= d) return;
+  float acc = 0.f;
+  for (int t = 0; t < n_tok; ++t) acc += dlogit[(size_t)t * ne + e] * Cvt<T>::to_f(x16[(size_t)t * d + c]);
+  dw[(size_t)e * d + c] += acc;
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+static int moe_check(const gb_moe_args* a) {
+  if (!a || a->n_tok <= 0 || a->d <= 0 || a->d % 8) return -1;
+  if (a->ne <= 0 || a->ne > MAX_NE || a->top_k <= 0 || a->top_k > MAX_K || a->top_k > a->ne) return -2;
+  return 0;
+}
+
+extern "C" int gb_moe_num_blocks(int n_tok) { return (n_tok + BLK_TOK - 1) / BLK_TOK; }
+
+extern "C" int gb_moe_capacity(int n_tok, int ne, int top_k, int shared) {
+  const long long slots = (long long)n_tok * (top_k + (shared ? 1 : 0));
+  const long long cap = slots + (long long)(ne + (shared ? 1 : 0)) * 127;
+  return (int)((cap + 127) / 128 * 128);
+}
+
+#define GB_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+
+extern "C" int gb_moe_route(const gb_moe_args* a, cudaStream_t st) {
+  int rc = moe_check(a);
+  if (rc) return rc;
+  const int nb = gb_moe_num_blocks(a->n_tok);
+  if (a->is_bf16) moe_route_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(*a);
+  else moe_route_kernel<__half><<<nb, 256, 0, st>>>(*a);
+  if (a->aux_m) moe_colmean_kernel<<<a->ne, 256, 0, st>>>(a->probs, a->aux_m, a->n_tok, a->ne);
+  return GB_OK();
+}
+
+extern "C" int gb_moe_group(const gb_moe_args* a, cudaStream_t st) {
+  int rc = moe_check(a);
+  if (rc) return rc;
+  const int nb = gb_moe_num_blocks(a->n_tok);
+  if (nb > 4096) return -3;
+  const int ne1 = a->ne + (a->shared ? 1 : 0);
+  moe_scan_kernel<<<1, 128, 0, st>>>(*a, nb);
+  const int* totals = a->block_base + (size_t)nb * (a->ne + 1);
+  if (a->is_bf16) {
+    moe_pack_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(*a);
+    moe_zero_pads_kernel<__nv_bfloat16><<<ne1, 256, 0, st>>>((__nv_bfloat16*)a->x_perm, a->seg_offsets, totals, a->d);
+  } else {
+    moe_pack_kernel<__half><<<nb, 256, 0, st>>>(*a);
+    moe_zero_pads_kernel<__half><<<ne1, 256, 0, st>>>((__half*)a->x_perm, a->seg_offsets, totals, a->d);
+  }
+  return GB_OK();
+}
+
+extern "C" int gb_moe_combine(const gb_moe_args* a, cudaStream_t st) {
+  int rc = moe_check(a);
+  if (rc) return rc;
+  const int grid = (a->n_tok + 7) / 8;
+  if (a->is_bf16) moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*a);
+  else moe_combine_kernel<__half><<<grid, 256, 0, st>>>(*a);
+  return GB_OK();
+}
+
+extern "C" int gb_moe_combine_bwd(const gb_moe_args* a, cudaStream_t st) {
+  int rc = moe_check(a);
+  if (rc) return rc;
+  const int nb = gb_moe_num_blocks(a->n_tok);
+  const int grid = (a->n_tok + 7) / 8;
+  const int ne1 = a->ne + (a->shared ? 1 : 0);
+  const int* totals = a->block_base + (size_t)nb * (a->ne + 1);
+  if (a->is_bf16) {
+    moe_combine_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*a);
+    moe_zero_pads_kernel<__nv_bfloat16><<<ne1, 256, 0, st>>>((__nv_bfloat16*)a->dy_perm, a->seg_offsets, totals, a->d);
+  } else {
+    moe_combine_bwd_kernel<__half><<<grid, 256, 0, st>>>(*a);
+    moe_zero_pads_kernel<__half><<<ne1, 256, 0, st>>>((__half*)a->dy_perm, a->seg_offsets, totals, a->d);
+  }
+  return GB_OK();
+}
+
+extern "C" int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st) {
+  int rc = moe_check(a);
+  if (rc) return rc;
+  const int grid = (a->n_tok + 7) / 8;
+  dim3 g2((a->d + 255) / 256, a->ne);
+  if (a->is_bf16) {
+    moe_router_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*a);
+    if (a->d_router_w)
+      moe_router_wgrad_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>(a->part, (const __nv_bfloat16*)a->x16, a->d_router_w,
+                                                                 a->n_tok, a->ne, a->d);
+  } else {
+    moe_router_bwd_kernel<__half><<<grid, 256, 0, st>>>(*a);
+    if (a->d_router_w)
+      moe_router_wgrad_kernel<__half><<<g2, 256, 0, st>>>(a->part, (const __half*)a->x16, a->d_router_w, a->n_tok, a->ne,
+                                                          a->d);
+  }
+  return GB_OK();
+}

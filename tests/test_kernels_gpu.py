@@ -1,0 +1,367 @@
+"""Each sm_100a kernel against a plain PyTorch fp32 reference of the same op (mixed abs/rel tolerance)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DT = [torch.float16, torch.bfloat16]
+
+
+def near(got, ref, rtol=2e-2, atol_frac=2e-2):
+    got, ref = got.float(), ref.float()
+    atol = atol_frac * ref.abs().max().item() + 1e-5
+    bad = (got - ref).abs() > atol + rtol * ref.abs()
+    return not bool(bad.any()), float((got - ref).abs().max()), atol
+
+
+def K():
+    from ghassan_b200.ops import kernels
+    return kernels
+
+
+def R():
+    from ghassan_b200.models import reference
+    return reference
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_rmsnorm_fwd_bwd(dt):
+    k, r = K(), R()
+    rows, d, eps = 333, 768, 1e-5
+    x = rnd(rows, d, seed=1).requires_grad_(True)
+    w = (1 + 0.1 * rnd(d, seed=2)).requires_grad_(True)
+    y16 = torch.empty(rows, d, dtype=dt, device="cuda")
+    rrms = torch.empty(rows, device="cuda")
+    k.rmsnorm_fwd(x.detach(), w.detach(), y16, rrms, eps)
+    ref = r.rmsnorm(x, w, eps)
+    ok, err, _ = near(y16, ref.detach())
+    assert ok, err
+    g = rnd(rows, d, seed=3).to(dt)
+    dres = rnd(rows, d, seed=4)
+    (ref * g.float()).sum().backward()
+    dx = torch.empty_like(dres)
+    dx16 = torch.empty(rows, d, dtype=dt, device="cuda")
+    dw = torch.ones(d, device="cuda")
+    part = k.rmsnorm_bwd_scratch(rows, d, "cuda")
+    k.rmsnorm_bwd(g, x.detach(), w.detach(), rrms, dres, dx, dx16, part, dw)
+    ok, err, _ = near(dx, dres + x.grad, 1e-3, 1e-3)
+    assert ok, err
+    ok, err, _ = near(dw, 1 + w.grad, 1e-3, 1e-3)
+    assert ok, err
+    assert near(dx16, dx)[0]
+    # determinism: a second run gives the same bits
+    dw2 = torch.ones(d, device="cuda")
+    k.rmsnorm_bwd(g, x.detach(), w.detach(), rrms, dres, dx, dx16, part, dw2)
+    assert torch.equal(dw, dw2)
+
+
+@pytest.mark.parametrize("hd,rope_type,use_norm", [(64, 0, True), (64, 1, True), (32, 0, False), (128, 1, True)])
+def test_qk_norm_rope(hd, rope_type, use_norm):
+    k, r = K(), R()
+    dt = torch.float16
+    n, H, KV, eps = 70, 4, 2, 1e-5
+    ld = (H + 2 * KV) * hd
+    qkv = rnd(n, ld, seed=5).to(dt)
+    qw = (1 + 0.1 * rnd(hd, seed=6)) if use_norm else None
+    kw = (1 + 0.1 * rnd(hd, seed=7)) if use_norm else None
+    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], device="cuda")
+    cs = k.rope_table(inv_freq, 128, "cuda")
+    pos = (torch.arange(n, device="cuda", dtype=torch.int32) * 3) % 128
+    out = torch.empty(n, (H + KV) * hd, dtype=dt, device="cuda")
+    k.qk_norm_rope_fwd(qkv, out, qw, kw, cs, pos, H, KV, hd, eps, rope_type)
+
+    def ref_fn(raw):
+        q = raw[:, :H * hd].view(n, H, hd)
+        kk = raw[:, H * hd:(H + KV) * hd].view(n, KV, hd)
+        if use_norm:
+            q, kk = r.rmsnorm(q, qw, eps), r.rmsnorm(kk, kw, eps)
+        q, kk = r.rope(q, pos, inv_freq, rope_type), r.rope(kk, pos, inv_freq, rope_type)
+        return torch.cat([q.reshape(n, -1), kk.reshape(n, -1)], dim=1)
+
+    raw = qkv.float().requires_grad_(True)
+    if use_norm:
+        qw.requires_grad_(True)
+        kw.requires_grad_(True)
+    ref = ref_fn(raw)
+    ok, err, _ = near(out, ref.detach())
+    assert ok, err
+    g = rnd(n, (H + KV) * hd, seed=8).to(dt)
+    (ref * g.float()).sum().backward()
+    dqkv = torch.zeros(n, ld, dtype=dt, device="cuda")
+    part = k.qk_rope_scratch(n, H + KV, hd, "cuda")
+    dqw = torch.zeros(hd, device="cuda") if use_norm else None
+    dkw = torch.zeros(hd, device="cuda") if use_norm else None
+    k.qk_norm_rope_bwd(g, qkv, dqkv, qw.detach() if use_norm else None, kw.detach() if use_norm else None, cs, pos, part,
+                       dqw, dkw, H, KV, hd, eps, rope_type)
+    ok, err, _ = near(dqkv[:, :(H + KV) * hd], raw.grad[:, :(H + KV) * hd])
+    assert ok, err
+    if use_norm:
+        assert near(dqw, qw.grad, 2e-2, 2e-2)[0]
+        assert near(dkw, kw.grad, 2e-2, 2e-2)[0]
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("B,T,H,KV,hd,window,use_seg", [
+    (2, 96, 4, 2, 64, 0, False), (1, 130, 4, 4, 32, 0, True), (2, 64, 8, 2, 64, 17, True),
+    (1, 1, 2, 1, 64, 0, False), (1, 77, 2, 1, 128, 0, False)])
+def test_attention_fwd_bwd(dt, B, T, H, KV, hd, window, use_seg):
+    k, r = K(), R()
+    n = B * T
+    scale = hd ** -0.5
+    q = rnd(n, H * hd, seed=11).to(dt)
+    kk = rnd(n, KV * hd, seed=12).to(dt)
+    v = rnd(n, KV * hd, seed=13).to(dt)
+    seg = None
+    if use_seg:
+        seg = (torch.arange(T, device="cuda") // 23).repeat(B).to(torch.int32)
+    o = torch.empty(n, H * hd, dtype=dt, device="cuda")
+    lse = torch.empty(n, H, device="cuda")
+    k.attn_fwd(q, kk, v, o, lse, seg, B, T, H, KV, hd, window, scale)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, kk, v))
+    ref = r.attention(qf.view(n, H, hd), kf.view(n, KV, hd), vf.view(n, KV, hd), B, T, scale, window, seg)
+    ok, err, _ = near(o, ref.detach())
+    assert ok, err
+    g = rnd(n, H * hd, seed=14).to(dt)
+    (ref * g.float()).sum().backward()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(kk), torch.empty_like(v)
+    delta = torch.empty(n, H, device="cuda")
+    k.attn_bwd(q, kk, v, o, lse, seg, g, delta, dq, dk, dv, B, T, H, KV, hd, window, scale)
+    for got, want, name in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
+        ok, err, atol = near(got, want)
+        assert ok, (name, err, atol)
+
+
+def test_attention_strided_views_match_contiguous():
+    """q/k come from one buffer, v from the fused projection buffer (row strides differ from head widths)."""
+    k = K()
+    B, T, H, KV, hd = 1, 50, 4, 2, 64
+    n = B * T
+    dt = torch.float16
+    qkv = rnd(n, (H + 2 * KV) * hd, seed=21).to(dt)
+    qk = rnd(n, (H + KV) * hd, seed=22).to(dt)
+    q, kk, v = qk[:, :H * hd], qk[:, H * hd:], qkv[:, (H + KV) * hd:]
+    o1 = torch.empty(n, H * hd, dtype=dt, device="cuda")
+    o2 = torch.empty_like(o1)
+    lse = torch.empty(n, H, device="cuda")
+    k.attn_fwd(q, kk, v, o1, lse, None, B, T, H, KV, hd, 0, 0.125)
+    k.attn_fwd(q.contiguous(), kk.contiguous(), v.contiguous(), o2, lse, None, B, T, H, KV, hd, 0, 0.125)
+    assert torch.equal(o1, o2)
+
+
+def _moe_setup(n, d, ne, Kk, shared, seed=0, dt=torch.float16):
+    x16 = rnd(n, d, seed=seed + 1).to(dt)
+    rw = rnd(ne, d, seed=seed + 2, scale=0.05)
+    return x16, rw
+
+
+@pytest.mark.parametrize("n,ne,Kk,shared,jit", [(300, 8, 2, True, 0.0), (513, 8, 4, True, 0.01), (64, 4, 2, False, 0.0),
+                                               (1000, 64, 8, True, 0.0)])
+def test_moe_route_group_matches_reference(n, ne, Kk, shared, jit):
+    k, r = K(), R()
+    from ghassan_b200.models.config import ModelConfig
+    d = 128
+    dt = torch.float16
+    x16, rw = _moe_setup(n, d, ne, Kk, shared)
+    bias = rnd(ne, seed=9, scale=0.01)
+    cfg = ModelConfig(num_experts=ne, moe_top_k=Kk, moe_jitter=jit, moe_allow_dense=True)
+    probs, idx, w = r.route(x16.float(), rw, bias, cfg, 1234 if jit > 0 else None)
+    ws = k.MoeWorkspace(n, d, ne, Kk, shared, dt, "cuda")
+    xp = torch.full((ws.cap, d), 7.0, dtype=dt, device="cuda")
+    counts = torch.zeros(ne, device="cuda")
+    k.moe_route_group(ws, x16, rw, bias, xp, counts, jitter=jit, jitter_seed=1234 if jit > 0 else None, want_aux=True)
+    assert near(ws.probs, probs, 1e-3, 1e-4)[0]
+    # routing may differ only where two selection scores are closer than fp32 round-off
+    same = (ws.idx.long() == idx).all(dim=1)
+    assert same.float().mean().item() > 0.995
+    assert near(ws.w[same], w[same], 1e-3, 1e-4)[0]
+    ref_counts = torch.bincount(ws.idx.reshape(-1).long(), minlength=ne).float()
+    assert torch.equal(counts, ref_counts)
+    assert near(ws.f_frac, ref_counts / (n * Kk), 1e-5, 1e-6)[0]
+    assert near(ws.aux_m, ws.probs.mean(0), 1e-4, 1e-5)[0]
+    # segments: padded to 128, rows stable in token order, pads zero
+    so = ws.seg_offsets.cpu().tolist()
+    tot = ref_counts.cpu().long().tolist() + ([n] if shared else [])
+    ne1 = ne + int(shared)
+    for e in range(ne1):
+        assert so[e] % 128 == 0 and so[e + 1] - so[e] == (tot[e] + 127) // 128 * 128
+    assert int(ws.num_tiles[0]) == so[ne1] // 128
+    te = ws.tile_expert.cpu().tolist()
+    for e in range(ne1):
+        assert all(te[t] == e for t in range(so[e] // 128, so[e + 1] // 128))
+    pos = ws.slot_pos.cpu().long()
+    idxc = ws.idx.cpu().long()
+    for e in range(ne):
+        rows = [(t, kk) for t in range(n) for kk in range(Kk) if idxc[t, kk] == e] if n <= 600 else None
+        if rows is not None:
+            want = list(range(so[e], so[e] + len(rows)))
+            assert [int(pos[t, kk]) for t, kk in rows] == want
+    flat = pos.reshape(-1)
+    assert flat.unique().numel() == flat.numel()
+    tok_of = torch.arange(n).repeat_interleave(pos.shape[1])
+    assert torch.equal(xp[flat.cuda()], x16[tok_of.cuda()])
+    for e in range(ne1):
+        assert float(xp[so[e] + tot[e]:so[e + 1]].abs().max() if so[e + 1] > so[e] + tot[e] else 0) == 0.0
+
+
+@pytest.mark.parametrize("aux,jit", [(0.0, 0.0), (0.01, 0.01)])
+def test_moe_layer_forward_backward(aux, jit):
+    """route -> grouped SwiGLU GEMM -> grouped down GEMM -> combine, and the whole backward, vs autograd."""
+    k, r = K(), R()
+    from ghassan_b200.ops import gemm as G
+    from ghassan_b200.models.config import ModelConfig
+    n, d, E, ne, Kk = 384, 128, 128, 8, 2
+    dt = torch.float16
+    cfg = ModelConfig(num_experts=ne, moe_top_k=Kk, moe_jitter=jit, hidden_size=d, moe_expert_dim=E)
+    seed = 77
+    x16 = rnd(n, d, seed=31).to(dt)
+    rw = rnd(ne, d, seed=32, scale=0.05)
+    gate = rnd(ne + 1, E, d, seed=33, scale=0.08).to(dt)
+    up = rnd(ne + 1, E, d, seed=34, scale=0.08).to(dt)
+    down = rnd(ne + 1, d, E, seed=35, scale=0.08).to(dt)
+    resid = rnd(n, d, seed=36)
+    dout = rnd(n, d, seed=37)
+    aux_coef = aux * 3.0
+    # ---- reference with autograd
+    xf = x16.float().requires_grad_(True)
+    rwf = rw.clone().requires_grad_(True)
+    gf, uf, df = (t.float().requires_grad_(True) for t in (gate, up, down))
+    probs, idx, w = r.route(xf, rwf, None, cfg, seed if jit > 0 else None)
+    out = resid + r.swiglu_ffn(xf, gf[ne], uf[ne], df[ne])
+    for e in range(ne):
+        hit = idx == e
+        rows = hit.any(1).nonzero(as_tuple=True)[0]
+        if rows.numel():
+            out = out.index_add(0, rows, r.swiglu_ffn(xf[rows], gf[e], uf[e], df[e]) * (w * hit).sum(1)[rows][:, None])
+    cnt = torch.bincount(idx.reshape(-1), minlength=ne).float()
+    f = cnt / (n * Kk)
+    obj = (out * dout).sum() + aux_coef * n * (probs.mean(0) * f).sum()
+    obj.backward()
+    # ---- kernels
+    ws = k.MoeWorkspace(n, d, ne, Kk, True, dt, "cuda")
+    xp = torch.empty(ws.cap, d, dtype=dt, device="cuda")
+    k.moe_route_group(ws, x16, rw, None, xp, None, jitter=jit, jitter_seed=seed if jit > 0 else None, want_aux=aux > 0)
+    assert torch.equal(ws.idx.long(), idx)
+    wgu = G.interleave_gate_up(gate, up).reshape((ne + 1) * 2 * E, d).contiguous()
+    wdn = down.reshape((ne + 1) * d, E).contiguous()
+    gu = torch.empty(ws.cap, 2 * E, dtype=dt, device="cuda")
+    act = torch.empty(ws.cap, E, dtype=dt, device="cuda")
+    G.gemm_swiglu(xp, wgu, act_out=act, gu_out=gu, tile_expert=ws.tile_expert, num_m_tiles=ws.num_tiles, group_rows=2 * E)
+    y = G.gemm_grouped_rows(act, wdn, ws.tile_expert, ws.num_tiles, n=d, group_rows=d)
+    got = torch.empty(n, d, device="cuda")
+    k.moe_combine(ws, y, resid, got)
+    ok, err, _ = near(got, out.detach())
+    assert ok, err
+    dy = torch.empty(ws.cap, d, dtype=dt, device="cuda")
+    gdot = torch.empty(n, Kk, device="cuda")
+    k.moe_combine_bwd(ws, dout, y, dy, gdot)
+    dgu = G.gemm_swiglu_bwd(dy, wdn, gu, tile_expert=ws.tile_expert, num_m_tiles=ws.num_tiles, group_rows=d, n=E)
+    dxp = G.gemm_grouped_rows(dgu, wgu, ws.tile_expert, ws.num_tiles, n=d, b_mn=True, group_rows=2 * E)
+    d_wdn = torch.zeros(ne + 1, d, E, device="cuda")
+    G.gemm_grouped_reduce(dy, act, ws.seg_offsets, ne + 1, d_wdn)
+    d_wgu = torch.zeros(ne + 1, 2 * E, d, device="cuda")
+    G.gemm_grouped_reduce(dgu, xp, ws.seg_offsets, ne + 1, d_wgu)
+    dx16 = torch.empty(n, d, dtype=dt, device="cuda")
+    d_rw = torch.zeros(ne, d, device="cuda")
+    part = torch.empty(n, ne, device="cuda")
+    k.moe_router_bwd(ws, x16, rw, gdot, dxp, dx16, d_rw, part, aux_coef=aux_coef * ne / ne, jitter=jit,
+                     jitter_seed=seed if jit > 0 else None)
+    from ghassan_b200.ops import _lib
+    _lib.check_status(what="moe layer")
+    ok, err, atol = near(dx16, xf.grad, 3e-2, 3e-2)
+    assert ok, ("dx", err, atol)
+    ok, err, atol = near(d_wdn, df.grad, 3e-2, 3e-2)
+    assert ok, ("d_down", err, atol)
+    dg_got, du_got = G.deinterleave_gate_up(d_wgu)
+    assert near(dg_got, gf.grad, 3e-2, 3e-2)[0]
+    assert near(du_got, uf.grad, 3e-2, 3e-2)[0]
+    ok, err, atol = near(d_rw, rwf.grad, 3e-2, 3e-2)
+    assert ok, ("d_router", err, atol)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("V,z", [(32000, 1e-4), (600, 0.0), (1003, 1e-3)])
+def test_softmax_ce(dt, V, z):
+    k = K()
+    rows = 40
+    ld = (V + 7) // 8 * 8
+    buf = torch.zeros(rows, ld, dtype=dt, device="cuda")
+    buf[:, :V] = rnd(rows, V, seed=41, scale=2.0).to(dt)
+    logits = buf[:, :V]
+    tgt = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+    tgt[::7] = -100
+    lf = logits.float().requires_grad_(True)
+    logz = torch.logsumexp(lf, -1)
+    sup = tgt >= 0
+    per = logz - lf.gather(1, tgt.clamp_min(0).long()[:, None]).squeeze(1) + z * logz * logz
+    loss = (per * sup).sum()
+    gs = 64.0
+    (loss * gs).backward()
+    acc = torch.zeros(2, dtype=torch.float64, device="cuda")
+    row_loss = torch.empty(rows, device="cuda")
+    k.softmax_ce_(logits, tgt, z, gs, True, row_loss, acc)
+    assert abs(float(acc[0]) - float(loss)) < 2e-3 * abs(float(loss)) + 1e-3
+    assert int(acc[1]) == int(sup.sum())
+    ok, err, atol = near(logits, lf.grad, 2e-2, 2e-3)
+    assert ok, (err, atol)
+
+
+@pytest.mark.parametrize("kind", ["adamw", "lion"])
+def test_flat_optimizer_matches_reference(kind):
+    k = K()
+    from ghassan_b200.training import optim as O
+    n = 100003
+    w0 = rnd(n, seed=51)
+    g = rnd(n, seed=52) * 300.0
+    p = O.OptParam("w", w0.clone(), True)
+    p.w.grad = g.clone()
+    ref = O.AdamW([p], 1e-3, 0.9, 0.95, 1e-8, 0.1, 1.0) if kind == "adamw" else O.Lion([p], 1e-4, 0.9, 0.99, 0.1, 1.0)
+    w = w0.clone()
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    w16 = torch.empty(n, dtype=torch.float16, device="cuda")
+    nb = k.sqnorm_blocks(n)
+    partial = torch.empty(nb, dtype=torch.float64, device="cuda")
+    out = torch.empty(2, device="cuda")
+    hyper = torch.empty(3, device="cuda")
+    grad_scale = 1.0 / 512.0
+    for step in range(1, 4):
+        gn_ref = ref.step(1e-3, grad_scale)
+        bc1, bc2 = ref._bias_corrections(ref.beta1, ref.beta2)
+        hyper.copy_(torch.tensor([1e-3, bc1, bc2]))
+        k.sqnorm_partial(g, partial)
+        k.finish_norm(partial, nb, None, grad_scale, 1.0, out)
+        k.optimizer_step(kind, w, g, m, v if kind == "adamw" else None, w16, hyper, out[0:1], ref.beta1, ref.beta2,
+                         1e-8, 0.1)
+        assert abs(float(out[1]) - gn_ref) < 1e-4 * gn_ref
+        assert near(w, p.w, 1e-5, 1e-6)[0]
+        assert near(w16, p.w, 2e-3, 1e-3)[0]
+    # a non-finite gradient skips the step without touching anything
+    g2 = g.clone()
+    g2[5] = float("inf")
+    before = w.clone()
+    k.sqnorm_partial(g2, partial)
+    k.finish_norm(partial, nb, None, grad_scale, 1.0, out)
+    k.optimizer_step(kind, w, g2, m, v if kind == "adamw" else None, w16, hyper, out[0:1], 0.9, 0.95, 1e-8, 0.1)
+    assert float(out[0]) == 0.0 and not math.isfinite(float(out[1]))
+    assert torch.equal(w, before)
+
+
+def test_embedding_gather_scatter():
+    k = K()
+    V, d, n = 100, 64, 50
+    table = rnd(V, d, seed=61)
+    ids = torch.randint(0, V, (n,), device="cuda", dtype=torch.int32)
+    out = torch.empty(n, d, device="cuda")
+    k.embed_fwd(ids, table, out)
+    assert torch.equal(out, table[ids.long()])
+    dx = rnd(n, d, seed=62)
+    dt_ = torch.zeros(V, d, device="cuda")
+    k.embed_bwd(ids, dx, dt_)
+    ref = torch.zeros(V, d, device="cuda").index_add_(0, ids.long(), dx)
+    assert near(dt_, ref, 1e-5, 1e-6)[0]
