@@ -11,7 +11,8 @@ namespace gb {
 
 template <typename T>
 __global__ void __launch_bounds__(256) ce_row_kernel(T* __restrict__ logits, long long ld, const int* __restrict__ targets,
-                                                     int V, float z, float grad_scale, int write_grad,
+                                                     int V, float z, float grad_scale_val,
+                                                     const float* __restrict__ grad_scale_dev, int write_grad,
                                                      float* __restrict__ row_loss) {
   __shared__ float red[8];
   __shared__ float bcast;
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(256) ce_row_kernel(T* __restrict__ logits, lon
   __syncthreads();   // everyone has read the target logit before it is overwritten
   if (threadIdx.x == 0) row_loss[row] = logz - tl + z * logz * logz;
   if (!write_grad) return;
+  const float grad_scale = grad_scale_dev ? grad_scale_dev[0] : grad_scale_val;
   const float coef = (1.f + 2.f * z * logz) / sum * grad_scale;
   for (int i = threadIdx.x; i < vec; i += 256) {
     const uint4 q = reinterpret_cast<const uint4*>(lr)[i];
@@ -116,14 +118,16 @@ using namespace gb;
 
 // row_loss: scratch of `rows` floats.  The logits base and ld must keep rows 16-byte aligned.
 extern "C" int gb_softmax_ce(void* logits, long long ld, const int* targets, int rows, int V, float z_loss,
-                             float grad_scale, int write_grad, float* row_loss, double* acc, int is_bf16,
+                             float grad_scale, const float* grad_scale_dev, int write_grad, float* row_loss, double* acc,
+                             int is_bf16,
                              cudaStream_t st) {
   if (rows <= 0 || V <= 0 || (ld * 2) % 16 || (reinterpret_cast<uintptr_t>(logits) & 15)) return -1;
   if (is_bf16)
     ce_row_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>((__nv_bfloat16*)logits, ld, targets, V, z_loss, grad_scale,
-                                                       write_grad, row_loss);
+                                                       grad_scale_dev, write_grad, row_loss);
   else
-    ce_row_kernel<__half><<<rows, 256, 0, st>>>((__half*)logits, ld, targets, V, z_loss, grad_scale, write_grad, row_loss);
+    ce_row_kernel<__half><<<rows, 256, 0, st>>>((__half*)logits, ld, targets, V, z_loss, grad_scale, grad_scale_dev,
+                                                write_grad, row_loss);
   ce_fold_kernel<<<1, 256, 0, st>>>(row_loss, rows, acc);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

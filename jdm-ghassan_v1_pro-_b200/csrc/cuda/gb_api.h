@@ -111,7 +111,10 @@ typedef struct gb_moe_args {
   float* d_router_w;                 // [ne, d] fp32, accumulated
   void* dx16;                        // [n_tok, d] 16-bit gradient w.r.t. x16 (all paths summed)
   float* aux_m;                      // [ne] mean router probability per expert (aux loss), or NULL
-  float* part;                       // scratch for d_router_w partials: [n_blocks, ne, d]
+  float* part;                       // scratch: router-logit gradients [n_tok, ne]
+  float* aux_acc;                    // [1] += ne * sum_e aux_m[e] * f[e] of this call (needs aux_m), or NULL
+  const unsigned long long* dyn_seed;// device copy of jitter_seed (overrides it; lets a captured graph change seeds)
+  const float* dyn_aux_coef;         // device copy of aux_coef (overrides it)
 } gb_moe_args;
 int gb_moe_num_blocks(int n_tok);
 int gb_moe_capacity(int n_tok, int ne, int top_k, int shared);
@@ -125,8 +128,10 @@ int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st);     // dx16 (un-pe
 // logits: [rows, V] 16-bit (in place: overwritten with d(logits) * grad_scale when write_grad != 0).
 // acc[0] += sum of losses (double), acc[1] += number of supervised rows (as double); z-loss z*logZ^2.
 // row_loss: scratch of `rows` floats.
+// grad_scale_dev (optional, device): overrides grad_scale, so a captured graph can follow the loss scaler.
 int gb_softmax_ce(void* logits, long long ld, const int* targets, int rows, int V, float z_loss, float grad_scale,
-                  int write_grad, float* row_loss, double* acc, int is_bf16, cudaStream_t st);
+                  const float* grad_scale_dev, int write_grad, float* row_loss, double* acc, int is_bf16,
+                  cudaStream_t st);
 
 // ----------------------------------------------------------------------------- optim.cu
 typedef struct gb_opt_args {

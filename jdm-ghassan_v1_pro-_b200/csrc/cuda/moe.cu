@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
   const int t0 = blockIdx.x * BLK_TOK;
   const int t1 = min(a.n_tok, t0 + BLK_TOK);
   const T* x16 = reinterpret_cast<const T*>(a.x16);
+  const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;   // device copy wins (graph replay)
   for (int t = t0 + warp; t < t1; t += 8) {
     const T* xr = x16 + (size_t)t * d;
     // lane holds the logits of experts `lane` and `lane + 32`
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
         s += xv.x * wv.x + xv.y * wv.y;
       }
       s = warp_sum(s);
-      if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, a.jitter_seed);
+      if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, jseed);
       if (e == lane) l0 = s;
       if (e == lane + 32) l1 = s;
     }
@@ -146,6 +147,12 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks) {
   if (e < a.ne) {
     if (a.counts) a.counts[e] += (float)s_total[e];
     if (a.f_frac) a.f_frac[e] = (float)s_total[e] / (float)((long long)a.n_tok * a.top_k);
+  }
+  if (threadIdx.x == 0 && a.aux_acc && a.aux_m) {
+    // balance loss of this call: ne * sum_e mean_prob[e] * slot_share[e]
+    float raw = 0.f;
+    for (int i = 0; i < a.ne; ++i) raw += a.aux_m[i] * ((float)s_total[i] / (float)((long long)a.n_tok * a.top_k));
+    a.aux_acc[0] += (float)a.ne * raw;
   }
 }
 
@@ -308,9 +315,11 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
   const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
   const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
   float dp0 = 0.f, dp1 = 0.f;
-  if (a.f_frac && a.aux_coef != 0.f) {
-    if (lane < ne) dp0 = a.aux_coef * a.f_frac[lane];
-    if (lane + 32 < ne) dp1 = a.aux_coef * a.f_frac[lane + 32];
+  const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[0] : a.aux_coef;
+  const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;
+  if (a.f_frac && aux_coef != 0.f) {
+    if (lane < ne) dp0 = aux_coef * a.f_frac[lane];
+    if (lane + 32 < ne) dp1 = aux_coef * a.f_frac[lane + 32];
   }
   float ssum = 0.f, gbar = 0.f;
   for (int k = 0; k < K; ++k) {
@@ -331,8 +340,8 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
   const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
   float dl0 = p0 * (dp0 - pdp), dl1 = p1 * (dp1 - pdp);
   if (a.use_jitter) {
-    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane, a.jitter_seed);
-    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane + 32, a.jitter_seed);
+    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane, jseed);
+    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane + 32, jseed);
   }
   if (lane < ne) a.part[(size_t)t * ne + lane] = dl0;
   if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1;

@@ -44,7 +44,8 @@ class MoeArgs(ctypes.Structure):
                 ("y_perm", c_void_p), ("resid", c_void_p), ("out", c_void_p),
                 ("dout", c_void_p), ("dy_perm", c_void_p), ("gdot", c_void_p), ("dx_perm", c_void_p),
                 ("aux_coef", c_float), ("f_frac", c_void_p), ("d_router_w", c_void_p), ("dx16", c_void_p),
-                ("aux_m", c_void_p), ("part", c_void_p)]
+                ("aux_m", c_void_p), ("part", c_void_p), ("aux_acc", c_void_p), ("dyn_seed", c_void_p),
+                ("dyn_aux_coef", c_void_p)]
 
 
 class OptArgs(ctypes.Structure):
@@ -61,8 +62,8 @@ def _protos():
     if _proto_done:
         return lib()
     L = lib()
-    L.gb_softmax_ce.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
-                                c_int, c_void_p]
+    L.gb_softmax_ce.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p,
+                                c_void_p, c_int, c_void_p]
     L.gb_embed_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     L.gb_embed_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     L.gb_rmsnorm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
@@ -214,12 +215,16 @@ class MoeWorkspace:
 
 
 def moe_route_group(ws: MoeWorkspace, x16, router_w, bias, x_perm, counts=None, jitter=0.0, jitter_seed=None,
-                    want_aux=False):
+                    want_aux=False, aux_acc=None, seed_dev=None):
+    """``jitter_seed`` (host int) or ``seed_dev`` (uint64 device tensor, read at run time) enables the jitter."""
     a = ws.args()
     a.x16, a.router_w, a.bias = _p(x16), _p(router_w), _p(bias)
-    a.jitter, a.use_jitter = float(jitter), int(jitter > 0 and jitter_seed is not None)
+    a.jitter = float(jitter)
+    a.use_jitter = int(jitter > 0 and (jitter_seed is not None or seed_dev is not None))
     a.jitter_seed = int(jitter_seed or 0)
+    a.dyn_seed = _p(seed_dev)
     a.x_perm, a.counts = _p(x_perm), _p(counts)
+    a.aux_acc = _p(aux_acc)
     if not want_aux:
         a.aux_m = None
         a.f_frac = None
@@ -241,24 +246,27 @@ def moe_combine_bwd(ws: MoeWorkspace, dout, y_perm, dy_perm, gdot):
 
 
 def moe_router_bwd(ws: MoeWorkspace, x16, router_w, gdot, dx_perm, dx16, d_router_w, part, aux_coef=0.0, jitter=0.0,
-                   jitter_seed=None):
+                   jitter_seed=None, seed_dev=None, aux_coef_dev=None):
     a = ws.args()
     a.x16, a.router_w, a.gdot, a.dx_perm, a.dx16 = _p(x16), _p(router_w), _p(gdot), _p(dx_perm), _p(dx16)
     a.d_router_w, a.part, a.aux_coef = _p(d_router_w), _p(part), float(aux_coef)
-    a.jitter, a.use_jitter = float(jitter), int(jitter > 0 and jitter_seed is not None)
+    a.jitter = float(jitter)
+    a.use_jitter = int(jitter > 0 and (jitter_seed is not None or seed_dev is not None))
     a.jitter_seed = int(jitter_seed or 0)
-    if aux_coef == 0.0:
+    a.dyn_seed, a.dyn_aux_coef = _p(seed_dev), _p(aux_coef_dev)
+    if aux_coef == 0.0 and aux_coef_dev is None:
         a.f_frac = None
     check_rc(lib().gb_moe_router_bwd(ctypes.byref(a), stream_ptr()), "moe_router_bwd")
 
 
 # ------------------------------------------------------------------------------------------ CE / optimizer
-def softmax_ce_(logits16, targets, z_loss, grad_scale, write_grad, row_loss, acc):
-    """In place on a [rows, V] 16-bit chunk; ``acc`` (float64[2]) accumulates (loss sum, supervised rows)."""
+def softmax_ce_(logits16, targets, z_loss, grad_scale, write_grad, row_loss, acc, grad_scale_dev=None):
+    """In place on a [rows, V] 16-bit chunk; ``acc`` (float64[2]) accumulates (loss sum, supervised rows).
+    ``grad_scale_dev`` (fp32 device scalar) overrides ``grad_scale`` when given."""
     rows, V = logits16.shape
     check_rc(_protos().gb_softmax_ce(_p(logits16), logits16.stride(0), _p(targets), rows, V, float(z_loss),
-                                     float(grad_scale), int(write_grad), _p(row_loss), _p(acc), _bf(logits16.dtype),
-                                     stream_ptr()), "softmax_ce")
+                                     float(grad_scale), _p(grad_scale_dev), int(write_grad), _p(row_loss), _p(acc),
+                                     _bf(logits16.dtype), stream_ptr()), "softmax_ce")
 
 
 def sqnorm_blocks(n):

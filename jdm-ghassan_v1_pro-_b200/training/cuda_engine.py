@@ -1,0 +1,346 @@
+"""Training engine for a B200: drives :class:`CudaModel` and the flat-buffer optimizer kernels.
+
+Same protocol as ``TorchEngine`` (begin_step / micro_step / end_step / eval_batch).  Differences that matter:
+
+* one micro-batch = one CUDA-graph replay (captured after two eager warm-up runs), inputs staged from pinned
+  host memory into static device buffers, per-launch scalars (loss scale, aux coefficient, jitter seed) in
+  device memory so the captured graph follows them;
+* the host reads back exactly one small record per optimizer step (gradient norm / skip flag, loss sum, token
+  count, aux sum) instead of the reference's per-layer and per-tensor round trips
+  (training/trainer.cpp:1476-1536, cuda/moe.cu:601-676, cuda/kernels.cu:1108-1128);
+* gradients of all ranks are combined by ``parallel.grad_sync`` (peer-memory reduce-scatter fused with the
+  optimizer and the parameter all-gather) or, with ``b200.grad_sync: nccl``, by one NCCL all-reduce.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..models.config import ModelConfig
+from ..models.cuda_model import CudaModel
+from ..ops import _lib
+from ..ops import kernels as K
+from ..utils.log import log_info, log_warn
+from ..utils.telemetry import PERF
+from . import optim as O
+from .engine import MOE_BIAS_CLAMP, MOE_BIAS_LR, DistInfo, StepResult, jitter_seed_for, moe_bias_update
+
+_F32 = np.float32
+
+
+class _FlatOptimizer:
+    """AdamW / Lion over the flat [no-decay | decay] layout; moments are flat fp32 buffers."""
+
+    def __init__(self, kind, model: CudaModel, tcfg):
+        self.kind = kind
+        self.model = model
+        self.t = 0
+        self.beta1, self.beta2, self.eps = tcfg.beta1, tcfg.beta2, tcfg.eps
+        self.weight_decay, self.grad_clip = tcfg.weight_decay, tcfg.grad_clip
+        self.lr = tcfg.effective_peak_lr()
+        n = model.layout.total
+        self.m_flat = torch.zeros(n, dtype=torch.float32, device=model.dev)
+        self.v_flat = torch.zeros(n, dtype=torch.float32, device=model.dev) if kind == "adamw" else None
+        self.hyper_dev = torch.zeros(3, dtype=torch.float32, device=model.dev)
+        self.hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory()
+
+    def hyper(self):
+        h = dict(lr=self.lr, beta1=self.beta1, beta2=self.beta2, weight_decay=self.weight_decay, grad_clip=self.grad_clip)
+        if self.kind == "adamw":
+            h["eps"] = self.eps
+        return h
+
+    def launch(self, lr: float, scale_dev: torch.Tensor, lo: int = 0, hi: Optional[int] = None):
+        """Update elements [lo, hi) of the flat buffers (both regions, each with its own weight decay)."""
+        m = self.model
+        hi = m.layout.total if hi is None else hi
+        t = self.t + 1   # applied count if this step is accepted; a rejected step leaves everything untouched
+        bc1 = float(_F32(1.0) - np.power(_F32(self.beta1), _F32(t), dtype=_F32))
+        bc2 = float(_F32(1.0) - np.power(_F32(self.beta2), _F32(t), dtype=_F32))
+        self.hyper_host[0], self.hyper_host[1], self.hyper_host[2] = lr, bc1, bc2
+        self.hyper_dev.copy_(self.hyper_host, non_blocking=True)
+        ds = m.layout.decay_start
+        for a, b, wd in ((lo, min(hi, ds), 0.0), (max(lo, ds), hi, self.weight_decay)):
+            if b > a:
+                K.optimizer_step(self.kind, m.P[a:b], m.Gr[a:b], self.m_flat[a:b],
+                                 None if self.v_flat is None else self.v_flat[a:b], m.W16[a:b], self.hyper_dev,
+                                 scale_dev, self.beta1, self.beta2, self.eps, wd)
+
+
+class CudaEngine:
+    kind = "cuda"
+
+    def __init__(self, mcfg: ModelConfig, tcfg, seed: Optional[int] = None, device=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CudaEngine needs a CUDA device")
+        if not _lib.available():
+            raise RuntimeError("the sm_100a kernel library is not built: run `python -m ghassan_b200.build`")
+        self.mcfg, self.tcfg = mcfg, tcfg
+        self.dist = DistInfo()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.dtype = torch.bfloat16 if tcfg.operand_dtype() == "bf16" else torch.float16
+        self.uses_loss_scaling = self.dtype == torch.float16 and tcfg.gemm_fp16
+        self.model = CudaModel(mcfg, tcfg.batch_size, tcfg.seq_len, self.dtype, self.device, tcfg.ce_chunks,
+                               use_segments=tcfg.pack_sequences, train=True)
+        self.model.init_weights(tcfg.seed if seed is None else seed)
+        self.sync_model()
+        self.muon = None
+        if tcfg.optimizer == "muon":
+            self.optimizer = self._make_muon()
+        else:
+            self.optimizer = _FlatOptimizer(tcfg.optimizer, self.model, tcfg)
+        n = self.model.layout.total
+        self.sq_partial = torch.zeros(K.sqnorm_blocks(n), dtype=torch.float64, device=self.device)
+        self.norm_out = torch.zeros(2, dtype=torch.float32, device=self.device)   # [scale or 0, gnorm]
+        self.gs_dev = torch.zeros(1, dtype=torch.float32, device=self.device)     # 1 / (ntok_global * loss_scale)
+        self.ntok_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.aux_weighted = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.readback = torch.zeros(6, dtype=torch.float64).pin_memory()
+        self.dyn_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+        self.seed_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.eval_graph: Optional[torch.cuda.CUDAGraph] = None
+        self._warm = 0
+        self._ntok = 0
+        self._loss_scale = 1.0
+        self.weight_ema = torch.empty_like(self.model.P).copy_(self.model.P) if tcfg.weight_ema > 0 else None
+        self.grad_sync = None
+        if self.dist.world > 1 and tcfg.grad_sync == "fused":
+            from ..parallel.grad_sync import FusedGradSync
+            self.grad_sync = FusedGradSync(self)
+        self.last_step_ms = None
+        self._ev0, self._ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.kernel_launches = 0
+        log_info("[cuda] %s operands, %s activations+workspace, %s parameters (flat)" % (
+            "bf16" if self.dtype == torch.bfloat16 else "fp16",
+            _human(self.model.activation_bytes()), _human(n * 4)))
+
+    # ------------------------------------------------------------------ distributed
+    def sync_model(self):
+        if self.dist.world > 1:
+            self.dist.broadcast_(self.model.P, 0)
+            if self.model.moe_bias is not None:
+                self.dist.broadcast_(self.model.moe_bias, 0)
+            self.model.refresh_shadows()
+
+    # ------------------------------------------------------------------ muon (matrix-wise, reference arithmetic)
+    def _make_muon(self):
+        t = self.tcfg
+        specs = {s.name: s for s in self.mcfg.param_specs()}
+        named = self.model.layout.from_internal(self.model.P)
+        self._muon_w = {n: named[n].clone() for n in specs}
+        params = [O.OptParam(s.name, self._muon_w[s.name], s.decay) for s in self.mcfg.param_specs()]
+        return O.Muon(params, t.learning_rate, t.muon_vec_ratio, t.beta1, t.beta2, t.eps, t.weight_decay, t.grad_clip,
+                      t.muon_ns_steps, t.muon_min_ns_dim)
+
+    def _muon_step(self, lr, grad_scale):
+        m = self.model
+        named_g = m.layout.from_internal(m.Gr)
+        named_w = m.layout.from_internal(m.P)
+        for p in self.optimizer.params:
+            p.w.copy_(named_w[p.name])
+            p.w.grad = named_g[p.name].contiguous()
+        gnorm = self.optimizer.step(lr, grad_scale)
+        if math.isfinite(gnorm):
+            m.layout.to_internal({p.name: p.w for p in self.optimizer.params}, m.P)
+            m.refresh_shadows()
+        for p in self.optimizer.params:
+            p.w.grad = None
+        return gnorm
+
+    # ------------------------------------------------------------------ step protocol
+    def begin_step(self, step: int, loss_scale: float):
+        m = self.model
+        self._ev0.record()
+        m.zero_grad()
+        m.ce_acc.zero_()
+        m.aux_acc.zero_()
+        self.aux_weighted.zero_()
+        if m.bias_counts is not None:
+            m.bias_counts.zero_()
+        self._ntok = 0
+        self._loss_scale = float(loss_scale)
+        seed = jitter_seed_for(self.tcfg.seed, step, self.dist.rank)
+        self.seed_host[0] = seed - (1 << 64) if seed >= (1 << 63) else seed
+        m.seed_dev.copy_(self.seed_host, non_blocking=True)
+
+    def _run_micro(self):
+        m = self.model
+        freeze = self.tcfg.freeze_embeddings
+        if not self.tcfg.cuda_graphs:
+            m.forward_backward(freeze)
+        elif self.graph is not None:
+            self.graph.replay()
+        elif self._warm < 2:
+            m.forward_backward(freeze)
+            self._warm += 1
+        else:
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                m.forward_backward(freeze)
+            self.graph = g
+            g.replay()   # capture does not execute: run the micro-batch that triggered it
+        self.kernel_launches += m.launches_per_micro_batch()
+
+    def micro_step(self, ids, targets, segments, B, T):
+        m = self.model
+        ntok = int((targets.view(-1) >= 0).sum()) if not targets.is_cuda else int((targets >= 0).sum().item())
+        if ntok == 0:
+            return 0.0, 0    # nothing supervised: no forward/backward, no router counts
+        cfg = self.mcfg
+        self.dyn_host[0] = self._loss_scale
+        self.dyn_host[1] = (cfg.moe_aux_scale * self._loss_scale * ntok / cfg.num_layers *
+                            cfg.num_experts / float(B * T)) if cfg.use_moe else 0.0
+        m.dyn.copy_(self.dyn_host, non_blocking=True)
+        m.set_inputs(ids, targets, segments)
+        PERF.add("h2d_bytes", ids.numel() * 4 * (3 if m.use_segments else 2))
+        self._run_micro()
+        if cfg.use_moe and cfg.moe_aux_scale > 0:
+            self.aux_weighted.add_(m.aux_acc, alpha=float(ntok))
+            m.aux_acc.zero_()
+        self._ntok += ntok
+        return None, ntok
+
+    def end_step(self, lr: float) -> StepResult:
+        m, d, cfg = self.model, self.dist, self.mcfg
+        ntok_global = self._ntok
+        if d.world > 1:
+            self.ntok_dev[0] = self._ntok
+            d.all_reduce_sum_(self.ntok_dev)
+            if m.bias_counts is not None:
+                d.all_reduce_sum_(m.bias_counts)
+        gnorm, applied = 0.0, False
+        if d.world > 1:
+            ntok_global = int(self.ntok_dev.item())   # small host read; also orders the step on every rank
+        if ntok_global > 0:
+            grad_scale = float(_F32(1.0) / (_F32(ntok_global) * _F32(self._loss_scale)))
+            if self.tcfg.freeze_embeddings:
+                m.g("tok_embeddings").zero_()
+            if self.tcfg.optimizer == "muon":
+                if d.world > 1:
+                    d.all_reduce_sum_(m.Gr)
+                gnorm = self._muon_step(lr, grad_scale)
+                self.norm_out[1] = gnorm if math.isfinite(gnorm) else float("nan")
+            elif self.grad_sync is not None:
+                self.grad_sync.step(lr, grad_scale)
+            else:
+                if d.world > 1:
+                    d.all_reduce_sum_(m.Gr)
+                K.sqnorm_partial(m.Gr, self.sq_partial)
+                K.finish_norm(self.sq_partial, self.sq_partial.numel(), None, grad_scale, self.tcfg.grad_clip, self.norm_out)
+                self.optimizer.launch(lr, self.norm_out[0:1])
+        # ---- the one host read-back of the step
+        self._ev1.record()
+        rb = torch.cat([self.norm_out.double(), m.ce_acc, self.aux_weighted.double()])
+        self.readback[:5].copy_(rb, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        PERF.add("sync")
+        PERF.add("d2h_bytes", 40)
+        _lib.check_status(self.device, "training step")
+        self.last_step_ms = self._ev0.elapsed_time(self._ev1)
+        _, gn, loss_sum, rows, aux_w = (float(x) for x in self.readback[:5])
+        if ntok_global > 0:
+            gnorm = gn
+            applied = math.isfinite(gnorm)
+            if applied and self.tcfg.optimizer != "muon":
+                self.optimizer.t += 1
+        loss = 0.0
+        if self._ntok > 0:
+            loss = loss_sum / self._ntok
+            if cfg.use_moe and cfg.moe_aux_scale > 0:
+                loss += cfg.moe_aux_scale * aux_w / cfg.num_layers / self._ntok
+        if m.moe_bias is not None and applied:
+            moe_bias_update(m.moe_bias, m.bias_counts)
+        if applied and self.weight_ema is not None:
+            self.weight_ema.lerp_(m.P, 1.0 - self.tcfg.weight_ema)
+        PERF.add("opt_steps")
+        return StepResult(loss, self._ntok, ntok_global, gnorm, applied)
+
+    @torch.no_grad()
+    def eval_batch(self, ids, targets, segments, B, T):
+        m = self.model
+        m.ce_acc.zero_()
+        m.set_inputs(ids, targets, segments)
+        m.forward(False)
+        acc = m.ce_acc.cpu()
+        return float(acc[0]), int(acc[1])
+
+    def balance_report(self) -> str:
+        return ""
+
+    # ------------------------------------------------------------------ checkpoint state
+    def export_weights(self) -> List:
+        named = self.model.export_named()
+        return [(s.name, named[s.name]) for s in self.mcfg.param_specs()]
+
+    def import_weights(self, named: Dict[str, np.ndarray], strict=True) -> List[str]:
+        missing = self.model.load_named(named, missing_ok=not strict)
+        return missing
+
+    def export_moe_bias(self):
+        if self.model.moe_bias is None:
+            return []
+        return [np.ascontiguousarray(r.cpu().numpy()) for r in self.model.moe_bias]
+
+    def import_moe_bias(self, rows):
+        if self.model.moe_bias is None:
+            return
+        for l, r in enumerate(rows):
+            self.model.moe_bias[l].copy_(torch.as_tensor(np.asarray(r, dtype=np.float32)))
+
+    def export_optimizer(self) -> dict:
+        """Moments in the reference's per-parameter order and layout (replicated view of the flat state)."""
+        opt = self.optimizer
+        specs = self.mcfg.param_specs()
+        if self.tcfg.optimizer == "muon":
+            cpu = lambda t: None if t is None else np.ascontiguousarray(t.detach().cpu().numpy().reshape(-1))
+            return {"kind": "muon", "t": int(opt.t), "hyper": {k: (int(v) if isinstance(v, int) else float(v))
+                                                               for k, v in opt.hyper().items()},
+                    "m": [cpu(t) for t in opt.m], "v": [cpu(t) for t in opt.v], "fmt": 1}
+        m_named = self.model.export_named(opt.m_flat)
+        v_named = self.model.export_named(opt.v_flat) if opt.v_flat is not None else None
+        return {"kind": opt.kind, "t": int(opt.t), "hyper": {k: float(v) for k, v in opt.hyper().items()},
+                "m": [m_named[s.name].reshape(-1) for s in specs],
+                "v": [v_named[s.name].reshape(-1) if v_named is not None else None for s in specs], "fmt": 1}
+
+    def import_optimizer(self, blob: dict) -> bool:
+        opt = self.optimizer
+        specs = self.mcfg.param_specs()
+        if blob is None or blob.get("kind") != opt.kind or len(blob["m"]) != len(specs):
+            return False
+        if self.tcfg.optimizer == "muon":
+            for i, (mm, vv) in enumerate(zip(blob["m"], blob["v"])):
+                if mm is not None and opt.m[i] is not None:
+                    opt.m[i].copy_(torch.from_numpy(np.asarray(mm)).view_as(opt.m[i]))
+                if vv is not None and opt.v[i] is not None:
+                    opt.v[i].copy_(torch.from_numpy(np.asarray(vv)).view_as(opt.v[i]))
+        else:
+            for i, s in enumerate(specs):
+                if blob["m"][i] is not None and blob["m"][i].size != s.numel:
+                    return False
+            self.model.layout.to_internal({s.name: blob["m"][i].reshape(s.shape) for i, s in enumerate(specs)
+                                           if blob["m"][i] is not None}, opt.m_flat, missing_ok=True)
+            if opt.v_flat is not None:
+                self.model.layout.to_internal({s.name: blob["v"][i].reshape(s.shape) for i, s in enumerate(specs)
+                                               if blob["v"][i] is not None}, opt.v_flat, missing_ok=True)
+        opt.t = int(blob["t"])
+        h = blob["hyper"]
+        opt.beta1, opt.beta2 = float(h["beta1"]), float(h["beta2"])
+        if "eps" in h:
+            opt.eps = float(h["eps"])
+        return True
+
+    def optimizer_hyper(self) -> dict:
+        return self.optimizer.hyper()
+
+    def set_opt_step(self, t: int):
+        self.optimizer.t = int(t)
+
+
+def _human(n):
+    from ..utils.log import human_bytes
+    return human_bytes(n)
