@@ -408,6 +408,42 @@ class Trainer:
                                     "gnorm": gnorm, "tok_s_host": tps, "ntok": ntok, "device_ms": dev_ms,
                                     "loss_scale": self.scaler.for_step(), "tokens_seen": self.state.tokens_seen}) + "\n")
 
+    # ------------------------------------------------------------------ one optimizer step
+    def prepare(self):
+        """Plan the schedule and start the loader thread; ``run`` calls this, step-wise callers call it once."""
+        if self.total_steps == 0:
+            self._plan_schedule()
+        self.prefetch.start()
+
+    def train_step(self):
+        """One optimizer step: ``grad_accum`` micro-batches, gradient exchange, optimizer, scaler and state
+        bookkeeping.  Returns ``(StepResult, lr, host_seconds)``."""
+        c = self.cfg
+        t0 = time.perf_counter()
+        dscale = self.scaler.for_step()
+        self.engine.begin_step(self.state.step, dscale)
+        for _ in range(c.grad_accum):
+            self.phases.start("load")
+            b = self.prefetch.get()
+            self.phases.stop("load")
+            self.engine.micro_step(b.ids, b.targets, b.segments, b.B, b.T)
+        lr = self.sched.lr_at(self.state.step)
+        res = self.engine.end_step(lr)
+        loss = res.loss
+        self.ema_loss = loss if (self.state.step == 0 and self.ema_loss == 0.0) else 0.98 * self.ema_loss + 0.02 * loss
+        if res.ntok_global > 0 and not res.applied:
+            self.skipped_steps += 1
+        if res.ntok_global == 0:
+            log_warn("[train] all-masked step (ntok=0): optimizer skipped")
+        before = self.scaler.scale
+        self.scaler.update(res.gnorm)
+        if self.scaler.scale != before:
+            log_info("[scaler] step %d: scale %.0f -> %.0f" % (self.state.step, before, self.scaler.scale))
+        self.state.step += 1
+        self.state.tokens_seen += res.ntok_global
+        self.state.last_loss = loss
+        return res, lr, time.perf_counter() - t0
+
     # ------------------------------------------------------------------ the loop
     def run(self):
         STOP.install()
@@ -425,30 +461,8 @@ class Trainer:
         watchdog.start()
         try:
             while self.state.step < self.total_steps:
-                t0 = time.perf_counter()
-                dscale = self.scaler.for_step()
-                self.engine.begin_step(self.state.step, dscale)
-                for _ in range(c.grad_accum):
-                    self.phases.start("load")
-                    b = self.prefetch.get()
-                    self.phases.stop("load")
-                    self.engine.micro_step(b.ids, b.targets, b.segments, b.B, b.T)
-                lr = self.sched.lr_at(self.state.step)
-                res = self.engine.end_step(lr)
+                res, lr, dt = self.train_step()
                 loss = res.loss
-                self.ema_loss = loss if (self.state.step == 0 and self.ema_loss == 0.0) else 0.98 * self.ema_loss + 0.02 * loss
-                if res.ntok_global > 0 and not res.applied:
-                    self.skipped_steps += 1
-                if res.ntok_global == 0:
-                    log_warn("[train] all-masked step (ntok=0): optimizer skipped")
-                before = self.scaler.scale
-                self.scaler.update(res.gnorm)
-                if self.scaler.scale != before:
-                    log_info("[scaler] step %d: scale %.0f -> %.0f" % (self.state.step, before, self.scaler.scale))
-                self.state.step += 1
-                self.state.tokens_seen += res.ntok_global
-                self.state.last_loss = loss
-                dt = time.perf_counter() - t0
                 watchdog.kick()
                 main = self.is_main()
                 if main and c.log_every > 0 and self.state.step % c.log_every == 0:
