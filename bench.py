@@ -283,6 +283,7 @@ def run_reference(args):
     c.kv.pop("data.train_prefix", None)
     c.kv.pop("data.val_prefix", None)
     c.kv.pop("training.data_dir", None)
+    c.set("training.ddp", "true" if world > 1 else "false")   # the binary refuses ddp with one visible rank
     yml = os.path.join(work, "bench_recipe.yaml")
     dump_yaml(c, yml)
     shutil.rmtree(os.path.join(work, "ckpt"), ignore_errors=True)

@@ -1,0 +1,762 @@
+// Causal flash attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head_dim 64 or 128.
+//
+// Forward, one CTA per (batch, head, 128 query rows):
+//   warp 4 : TMA producer  - Q tile once, then K/V tiles of 128 keys through a 2-stage ring
+//   warp 5 : MMA issuer    - S = Q K^T into tensor memory, then O_part = P V (P read from shared memory)
+//   warps 0-3 (one thread per query row): tcgen05.ld of S, scale + causal/window/segment mask, online softmax,
+//            P (16-bit) written to shared memory in the 128-byte-swizzled operand layout, O rescaled and
+//            accumulated in registers, final normalisation, O and log-sum-exp stored.
+// The backward pass (further down) uses the same tile machinery: a dQ kernel per query tile and a dK/dV kernel
+// per key tile that loops over the query heads of its group, both recomputing P from the saved log-sum-exp.
+// Scores are never written to global memory (the reference materialises B*H*T^2 floats and re-runs the forward
+// in its backward, cuda/attention.cu:297-550, 805-898).
+//
+// Segment masks are passed as `lo[i]` = first key position visible to query i (start of its packed document,
+// or 0): visible(i, j) <=> max(lo[i], i - window + 1) <= j <= i.  Every wait is bounded (status word on expiry).
+#include <type_traits>
+
+#include "sm100_common.cuh"
+#include "gb_api.h"
+
+namespace gb {
+
+template <typename T> struct OperandFmt { static constexpr int value = std::is_same<T, __nv_bfloat16>::value ? 1 : 0; };
+
+constexpr int AT_M = 128;        // query rows per tile
+constexpr int AT_N = 128;        // keys per tile
+constexpr int AT_THREADS = 192;
+
+struct AttnTcParams {
+  int B, T, H, KV, window;
+  float scale;
+  const int* lo;          // [B*T] or null
+  void* o; long long ld_o;
+  float* lse;             // [B*T, H]
+  // backward
+  const float* delta;     // [B*T, H]
+  void* dq; long long ld_dq;
+  void* dk; long long ld_dk;
+  void* dv; long long ld_dv;
+  int* status;
+};
+
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, int* status, int code, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > 4000000000LL) {
+      atomicCAS(status, 0, code);
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// [rows x 64] 16-bit tile with 128-byte rows, 128B swizzle: byte offset of element (r, c), c < 64
+__device__ __forceinline__ uint32_t sw128_off(int r, int c) {
+  return (uint32_t)(r * 128 + ((((c >> 3) ^ (r & 7)) << 4) | ((c & 7) << 1)));
+}
+
+// write 32 consecutive columns [c0, c0+32) of row r into a [128 x 128] operand buffer made of two 64-column panels
+template <typename T>
+__device__ __forceinline__ void store_p_chunk(uint8_t* sP, int r, int c0, const float (&v)[32]) {
+  uint8_t* panel = sP + (c0 >> 6) * (AT_M * 128);
+  const int cc = c0 & 63;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 q;
+    q.x = Cvt<T>::pack2(v[8 * j + 0], v[8 * j + 1]);
+    q.y = Cvt<T>::pack2(v[8 * j + 2], v[8 * j + 3]);
+    q.z = Cvt<T>::pack2(v[8 * j + 4], v[8 * j + 5]);
+    q.w = Cvt<T>::pack2(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(panel + sw128_off(r, cc + 8 * j)) = q;
+  }
+}
+
+// TMA load of a [128 rows x HD] tile as HD/64 panels
+template <int HD>
+__device__ __forceinline__ void load_tile(const CUtensorMap* tm, uint64_t* bar, uint8_t* dst, int col0, int row0) {
+#pragma unroll
+  for (int p = 0; p < HD / 64; ++p) tma_load_2d(tm, bar, dst + p * (AT_M * 128), col0 + 64 * p, row0);
+}
+
+// D[128 x N] (+)= A[128 x K] * B, all operands in the panelled SW128 layout.
+//   a_kmajor tile: K runs along the 64-column panels.   b_mn: B given as [K rows x N cols] (N contiguous).
+template <int KDIM>
+__device__ __forceinline__ void mma_kmajor_kmajor(uint32_t tmem_d, uint32_t sa, uint32_t sb, uint32_t idesc, bool accumulate) {
+  // A: [128 x KDIM] K-major, B: [N x KDIM] K-major
+#pragma unroll
+  for (int kk = 0; kk < KDIM / 16; ++kk) {
+    const uint32_t off = (kk >> 2) * (AT_M * 128) + (kk & 3) * 32;
+    umma_f16(tmem_d, make_smem_desc_sw128(sa + off, 16, 1024), make_smem_desc_sw128(sb + off, 16, 1024), idesc,
+             (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+template <int KDIM>
+__device__ __forceinline__ void mma_kmajor_mnmajor(uint32_t tmem_d, uint32_t sa, uint32_t sb, uint32_t idesc, bool accumulate) {
+  // A: [128 x KDIM] K-major (panels of 64 along K), B: [KDIM rows x N] with N contiguous (panels of 64 along N)
+#pragma unroll
+  for (int kk = 0; kk < KDIM / 16; ++kk) {
+    const uint32_t aoff = (kk >> 2) * (AT_M * 128) + (kk & 3) * 32;
+    const uint32_t boff = kk * 2048;   // 16 rows of 128 bytes
+    umma_f16(tmem_d, make_smem_desc_sw128(sa + aoff, 16, 1024), make_smem_desc_sw128(sb + boff, AT_N * 128, 1024), idesc,
+             (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+// ============================================================================================ forward
+template <typename T, int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                 const __grid_constant__ CUtensorMap tmK,
+                                                                 const __grid_constant__ CUtensorMap tmV,
+                                                                 const AttnTcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t TILE = AT_M * HD * 2;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE;            // 2 stages
+  uint8_t* sV = sK + 2 * TILE;        // 2 stages
+  uint8_t* sP = sV + 2 * TILE;        // [128 x 128] 16-bit
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + AT_M * AT_N * 2);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * AT_M;
+  const int kvh = h / (p.H / p.KV);
+  const long long row_base = (long long)b * p.T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    *s_lo_min = 0x7fffffff;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + AT_N;
+
+  // visible key range of this tile: [k_lo, k_hi)
+  const int r = threadIdx.x;                  // query row for the first 128 threads
+  const int i = q0 + r;
+  const bool row_ok = r < AT_M && i < p.T;
+  int lo_i = 0;
+  if (row_ok) {
+    if (p.lo) lo_i = p.lo[row_base + i];
+    if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
+    atomicMin(s_lo_min, lo_i);
+  }
+  __syncthreads();
+  const int k_hi = min(p.T, q0 + AT_M);
+  const int k_lo = (min(*s_lo_min, k_hi - 1) / AT_N) * AT_N;
+  const int n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, TILE);
+      load_tile<HD>(&tmQ, q_full, sQ, h * HD, (int)row_base + q0);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t & 1, ph = (t >> 1) & 1;
+        if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
+        load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
+        load_tile<HD>(&tmV, &kv_full[s], sV + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr int fmt = OperandFmt<T>::value;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
+      const uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, AT_M, HD);
+      bool ok = at_wait(q_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int s = t & 1, ph = (t >> 1) & 1;
+        if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        tc_fence_after();
+        // S(t) may overwrite S(t-1) only after the softmax threads have read it: p_ready(t-1) was waited below
+        mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
+        umma_commit(s_full);
+        if (!at_wait(p_ready, t & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) break;
+        tc_fence_after();
+        mma_kmajor_mnmajor<AT_N>(tmem_O, smem_u32(sP), smem_u32(sV + s * TILE), idesc_o, false);
+        umma_commit(o_full);
+        umma_commit(&kv_empty[s]);
+      }
+    }
+    __syncwarp();
+  } else {
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float sc = p.scale;
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int j0 = k_lo + t * AT_N;
+      if (!at_wait(s_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
+      // pass A: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < AT_N / 32; ++c) {
+        uint32_t rg[32];
+        tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int j = j0 + c * 32 + k;
+          const bool vis = !need_mask || (j <= i && j >= lo_i);
+          if (vis) mx = fmaxf(mx, __uint_as_float(rg[k]) * sc);
+        }
+      }
+      if (!row_ok) mx = 0.f;
+      const float m_new = mx;
+      const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
+      float lsum = 0.f;
+      // pass B: probabilities -> shared memory (operand layout)
+#pragma unroll 1
+      for (int c = 0; c < AT_N / 32; ++c) {
+        uint32_t rg[32];
+        tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int j = j0 + c * 32 + k;
+          const bool vis = row_ok && (!need_mask || (j <= i && j >= lo_i));
+          const float e = (vis && m_new != -INFINITY) ? __expf(__uint_as_float(rg[k]) * sc - m_new) : 0.f;
+          pv[k] = e;
+          lsum += e;
+        }
+        store_p_chunk<T>(sP, r, c * 32, pv);
+      }
+      l = l * corr + lsum;
+      m = m_new;
+      tc_fence_before();
+      fence_proxy_async();          // generic-proxy writes of P must be visible to the tensor core
+      mbar_arrive(p_ready);
+      if (!at_wait(o_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t rg[32];
+        tmem_ld_32x32(tmem_O + lane_base + c * 32, rg);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) o[c * 32 + k] = o[c * 32 + k] * corr + __uint_as_float(rg[k]);
+      }
+      tc_fence_before();
+    }
+    if (ok && row_ok) {
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      T* op = reinterpret_cast<T*>(p.o) + (row_base + i) * p.ld_o + (long long)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
+        uint4 q;
+        q.x = Cvt<T>::pack2(o[8 * c + 0] * inv_l, o[8 * c + 1] * inv_l);
+        q.y = Cvt<T>::pack2(o[8 * c + 2] * inv_l, o[8 * c + 3] * inv_l);
+        q.z = Cvt<T>::pack2(o[8 * c + 4] * inv_l, o[8 * c + 5] * inv_l);
+        q.w = Cvt<T>::pack2(o[8 * c + 6] * inv_l, o[8 * c + 7] * inv_l);
+        reinterpret_cast<uint4*>(op)[c] = q;
+      }
+      if (p.lse) p.lse[(row_base + i) * p.H + h] = l > 0.f ? m + __logf(l) : INFINITY;
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
+// ============================================================================================ backward: dQ
+// One CTA per (batch, head, 128 query rows).  Per key tile: S = Q K^T and dP = dO V^T into tensor memory,
+// dS = P o (dP - delta) * scale written to shared memory (16-bit operand layout), dQ += dS K accumulated in
+// tensor memory over the whole key loop and read out once.
+template <typename T, int HD, int STAGES>
+__global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                    const __grid_constant__ CUtensorMap tmK,
+                                                                    const __grid_constant__ CUtensorMap tmV,
+                                                                    const __grid_constant__ CUtensorMap tmDO,
+                                                                    const AttnTcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t TILE = AT_M * HD * 2;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + TILE;
+  uint8_t* sK = sDO + TILE;                 // STAGES
+  uint8_t* sV = sK + STAGES * TILE;         // STAGES
+  uint8_t* sDS = sV + STAGES * TILE;        // [128 x 128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + AT_M * AT_N * 2);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;             // STAGES (<= 2)
+  uint64_t* kv_empty = bars + 3;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* ds_ready = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * AT_M;
+  const int kvh = h / (p.H / p.KV);
+  const long long row_base = (long long)b * p.T;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 128);
+    mbar_init(dq_full, 1);
+    *abort_flag = 0;
+    *s_lo_min = 0x7fffffff;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + AT_N, tmem_dQ = tmem_base + 2 * AT_N;
+
+  const int r = threadIdx.x;
+  const int i = q0 + r;
+  const bool row_ok = r < AT_M && i < p.T;
+  int lo_i = 0;
+  if (row_ok) {
+    if (p.lo) lo_i = p.lo[row_base + i];
+    if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
+    atomicMin(s_lo_min, lo_i);
+  }
+  __syncthreads();
+  const int k_hi = min(p.T, q0 + AT_M);
+  const int k_lo = (min(*s_lo_min, k_hi - 1) / AT_N) * AT_N;
+  const int n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 2 * TILE);
+      load_tile<HD>(&tmQ, q_full, sQ, h * HD, (int)row_base + q0);
+      load_tile<HD>(&tmDO, q_full, sDO, h * HD, (int)row_base + q0);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % STAGES, ph = (t / STAGES) & 1;
+        if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
+        load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
+        load_tile<HD>(&tmV, &kv_full[s], sV + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr int fmt = OperandFmt<T>::value;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
+      const uint32_t idesc_dq = make_idesc_f16(fmt, 0, 1, AT_M, HD);
+      bool ok = at_wait(q_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int s = t % STAGES, ph = (t / STAGES) & 1;
+        if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
+        mma_kmajor_kmajor<HD>(tmem_dP, smem_u32(sDO), smem_u32(sV + s * TILE), idesc_s, false);
+        umma_commit(sdp_full);
+        if (!at_wait(ds_ready, t & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmajor_mnmajor<AT_N>(tmem_dQ, smem_u32(sDS), smem_u32(sK + s * TILE), idesc_dq, t > 0);
+        umma_commit(&kv_empty[s]);
+      }
+      if (ok) umma_commit(dq_full);
+    }
+    __syncwarp();
+  } else {
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float sc = p.scale;
+    float lse = INFINITY, dl = 0.f;
+    if (row_ok) {
+      lse = p.lse[(row_base + i) * p.H + h];
+      dl = p.delta[(row_base + i) * p.H + h];
+    }
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int j0 = k_lo + t * AT_N;
+      if (!at_wait(sdp_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
+#pragma unroll 1
+      for (int c = 0; c < AT_N / 32; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_S + lane_base + c * 32, rs);
+        tmem_ld_32x32(tmem_dP + lane_base + c * 32, rp);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int j = j0 + c * 32 + k;
+          const bool vis = row_ok && (!need_mask || (j <= i && j >= lo_i));
+          const float pr = vis ? __expf(__uint_as_float(rs[k]) * sc - lse) : 0.f;
+          ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+        }
+        store_p_chunk<T>(sDS, r, c * 32, ds);
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(ds_ready);
+    }
+    if (ok && at_wait(dq_full, 0, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) {
+      tc_fence_after();
+      T* dqp = reinterpret_cast<T*>(p.dq) + (row_base + i) * p.ld_dq + (long long)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t rg[32];
+        tmem_ld_32x32(tmem_dQ + lane_base + c * 32, rg);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 q;
+            q.x = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 0]), __uint_as_float(rg[8 * k + 1]));
+            q.y = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 2]), __uint_as_float(rg[8 * k + 3]));
+            q.z = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 4]), __uint_as_float(rg[8 * k + 5]));
+            q.w = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 6]), __uint_as_float(rg[8 * k + 7]));
+            reinterpret_cast<uint4*>(dqp + c * 32)[k] = q;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ============================================================================================ backward: dK, dV
+// One CTA per (batch, kv head, 128 key rows).  Loops over the query heads that share the kv head and over the
+// query tiles at or after the key tile.  Per iteration: S^T = K Q^T and dP^T = V dO^T into tensor memory (rows =
+// keys, columns = queries), P^T and dS^T written to shared memory, dV += P^T dO and dK += dS^T Q accumulated in
+// tensor memory over all iterations (ordered, so the GQA reduction is deterministic) and read out once.
+template <typename T, int HD, int STAGES>
+__global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                     const __grid_constant__ CUtensorMap tmK,
+                                                                     const __grid_constant__ CUtensorMap tmV,
+                                                                     const __grid_constant__ CUtensorMap tmDO,
+                                                                     const AttnTcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t TILE = AT_M * HD * 2;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;                  // STAGES
+  uint8_t* sDO = sQ + STAGES * TILE;        // STAGES
+  uint8_t* sPT = sDO + STAGES * TILE;       // [128 keys x 128 queries]
+  uint8_t* sDST = sPT + AT_M * AT_N * 2;
+  float* sLse = reinterpret_cast<float*>(sDST + AT_M * AT_N * 2);   // [2][128]
+  float* sDl = sLse + 2 * AT_N;
+  int* sLo = reinterpret_cast<int*>(sDl + 2 * AT_N);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sLo + 2 * AT_N);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;              // 2
+  uint64_t* q_empty = bars + 3;             // 2
+  uint64_t* st_full = bars + 5;
+  uint64_t* pt_ready = bars + 6;
+  uint64_t* dkv_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, kvh = blockIdx.y, j0 = blockIdx.x * AT_N;
+  const int group = p.H / p.KV;
+  const long long row_base = (long long)b * p.T;
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(st_full, 1);
+    mbar_init(pt_ready, 128);
+    mbar_init(dkv_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + AT_M, tmem_dV = tmem_base + 2 * AT_M,
+                 tmem_dK = tmem_base + 2 * AT_M + HD;
+
+  const int i_lo = j0;   // key tile and query tiles share the 128-row grid
+  int i_hi = p.T;
+  if (p.window > 0) i_hi = min(p.T, j0 + AT_N - 1 + p.window);
+  const int n_qt = (i_hi - i_lo + AT_M - 1) / AT_M;
+  const int n_it = group * n_qt;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * TILE);
+      load_tile<HD>(&tmK, kv_full, sK, kvh * HD, (int)row_base + j0);
+      load_tile<HD>(&tmV, kv_full, sV, kvh * HD, (int)row_base + j0);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it % STAGES, ph = (it / STAGES) & 1;
+        const int h = kvh * group + it / n_qt;
+        const int i0 = i_lo + (it % n_qt) * AT_M;
+        if (!at_wait(&q_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(&q_full[s], 2 * TILE);
+        load_tile<HD>(&tmQ, &q_full[s], sQ + s * TILE, h * HD, (int)row_base + i0);
+        load_tile<HD>(&tmDO, &q_full[s], sDO + s * TILE, h * HD, (int)row_base + i0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr int fmt = OperandFmt<T>::value;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
+      const uint32_t idesc_d = make_idesc_f16(fmt, 0, 1, AT_M, HD);
+      bool ok = at_wait(kv_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % STAGES, ph = (it / STAGES) & 1;
+        if (!at_wait(&q_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmajor_kmajor<HD>(tmem_ST, smem_u32(sK), smem_u32(sQ + s * TILE), idesc_s, false);
+        mma_kmajor_kmajor<HD>(tmem_dPT, smem_u32(sV), smem_u32(sDO + s * TILE), idesc_s, false);
+        umma_commit(st_full);
+        if (!at_wait(pt_ready, it & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        mma_kmajor_mnmajor<AT_M>(tmem_dV, smem_u32(sPT), smem_u32(sDO + s * TILE), idesc_d, it > 0);
+        mma_kmajor_mnmajor<AT_M>(tmem_dK, smem_u32(sDST), smem_u32(sQ + s * TILE), idesc_d, it > 0);
+        umma_commit(&q_empty[s]);
+      }
+      if (ok) umma_commit(dkv_full);
+    }
+    __syncwarp();
+  } else {
+    const int r = threadIdx.x;          // key row of this thread
+    const int j = j0 + r;
+    const bool row_ok = j < p.T;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float sc = p.scale;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = kvh * group + it / n_qt;
+      const int i0 = i_lo + (it % n_qt) * AT_M;
+      const int bufi = it & 1;
+      {  // stage the per-query statistics of this tile (column r)
+        const int i = i0 + r;
+        const bool in = i < p.T;
+        sLse[bufi * AT_N + r] = in ? p.lse[(row_base + i) * p.H + h] : INFINITY;
+        sDl[bufi * AT_N + r] = in ? p.delta[(row_base + i) * p.H + h] : 0.f;
+        int lo = 0;
+        if (in && p.lo) lo = p.lo[row_base + i];
+        if (in && p.window > 0) lo = max(lo, i - p.window + 1);
+        sLo[bufi * AT_N + r] = in ? lo : 0x7fffffff;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // after a failed wait the loop keeps running (without waiting or computing) so that every thread still
+      // reaches the named barrier above in every iteration
+      if (ok && !at_wait(st_full, it & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
+      if (!ok) continue;
+      tc_fence_after();
+      const float* lse = sLse + bufi * AT_N;
+      const float* dl = sDl + bufi * AT_N;
+      const int* lo = sLo + bufi * AT_N;
+#pragma unroll 1
+      for (int c = 0; c < AT_M / 32; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_ST + lane_base + c * 32, rs);
+        tmem_ld_32x32(tmem_dPT + lane_base + c * 32, rp);
+        tmem_ld_wait();
+        float pt[32], ds[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int col = c * 32 + k;
+          const int i = i0 + col;
+          const bool vis = row_ok && j <= i && j >= lo[col];
+          const float pr = vis ? __expf(__uint_as_float(rs[k]) * sc - lse[col]) : 0.f;
+          pt[k] = pr;
+          ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+        }
+        store_p_chunk<T>(sPT, r, c * 32, pt);
+        store_p_chunk<T>(sDST, r, c * 32, ds);
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      mbar_arrive(pt_ready);
+    }
+    if (ok && at_wait(dkv_full, 0, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) {
+      tc_fence_after();
+      T* dkp = reinterpret_cast<T*>(p.dk) + (row_base + j) * p.ld_dk + (long long)kvh * HD;
+      T* dvp = reinterpret_cast<T*>(p.dv) + (row_base + j) * p.ld_dv + (long long)kvh * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t rv[32], rk[32];
+        tmem_ld_32x32(tmem_dV + lane_base + c * 32, rv);
+        tmem_ld_32x32(tmem_dK + lane_base + c * 32, rk);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 qv, qk;
+            qv.x = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 0]), __uint_as_float(rv[8 * k + 1]));
+            qv.y = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 2]), __uint_as_float(rv[8 * k + 3]));
+            qv.z = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 4]), __uint_as_float(rv[8 * k + 5]));
+            qv.w = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 6]), __uint_as_float(rv[8 * k + 7]));
+            qk.x = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 0]), __uint_as_float(rk[8 * k + 1]));
+            qk.y = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 2]), __uint_as_float(rk[8 * k + 3]));
+            qk.z = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 4]), __uint_as_float(rk[8 * k + 5]));
+            qk.w = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 6]), __uint_as_float(rk[8 * k + 7]));
+            reinterpret_cast<uint4*>(dvp + c * 32)[k] = qv;
+            reinterpret_cast<uint4*>(dkp + c * 32)[k] = qk;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// lo[i] = first position of the run of equal segment ids that contains i (per sequence); seg < 0 -> 0
+__global__ void attn_seg_lo_kernel(const int* __restrict__ seg, int* __restrict__ lo, int B, int T) {
+  const long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (g >= (long long)B * T) return;
+  const int i = (int)(g % T);
+  const long long base = g - i;
+  const int s = seg[g];
+  if (s < 0) { lo[g] = 0; return; }
+  int j = i;
+  while (j > 0 && seg[base + j - 1] == s) --j;
+  lo[g] = j;
+}
+
+template <typename T, int HD>
+int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) {
+  CUtensorMap tq, tk, tv;
+  const long long rows = (long long)a->B * a->T;
+  if (gb_make_tmap_2d_16b(&tq, a->q, rows, (uint64_t)a->H * HD, a->ld_q, AT_M, 64, a->is_bf16)) return -20;
+  if (gb_make_tmap_2d_16b(&tk, a->k, rows, (uint64_t)a->KV * HD, a->ld_k, AT_N, 64, a->is_bf16)) return -21;
+  if (gb_make_tmap_2d_16b(&tv, a->v, rows, (uint64_t)a->KV * HD, a->ld_v, AT_N, 64, a->is_bf16)) return -22;
+  AttnTcParams p{};
+  p.B = a->B; p.T = a->T; p.H = a->H; p.KV = a->KV; p.window = a->window; p.scale = a->scale;
+  p.lo = lo; p.o = a->o; p.ld_o = a->ld_o; p.lse = a->lse; p.status = status;
+  constexpr size_t smem = (size_t)AT_M * HD * 2 * 5 + AT_M * AT_N * 2 + 128 + 1024;
+  auto kern = attn_tc_fwd_kernel<T, HD>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -10;
+    attr = true;
+  }
+  dim3 grid((a->T + AT_M - 1) / AT_M, a->H, a->B);
+  kern<<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <typename T>
+__global__ void attn_tc_delta_kernel(const T* __restrict__ d_o, long long ld_do, const T* __restrict__ o, long long ld_o,
+                                     float* __restrict__ delta, long long n_tok, int H, int hd) {
+  const long long gw = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (gw >= n_tok * H) return;
+  const long long t = gw / H;
+  const int h = (int)(gw - t * H);
+  const T* a = d_o + t * ld_do + (long long)h * hd;
+  const T* b = o + t * ld_o + (long long)h * hd;
+  float s = 0.f;
+  for (int d = lane; d < hd; d += 32) s += Cvt<T>::to_f(a[d]) * Cvt<T>::to_f(b[d]);
+  s = warp_sum(s);
+  if (lane == 0) delta[gw] = s;
+}
+
+template <typename T, int HD>
+int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) {
+  constexpr int STAGES = HD == 64 ? 2 : 1;
+  CUtensorMap tq, tk, tv, tdo;
+  const long long rows = (long long)a->B * a->T;
+  if (gb_make_tmap_2d_16b(&tq, a->q, rows, (uint64_t)a->H * HD, a->ld_q, AT_M, 64, a->is_bf16)) return -20;
+  if (gb_make_tmap_2d_16b(&tk, a->k, rows, (uint64_t)a->KV * HD, a->ld_k, AT_N, 64, a->is_bf16)) return -21;
+  if (gb_make_tmap_2d_16b(&tv, a->v, rows, (uint64_t)a->KV * HD, a->ld_v, AT_N, 64, a->is_bf16)) return -22;
+  if (gb_make_tmap_2d_16b(&tdo, a->d_o, rows, (uint64_t)a->H * HD, a->ld_do, AT_M, 64, a->is_bf16)) return -23;
+  attn_tc_delta_kernel<T><<<(unsigned)((rows * a->H + 7) / 8), 256, 0, st>>>(
+      reinterpret_cast<const T*>(a->d_o), a->ld_do, reinterpret_cast<const T*>(a->o), a->ld_o, a->delta, rows, a->H, HD);
+  AttnTcParams p{};
+  p.B = a->B; p.T = a->T; p.H = a->H; p.KV = a->KV; p.window = a->window; p.scale = a->scale;
+  p.lo = lo; p.lse = a->lse; p.delta = a->delta; p.status = status;
+  p.dq = a->dq; p.ld_dq = a->ld_dq; p.dk = a->dk; p.ld_dk = a->ld_dk; p.dv = a->dv; p.ld_dv = a->ld_dv;
+  constexpr size_t TILE = (size_t)AT_M * HD * 2;
+  constexpr size_t smem_q = TILE * (2 + 2 * STAGES) + AT_M * AT_N * 2 + 128 + 1024;
+  constexpr size_t smem_kv = TILE * (2 + 2 * STAGES) + 2 * AT_M * AT_N * 2 + 6 * AT_N * 4 + 128 + 1024;
+  auto kq = attn_tc_bwd_dq_kernel<T, HD, STAGES>;
+  auto kkv = attn_tc_bwd_dkv_kernel<T, HD, STAGES>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv) != cudaSuccess) return -10;
+    attr = true;
+  }
+  dim3 gq((a->T + AT_M - 1) / AT_M, a->H, a->B), gkv((a->T + AT_N - 1) / AT_N, a->KV, a->B);
+  kq<<<gq, AT_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
+  kkv<<<gkv, AT_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+extern "C" int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st) {
+  if (!a || !status || a->B <= 0 || a->T <= 0 || a->H % a->KV) return -1;
+  if (a->hd != 64 && a->hd != 128) return -2;
+  if (!a->d_o || !a->delta || !a->lse || !a->dq || !a->dk || !a->dv || !a->o) return -1;
+  if (a->seg && !lo_scratch) return -1;
+  int* lo = nullptr;
+  if (a->seg) {
+    const long long n = (long long)a->B * a->T;
+    attn_seg_lo_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a->seg, lo_scratch, a->B, a->T);
+    lo = lo_scratch;
+  }
+  if (a->is_bf16) return a->hd == 64 ? launch_tc_bwd<__nv_bfloat16, 64>(a, lo, status, st) : launch_tc_bwd<__nv_bfloat16, 128>(a, lo, status, st);
+  return a->hd == 64 ? launch_tc_bwd<__half, 64>(a, lo, status, st) : launch_tc_bwd<__half, 128>(a, lo, status, st);
+}
+
+// Tensor-core attention forward.  `lo_scratch` ([B*T] int32) is needed when a->seg is given: segment ids must form
+// contiguous runs inside each sequence (packed documents).  Supports head_dim 64 and 128; other sizes: gb_attn_fwd.
+extern "C" int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st) {
+  if (!a || !status || a->B <= 0 || a->T <= 0 || a->H % a->KV) return -1;
+  if (a->hd != 64 && a->hd != 128) return -2;
+  if (a->seg && !lo_scratch) return -1;
+  int* lo = nullptr;
+  if (a->seg) {
+    const long long n = (long long)a->B * a->T;
+    attn_seg_lo_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a->seg, lo_scratch, a->B, a->T);
+    lo = lo_scratch;
+  }
+  if (a->is_bf16) return a->hd == 64 ? launch_tc_fwd<__nv_bfloat16, 64>(a, lo, status, st) : launch_tc_fwd<__nv_bfloat16, 128>(a, lo, status, st);
+  return a->hd == 64 ? launch_tc_fwd<__half, 64>(a, lo, status, st) : launch_tc_fwd<__half, 128>(a, lo, status, st);
+}

@@ -326,8 +326,8 @@ extern "C" int gb_rmsnorm_fwd(const float* x, const float* w, void* y, float* rr
 
 // Number of row blocks (and rows of the partial buffer) gb_rmsnorm_bwd uses for `rows`.
 extern "C" int gb_rmsnorm_bwd_blocks(int rows) {
-  int b = (rows + 63) / 64;
-  return b > 592 ? 592 : (b < 1 ? 1 : b);
+  int b = (rows + 7) / 8;   // one row per warp while that still fits a modest partial buffer
+  return b > 296 ? 296 : (b < 1 ? 1 : b);
 }
 
 // dw (fp32 [d]) is accumulated (+=).  `part` must hold gb_rmsnorm_bwd_blocks(rows) * d floats.
@@ -355,7 +355,7 @@ extern "C" int gb_rmsnorm_bwd(const void* g, const float* x, const float* w, con
 }
 
 extern "C" int gb_qk_rope_blocks(int n_items) {
-  int b = (n_items + 255) / 256;
+  int b = (n_items + 31) / 32;
   return b > 592 ? 592 : (b < 1 ? 1 : b);
 }
 

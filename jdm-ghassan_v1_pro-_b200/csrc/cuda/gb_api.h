@@ -74,6 +74,11 @@ typedef struct gb_attn_args {
 } gb_attn_args;
 int gb_attn_fwd(const gb_attn_args* a, cudaStream_t st);
 int gb_attn_bwd(const gb_attn_args* a, cudaStream_t st);
+// Tensor-core (tcgen05) versions for head_dim 64 / 128.  Segment ids must form contiguous runs per sequence;
+// lo_scratch: [B*T] int32 (needed when a->seg != NULL); status: device status word.
+int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st);
+// dq_acc: fp32 scratch [B*T, H*hd] is not needed: dQ accumulates in tensor memory.  delta is computed inside.
+int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st);
 
 // ----------------------------------------------------------------------------- moe.cu
 typedef struct gb_moe_args {
@@ -115,7 +120,9 @@ typedef struct gb_moe_args {
   float* aux_acc;                    // [1] += ne * sum_e aux_m[e] * f[e] of this call (needs aux_m), or NULL
   const unsigned long long* dyn_seed;// device copy of jitter_seed (overrides it; lets a captured graph change seeds)
   const float* dyn_aux_coef;         // device copy of aux_coef (overrides it)
+  float* part2;                      // scratch [GB_ROUTER_WGRAD_CHUNKS, ne, d] for the router weight gradient, or NULL
 } gb_moe_args;
+#define GB_ROUTER_WGRAD_CHUNKS 32
 int gb_moe_num_blocks(int n_tok);
 int gb_moe_capacity(int n_tok, int ne, int top_k, int shared);
 int gb_moe_route(const gb_moe_args* a, cudaStream_t st);          // router + top-k + histograms

@@ -15,7 +15,10 @@
 
 namespace gb {
 
-constexpr int BLK_TOK = 256;   // tokens per routing block
+constexpr int BLK_TOK = 256;   // most tokens a routing block handles
+// Tokens per routing block: small blocks for small batches so that the grid covers the GPU, large blocks for
+// large batches so that the single-block scan over [blocks, experts] stays short.
+__host__ __device__ inline int blk_tok(int n_tok) { return n_tok < 8192 ? 8 : (n_tok < 65536 ? 64 : BLK_TOK); }
 constexpr int MAX_NE = 64;
 constexpr int MAX_K = 8;
 
@@ -46,8 +49,9 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
   const int ne = a.ne, K = a.top_k, d = a.d;
   for (int i = threadIdx.x; i <= ne; i += blockDim.x) s_hist[i] = 0;
   __syncthreads();
-  const int t0 = blockIdx.x * BLK_TOK;
-  const int t1 = min(a.n_tok, t0 + BLK_TOK);
+  const int bt = blk_tok(a.n_tok);
+  const int t0 = blockIdx.x * bt;
+  const int t1 = min(a.n_tok, t0 + bt);
   const T* x16 = reinterpret_cast<const T*>(a.x16);
   const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;   // device copy wins (graph replay)
   for (int t = t0 + warp; t < t1; t += 8) {
@@ -178,8 +182,9 @@ __global__ void __launch_bounds__(256) moe_pack_kernel(const gb_moe_args a) {
   __shared__ int s_pos[BLK_TOK * (MAX_K + 1)];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
-  const int t0 = blockIdx.x * BLK_TOK;
-  const int nt = min(a.n_tok, t0 + BLK_TOK) - t0;
+  const int bt = blk_tok(a.n_tok);
+  const int t0 = blockIdx.x * bt;
+  const int nt = min(a.n_tok, t0 + bt) - t0;
   for (int i = threadIdx.x; i < nt * K; i += blockDim.x) s_idx[i] = a.idx[(size_t)t0 * K + i];
   __syncthreads();
   const int* base = a.block_base + (size_t)blockIdx.x * (ne + 1);
@@ -381,12 +386,38 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
 template <typename T>
 __global__ void moe_router_wgrad_kernel(const float* __restrict__ dlogit, const T* __restrict__ x16,
                                         float* __restrict__ dw, int n_tok, int ne, int d) {
+  // grid (d/128, token chunks, expert groups of 8); with more than one token chunk `dw` is a partial buffer
+  // [chunks, ne, d] that moe_router_wgrad_fold_kernel adds up in chunk order.
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int e = blockIdx.y;
+  const int e0 = blockIdx.z * 8;
   if (c >= d) return;
-  float acc = 0.f;
-  for (int t = 0; t < n_tok; ++t) acc += dlogit[(size_t)t * ne + e] * Cvt<T>::to_f(x16[(size_t)t * d + c]);
-  dw[(size_t)e * d + c] += acc;
+  const int chunks = gridDim.y;
+  const int per = (n_tok + chunks - 1) / chunks;
+  const int ta = blockIdx.y * per, tb = min(n_tok, ta + per);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int t = ta; t < tb; ++t) {
+    const float xv = Cvt<T>::to_f(x16[(size_t)t * d + c]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (e0 + j < ne) acc[j] += dlogit[(size_t)t * ne + e0 + j] * xv;
+  }
+  float* out = dw + (chunks > 1 ? (size_t)blockIdx.y * ne * d : 0);
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (e0 + j < ne) {
+      if (chunks > 1) out[(size_t)(e0 + j) * d + c] = acc[j];
+      else out[(size_t)(e0 + j) * d + c] += acc[j];
+    }
+}
+
+__global__ void moe_router_wgrad_fold_kernel(const float* __restrict__ part, float* __restrict__ dw, int chunks, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int z = 0; z < chunks; ++z) s += part[(size_t)z * n + i];
+  dw[i] += s;
 }
 
 }  // namespace gb
@@ -399,7 +430,7 @@ static int moe_check(const gb_moe_args* a) {
   return 0;
 }
 
-extern "C" int gb_moe_num_blocks(int n_tok) { return (n_tok + BLK_TOK - 1) / BLK_TOK; }
+extern "C" int gb_moe_num_blocks(int n_tok) { return (n_tok + blk_tok(n_tok) - 1) / blk_tok(n_tok); }
 
 extern "C" int gb_moe_capacity(int n_tok, int ne, int top_k, int shared) {
   const long long slots = (long long)n_tok * (top_k + (shared ? 1 : 0));
@@ -467,17 +498,24 @@ extern "C" int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st) {
   int rc = moe_check(a);
   if (rc) return rc;
   const int grid = (a->n_tok + 7) / 8;
-  dim3 g2((a->d + 255) / 256, a->ne);
+  // token chunks for the router weight gradient: partials in part2 ([chunks, ne, d]) when it is provided
+  int chunks = a->part2 ? (a->n_tok + 31) / 32 : 1;
+  if (chunks > GB_ROUTER_WGRAD_CHUNKS) chunks = GB_ROUTER_WGRAD_CHUNKS;
+  dim3 g2((a->d + 127) / 128, chunks, (a->ne + 7) / 8);
+  float* wout = chunks > 1 ? a->part2 : a->d_router_w;
   if (a->is_bf16) {
     moe_router_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*a);
     if (a->d_router_w)
-      moe_router_wgrad_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>(a->part, (const __nv_bfloat16*)a->x16, a->d_router_w,
-                                                                 a->n_tok, a->ne, a->d);
+      moe_router_wgrad_kernel<__nv_bfloat16><<<g2, 128, 0, st>>>(a->part, (const __nv_bfloat16*)a->x16, wout, a->n_tok,
+                                                                 a->ne, a->d);
   } else {
     moe_router_bwd_kernel<__half><<<grid, 256, 0, st>>>(*a);
     if (a->d_router_w)
-      moe_router_wgrad_kernel<__half><<<g2, 256, 0, st>>>(a->part, (const __half*)a->x16, a->d_router_w, a->n_tok, a->ne,
-                                                          a->d);
+      moe_router_wgrad_kernel<__half><<<g2, 128, 0, st>>>(a->part, (const __half*)a->x16, wout, a->n_tok, a->ne, a->d);
+  }
+  if (a->d_router_w && chunks > 1) {
+    const int n = a->ne * a->d;
+    moe_router_wgrad_fold_kernel<<<(n + 255) / 256, 256, 0, st>>>(a->part2, a->d_router_w, chunks, n);
   }
   return GB_OK();
 }

@@ -66,14 +66,29 @@ class DataLoader:
             self.s.set_vocab(self.vocab)
         return self._opened
 
-    def _buf(self):
+    def set_ring(self, n: int):
+        """Stage batches in a ring of ``n`` pre-pinned buffer triples instead of pinning fresh memory per batch
+        (pinning allocates through the driver and stalls the device).  ``n`` must exceed the number of batches
+        that can be in flight between two host synchronisations (grad_accum + prefetch depth + 1)."""
+        self._ring = [tuple(self._new_buf() for _ in range(3)) for _ in range(max(1, n))]
+        self._ring_pos = 0
+
+    def _new_buf(self):
         t = torch.empty(self.B * self.T, dtype=torch.int32)
         return t.pin_memory() if self.pin else t
+
+    def _bufs(self):
+        ring = getattr(self, "_ring", None)
+        if not ring:
+            return self._new_buf(), self._new_buf(), self._new_buf()
+        out = ring[self._ring_pos]
+        self._ring_pos = (self._ring_pos + 1) % len(ring)
+        return out
 
     def next(self) -> Batch:
         if not self._opened:
             raise RuntimeError("dataloader has no shards")
-        ids, tgt, seg = self._buf(), self._buf(), self._buf()
+        ids, tgt, seg = self._bufs()
         sup = self.s.next(ids.numpy(), tgt.numpy(), seg.numpy())
         return Batch(ids, tgt, seg, self.B, self.T, int(sup), self.s.get_state())
 

@@ -255,6 +255,7 @@ class CudaModel:
         if cfg.use_moe:
             t.dy_perm, t.dxperm = torch.zeros(rows, d, **c16), torch.zeros(rows, d, **c16)
             t.gdot, t.part = torch.empty(N, cfg.moe_top_k, **f32), torch.empty(N, cfg.num_experts, **f32)
+            t.part2 = torch.empty(K.ROUTER_WGRAD_CHUNKS * cfg.num_experts * d, **f32)
         else:
             t.dact = torch.empty(N, E, **c16)
         t.norm_part = K.rmsnorm_bwd_scratch(N, d, dev)
@@ -395,7 +396,7 @@ class CudaModel:
             want_aux = cfg.moe_aux_scale > 0
             K.moe_router_bwd(ws, b.xb2, self.w(p + "router"), t.gdot, t.dxperm, t.dxb, self.g(p + "router"), t.part,
                              jitter=cfg.moe_jitter, seed_dev=self.seed_dev if cfg.moe_jitter > 0 else None,
-                             aux_coef_dev=self.dyn[1:2] if want_aux else None)
+                             aux_coef_dev=self.dyn[1:2] if want_aux else None, part2=t.part2)
         else:
             G.gemm_swiglu_bwd(t.dx16, self.w16(p + "w_down"), b.gu, dgu_out=t.dgu, n=E)
             gd = self.g(p + "w_down")

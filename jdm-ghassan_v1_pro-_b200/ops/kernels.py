@@ -45,7 +45,9 @@ class MoeArgs(ctypes.Structure):
                 ("dout", c_void_p), ("dy_perm", c_void_p), ("gdot", c_void_p), ("dx_perm", c_void_p),
                 ("aux_coef", c_float), ("f_frac", c_void_p), ("d_router_w", c_void_p), ("dx16", c_void_p),
                 ("aux_m", c_void_p), ("part", c_void_p), ("aux_acc", c_void_p), ("dyn_seed", c_void_p),
-                ("dyn_aux_coef", c_void_p)]
+                ("dyn_aux_coef", c_void_p), ("part2", c_void_p)]
+
+ROUTER_WGRAD_CHUNKS = 32
 
 
 class OptArgs(ctypes.Structure):
@@ -171,6 +173,27 @@ def attn_bwd(q, k, v, o, lse, seg, d_o, delta, dq, dk, dv, B, T, H, KV, hd, wind
     check_rc(lib().gb_attn_bwd(ctypes.byref(a), stream_ptr()), "attn_bwd")
 
 
+def attn_tc_supported(hd: int) -> bool:
+    """Head sizes served by the tcgen05 attention kernels (others use the CUDA-core kernels)."""
+    return hd in (64, 128)
+
+
+def attn_tc_fwd(q, k, v, o, lse, seg, lo_scratch, B, T, H, KV, hd, window, scale):
+    """Tensor-core forward; ``seg`` ids must form contiguous runs per sequence, ``lo_scratch`` int32 [B*T]."""
+    a = _attn_args(q, k, v, o, lse, seg, B, T, H, KV, hd, window, scale)
+    check_rc(lib().gb_attn_tc_fwd(ctypes.byref(a), c_void_p(_p(lo_scratch)), c_void_p(_lib.status_word(q.device).data_ptr()),
+                                  stream_ptr()), "attn_tc_fwd")
+    return o
+
+
+def attn_tc_bwd(q, k, v, o, lse, seg, lo_scratch, d_o, delta, dq, dk, dv, B, T, H, KV, hd, window, scale):
+    a = _attn_args(q, k, v, o, lse, seg, B, T, H, KV, hd, window, scale)
+    a.d_o, a.ld_do, a.delta = _p(d_o), d_o.stride(0), _p(delta)
+    a.dq, a.ld_dq, a.dk, a.ld_dk, a.dv, a.ld_dv = _p(dq), dq.stride(0), _p(dk), dk.stride(0), _p(dv), dv.stride(0)
+    check_rc(lib().gb_attn_tc_bwd(ctypes.byref(a), c_void_p(_p(lo_scratch)), c_void_p(_lib.status_word(q.device).data_ptr()),
+                                  stream_ptr()), "attn_tc_bwd")
+
+
 # ------------------------------------------------------------------------------------------ MoE
 def moe_num_blocks(n_tok):
     return lib().gb_moe_num_blocks(n_tok)
@@ -246,8 +269,10 @@ def moe_combine_bwd(ws: MoeWorkspace, dout, y_perm, dy_perm, gdot):
 
 
 def moe_router_bwd(ws: MoeWorkspace, x16, router_w, gdot, dx_perm, dx16, d_router_w, part, aux_coef=0.0, jitter=0.0,
-                   jitter_seed=None, seed_dev=None, aux_coef_dev=None):
+                   jitter_seed=None, seed_dev=None, aux_coef_dev=None, part2=None):
+    """``part2`` (fp32 [ROUTER_WGRAD_CHUNKS * ne * d]) lets the router weight gradient run on many blocks."""
     a = ws.args()
+    a.part2 = _p(part2)
     a.x16, a.router_w, a.gdot, a.dx_perm, a.dx16 = _p(x16), _p(router_w), _p(gdot), _p(dx_perm), _p(dx16)
     a.d_router_w, a.part, a.aux_coef = _p(d_router_w), _p(part), float(aux_coef)
     a.jitter = float(jitter)

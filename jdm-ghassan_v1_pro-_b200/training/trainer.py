@@ -100,6 +100,9 @@ class Trainer:
         self.val_loader = DataLoader(c.batch_size, c.seq_len, c.pack_sequences, (c.seed + 1) & (2 ** 64 - 1),
                                      self.mcfg.vocab_size)
         self.have_val = self.val_loader.open_glob(c.data_dir, c.val_prefix)
+        if getattr(self.engine, "kind", "") == "cuda":
+            self.train_loader.set_ring(c.grad_accum + 6)
+            self.val_loader.set_ring(4)
         self.prefetch = Prefetcher(self.train_loader)
         log_info("[data] %d train shard(s), %s tokens%s" % (self.train_loader.num_shards,
                                                           human_count(self.train_loader.total_tokens),

@@ -1,0 +1,83 @@
+"""tcgen05 flash attention (forward, dQ, dK/dV) against the fp32 PyTorch attention of the oracle model."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def near(got, ref, rtol=3e-2, atol_frac=2e-2):
+    got, ref = got.float(), ref.float()
+    atol = atol_frac * ref.abs().max().item() + 1e-5
+    bad = (got - ref).abs() > atol + rtol * ref.abs()
+    return not bool(bad.any()), float((got - ref).abs().max()), atol
+
+
+def rnd(*shape, seed=0, dtype=torch.float16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(*shape, device="cuda", generator=g).to(dtype)
+
+
+CASES = [
+    # B, T, H, KV, hd, window, segments
+    (1, 128, 2, 2, 64, 0, False),
+    (2, 512, 12, 4, 64, 0, True),
+    (1, 300, 4, 2, 64, 0, False),
+    (2, 200, 4, 1, 64, 37, True),
+    (1, 260, 2, 1, 128, 0, True),
+    (1, 1, 2, 2, 64, 0, False),
+    (1, 1024, 4, 4, 64, 0, False),
+]
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,T,H,KV,hd,window,use_seg", CASES)
+def test_tc_attention_matches_oracle(dt, B, T, H, KV, hd, window, use_seg):
+    from ghassan_b200.models import reference as R
+    from ghassan_b200.ops import _lib, kernels as K
+    n = B * T
+    scale = hd ** -0.5
+    qk = rnd(n, (H + KV) * hd, seed=1, dtype=dt)          # q and k share a buffer, v lives in a wider one
+    qkv = rnd(n, (H + 2 * KV) * hd, seed=2, dtype=dt)
+    q, k, v = qk[:, :H * hd], qk[:, H * hd:], qkv[:, (H + KV) * hd:]
+    seg = None
+    if use_seg:
+        seg = (torch.arange(T, device="cuda") // 97).repeat(B).to(torch.int32)
+    lo = torch.empty(n, dtype=torch.int32, device="cuda")
+    o = torch.empty(n, H * hd, dtype=dt, device="cuda")
+    lse = torch.empty(n, H, device="cuda")
+    K.attn_tc_fwd(q, k, v, o, lse, seg, lo, B, T, H, KV, hd, window, scale)
+    _lib.check_status(what="attn_tc_fwd")
+    qf, kf, vf = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    ref = R.attention(qf.view(n, H, hd), kf.view(n, KV, hd), vf.view(n, KV, hd), B, T, scale, window, seg)
+    ok, err, atol = near(o, ref.detach())
+    assert ok, ("o", err, atol)
+    g = rnd(n, H * hd, seed=3, dtype=dt)
+    (ref * g.float()).sum().backward()
+    dqk = torch.zeros_like(qk)
+    dqkv = torch.zeros_like(qkv)
+    delta = torch.empty(n, H, device="cuda")
+    K.attn_tc_bwd(q, k, v, o, lse, seg, lo, g, delta, dqk[:, :H * hd], dqk[:, H * hd:], dqkv[:, (H + KV) * hd:], B, T, H,
+                  KV, hd, window, scale)
+    _lib.check_status(what="attn_tc_bwd")
+    for got, want, name in ((dqk[:, :H * hd], qf.grad, "dq"), (dqk[:, H * hd:], kf.grad, "dk"),
+                            (dqkv[:, (H + KV) * hd:], vf.grad, "dv")):
+        ok, err, atol = near(got, want)
+        assert ok, (name, err, atol)
+
+
+def test_tc_attention_agrees_with_cuda_core_kernels():
+    from ghassan_b200.ops import kernels as K
+    B, T, H, KV, hd = 2, 384, 6, 2, 64
+    n = B * T
+    q, k, v = rnd(n, H * hd, seed=4), rnd(n, KV * hd, seed=5), rnd(n, KV * hd, seed=6)
+    o1, o2 = torch.empty_like(q), torch.empty_like(q)
+    l1, l2 = torch.empty(n, H, device="cuda"), torch.empty(n, H, device="cuda")
+    lo = torch.empty(n, dtype=torch.int32, device="cuda")
+    K.attn_fwd(q, k, v, o1, l1, None, B, T, H, KV, hd, 0, 0.125)
+    K.attn_tc_fwd(q, k, v, o2, l2, None, lo, B, T, H, KV, hd, 0, 0.125)
+    assert near(o2, o1)[0]
+    assert near(l2, l1, 1e-3, 1e-3)[0]
+    # bitwise reproducible from run to run
+    o3 = torch.empty_like(q)
+    K.attn_tc_fwd(q, k, v, o3, l2, None, lo, B, T, H, KV, hd, 0, 0.125)
+    assert torch.equal(o2, o3)
