@@ -644,16 +644,45 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
 }
 
 // lo[i] = first position of the run of equal segment ids that contains i (per sequence); seg < 0 -> 0
-__global__ void attn_seg_lo_kernel(const int* __restrict__ seg, int* __restrict__ lo, int B, int T) {
-  const long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (g >= (long long)B * T) return;
-  const int i = (int)(g % T);
-  const long long base = g - i;
-  const int s = seg[g];
-  if (s < 0) { lo[g] = 0; return; }
-  int j = i;
-  while (j > 0 && seg[base + j - 1] == s) --j;
-  lo[g] = j;
+// One block of 1024 threads per sequence: running maximum of the run-start positions (chunked inclusive scan).
+__global__ void __launch_bounds__(1024) attn_seg_lo_kernel(const int* __restrict__ seg, int* __restrict__ lo, int B, int T) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  const long long base = (long long)blockIdx.x * T;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < T; c0 += 1024) {
+    const int i = c0 + threadIdx.x;
+    int s = 0, v = 0;
+    if (i < T) {
+      s = seg[base + i];
+      if (i == 0 || seg[base + i - 1] != s) v = i;
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v = max(v, n);
+    }
+    if (lane == 31) s_warp[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w = max(w, n);
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    if (warp > 0) v = max(v, s_warp[warp - 1]);
+    v = max(v, s_carry);
+    if (i < T) lo[base + i] = s < 0 ? 0 : v;
+    __syncthreads();
+    if (threadIdx.x == 1023) s_carry = v;
+    __syncthreads();
+  }
 }
 
 template <typename T, int HD>
@@ -730,15 +759,16 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
 
 using namespace gb;
 
-extern "C" int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st) {
+extern "C" int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int lo_ready, int* status, cudaStream_t st) {
   if (!a || !status || a->B <= 0 || a->T <= 0 || a->H % a->KV) return -1;
   if (a->hd != 64 && a->hd != 128) return -2;
   if (!a->d_o || !a->delta || !a->lse || !a->dq || !a->dk || !a->dv || !a->o) return -1;
-  if (a->seg && !lo_scratch) return -1;
+  if ((a->seg || lo_ready) && !lo_scratch) return -1;
   int* lo = nullptr;
-  if (a->seg) {
-    const long long n = (long long)a->B * a->T;
-    attn_seg_lo_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a->seg, lo_scratch, a->B, a->T);
+  if (lo_ready) {
+    lo = lo_scratch;                 // filled earlier by gb_attn_seg_lo for the same segment ids
+  } else if (a->seg) {
+    attn_seg_lo_kernel<<<a->B, 1024, 0, st>>>(a->seg, lo_scratch, a->B, a->T);
     lo = lo_scratch;
   }
   if (a->is_bf16) return a->hd == 64 ? launch_tc_bwd<__nv_bfloat16, 64>(a, lo, status, st) : launch_tc_bwd<__nv_bfloat16, 128>(a, lo, status, st);
@@ -747,14 +777,22 @@ extern "C" int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int* statu
 
 // Tensor-core attention forward.  `lo_scratch` ([B*T] int32) is needed when a->seg is given: segment ids must form
 // contiguous runs inside each sequence (packed documents).  Supports head_dim 64 and 128; other sizes: gb_attn_fwd.
-extern "C" int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st) {
+// lo[i] = start of the run of equal segment ids containing i; compute once per batch and pass lo_ready = 1 below.
+extern "C" int gb_attn_seg_lo(const int* seg, int* lo, int B, int T, cudaStream_t st) {
+  if (!seg || !lo || B <= 0 || T <= 0) return -1;
+  attn_seg_lo_kernel<<<B, 1024, 0, st>>>(seg, lo, B, T);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int lo_ready, int* status, cudaStream_t st) {
   if (!a || !status || a->B <= 0 || a->T <= 0 || a->H % a->KV) return -1;
   if (a->hd != 64 && a->hd != 128) return -2;
-  if (a->seg && !lo_scratch) return -1;
+  if ((a->seg || lo_ready) && !lo_scratch) return -1;
   int* lo = nullptr;
-  if (a->seg) {
-    const long long n = (long long)a->B * a->T;
-    attn_seg_lo_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a->seg, lo_scratch, a->B, a->T);
+  if (lo_ready) {
+    lo = lo_scratch;                 // filled earlier by gb_attn_seg_lo for the same segment ids
+  } else if (a->seg) {
+    attn_seg_lo_kernel<<<a->B, 1024, 0, st>>>(a->seg, lo_scratch, a->B, a->T);
     lo = lo_scratch;
   }
   if (a->is_bf16) return a->hd == 64 ? launch_tc_fwd<__nv_bfloat16, 64>(a, lo, status, st) : launch_tc_fwd<__nv_bfloat16, 128>(a, lo, status, st);

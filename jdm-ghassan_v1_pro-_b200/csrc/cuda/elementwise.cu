@@ -138,12 +138,22 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ g, const float* __restr
 }
 
 // dw[c] += sum_b part[b, c]
+// 256 threads = 32 columns x 8 row lanes; fixed summation order (row lane, then lanes 0..7)
 __global__ void colsum_finalize_kernel(const float* __restrict__ part, float* __restrict__ dw, int nblocks, int d) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+  __shared__ float s_part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * d + c];
-  dw[c] += s;
+  if (c < d)
+    for (int b = ty; b < nblocks; b += 8) s += part[(size_t)b * d + c];
+  s_part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += s_part[k][tx];
+    dw[c] += t;
+  }
 }
 
 // ------------------------------------------------------------------------------------------ QK-norm + RoPE
@@ -350,7 +360,7 @@ extern "C" int gb_rmsnorm_bwd(const void* g, const float* x, const float* w, con
   else
     rmsnorm_bwd_kernel<__half><<<nb, threads, smem, st>>>((const __half*)g, x, w, rrms, dres, dx_out, (__half*)dx16, part,
                                                       rows, d, rpb);
-  if (dw) colsum_finalize_kernel<<<(d + 255) / 256, 256, 0, st>>>(part, dw, nb, d);
+  if (dw) colsum_finalize_kernel<<<(d + 31) / 32, 256, 0, st>>>(part, dw, nb, d);
   return GB_LAUNCH_OK();
 }
 
@@ -408,8 +418,8 @@ static int qk_bwd_t(const void* dout, int ld_dout, const void* qkv, int ld_in, v
   }
 #undef GB_QK_BWD
   if (qw && part && dqw) {
-    colsum_finalize_kernel<<<1, 256, 0, st>>>(pq, dqw, nb, hd);
-    colsum_finalize_kernel<<<1, 256, 0, st>>>(pk, dkw, nb, hd);
+    colsum_finalize_kernel<<<(hd + 31) / 32, 256, 0, st>>>(pq, dqw, nb, hd);
+    colsum_finalize_kernel<<<(hd + 31) / 32, 256, 0, st>>>(pk, dkw, nb, hd);
   }
   return GB_LAUNCH_OK();
 }
@@ -423,6 +433,33 @@ extern "C" int gb_qk_norm_rope_bwd(const void* dout, int ld_dout, const void* qk
                                            n_tok, H, KV, hd, eps, rope_type, st)
                  : qk_bwd_t<__half>(dout, ld_dout, qkv, ld_in, dqkv, ld_dqkv, qw, kw, cos_sin, pos, part, dqw, dkw, n_tok,
                                     H, KV, hd, eps, rope_type, st);
+}
+
+// out16[i] = sum_s part[s * n + i] (fixed order), the second stage of a split-K GEMM
+template <typename T>
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, long long n, T* __restrict__ out) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4;
+  const long long stride = (long long)gridDim.x * blockDim.x * 4;
+  for (; i < n; i += stride) {
+    float4 acc = *reinterpret_cast<const float4*>(part + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(part + (long long)s * n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    uint2 q;
+    q.x = gb::Cvt<T>::pack2(acc.x, acc.y);
+    q.y = gb::Cvt<T>::pack2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out + i) = q;
+  }
+}
+
+extern "C" int gb_splitk_reduce(const float* part, int splits, long long n, void* out16, int is_bf16, cudaStream_t st) {
+  if (n <= 0 || n % 4 || splits < 1) return -1;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (is_bf16) splitk_reduce_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(part, splits, n, (__nv_bfloat16*)out16);
+  else splitk_reduce_kernel<__half><<<(int)blocks, 256, 0, st>>>(part, splits, n, (__half*)out16);
+  return GB_LAUNCH_OK();
 }
 
 extern "C" int gb_cast_f32_to_16(const float* src, void* dst, long long n, int is_bf16, cudaStream_t st) {

@@ -55,6 +55,8 @@ int gb_qk_norm_rope_bwd(const void* dout, int ld_dout, const void* qkv, int ld_i
                         float* dkw, int n_tok, int H, int KV, int hd, float eps, int rope_type, int is_bf16,
                         cudaStream_t st);
 int gb_cast_f32_to_16(const float* src, void* dst, long long n, int is_bf16, cudaStream_t st);
+// out16[i] = sum over splits of part[s*n + i]: second stage of a split-K GEMM (gb_gemm mode 2 with equal K ranges)
+int gb_splitk_reduce(const float* part, int splits, long long n, void* out16, int is_bf16, cudaStream_t st);
 
 // ----------------------------------------------------------------------------- attention
 typedef struct gb_attn_args {
@@ -76,9 +78,11 @@ int gb_attn_fwd(const gb_attn_args* a, cudaStream_t st);
 int gb_attn_bwd(const gb_attn_args* a, cudaStream_t st);
 // Tensor-core (tcgen05) versions for head_dim 64 / 128.  Segment ids must form contiguous runs per sequence;
 // lo_scratch: [B*T] int32 (needed when a->seg != NULL); status: device status word.
-int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st);
+int gb_attn_seg_lo(const int* seg, int* lo, int B, int T, cudaStream_t st);
+// lo_ready != 0: lo_scratch already holds gb_attn_seg_lo output (a->seg is then ignored)
+int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int lo_ready, int* status, cudaStream_t st);
 // dq_acc: fp32 scratch [B*T, H*hd] is not needed: dQ accumulates in tensor memory.  delta is computed inside.
-int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int* status, cudaStream_t st);
+int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int lo_ready, int* status, cudaStream_t st);
 
 // ----------------------------------------------------------------------------- moe.cu
 typedef struct gb_moe_args {

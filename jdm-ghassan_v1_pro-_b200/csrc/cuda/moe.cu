@@ -115,18 +115,34 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
 }
 
 // Single block.  Totals, padded offsets, per-block bases, tile map, balance statistics.
-__global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks) {
+// `staged` != 0: the histogram table fits the dynamic shared memory passed at launch and is scanned there
+// (the per-expert scans are chains of dependent loads; in global memory they dominate the kernel).
+__global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks, int staged) {
   __shared__ int s_total[MAX_NE + 1];
   __shared__ int s_off[MAX_NE + 2];
+  extern __shared__ int s_tab[];
   const int ne1 = a.ne + (a.shared ? 1 : 0);
   const int stride = a.ne + 1;
   const int e = threadIdx.x;
+  const int cells = n_blocks * stride;
+  if (staged) {
+    for (int i = threadIdx.x; i < cells; i += blockDim.x) s_tab[i] = a.block_hist[i];
+    __syncthreads();
+  }
   if (e < ne1) {
     int run = 0;
-    for (int b = 0; b < n_blocks; ++b) {
-      const int c = a.block_hist[(size_t)b * stride + e];
-      a.block_base[(size_t)b * stride + e] = run;   // relative for now
-      run += c;
+    if (staged) {
+      for (int b = 0; b < n_blocks; ++b) {
+        const int c = s_tab[b * stride + e];
+        s_tab[b * stride + e] = run;
+        run += c;
+      }
+    } else {
+      for (int b = 0; b < n_blocks; ++b) {
+        const int c = a.block_hist[(size_t)b * stride + e];
+        a.block_base[(size_t)b * stride + e] = run;   // relative for now
+        run += c;
+      }
     }
     s_total[e] = run;
     a.block_base[(size_t)n_blocks * stride + e] = run;  // last row: totals
@@ -144,10 +160,16 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks) {
     a.num_tiles[0] = off / 128;
   }
   __syncthreads();
-  if (e < ne1) {
+  if (staged) {
+    for (int i = threadIdx.x; i < cells; i += blockDim.x) {
+      const int col = i % stride;
+      a.block_base[i] = s_tab[i] + (col < ne1 ? s_off[col] : 0);
+    }
+  } else if (e < ne1) {
     for (int b = 0; b < n_blocks; ++b) a.block_base[(size_t)b * stride + e] += s_off[e];
-    for (int tle = s_off[e] / 128; tle < s_off[e + 1] / 128; ++tle) a.tile_expert[tle] = e;
   }
+  if (e < ne1)
+    for (int tle = s_off[e] / 128; tle < s_off[e + 1] / 128; ++tle) a.tile_expert[tle] = e;
   if (e < a.ne) {
     if (a.counts) a.counts[e] += (float)s_total[e];
     if (a.f_frac) a.f_frac[e] = (float)s_total[e] / (float)((long long)a.n_tok * a.top_k);
@@ -456,7 +478,9 @@ extern "C" int gb_moe_group(const gb_moe_args* a, cudaStream_t st) {
   const int nb = gb_moe_num_blocks(a->n_tok);
   if (nb > 4096) return -3;
   const int ne1 = a->ne + (a->shared ? 1 : 0);
-  moe_scan_kernel<<<1, 128, 0, st>>>(*a, nb);
+  const size_t tab_bytes = (size_t)nb * (a->ne + 1) * sizeof(int);
+  const int staged = tab_bytes <= 40 * 1024;
+  moe_scan_kernel<<<1, 256, staged ? tab_bytes : 0, st>>>(*a, nb, staged);
   const int* totals = a->block_base + (size_t)nb * (a->ne + 1);
   if (a->is_bf16) {
     moe_pack_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(*a);

@@ -211,6 +211,8 @@ class CudaModel:
         self.ids = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
         self.targets = torch.full((self.N,), -100, dtype=torch.int32, device=self.dev)
         self.segs = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
+        self.attn_tc = K.attn_tc_supported(cfg.head_dim)
+        self.seg_lo = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
         self._alloc_activations(train)
 
     # ------------------------------------------------------------------ buffers
@@ -240,12 +242,18 @@ class CudaModel:
             self.layers.append(b)
         rows = self.layers[0].ws.cap if cfg.use_moe else N
         self.h16, self.rrms_f = torch.empty(N, d, **c16), torch.empty(N, **f32)
-        self.chunk_rows = (N + self.ce_chunks - 1) // self.ce_chunks
+        # ce_chunks bounds the logits buffer (rows x vocab, 16-bit); chunks below 2048 rows only add launches
+        self.chunk_rows = max((N + self.ce_chunks - 1) // self.ce_chunks, min(N, 2048))
         self.Vpad = (cfg.vocab_size + 7) // 8 * 8
         self.logits = torch.zeros(self.chunk_rows, self.Vpad, **c16)
         self.row_loss = torch.empty(self.chunk_rows, **f32)
+        self.head_splitk = None
         if not train:
             return
+        tiles = ((self.chunk_rows + 127) // 128) * ((d + 127) // 128)
+        if cfg.vocab_size >= 4096 and tiles < 148:
+            splits = max(2, min(32, 296 // tiles, cfg.vocab_size // 512))
+            self.head_splitk = G.SplitK(self.chunk_rows, d, cfg.vocab_size, splits, dt, dev)
         t = _LayerBuf()   # backward temporaries shared by all layers
         t.dx, t.dx16 = torch.empty(N, d, **f32), torch.empty(N, d, **c16)
         t.dxb, t.dh16 = torch.empty(N, d, **c16), torch.empty(N, d, **c16)
@@ -324,8 +332,12 @@ class CudaModel:
         qw = self.w(p + "qk_qnorm") if cfg.use_qk_norm else None
         kw = self.w(p + "qk_knorm") if cfg.use_qk_norm else None
         K.qk_norm_rope_fwd(b.qkv, b.qk, qw, kw, self.cos_sin, self.pos, H, KV, hd, cfg.rms_eps, cfg.rope_type)
-        K.attn_fwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, self._seg(), self.B, self.T, H, KV, hd,
-                   cfg.sliding_window, cfg.attn_scale())
+        if self.attn_tc:   # tcgen05 path (packed-document segment ids are contiguous runs, as the loader emits them)
+            K.attn_tc_fwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, None, self.seg_lo,
+                          self.B, self.T, H, KV, hd, cfg.sliding_window, cfg.attn_scale(), lo_ready=self.use_segments)
+        else:
+            K.attn_fwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, self._seg(), self.B, self.T, H,
+                       KV, hd, cfg.sliding_window, cfg.attn_scale())
         G.gemm(b.att, self.w16(p + "wo"), out=b.x_mid, addend=x_in)
         K.rmsnorm_fwd(b.x_mid, self.w(p + "ffn_norm"), b.xb2, b.rrms2, cfg.rms_eps)
         if cfg.use_moe:
@@ -356,6 +368,8 @@ class CudaModel:
         cfg = self.cfg
         want_aux = train and cfg.use_moe and cfg.moe_aux_scale > 0
         K.embed_fwd(self.ids, self.w("tok_embeddings"), self.x[0])
+        if self.attn_tc and self.use_segments:
+            K.attn_seg_lo(self.segs, self.seg_lo, self.B, self.T)   # once per micro-batch, shared by all layers
         for l in range(cfg.num_layers):
             if train:
                 self._layer_forward(l, self.x[l], self.x[l + 1], self.layers[l], True, want_aux)
@@ -372,7 +386,10 @@ class CudaModel:
             K.softmax_ce_(lg, self.targets[r0:r1], cfg.z_loss_scale, 1.0, train, self.row_loss, self.ce_acc,
                           grad_scale_dev=self.dyn[0:1] if train else None)
             if train:
-                G.gemm(lg, Wh, b_mn=True, out=self.tmp.dh16[r0:r1])
+                if self.head_splitk is not None:   # long reduction over the vocabulary, few output tiles
+                    self.head_splitk.run(lg, Wh, self.tmp.dh16[r0:r1], b_mn=True)
+                else:
+                    G.gemm(lg, Wh, b_mn=True, out=self.tmp.dh16[r0:r1])
                 hg = self._head_grad()
                 G.gemm(lg, self.h16[r0:r1], a_mn=True, b_mn=True, out=hg, addend=hg)
         return xf
@@ -410,9 +427,14 @@ class CudaModel:
         G.gemm(t.dx16, self.w16(p + "wo"), b_mn=True, out=t.datt)
         gwo = self.g(p + "wo")
         G.gemm(t.dx16, b.att, a_mn=True, b_mn=True, out=gwo, addend=gwo)
-        K.attn_bwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, self._seg(), t.datt, t.delta,
-                   t.dqk[:, :qd], t.dqk[:, qd:], t.dqkv[:, qd + kvd:], self.B, self.T, H, KV, hd, cfg.sliding_window,
-                   cfg.attn_scale())
+        if self.attn_tc:
+            K.attn_tc_bwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, None, self.seg_lo, t.datt,
+                          t.delta, t.dqk[:, :qd], t.dqk[:, qd:], t.dqkv[:, qd + kvd:], self.B, self.T, H, KV, hd,
+                          cfg.sliding_window, cfg.attn_scale(), lo_ready=self.use_segments)
+        else:
+            K.attn_bwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, self._seg(), t.datt, t.delta,
+                       t.dqk[:, :qd], t.dqk[:, qd:], t.dqkv[:, qd + kvd:], self.B, self.T, H, KV, hd,
+                       cfg.sliding_window, cfg.attn_scale())
         qn = cfg.use_qk_norm
         K.qk_norm_rope_bwd(t.dqk, b.qkv, t.dqkv, self.w(p + "qk_qnorm") if qn else None,
                            self.w(p + "qk_knorm") if qn else None, self.cos_sin, self.pos, t.qk_part,

@@ -168,6 +168,40 @@ def gemm_grouped_reduce(a, b, seg_offsets, groups, out, *, accumulate=True, bloc
     return out
 
 
+class SplitK:
+    """Split-K plan for a product with a long reduction and few output tiles (e.g. d(hidden) = d(logits) @ W over
+    the vocabulary): ``splits`` CTAs per output tile each reduce a K range into an fp32 partial, a second kernel
+    adds the partials in a fixed order and casts.  Buffers are created once and reused."""
+
+    def __init__(self, M, N, K, splits, dtype, device):
+        kc = (K + splits - 1) // splits
+        kc = (kc + 63) // 64 * 64
+        offs = [min(K, i * kc) for i in range(splits + 1)]
+        self.splits, self.M, self.N, self.K = splits, M, N, K
+        self.offsets = torch.tensor(offs, dtype=torch.int32, device=device)
+        self.partial = torch.empty(splits, M, N, dtype=torch.float32, device=device)
+        self.dtype = dtype
+
+    def run(self, a, b, out16, *, a_mn=False, b_mn=False, block_n=0):
+        """``out16[:M] = A @ B^T`` for the first ``a`` rows given (M may be smaller than planned)."""
+        M = a.shape[1] if a_mn else a.shape[0]
+        N = self.N
+        part = self.partial[:, :M, :] if M == self.M else self.partial.view(-1)[:self.splits * M * N].view(self.splits, M, N)
+        g = _base_args(a, b, M, N, 0, a_mn, b_mn, part, block_n or (64 if N % 128 else 128))
+        g.epilogue = EPI_STORE
+        g.mode = 2
+        g.seg_offsets = self.offsets.data_ptr()
+        g.groups = self.splits
+        g.out_group_stride = M * N
+        g.ldo = N
+        _launch(g)
+        rc = _lib.lib().gb_splitk_reduce(ctypes.c_void_p(part.data_ptr()), ctypes.c_int(self.splits),
+                                         ctypes.c_longlong(M * N), ctypes.c_void_p(out16.data_ptr()),
+                                         ctypes.c_int(int(out16.dtype == torch.bfloat16)), _lib.stream_ptr())
+        _lib.check_rc(rc, "gb_splitk_reduce")
+        return out16
+
+
 def interleave_gate_up(gate, up, block=64):
     """``[.., E, d]`` gate and up -> ``[.., 2E, d]`` with rows interleaved in blocks of ``block``."""
     *lead, E, d = gate.shape

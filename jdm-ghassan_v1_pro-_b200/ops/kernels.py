@@ -178,20 +178,27 @@ def attn_tc_supported(hd: int) -> bool:
     return hd in (64, 128)
 
 
-def attn_tc_fwd(q, k, v, o, lse, seg, lo_scratch, B, T, H, KV, hd, window, scale):
-    """Tensor-core forward; ``seg`` ids must form contiguous runs per sequence, ``lo_scratch`` int32 [B*T]."""
+def attn_seg_lo(seg, lo, B, T):
+    """``lo[i]`` = start of the run of equal segment ids containing position i (per sequence)."""
+    check_rc(lib().gb_attn_seg_lo(c_void_p(_p(seg)), c_void_p(_p(lo)), c_int(B), c_int(T), stream_ptr()), "attn_seg_lo")
+    return lo
+
+
+def attn_tc_fwd(q, k, v, o, lse, seg, lo_scratch, B, T, H, KV, hd, window, scale, lo_ready=False):
+    """Tensor-core forward; ``seg`` ids must form contiguous runs per sequence, ``lo_scratch`` int32 [B*T].
+    With ``lo_ready`` the scratch already holds :func:`attn_seg_lo` output and ``seg`` is not read."""
     a = _attn_args(q, k, v, o, lse, seg, B, T, H, KV, hd, window, scale)
-    check_rc(lib().gb_attn_tc_fwd(ctypes.byref(a), c_void_p(_p(lo_scratch)), c_void_p(_lib.status_word(q.device).data_ptr()),
-                                  stream_ptr()), "attn_tc_fwd")
+    check_rc(lib().gb_attn_tc_fwd(ctypes.byref(a), c_void_p(_p(lo_scratch)), c_int(int(lo_ready)),
+                                  c_void_p(_lib.status_word(q.device).data_ptr()), stream_ptr()), "attn_tc_fwd")
     return o
 
 
-def attn_tc_bwd(q, k, v, o, lse, seg, lo_scratch, d_o, delta, dq, dk, dv, B, T, H, KV, hd, window, scale):
+def attn_tc_bwd(q, k, v, o, lse, seg, lo_scratch, d_o, delta, dq, dk, dv, B, T, H, KV, hd, window, scale, lo_ready=False):
     a = _attn_args(q, k, v, o, lse, seg, B, T, H, KV, hd, window, scale)
     a.d_o, a.ld_do, a.delta = _p(d_o), d_o.stride(0), _p(delta)
     a.dq, a.ld_dq, a.dk, a.ld_dk, a.dv, a.ld_dv = _p(dq), dq.stride(0), _p(dk), dk.stride(0), _p(dv), dv.stride(0)
-    check_rc(lib().gb_attn_tc_bwd(ctypes.byref(a), c_void_p(_p(lo_scratch)), c_void_p(_lib.status_word(q.device).data_ptr()),
-                                  stream_ptr()), "attn_tc_bwd")
+    check_rc(lib().gb_attn_tc_bwd(ctypes.byref(a), c_void_p(_p(lo_scratch)), c_int(int(lo_ready)),
+                                  c_void_p(_lib.status_word(q.device).data_ptr()), stream_ptr()), "attn_tc_bwd")
 
 
 # ------------------------------------------------------------------------------------------ MoE

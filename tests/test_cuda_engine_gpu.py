@@ -90,6 +90,8 @@ def _run(c, device, steps=None):
                                        ("adamw", {"model.use_moe": "false", "training.pack_sequences": "true"}),
                                        ("adamw", {"model.moe_aux_free": "true", "model.moe_aux_scale": "0.0",
                                                   "b200.cuda_graphs": "false"}),
+                                       ("lion", {"model.hidden_size": "256", "training.pack_sequences": "true",
+                                                 "model.moe_expert_dim": "128"}),     # head_dim 64: tcgen05 attention
                                        ("muon", {})])
 def test_cuda_engine_tracks_fp32_engine(tmp_path, opt, extra):
     tmp = str(tmp_path)

@@ -151,6 +151,22 @@ def test_grouped_rows_and_grouped_reduce():
         assert ok, (e, rel)
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(512, 768, 32000, 16), (100, 128, 600, 4)])
+def test_split_k(M, N, K, splits):
+    G, L = _ops()
+    a = _rand(M, K, seed=60) * 0.2
+    w = _rand(K, N, seed=61) * 0.2          # B stored [K, N]
+    plan = G.SplitK(M, N, K, splits, torch.float16, "cuda")
+    out = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    plan.run(a, w, out, b_mn=True)
+    L.check_status(what="split-k")
+    rel, ok = _close(out, a.float() @ w.float())
+    assert ok, rel
+    out2 = torch.empty_like(out)
+    plan.run(a, w, out2, b_mn=True)
+    assert torch.equal(out, out2)
+
+
 def test_large_gemm_matches():
     G, L = _ops()
     a, b = _rand(4096, 1024, seed=50), _rand(2048, 1024, seed=51)
