@@ -183,7 +183,7 @@ def run_ours(args):
     mix = TrainerConfig.from_config(base).mix
     work = os.path.join(args.workdir, "rank%d" % rank)
     data, tok = make_data(work, vocab, mix)
-    total = args.warmup + 2 * args.steps + 1
+    total = args.settle_max + args.warmup + 2 * args.steps + 1
     c = load_recipe(args.config, data, os.path.join(work, "ckpt"), tok, total)
     for k, v in (args.set or []):
         c.set(k, v)
@@ -191,6 +191,17 @@ def run_ours(args):
     tr = Trainer(mcfg, tcfg, device="cuda")
     tr.prepare()
     eng = tr.engine
+    # The recipe's dynamic loss scale starts high and halves on every overflowing step (those steps skip the
+    # optimizer).  Run untimed steps until one applies, so that the warm-up and the timed steps all do the full work.
+    settle = 0
+    while settle < args.settle_max:
+        res, _, _ = tr.train_step()
+        settle += 1
+        ok = torch.tensor([1.0 if res.applied else 0.0], device="cuda")
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) > 0:
+            break
     for _ in range(args.warmup):
         tr.train_step()
 
@@ -208,10 +219,12 @@ def run_ours(args):
     ev0.record()
     toks = 0
     losses = []
+    applied = 0
     for _ in range(args.steps):
         res, _, _ = tr.train_step()
         toks += res.ntok_global
         losses.append(res.loss)
+        applied += int(res.applied)
     ev1.record()
     fence()
     clocks = sampler.stop()
@@ -240,7 +253,8 @@ def run_ours(args):
            "e2e": {"value": toks_e / sec_e, "unit": "tokens/s",
                    "h2d_bytes_per_step": tcfg.grad_accum * tcfg.batch_size * tcfg.seq_len * 4 * n_in + 64,
                    "d2h_bytes_per_step": 40},
-           "gpu_launches": int(launches), "loss_first": losses[0], "loss_last": losses[-1],
+           "gpu_launches": int(launches), "optimizer_steps_applied": applied, "settle_steps": settle,
+           "loss_first": losses[0], "loss_last": losses[-1],
            "supervised_tokens_per_step": toks / args.steps}
     if rank == 0:
         print(json.dumps(out), flush=True)
@@ -337,6 +351,8 @@ def main():
     ap.add_argument("--workdir", default=os.environ.get("GB200_BENCH_DIR", "/tmp/gb200_bench"))
     ap.add_argument("--set", nargs=2, action="append", metavar=("KEY", "VALUE"), help="override a recipe key")
     ap.add_argument("--ref-timeout", type=int, default=1500)
+    ap.add_argument("--settle-max", type=int, default=12,
+                    help="untimed steps allowed before warm-up for the dynamic loss scale to stop overflowing")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
     world = env_int("WORLD_SIZE", 1)
