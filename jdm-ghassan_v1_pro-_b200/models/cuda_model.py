@@ -55,6 +55,7 @@ class ParamLayout:
         if self.Eff % 64:
             raise ValueError("expert/FFN hidden size must be a multiple of 64 for the fused SwiGLU layout")
         nd: List[Segment] = [Segment("tok_embeddings", (V, d), False), Segment("final_norm", (d,), False)]
+        rt: List[Segment] = []     # routers: weight decay like the matrices, but kernels read them in fp32
         dc: List[Segment] = []
         for i in range(cfg.num_layers):
             p = f"L{i}."
@@ -63,20 +64,25 @@ class ParamLayout:
                 nd += [Segment(p + "qk_qnorm", (hd,), False), Segment(p + "qk_knorm", (hd,), False)]
             dc += [Segment(p + "wqkv", (qd + 2 * kvd, d), True), Segment(p + "wo", (d, qd), True)]
             if cfg.use_moe:
-                dc.append(Segment(p + "router", (cfg.num_experts, d), True))
+                rt.append(Segment(p + "router", (cfg.num_experts, d), True))
             dc += [Segment(p + "w_gu", (self.ne1 * 2 * self.Eff, d), True),
                    Segment(p + "w_down", (self.ne1 * d, self.Eff), True)]
         if not cfg.tie_embeddings:
             dc.append(Segment("lm_head", (V, d), True))
+        # [no decay | routers | matrices]: one boundary for weight decay (decay_start) and one for "read in fp32
+        # by the kernels" (f32_end), so range-based kernels need no per-tensor table
         off = 0
-        for s in nd + dc:
+        self.decay_start = self.f32_end = 0
+        for s in nd + rt + dc:
             s.offset = off
             off += (s.numel + ALIGN - 1) // ALIGN * ALIGN
             if s is nd[-1]:
-                self.decay_start = off
+                self.decay_start = self.f32_end = off
+            if rt and s is rt[-1]:
+                self.f32_end = off
         self.total = off
-        self.segments = {s.key: s for s in nd + dc}
-        self.order = [s.key for s in nd + dc]
+        self.segments = {s.key: s for s in nd + rt + dc}
+        self.order = [s.key for s in nd + rt + dc]
 
     def view(self, flat: torch.Tensor, key: str) -> torch.Tensor:
         s = self.segments[key]

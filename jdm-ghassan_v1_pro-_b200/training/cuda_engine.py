@@ -73,7 +73,7 @@ class _FlatOptimizer:
 class CudaEngine:
     kind = "cuda"
 
-    def __init__(self, mcfg: ModelConfig, tcfg, seed: Optional[int] = None, device=None):
+    def __init__(self, mcfg: ModelConfig, tcfg, seed: Optional[int] = None, device=None, fused_sync_single=False):
         if not torch.cuda.is_available():
             raise RuntimeError("CudaEngine needs a CUDA device")
         if not _lib.available():
@@ -94,7 +94,7 @@ class CudaEngine:
             self.optimizer = _FlatOptimizer(tcfg.optimizer, self.model, tcfg)
         n = self.model.layout.total
         self.sq_partial = torch.zeros(K.sqnorm_blocks(n), dtype=torch.float64, device=self.device)
-        self.norm_out = torch.zeros(2, dtype=torch.float32, device=self.device)   # [scale or 0, gnorm]
+        self.norm_out = torch.zeros(4, dtype=torch.float32, device=self.device)   # [scale or 0, gnorm, -, -]
         self.gs_dev = torch.zeros(1, dtype=torch.float32, device=self.device)     # 1 / (ntok_global * loss_scale)
         self.ntok_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.aux_weighted = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -108,9 +108,12 @@ class CudaEngine:
         self._loss_scale = 1.0
         self.weight_ema = torch.empty_like(self.model.P).copy_(self.model.P) if tcfg.weight_ema > 0 else None
         self.grad_sync = None
-        if self.dist.world > 1 and tcfg.grad_sync == "fused":
+        fused_ok = tcfg.optimizer != "muon" and tcfg.tokens_per_step_global(self.dist.world) < (1 << 24)
+        if fused_ok and ((self.dist.world > 1 and tcfg.grad_sync == "fused") or fused_sync_single):
             from ..parallel.grad_sync import FusedGradSync
-            self.grad_sync = FusedGradSync(self)
+            self.grad_sync = FusedGradSync(self)   # moves P / W16 / Gr (and routing counts) into symmetric memory
+            if self.weight_ema is not None:
+                self.weight_ema = torch.empty_like(self.model.P).copy_(self.model.P)
         self.last_step_ms = None
         self._ev0, self._ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         self.kernel_launches = 0
@@ -208,15 +211,22 @@ class CudaEngine:
     def end_step(self, lr: float) -> StepResult:
         m, d, cfg = self.model, self.dist, self.mcfg
         ntok_global = self._ntok
-        if d.world > 1:
+        fused = self.grad_sync is not None
+        if d.world > 1 and not fused:
             self.ntok_dev[0] = self._ntok
             d.all_reduce_sum_(self.ntok_dev)
             if m.bias_counts is not None:
                 d.all_reduce_sum_(m.bias_counts)
         gnorm, applied = 0.0, False
-        if d.world > 1:
+        if d.world > 1 and not fused:
             ntok_global = int(self.ntok_dev.item())   # small host read; also orders the step on every rank
-        if ntok_global > 0:
+        if fused:
+            # token count, routing counts, gradients, norm, clip, skip decision, optimizer and the parameter
+            # all-gather are one kernel sequence; nothing is read on the host until the step's single read-back
+            if self.tcfg.freeze_embeddings:
+                m.g("tok_embeddings").zero_()
+            self.grad_sync.step(lr, self._loss_scale, self._ntok)
+        elif ntok_global > 0:
             grad_scale = float(_F32(1.0) / (_F32(ntok_global) * _F32(self._loss_scale)))
             if self.tcfg.freeze_embeddings:
                 m.g("tok_embeddings").zero_()
@@ -225,8 +235,6 @@ class CudaEngine:
                     d.all_reduce_sum_(m.Gr)
                 gnorm = self._muon_step(lr, grad_scale)
                 self.norm_out[1] = gnorm if math.isfinite(gnorm) else float("nan")
-            elif self.grad_sync is not None:
-                self.grad_sync.step(lr, grad_scale)
             else:
                 if d.world > 1:
                     d.all_reduce_sum_(m.Gr)
@@ -235,14 +243,17 @@ class CudaEngine:
                 self.optimizer.launch(lr, self.norm_out[0:1])
         # ---- the one host read-back of the step
         self._ev1.record()
-        rb = torch.cat([self.norm_out.double(), m.ce_acc, self.aux_weighted.double()])
-        self.readback[:5].copy_(rb, non_blocking=True)
+        norm_src = self.grad_sync.out if fused else self.norm_out
+        rb = torch.cat([norm_src[:2].double(), m.ce_acc, self.aux_weighted.double(), norm_src[2:3].double()])
+        self.readback[:6].copy_(rb, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         PERF.add("sync")
         PERF.add("d2h_bytes", 40)
         _lib.check_status(self.device, "training step")
         self.last_step_ms = self._ev0.elapsed_time(self._ev1)
-        _, gn, loss_sum, rows, aux_w = (float(x) for x in self.readback[:5])
+        _, gn, loss_sum, rows, aux_w, ntok_dev = (float(x) for x in self.readback[:6])
+        if fused:
+            ntok_global = int(round(ntok_dev))
         if ntok_global > 0:
             gnorm = gn
             applied = math.isfinite(gnorm)
@@ -254,9 +265,13 @@ class CudaEngine:
             if cfg.use_moe and cfg.moe_aux_scale > 0:
                 loss += cfg.moe_aux_scale * aux_w / cfg.num_layers / self._ntok
         if m.moe_bias is not None and applied:
-            moe_bias_update(m.moe_bias, m.bias_counts)
+            moe_bias_update(m.moe_bias, self.grad_sync.counts_global if fused else m.bias_counts)
         if applied and self.weight_ema is not None:
-            self.weight_ema.lerp_(m.P, 1.0 - self.tcfg.weight_ema)
+            if fused:   # the master copy is current on the owned shard only; checkpoints gather the rest
+                own = slice(self.grad_sync.lo, self.grad_sync.hi)
+                self.weight_ema[own].lerp_(m.P[own], 1.0 - self.tcfg.weight_ema)
+            else:
+                self.weight_ema.lerp_(m.P, 1.0 - self.tcfg.weight_ema)
         PERF.add("opt_steps")
         return StepResult(loss, self._ntok, ntok_global, gnorm, applied)
 
@@ -273,6 +288,11 @@ class CudaEngine:
         return ""
 
     # ------------------------------------------------------------------ checkpoint state
+    def prepare_export(self):
+        """Collective: every rank calls this before rank 0 captures a checkpoint."""
+        if self.grad_sync is not None:
+            self.grad_sync.gather_full_state()
+
     def export_weights(self) -> List:
         named = self.model.export_named()
         return [(s.name, named[s.name]) for s in self.mcfg.param_specs()]

@@ -363,6 +363,9 @@ class Trainer:
     def save(self, name: str):
         """Snapshot on rank 0 (loader quiesced so its cursor equals the consumed batches), publish in background."""
         ok = torch.ones(1, dtype=torch.uint8)
+        prep = getattr(self.engine, "prepare_export", None)
+        if prep is not None:
+            prep()          # sharded state is completed on every rank before rank 0 captures it
         if self.is_main():
             try:
                 self.prefetch.quiesce()
