@@ -249,7 +249,9 @@ def run_ours(args):
     out = {"metric": "train tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "bf16" if tcfg.operand_dtype() == "bf16" else "fp16", "data": "synthetic",
-           "impl": "ours", "config": recipe_label(args.config, mcfg, tcfg, world), "clocks": clocks,
+           "impl": "ours", "config": dict(recipe_label(args.config, mcfg, tcfg, world), fuse_micro_batches=tr.fuse,
+                                            grad_sync=("fused peer-memory" if eng.grad_sync is not None else
+                                                       ("nccl" if world > 1 else "none"))), "clocks": clocks,
            "e2e": {"value": toks_e / sec_e, "unit": "tokens/s",
                    "h2d_bytes_per_step": tcfg.grad_accum * tcfg.batch_size * tcfg.seq_len * 4 * n_in + 64,
                    "d2h_bytes_per_step": 40},

@@ -70,11 +70,25 @@ __global__ void __launch_bounds__(256) sync_reduce_kernel(gb_sync_args a) {
   const long long hi = min(a.total, lo + a.shard);
   float* mine = gp[a.rank];
   double sq = 0.0;
-  const long long stride = (long long)gridDim.x * 256 * 4;
-  for (long long i = lo + ((long long)blockIdx.x * 256 + threadIdx.x) * 4; i < hi; i += stride) {
-    const float4 s = sum_peers<W>(gp, i, a.world);
-    *reinterpret_cast<float4*>(mine + i) = s;   // own shard of the own buffer: no peer reads this range
-    sq += (double)s.x * s.x + (double)s.y * s.y + (double)s.z * s.z + (double)s.w * s.w;
+  // U independent 16-byte loads per peer and thread in flight: NVLink latency is several microseconds
+  constexpr int U = W == 0 ? 1 : (W >= 8 ? 2 : 4);
+  const long long tile = 256LL * 4 * U;
+  const long long stride = (long long)gridDim.x * tile;
+  for (long long base = lo + (long long)blockIdx.x * tile; base < hi; base += stride) {
+    float4 s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = base + ((long long)u * 256 + threadIdx.x) * 4;
+      s[u] = i < hi ? sum_peers<W>(gp, i, a.world) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = base + ((long long)u * 256 + threadIdx.x) * 4;
+      if (i < hi) {
+        *reinterpret_cast<float4*>(mine + i) = s[u];   // own shard of the own buffer: no peer reads this range
+        sq += (double)s[u].x * s[u].x + (double)s[u].y * s[u].y + (double)s[u].z * s[u].z + (double)s[u].w * s[u].w;
+      }
+    }
   }
   red[threadIdx.x] = sq;
   __syncthreads();

@@ -112,7 +112,7 @@ class TrainerConfig:
     ep_size: int = 1                  # expert-parallel degree (num_experts % ep_size == 0)
     grad_sync: str = "fused"          # fused (peer-memory reduce-scatter + optimizer + all-gather) | nccl
     weight_ema: float = 0.0           # > 0: keep an exponential moving average of the weights with this decay
-    fuse_micro_batches: int = 1       # run this many micro-batches as one forward/backward (same gradient sum)
+    fuse_micro_batches: int = 0       # micro-batches run as one forward/backward pass (same gradient sum); 0 = choose
     cuda_graphs: bool = True
     compute_dtype: str = ""           # "" = derive from precision/gemm_fp16; fp16 | bf16
 
@@ -275,7 +275,7 @@ class TrainerConfig:
         if t.grad_sync not in ("fused", "nccl"):
             raise ConfigError(f"unknown b200.grad_sync '{t.grad_sync}' (fused|nccl)")
         t.weight_ema = c.get_float("b200.weight_ema", t.weight_ema)
-        t.fuse_micro_batches = max(1, c.get_int("b200.fuse_micro_batches", t.fuse_micro_batches))
+        t.fuse_micro_batches = max(0, c.get_int("b200.fuse_micro_batches", t.fuse_micro_batches))
         t.cuda_graphs = c.get_bool("b200.cuda_graphs", t.cuda_graphs)
         t.compute_dtype = c.get_str("b200.compute_dtype", t.compute_dtype)
         if t.compute_dtype not in ("", "fp16", "bf16"):

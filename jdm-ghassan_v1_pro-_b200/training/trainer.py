@@ -7,6 +7,7 @@ on the device (CUDA events) when a GPU engine is used and reported next to the h
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import math
 import os
@@ -37,6 +38,7 @@ class Trainer:
     def __init__(self, mcfg: ModelConfig, tcfg: TrainerConfig, engine=None, device: Optional[str] = None):
         self.mcfg, self.cfg = mcfg, tcfg
         self._check_ranges()
+        self.fuse = 1
         self.engine = engine if engine is not None else self._make_engine(device)
         self.dist = self.engine.dist
         self.rank, self.world = self.dist.rank, self.dist.world
@@ -75,11 +77,60 @@ class Trainer:
             dev = "cuda" if torch.cuda.is_available() else "cpu"
         if dev == "cuda":
             from .cuda_engine import CudaEngine
-            return CudaEngine(self.mcfg, self.cfg)
+            self.fuse = self._pick_fuse()
+            ecfg = self.cfg
+            if self.fuse > 1:
+                ecfg = dataclasses.replace(self.cfg, batch_size=self.cfg.batch_size * self.fuse,
+                                           grad_accum=self.cfg.grad_accum // self.fuse)
+                log_info("[cuda] %d micro-batches of %d x %d tokens run as one pass of %d tokens (%d passes per step)" % (
+                    self.fuse, self.cfg.batch_size, self.cfg.seq_len, ecfg.batch_size * ecfg.seq_len, ecfg.grad_accum))
+            return CudaEngine(self.mcfg, ecfg)
         if dev != "cpu":
             log_warn(f"device '{dev}' is not supported; falling back to cpu")
         from .engine import TorchEngine
         return TorchEngine(self.mcfg, self.cfg, "cpu")
+
+    def _pick_fuse(self) -> int:
+        """How many of the recipe's micro-batches one forward/backward pass covers.  The gradient of a step is a sum
+        over its micro-batches, so running F of them as one batch of F*batch_size rows gives the same sum with F times
+        fewer, F times larger kernels.  Two things are then defined over the fused batch instead of per micro-batch:
+        the auxiliary balance statistics (mean router probability and routed share) and the token index that feeds
+        the router-jitter hash.  ``b200.fuse_micro_batches: 1`` keeps the per-micro-batch definitions."""
+        c = self.cfg
+        f = c.fuse_micro_batches
+        if f <= 0:      # auto: the largest divisor of grad_accum that keeps a pass at or below 8192 tokens
+            f = 1
+            for cand in range(1, min(c.grad_accum, 64) + 1):
+                if c.grad_accum % cand == 0 and c.batch_size * cand * c.seq_len <= 8192:
+                    f = cand
+        if c.grad_accum % f:
+            raise TrainerError("b200.fuse_micro_batches=%d must divide training.grad_accum=%d" % (f, c.grad_accum))
+        return f
+
+    def _fused(self, batches):
+        """Concatenate up to ``self.fuse`` loader batches into one pinned buffer triple (missing rows unsupervised)."""
+        if self.fuse == 1:
+            b = batches[0]
+            return b.ids, b.targets, b.segments, b.B, b.T
+        c = self.cfg
+        n = c.batch_size * c.seq_len
+        if not hasattr(self, "_fuse_ring"):
+            pin = torch.cuda.is_available()
+            mk = lambda: (torch.zeros(self.fuse * n, dtype=torch.int32).pin_memory() if pin
+                          else torch.zeros(self.fuse * n, dtype=torch.int32))
+            self._fuse_ring = [(mk(), mk(), mk()) for _ in range(c.grad_accum // self.fuse + 3)]
+            self._fuse_pos = 0
+        ids, tg, sg = self._fuse_ring[self._fuse_pos]
+        self._fuse_pos = (self._fuse_pos + 1) % len(self._fuse_ring)
+        for j, b in enumerate(batches):
+            ids[j * n:(j + 1) * n].copy_(b.ids.view(-1))
+            tg[j * n:(j + 1) * n].copy_(b.targets.view(-1))
+            sg[j * n:(j + 1) * n].copy_(b.segments.view(-1))
+        if len(batches) < self.fuse:
+            tg[len(batches) * n:].fill_(-100)
+            ids[len(batches) * n:].zero_()
+            sg[len(batches) * n:].zero_()
+        return ids, tg, sg, c.batch_size * self.fuse, c.seq_len
 
     def _open_loaders(self):
         c = self.cfg
@@ -350,9 +401,11 @@ class Trainer:
         if not self.have_val:
             return 0.0
         total, ntok = 0.0, 0
-        for _ in range(max_batches):
-            b = self.val_loader.next()
-            s, n = self.engine.eval_batch(b.ids, b.targets, b.segments, b.B, b.T)
+        left = max_batches
+        while left > 0:
+            group = [self.val_loader.next() for _ in range(min(self.fuse, left))]
+            left -= len(group)
+            s, n = self.engine.eval_batch(*self._fused(group))
             total += s
             ntok += n
         return total / ntok if ntok > 0 else 0.0
@@ -428,11 +481,11 @@ class Trainer:
         t0 = time.perf_counter()
         dscale = self.scaler.for_step()
         self.engine.begin_step(self.state.step, dscale)
-        for _ in range(c.grad_accum):
+        for _ in range(c.grad_accum // self.fuse):
             self.phases.start("load")
-            b = self.prefetch.get()
+            group = [self.prefetch.get() for _ in range(self.fuse)]
             self.phases.stop("load")
-            self.engine.micro_step(b.ids, b.targets, b.segments, b.B, b.T)
+            self.engine.micro_step(*self._fused(group))
         lr = self.sched.lr_at(self.state.step)
         res = self.engine.end_step(lr)
         loss = res.loss

@@ -58,6 +58,8 @@ training:
   loss_scale_init: 1024
   loss_scale_max: 1024
   ce_chunks: 2
+b200:
+  fuse_micro_batches: 1
 """)
     c.set("training.data_dir", tmp)
     c.set("training.checkpoint_dir", os.path.join(tmp, "ckpt"))
@@ -113,6 +115,24 @@ def test_cuda_engine_tracks_fp32_engine(tmp_path, opt, extra):
     for name in a:
         err = np.abs(a[name] - b[name]).max()
         assert err < 5e-3, (name, err)
+
+
+def test_fused_micro_batches_give_the_same_step(tmp_path):
+    """Two micro-batches run as one pass of twice the rows: same gradient sum, hence the same trajectory as the
+    unfused fp32 engine (no auxiliary loss or jitter here, whose statistics are defined per pass)."""
+    tmp = str(tmp_path)
+    _make_shards(tmp, 608)
+    over = {"model.moe_aux_free": "true", "model.moe_aux_scale": "0.0", "training.pack_sequences": "true",
+            "training.grad_accum": "4"}
+    _, ref = _run(_recipe(tmp, **over), "cpu")
+    for fuse in ("2", "0"):         # explicit, and chosen automatically (4 here: 4 x 2 x 64 tokens fit easily)
+        tr, got = _run(_recipe(tmp, **dict(over, **{"b200.fuse_micro_batches": fuse})), "cuda")
+        assert tr.fuse == (2 if fuse == "2" else 4)
+        assert tr.engine.model.B == 2 * tr.fuse
+        for (l0, g0, n0, a0), (l1, g1, n1, a1) in zip(ref, got):
+            assert n0 == n1 and a0 == a1
+            assert abs(l0 - l1) < 2e-2 * abs(l0), (l0, l1)
+            assert abs(g0 - g1) < 8e-2 * abs(g0) + 1e-3, (g0, g1)
 
 
 def test_cuda_checkpoint_roundtrip_and_resume(tmp_path):
