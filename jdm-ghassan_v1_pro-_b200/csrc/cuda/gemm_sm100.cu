@@ -18,7 +18,8 @@ namespace gb {
 static constexpr int BM = 128;
 static constexpr int BK = 64;       // 64 x 2 B = one 128-byte swizzle row
 static constexpr int UMMA_K = 16;
-static constexpr int GEMM_THREADS = 192;  // warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer
+static constexpr int GEMM_THREADS = 320;  // warps 0-7 epilogue (two per TMEM lane quarter), warp 8 TMA producer, warp 9 MMA issuer
+static constexpr int W_TMA = 8, W_MMA = 9, EPI_THREADS = 256;
 
 struct GemmParams {
   int M, N, K;
@@ -166,15 +167,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], EPI_THREADS); }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == W_MMA) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == W_TMA && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -184,7 +185,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_n = (p.N + BN - 1) / BN;
   const int total_tiles = tiles_m * tiles_n * (p.mode == 2 ? p.groups : 1);
 
-  if (warp == 4) {
+  if (warp == W_TMA) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
       uint32_t it = 0;
@@ -214,7 +215,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == W_MMA) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(p.fmt, p.a_mn_major, p.b_mn_major, BM, BN);
@@ -253,10 +254,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------- epilogue (warps 0-3, one row per thread)
+    // ------------------------------------------------------------- epilogue (warps 0-7)
+    // A warp reads the 32 TMEM lanes of its quarter (warp % 4); warps q and q+4 share a quarter and split the
+    // tile's columns in halves, so two warps drain each row group.  One row per thread.
     uint32_t acc_it = 0;
     bool ok = true;
-    const int r_in_tile = warp * 32 + lane;
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r_in_tile = quarter * 32 + lane;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       TileInfo t = decode_tile<BN>(p, tile, tiles_m, tiles_n);
       const bool empty_k = (t.k_end <= t.k_begin);
@@ -269,45 +273,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       const int row = t.a_row0 + r_in_tile;
       const bool row_ok = row < p.M;
-      const uint32_t taddr0 = tmem_base + ab * BN + (uint32_t(warp * 32) << 16);
+      const uint32_t taddr0 = tmem_base + ab * BN + (uint32_t(quarter * 32) << 16);
       if constexpr (EPI == EPI_STORE) {
         OutT* orow = reinterpret_cast<OutT*>(p.out) + t.out_off + (long long)row * p.ldo;
         const float* arow = p.addend ? p.addend + t.out_off + (long long)row * p.ld_add : nullptr;
+        constexpr int CH = BN / 64;            // 32-column chunks per half
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          float v[32];
+        for (int c0 = half * CH; c0 < (half + 1) * CH; c0 += 2) {
+          constexpr int NB = CH >= 2 ? 2 : 1;   // chunks loaded per wait
+          uint32_t r[NB][32];
           if (!empty_k) {
-            uint32_t r[32];
-            tmem_ld_32x32(taddr0 + c * 32, r);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) tmem_ld_32x32(taddr0 + (c0 + b) * 32, r[b]);
             tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
           }
-          const int col = t.n0 + c * 32;
-          const int nvalid = p.N - col;
-          if (row_ok && nvalid > 0) {
-            if (arow) {
-              float a[32];
-              load_row32<float>(arow + col, a, nvalid);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] += a[i];
+          for (int b = 0; b < NB; ++b) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[b][i]);
+            const int col = t.n0 + (c0 + b) * 32;
+            const int nvalid = p.N - col;
+            if (row_ok && nvalid > 0) {
+              if (arow) {
+                float a[32];
+                load_row32<float>(arow + col, a, nvalid);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += a[i];
+              }
+              store_row32<OutT>(orow + col, v, nvalid);
             }
-            store_row32<OutT>(orow + col, v, nvalid);
           }
         }
       } else if constexpr (EPI == EPI_SWIGLU_FWD) {
-        // tile columns: [0,64) gate_j, [64,128) up_j for j in [tn*64, tn*64+64)
-        static_assert(EPI != EPI_SWIGLU_FWD || BN == 128, "SwiGLU forward epilogue needs BN == 128");
-        OutT* act = reinterpret_cast<OutT*>(p.out) + (long long)row * p.ldo + (t.n0 >> 1);
-        OutT* gu = p.aux_out ? reinterpret_cast<OutT*>(p.aux_out) + (long long)row * p.ld_aux + t.n0 : nullptr;
+        // every 128 tile columns hold [64 gate_j | 64 up_j] for 64 consecutive j; a pair = 32 gate columns and the
+        // matching 32 up columns.  BN/64 pairs per tile, split between the two column halves.
+        static_assert(EPI != EPI_SWIGLU_FWD || BN % 128 == 0, "SwiGLU forward epilogue needs BN % 128 == 0");
+        constexpr int PAIRS_PER_HALF = BN / 128;
+        OutT* act_row = reinterpret_cast<OutT*>(p.out) + (long long)row * p.ldo;
+        OutT* gu_row = p.aux_out ? reinterpret_cast<OutT*>(p.aux_out) + (long long)row * p.ld_aux : nullptr;
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
+        for (int pp = half * PAIRS_PER_HALF; pp < (half + 1) * PAIRS_PER_HALF; ++pp) {
+          const int gcol = (pp >> 1) * 128 + (pp & 1) * 32;   // gate columns inside the tile; up = gcol + 64
           uint32_t rg[32], ru[32];
-          tmem_ld_32x32(taddr0 + h * 32, rg);
-          tmem_ld_32x32(taddr0 + 64 + h * 32, ru);
+          tmem_ld_32x32(taddr0 + gcol, rg);
+          tmem_ld_32x32(taddr0 + gcol + 64, ru);
           tmem_ld_wait();
           float g[32], u[32], a[32];
 #pragma unroll
@@ -316,13 +326,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             u[i] = __uint_as_float(ru[i]);
             a[i] = silu_f(g[i]) * u[i];
           }
-          const int nvalid = (p.N - t.n0 - 64 - h * 32);  // columns of the up half bound both halves
+          const int nvalid = p.N - (t.n0 + gcol + 64);  // columns of the up half bound both halves
           if (row_ok && nvalid > 0) {
-            if (gu) {
-              store_row32<OutT>(gu + h * 32, g, nvalid);
-              store_row32<OutT>(gu + 64 + h * 32, u, nvalid);
+            if (gu_row) {
+              store_row32<OutT>(gu_row + t.n0 + gcol, g, nvalid);
+              store_row32<OutT>(gu_row + t.n0 + gcol + 64, u, nvalid);
             }
-            store_row32<OutT>(act + h * 32, a, nvalid);
+            store_row32<OutT>(act_row + (t.n0 >> 1) + (pp >> 1) * 64 + (pp & 1) * 32, a, nvalid);
           }
         }
       } else {
@@ -330,7 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const InT* gu = reinterpret_cast<const InT*>(p.aux_in) + (long long)row * p.ld_aux;
         OutT* dgu = reinterpret_cast<OutT*>(p.out) + (long long)row * p.ldo;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
           uint32_t r[32];
           tmem_ld_32x32(taddr0 + c * 32, r);
           tmem_ld_wait();
@@ -368,7 +378,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == W_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -442,6 +452,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const gb::GemmPara
 template <int EPI, typename OutT, typename InT>
 int dispatch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const gb::GemmParams& p, int max_tiles, cudaStream_t st) {
   if constexpr (EPI == gb::EPI_SWIGLU_FWD) {
+    if (bn == 256) return launch_gemm<256, 4, EPI, OutT, InT>(ta, tb, p, max_tiles, st);
     return launch_gemm<128, 6, EPI, OutT, InT>(ta, tb, p, max_tiles, st);
   } else {
     if (bn == 64) return launch_gemm<64, 8, EPI, OutT, InT>(ta, tb, p, max_tiles, st);
@@ -491,11 +502,10 @@ extern "C" int gb_gemm(const gb_gemm_args* a, cudaStream_t st) {
       if (ot == 1) return dispatch_bn<gb::EPI_STORE, __nv_bfloat16, __nv_bfloat16>(bn, ta, tb, p, max_tiles, st);
       return dispatch_bn<gb::EPI_STORE, __half, __half>(bn, ta, tb, p, max_tiles, st);
     case gb::EPI_SWIGLU_FWD:
-      if (ot == 1) return dispatch_bn<gb::EPI_SWIGLU_FWD, __nv_bfloat16, __nv_bfloat16>(128, ta, tb, p, max_tiles, st);
-      if (ot == 0) return dispatch_bn<gb::EPI_SWIGLU_FWD, __half, __half>(128, ta, tb, p, max_tiles, st);
+      if (ot == 1) return dispatch_bn<gb::EPI_SWIGLU_FWD, __nv_bfloat16, __nv_bfloat16>(bn == 256 ? 256 : 128, ta, tb, p, max_tiles, st);
+      if (ot == 0) return dispatch_bn<gb::EPI_SWIGLU_FWD, __half, __half>(bn == 256 ? 256 : 128, ta, tb, p, max_tiles, st);
       return -1;
     case gb::EPI_SWIGLU_BWD:
-      if (bn == 256) return -1;
       if (ot == 1) return dispatch_bn<gb::EPI_SWIGLU_BWD, __nv_bfloat16, __nv_bfloat16>(bn, ta, tb, p, max_tiles, st);
       if (ot == 0) return dispatch_bn<gb::EPI_SWIGLU_BWD, __half, __half>(bn, ta, tb, p, max_tiles, st);
       return -1;

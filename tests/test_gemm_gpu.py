@@ -67,9 +67,9 @@ def test_fp32_accumulate_and_residual():
     assert ok, rel
 
 
-def test_swiglu_forward_backward_epilogues():
+@pytest.mark.parametrize("M,d,E", [(200, 256, 192), (4136, 256, 512)])     # the second takes the 256-wide tiles
+def test_swiglu_forward_backward_epilogues(M, d, E):
     G, L = _ops()
-    M, d, E = 200, 256, 192
     x = _rand(M, d, seed=7)
     wg, wu = _rand(E, d, seed=8) * 0.2, _rand(E, d, seed=9) * 0.2
     wgu = G.interleave_gate_up(wg, wu).contiguous()
