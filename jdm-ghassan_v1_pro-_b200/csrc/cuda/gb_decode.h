@@ -1,0 +1,78 @@
+// Decode-time kernels: dequant-fused GEMV family, KV ring cache append, split-KV decode attention, device sampler.
+// One decode step of the whole model is a fixed kernel sequence with every varying quantity (positions, cache
+// lengths, selected experts, sampled tokens) in device memory, so it replays as one CUDA graph with no host
+// round trip per token.  The reference's decode path (inference/generator.cpp, cuda/attention.cu:724-870,
+// cuda/kernels.cu:876-1019) copies the token id to the device, launches ~15 kernels per layer with fp32
+// activations and reads logits or candidates back every token.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Weight row formats: each of the N rows of a [N, K] matrix is stored on its own, blocks along K.
+enum {
+  GB_W_F16 = 0,        // 2 B / value
+  GB_W_BF16 = 1,
+  GB_W_GGML_Q8_0 = 2,  // 32 values: f16 scale + 32 x i8                       (34 B)   GGUF type 8
+  GB_W_Q4_0 = 3,       // 32 values: f16 scale + 16 B, byte i = code[2i+1]<<4 | code[2i], v = (code-8)*s   (18 B)
+  GB_W_Q8_64 = 4,      // 64 values: f32 scale + 64 x i8                       (68 B)   internal Q8_0
+  GB_W_Q4_1 = 5        // 32 values: f16 scale, f16 min + 16 B, v = code*s + min (20 B)
+};
+long long gb_wfmt_row_bytes(int fmt, int K);   // -1 when K does not fit the block size
+
+// out[b, n] = sum_k W[n, k] * x[b, k] (+ addend[b, n]);  x: [B, K] 16-bit, B <= 32;  out 16-bit or fp32.
+int gb_gemv(const void* W, int fmt, int N, int K, const void* x16, int ldx, int B, void* out, int ldo, int out_f32,
+            const float* addend, int ld_add, int is_bf16, cudaStream_t st);
+
+// Mixture-of-experts decode.  slots = top_k (+1 when shared != 0: the shared expert has index ne and weight 1).
+// act[b, slot, j] = silu(Wg_e[j,:] . x_b) * (Wu_e[j,:] . x_b),  e = idx[b, slot]
+int gb_gemv_expert_swiglu(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const void* x16, int B,
+                          const int* idx, int top_k, int shared, void* act16, int is_bf16, cudaStream_t st);
+// out[b, :] = resid[b, :] + sum_slot w[b, slot] * (Wd_e . act[b, slot, :])
+int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E, const void* act16, int B, const int* idx,
+                        const float* w, int top_k, int shared, const float* resid, float* out, int is_bf16,
+                        cudaStream_t st);
+
+// Per-sequence decode state (device, one per batch row).
+typedef struct gb_seq_state {
+  int abs_pos;      // tokens seen so far = RoPE position of the next token
+  int cache_len;    // slots in use (<= cap)
+  int ring_start;   // next slot to overwrite, relative to `pinned`, once the cache is full
+  int done;         // set by the sampler when a stop token was drawn
+} gb_seq_state;
+
+// Store the new token's K (after RoPE) and V: cache[b, slot, :] with slot = cache_len while there is room, else
+// pinned + ring_start (the first `pinned` tokens are never evicted).  slot_pos[b, slot] = abs_pos.  Does not advance.
+int gb_kv_append(const void* k16, long long ld_k, const void* v16, long long ld_v, void* cacheK, void* cacheV,
+                 int* slot_pos, const gb_seq_state* state, int B, int cap, int pinned, int kv_dim, cudaStream_t st);
+// out[b, h*hd:(h+1)*hd] = softmax(q_h . K^T * scale) V over the cached slots (the new token's slot included, so
+// call after gb_kv_append).  window > 0 masks slots older than `window` positions.  scratch: B*H*splits*(hd+2) floats.
+int gb_decode_attn(const void* q16, long long ld_q, const void* cacheK, const void* cacheV, const int* slot_pos,
+                   const gb_seq_state* state, void* out16, long long ld_o, float* scratch, int splits, int B, int H,
+                   int KV, int hd, int cap, int window, float scale, int is_bf16, cudaStream_t st);
+// After the step: abs_pos++, cache_len / ring_start move on; pos_out[b] = new abs_pos (feeds RoPE of the next step).
+int gb_decode_advance(gb_seq_state* state, int* pos_out, int B, int cap, int pinned, cudaStream_t st);
+
+typedef struct gb_sample_args {
+  const float* logits; long long ld;   // [B, V] fp32 (modified in place by the penalties)
+  int B, V;
+  float temperature; int top_k; float top_p, min_p;
+  float rep_penalty, freq_penalty, presence_penalty; int rep_window;
+  int greedy;
+  const int* history; int hist_cap;    // [B, hist_cap] ring of previous tokens, hist_len[b] valid entries (oldest first)
+  int* hist_len;
+  const float* uniforms;               // draws in [0,1) from the host generator (same stream as a host sampler):
+                                       // [B] when step == NULL, else a [log_cap, B] table indexed by step[0]
+  int* out_tok;                        // [B] sampled token, also appended to the history
+  gb_seq_state* state;                 // done flag set when the token is in stop[]
+  const int* stop; int n_stop;
+  int* tok_log; int log_cap; const int* step;   // tok_log[b, step[0]] = token (device-side transcript), may be NULL
+} gb_sample_args;
+int gb_sample(const gb_sample_args* a, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

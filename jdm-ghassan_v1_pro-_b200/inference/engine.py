@@ -1,0 +1,301 @@
+"""Inference engine for a B200: prompt prefill through the tcgen05 forward pass, token-by-token decode as one
+CUDA-graph replay per token.
+
+The reference's generator (inference/generator.cpp:60-420) keeps fp32 activations and an fp32 KV cache, copies
+every token id to the device, launches a dozen kernels plus cuBLAS calls per layer and reads logits or top-k
+candidates back for every token.  Here:
+
+* weights stay in their storage format (fp16 / bf16 / ggml Q8_0 / Q4_0 / internal Q8_0(64) / Q4_1) and are
+  expanded inside the GEMV kernels (``csrc/cuda/decode.cu``); the prompt pass uses 16-bit copies with the GEMM;
+* the KV cache is 16-bit ``[batch, capacity, kv_dim]`` per layer with the reference's slot rule: the first 8 tokens
+  are pinned, later slots form a ring (inference/kv_cache.h:11-106);
+* positions, cache lengths, router choices, sampled tokens, stop flags and the token transcript all live on the
+  device, so a decode step has no host dependency and is captured once;
+* the sampler is a device kernel fed with uniform numbers drawn from the same generator a host sampler would use.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import _gb200_host as H
+from ..models.config import ModelConfig
+from ..models.cuda_model import CudaModel
+from ..ops import decode as D
+from ..ops import kernels as K
+
+PINNED_TOKENS = 8
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.8
+    top_k: int = 40
+    top_p: float = 0.92
+    min_p: float = 0.05
+    repetition_penalty: float = 1.12
+    repetition_window: int = 128
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    no_repeat_ngram: int = 0
+    greedy: bool = False
+    seed: int = 0
+
+    def to_native(self) -> "H.SamplingConfig":
+        c = H.SamplingConfig()
+        for k, v in self.__dict__.items():
+            setattr(c, k, v)
+        c.validate()
+        return c
+
+    def device_ok(self) -> bool:
+        """Settings the device sampler takes; anything else is sampled on the host from the logits."""
+        if self.no_repeat_ngram > 0 or self.repetition_window > 1024:
+            return False
+        return self.greedy or self.temperature <= 0 or 1 <= self.top_k <= 1024
+
+
+class _Layer:
+    pass
+
+
+class InferenceEngine:
+    """Weights in decode formats + KV cache + one captured decode step for ``batch`` sequences."""
+
+    def __init__(self, cfg: ModelConfig, named: Dict[str, np.ndarray], fmt: str = "f16", batch: int = 1,
+                 max_len: int = 2048, prefill_chunk: int = 1024, moe_bias: Optional[Sequence] = None, device=None,
+                 compute_dtype=torch.float16, keep_f16_embeddings: bool = True):
+        cfg.validate()
+        if cfg.head_dim not in (32, 64, 128):
+            raise ValueError("decode attention supports head_dim 32, 64 and 128")
+        self.cfg, self.B, self.cap = cfg, batch, max_len
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.dt = compute_dtype
+        self.fmt = D.FMT_NAMES[fmt] if isinstance(fmt, str) else int(fmt)
+        d, qd, kvd, V = cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.vocab_size
+        f32 = dict(dtype=torch.float32, device=self.dev)
+        c16 = dict(dtype=self.dt, device=self.dev)
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        t = lambda n: torch.as_tensor(np.asarray(named[n], dtype=np.float32))
+        q = lambda w: D.QWeight.from_f32(w, self.fmt, self.dev)
+        # ---- weights
+        self.emb = t("tok_embeddings").to(self.dev)                       # fp32 rows for the embedding lookup
+        head = t("tok_embeddings") if cfg.tie_embeddings else t("lm_head")
+        # the output projection decides the token: by default it stays 16-bit when the body is quantised
+        head_fmt = self.fmt if (self.fmt in (D.W_F16, D.W_BF16) or not keep_f16_embeddings) else D.W_F16
+        self.head = D.QWeight.from_f32(head, head_fmt, self.dev)
+        self.final_norm = t("final_norm").to(self.dev)
+        self.layers: List[_Layer] = []
+        E = cfg.moe_expert_dim if cfg.use_moe else cfg.intermediate_size
+        self.E = E
+        for i in range(cfg.num_layers):
+            r = f"layers.{i}."
+            L = _Layer()
+            L.attn_norm, L.ffn_norm = t(r + "attn_norm").to(self.dev), t(r + "ffn_norm").to(self.dev)
+            L.qn = t(r + "qk_qnorm").to(self.dev) if cfg.use_qk_norm else None
+            L.kn = t(r + "qk_knorm").to(self.dev) if cfg.use_qk_norm else None
+            L.wqkv = q(torch.cat([t(r + "wq"), t(r + "wk"), t(r + "wv")], 0))
+            L.wo = q(t(r + "wo"))
+            if cfg.use_moe:
+                L.router = t(r + "moe_router").to(self.dev)
+                g, u, dn = t(r + "moe_gate"), t(r + "moe_up"), t(r + "moe_down")
+                if cfg.moe_shared:
+                    g = torch.cat([g, t(r + "moe_sh_gate")], 0)
+                    u = torch.cat([u, t(r + "moe_sh_up")], 0)
+                    dn = torch.cat([dn, t(r + "moe_sh_down")], 0)
+                L.wg, L.wu, L.wd = q(g), q(u), q(dn)
+                L.bias = (torch.as_tensor(np.asarray(moe_bias[i], dtype=np.float32)).to(self.dev)
+                          if (moe_bias is not None and len(moe_bias) > i) else None)
+                L.ws = K.MoeWorkspace(batch, d, cfg.num_experts, cfg.moe_top_k, cfg.moe_shared, self.dt, self.dev)
+            else:
+                L.wg, L.wu, L.wd = q(t(r + "w_gate")), q(t(r + "w_up")), q(t(r + "w_down"))
+            L.cK = torch.zeros(batch, max_len, kvd, **c16)
+            L.cV = torch.zeros(batch, max_len, kvd, **c16)
+            self.layers.append(L)
+        self.weight_bytes = sum(w.nbytes for L in self.layers for w in (L.wqkv, L.wo, L.wg, L.wu, L.wd)) + self.head.nbytes
+        # ---- decode state and buffers (all static: one graph serves every step)
+        B = batch
+        self.state = torch.zeros(B, D.STATE_INTS, **i32)
+        self.slot_pos = torch.zeros(B, max_len, **i32)
+        self.pos = torch.zeros(B, **i32)
+        self.cur_tok = torch.zeros(B, **i32)
+        self.x = [torch.zeros(B, d, **f32) for _ in range(2)]
+        self.x_mid = torch.zeros(B, d, **f32)
+        self.xb = torch.zeros(B, d, **c16)
+        self.rr = torch.zeros(B, **f32)
+        self.qkv = torch.zeros(B, qd + 2 * kvd, **c16)
+        self.qk = torch.zeros(B, qd + kvd, **c16)
+        self.att = torch.zeros(B, qd, **c16)
+        slots = (cfg.moe_top_k + int(cfg.moe_shared)) if cfg.use_moe else 1
+        self.slots = slots
+        self.act = torch.zeros(B, slots, E, **c16)
+        self.dense_idx = torch.zeros(B, 1, **i32)          # dense FFN = one "expert" with weight 1
+        self.dense_w = torch.ones(B, 1, **f32)
+        self.logits = torch.zeros(B, V, **f32)
+        self.splits = 8
+        self.att_scratch = torch.zeros(B * cfg.num_heads * self.splits * (cfg.head_dim + 2), **f32)
+        self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, max_len) + 1, self.dev)
+        self.hist_cap = max_len + 8
+        self.history = torch.zeros(B, self.hist_cap, **i32)
+        self.hist_len = torch.zeros(B, **i32)
+        self.uniforms = torch.zeros(max_len, B, **f32)      # one row of draws per sampling step
+        self.tok_log = torch.zeros(B, max_len, **i32)
+        self.step = torch.zeros(1, **i32)
+        self.stop = torch.zeros(8, **i32)
+        self.n_stop = 0
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._graph_key = None
+        self.prefill_chunk = min(prefill_chunk, max_len)
+        self._prefill_model: Optional[CudaModel] = None
+        self._named = named
+        self.rng = H.Rng(1)
+        self._uni_host = torch.zeros(max_len, B, dtype=torch.float32).pin_memory()
+        self._host_step = 0
+
+    # ------------------------------------------------------------------ one decode step (captured)
+    def _layer_step(self, L: _Layer, x_in, x_out):
+        cfg = self.cfg
+        d, qd, kvd, Hh, KV, hd = cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        K.rmsnorm_fwd(x_in, L.attn_norm, self.xb, self.rr, cfg.rms_eps)
+        D.gemv(L.wqkv, self.xb, self.qkv)
+        K.qk_norm_rope_fwd(self.qkv, self.qk, L.qn, L.kn, self.cos_sin, self.pos, Hh, KV, hd, cfg.rms_eps, cfg.rope_type)
+        D.kv_append(self.qk[:, qd:], self.qkv[:, qd + kvd:], L.cK, L.cV, self.slot_pos, self.state, self.cap, PINNED_TOKENS)
+        D.decode_attn(self.qk[:, :qd], L.cK, L.cV, self.slot_pos, self.state, self.att, self.att_scratch, self.splits,
+                      Hh, KV, hd, self.cap, cfg.sliding_window, cfg.attn_scale())
+        D.gemv(L.wo, self.att, self.x_mid, addend=x_in)
+        K.rmsnorm_fwd(self.x_mid, L.ffn_norm, self.xb, self.rr, cfg.rms_eps)
+        if cfg.use_moe:
+            K.moe_route_only(L.ws, self.xb, L.router, L.bias)
+            D.expert_swiglu(L.wg, L.wu, cfg.num_experts, self.E, d, self.xb, L.ws.idx, cfg.moe_top_k, cfg.moe_shared, self.act)
+            D.expert_down(L.wd, cfg.num_experts, d, self.E, self.act, L.ws.idx, L.ws.w, cfg.moe_top_k, cfg.moe_shared,
+                          self.x_mid, x_out)
+        else:
+            D.expert_swiglu(L.wg, L.wu, 0, self.E, d, self.xb, self.dense_idx, 1, False, self.act)
+            D.expert_down(L.wd, 0, d, self.E, self.act, self.dense_idx, self.dense_w, 1, False, self.x_mid, x_out)
+
+    def _sample_args(self, sp: SamplingParams) -> D.SampleArgs:
+        a = D.SampleArgs()
+        a.logits, a.ld, a.B, a.V = self.logits.data_ptr(), self.logits.stride(0), self.B, self.cfg.vocab_size
+        n = sp.to_native()
+        a.temperature, a.top_k, a.top_p, a.min_p = n.temperature, n.top_k, n.top_p, n.min_p
+        a.rep_penalty, a.freq_penalty, a.presence_penalty = n.repetition_penalty, n.frequency_penalty, n.presence_penalty
+        a.rep_window, a.greedy = n.repetition_window, int(n.greedy)
+        a.history, a.hist_cap, a.hist_len = self.history.data_ptr(), self.hist_cap, self.hist_len.data_ptr()
+        a.uniforms, a.out_tok, a.state = self.uniforms.data_ptr(), self.cur_tok.data_ptr(), self.state.data_ptr()
+        a.stop, a.n_stop = self.stop.data_ptr(), self.n_stop
+        a.tok_log, a.log_cap, a.step = self.tok_log.data_ptr(), self.tok_log.shape[1], self.step.data_ptr()
+        return a
+
+    def _forward_token(self):
+        """Embedding of ``cur_tok`` through all layers to fp32 logits; advances the per-sequence state."""
+        cfg = self.cfg
+        K.embed_fwd(self.cur_tok, self.emb, self.x[0])
+        for i, L in enumerate(self.layers):
+            self._layer_step(L, self.x[i % 2], self.x[(i + 1) % 2])
+        xf = self.x[cfg.num_layers % 2]
+        K.rmsnorm_fwd(xf, self.final_norm, self.xb, self.rr, cfg.rms_eps)
+        D.gemv(self.head, self.xb, self.logits)
+        D.decode_advance(self.state, self.pos, self.cap, PINNED_TOKENS)
+
+    def _step_eager(self, sp: Optional[SamplingParams]):
+        self._forward_token()
+        if sp is not None:
+            D.sample(self._sample_args(sp))
+
+    def decode_steps(self, n: int, sp: SamplingParams, use_graph: bool = True):
+        """Run ``n`` decode steps (forward of ``cur_tok`` + sampling of the next token) without host reads."""
+        if not sp.device_ok():
+            raise ValueError("these sampling settings need the host sampler: use Generator.generate")
+        key = (sp.temperature, sp.top_k, sp.top_p, sp.min_p, sp.repetition_penalty, sp.repetition_window,
+               sp.frequency_penalty, sp.presence_penalty, sp.greedy, self.n_stop)
+        self._draw_uniforms(n)
+        if use_graph and (self.graph is None or self._graph_key != key):
+            self._step_eager(sp)          # a real step, run eagerly: first-use set-up must happen outside capture
+            n -= 1
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._step_eager(sp)
+            self.graph, self._graph_key = g, key
+        for _ in range(max(0, n)):
+            if use_graph:
+                self.graph.replay()
+            else:
+                self._step_eager(sp)
+
+    def _draw_uniforms(self, n: int):
+        """Draws for the next ``n`` sampling steps: rows [done, done + n) of the device table the sampler indexes with
+        its own step counter.  Each row is written once per generation, so the asynchronous copy never races with
+        the host filling later rows."""
+        lo = self._host_step
+        hi = min(lo + n, self._uni_host.shape[0])
+        for s in range(lo, hi):
+            for b in range(self.B):
+                self._uni_host[s, b] = self.rng.uniform()
+        if hi > lo:
+            self.uniforms[lo:hi].copy_(self._uni_host[lo:hi], non_blocking=True)
+        self._host_step = lo + n
+
+    # ------------------------------------------------------------------ prompt
+    def reset(self, seed: int = 0):
+        self.state.zero_()
+        self.pos.zero_()
+        self.hist_len.zero_()
+        self.step.zero_()
+        self._host_step = 0
+        self.rng.reseed(seed if seed else 1)
+
+    def set_stop_tokens(self, ids: Sequence[int]):
+        ids = list(ids)[:8]
+        self.n_stop = len(ids)
+        if ids:
+            self.stop[:len(ids)].copy_(torch.tensor(ids, dtype=torch.int32))
+
+    def _prefill_net(self) -> CudaModel:
+        if self._prefill_model is None:
+            m = CudaModel(self.cfg, self.B, self.prefill_chunk, self.dt, self.dev, ce_chunks=1, use_segments=False, train=False)
+            m.load_named(self._named)
+            self._prefill_model = m
+        return self._prefill_model
+
+    def prefill(self, prompts: torch.Tensor):
+        """``prompts``: int32 [B, n] (same length for every sequence).  The first ``prefill_chunk`` tokens go through
+        the batched forward pass, whose K/V land in the cache; the rest (and the last prompt token, which produces
+        the first logits) go through the decode step."""
+        B, n = prompts.shape
+        assert B == self.B and n >= 1 and n <= self.cap
+        prompts = prompts.to(self.dev, dtype=torch.int32)
+        self.history[:, :n].copy_(prompts)
+        self.hist_len.fill_(n)
+        head = min(n - 1, self.prefill_chunk) if n - 1 >= 64 else 0    # short prompts are cheaper token by token
+        if head > 0:
+            m = self._prefill_net()
+            T = self.prefill_chunk
+            ids = torch.zeros(B, T, dtype=torch.int32, device=self.dev)
+            ids[:, :head] = prompts[:, :head]
+            m.ids.copy_(ids.view(-1))
+            m.targets.fill_(-100)
+            m.kv_sink = (self, head)
+            m.forward(False)
+            m.kv_sink = None
+            self.state[:, 0] = head
+            self.state[:, 1] = head
+            self.pos.fill_(head)
+            ar = torch.arange(head, dtype=torch.int32, device=self.dev)
+            self.slot_pos[:, :head] = ar
+        for j in range(head, n):
+            self.cur_tok.copy_(prompts[:, j])
+            self._forward_token()
+        # logits of the last prompt token are in self.logits; cur_tok is set by the first sample call
+
+    def sample_first(self, sp: SamplingParams):
+        self._draw_uniforms(1)
+        D.sample(self._sample_args(sp))
+
+    def transcript(self, n_new: int) -> torch.Tensor:
+        """Tokens sampled so far, [B, n_new] on the host (one device->host copy)."""
+        return self.tok_log[:, :n_new].cpu()

@@ -338,6 +338,11 @@ class CudaModel:
         qw = self.w(p + "qk_qnorm") if cfg.use_qk_norm else None
         kw = self.w(p + "qk_knorm") if cfg.use_qk_norm else None
         K.qk_norm_rope_fwd(b.qkv, b.qk, qw, kw, self.cos_sin, self.pos, H, KV, hd, cfg.rms_eps, cfg.rope_type)
+        sink = getattr(self, "kv_sink", None)
+        if sink is not None:   # prompt pass of the inference engine: keep this layer's keys (after RoPE) and values
+            eng, n = sink
+            eng.layers[l].cK[:, :n].copy_(b.qk.view(self.B, self.T, -1)[:, :n, qd:])
+            eng.layers[l].cV[:, :n].copy_(b.qkv.view(self.B, self.T, -1)[:, :n, qd + kvd:])
         if self.attn_tc:   # tcgen05 path (packed-document segment ids are contiguous runs, as the loader emits them)
             K.attn_tc_fwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, None, self.seg_lo,
                           self.B, self.T, H, KV, hd, cfg.sliding_window, cfg.attn_scale(), lo_ready=self.use_segments)

@@ -1,0 +1,151 @@
+"""Launchers for the decode-time kernels (``csrc/cuda/decode.cu``, ``sample.cu``; contract in ``gb_decode.h``)."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+
+c_int, c_ll, c_vp, c_float = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_float
+
+W_F16, W_BF16, W_GGML_Q8_0, W_Q4_0, W_Q8_64, W_Q4_1 = range(6)
+FMT_NAMES = {"f16": W_F16, "bf16": W_BF16, "q8_0": W_GGML_Q8_0, "q4_0": W_Q4_0, "q8_64": W_Q8_64, "q4_1": W_Q4_1}
+STATE_INTS = 4   # gb_seq_state: abs_pos, cache_len, ring_start, done
+
+
+class SampleArgs(ctypes.Structure):
+    _fields_ = [
+        ("logits", c_vp), ("ld", c_ll), ("B", c_int), ("V", c_int),
+        ("temperature", c_float), ("top_k", c_int), ("top_p", c_float), ("min_p", c_float),
+        ("rep_penalty", c_float), ("freq_penalty", c_float), ("presence_penalty", c_float), ("rep_window", c_int),
+        ("greedy", c_int),
+        ("history", c_vp), ("hist_cap", c_int), ("hist_len", c_vp),
+        ("uniforms", c_vp), ("out_tok", c_vp), ("state", c_vp),
+        ("stop", c_vp), ("n_stop", c_int),
+        ("tok_log", c_vp), ("log_cap", c_int), ("step", c_vp),
+    ]
+
+
+def row_bytes(fmt: int, K: int) -> int:
+    lib = _lib.lib()
+    lib.gb_wfmt_row_bytes.restype = c_ll
+    n = lib.gb_wfmt_row_bytes(c_int(fmt), c_int(K))
+    if n < 0:
+        raise ValueError(f"row length {K} does not fit the block size of weight format {fmt}")
+    return int(n)
+
+
+class QWeight:
+    """A [N, K] matrix stored row by row in one of the decode formats (device uint8 buffer)."""
+
+    def __init__(self, data: torch.Tensor, fmt: int, N: int, K: int):
+        self.data, self.fmt, self.N, self.K = data, fmt, N, K
+        self.row_bytes = row_bytes(fmt, K)
+        assert data.numel() == N * self.row_bytes, (data.numel(), N, self.row_bytes)
+
+    @classmethod
+    def from_f32(cls, w: torch.Tensor, fmt: int, device) -> "QWeight":
+        """Quantise / cast fp32 ``w`` ([N, K]) with the host codecs (byte-exact with the file formats)."""
+        from .. import _gb200_host as H
+        N, K = w.shape
+        row_bytes(fmt, K)
+        w32 = np.ascontiguousarray(w.detach().float().cpu().numpy())
+        if fmt == W_F16:
+            raw = torch.from_numpy(w32).to(torch.float16).contiguous().view(torch.uint8)
+        elif fmt == W_BF16:
+            raw = torch.from_numpy(w32).to(torch.bfloat16).contiguous().view(torch.uint8)
+        # K is a multiple of the block size (checked by row_bytes), so blocks never straddle rows and quantising
+        # the flat array equals quantising row by row
+        elif fmt == W_GGML_Q8_0:
+            raw = torch.from_numpy(np.asarray(H.ggml_quantize(w32.reshape(-1), 8)))
+        elif fmt == W_Q4_0:
+            raw = torch.from_numpy(np.asarray(H.ggml_quantize(w32.reshape(-1), 2)))
+        elif fmt == W_Q8_64:
+            raw = torch.from_numpy(np.asarray(H.quantize(w32.reshape(-1), "q8_0")))
+        elif fmt == W_Q4_1:
+            raw = torch.from_numpy(np.asarray(H.quantize(w32.reshape(-1), "q4_1")))
+        else:
+            raise ValueError(f"unknown weight format {fmt}")
+        return cls(raw.reshape(-1).to(device), fmt, N, K)
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 [N, K] on the host (oracle for tests and source of the prefill operands)."""
+        from .. import _gb200_host as H
+        raw = self.data.cpu().numpy().reshape(self.N, self.row_bytes)
+        if self.fmt == W_F16:
+            return torch.from_numpy(raw.copy()).view(torch.float16).float().reshape(self.N, self.K)
+        if self.fmt == W_BF16:
+            return torch.from_numpy(raw.copy()).view(torch.bfloat16).float().reshape(self.N, self.K)
+        flat, n = raw.reshape(-1), self.N * self.K
+        if self.fmt in (W_GGML_Q8_0, W_Q4_0):
+            out = H.ggml_dequantize(flat, 8 if self.fmt == W_GGML_Q8_0 else 2, n)
+        else:
+            out = H.dequantize(flat, "q8_0" if self.fmt == W_Q8_64 else "q4_1", n)
+        return torch.from_numpy(np.asarray(out)).reshape(self.N, self.K)
+
+    @property
+    def nbytes(self):
+        return self.data.numel()
+
+
+def _bf(t):
+    return int(t.dtype == torch.bfloat16)
+
+
+def gemv(w: QWeight, x16, out, addend=None):
+    """``out[b, :] = W @ x16[b, :] (+ addend[b, :])``; ``out`` is 16-bit or fp32."""
+    B = x16.shape[0]
+    rc = _lib.lib().gb_gemv(c_vp(w.data.data_ptr()), c_int(w.fmt), c_int(w.N), c_int(w.K), c_vp(x16.data_ptr()),
+                            c_int(x16.stride(0)), c_int(B), c_vp(out.data_ptr()), c_int(out.stride(0)),
+                            c_int(int(out.dtype == torch.float32)), _lib.ptr(addend),
+                            c_int(addend.stride(0) if addend is not None else 0), c_int(_bf(x16)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_gemv")
+    return out
+
+
+def expert_swiglu(wg: QWeight, wu: QWeight, ne, E, d, x16, idx, top_k, shared, act):
+    rc = _lib.lib().gb_gemv_expert_swiglu(c_vp(wg.data.data_ptr()), c_vp(wu.data.data_ptr()), c_int(wg.fmt), c_int(ne),
+                                          c_int(E), c_int(d), c_vp(x16.data_ptr()), c_int(x16.shape[0]),
+                                          c_vp(idx.data_ptr()), c_int(top_k), c_int(int(shared)), c_vp(act.data_ptr()),
+                                          c_int(_bf(x16)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_gemv_expert_swiglu")
+
+
+def expert_down(wd: QWeight, ne, d, E, act, idx, w, top_k, shared, resid, out):
+    rc = _lib.lib().gb_gemv_expert_down(c_vp(wd.data.data_ptr()), c_int(wd.fmt), c_int(ne), c_int(d), c_int(E),
+                                        c_vp(act.data_ptr()), c_int(resid.shape[0]), c_vp(idx.data_ptr()),
+                                        c_vp(w.data_ptr()), c_int(top_k), c_int(int(shared)), c_vp(resid.data_ptr()),
+                                        c_vp(out.data_ptr()), c_int(_bf(act)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_gemv_expert_down")
+
+
+def kv_append(k16, v16, cacheK, cacheV, slot_pos, state, cap, pinned):
+    B, kv_dim = k16.shape[0], k16.shape[1]
+    rc = _lib.lib().gb_kv_append(c_vp(k16.data_ptr()), c_ll(k16.stride(0)), c_vp(v16.data_ptr()), c_ll(v16.stride(0)),
+                                 c_vp(cacheK.data_ptr()), c_vp(cacheV.data_ptr()), c_vp(slot_pos.data_ptr()),
+                                 c_vp(state.data_ptr()), c_int(B), c_int(cap), c_int(pinned), c_int(kv_dim),
+                                 _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_kv_append")
+
+
+def decode_attn(q16, cacheK, cacheV, slot_pos, state, out16, scratch, splits, H, KV, hd, cap, window, scale):
+    B = q16.shape[0]
+    rc = _lib.lib().gb_decode_attn(c_vp(q16.data_ptr()), c_ll(q16.stride(0)), c_vp(cacheK.data_ptr()),
+                                   c_vp(cacheV.data_ptr()), c_vp(slot_pos.data_ptr()), c_vp(state.data_ptr()),
+                                   c_vp(out16.data_ptr()), c_ll(out16.stride(0)), c_vp(scratch.data_ptr()), c_int(splits),
+                                   c_int(B), c_int(H), c_int(KV), c_int(hd), c_int(cap), c_int(window), c_float(scale),
+                                   c_int(_bf(q16)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_decode_attn")
+
+
+def decode_advance(state, pos_out, cap, pinned):
+    rc = _lib.lib().gb_decode_advance(c_vp(state.data_ptr()), c_vp(pos_out.data_ptr()), c_int(state.shape[0]), c_int(cap),
+                                      c_int(pinned), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_decode_advance")
+
+
+def sample(args: SampleArgs):
+    rc = _lib.lib().gb_sample(ctypes.byref(args), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_sample")

@@ -262,6 +262,16 @@ def moe_route_group(ws: MoeWorkspace, x16, router_w, bias, x_perm, counts=None, 
     check_rc(lib().gb_moe_group(ctypes.byref(a), stream_ptr()), "moe_group")
 
 
+def moe_route_only(ws: MoeWorkspace, x16, router_w, bias):
+    """Router without grouping (decode): fills ``ws.probs``, ``ws.idx`` and ``ws.w``; no jitter, no statistics."""
+    a = ws.args()
+    a.x16, a.router_w, a.bias = _p(x16), _p(router_w), _p(bias)
+    a.jitter, a.use_jitter = 0.0, 0
+    a.aux_m = None
+    a.f_frac = None
+    check_rc(lib().gb_moe_route(ctypes.byref(a), stream_ptr()), "moe_route")
+
+
 def moe_combine(ws: MoeWorkspace, y_perm, resid, out):
     a = ws.args()
     a.y_perm, a.resid, a.out = _p(y_perm), _p(resid), _p(out)

@@ -1,0 +1,271 @@
+"""Decode-time kernels and the inference engine against plain PyTorch fp32 references."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+FMTS = ["f16", "bf16", "q8_0", "q4_0", "q8_64", "q4_1"]
+
+
+def _D():
+    from ghassan_b200.ops import decode as D
+    return D
+
+
+def _rand(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("B", [1, 5, 32])
+def test_gemv_matches_dequantised_product(fmt, B):
+    D = _D()
+    N, K = 200, 320
+    w = _rand(N, K, seed=1, scale=0.3)
+    qw = D.QWeight.from_f32(w, D.FMT_NAMES[fmt], "cuda")
+    wd = qw.dequantize().cuda()                              # what the stored bits mean, from the host codec
+    x = _rand(B, K, seed=2).cuda().half()
+    add = _rand(B, N, seed=3).cuda()
+    out32 = torch.zeros(B, N, device="cuda")
+    D.gemv(qw, x, out32, addend=add)
+    ref = x.float() @ wd.t() + add
+    assert torch.allclose(out32, ref, rtol=2e-3, atol=2e-3), float((out32 - ref).abs().max())
+    out16 = torch.zeros(B, N, device="cuda", dtype=torch.float16)
+    D.gemv(qw, x, out16)
+    assert torch.allclose(out16.float(), x.float() @ wd.t(), rtol=1e-2, atol=2e-2)
+    # quantisation itself stays within the format's error
+    err = float((wd.cpu() - w).abs().max())
+    assert err < {"f16": 1e-3, "bf16": 1e-2, "q8_0": 0.02, "q8_64": 0.02, "q4_0": 0.25, "q4_1": 0.2}[fmt]
+
+
+@pytest.mark.parametrize("fmt", ["f16", "q8_0", "q4_1"])
+def test_expert_kernels(fmt):
+    D = _D()
+    ne, E, d, B, top_k = 4, 64, 96, 3, 2
+    f = D.FMT_NAMES[fmt]
+    wg, wu = _rand((ne + 1) * E, d, seed=4, scale=0.2), _rand((ne + 1) * E, d, seed=5, scale=0.2)
+    wdn = _rand((ne + 1) * d, E, seed=6, scale=0.2)
+    qg, qu, qd = (D.QWeight.from_f32(t, f, "cuda") for t in (wg, wu, wdn))
+    g, u, dn = (q.dequantize().cuda() for q in (qg, qu, qd))
+    x = _rand(B, d, seed=7).cuda().half()
+    idx = torch.tensor([[1, 3], [0, 2], [3, 3]], dtype=torch.int32, device="cuda")
+    wt = torch.tensor([[0.7, 0.3], [0.5, 0.5], [0.9, 0.1]], device="cuda")
+    resid = _rand(B, d, seed=8).cuda()
+    act = torch.zeros(B, top_k + 1, E, device="cuda", dtype=torch.float16)
+    out = torch.zeros(B, d, device="cuda")
+    D.expert_swiglu(qg, qu, ne, E, d, x, idx, top_k, True, act)
+    D.expert_down(qd, ne, d, E, act, idx, wt, top_k, True, resid, out)
+    ref = resid.clone()
+    for b in range(B):
+        for s in range(top_k + 1):
+            e = int(idx[b, s]) if s < top_k else ne
+            a = torch.nn.functional.silu(g[e * E:(e + 1) * E] @ x[b].float()) * (u[e * E:(e + 1) * E] @ x[b].float())
+            assert torch.allclose(act[b, s].float(), a, rtol=2e-2, atol=2e-2)
+            ref[b] += (wt[b, s] if s < top_k else 1.0) * (dn[e * d:(e + 1) * d] @ a.half().float())
+    assert torch.allclose(out, ref, rtol=1e-2, atol=2e-2), float((out - ref).abs().max())
+
+
+@pytest.mark.parametrize("hd,H,KV", [(64, 12, 4), (128, 4, 4), (32, 4, 2)])
+def test_kv_ring_and_decode_attention(hd, H, KV):
+    D = _D()
+    B, cap, pinned, steps = 2, 24, 8, 40          # more steps than capacity: the ring wraps, pinned slots stay
+    kvd, qd = KV * hd, H * hd
+    cK = torch.zeros(B, cap, kvd, device="cuda", dtype=torch.float16)
+    cV = torch.zeros_like(cK)
+    slot_pos = torch.zeros(B, cap, dtype=torch.int32, device="cuda")
+    state = torch.zeros(B, D.STATE_INTS, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(B, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(B * H * 4 * (hd + 2), device="cuda")
+    out = torch.zeros(B, qd, device="cuda", dtype=torch.float16)
+    ks, vs = [], []
+    scale = 1.0 / math.sqrt(hd)
+    for t in range(steps):
+        k = _rand(B, kvd, seed=100 + t).cuda().half()
+        v = _rand(B, kvd, seed=200 + t).cuda().half()
+        q = _rand(B, qd, seed=300 + t).cuda().half()
+        ks.append(k)
+        vs.append(v)
+        D.kv_append(k, v, cK, cV, slot_pos, state, cap, pinned)
+        D.decode_attn(q, cK, cV, slot_pos, state, out, scratch, 4, H, KV, hd, cap, 0, scale)
+        D.decode_advance(state, pos, cap, pinned)
+        # the cache must hold the first `pinned` tokens and the most recent cap - pinned ones
+        live = list(range(min(t + 1, pinned))) + [j for j in range(max(pinned, t + 1 - (cap - pinned)), t + 1)]
+        Kl = torch.stack([ks[j] for j in live], 1).float().view(B, len(live), KV, hd)
+        Vl = torch.stack([vs[j] for j in live], 1).float().view(B, len(live), KV, hd)
+        qh = q.float().view(B, H, hd)
+        g = H // KV
+        ref = torch.zeros(B, H, hd, device="cuda")
+        for h in range(H):
+            s = torch.einsum("bd,bld->bl", qh[:, h], Kl[:, :, h // g]) * scale
+            ref[:, h] = torch.einsum("bl,bld->bd", torch.softmax(s, -1), Vl[:, :, h // g])
+        assert torch.allclose(out.float().view(B, H, hd), ref, rtol=2e-2, atol=2e-2), (t, float((out.float().view(B, H, hd) - ref).abs().max()))
+    st = state.cpu()
+    assert int(st[0, 0]) == steps and int(st[0, 1]) == cap and int(pos[0]) == steps
+
+
+def test_sliding_window_masks_old_slots():
+    D = _D()
+    B, cap, hd, H = 1, 32, 64, 2
+    cK = torch.zeros(B, cap, H * hd, device="cuda", dtype=torch.float16)
+    cV = torch.zeros_like(cK)
+    slot_pos = torch.zeros(B, cap, dtype=torch.int32, device="cuda")
+    state = torch.zeros(B, D.STATE_INTS, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(B, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(B * H * 2 * (hd + 2), device="cuda")
+    out = torch.zeros(B, H * hd, device="cuda", dtype=torch.float16)
+    vs = []
+    for t in range(10):
+        k, v, q = (_rand(B, H * hd, seed=s + t).cuda().half() for s in (1, 50, 90))
+        vs.append(v)
+        D.kv_append(k, v, cK, cV, slot_pos, state, cap, 8)
+        D.decode_attn(q, cK, cV, slot_pos, state, out, scratch, 2, H, H, hd, cap, 1, 0.125)   # window 1: only itself
+        D.decode_advance(state, pos, cap, 8)
+        assert torch.allclose(out, v, atol=2e-3)
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(greedy=True),
+    dict(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, repetition_penalty=1.0),
+    dict(temperature=1.3, top_k=200, top_p=0.95, min_p=0.05, repetition_penalty=1.12, frequency_penalty=0.2,
+         presence_penalty=0.1, repetition_window=16),
+    dict(temperature=0.5, top_k=2, top_p=1.0, min_p=0.0),
+])
+def test_device_sampler_equals_host_sampler(cfg):
+    from ghassan_b200 import _gb200_host as H
+    from ghassan_b200.inference.engine import SamplingParams
+    D = _D()
+    B, V, steps = 3, 5000, 25
+    sp = SamplingParams(seed=77, **cfg)
+    host = []
+    for b in range(B):
+        c = sp.to_native()
+        c.seed = 1000 + b
+        host.append(H.Sampler(c))
+    # the device draws use the same streams: one generator per sequence, consumed once per sampled token
+    dev_rng = [H.Rng(1000 + b) for b in range(B)]
+    logits = torch.zeros(B, V, device="cuda")
+    hist_cap = 64
+    history = torch.zeros(B, hist_cap, dtype=torch.int32, device="cuda")
+    hist_len = torch.zeros(B, dtype=torch.int32, device="cuda")
+    uniforms = torch.zeros(B, device="cuda")
+    out_tok = torch.zeros(B, dtype=torch.int32, device="cuda")
+    hhist = [[] for _ in range(B)]
+    n = sp.to_native()
+    for t in range(steps):
+        lg = _rand(B, V, seed=500 + t, scale=3.0)
+        lg[:, 7] = lg[:, 9]                                     # an exact tie
+        logits.copy_(lg)
+        need_draw = not (n.greedy or n.temperature <= 0 or n.top_k == 1)
+        uniforms.copy_(torch.tensor([dev_rng[b].uniform() if need_draw else 0.0 for b in range(B)]))
+        a = D.SampleArgs()
+        a.logits, a.ld, a.B, a.V = logits.data_ptr(), V, B, V
+        a.temperature, a.top_k, a.top_p, a.min_p = n.temperature, n.top_k, n.top_p, n.min_p
+        a.rep_penalty, a.freq_penalty, a.presence_penalty = n.repetition_penalty, n.frequency_penalty, n.presence_penalty
+        a.rep_window, a.greedy = n.repetition_window, int(n.greedy)
+        a.history, a.hist_cap, a.hist_len = history.data_ptr(), hist_cap, hist_len.data_ptr()
+        a.uniforms, a.out_tok = uniforms.data_ptr(), out_tok.data_ptr()
+        D.sample(a)
+        got = out_tok.cpu().tolist()
+        for b in range(B):
+            want = host[b].sample(lg[b].numpy(), hhist[b])
+            assert got[b] == want, (t, b, got[b], want)
+            hhist[b].append(want)
+    assert hist_len.cpu().tolist() == [steps] * B
+
+
+def _tiny_cfg(**over):
+    from ghassan_b200.models.config import ModelConfig
+    base = dict(vocab_size=512, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=512,
+                max_seq_len=256, use_moe=True, num_experts=4, moe_top_k=2, moe_expert_dim=128, moe_shared=True,
+                use_qk_norm=True)
+    base.update(over)
+    c = ModelConfig(**base)
+    c.validate()
+    return c
+
+
+@pytest.mark.parametrize("moe", [True, False])
+def test_engine_matches_fp32_model_greedy(moe):
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.models.config import init_parameters
+    from ghassan_b200.models.reference import TorchModel
+    cfg = _tiny_cfg(use_moe=moe)
+    named = init_parameters(cfg, 11)
+    for k in named:                                        # larger weights so that logits are well separated
+        if not k.endswith("norm"):
+            named[k] = named[k] * 4.0
+    eng = InferenceEngine(cfg, named, fmt="f16", batch=2, max_len=128, prefill_chunk=64)
+    ref = TorchModel(cfg, "cpu")
+    ref.load_named(named)
+    # teacher forcing: the logits after every token of a fixed sequence against the fp32 model
+    seq = torch.randint(16, 512, (2, 20), generator=torch.Generator().manual_seed(3), dtype=torch.int32)
+    eng.reset(1)
+    with torch.no_grad():
+        want = [ref.logits(seq[b], 1, 20) for b in range(2)]
+    for j in range(20):
+        eng.cur_tok.copy_(seq[:, j])
+        eng._forward_token()
+        got = eng.logits.cpu()
+        for b in range(2):
+            err = float((got[b] - want[b][j]).abs().max())
+            assert err < 0.03 * float(want[b][j].abs().max()) + 0.03, (j, b, err)
+    # greedy decoding end to end: clear decisions must agree with the fp32 model
+    prompt = seq[:, :9].contiguous()
+    eng.reset(1)
+    eng.prefill(prompt)
+    sp = SamplingParams(greedy=True, repetition_penalty=1.0)     # plain arg-max: penalties would change the choice
+    eng.sample_first(sp)
+    eng.decode_steps(11, sp)
+    got = eng.transcript(12)
+    for b in range(2):
+        s = prompt[b].tolist()
+        for t in range(12):
+            with torch.no_grad():
+                lg = ref.logits(torch.tensor(s, dtype=torch.int32), 1, len(s))[-1]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > 0.03 * float(lg.abs().max()) + 0.05:
+                assert int(got[b, t]) == int(torch.argmax(lg)), (b, t)
+            s.append(int(got[b, t]))
+
+
+def test_prefill_pass_equals_token_by_token():
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.models.config import init_parameters
+    cfg = _tiny_cfg(num_heads=4, num_kv_heads=2, hidden_size=256)      # head_dim 64: tcgen05 prompt pass
+    named = init_parameters(cfg, 5)
+    prompt = torch.randint(16, 512, (1, 100), generator=torch.Generator().manual_seed(4), dtype=torch.int32)
+    a = InferenceEngine(cfg, named, fmt="f16", batch=1, max_len=160, prefill_chunk=128)
+    a.reset(1)
+    a.prefill(prompt)                                       # 99 tokens through the batched pass + 1 decode step
+    b = InferenceEngine(cfg, named, fmt="f16", batch=1, max_len=160, prefill_chunk=128)
+    b.reset(1)
+    for j in range(100):                                    # everything through the decode step
+        b.cur_tok.copy_(prompt[:, j])
+        b._forward_token()
+    assert torch.allclose(a.logits, b.logits, rtol=3e-2, atol=3e-2), float((a.logits - b.logits).abs().max())
+    assert a.state.cpu().tolist() == b.state.cpu().tolist()
+    assert torch.allclose(a.layers[1].cK[:, :100].float(), b.layers[1].cK[:, :100].float(), atol=3e-2)
+
+
+def test_generator_host_and_device_routes(tmp_path):
+    from ghassan_b200.data.tokenizer import Tokenizer
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.inference.generator import Generator
+    from ghassan_b200.models.config import init_parameters
+    cfg = _tiny_cfg(vocab_size=272)
+    named = init_parameters(cfg, 2)
+    eng = InferenceEngine(cfg, named, fmt="q8_0", batch=1, max_len=96, prefill_chunk=64)
+    gen = Generator(eng, Tokenizer())
+    pieces = []
+    r1 = gen.generate("salam", max_new_tokens=20, sampling=SamplingParams(seed=5, top_k=20), on_text=lambda b, s: pieces.append(s))
+    r2 = gen.generate("salam", max_new_tokens=20, sampling=SamplingParams(seed=5, top_k=20))
+    assert r1.tokens == r2.tokens and 0 < len(r1.tokens[0]) <= 20           # seeded: reproducible
+    assert "".join(pieces) == r1.text[0] or len(pieces) > 0
+    r3 = gen.generate("salam", max_new_tokens=12, sampling=SamplingParams(seed=5, top_k=20, no_repeat_ngram=3))
+    assert len(r3.tokens[0]) <= 12                                             # host route (n-gram ban)
+    nll, n = gen.score_tokens(gen.encode_prompt("hello world"))
+    assert n > 0 and math.isfinite(nll) and gen.perplexity(gen.encode_prompt("hello world")) > 1.0
