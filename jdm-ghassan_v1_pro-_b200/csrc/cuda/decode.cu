@@ -81,41 +81,58 @@ __device__ __forceinline__ float dot8(const float (&w)[8], const XT* __restrict_
   return s;
 }
 
-// one warp: dot products of one stored row with NB activation rows
-template <int FMT, int NB, typename XT>
-__device__ __forceinline__ void row_dots(const uint8_t* __restrict__ wrow, int K, const XT* __restrict__ x, long long ldx,
-                                         int nb, float (&acc)[NB]) {
+// KS warps share one stored row: warp slice ks takes units ks*32 + lane, stepping by 32*KS.  Decoding one token is
+// bound by load latency, not bandwidth (a row is a few hundred bytes), so the short rows are spread over more warps
+// and every lane keeps several independent loads in flight; the slices meet in shared memory.
+template <int FMT, int NB, int KS, typename XT>
+__device__ __forceinline__ void row_partial(const uint8_t* __restrict__ wrow, int K, const XT* __restrict__ x, long long ldx,
+                                            int nb, int ks, float (&acc)[NB]) {
   const int lane = threadIdx.x & 31;
-#pragma unroll
-  for (int j = 0; j < NB; ++j) acc[j] = 0.f;
-  for (int u = lane; u < (K >> 3); u += 32) {
+#pragma unroll 2
+  for (int u = lane + 32 * ks; u < (K >> 3); u += 32 * KS) {
     float w[8];
     load8<FMT>(wrow, u, w);
 #pragma unroll
     for (int j = 0; j < NB; ++j)
       if (j < nb) acc[j] += dot8<XT>(w, x + j * ldx + 8 * u);
   }
-#pragma unroll
-  for (int j = 0; j < NB; ++j) acc[j] = warp_sum(acc[j]);
 }
 
-template <int FMT, int NB, typename XT>
+// sum over lanes, then over the KS warps of the row; the result is valid in lane 0 of slice 0
+template <int KS>
+__device__ __forceinline__ float row_finish(float v, float* __restrict__ sm, int row_in_cta, int ks) {
+  v = warp_sum(v);
+  if constexpr (KS == 1) return v;
+  if ((threadIdx.x & 31) == 0) sm[row_in_cta * KS + ks] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < KS; ++i) t += sm[row_in_cta * KS + i];
+  __syncthreads();
+  return t;
+}
+
+template <int FMT, int NB, int KS, typename XT>
 __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const uint8_t* __restrict__ W, long long row_bytes, int N, int K,
                                                          const XT* __restrict__ x, long long ldx, int B,
                                                          void* __restrict__ out, long long ldo, int out_f32,
                                                          const float* __restrict__ addend, long long ld_add) {
-  const int row = blockIdx.x * GV_WARPS + (threadIdx.x >> 5);
-  if (row >= N) return;
-  const uint8_t* wrow = W + (size_t)row * row_bytes;
+  __shared__ float sm[GV_WARPS];
+  const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
+  const int row = blockIdx.x * (GV_WARPS / KS) + ric;
+  const bool live = row < N;                              // dead rows still take part in the block barriers
+  const uint8_t* wrow = W + (size_t)(live ? row : 0) * row_bytes;
   for (int b0 = 0; b0 < B; b0 += NB) {
     float acc[NB];
-    const int nb = min(NB, B - b0);
-    row_dots<FMT, NB, XT>(wrow, K, x + (long long)b0 * ldx, ldx, nb, acc);
-    if ((threadIdx.x & 31) == 0) {
 #pragma unroll
-      for (int j = 0; j < NB; ++j) {
-        if (j >= nb) break;
-        float v = acc[j];
+    for (int j = 0; j < NB; ++j) acc[j] = 0.f;
+    const int nb = min(NB, B - b0);
+    if (live) row_partial<FMT, NB, KS, XT>(wrow, K, x + (long long)b0 * ldx, ldx, nb, ks, acc);
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const float v0 = row_finish<KS>(acc[j], sm, ric, ks);
+      if (live && j < nb && ks == 0 && (threadIdx.x & 31) == 0) {
+        float v = v0;
         if (addend) v += addend[(long long)(b0 + j) * ld_add + row];
         if (out_f32) reinterpret_cast<float*>(out)[(long long)(b0 + j) * ldo + row] = v;
         else reinterpret_cast<XT*>(out)[(long long)(b0 + j) * ldo + row] = Cvt<XT>::from_f(v);
@@ -124,44 +141,106 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const uint8_t* __restr
   }
 }
 
-template <int FMT, typename XT>
+template <int FMT, int KS, typename XT>
 __global__ void __launch_bounds__(GV_THREADS) expert_swiglu_kernel(const uint8_t* __restrict__ Wg, const uint8_t* __restrict__ Wu,
                                                                   long long row_bytes, int ne, int E, int d,
                                                                   const XT* __restrict__ x, const int* __restrict__ idx,
                                                                   int top_k, int slots, XT* __restrict__ act) {
-  const int j = blockIdx.x * GV_WARPS + (threadIdx.x >> 5);
+  __shared__ float sm[2 * GV_WARPS];
+  const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
+  const int j = blockIdx.x * (GV_WARPS / KS) + ric;
   const int b = blockIdx.y / slots, slot = blockIdx.y % slots;
-  if (j >= E) return;
   const int e = slot < top_k ? idx[b * top_k + slot] : ne;
-  if (e < 0 || e > ne) return;
-  const size_t r = (size_t)e * E + j;
-  float g[1], u[1];
-  row_dots<FMT, 1, XT>(Wg + r * row_bytes, d, x + (long long)b * d, d, 1, g);
-  row_dots<FMT, 1, XT>(Wu + r * row_bytes, d, x + (long long)b * d, d, 1, u);
-  if ((threadIdx.x & 31) == 0) {
-    const float a = g[0] / (1.f + __expf(-g[0])) * u[0];
-    act[((long long)b * slots + slot) * E + j] = Cvt<XT>::from_f(a);
+  const bool live = j < E && e >= 0 && e <= ne;
+  float g[1] = {0.f}, u[1] = {0.f};
+  if (live) {
+    const size_t r = (size_t)e * E + j;
+    row_partial<FMT, 1, KS, XT>(Wg + r * row_bytes, d, x + (long long)b * d, d, 1, ks, g);
+    row_partial<FMT, 1, KS, XT>(Wu + r * row_bytes, d, x + (long long)b * d, d, 1, ks, u);
   }
+  const float gs = row_finish<KS>(g[0], sm, ric, ks);
+  const float us = row_finish<KS>(u[0], sm + GV_WARPS, ric, ks);
+  if (live && ks == 0 && (threadIdx.x & 31) == 0)
+    act[((long long)b * slots + slot) * E + j] = Cvt<XT>::from_f(gs / (1.f + __expf(-gs)) * us);
 }
 
-template <int FMT, typename XT>
+template <int FMT, int KS, typename XT>
 __global__ void __launch_bounds__(GV_THREADS) expert_down_kernel(const uint8_t* __restrict__ Wd, long long row_bytes, int ne, int d,
                                                                 int E, const XT* __restrict__ act, const int* __restrict__ idx,
                                                                 const float* __restrict__ w, int top_k, int slots,
                                                                 const float* __restrict__ resid, float* __restrict__ out) {
-  const int r = blockIdx.x * GV_WARPS + (threadIdx.x >> 5);
+  __shared__ float sm[GV_WARPS];
+  const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
+  const int r = blockIdx.x * (GV_WARPS / KS) + ric;
   const int b = blockIdx.y;
-  if (r >= d) return;
+  const bool live = r < d;
+  // weighted sum over the slots taken per lane before any reduction: one reduction per output value, and the
+  // loads of different slots do not wait for one another.  Slot order and lane order are fixed: reproducible.
   float total = 0.f;
-  for (int slot = 0; slot < slots; ++slot) {          // fixed slot order: the sum is reproducible
-    const int e = slot < top_k ? idx[b * top_k + slot] : ne;
-    if (e < 0 || e > ne) continue;
-    const float wgt = slot < top_k ? w[b * top_k + slot] : 1.f;
-    float y[1];
-    row_dots<FMT, 1, XT>(Wd + ((size_t)e * d + r) * row_bytes, E, act + ((long long)b * slots + slot) * E, E, 1, y);
-    total += wgt * y[0];
+  if (live) {
+    for (int slot = 0; slot < slots; ++slot) {
+      const int e = slot < top_k ? idx[b * top_k + slot] : ne;
+      if (e < 0 || e > ne) continue;
+      const float wgt = slot < top_k ? w[b * top_k + slot] : 1.f;
+      float y[1] = {0.f};
+      row_partial<FMT, 1, KS, XT>(Wd + ((size_t)e * d + r) * row_bytes, E, act + ((long long)b * slots + slot) * E, E, 1, ks, y);
+      total += wgt * y[0];
+    }
   }
-  if ((threadIdx.x & 31) == 0) out[(long long)b * d + r] = resid[(long long)b * d + r] + total;
+  const float t = row_finish<KS>(total, sm, ric, ks);
+  if (live && ks == 0 && (threadIdx.x & 31) == 0) out[(long long)b * d + r] = resid[(long long)b * d + r] + t;
+}
+
+// Router for decode: one block per token, one warp per expert (round robin), then a serial soft-max / top-k over at
+// most 64 experts.  Same rules as the training router: bias steers the selection only, ties go to the lowest index,
+// weights are the selected probabilities renormalised.
+template <typename XT>
+__global__ void __launch_bounds__(256) decode_route_kernel(const XT* __restrict__ x, const float* __restrict__ rw,
+                                                          const float* __restrict__ bias, int d, int ne, int top_k,
+                                                          int* __restrict__ idx, float* __restrict__ wout) {
+  __shared__ float lg[64];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const XT* xr = x + (long long)b * d;
+  for (int e = warp; e < ne; e += 8) {
+    const float* wr = rw + (size_t)e * d;
+    float s = 0.f;
+    for (int i = lane * 2; i < d; i += 64) {
+      const float2 xv = Cvt<XT>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
+      const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+      s += xv.x * wv.x + xv.y * wv.y;
+    }
+    s = warp_sum(s);
+    if (lane == 0) lg[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mx = -INFINITY;
+    for (int e = 0; e < ne; ++e) mx = fmaxf(mx, lg[e]);
+    float sum = 0.f;
+    for (int e = 0; e < ne; ++e) { lg[e] = __expf(lg[e] - mx); sum += lg[e]; }
+    const float inv = 1.f / sum;
+    unsigned long long taken = 0ull;
+    float psel[8], psum = 0.f;
+    int esel[8];
+    for (int k = 0; k < top_k; ++k) {
+      float bv = -INFINITY;
+      int bi = 0;
+      for (int e = 0; e < ne; ++e) {
+        if (taken >> e & 1ull) continue;
+        const float sc = lg[e] * inv + (bias ? bias[e] : 0.f);
+        if (sc > bv) { bv = sc; bi = e; }
+      }
+      taken |= 1ull << bi;
+      esel[k] = bi;
+      psel[k] = lg[bi] * inv;
+      psum += psel[k];
+    }
+    const float invs = psum > 1e-8f ? 1.f / psum : 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      idx[b * top_k + k] = esel[k];
+      wout[b * top_k + k] = psel[k] * invs;
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- KV cache
@@ -315,18 +394,24 @@ extern "C" int gb_gemv(const void* W, int fmt, int N, int K, const void* x16, in
                        const float* addend, int ld_add, int is_bf16, cudaStream_t st) {
   const long long rb = gb_wfmt_row_bytes(fmt, K);
   if (!W || !x16 || !out || N <= 0 || B <= 0 || B > 32 || rb < 0 || (ldx % 8)) return -1;
-  const dim3 grid((N + GV_WARPS - 1) / GV_WARPS);
+  const bool split = N <= 8192;   // few rows: spread each over four warps (latency bound); many rows fill the GPU anyway
   const uint8_t* w = static_cast<const uint8_t*>(W);
-#define CALL(F)                                                                                                          \
-  if (is_bf16) {                                                                                                         \
-    if (B == 1) gemv_kernel<F, 1, __nv_bfloat16><<<grid, GV_THREADS, 0, st>>>(w, rb, N, K, (const __nv_bfloat16*)x16, ldx, B, out, ldo, out_f32, addend, ld_add); \
-    else gemv_kernel<F, 4, __nv_bfloat16><<<grid, GV_THREADS, 0, st>>>(w, rb, N, K, (const __nv_bfloat16*)x16, ldx, B, out, ldo, out_f32, addend, ld_add);        \
-  } else {                                                                                                               \
-    if (B == 1) gemv_kernel<F, 1, __half><<<grid, GV_THREADS, 0, st>>>(w, rb, N, K, (const __half*)x16, ldx, B, out, ldo, out_f32, addend, ld_add);             \
-    else gemv_kernel<F, 4, __half><<<grid, GV_THREADS, 0, st>>>(w, rb, N, K, (const __half*)x16, ldx, B, out, ldo, out_f32, addend, ld_add);                    \
+#define GEMV_GO(F, NB, KS, XT)                                                                                     \
+  gemv_kernel<F, NB, KS, XT><<<dim3((N + GV_WARPS / KS - 1) / (GV_WARPS / KS)), GV_THREADS, 0, st>>>(                 \
+      w, rb, N, K, (const XT*)x16, ldx, B, out, ldo, out_f32, addend, ld_add)
+#define CALL(F)                                                                        \
+  if (is_bf16) {                                                                       \
+    if (B == 1 && split) GEMV_GO(F, 1, 4, __nv_bfloat16);                              \
+    else if (B == 1) GEMV_GO(F, 1, 1, __nv_bfloat16);                                  \
+    else GEMV_GO(F, 4, 1, __nv_bfloat16);                                              \
+  } else {                                                                             \
+    if (B == 1 && split) GEMV_GO(F, 1, 4, __half);                                     \
+    else if (B == 1) GEMV_GO(F, 1, 1, __half);                                         \
+    else GEMV_GO(F, 4, 1, __half);                                                     \
   }
   GB_FMT_SWITCH(fmt, CALL)
 #undef CALL
+#undef GEMV_GO
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -335,11 +420,14 @@ extern "C" int gb_gemv_expert_swiglu(const void* Wg, const void* Wu, int fmt, in
   const long long rb = gb_wfmt_row_bytes(fmt, d);
   if (!Wg || !Wu || !x16 || !idx || !act16 || rb < 0 || B <= 0 || top_k <= 0) return -1;
   const int slots = top_k + (shared ? 1 : 0);
-  const dim3 grid((E + GV_WARPS - 1) / GV_WARPS, B * slots);
   const uint8_t *g = static_cast<const uint8_t*>(Wg), *u = static_cast<const uint8_t*>(Wu);
-#define CALL(F)                                                                                                                           \
-  if (is_bf16) expert_swiglu_kernel<F, __nv_bfloat16><<<grid, GV_THREADS, 0, st>>>(g, u, rb, ne, E, d, (const __nv_bfloat16*)x16, idx, top_k, slots, (__nv_bfloat16*)act16); \
-  else expert_swiglu_kernel<F, __half><<<grid, GV_THREADS, 0, st>>>(g, u, rb, ne, E, d, (const __half*)x16, idx, top_k, slots, (__half*)act16);
+  const bool split = B * slots <= 64;
+#define SW_GO(F, KS, XT)                                                                                              \
+  expert_swiglu_kernel<F, KS, XT><<<dim3((E + GV_WARPS / KS - 1) / (GV_WARPS / KS), B * slots), GV_THREADS, 0, st>>>( \
+      g, u, rb, ne, E, d, (const XT*)x16, idx, top_k, slots, (XT*)act16)
+#define CALL(F)                                                                                   \
+  if (is_bf16) { if (split) SW_GO(F, 4, __nv_bfloat16); else SW_GO(F, 1, __nv_bfloat16); }        \
+  else { if (split) SW_GO(F, 4, __half); else SW_GO(F, 1, __half); }
   GB_FMT_SWITCH(fmt, CALL)
 #undef CALL
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -351,13 +439,24 @@ extern "C" int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E
   const long long rb = gb_wfmt_row_bytes(fmt, E);
   if (!Wd || !act16 || !idx || !w || !resid || !out || rb < 0 || B <= 0 || top_k <= 0) return -1;
   const int slots = top_k + (shared ? 1 : 0);
-  const dim3 grid((d + GV_WARPS - 1) / GV_WARPS, B);
   const uint8_t* wd = static_cast<const uint8_t*>(Wd);
-#define CALL(F)                                                                                                                    \
-  if (is_bf16) expert_down_kernel<F, __nv_bfloat16><<<grid, GV_THREADS, 0, st>>>(wd, rb, ne, d, E, (const __nv_bfloat16*)act16, idx, w, top_k, slots, resid, out); \
-  else expert_down_kernel<F, __half><<<grid, GV_THREADS, 0, st>>>(wd, rb, ne, d, E, (const __half*)act16, idx, w, top_k, slots, resid, out);
+  const bool split = B <= 16;
+#define DN_GO(F, KS, XT)                                                                                    \
+  expert_down_kernel<F, KS, XT><<<dim3((d + GV_WARPS / KS - 1) / (GV_WARPS / KS), B), GV_THREADS, 0, st>>>( \
+      wd, rb, ne, d, E, (const XT*)act16, idx, w, top_k, slots, resid, out)
+#define CALL(F)                                                                                   \
+  if (is_bf16) { if (split) DN_GO(F, 4, __nv_bfloat16); else DN_GO(F, 1, __nv_bfloat16); }        \
+  else { if (split) DN_GO(F, 4, __half); else DN_GO(F, 1, __half); }
   GB_FMT_SWITCH(fmt, CALL)
 #undef CALL
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int gb_decode_route(const void* x16, const float* router_w, const float* bias, int B, int d, int ne, int top_k,
+                               int* idx, float* w, int is_bf16, cudaStream_t st) {
+  if (!x16 || !router_w || !idx || !w || B <= 0 || ne <= 0 || ne > 64 || top_k <= 0 || top_k > 8 || top_k > ne || d % 2) return -1;
+  if (is_bf16) decode_route_kernel<__nv_bfloat16><<<B, 256, 0, st>>>((const __nv_bfloat16*)x16, router_w, bias, d, ne, top_k, idx, w);
+  else decode_route_kernel<__half><<<B, 256, 0, st>>>((const __half*)x16, router_w, bias, d, ne, top_k, idx, w);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

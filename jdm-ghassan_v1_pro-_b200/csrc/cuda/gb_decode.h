@@ -36,6 +36,11 @@ int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E, const voi
                         const float* w, int top_k, int shared, const float* resid, float* out, int is_bf16,
                         cudaStream_t st);
 
+// Router for B tokens (no jitter, no statistics): idx[b, k] experts, w[b, k] renormalised probabilities; `bias`
+// (optional) is added to the probabilities for the selection only; ties go to the lowest index.
+int gb_decode_route(const void* x16, const float* router_w, const float* bias, int B, int d, int ne, int top_k,
+                    int* idx, float* w, int is_bf16, cudaStream_t st);
+
 // Per-sequence decode state (device, one per batch row).
 typedef struct gb_seq_state {
   int abs_pos;      // tokens seen so far = RoPE position of the next token

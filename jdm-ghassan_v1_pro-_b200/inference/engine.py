@@ -133,10 +133,14 @@ class InferenceEngine:
         slots = (cfg.moe_top_k + int(cfg.moe_shared)) if cfg.use_moe else 1
         self.slots = slots
         self.act = torch.zeros(B, slots, E, **c16)
+        self.r_idx = torch.zeros(B, max(1, cfg.moe_top_k), **i32)      # router output of the current layer
+        self.r_w = torch.zeros(B, max(1, cfg.moe_top_k), **f32)
         self.dense_idx = torch.zeros(B, 1, **i32)          # dense FFN = one "expert" with weight 1
         self.dense_w = torch.ones(B, 1, **f32)
         self.logits = torch.zeros(B, V, **f32)
-        self.splits = 8
+        # split-KV: enough (sequence, kv head, split) blocks to cover the GPU; a warp walks its slots one by one,
+        # so at batch 1 the cache is cut fine (a few slots per warp) and the partial results merged afterwards
+        self.splits = int(min(64, max(8, 512 // (B * cfg.num_kv_heads))))
         self.att_scratch = torch.zeros(B * cfg.num_heads * self.splits * (cfg.head_dim + 2), **f32)
         self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, max_len) + 1, self.dev)
         self.hist_cap = max_len + 8
@@ -169,9 +173,9 @@ class InferenceEngine:
         D.gemv(L.wo, self.att, self.x_mid, addend=x_in)
         K.rmsnorm_fwd(self.x_mid, L.ffn_norm, self.xb, self.rr, cfg.rms_eps)
         if cfg.use_moe:
-            K.moe_route_only(L.ws, self.xb, L.router, L.bias)
-            D.expert_swiglu(L.wg, L.wu, cfg.num_experts, self.E, d, self.xb, L.ws.idx, cfg.moe_top_k, cfg.moe_shared, self.act)
-            D.expert_down(L.wd, cfg.num_experts, d, self.E, self.act, L.ws.idx, L.ws.w, cfg.moe_top_k, cfg.moe_shared,
+            D.decode_route(self.xb, L.router, L.bias, cfg.moe_top_k, self.r_idx, self.r_w)
+            D.expert_swiglu(L.wg, L.wu, cfg.num_experts, self.E, d, self.xb, self.r_idx, cfg.moe_top_k, cfg.moe_shared, self.act)
+            D.expert_down(L.wd, cfg.num_experts, d, self.E, self.act, self.r_idx, self.r_w, cfg.moe_top_k, cfg.moe_shared,
                           self.x_mid, x_out)
         else:
             D.expert_swiglu(L.wg, L.wu, 0, self.E, d, self.xb, self.dense_idx, 1, False, self.act)

@@ -121,6 +121,15 @@ def expert_down(wd: QWeight, ne, d, E, act, idx, w, top_k, shared, resid, out):
     _lib.check_rc(rc, "gb_gemv_expert_down")
 
 
+def decode_route(x16, router_w, bias, top_k, idx, w):
+    """Router for the ``B`` rows of ``x16``: ``idx[b, k]`` experts and ``w[b, k]`` renormalised probabilities."""
+    B, d = x16.shape
+    rc = _lib.lib().gb_decode_route(c_vp(x16.data_ptr()), c_vp(router_w.data_ptr()), _lib.ptr(bias), c_int(B), c_int(d),
+                                    c_int(router_w.shape[0]), c_int(top_k), c_vp(idx.data_ptr()), c_vp(w.data_ptr()),
+                                    c_int(_bf(x16)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_decode_route")
+
+
 def kv_append(k16, v16, cacheK, cacheV, slot_pos, state, cap, pinned):
     B, kv_dim = k16.shape[0], k16.shape[1]
     rc = _lib.lib().gb_kv_append(c_vp(k16.data_ptr()), c_ll(k16.stride(0)), c_vp(v16.data_ptr()), c_ll(v16.stride(0)),

@@ -69,6 +69,26 @@ def test_expert_kernels(fmt):
     assert torch.allclose(out, ref, rtol=1e-2, atol=2e-2), float((out - ref).abs().max())
 
 
+def test_decode_router_matches_reference_rules():
+    from ghassan_b200.models.config import ModelConfig
+    from ghassan_b200.models.reference import route
+    D = _D()
+    cfg = ModelConfig(vocab_size=320, hidden_size=96, num_layers=1, num_heads=4, num_kv_heads=2, intermediate_size=128,
+                      max_seq_len=32, use_moe=True, num_experts=8, moe_top_k=3, moe_expert_dim=64, moe_allow_dense=True)
+    x = _rand(6, 96, seed=1).half()
+    x[0] = 0                                                   # all logits equal: ties go to the lowest index
+    rw = _rand(8, 96, seed=2, scale=0.5)
+    bias = torch.tensor([0.0, 0.0, 0.4, 0.0, 0.0, 0.0, -0.4, 0.0])
+    idx = torch.zeros(6, 3, dtype=torch.int32, device="cuda")
+    w = torch.zeros(6, 3, device="cuda")
+    for b in (None, bias):
+        D.decode_route(x.cuda(), rw.cuda(), None if b is None else b.cuda(), 3, idx, w)
+        _, ridx, rwt = route(x.float(), rw, b, cfg, None)
+        assert idx.cpu().tolist() == ridx.tolist()
+        assert torch.allclose(w.cpu(), rwt, atol=1e-5)
+    assert idx[0].tolist()[0] == 2                             # the bias steers selection ...
+
+
 @pytest.mark.parametrize("hd,H,KV", [(64, 12, 4), (128, 4, 4), (32, 4, 2)])
 def test_kv_ring_and_decode_attention(hd, H, KV):
     D = _D()
