@@ -1,0 +1,135 @@
+"""File formats against files written by the reference's own tools (``tests/golden/formats``):
+
+* ``tiny_ref.ckpt``   checkpoint (v12, AdamW moments) left by its trainer after 3 steps of a tiny MoE model;
+* ``tiny400.gtok``    the tokenizer its ``train_tokenizer --vocab 400`` learned from ``golden/text/corpus_small.txt``;
+* ``tiny_*.gguf``     its ``ghassan-ai export`` of that checkpoint with profiles fp16, q8_k and q4_0.
+"""
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "formats")
+
+
+def H():
+    from ghassan_b200 import _gb200_host as h
+    return h
+
+
+@pytest.fixture(scope="module")
+def ckpt():
+    return H().read_checkpoint(os.path.join(GOLD, "tiny_ref.ckpt"), False, True)
+
+
+def test_reference_checkpoint_reads_and_rewrites_identically(ckpt, tmp_path):
+    h = H()
+    assert ckpt["version"] == 12 and ckpt["state"]["step"] == 3 and ckpt["payload_finite"]
+    assert ckpt["has_optimizer"] and ckpt["optimizer"]["kind"] == "adamw" and ckpt["optimizer"]["t"] == 3
+    assert ckpt["trailing_bytes"] == 0 and len(ckpt["moe_bias"]) == 1
+    from ghassan_b200.training import checkpoint as C
+    cfg = C.config_from_dict(ckpt["config"])
+    assert [n for n, _ in ckpt["params"]] == [s.name for s in cfg.param_specs()]
+    out = str(tmp_path / "again.ckpt")
+    h.write_checkpoint(out, ckpt["config"], ckpt["state"], ckpt["moe_bias"], ckpt["params"], ckpt["optimizer"])
+    assert open(out, "rb").read() == open(os.path.join(GOLD, "tiny_ref.ckpt"), "rb").read()
+    head = h.read_checkpoint(os.path.join(GOLD, "tiny_ref.ckpt"), True, False)       # header only
+    assert head["state"]["step"] == 3
+
+
+def test_checkpoint_damage_is_detected(ckpt, tmp_path):
+    h = H()
+    blob = open(os.path.join(GOLD, "tiny_ref.ckpt"), "rb").read()
+    p = str(tmp_path / "bad.ckpt")
+    open(p, "wb").write(b"XXXX" + blob[4:])
+    with pytest.raises(Exception):
+        h.read_checkpoint(p, False, True)
+    open(p, "wb").write(blob[:len(blob) // 3])
+    with pytest.raises(Exception):
+        h.read_checkpoint(p, False, True)
+    open(p, "wb").write(blob + b"\0\0\0")
+    assert h.read_checkpoint(p, False, True)["trailing_bytes"] == 3
+
+
+@pytest.mark.parametrize("profile", ["fp16", "q8_k", "q4_0"])
+def test_gguf_export_is_byte_identical(ckpt, tmp_path, profile):
+    from ghassan_b200.formats import gguf as G
+    from ghassan_b200.training import checkpoint as C
+    cfg = C.config_from_dict(ckpt["config"])
+    st = ckpt["state"]
+    out = str(tmp_path / "m.gguf")
+    info = G.export_gguf(out, cfg, dict(ckpt["params"]), os.path.join(GOLD, "tiny400.gtok"), profile,
+                         moe_bias=ckpt["moe_bias"], extra_meta={"steps": str(st["step"]), "val_loss": "%.6f" % st["best_val"]})
+    assert info["tensors"] == len(cfg.param_specs()) + 1          # + one balancing-bias row
+    assert open(out, "rb").read() == open(os.path.join(GOLD, "tiny_%s.gguf" % profile), "rb").read()
+
+
+@pytest.mark.parametrize("profile,tol", [("fp16", 1e-3), ("q8_k", 0.02), ("q4_0", 0.2)])
+def test_gguf_import(ckpt, profile, tol):
+    from ghassan_b200.formats import gguf as G
+    from ghassan_b200.training import checkpoint as C
+    m = G.load_gguf(os.path.join(GOLD, "tiny_%s.gguf" % profile))
+    cfg = C.config_from_dict(ckpt["config"])
+    assert m.cfg.same_architecture_as(cfg)[0]
+    assert m.tokenizer is not None and m.tokenizer.to_bytes() == open(os.path.join(GOLD, "tiny400.gtok"), "rb").read()
+    src = dict(ckpt["params"])
+    for name, arr in m.named.items():
+        ref = np.asarray(src[name]).reshape(arr.shape)
+        scale = np.abs(ref).max() + 1e-9
+        assert np.abs(arr - ref).max() <= tol * scale, name
+        if "norm" in name:
+            assert np.array_equal(arr, ref)                         # norm gains are stored in fp32 in every profile
+    assert len(m.moe_bias) == 1 and np.allclose(m.moe_bias[0], np.asarray(ckpt["moe_bias"][0]))
+    assert "Q4_0" in G.describe(os.path.join(GOLD, "tiny_q4_0.gguf"))
+
+
+def test_tokenizer_rebuilds_from_token_and_merge_arrays():
+    from ghassan_b200.formats import gguf as G
+    f = H().GgufFile(os.path.join(GOLD, "tiny_fp16.gguf"))
+    md = dict(f.metadata)
+    full = G.tokenizer_from_metadata(md)
+    md.pop("ghassan.tokenizer.gtok")
+    rebuilt = G.tokenizer_from_metadata(md)                         # llama.cpp-style arrays only
+    for text in ("salam 3lik, kidayr?", "The quick brown fox", "السلام عليكم ١٢٣"):
+        assert rebuilt.encode(text).tolist() == full.encode(text).tolist()
+
+
+def test_gguf_reader_refuses_garbage(tmp_path):
+    h = H()
+    blob = open(os.path.join(GOLD, "tiny_fp16.gguf"), "rb").read()
+    for bad in (b"NOPE" + blob[4:], blob[:200], blob[:len(blob) - 64]):
+        p = str(tmp_path / "bad.gguf")
+        open(p, "wb").write(bad)
+        with pytest.raises(Exception):
+            h.GgufFile(p)
+
+
+@pytest.mark.parametrize("name,block,nbytes", [("q8_0", 64, 68), ("q4_0", 32, 18), ("q4_1", 32, 20)])
+def test_internal_quantisers(name, block, nbytes):
+    h = H()
+    rs = np.random.RandomState(0)
+    x = (rs.randn(block * 7 + 5) * 0.3).astype(np.float32)            # ragged tail
+    q = np.asarray(h.quantize(x, name))
+    assert q.size == 8 * nbytes
+    y = np.asarray(h.dequantize(q, name, x.size))
+    err = h.quant_error(x, y)
+    assert err["cosine"] > (0.999 if name == "q8_0" else 0.98)
+    x[3] = np.inf                                                      # a block with a non-finite value is zeroed
+    z = np.asarray(h.dequantize(np.asarray(h.quantize(x, name)), name, x.size))
+    assert np.all(z[:block] == 0) and np.allclose(z[block:], y[block:])
+
+
+def test_ggml_block_layouts():
+    h = H()
+    x = np.linspace(-1, 1, 64).astype(np.float32)
+    q8 = np.asarray(h.ggml_quantize(x, 8))
+    assert q8.size == 2 * 34
+    scale = np.frombuffer(q8[:2].tobytes(), dtype=np.float16)[0]
+    assert float(scale) == pytest.approx(np.abs(x[:32]).max() / 127, rel=1e-3)
+    assert np.frombuffer(q8[2:34].tobytes(), dtype=np.int8)[0] == -127
+    q4 = np.asarray(h.ggml_quantize(x, 2))
+    assert q4.size == 2 * 18
+    byte0 = int(q4[2])
+    lo, hi = byte0 & 15, byte0 >> 4                                    # adjacent values share a byte, first one low
+    d = float(np.frombuffer(q4[:2].tobytes(), dtype=np.float16)[0])
+    assert (lo - 8) * d == pytest.approx(x[0], abs=d) and (hi - 8) * d == pytest.approx(x[1], abs=d)
