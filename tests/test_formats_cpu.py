@@ -133,3 +133,46 @@ def test_ggml_block_layouts():
     lo, hi = byte0 & 15, byte0 >> 4                                    # adjacent values share a byte, first one low
     d = float(np.frombuffer(q4[:2].tobytes(), dtype=np.float16)[0])
     assert (lo - 8) * d == pytest.approx(x[0], abs=d) and (hi - 8) * d == pytest.approx(x[1], abs=d)
+
+
+@pytest.mark.parametrize("profile,tol", [("fp32", 0.0), ("fp16", 1e-3), ("int8", 0.02), ("int4", 0.2)])
+def test_gai_round_trip(ckpt, tmp_path, profile, tol):
+    """The reference's tools read files written here (checked by hand with its ``info`` and ``quantize`` commands);
+    this test pins the layout and the round trip."""
+    import struct
+    from ghassan_b200.formats import gai as GA
+    from ghassan_b200.training import checkpoint as C
+    cfg = C.config_from_dict(ckpt["config"])
+    named = dict(ckpt["params"])
+    p = str(tmp_path / "m.gai")
+    GA.export_gai(p, cfg, named, os.path.join(GOLD, "tiny400.gtok"), profile, {"steps": "3"})
+    blob = open(p, "rb").read()
+    magic, version, hb = struct.unpack_from("<III", blob, 0)
+    assert magic == 0x31494147 and version == 1
+    header = blob[12:12 + hb].decode()
+    keys = [l.split("=")[0] for l in header.splitlines()]
+    assert keys == sorted(keys) and "rms_eps=0.000010000" in header and "quant_profile=" + profile in header
+    m = GA.load_gai(p)
+    assert m.cfg.same_architecture_as(cfg)[0] and m.tokenizer.vocab_size == 400
+    for t in m.raw.tensors:
+        assert t["offset"] % 64 == 0
+    for name, arr in m.named.items():
+        ref = np.asarray(named[name]).reshape(arr.shape)
+        assert np.abs(arr - ref).max() <= tol * (np.abs(ref).max() + 1e-9), name
+    view = m.raw.tensor_view("final_norm")                       # zero-copy bytes out of the mapping
+    assert np.array_equal(np.frombuffer(view, dtype=np.float32), np.asarray(named["final_norm"]).ravel())
+
+
+def test_graw_round_trip(ckpt, tmp_path):
+    from ghassan_b200.formats import gai as GA
+    from ghassan_b200.training import checkpoint as C
+    cfg = C.config_from_dict(ckpt["config"])
+    named = dict(ckpt["params"])
+    p = str(tmp_path / "m.graw")
+    GA.save_raw(p, cfg, named)
+    back = GA.load_raw(p, cfg)
+    for s in cfg.param_specs():
+        assert np.array_equal(back[s.name], np.asarray(named[s.name]).reshape(s.shape))
+    open(p, "r+b").write(b"XXXX")
+    with pytest.raises(Exception):
+        GA.load_raw(p, cfg)
