@@ -300,6 +300,13 @@ def run_reference(args):
     c.kv.pop("data.val_prefix", None)
     c.kv.pop("training.data_dir", None)
     c.set("training.ddp", "true" if world > 1 else "false")   # the binary refuses ddp with one visible rank
+    for k, v in (args.ref_set or []):      # explicit, non-default reference settings (reported in the JSON line)
+        if k == "training.gemm_fp16" and str(v).lower() in ("false", "0", "no", "off"):
+            # measured once on a B200: with fp32 GEMMs the reference's own code raised "an illegal memory access was
+            # encountered" (cuda/cuda_utils.cu:99); a path that faults the GPU is not run again
+            return unavailable("the reference's gemm_fp16=false path faults on B200 (illegal memory access in its own "
+                               "code); its default fp16 path aborts with cuBLAS status 15 in cuda/attention.cu:362")
+        c.set(k, v)
     yml = os.path.join(work, "bench_recipe.yaml")
     dump_yaml(c, yml)
     shutil.rmtree(os.path.join(work, "ckpt"), ignore_errors=True)
@@ -338,6 +345,7 @@ def run_reference(args):
            "scaling": "weak", "vs_baseline": None, "dtype": "fp16 GEMM inputs, fp32 accumulate/activations",
            "data": "synthetic", "impl": "reference", "config": recipe_label(args.config, mcfg0, tcfg0, world),
            "clocks": clocks, "timing": "the reference's own per-step tok/s (host wall clock), steps after warm-up",
+           "reference_overrides": {k: v for k, v in (args.ref_set or [])},
            "wall_seconds_total": wall}
     print(json.dumps(out), flush=True)
     return 0
@@ -353,6 +361,8 @@ def main():
     ap.add_argument("--workdir", default=os.environ.get("GB200_BENCH_DIR", "/tmp/gb200_bench"))
     ap.add_argument("--set", nargs=2, action="append", metavar=("KEY", "VALUE"), help="override a recipe key")
     ap.add_argument("--ref-timeout", type=int, default=1500)
+    ap.add_argument("--ref-set", nargs=2, action="append", metavar=("KEY", "VALUE"),
+                    help="recipe override for the reference arm only (e.g. training.gemm_fp16 false); default: none")
     ap.add_argument("--settle-max", type=int, default=12,
                     help="untimed steps allowed before warm-up for the dynamic loss scale to stop overflowing")
     ap.add_argument("--verbose", action="store_true")
