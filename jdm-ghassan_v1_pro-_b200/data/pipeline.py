@@ -1,0 +1,354 @@
+"""Dataset construction: readers (text lines, JSON / JSON lines, Parquet), cleaning, quality and style gates,
+language tagging, exact + near-duplicate removal with an evaluation blocklist, tokenisation and shard writing
+(tools/data_pipeline_cli.cpp, dataset/*.cpp in the reference).
+
+Documents become token windows ``<s> ... </s>`` of at most ``seq_len`` tokens (long documents are split, not cut
+off); chat records go through the chat template and carry a loss mask (assistant spans).  Windows are dealt to
+``train_[<domain>_]NNNN.gbin`` / ``val_[<domain>_]NNNN.gbin`` shards of ``shard_tokens`` tokens; every
+``1/val_ratio``-th window goes to validation.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+from collections import Counter
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, Iterator, List, Optional, Tuple
+
+import numpy as np
+
+from .. import _gb200_host as H
+from . import tokenizer as T
+
+
+# ---------------------------------------------------------------------------------------------- readers
+@dataclass
+class Record:
+    text: str = ""
+    messages: Optional[List[T.Message]] = None       # chat record when not None
+    source: str = ""
+
+
+def _messages_from(obj) -> Optional[List[T.Message]]:
+    """Accepts {"messages": [{role, content}...]}, {"conversations": [{from, value}...]}, question/answer,
+    instruction/(input)/output, prompt/response."""
+    if not isinstance(obj, dict):
+        return None
+    roles = {"human": "user", "user": "user", "gpt": "assistant", "assistant": "assistant", "system": "system", "bot": "assistant"}
+    for key in ("messages", "conversations", "conversation", "dialog"):
+        seq = obj.get(key)
+        if isinstance(seq, list) and seq:
+            out = []
+            for m in seq:
+                if not isinstance(m, dict):
+                    return None
+                role = roles.get(str(m.get("role", m.get("from", ""))).lower())
+                content = m.get("content", m.get("value"))
+                if role is None or not isinstance(content, str):
+                    return None
+                out.append(T.Message(role, content))
+            return out
+    for q, a in (("question", "answer"), ("prompt", "response"), ("instruction", "output"), ("input", "output")):
+        if isinstance(obj.get(q), str) and isinstance(obj.get(a), str):
+            user = obj[q]
+            if q == "instruction" and isinstance(obj.get("input"), str) and obj["input"].strip():
+                user = user + "\n" + obj["input"]
+            msgs = [T.Message("user", user), T.Message("assistant", obj[a])]
+            if isinstance(obj.get("system"), str) and obj["system"].strip():
+                msgs.insert(0, T.Message("system", obj["system"]))
+            return msgs
+    return None
+
+
+def _record_from(obj, source) -> Optional[Record]:
+    msgs = _messages_from(obj)
+    if msgs:
+        return Record(messages=msgs, source=source)
+    if isinstance(obj, dict):
+        for key in ("text", "content", "body", "document"):
+            if isinstance(obj.get(key), str):
+                return Record(text=obj[key], source=source)
+    if isinstance(obj, str):
+        return Record(text=obj, source=source)
+    return None
+
+
+def read_text_lines(path: str) -> Iterator[Record]:
+    with open(path, "rb") as f:
+        for raw in f:
+            line = raw.rstrip(b"\r\n")
+            if line:
+                yield Record(text=line.decode("utf-8", errors="surrogateescape"), source=path)
+
+
+def read_json(path: str) -> Iterator[Record]:
+    """A JSON array / object, or one JSON value per line."""
+    data = open(path, "rb").read().decode("utf-8", errors="replace")
+    try:
+        top = json.loads(data)
+        rows = top if isinstance(top, list) else (top.get("data") or top.get("rows") or [top])
+    except json.JSONDecodeError:
+        rows = []
+        for line in data.splitlines():
+            line = line.strip()
+            if line:
+                try:
+                    rows.append(json.loads(line))
+                except json.JSONDecodeError:
+                    continue
+    for r in rows:
+        rec = _record_from(r, path)
+        if rec is not None:
+            yield rec
+
+
+def read_parquet(path: str, limit: int = 0) -> Iterator[Record]:
+    """Rows of a Parquet file: chat columns (messages / conversations, as lists of structs or JSON strings),
+    question/answer style pairs, or a text column."""
+    import pyarrow.parquet as pq
+    pf = pq.ParquetFile(path)
+    n = 0
+    for batch in pf.iter_batches(batch_size=2048):
+        for row in batch.to_pylist():
+            for k, v in list(row.items()):
+                if isinstance(v, str) and k in ("messages", "conversations") and v[:1] in "[{":
+                    try:
+                        row[k] = json.loads(v)
+                    except json.JSONDecodeError:
+                        pass
+            rec = _record_from(row, path)
+            if rec is not None:
+                yield rec
+                n += 1
+                if limit and n >= limit:
+                    return
+
+
+def iter_inputs(path: str, match: str = "") -> Iterator[Record]:
+    files = [path] if os.path.isfile(path) else sorted(
+        p for p in glob.glob(os.path.join(path, "**", "*"), recursive=True) if os.path.isfile(p))
+    for p in files:
+        if match and match not in os.path.basename(p):
+            continue
+        ext = os.path.splitext(p)[1].lower()
+        if ext == ".parquet":
+            yield from read_parquet(p)
+        elif ext in (".json", ".jsonl"):
+            yield from read_json(p)
+        elif ext in (".txt", ".text", ".md", ""):
+            yield from read_text_lines(p)
+
+
+# ---------------------------------------------------------------------------------------------- builder
+@dataclass
+class BuildConfig:
+    seq_len: int = 4096
+    shard_tokens: int = 50_000_000
+    val_ratio: float = 0.005
+    domain: str = ""
+    style_mode: str = "darija"          # darija | en | off : which quality / robotic-style gates apply
+    keep_robotic: bool = False
+    min_keep: int = 1
+    dedup: bool = True
+    blocklist: List[str] = field(default_factory=list)     # texts (e.g. evaluation prompts) that must not enter training
+
+
+@dataclass
+class BuildReport:
+    seen: int = 0
+    kept_docs: int = 0
+    kept_windows: int = 0
+    train_windows: int = 0
+    train_tokens: int = 0
+    val_windows: int = 0
+    val_tokens: int = 0
+    train_shards: int = 0
+    val_shards: int = 0
+    dropped: Counter = field(default_factory=Counter)
+    languages: Counter = field(default_factory=Counter)
+    dedup: Dict[str, int] = field(default_factory=dict)
+
+    def summary(self) -> str:
+        lines = ["seen documents      : %d" % self.seen, "kept documents      : %d" % self.kept_docs,
+                 "kept windows        : %d" % self.kept_windows,
+                 "train windows/tokens: %d / %d  (%d shards)" % (self.train_windows, self.train_tokens, self.train_shards),
+                 "val   windows/tokens: %d / %d  (%d shards)" % (self.val_windows, self.val_tokens, self.val_shards)]
+        for k, v in sorted(self.dropped.items()):
+            lines.append("dropped %-12s: %d" % (k, v))
+        total = sum(self.languages.values()) or 1
+        for k, v in self.languages.most_common():
+            lines.append("  %-12s %8d  %6.2f%%" % (k, v, 100.0 * v / total))
+        if self.dedup:
+            lines.append("dedup: " + " ".join("%s=%d" % kv for kv in self.dedup.items()))
+        return "\n".join(lines)
+
+
+class _ShardSink:
+    def __init__(self, out_dir, prefix, vocab, with_mask, shard_tokens):
+        self.dir, self.prefix, self.vocab, self.with_mask, self.cap = out_dir, prefix, vocab, with_mask, shard_tokens
+        self.w, self.n_shards, self.in_shard, self.windows, self.tokens = None, 0, 0, 0, 0
+
+    def add(self, ids: np.ndarray, mask: Optional[np.ndarray]):
+        if self.w is None or self.in_shard + len(ids) > self.cap:
+            self.close()
+            path = os.path.join(self.dir, "%s%04d.gbin" % (self.prefix, self.n_shards))
+            self.w = H.ShardWriter(path, self.vocab, self.with_mask)
+            self.n_shards += 1
+            self.in_shard = 0
+        self.w.add_document(ids, mask if self.with_mask else None)
+        self.in_shard += len(ids)
+        self.windows += 1
+        self.tokens += len(ids)
+
+    def close(self):
+        if self.w is not None:
+            self.w.close()
+            self.w = None
+
+
+def _windows(ids: np.ndarray, mask: Optional[np.ndarray], seq_len: int):
+    """Split one encoded document into windows of at most seq_len tokens (a tail shorter than 8 tokens joins the
+    previous window's fate: it is dropped rather than written as a stub)."""
+    n = len(ids)
+    if n <= seq_len:
+        yield ids, mask
+        return
+    for lo in range(0, n, seq_len):
+        hi = min(n, lo + seq_len)
+        if hi - lo < 8:
+            break
+        yield ids[lo:hi], (None if mask is None else mask[lo:hi])
+
+
+def build_shards(records: Iterable[Record], tok: T.Tokenizer, out_dir: str, cfg: BuildConfig) -> BuildReport:
+    os.makedirs(out_dir, exist_ok=True)
+    rep = BuildReport()
+    cleaner = H.Cleaner()
+    qcfg = H.english_quality_config() if cfg.style_mode == "en" else H.QualityConfig()
+    dd = H.Deduplicator() if cfg.dedup else None
+    if dd is not None:
+        for t in cfg.blocklist:
+            dd.add_blocklist_text(t)
+    st = H.CleanStats()
+    staged: List[Tuple[np.ndarray, Optional[np.ndarray]]] = []
+    any_mask = False
+
+    def clean(text: str) -> Optional[str]:
+        return cleaner.clean_line(text.encode("utf-8", errors="surrogateescape"), st)
+
+    for rec in records:
+        rep.seen += 1
+        if rec.messages is not None:
+            msgs = []
+            for m in rec.messages:
+                c = clean(m.content)
+                if c is None:
+                    msgs = None
+                    break
+                msgs.append(T.Message(m.role, c))
+            if not msgs or not any(m.role == "assistant" for m in msgs):
+                rep.dropped["clean"] += 1
+                continue
+            reply = " ".join(m.content for m in msgs if m.role == "assistant")
+            user = " ".join(m.content for m in msgs if m.role == "user")
+            if cfg.style_mode != "off" and not cfg.keep_robotic and H.check_assistant_style(reply, user)["robotic"]:
+                rep.dropped["robotic"] += 1
+                continue
+            key_text = user + "\n" + reply
+            body = key_text
+        else:
+            body = clean(rec.text)
+            if body is None:
+                rep.dropped["clean"] += 1
+                continue
+            key_text = body
+            msgs = None
+        if cfg.style_mode != "off":
+            ok, why = H.quality_check(body, qcfg)
+            if not ok:
+                rep.dropped["quality:" + why] += 1
+                continue
+        if dd is not None and not dd.add(key_text):
+            rep.dropped["duplicate"] += 1
+            continue
+        rep.languages[H.classify_language(body)["tag"]] += 1
+        if msgs is not None:
+            ids, mask = T.encode_chat(tok, msgs)
+            ids = np.concatenate([ids, np.array([T.EOS], dtype=np.int32)])
+            mask = np.concatenate([mask, np.array([0], dtype=np.uint8)])
+            any_mask = True
+        else:
+            ids, mask = tok.encode(body, add_bos=True, add_eos=True), None
+        rep.kept_docs += 1
+        for w_ids, w_mask in _windows(ids, mask, cfg.seq_len):
+            staged.append((np.ascontiguousarray(w_ids), w_mask))
+    if dd is not None:
+        rep.dedup = {"seen": dd.seen, "exact_dup": dd.exact_dups, "near_dup": dd.near_dups, "blocked": dd.blocked}
+    rep.dropped["pii"] += int(st.dropped_pii)
+    rep.dropped["encoding"] += int(st.dropped_encoding)
+    rep.kept_windows = len(staged)
+    if rep.kept_windows < cfg.min_keep:
+        raise ValueError("only %d windows kept (min_keep %d)" % (rep.kept_windows, cfg.min_keep))
+    dom = (cfg.domain + "_") if cfg.domain else ""
+    train = _ShardSink(out_dir, "train_" + dom, tok.vocab_size, any_mask, cfg.shard_tokens)
+    val = _ShardSink(out_dir, "val_" + dom, tok.vocab_size, any_mask, cfg.shard_tokens)
+    every = int(round(1.0 / cfg.val_ratio)) if cfg.val_ratio > 0 else 0
+    for i, (ids, mask) in enumerate(staged):
+        if any_mask and mask is None:
+            mask = np.ones(len(ids), dtype=np.uint8)        # plain text inside an SFT build: supervise everything
+        (val if (every and i % every == every - 1) else train).add(ids, mask)
+    train.close()
+    val.close()
+    rep.train_windows, rep.train_tokens, rep.train_shards = train.windows, train.tokens, train.n_shards
+    rep.val_windows, rep.val_tokens, rep.val_shards = val.windows, val.tokens, val.n_shards
+    return rep
+
+
+def inspect_shards(directory: str, tok: Optional[T.Tokenizer] = None, show: int = 2) -> str:
+    lines = []
+    for p in sorted(glob.glob(os.path.join(directory, "*.gbin"))):
+        s = H.ShardFile()
+        ok, why = s.open(p)
+        if not ok:
+            lines.append("%s: INVALID (%s)" % (os.path.basename(p), why))
+            continue
+        lines.append("%s: %d docs, %d tokens%s" % (os.path.basename(p), s.n_docs, s.n_tokens, ", loss masks" if s.has_mask else ""))
+        start = 0
+        for d in range(min(show, s.n_docs)):
+            end = s.doc_end_after(start)
+            ids = np.asarray(s.tokens(start, end - start))
+            txt = tok.decode(ids, skip_special=True) if tok is not None else " ".join(map(str, ids[:24]))
+            lines.append("    [%d] %s" % (d, txt[:160].replace("\n", " ")))
+            start = end
+    return "\n".join(lines)
+
+
+def corpus_stats(records: Iterable[Record], tok: Optional[T.Tokenizer] = None) -> dict:
+    """Counts for the ``corpus_stats`` command: documents, characters, words, language mix, script mix, fertility."""
+    n = chars = words = toks = 0
+    langs, scripts = Counter(), Counter()
+    lengths = []
+    for rec in records:
+        text = rec.text if rec.messages is None else "\n".join(m.content for m in rec.messages)
+        if not text:
+            continue
+        n += 1
+        chars += len(text)
+        w = len(text.split())
+        words += w
+        lengths.append(w)
+        langs[H.classify_language(text)["tag"]] += 1
+        st = H.script_stats(text)
+        scripts["arabic"] += st["arabic"]
+        scripts["latin"] += st["latin"]
+        scripts["digits"] += st["digits"]
+        scripts["emoji"] += st["emoji"]
+        if tok is not None:
+            toks += len(tok.encode(text))
+    lengths.sort()
+    pct = lambda q: lengths[min(len(lengths) - 1, int(q * len(lengths)))] if lengths else 0
+    return {"documents": n, "characters": chars, "words": words, "tokens": toks,
+            "tokens_per_word": (toks / words) if (tok is not None and words) else None,
+            "words_p50": pct(0.5), "words_p90": pct(0.9), "words_p99": pct(0.99),
+            "languages": dict(langs.most_common()), "scripts": dict(scripts)}

@@ -68,20 +68,42 @@ class InferenceEngine:
 
     def __init__(self, cfg: ModelConfig, named: Dict[str, np.ndarray], fmt: str = "f16", batch: int = 1,
                  max_len: int = 2048, prefill_chunk: int = 1024, moe_bias: Optional[Sequence] = None, device=None,
-                 compute_dtype=torch.float16, keep_f16_embeddings: bool = True):
+                 compute_dtype=torch.float16, keep_f16_embeddings: bool = True, raw=None, raw_types=None):
+        """``named``: fp32 tensors by parameter name.  ``fmt``: decode weight format, or "auto" with ``raw`` (an object
+        with ``tensor_raw(name)``, e.g. a GGUF file) and ``raw_types`` (name -> ggml type) to take the stored bytes."""
         cfg.validate()
         if cfg.head_dim not in (32, 64, 128):
             raise ValueError("decode attention supports head_dim 32, 64 and 128")
         self.cfg, self.B, self.cap = cfg, batch, max_len
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.dt = compute_dtype
-        self.fmt = D.FMT_NAMES[fmt] if isinstance(fmt, str) else int(fmt)
+        raw_types = raw_types or {}
+        if fmt == "auto":
+            kinds = [raw_types.get("layers.0.wq")]
+            self.fmt = {1: D.W_F16, 8: D.W_GGML_Q8_0, 2: D.W_Q4_0}.get(kinds[0], D.W_F16)
+        else:
+            self.fmt = D.FMT_NAMES[fmt] if isinstance(fmt, str) else int(fmt)
         d, qd, kvd, V = cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.vocab_size
         f32 = dict(dtype=torch.float32, device=self.dev)
         c16 = dict(dtype=self.dt, device=self.dev)
         i32 = dict(dtype=torch.int32, device=self.dev)
         t = lambda n: torch.as_tensor(np.asarray(named[n], dtype=np.float32))
-        q = lambda w: D.QWeight.from_f32(w, self.fmt, self.dev)
+        ggml_to_fmt = {1: D.W_F16, 8: D.W_GGML_Q8_0, 2: D.W_Q4_0}
+
+        def q(*names):
+            """Rows of the named matrices stacked in one decode-format weight.  With a GGUF source whose stored type
+            is one the kernels read directly, the file's bytes are used as they are (no second quantisation)."""
+            if raw is not None:
+                kinds = {raw_types.get(n) for n in names}
+                if len(kinds) == 1 and next(iter(kinds)) in ggml_to_fmt and (fmt == "auto" or ggml_to_fmt[next(iter(kinds))] == self.fmt):
+                    f = ggml_to_fmt[next(iter(kinds))]
+                    blob = b"".join(bytes(raw.tensor_raw(n)) for n in names)
+                    rows = sum(int(np.asarray(named[n]).shape[0]) for n in names)
+                    K_ = int(np.asarray(named[names[0]]).shape[1])
+                    data = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(self.dev)
+                    return D.QWeight(data, f, rows, K_)
+            w = torch.cat([t(n) for n in names], 0) if len(names) > 1 else t(names[0])
+            return D.QWeight.from_f32(w, self.fmt, self.dev)
         # ---- weights
         self.emb = t("tok_embeddings").to(self.dev)                       # fp32 rows for the embedding lookup
         head = t("tok_embeddings") if cfg.tie_embeddings else t("lm_head")
@@ -98,21 +120,19 @@ class InferenceEngine:
             L.attn_norm, L.ffn_norm = t(r + "attn_norm").to(self.dev), t(r + "ffn_norm").to(self.dev)
             L.qn = t(r + "qk_qnorm").to(self.dev) if cfg.use_qk_norm else None
             L.kn = t(r + "qk_knorm").to(self.dev) if cfg.use_qk_norm else None
-            L.wqkv = q(torch.cat([t(r + "wq"), t(r + "wk"), t(r + "wv")], 0))
-            L.wo = q(t(r + "wo"))
+            L.wqkv = q(r + "wq", r + "wk", r + "wv")
+            L.wo = q(r + "wo")
             if cfg.use_moe:
                 L.router = t(r + "moe_router").to(self.dev)
-                g, u, dn = t(r + "moe_gate"), t(r + "moe_up"), t(r + "moe_down")
-                if cfg.moe_shared:
-                    g = torch.cat([g, t(r + "moe_sh_gate")], 0)
-                    u = torch.cat([u, t(r + "moe_sh_up")], 0)
-                    dn = torch.cat([dn, t(r + "moe_sh_down")], 0)
-                L.wg, L.wu, L.wd = q(g), q(u), q(dn)
+                sh = cfg.moe_shared
+                L.wg = q(*([r + "moe_gate"] + ([r + "moe_sh_gate"] if sh else [])))
+                L.wu = q(*([r + "moe_up"] + ([r + "moe_sh_up"] if sh else [])))
+                L.wd = q(*([r + "moe_down"] + ([r + "moe_sh_down"] if sh else [])))
                 L.bias = (torch.as_tensor(np.asarray(moe_bias[i], dtype=np.float32)).to(self.dev)
                           if (moe_bias is not None and len(moe_bias) > i) else None)
                 L.ws = K.MoeWorkspace(batch, d, cfg.num_experts, cfg.moe_top_k, cfg.moe_shared, self.dt, self.dev)
             else:
-                L.wg, L.wu, L.wd = q(t(r + "w_gate")), q(t(r + "w_up")), q(t(r + "w_down"))
+                L.wg, L.wu, L.wd = q(r + "w_gate"), q(r + "w_up"), q(r + "w_down")
             L.cK = torch.zeros(batch, max_len, kvd, **c16)
             L.cV = torch.zeros(batch, max_len, kvd, **c16)
             self.layers.append(L)

@@ -1,0 +1,227 @@
+"""Text pipeline on the CPU: cleaning primitives, language id, dedup, shard building (against a shard the reference's
+``data_pipeline build`` wrote from the same probe file with the same tokenizer), synthesis, retrieval."""
+import io
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "text")
+
+
+def H():
+    import ghassan_b200
+    from ghassan_b200 import _gb200_host as h
+    return h
+
+
+@pytest.fixture(scope="module")
+def tok():
+    from ghassan_b200.data.tokenizer import Tokenizer
+    return Tokenizer.load(os.path.join(GOLD, "ref_small.gtok"))
+
+
+def _docs(path):
+    h = H()
+    s = h.ShardFile()
+    ok, why = s.open(path)
+    assert ok, why
+    t = np.asarray(s.tokens(0, s.n_tokens))
+    out, st = [], 0
+    for _ in range(s.n_docs):
+        e = s.doc_end_after(st)
+        out.append(tuple(t[st:e].tolist()))
+        st = e
+    return out, s
+
+
+# ------------------------------------------------------------------------------------------ primitives
+def test_pii_scan_and_redaction():
+    h = H()
+    text = "ping me at someone@example.com or +212 661-234567, server 192.168.10.44, https://bob:hunter2@host.tld/x"
+    rep = h.scan_pii(text)
+    assert rep["emails"] == 1 and rep["phones"] >= 1 and rep["ips"] == 1 and rep["urls_with_creds"] == 1
+    red, rep2 = h.redact_pii(text)
+    assert "someone@example.com" not in red and "hunter2" not in red and "192.168.10.44" not in red
+    assert rep2["total"] == rep["total"]
+    assert h.scan_pii("كيداير اليوم؟ كلشي بخير الحمد لله")["total"] == 0
+
+
+def test_html_and_mojibake():
+    h = H()
+    assert h.strip_html_tags("<p>salam <b>sahbi</b></p>&amp; more").replace("  ", " ").strip().startswith("salam sahbi")
+    broken = "café".encode("utf-8").decode("latin-1")
+    assert h.fix_mojibake(broken) == "café"
+    assert h.fix_mojibake("plain ascii") == "plain ascii"
+
+
+def test_cleaner_drops_and_counts():
+    h = H()
+    c, st = h.Cleaner(), h.CleanStats()
+    assert c.clean_line("   ".encode(), st) is None
+    assert c.clean_line("mail me: x.y@z.org please, this line is long enough".encode(), st) is None
+    out = c.clean_line("<i>واش نتا بخير؟</i> kolchi mzyan had nhar".encode(), st)
+    assert out is not None and "<i>" not in out
+    assert st.lines_in == 3 and st.lines_out == 1 and st.dropped_pii == 1 and st.dropped_empty == 1
+    cfg = h.CleanConfig()
+    cfg.redact_instead_drop = True
+    out = h.Cleaner(cfg).clean_line("mail me: x.y@z.org please, this line is long enough".encode(), h.CleanStats())
+    assert out is not None and "x.y@z.org" not in out
+
+
+def test_quality_and_toxicity_gates():
+    h = H()
+    ok, _ = h.quality_check("واش كاين شي حد هنا باش يعاوني ف هاد المشكل ديال الخدمة؟")
+    assert ok
+    ok, why = h.quality_check("$$$ ### @@@ !!! %%% ^^^ &&& *** ((( )))")
+    assert not ok and why
+    ok, why = h.quality_check("spam spam spam spam spam spam spam spam spam spam spam spam")
+    assert not ok and why == "repetitive"
+    ok, why = h.quality_check("As an AI language model, I cannot help with that request at all.", h.english_quality_config())
+    assert not ok
+    assert not h.check_toxicity("nhar zwin had lyoum, nmchiw l b7ar")["toxic"]
+
+
+def test_language_tags():
+    h = H()
+    want = {"واش نتا بخير؟ بغيت نمشي للسوق دابا حيت خاصني الخضرة": "ar-MA-arab",
+            "wach nta bikhir? bghit nmchi l souk daba 7it khassni lkhodra": "ar-MA-latn",
+            "إن هذا الأمر يتطلب دراسة معمقة حيث أن النتائج التي تم الحصول عليها ليست كافية": "ar-MSA",
+            "Je voudrais savoir comment aller à la gare, s'il vous plaît, parce que je suis en retard": "fr",
+            "I would like to know how the weather is going to be tomorrow because we are travelling": "en"}
+    for text, tag in want.items():
+        r = h.classify_language(text)
+        assert r["tag"] == tag, (text, r)
+        assert 0.0 <= r["confidence"] <= 1.0
+    assert h.msa_ratio(list(want)[2]) > h.msa_ratio(list(want)[0])
+
+
+def test_dedup_exact_near_and_blocklist():
+    h = H()
+    d = h.Deduplicator()
+    base = "had nhar mchit l souk m3a sahbi w chrina bzaf dyal l7wayj zwinin b taman mzyan bzaf"
+    assert d.add(base)
+    assert not d.add(base)                                   # exact
+    assert not d.add(base + " .")                            # near (one extra shingle)
+    assert d.add("chi 7aja khra kamla ma3ndha 7ta 3ala9a m3a dakchi li dazt 9bel f had lista")
+    d.add_blocklist_text("what is the capital of morocco and why is it rabat")
+    assert not d.add("what is the capital of morocco and why is it rabat")
+    assert d.exact_dups == 1 and d.near_dups == 1 and d.blocked == 1 and d.seen == 5
+    assert d.is_duplicate(base) and not d.is_duplicate("completely unseen sentence with other words inside of it")
+
+
+def test_assistant_style_flags():
+    h = H()
+    f = h.check_assistant_style("As an AI language model, I cannot have opinions.", "chno ban lik?")
+    assert f["robotic"] and f["has_boilerplate"] and f["matched_phrases"]
+    assert h.has_hard_ai_boilerplate("As an AI language model, I do not have feelings")
+    g = h.check_assistant_style("واخا، نمشيو دابا للسوق ونشريو الخضرة", "فين نمشيو؟")
+    assert not g["robotic"]
+    many = "\n".join("- point %d" % i for i in range(12))
+    assert h.check_assistant_style(many, "list")["too_many_bullets"]
+
+
+# ------------------------------------------------------------------------------------------ shard builder
+def test_build_matches_reference_documents(tok, tmp_path):
+    from ghassan_b200.data import pipeline as P
+    ref, _ = _docs(os.path.join(GOLD, "probe_train_0000.gbin"))
+    rep = P.build_shards(P.iter_inputs(os.path.join(GOLD, "probe.txt")), tok, str(tmp_path), P.BuildConfig(val_ratio=0.0))
+    mine, s = _docs(str(tmp_path / "train_0000.gbin"))
+    assert rep.kept_docs == 60 and rep.val_shards == 0 and not s.has_mask
+    assert set(ref) <= set(mine) and len(ref) == 59          # the reference held one document back for validation
+    assert all(d[0] == 1 and d[-1] == 2 for d in mine)
+
+
+def test_build_chat_masks_val_split_and_windows(tok, tmp_path):
+    from ghassan_b200.data import pipeline as P, synth as S
+    rows = list(S.darija_conversations(40, seed=3)) + list(S.english_conversations(20, seed=4))
+    src = tmp_path / "c.jsonl"
+    S.write_jsonl(str(src), rows)
+    recs = list(P.iter_inputs(str(src)))
+    assert len(recs) == 60 and recs[0].messages and recs[0].messages[0].role == "user"
+    rep = P.build_shards(recs, tok, str(tmp_path / "o"), P.BuildConfig(seq_len=48, val_ratio=0.1, style_mode="off"))
+    assert rep.dropped["duplicate"] > 0 and rep.kept_docs + rep.dropped["duplicate"] == 60
+    assert rep.val_windows == rep.kept_windows // 10 and rep.train_windows + rep.val_windows == rep.kept_windows
+    docs, s = _docs(str(tmp_path / "o" / "train_0000.gbin"))
+    assert s.has_mask and max(len(d) for d in docs) <= 48
+    m = np.asarray([s.mask(i) for i in range(s.n_tokens)])
+    assert 0 < int(m.sum()) < s.n_tokens                      # only assistant tokens are supervised
+    text = P.inspect_shards(str(tmp_path / "o"), tok, 1)
+    assert "train_0000.gbin" in text and "loss masks" in text
+    with pytest.raises(ValueError):
+        P.build_shards([], tok, str(tmp_path / "e"), P.BuildConfig())
+
+
+def test_blocklist_keeps_eval_prompts_out(tok, tmp_path):
+    from ghassan_b200.data import pipeline as P
+    secret = "what is the tallest mountain in north africa and where exactly is it located"
+    recs = [P.Record(text=secret), P.Record(text="lyoum ljow zwin bzaf w bghit nmchi nt3awd m3a s7abi f lb7ar")]
+    rep = P.build_shards(recs, tok, str(tmp_path), P.BuildConfig(val_ratio=0.0, style_mode="off", blocklist=[secret]))
+    assert rep.kept_docs == 1 and rep.dedup["blocked"] == 1
+
+
+def test_readers_accept_common_layouts(tmp_path):
+    from ghassan_b200.data import pipeline as P
+    (tmp_path / "a.json").write_text(json.dumps([
+        {"conversations": [{"from": "human", "value": "salam"}, {"from": "gpt", "value": "wa 3alaykom salam"}]},
+        {"instruction": "translate", "input": "hello", "output": "salam"},
+        {"prompt": "chno smitek?", "response": "smiti ghassan"},
+        {"text": "plain document"}]), encoding="utf-8")
+    recs = list(P.iter_inputs(str(tmp_path / "a.json")))
+    assert len(recs) == 4
+    assert [m.role for m in recs[0].messages] == ["user", "assistant"]
+    assert recs[1].messages[-1].content == "salam" and "hello" in recs[1].messages[0].content
+    assert recs[2].messages[0].content == "chno smitek?"
+    assert recs[3].messages is None and recs[3].text == "plain document"
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.parquet as pq
+    pq.write_table(pa.table({"text": ["wa7ed", "jouj", "tlata"]}), str(tmp_path / "t.parquet"))
+    assert [r.text for r in P.read_parquet(str(tmp_path / "t.parquet"), limit=2)] == ["wa7ed", "jouj"]
+    assert len(list(P.iter_inputs(str(tmp_path)))) == 7
+
+
+def test_corpus_stats(tok):
+    from ghassan_b200.data import pipeline as P
+    st = P.corpus_stats(P.iter_inputs(os.path.join(GOLD, "probe.txt")), tok)
+    assert st["documents"] == 60 and st["tokens"] > 0 and st["tokens_per_word"] > 0.5
+    assert sum(st["languages"].values()) == 60 and st["scripts"]["latin"] > st["scripts"]["arabic"] > 0
+
+
+# ------------------------------------------------------------------------------------------ synthesis
+def test_synthesis_is_deterministic_and_tagged():
+    from ghassan_b200.data import synth as S
+    a, b = list(S.darija_conversations(30, seed=9)), list(S.darija_conversations(30, seed=9))
+    assert a == b and a != list(S.darija_conversations(30, seed=10))
+    h = H()
+    for row in a:
+        text = " ".join(m["content"] for m in row["messages"])
+        arabic = h.script_stats(text)["arabic"]
+        assert (arabic == 0) == (row["lang"] == "ar-MA-latn")
+        assert len(row["messages"]) % 2 == 0 and "{" not in text
+    en = list(S.english_conversations(25, seed=2))
+    assert {r["act"] for r in en} >= {"coding", "question"} and all("{" not in r["messages"][1]["content"].replace("```", "") or r["act"] == "coding" for r in en)
+    assert S.to_arabizi("شنو خبارك؟") == "chno khbark?"
+
+
+# ------------------------------------------------------------------------------------------ retrieval
+def test_retrieval_ranks_and_rejects(tmp_path):
+    from ghassan_b200.data import retrieval as R
+    rows = [{"question": "شنو هي عاصمة المغرب؟", "answer": "العاصمة هي الرباط."},
+            {"question": "كيفاش نطيب الطاجين؟", "answer": "خاصك اللحم والخضرة."},
+            {"question": "what is python", "answer": "a programming language"},
+            {"question": "how do i install python on linux", "answer": "use your package manager"}]
+    (tmp_path / "qa.json").write_text(json.dumps(rows, ensure_ascii=False), encoding="utf-8")
+    ix = R.build_index(str(tmp_path / "qa.json"))
+    assert len(ix) == 4
+    assert ix.query("عاصمة المغرب")[0][0] == 0
+    assert ix.query("what is python?")[0][0] == 2
+    assert ix.query("pythn instal linux")[0][0] == 3         # typos still land on the right entry
+    assert ix.query("zzzz qqqq") == []
+    hits = ix.query("python", top_k=5)
+    assert [h[1] for h in hits] == sorted((h[1] for h in hits), reverse=True) and len(hits) == 2
+    assert ix.query("python", top_k=5, min_score=1e9) == []
+    assert R.normalize("أَهْلاً  بِكَ!") == R.normalize("أهلا بك") == "أهلا بك"      # harakat and punctuation go
+    assert R.normalize("Sba7 L-Khir") == "sbah l khir"                            # arabizi digits fold to letters
+    assert len(R.build_index(str(tmp_path))) == 4            # a directory of .json files
+    assert len(R.build_index(str(tmp_path / "missing.json"))) == 0
