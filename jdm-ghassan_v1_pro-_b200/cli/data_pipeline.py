@@ -1,0 +1,338 @@
+"""Dataset construction (the reference's ``data_pipeline``, tools/data_pipeline_cli.cpp:30-1720).
+
+    data_pipeline parquet        --lake <dir|file.parquet> --tokenizer tok.gtok --out shards [--match s] [--domain d] [--mode auto|qa|text|chat]
+    data_pipeline parquet-corpus --lake <dir> --out corpus.txt [--limit n]
+    data_pipeline build          --tokenizer tok.gtok --out shards [--text path] [--chat file.jsonl] [--synth n]
+    data_pipeline synth          --out synth.jsonl --n 50000 [--english]
+    data_pipeline inspect        --shards shards [--tokenizer tok.gtok]
+    data_pipeline tok-info       --tokenizer tok.gtok
+    data_pipeline csvs           --dir <csv-root> --out corpus_csv.txt [--with-english]
+    data_pipeline csv2json       --dir <csv-root> --out json_shards [--docs-per-file n] [--id-start n]
+    data_pipeline jsons          --dir <json-root> --out corpus_json.txt
+    data_pipeline json           --input <file.json|jsonl> [--limit n]          # show how records are read
+    data_pipeline retrieve       --index <json file|dir> --query "salam labas" [--top 3] [--min-score f]
+
+(run as ``python -m ghassan_b200.cli.data_pipeline <command> ...``).  Shard-building commands share: --val-ratio
+--shard-tokens --seq-len --domain --min-keep --keep-robotic --style-mode darija|en|off --no-dedup --expect-vocab
+--blocklist <file>.
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import glob
+import itertools
+import json
+import os
+import sys
+from typing import Iterator, List, Optional
+
+from .. import _gb200_host as H
+from ..data import pipeline as P
+from ..data import retrieval as R
+from ..data import synth as S
+from ..data import tokenizer as T
+from ..utils.log import human_count, log_error, log_info, log_warn
+
+COMMANDS = ["parquet", "parquet-corpus", "build", "synth", "inspect", "tok-info", "csvs", "csv2json", "jsons", "json",
+            "json-inspect", "dump-text", "retrieve"]
+
+
+def _parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="data_pipeline")
+    ap.add_argument("command", choices=COMMANDS)
+    ap.add_argument("rest", nargs="*")
+    for n in ("lake", "dir", "match", "tokenizer", "out", "domain", "style-mode", "mode", "text", "chat", "shards", "index", "query",
+              "input", "blocklist"):
+        ap.add_argument("--" + n, default="")
+    for n, d in (("val-ratio", 0.005), ("min-score", 0.0)):
+        ap.add_argument("--" + n, type=float, default=d)
+    for n, d in (("shard-tokens", 50_000_000), ("seq-len", 4096), ("min-keep", 1), ("expect-vocab", 0), ("limit", 0), ("n", 50000),
+                 ("synth", 0), ("seed", 1), ("top", 3), ("docs-per-file", 20000), ("id-start", 1_000_000), ("min-chars", 2)):
+        ap.add_argument("--" + n, type=int, default=d)
+    for n in ("keep-robotic", "keep-case", "no-dedup", "probe", "with-english", "english"):
+        ap.add_argument("--" + n, action="store_true")
+    return ap
+
+
+def _load_tok(a) -> T.Tokenizer:
+    if not a.tokenizer:
+        raise SystemExit("--tokenizer <path> is required")
+    tok = T.Tokenizer.load(a.tokenizer)
+    if a.expect_vocab and tok.vocab_size != a.expect_vocab:
+        raise SystemExit("tokenizer vocab %d != --expect-vocab %d" % (tok.vocab_size, a.expect_vocab))
+    lower = bool(H.NormalizerConfig.unpack(tok.normalizer_bits).lowercase_latin)
+    if a.keep_case and lower:
+        raise SystemExit("--keep-case given but the tokenizer lowercases Latin; retrain it with --keep-case")
+    if not a.keep_case and not lower:
+        log_warn("[tok ] the tokenizer keeps Latin case; pass --keep-case to acknowledge (shards follow the tokenizer)")
+    return tok
+
+
+def _build_cfg(a) -> P.BuildConfig:
+    style = a.style_mode or "darija"
+    if style not in ("darija", "en", "off"):
+        raise SystemExit("--style-mode must be darija|en|off")
+    block: List[str] = []
+    if a.blocklist:
+        block = [ln.strip() for ln in open(a.blocklist, encoding="utf-8") if ln.strip()]
+    if a.seq_len < 8 or a.shard_tokens < a.seq_len or not (0.0 <= a.val_ratio < 1.0):
+        raise SystemExit("--seq-len must be >= 8, --shard-tokens >= --seq-len and --val-ratio in [0, 1)")
+    return P.BuildConfig(seq_len=a.seq_len, shard_tokens=a.shard_tokens, val_ratio=a.val_ratio, domain=a.domain, style_mode=style,
+                         keep_robotic=a.keep_robotic, min_keep=a.min_keep, dedup=not a.no_dedup, blocklist=block)
+
+
+def _mode_filter(recs: Iterator[P.Record], mode: str) -> Iterator[P.Record]:
+    """--mode of the parquet command: qa/chat keep conversations only, text flattens everything to lines."""
+    any_chat = False
+    for r in recs:
+        if mode in ("qa", "chat"):
+            if r.messages is None:
+                continue
+            any_chat = True
+            yield r
+        elif mode == "text":
+            yield r if r.messages is None else P.Record(text="\n".join(m.content for m in r.messages), source=r.source)
+        else:
+            yield r
+    if mode in ("qa", "chat") and not any_chat:
+        raise SystemExit("--mode %s: no question/answer or message rows in the input" % mode)
+
+
+def _csv_files(root: str) -> List[str]:
+    if os.path.isfile(root):
+        return [root]
+    return sorted(glob.glob(os.path.join(root, "**", "*.csv"), recursive=True))
+
+
+_DARIJA_COLS = ("darija", "darija_ar", "darija_arabic", "darija_latin", "arabizi", "n1", "n2", "n3", "n4", "root", "masculine", "feminine", "plural")
+_ENGLISH_COLS = ("eng", "english", "en", "gloss")
+_Q_COLS = ("question", "prompt", "instruction", "input", "eng", "english")
+_A_COLS = ("answer", "response", "output", "darija", "darija_ar")
+
+
+def _csv_rows(path: str):
+    with open(path, encoding="utf-8", errors="replace", newline="") as f:
+        rd = csv.DictReader(f)
+        for row in rd:
+            yield {(k or "").strip().lower(): (v or "").strip() for k, v in row.items()}
+
+
+def cmd_csvs(a) -> int:
+    files = _csv_files(a.dir or ".")
+    if not files:
+        log_error("no .csv files found under: " + (a.dir or "."))
+        return 1
+    log_info("[csvs] found %d file(s) under %s" % (len(files), a.dir or "."))
+    out_path = a.out or "corpus_csv.txt"
+    seen, kept = set(), 0
+    with open(out_path, "w", encoding="utf-8") as out:
+        for p in files:
+            for row in _csv_rows(p):
+                cols = [c for c in row if c in _DARIJA_COLS or (a.with_english and c in _ENGLISH_COLS)]
+                if not cols:                                   # unknown table: every text column that is not English
+                    cols = [c for c in row if a.with_english or c not in _ENGLISH_COLS]
+                for c in cols:
+                    v = row[c]
+                    if len(v) >= a.min_chars and v not in seen and not v.replace(".", "").isdigit():
+                        seen.add(v)
+                        out.write(v.replace("\n", " ") + "\n")
+                        kept += 1
+    log_info("[csvs] wrote %s lines to %s" % (human_count(kept), out_path))
+    if kept < a.min_keep:
+        log_error("only %d lines kept (--min-keep %d)" % (kept, a.min_keep))
+        return 1
+    return 0
+
+
+def cmd_csv2json(a) -> int:
+    files = _csv_files(a.dir or ".")
+    if not files:
+        log_error("no .csv files found under: " + (a.dir or "."))
+        return 1
+    if a.docs_per_file <= 0 or a.id_start < 0:
+        raise SystemExit("--docs-per-file must be > 0 and --id-start >= 0")
+    outdir = a.out or "json_shards"
+    os.makedirs(outdir, exist_ok=True)
+    seen, batch, pairs, idx, next_id = set(), [], 0, 0, a.id_start
+    skipped = {"same": 0, "empty": 0, "dup": 0}
+
+    def flush():
+        nonlocal batch, idx
+        if batch:
+            p = os.path.join(outdir, "train-%05d.json" % idx)
+            with open(p, "w", encoding="utf-8") as f:
+                json.dump(batch, f, ensure_ascii=False, indent=1)
+            log_info("[json] wrote " + p)
+            idx += 1
+            batch = []
+
+    for p in files:
+        for row in _csv_rows(p):
+            q = next((row[c] for c in _Q_COLS if row.get(c)), "")
+            ans = next((row[c] for c in _A_COLS if row.get(c) and row[c] != q), "")
+            if len(q) < a.min_chars or len(ans) < a.min_chars:
+                skipped["empty"] += 1
+                continue
+            if R.normalize(q) == R.normalize(ans):
+                skipped["same"] += 1
+                continue
+            key = R.normalize(q)
+            if key in seen:
+                skipped["dup"] += 1
+                continue
+            seen.add(key)
+            batch.append({"id": next_id, "question": q, "answer": ans})
+            next_id += 1
+            pairs += 1
+            if len(batch) >= a.docs_per_file:
+                flush()
+    flush()
+    log_info("[json] %s pairs in %d file(s); skipped: %s" % (human_count(pairs), idx, " ".join("%s=%d" % kv for kv in skipped.items())))
+    if pairs < a.min_keep:
+        log_error("only %d pairs kept (--min-keep %d)" % (pairs, a.min_keep))
+        return 1
+    return 0
+
+
+def cmd_jsons(a) -> int:
+    docs = R.load_qa_dir(a.dir) if os.path.isdir(a.dir or ".") else R.load_qa_json(a.dir)
+    out_path = a.out or "corpus_json.txt"
+    kept = 0
+    with open(out_path, "w", encoding="utf-8") as out:
+        for d in docs:
+            for v in (d.question, d.answer):
+                if len(v) >= a.min_chars:
+                    out.write(v.replace("\n", " ") + "\n")
+                    kept += 1
+    log_info("[jsons] %s pairs -> %s lines in %s" % (human_count(len(docs)), human_count(kept), out_path))
+    if kept < a.min_keep:
+        log_error("only %d lines kept (--min-keep %d)" % (kept, a.min_keep))
+        return 1
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = _parser().parse_args(argv)
+    cmd = a.command
+    if cmd in ("parquet", "parquet-corpus"):
+        try:
+            import pyarrow.parquet  # noqa: F401
+        except ImportError:
+            log_error("parquet support needs pyarrow, which is not importable here")
+            return 1
+        if a.probe:
+            return 0
+        lake = a.lake or a.dir or "dataset/parquet/by_domain"
+        recs = P.iter_inputs(lake, a.match)
+        if a.limit:
+            recs = itertools.islice(recs, a.limit)
+        if cmd == "parquet-corpus":
+            n = 0
+            with open(a.out or "corpus.txt", "w", encoding="utf-8") as out:
+                for r in recs:
+                    for t in ([r.text] if r.messages is None else [m.content for m in r.messages if m.role != "system"]):
+                        t = t.replace("\n", " ").strip()
+                        if t:
+                            out.write(t + "\n")
+                            n += 1
+            log_info("[parquet] wrote %s lines to %s" % (human_count(n), a.out or "corpus.txt"))
+            return 0 if n >= a.min_keep else 1
+        mode = a.mode or "auto"
+        if mode not in ("qa", "text", "chat", "auto"):
+            raise SystemExit("--mode must be qa|text|chat|auto")
+        tok = _load_tok(a)
+        try:
+            rep = P.build_shards(_mode_filter(recs, mode), tok, a.out or "artifacts/shards", _build_cfg(a))
+        except ValueError as e:
+            log_error(str(e))
+            return 1
+        log_info("\n" + rep.summary())
+        return 0
+    if cmd == "build":
+        tok = _load_tok(a)
+        streams = []
+        if a.text:
+            streams.append(P.iter_inputs(a.text))
+        if a.chat:
+            streams.append(P.iter_inputs(a.chat))
+        if a.synth:
+            gen = S.english_conversations if a.english else S.darija_conversations
+            streams.append(r for r in (P._record_from(row, "synth") for row in gen(a.synth, seed=a.seed)) if r is not None)
+        if not streams:
+            log_error("nothing to build: give --text, --chat and/or --synth")
+            return 1
+        try:
+            rep = P.build_shards(itertools.chain(*streams), tok, a.out or "artifacts/shards", _build_cfg(a))
+        except ValueError as e:
+            log_error(str(e))
+            return 1
+        log_info("\n" + rep.summary())
+        return 0
+    if cmd == "synth":
+        gen = S.english_conversations if a.english else S.darija_conversations
+        out = a.out or "data/synth.jsonl"
+        os.makedirs(os.path.dirname(os.path.abspath(out)), exist_ok=True)
+        n = S.write_jsonl(out, gen(a.n, seed=a.seed))
+        log_info("[synth] wrote %s conversations to %s" % (human_count(n), out))
+        return 0
+    if cmd == "inspect":
+        tok = T.Tokenizer.load(a.tokenizer) if a.tokenizer else None
+        print(P.inspect_shards(a.shards or "artifacts/shards", tok))
+        return 0
+    if cmd == "tok-info":
+        tok = _load_tok(a)
+        n = H.NormalizerConfig.unpack(tok.normalizer_bits)
+        print("vocab        : %d (%d special)" % (tok.vocab_size, T.N_SPECIAL))
+        print("fingerprint  : %s" % H.fingerprint_hex(H.fingerprint_file(a.tokenizer)))
+        print("normalizer   : " + " ".join(k for k in ("strip_diacritics", "strip_tatweel", "fold_letters", "lowercase_latin",
+                                                       "arabic_digits_ascii", "collapse_repeats", "collapse_whitespace") if getattr(n, k)))
+        longest = sorted(range(T.N_SPECIAL, tok.vocab_size), key=lambda i: -len(tok.token_bytes(i)))[:10]
+        print("longest      : " + " | ".join(tok.token_bytes(i).decode("utf-8", "replace") for i in longest))
+        return 0
+    if cmd == "csvs":
+        return cmd_csvs(a)
+    if cmd == "csv2json":
+        return cmd_csv2json(a)
+    if cmd == "jsons":
+        return cmd_jsons(a)
+    if cmd in ("json", "json-inspect", "dump-text"):
+        src = a.input or (a.rest[0] if a.rest else "")
+        if not src:
+            raise SystemExit("--input <file> is required")
+        n = 0
+        cap = (a.limit or None) if cmd == "dump-text" else (a.limit or 20)
+        for r in itertools.islice(P.iter_inputs(src), cap):
+            n += 1
+            if r.messages is None:
+                print(r.text if cmd == "dump-text" else "[text] " + r.text[:160])
+            elif cmd == "dump-text":
+                for m in r.messages:
+                    print(m.content.replace("\n", " "))
+            else:
+                print("[chat] " + " || ".join("%s: %s" % (m.role, m.content[:80]) for m in r.messages))
+        if cmd != "dump-text":
+            log_info("%d record(s) shown" % n)
+        return 0
+    if cmd == "retrieve":
+        query = a.query or (a.rest[0] if a.rest else "")
+        if not a.index or not query:
+            raise SystemExit("--index <train-*.json file|dir> and --query <text> are required")
+        ix = R.build_index(a.index)
+        if len(ix) == 0:
+            log_error("no QA pairs loaded from: " + a.index)
+            return 1
+        log_info("[retrieve] index: %s pairs" % human_count(len(ix)))
+        hits = ix.query(query, a.top if a.top > 0 else 3, a.min_score)
+        if not hits:
+            log_info("[retrieve] no hit above min-score (answer: spontaneous generation)")
+            return 0
+        for i, (doc, score) in enumerate(hits):
+            e = ix.doc(doc)
+            print("--- hit %d  id=%d  score=%.3f ---\nQ: %s\nA: %s" % (i + 1, e.id, score, e.question, e.answer))
+        return 0
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

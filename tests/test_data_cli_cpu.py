@@ -1,0 +1,129 @@
+"""Command-line front ends of the data side: data_pipeline, train_tokenizer, corpus_stats."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "text")
+TOK = os.path.join(GOLD, "ref_small.gtok")
+
+
+def test_train_tokenizer_cli_matches_reference_file(tmp_path, capsys):
+    """Same corpus, vocabulary size and frequency floor as the reference's trainer run that wrote ref_small.gtok."""
+    from ghassan_b200.cli import train_tokenizer as TT
+    out = str(tmp_path / "t.gtok")
+    assert TT.main(["--input", os.path.join(GOLD, "corpus_small.txt"), "--output", out, "--vocab", "800", "--min-freq", "2"]) == 0
+    assert open(out, "rb").read() == open(TOK, "rb").read()
+    text = (lambda o: o.out + o.err)(capsys.readouterr())
+    assert "fertility" in text and "tokens/word" in text and "fingerprint" in text
+    assert TT.main(["--input", str(tmp_path / "missing"), "--output", out]) == 1
+    assert TT.main(["--input", out, "--vocab", "0"]) == 2
+    out2 = str(tmp_path / "s.gtok")
+    assert TT.main(["--synth", "200", "--output", out2, "--vocab", "400", "--keep-case"]) == 0
+    from ghassan_b200 import _gb200_host as H
+    from ghassan_b200.data.tokenizer import Tokenizer
+    t = Tokenizer.load(out2)
+    assert 272 < t.vocab_size <= 400 and not H.NormalizerConfig.unpack(t.normalizer_bits).lowercase_latin
+    capsys.readouterr()
+
+
+def test_corpus_stats_cli(capsys):
+    from ghassan_b200.cli import corpus_stats as CS
+    assert CS.main(["--input", os.path.join(GOLD, "probe.txt"), "--tokenizer", TOK, "--dedup", "--pii", "--quality", "--sample", "1"]) == 0
+    text = (lambda o: o.out + o.err)(capsys.readouterr())
+    assert "documents : 60" in text and "tokens/word" in text and "ar-MA-latn" in text and "duplicates:" in text
+    assert "personal data:" in text and "quality filter would reject" in text and "---- sample: en ----" in text
+    assert CS.main(["--input", os.path.join(GOLD, "probe.txt"), "--limit", "7"]) == 0
+    assert "documents : 7" in (lambda o: o.out + o.err)(capsys.readouterr())
+    assert CS.main([]) == 2 and CS.main(["--input", "/nonexistent/dir"]) == 1
+    assert CS.main(["--input", os.path.join(GOLD, "probe.txt"), "--tokenizer", "/nonexistent.gtok"]) == 1
+    capsys.readouterr()
+
+
+def test_data_pipeline_build_inspect_tokinfo(tmp_path, capsys):
+    from ghassan_b200.cli import data_pipeline as DP
+    out = str(tmp_path / "shards")
+    rc = DP.main(["build", "--tokenizer", TOK, "--out", out, "--text", os.path.join(GOLD, "probe.txt"), "--synth", "30", "--seq-len", "64",
+                  "--val-ratio", "0.1", "--style-mode", "off", "--domain", "mix", "--expect-vocab", "800"])
+    text = (lambda o: o.out + o.err)(capsys.readouterr())
+    assert rc == 0, text
+    assert "kept documents" in text and sorted(os.listdir(out)) == ["train_mix_0000.gbin", "val_mix_0000.gbin"]
+    assert DP.main(["inspect", "--shards", out, "--tokenizer", TOK]) == 0
+    assert "train_mix_0000.gbin:" in capsys.readouterr().out
+    assert DP.main(["tok-info", "--tokenizer", TOK]) == 0
+    info = capsys.readouterr().out
+    assert "vocab        : 800" in info and "fingerprint" in info and "lowercase_latin" in info
+    with pytest.raises(SystemExit):
+        DP.main(["build", "--tokenizer", TOK, "--out", out, "--text", os.path.join(GOLD, "probe.txt"), "--expect-vocab", "801"])
+    with pytest.raises(SystemExit):
+        DP.main(["build", "--tokenizer", TOK, "--out", out, "--text", os.path.join(GOLD, "probe.txt"), "--keep-case"])
+    assert DP.main(["build", "--tokenizer", TOK, "--out", out]) == 1
+    capsys.readouterr()
+
+
+def test_data_pipeline_parquet_modes(tmp_path, capsys):
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.parquet as pq
+    from ghassan_b200 import _gb200_host as H
+    from ghassan_b200.cli import data_pipeline as DP
+    lake = tmp_path / "lake"
+    lake.mkdir()
+    qs = ["chno hiya 3asimat lmaghrib nta li 3aref", "kifach n9der nt3ellem lprogrammation b zerba", "fin kayn a7san tajin f mrrakch had l3am"]
+    ans = ["l3asima hiya rbat, mdina zwina bzaf 3la lb7ar", "bda b python w dir tamarin kol nhar chwiya b chwiya", "kayn bzaf dyal lblayes zwinin f jam3 lfna w 7daha"]
+    pq.write_table(pa.table({"question": qs, "answer": ans}), str(lake / "darija_qa_part0.parquet"))
+    pq.write_table(pa.table({"text": ["had nhar zwin bzaf w ljow mzyan l tamchya f lb7ar m3a s7abi", "lbare7 mchit l souk w chrit lkhodra w lfawakih b taman mzyan"]}),
+                   str(lake / "web_text_part0.parquet"))
+    assert DP.main(["parquet", "--probe"]) == 0
+    out = str(tmp_path / "o1")
+    assert DP.main(["parquet", "--lake", str(lake), "--tokenizer", TOK, "--out", out, "--val-ratio", "0", "--style-mode", "off"]) == 0
+    s = H.ShardFile()
+    assert s.open(os.path.join(out, "train_0000.gbin"))[0] and s.n_docs == 5 and s.has_mask
+    out = str(tmp_path / "o2")
+    assert DP.main(["parquet", "--lake", str(lake), "--match", "darija_qa", "--mode", "qa", "--tokenizer", TOK, "--out", out, "--val-ratio", "0",
+                    "--style-mode", "off", "--domain", "darija_qa"]) == 0
+    s = H.ShardFile()
+    assert s.open(os.path.join(out, "train_darija_qa_0000.gbin"))[0] and s.n_docs == 3
+    with pytest.raises(SystemExit):
+        DP.main(["parquet", "--lake", str(lake), "--match", "web_text", "--mode", "qa", "--tokenizer", TOK, "--out", str(tmp_path / "o3")])
+    corpus = str(tmp_path / "c.txt")
+    assert DP.main(["parquet-corpus", "--lake", str(lake), "--out", corpus]) == 0
+    assert len(open(corpus, encoding="utf-8").read().splitlines()) == 8
+    capsys.readouterr()
+
+
+def test_data_pipeline_csv_json_retrieve_synth(tmp_path, capsys):
+    from ghassan_b200.cli import data_pipeline as DP
+    root = tmp_path / "csv"
+    (root / "sub").mkdir(parents=True)
+    (root / "nouns.csv").write_text("n1,n2,eng\nktab,ktoba,book\ndar,dyour,house\nktab,ktoba,book\n", encoding="utf-8")
+    (root / "sub" / "qa.csv").write_text("question,answer\nwhat is a book?,ktab\nwhat is a house?,dar\nwhat is a book?,ktab\nsame,same\n,x\n", encoding="utf-8")
+    corpus = str(tmp_path / "corpus.txt")
+    assert DP.main(["csvs", "--dir", str(root), "--out", corpus]) == 0
+    lines = open(corpus, encoding="utf-8").read().splitlines()
+    assert {"ktab", "ktoba", "dar", "dyour"} <= set(lines) and "book" not in lines and len(lines) == len(set(lines))
+    assert DP.main(["csvs", "--dir", str(root), "--out", corpus, "--with-english"]) == 0
+    assert "book" in open(corpus, encoding="utf-8").read().splitlines()
+    js = str(tmp_path / "json")
+    assert DP.main(["csv2json", "--dir", str(root), "--out", js, "--docs-per-file", "1", "--id-start", "500"]) == 0
+    files = sorted(os.listdir(js))
+    rows = [r for f in files for r in json.load(open(os.path.join(js, f), encoding="utf-8"))]
+    assert {r["id"] for r in rows} == set(range(500, 500 + len(rows))) and all(r["question"] != r["answer"] for r in rows)
+    assert len([r for r in rows if r["question"] == "what is a book?"]) == 1 and len(files) == len(rows)
+    capsys.readouterr()
+    assert DP.main(["retrieve", "--index", js, "--query", "whats a house"]) == 0
+    hit = capsys.readouterr().out
+    assert "--- hit 1" in hit and "A: dar" in hit.split("--- hit 2")[0]
+    assert DP.main(["retrieve", "--index", js, "--query", "zzzzz"]) == 0
+    assert DP.main(["retrieve", "--index", str(tmp_path / "nothing"), "--query", "x"]) == 1
+    assert DP.main(["jsons", "--dir", js, "--out", corpus]) == 0
+    assert len(open(corpus, encoding="utf-8").read().splitlines()) == 2 * len(rows)
+    assert DP.main(["csvs", "--dir", str(tmp_path / "json")]) == 1
+    sy = str(tmp_path / "s.jsonl")
+    assert DP.main(["synth", "--out", sy, "--n", "25", "--seed", "5"]) == 0
+    assert len(open(sy, encoding="utf-8").read().splitlines()) == 25
+    capsys.readouterr()
+    assert DP.main(["json", "--input", sy, "--limit", "3"]) == 0
+    assert capsys.readouterr().out.count("[chat]") == 3
+    assert DP.main(["dump-text", "--input", sy, "--limit", "2"]) == 0
+    assert "[chat]" not in capsys.readouterr().out
