@@ -204,6 +204,8 @@ class Generator:
                   seed: int = 1234) -> dict:
         """Device-timed decode throughput after a synthetic uniform-random prompt (no host reads while decoding)."""
         eng = self.engine
+        if new_tokens < 10:
+            raise ValueError("benchmark needs at least 10 new tokens (the first 9 warm the graph up and are not timed)")
         sp = sampling or SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, seed=seed)
         rng = H.Rng(seed)
         V = eng.cfg.vocab_size

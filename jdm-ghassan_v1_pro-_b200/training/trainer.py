@@ -20,7 +20,8 @@ import torch
 from ..data.loader import RANK_SEED_STRIDE, DataLoader, Prefetcher, state_from_dict, state_to_dict
 from ..models.config import ModelConfig
 from ..utils.log import (human_bytes, human_count, human_duration, log_debug, log_error, log_info, log_warn)
-from ..utils.telemetry import PERF, STOP, PhaseTimers, StepWatchdog
+from ..parallel.watchdog import StepWatchdog
+from ..utils.telemetry import PERF, STOP, PhaseTimers
 from . import checkpoint as C
 from .config import TrainerConfig
 from .optim import LossScaler, LrScheduler
@@ -516,17 +517,23 @@ class Trainer:
         t_wall = time.perf_counter()
         self.prefetch.start()
         self.writer.start()
-        watchdog = StepWatchdog(float(os.environ.get("GB200_STEP_DEADLINE_S", "0")))
-        watchdog.start()
+        deadline = float(os.environ.get("GB200_STEP_DEADLINE_S", "0") or 0) or c.step_deadline_s
+        watchdog = None
+        if deadline > 0:                         # host thread: ends the process when a step (a peer) never arrives
+            watchdog = StepWatchdog(deadline, describe=lambda: "rank %d step %d/%d" % (self.rank, self.state.step, self.total_steps)).start()
         try:
             while self.state.step < self.total_steps:
                 res, lr, dt = self.train_step()
                 loss = res.loss
-                watchdog.kick()
+                if watchdog is not None:
+                    watchdog.beat()
                 main = self.is_main()
                 if main and c.log_every > 0 and self.state.step % c.log_every == 0:
                     self._log_step(loss, lr, res.gnorm, dt, res.ntok_global, getattr(self.engine, "last_step_ms", None))
                     self.writer.check_health()
+                if watchdog is not None and ((self.have_val and c.eval_every > 0 and self.state.step % c.eval_every == 0) or
+                                             (c.save_every > 0 and self.state.step % c.save_every == 0)):
+                    watchdog.hold()              # evaluation and checkpoint capture have no step cadence
                 if self.have_val and c.eval_every > 0 and self.state.step % c.eval_every == 0:
                     best = torch.zeros(2, dtype=torch.int64)
                     if main:
@@ -551,6 +558,8 @@ class Trainer:
                 if c.save_every > 0 and self.state.step % c.save_every == 0:
                     self.save("last.ckpt")
                 self.writer.check_health()
+                if watchdog is not None:
+                    watchdog.release()
                 if STOP.requested:
                     self.stopped_by_signal = True
                 if main:
@@ -566,7 +575,8 @@ class Trainer:
                 self.save("last.ckpt")
             self.writer.wait()
         finally:
-            watchdog.stop()
+            if watchdog is not None:
+                watchdog.stop()
             self.prefetch.stop()
             self.writer.stop()
         log_info("---------------- %s done: %d steps, %s tokens, %s --------------------" % (

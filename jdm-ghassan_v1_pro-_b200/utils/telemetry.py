@@ -119,43 +119,3 @@ class StopFlag:
 
 
 STOP = StopFlag()
-
-
-class StepWatchdog:
-    """Host thread that ends the process (exit code 3) when no step completes within ``deadline_s``; it prints
-    where the training thread is first.  Guards against a peer rank that never arrives."""
-
-    def __init__(self, deadline_s: float, on_timeout=None):
-        self.deadline = float(deadline_s)
-        self._last = time.monotonic()
-        self._stop = threading.Event()
-        self._thread: Optional[threading.Thread] = None
-        self.on_timeout = on_timeout
-        self.fired = False
-
-    def start(self):
-        if self.deadline <= 0 or self._thread is not None:
-            return
-        self._thread = threading.Thread(target=self._run, name="watchdog", daemon=True)
-        self._thread.start()
-
-    def kick(self):
-        self._last = time.monotonic()
-
-    def _run(self):
-        while not self._stop.wait(min(1.0, self.deadline / 4)):
-            if time.monotonic() - self._last > self.deadline:
-                self.fired = True
-                if self.on_timeout is not None:
-                    self.on_timeout()
-                    return
-                sys.stderr.write("[error] watchdog: no training step finished in %.0f s; aborting\n" % self.deadline)
-                import faulthandler
-                faulthandler.dump_traceback(file=sys.stderr)
-                os._exit(3)
-
-    def stop(self):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join(timeout=2)
-            self._thread = None

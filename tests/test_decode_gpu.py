@@ -289,3 +289,55 @@ def test_generator_host_and_device_routes(tmp_path):
     assert len(r3.tokens[0]) <= 12                                             # host route (n-gram ban)
     nll, n = gen.score_tokens(gen.encode_prompt("hello world"))
     assert n > 0 and math.isfinite(nll) and gen.perplexity(gen.encode_prompt("hello world")) > 1.0
+
+
+@pytest.mark.parametrize("profile,fmt_name", [("fp16", "f16"), ("q8_k", "q8_0"), ("q4_0", "q4_0")])
+def test_engine_from_exported_file_uses_stored_bytes(tmp_path, profile, fmt_name):
+    """A GGUF written by the exporter loads into an engine whose decode weights are the file's own quantised bytes;
+    its logits equal those of an engine that quantises the dequantised tensors again (the codec is idempotent)."""
+    import os
+    from ghassan_b200.formats.gguf import export_gguf
+    from ghassan_b200.inference import model_io as IO
+    from ghassan_b200.inference.engine import InferenceEngine
+    from ghassan_b200.models.config import init_parameters
+    gold = os.path.join(os.path.dirname(__file__), "golden", "formats")
+    cfg = _tiny_cfg(vocab_size=400, hidden_size=128, num_heads=4, num_kv_heads=2)
+    named = init_parameters(cfg, 21)
+    path = str(tmp_path / "m.gguf")
+    export_gguf(path, cfg, named, os.path.join(gold, "tiny400.gtok"), profile)
+    m = IO.load_model(path)
+    assert IO.sniff(path) == "gguf" and m.tokenizer is not None and m.tokenizer.vocab_size == 400
+    eng = IO.build_engine(m, batch=1, max_len=64)
+    again = InferenceEngine(m.cfg, m.named, fmt=fmt_name, batch=1, max_len=64, prefill_chunk=64)
+    seq = torch.randint(16, 400, (1, 12), generator=torch.Generator().manual_seed(8), dtype=torch.int32)
+    for e in (eng, again):
+        e.reset(1)
+    for j in range(12):
+        for e in (eng, again):
+            e.cur_tok.copy_(seq[:, j])
+            e._forward_token()
+        assert torch.allclose(eng.logits, again.logits, rtol=1e-3, atol=1e-3), (j, float((eng.logits - again.logits).abs().max()))
+
+
+def test_inference_cli_runs_the_model(tmp_path, capsys):
+    import json
+    import os
+    from ghassan_b200.cli import infer as I
+    from ghassan_b200.formats.gguf import export_gguf
+    from ghassan_b200.models.config import init_parameters
+    gold = os.path.join(os.path.dirname(__file__), "golden", "formats")
+    cfg = _tiny_cfg(vocab_size=400, hidden_size=128, num_heads=4, num_kv_heads=2)
+    named = init_parameters(cfg, 22)
+    path = str(tmp_path / "m.gguf")
+    export_gguf(path, cfg, named, os.path.join(gold, "tiny400.gtok"), "q8_k")
+    assert I.main(["generate", "--model", path, "--prompt", "salam", "--max-tokens", "8", "--seed", "3", "--no-stream", "--stats", "--ctx", "64"]) == 0
+    assert "decode" in capsys.readouterr().out
+    assert I.main(["bench", "--model", path, "--prompt-tokens", "16", "--tokens", "24", "--greedy"]) == 0
+    r = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert r["decode_tokens_per_s"] > 0 and r["new_tokens"] == 24
+    assert I.main(["perplexity", "--model", path, "--text", "salam labas 3lik", "--ctx", "64"]) == 0
+    assert "perplexity" in capsys.readouterr().out
+    assert I.main(["logits", "--model", path, "--prompt", "salam", "--out", str(tmp_path / "l.f32"), "--ctx", "64"]) == 0
+    assert os.path.getsize(str(tmp_path / "l.f32")) == 400 * 4
+    assert I.main(["eval", "--model", path, "--max-prompts", "2", "--max-tokens", "6", "--ctx", "128"]) == 0
+    assert "items 2" in capsys.readouterr().out
