@@ -302,7 +302,7 @@ int launch_fwd(const AttnArgs& a, cudaStream_t st) {
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid((a.T + ROWS - 1) / ROWS, a.H, a.B);
   kern<<<grid, 128, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 template <typename T, int HD>
@@ -324,7 +324,7 @@ int launch_bwd(const AttnArgs& a, cudaStream_t st) {
   dim3 gq((a.T + ROWS - 1) / ROWS, a.H, a.B), gkv((a.T + ROWS - 1) / ROWS, a.KV, a.B);
   kq<<<gq, 128, smem_q, st>>>(a);
   kkv<<<gkv, 128, smem_kv, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 }  // namespace gb

@@ -704,7 +704,7 @@ int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   }
   dim3 grid((a->T + AT_M - 1) / AT_M, a->H, a->B);
   kern<<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 template <typename T>
@@ -752,7 +752,7 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   dim3 gq((a->T + AT_M - 1) / AT_M, a->H, a->B), gkv((a->T + AT_N - 1) / AT_N, a->KV, a->B);
   kq<<<gq, AT_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
   kkv<<<gkv, AT_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 }  // namespace gb
@@ -781,7 +781,7 @@ extern "C" int gb_attn_tc_bwd(const gb_attn_args* a, int* lo_scratch, int lo_rea
 extern "C" int gb_attn_seg_lo(const int* seg, int* lo, int B, int T, cudaStream_t st) {
   if (!seg || !lo || B <= 0 || T <= 0) return -1;
   attn_seg_lo_kernel<<<B, 1024, 0, st>>>(seg, lo, B, T);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_attn_tc_fwd(const gb_attn_args* a, int* lo_scratch, int lo_ready, int* status, cudaStream_t st) {

@@ -129,5 +129,5 @@ extern "C" int gb_softmax_ce(void* logits, long long ld, const int* targets, int
     ce_row_kernel<__half><<<rows, 256, 0, st>>>((__half*)logits, ld, targets, V, z_loss, grad_scale, grad_scale_dev,
                                                 write_grad, row_loss);
   ce_fold_kernel<<<1, 256, 0, st>>>(row_loss, rows, acc);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }

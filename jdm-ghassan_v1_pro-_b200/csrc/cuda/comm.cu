@@ -46,6 +46,29 @@ __global__ void sync_barrier_kernel(unsigned int* const* __restrict__ peer_ctl, 
   __syncthreads();
 }
 
+// Same barrier with the epoch kept in device memory: a CUDA graph that contains it can be replayed.
+__global__ void sync_barrier_auto_kernel(unsigned int* const* __restrict__ peer_ctl, int rank, int world,
+                                         unsigned int* __restrict__ counter, long long spin_limit,
+                                         int* __restrict__ status) {
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) s_epoch = ++(*counter);
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  const int p = threadIdx.x;
+  if (p < world) {
+    __threadfence_system();
+    st_release_sys(peer_ctl[p] + CTL_BARRIER + rank, epoch);
+    const unsigned int* flag = peer_ctl[rank] + CTL_BARRIER + p;
+    bool ok = false;
+    for (long long it = 0; it < spin_limit; ++it) {
+      if ((int)(ld_acquire_sys(flag) - epoch) >= 0) { ok = true; break; }
+      __nanosleep(40);
+    }
+    if (!ok) atomicExch(status, ST_TIMEOUT_PEER);
+  }
+  __syncthreads();
+}
+
 // ---------------------------------------------------------------------------------------------- reduce-scatter
 template <int W>
 __device__ __forceinline__ float4 sum_peers(float* const* __restrict__ g, long long i, int world) {
@@ -250,7 +273,15 @@ extern "C" int gb_sync_barrier(unsigned int* const* peer_ctl, int rank, int worl
                                cudaStream_t st) {
   if (!peer_ctl || !status || world < 1 || world > GB_MAX_RANKS || rank < 0 || rank >= world) return -1;
   sync_barrier_kernel<<<1, 32, 0, st>>>(peer_ctl, rank, world, epoch, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
+}
+
+extern "C" int gb_sync_barrier_auto(unsigned int* const* peer_ctl, int rank, int world, unsigned int* counter,
+                                    long long spin_limit, int* status, cudaStream_t st) {
+  if (!peer_ctl || !status || !counter || world < 1 || world > GB_MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if (spin_limit <= 0) spin_limit = SPIN_LIMIT;
+  sync_barrier_auto_kernel<<<1, 32, 0, st>>>(peer_ctl, rank, world, counter, spin_limit, status);
+  return gb_launch_rc();
 }
 
 static int check_sync_args(const gb_sync_args* a) {
@@ -272,7 +303,7 @@ extern "C" int gb_sync_reduce(const gb_sync_args* a, cudaStream_t st) {
     case 8: sync_reduce_kernel<8><<<GB_SYNC_BLOCKS, 256, 0, st>>>(*a); break;
     default: sync_reduce_kernel<0><<<GB_SYNC_BLOCKS, 256, 0, st>>>(*a); break;
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_sync_update(const gb_sync_args* a, cudaStream_t st) {
@@ -285,12 +316,12 @@ extern "C" int gb_sync_update(const gb_sync_args* a, cudaStream_t st) {
     if (a->kind == 0) sync_update_kernel<__half, 0><<<blocks, 256, 0, st>>>(*a);
     else sync_update_kernel<__half, 1><<<blocks, 256, 0, st>>>(*a);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_sync_small_allreduce(const float* const* peer_src, float* dst, int n, int world, cudaStream_t st) {
   if (!peer_src || !dst || n < 0 || world < 1 || world > GB_MAX_RANKS) return -1;
   if (n == 0) return 0;
   sync_small_allreduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(peer_src, dst, n, world);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }

@@ -412,7 +412,7 @@ extern "C" int gb_gemv(const void* W, int fmt, int N, int K, const void* x16, in
   GB_FMT_SWITCH(fmt, CALL)
 #undef CALL
 #undef GEMV_GO
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_gemv_expert_swiglu(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const void* x16, int B,
@@ -430,7 +430,7 @@ extern "C" int gb_gemv_expert_swiglu(const void* Wg, const void* Wu, int fmt, in
   else { if (split) SW_GO(F, 4, __half); else SW_GO(F, 1, __half); }
   GB_FMT_SWITCH(fmt, CALL)
 #undef CALL
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E, const void* act16, int B, const int* idx,
@@ -449,7 +449,7 @@ extern "C" int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E
   else { if (split) DN_GO(F, 4, __half); else DN_GO(F, 1, __half); }
   GB_FMT_SWITCH(fmt, CALL)
 #undef CALL
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_decode_route(const void* x16, const float* router_w, const float* bias, int B, int d, int ne, int top_k,
@@ -457,7 +457,7 @@ extern "C" int gb_decode_route(const void* x16, const float* router_w, const flo
   if (!x16 || !router_w || !idx || !w || B <= 0 || ne <= 0 || ne > 64 || top_k <= 0 || top_k > 8 || top_k > ne || d % 2) return -1;
   if (is_bf16) decode_route_kernel<__nv_bfloat16><<<B, 256, 0, st>>>((const __nv_bfloat16*)x16, router_w, bias, d, ne, top_k, idx, w);
   else decode_route_kernel<__half><<<B, 256, 0, st>>>((const __half*)x16, router_w, bias, d, ne, top_k, idx, w);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_kv_append(const void* k16, long long ld_k, const void* v16, long long ld_v, void* cacheK, void* cacheV,
@@ -467,13 +467,13 @@ extern "C" int gb_kv_append(const void* k16, long long ld_k, const void* v16, lo
   // 16-bit elements of either type are copied as raw bits
   kv_append_kernel<__half><<<B, 128, 0, st>>>((const __half*)k16, ld_k, (const __half*)v16, ld_v, (__half*)cacheK,
                                               (__half*)cacheV, slot_pos, state, cap, pinned, kv_dim);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_decode_advance(gb_seq_state* state, int* pos_out, int B, int cap, int pinned, cudaStream_t st) {
   if (!state || !pos_out || B <= 0) return -1;
   decode_advance_kernel<<<(B + 63) / 64, 64, 0, st>>>(state, pos_out, B, cap, pinned);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 template <typename T, int HD>
@@ -496,7 +496,7 @@ static int launch_decode_attn(const void* q, long long ld_q, const void* cK, con
   }
 #undef ATT
   decode_attn_merge_kernel<T, HD><<<B * H, HD, 0, st>>>(scratch, splits, (T*)out, ld_o, H);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_decode_attn(const void* q16, long long ld_q, const void* cacheK, const void* cacheV, const int* slot_pos,

@@ -312,7 +312,7 @@ __global__ void cast_f32_to_16_kernel(const float* __restrict__ src, T* __restri
 
 using namespace gb;
 
-#define GB_LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+#define GB_LAUNCH_OK() gb_launch_rc()
 
 extern "C" int gb_embed_fwd(const int* ids, const float* table, float* out, int n_tok, int d, int vocab, cudaStream_t st) {
   if (d % 4) return -1;
@@ -459,6 +459,29 @@ extern "C" int gb_splitk_reduce(const float* part, int splits, long long n, void
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (is_bf16) splitk_reduce_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(part, splits, n, (__nv_bfloat16*)out16);
   else splitk_reduce_kernel<__half><<<(int)blocks, 256, 0, st>>>(part, splits, n, (__half*)out16);
+  return GB_LAUNCH_OK();
+}
+
+// out[i] += sum_s part[s * n + i] (fixed order): second stage of a split-K weight gradient
+__global__ void splitk_accumulate_kernel(const float* __restrict__ part, int splits, long long n, float* __restrict__ out) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4;
+  const long long stride = (long long)gridDim.x * blockDim.x * 4;
+  for (; i < n; i += stride) {
+    float4 acc = *reinterpret_cast<const float4*>(out + i);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(part + (long long)s * n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + i) = acc;
+  }
+}
+
+extern "C" int gb_splitk_accumulate(const float* part, int splits, long long n, float* out, cudaStream_t st) {
+  if (!part || !out || n <= 0 || n % 4 || splits < 1) return -1;
+  if ((reinterpret_cast<uintptr_t>(part) | reinterpret_cast<uintptr_t>(out)) & 15) return -2;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_accumulate_kernel<<<(int)blocks, 256, 0, st>>>(part, splits, n, out);
   return GB_LAUNCH_OK();
 }
 

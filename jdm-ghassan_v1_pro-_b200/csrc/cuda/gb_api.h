@@ -35,6 +35,8 @@ typedef struct gb_gemm_args {
   const float* addend; int ld_add;   // out = acc + addend (fp32), may alias out when out is fp32
   void* aux_out; const void* aux_in; int ld_aux;
   int* status;              // device status word
+  const long long* tile_out;  // mode 1 + plain store, no addend: device table with the address of output row 0 of every
+                              // 128-row tile (overrides out); destinations may be another GPU's mapped memory
 } gb_gemm_args;
 int gb_gemm(const gb_gemm_args* args, cudaStream_t stream);
 
@@ -57,6 +59,7 @@ int gb_qk_norm_rope_bwd(const void* dout, int ld_dout, const void* qkv, int ld_i
 int gb_cast_f32_to_16(const float* src, void* dst, long long n, int is_bf16, cudaStream_t st);
 // out16[i] = sum over splits of part[s*n + i]: second stage of a split-K GEMM (gb_gemm mode 2 with equal K ranges)
 int gb_splitk_reduce(const float* part, int splits, long long n, void* out16, int is_bf16, cudaStream_t st);
+int gb_splitk_accumulate(const float* part, int splits, long long n, float* out, cudaStream_t st);
 
 // ----------------------------------------------------------------------------- attention
 typedef struct gb_attn_args {

@@ -49,6 +49,10 @@ typedef struct gb_sync_args {
 
 // All ranks have reached this point, and their earlier writes are visible to peer loads issued after it.
 int gb_sync_barrier(unsigned int* const* peer_ctl, int rank, int world, unsigned int epoch, int* status, cudaStream_t st);
+// The same, with the epoch read from and advanced in `counter` (device memory, starts at 0, one per control block and
+// rank): usable inside a captured CUDA graph.  `spin_limit` polls of about 50 ns bound the wait (0 = about 2 s).
+int gb_sync_barrier_auto(unsigned int* const* peer_ctl, int rank, int world, unsigned int* counter, long long spin_limit,
+                         int* status, cudaStream_t st);
 int gb_sync_reduce(const gb_sync_args* a, cudaStream_t st);
 int gb_sync_update(const gb_sync_args* a, cudaStream_t st);
 // dst[i] = sum over ranks (in rank order) of peer_src[r][i]: replicated small tensors (routing counts).

@@ -35,6 +35,7 @@ struct GemmParams {
   void* aux_out;              // SwiGLU fwd: interleaved gate/up copy (may be null)
   const void* aux_in;         // SwiGLU bwd: saved interleaved gate/up
   int ld_aux;
+  const long long* tile_out;  // mode 1, plain store: address of row 0 of each 128-row tile's output (may be a peer GPU's memory)
   int* status;
 };
 
@@ -62,6 +63,7 @@ struct TileInfo {
   int b_row_off;   // stored-row offset applied to B (expert selection)
   int k_begin, k_end;
   long long out_off;
+  int tm;          // index of the 128-row tile (modes 0 and 1)
   bool valid;
 };
 
@@ -73,6 +75,7 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile, i
   t.out_off = 0;
   t.k_begin = 0;
   t.k_end = p.K;
+  t.tm = 0;
   if (p.mode == 2) {
     int per = tiles_m * tiles_n;
     int g = tile / per;
@@ -83,10 +86,13 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile, i
     t.k_end = p.seg_offsets[g + 1];
     t.out_off = (long long)g * p.out_group_stride;
   } else {
-    int tm = tile % tiles_m;
-    int tn = tile / tiles_m;
+    // column tiles of one row block are neighbours in the schedule: the CTAs that run at the same time share the
+    // A rows (fetched from DRAM once, then L2 hits), and B -- one expert's weights, a few MB -- stays in L2 anyway
+    int tm = tile / tiles_n;
+    int tn = tile - tm * tiles_n;
     t.a_row0 = tm * BM;
     t.n0 = tn * BN;
+    t.tm = tm;
     if (p.mode == 1) {
       int e = p.tile_expert[tm];
       t.b_row_off = e * p.b_group_rows;
@@ -275,7 +281,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool row_ok = row < p.M;
       const uint32_t taddr0 = tmem_base + ab * BN + (uint32_t(quarter * 32) << 16);
       if constexpr (EPI == EPI_STORE) {
-        OutT* orow = reinterpret_cast<OutT*>(p.out) + t.out_off + (long long)row * p.ldo;
+        // per-tile destinations: the rows of this tile go to wherever the table says (expert-parallel combine
+        // writes them straight into the buffer of the GPU that owns the tokens)
+        OutT* orow = p.tile_out ? reinterpret_cast<OutT*>(p.tile_out[t.tm]) + (long long)r_in_tile * p.ldo
+                                : reinterpret_cast<OutT*>(p.out) + t.out_off + (long long)row * p.ldo;
         const float* arow = p.addend ? p.addend + t.out_off + (long long)row * p.ld_add : nullptr;
         constexpr int CH = BN / 64;            // 32-column chunks per half
 #pragma unroll 1
@@ -446,7 +455,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const gb::GemmPara
   int grid = max_tiles < num_sms() ? max_tiles : num_sms();
   if (grid < 1) grid = 1;
   kern<<<grid, gb::GEMM_THREADS, smem, st>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 template <int EPI, typename OutT, typename InT>
@@ -478,6 +487,8 @@ extern "C" int gb_gemm(const gb_gemm_args* a, cudaStream_t st) {
   p.out = a->out; p.ldo = a->ldo; p.out_group_stride = a->out_group_stride;
   p.addend = a->addend; p.ld_add = a->ld_add;
   p.aux_out = a->aux_out; p.aux_in = a->aux_in; p.ld_aux = a->ld_aux;
+  p.tile_out = (a->mode == 1 && a->epilogue == gb::EPI_STORE && !a->addend) ? a->tile_out : nullptr;
+  if (a->tile_out && !p.tile_out) return -1;
   p.status = a->status;
   if (!p.status) return -1;
 

@@ -460,7 +460,7 @@ extern "C" int gb_moe_capacity(int n_tok, int ne, int top_k, int shared) {
   return (int)((cap + 127) / 128 * 128);
 }
 
-#define GB_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+#define GB_OK() (gb_launch_rc())
 
 extern "C" int gb_moe_route(const gb_moe_args* a, cudaStream_t st) {
   int rc = moe_check(a);

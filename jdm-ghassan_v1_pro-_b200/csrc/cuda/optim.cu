@@ -149,7 +149,7 @@ extern "C" int gb_optimizer_step(const gb_opt_args* a, cudaStream_t st) {
   if (a->is_bf16) { if (a->kind == 0) GB_OPT(__nv_bfloat16, 0); else GB_OPT(__nv_bfloat16, 1); }
   else { if (a->kind == 0) GB_OPT(__half, 0); else GB_OPT(__half, 1); }
 #undef GB_OPT
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_sqnorm_blocks(long long n) { return (int)((n + SQ_CHUNK - 1) / SQ_CHUNK); }
@@ -158,13 +158,13 @@ extern "C" int gb_sqnorm_partial(const float* g, long long n, double* partial, c
   if (n <= 0) return 0;
   if (reinterpret_cast<uintptr_t>(g) & 15) return -2;
   sqnorm_partial_kernel<<<gb_sqnorm_blocks(n), SQ_THREADS, 0, st>>>(g, n, partial);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_finish_norm(const double* partial, int n_partial, const float* grad_scale_dev, float grad_scale,
                               float clip, float* out, cudaStream_t st) {
   finish_norm_kernel<<<1, 256, 0, st>>>(partial, n_partial, grad_scale_dev, grad_scale, clip, out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }
 
 extern "C" int gb_fill_f32(float* p, float v, long long n, cudaStream_t st) {
@@ -172,5 +172,5 @@ extern "C" int gb_fill_f32(float* p, float v, long long n, cudaStream_t st) {
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   fill_f32_kernel<<<(int)blocks, 256, 0, st>>>(p, v, n);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }

@@ -213,5 +213,5 @@ extern "C" int gb_sample(const gb_sample_args* a, cudaStream_t st) {
   if (a->n_stop > 0 && !a->stop) return -1;
   gb::sample_kernel<<<a->B, gb::SM_THREADS, 0, st>>>(*a);
   if (a->tok_log && a->step) gb::step_inc_kernel<<<1, 1, 0, st>>>(const_cast<int*>(a->step));
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return gb_launch_rc();
 }

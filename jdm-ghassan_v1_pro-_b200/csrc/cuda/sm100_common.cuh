@@ -20,7 +20,18 @@ enum : int {
   ST_TIMEOUT_TMEM_EMPTY = 104,// MMA warp never got an accumulator buffer back
   ST_TIMEOUT_PEER = 201,      // a flag owned by another rank never changed
   ST_BAD_ARGUMENT = 301,
+  ST_EP_OVERFLOW = 302,       // expert parallelism: more rows routed to this rank's experts than its buffers hold
 };
+
+}  // namespace gb
+
+// Result of the launch just issued, for the C launchers: 0, or -(1000 + cudaError_t) so that the caller can name it.
+static inline int gb_launch_rc() {
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(1000 + static_cast<int>(e));
+}
+
+namespace gb {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

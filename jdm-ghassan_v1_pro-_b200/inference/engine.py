@@ -242,7 +242,7 @@ class InferenceEngine:
             n -= 1
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):   # other threads (prefetch, checkpoint writer) may call CUDA
                 self._step_eager(sp)
             self.graph, self._graph_key = g, key
         for _ in range(max(0, n)):

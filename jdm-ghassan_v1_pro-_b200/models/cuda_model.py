@@ -219,6 +219,7 @@ class CudaModel:
         self.segs = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
         self.attn_tc = K.attn_tc_supported(cfg.head_dim)
         self.seg_lo = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
+        self.ep = None                                      # set by enable_expert_parallel()
         self._alloc_activations(train)
 
     # ------------------------------------------------------------------ buffers
@@ -275,6 +276,12 @@ class CudaModel:
         t.norm_part = K.rmsnorm_bwd_scratch(N, d, dev)
         t.qk_part = K.qk_rope_scratch(N, H + cfg.num_kv_heads, cfg.head_dim, dev)
         self.tmp = t
+
+    def enable_expert_parallel(self, buffers=None, capacity: float = 2.0):
+        """Divide the routed experts among the ranks of the default process group (all ranks must call this)."""
+        from ..parallel.expert_parallel import ExpertParallel
+        self.ep = ExpertParallel(self, buffers, capacity, train=hasattr(self, "tmp"))
+        return self.ep
 
     def activation_bytes(self) -> int:
         n = 0
@@ -351,7 +358,9 @@ class CudaModel:
                        KV, hd, cfg.sliding_window, cfg.attn_scale())
         G.gemm(b.att, self.w16(p + "wo"), out=b.x_mid, addend=x_in)
         K.rmsnorm_fwd(b.x_mid, self.w(p + "ffn_norm"), b.xb2, b.rrms2, cfg.rms_eps)
-        if cfg.use_moe:
+        if cfg.use_moe and self.ep is not None:     # experts divided among the ranks (parallel/expert_parallel.py)
+            self.ep.forward(l, b, x_out, train, want_aux)
+        elif cfg.use_moe:
             bias = self.moe_bias[l] if self.moe_bias is not None else None
             counts = self.bias_counts[l] if (train and self.bias_counts is not None) else None
             jit = cfg.moe_jitter if train else 0.0
@@ -412,7 +421,9 @@ class CudaModel:
         d, qd, kvd, H, KV, hd = cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         E, ne1 = self.layout.Eff, self.layout.ne1
         x_in = self.x[l]
-        if cfg.use_moe:
+        if cfg.use_moe and self.ep is not None:
+            self.ep.backward(l, b)
+        elif cfg.use_moe:
             ws = b.ws
             K.moe_combine_bwd(ws, t.dx, b.yperm, t.dy_perm, t.gdot)
             G.gemm_swiglu_bwd(t.dy_perm, self.w16(p + "w_down"), b.gu, dgu_out=t.dgu, tile_expert=ws.tile_expert,
@@ -437,7 +448,7 @@ class CudaModel:
         # attention branch
         G.gemm(t.dx16, self.w16(p + "wo"), b_mn=True, out=t.datt)
         gwo = self.g(p + "wo")
-        G.gemm(t.dx16, b.att, a_mn=True, b_mn=True, out=gwo, addend=gwo)
+        G.gemm_wgrad(t.dx16, b.att, gwo)
         if self.attn_tc:
             K.attn_tc_bwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, None, self.seg_lo, t.datt,
                           t.delta, t.dqk[:, :qd], t.dqk[:, qd:], t.dqkv[:, qd + kvd:], self.B, self.T, H, KV, hd,
@@ -453,7 +464,7 @@ class CudaModel:
                            cfg.rms_eps, cfg.rope_type)
         G.gemm(t.dqkv, self.w16(p + "wqkv"), b_mn=True, out=t.dxb)
         gq = self.g(p + "wqkv")
-        G.gemm(t.dqkv, b.xb, a_mn=True, b_mn=True, out=gq, addend=gq)
+        G.gemm_wgrad(t.dqkv, b.xb, gq)
         K.rmsnorm_bwd(t.dxb, x_in, self.w(p + "attn_norm"), b.rrms1, t.dx, t.dx, t.dx16, t.norm_part,
                       self.g(p + "attn_norm"))
 

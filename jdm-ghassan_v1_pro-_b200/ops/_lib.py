@@ -37,6 +37,7 @@ class GemmArgs(ctypes.Structure):
         ("addend", c_vp), ("ld_add", c_int),
         ("aux_out", c_vp), ("aux_in", c_vp), ("ld_aux", c_int),
         ("status", c_vp),
+        ("tile_out", c_vp),
     ]
 
 
@@ -74,6 +75,8 @@ _status = {}
 def status_word(device=None) -> torch.Tensor:
     """Per-device int32 word that kernels write a non-zero code into when a bounded wait expires."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     key = (dev.type, dev.index)
     t = _status.get(key)
     if t is None:
@@ -90,6 +93,7 @@ STATUS_NAMES = {
     104: "timeout waiting for an accumulator buffer (tmem empty barrier)",
     201: "timeout waiting for a peer rank's flag",
     301: "bad argument detected on device",
+    302: "expert parallelism: more rows were routed to this rank's experts than its buffers hold (raise b200.ep_capacity)",
 }
 
 
@@ -103,6 +107,8 @@ def check_status(device=None, what="kernel") -> None:
 
 
 def check_rc(rc: int, what: str) -> None:
+    if rc <= -1000:            # the launch itself failed: -(1000 + cudaError_t)
+        raise RuntimeError(f"{what}: CUDA launch error {-rc - 1000}")
     if rc != 0:
         raise RuntimeError(f"{what}: launcher returned {rc}")
 

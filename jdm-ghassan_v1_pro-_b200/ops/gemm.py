@@ -133,14 +133,16 @@ def gemm_swiglu_bwd(dy, w_down, gu, *, dgu_out=None, b_mn=True, tile_expert=None
 
 
 def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_rows, out=None, out_dtype=None,
-                      block_n=0):
+                      block_n=0, tile_out=None, ldo=None):
     """Expert-sorted rows: every 128-row tile of ``a`` multiplies the weight block of ``tile_expert[tile]``.
 
     ``b`` stacks the per-expert matrices along its rows: ``group_rows`` stored rows per expert.
+    ``tile_out`` (device int64 table, one entry per 128-row tile) redirects each tile's rows to the given address,
+    row pitch ``ldo`` elements; the destinations may be buffers of other GPUs mapped into this process.
     """
     M, K = a.shape
     if out is None:
-        out = torch.empty(M, n, dtype=out_dtype or a.dtype, device=a.device)
+        out = torch.empty((M, n) if tile_out is None else (1, n), dtype=out_dtype or a.dtype, device=a.device)
     if not block_n:
         block_n = 256 if (n % 256 == 0 and M >= 4096) else 128
     g = _base_args(a, b, M, n, K, False, b_mn, out, block_n)
@@ -148,6 +150,11 @@ def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_ro
     g.mode = 1
     g.tile_expert, g.num_m_tiles = tile_expert.data_ptr(), num_m_tiles.data_ptr()
     g.b_group_rows = group_rows
+    if tile_out is not None:
+        if tile_out.dtype != torch.int64:
+            raise ValueError("tile_out must be int64 addresses")
+        g.tile_out = tile_out.data_ptr()
+        g.ldo = int(ldo if ldo is not None else n)
     _launch(g)
     return out
 
@@ -160,8 +167,8 @@ def gemm_grouped_reduce(a, b, seg_offsets, groups, out, *, accumulate=True, bloc
     M, N = a.shape[1], b.shape[1]
     if out.dtype != torch.float32 or out.shape != (groups, M, N) or not out.is_contiguous():
         raise ValueError("out must be contiguous fp32 [groups, M, N]")
-    if not block_n:
-        block_n = 128
+    if not block_n:    # 256-wide tiles measured 1.47x faster once the groups supply tiles for every SM
+        block_n = 256 if (N % 256 == 0 and groups * ((M + 127) // 128) * (N // 256) >= 222) else 128
     g = _base_args(a, b, M, N, 0, True, True, out, block_n)
     g.epilogue = EPI_STORE
     g.mode = 2
@@ -207,6 +214,44 @@ class SplitK:
                                          ctypes.c_int(int(out16.dtype == torch.bfloat16)), _lib.stream_ptr())
         _lib.check_rc(rc, "gb_splitk_reduce")
         return out16
+
+
+_WGRAD_PLANS = {}
+
+
+def gemm_wgrad(a, b, grad):
+    """``grad += a^T @ b`` for a weight gradient: ``a`` is ``[tokens, M]``, ``b`` is ``[tokens, N]``, ``grad`` is
+    contiguous fp32 ``[M, N]``.  A product with few output tiles and a long token dimension (the attention
+    projections: 36-60 tiles for 148 SMs) is split over the tokens: ``splits`` CTAs per tile write fp32 partials and
+    a second kernel adds them to ``grad`` in a fixed order (measured 60 us -> 23-36 us on the pro_1b shapes).
+    Everything else takes the plain accumulate path."""
+    Kt, M = a.shape
+    N = b.shape[1]
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    splits = min(8, 148 // max(1, tiles), Kt // 1024)
+    if splits < 2 or Kt % 64 or not grad.is_contiguous() or grad.shape != (M, N) or (M * N) % 4:
+        return gemm(a, b, a_mn=True, b_mn=True, out=grad, addend=grad)
+    key = (M, N, Kt, splits, a.device.index)
+    plan = _WGRAD_PLANS.get(key)
+    if plan is None:
+        kc = (Kt // splits + 63) // 64 * 64
+        offs = [min(Kt, i * kc) for i in range(splits)] + [Kt]
+        plan = (torch.tensor(offs, dtype=torch.int32, device=a.device),
+                torch.empty(splits, M, N, dtype=torch.float32, device=a.device))
+        _WGRAD_PLANS[key] = plan
+    offsets, part = plan
+    g = _base_args(a, b, M, N, 0, True, True, part, 128)
+    g.epilogue = EPI_STORE
+    g.mode = 2
+    g.seg_offsets = offsets.data_ptr()
+    g.groups = splits
+    g.out_group_stride = M * N
+    g.ldo = N
+    _launch(g)
+    rc = _lib.lib().gb_splitk_accumulate(ctypes.c_void_p(part.data_ptr()), ctypes.c_int(splits), ctypes.c_longlong(M * N),
+                                         ctypes.c_void_p(grad.data_ptr()), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_splitk_accumulate")
+    return grad
 
 
 def interleave_gate_up(gate, up, block=64):

@@ -114,6 +114,13 @@ class CudaEngine:
             self.grad_sync = FusedGradSync(self)   # moves P / W16 / Gr (and routing counts) into symmetric memory
             if self.weight_ema is not None:
                 self.weight_ema = torch.empty_like(self.model.P).copy_(self.model.P)
+        self.expert_parallel = None
+        if tcfg.ep_size > 1:
+            if not mcfg.use_moe:
+                raise ValueError("b200.ep_size > 1 needs a mixture-of-experts model")
+            if tcfg.ep_size != self.dist.world:
+                raise ValueError("b200.ep_size must equal the number of ranks (%d): the expert group is the whole job" % self.dist.world)
+            self.expert_parallel = self.model.enable_expert_parallel(capacity=tcfg.ep_capacity)
         self.last_step_ms = None
         self._ev0, self._ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         self.kernel_launches = 0
@@ -183,7 +190,7 @@ class CudaEngine:
         else:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):   # other threads (prefetch, checkpoint writer) may call CUDA
                 m.forward_backward(freeze)
             self.graph = g
             g.replay()   # capture does not execute: run the micro-batch that triggered it

@@ -2,6 +2,8 @@
 
 parity      train a small MoE model for a few steps twice, once with the fused peer-memory gradient exchange and
             once with the NCCL all-reduce path, from the same seed and data; weights must agree.
+ep_parity   the same model trained with the routed experts divided among the ranks (peer-memory dispatch, combine in
+            the GEMM epilogue) and with replicated experts: same losses, same weights.
 bench_sync  time the exchange alone on buffers of the pro_1b size (device time, max over ranks) against one NCCL
             all-reduce of the same gradient buffer.
 """
@@ -63,7 +65,7 @@ def make_shards(d, vocab):
     write_shard(os.path.join(d, "train_0000.gbin"), docs, vocab, None)
 
 
-def run_engine(work, sync, steps=5, opt="adamw"):
+def run_engine(work, sync, steps=5, opt="adamw", extra=None):
     from ghassan_b200.models.config import ModelConfig
     from ghassan_b200.training.config import TrainerConfig
     from ghassan_b200.training.trainer import Trainer
@@ -75,6 +77,8 @@ def run_engine(work, sync, steps=5, opt="adamw"):
     c.set("training.checkpoint_dir", os.path.join(work, "ck_" + sync))
     c.set("training.optimizer", opt)
     c.set("b200.grad_sync", sync)
+    for k, v in (extra or {}).items():
+        c.set(k, v)
     tr = Trainer(ModelConfig.from_config(c), TrainerConfig.from_config(c), device="cuda")
     tr.prepare()
     out = []
@@ -127,6 +131,39 @@ def parity(work):
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
         print("PARITY OK" if int(flag) else "PARITY FAILED", flush=True)
+    return 0 if int(flag) else 1
+
+
+def ep_parity(work):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    if rank == 0:
+        os.makedirs(work, exist_ok=True)
+        make_shards(work, 608)
+    dist.barrier()
+    ok = True
+    for graphs in ("false", "true"):
+        a, wa, _, tra = run_engine(work, "fused", extra={"b200.ep_size": str(world), "b200.cuda_graphs": graphs,
+                                                         "training.checkpoint_dir": os.path.join(work, "ck_ep" + graphs)})
+        assert tra.engine.expert_parallel is not None, "expert-parallel path not taken"
+        tra.engine.expert_parallel.check("expert parallel run")
+        b, wb, _, _ = run_engine(work, "fused", extra={"b200.cuda_graphs": graphs})
+        for (la, ga, na, apa), (lb, gb_, nb, apb) in zip(a, b):
+            if na != nb or apa != apb or abs(la - lb) > 1e-3 * max(1.0, abs(lb)) or abs(ga - gb_) > 2e-2 * max(1e-3, abs(gb_)):
+                print(rank, "step mismatch", (la, ga, na, apa), (lb, gb_, nb, apb), flush=True)
+                ok = False
+        if a[0][0] != b[0][0]:                       # the first forward pass sees identical weights: bit-equal loss
+            print(rank, "first loss differs", a[0][0], b[0][0], flush=True)
+            ok = False
+        worst = max(float(np.abs(wa[n] - wb[n]).max()) / (float(np.abs(wb[n]).max()) + 1e-9) for n in wb)
+        if worst > 2e-3:
+            print(rank, "weights differ", worst, flush=True)
+            ok = False
+        print(rank, "graphs", graphs, "losses", [round(x[0], 4) for x in a], "vs", [round(x[0], 4) for x in b],
+              "worst rel weight diff", worst, flush=True)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("EP PARITY OK" if int(flag) else "EP PARITY FAILED", flush=True)
     return 0 if int(flag) else 1
 
 
@@ -221,7 +258,7 @@ def main():
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    rc = parity(work) if mode == "parity" else bench_sync(work)
+    rc = {"parity": parity, "ep_parity": ep_parity, "bench_sync": bench_sync}[mode](work)
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(rc)

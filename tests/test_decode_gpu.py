@@ -293,8 +293,10 @@ def test_generator_host_and_device_routes(tmp_path):
 
 @pytest.mark.parametrize("profile,fmt_name", [("fp16", "f16"), ("q8_k", "q8_0"), ("q4_0", "q4_0")])
 def test_engine_from_exported_file_uses_stored_bytes(tmp_path, profile, fmt_name):
-    """A GGUF written by the exporter loads into an engine whose decode weights are the file's own quantised bytes;
-    its logits equal those of an engine that quantises the dequantised tensors again (the codec is idempotent)."""
+    """A GGUF written by the exporter loads into an engine whose decode weights are the file's own quantised bytes.
+    For the single-format profiles its logits equal those of an engine that quantises the dequantised tensors again
+    (the codec is idempotent); the q4_0 profile mixes Q4_0 and Q8_0 tensors, so it is compared with an fp16 engine
+    over the dequantised tensors (difference: fp16 rounding of q*d)."""
     import os
     from ghassan_b200.formats.gguf import export_gguf
     from ghassan_b200.inference import model_io as IO
@@ -308,7 +310,9 @@ def test_engine_from_exported_file_uses_stored_bytes(tmp_path, profile, fmt_name
     m = IO.load_model(path)
     assert IO.sniff(path) == "gguf" and m.tokenizer is not None and m.tokenizer.vocab_size == 400
     eng = IO.build_engine(m, batch=1, max_len=64)
-    again = InferenceEngine(m.cfg, m.named, fmt=fmt_name, batch=1, max_len=64, prefill_chunk=64)
+    mixed = profile == "q4_0"
+    again = InferenceEngine(m.cfg, m.named, fmt="f16" if mixed else fmt_name, batch=1, max_len=64, prefill_chunk=64)
+    tol = 1e-2 if mixed else 1e-3
     seq = torch.randint(16, 400, (1, 12), generator=torch.Generator().manual_seed(8), dtype=torch.int32)
     for e in (eng, again):
         e.reset(1)
@@ -316,7 +320,7 @@ def test_engine_from_exported_file_uses_stored_bytes(tmp_path, profile, fmt_name
         for e in (eng, again):
             e.cur_tok.copy_(seq[:, j])
             e._forward_token()
-        assert torch.allclose(eng.logits, again.logits, rtol=1e-3, atol=1e-3), (j, float((eng.logits - again.logits).abs().max()))
+        assert torch.allclose(eng.logits, again.logits, rtol=tol, atol=tol), (j, float((eng.logits - again.logits).abs().max()))
 
 
 def test_inference_cli_runs_the_model(tmp_path, capsys):

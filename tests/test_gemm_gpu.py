@@ -149,6 +149,19 @@ def test_grouped_rows_and_grouped_reduce():
         ref = 1.0 + y16[offs[e]:offs[e] + c].float().t() @ x[offs[e]:offs[e] + c].float()
         rel, ok = _close(dw[e], ref, tol=5e-3)
         assert ok, (e, rel)
+    # the same product with 256-wide tiles (N = 512)
+    x2 = torch.zeros(rows, 512, dtype=torch.float16, device="cuda")
+    for e, c in enumerate(counts):
+        if c:
+            x2[offs[e]:offs[e] + c] = _rand(c, 512, seed=50 + e)
+    for bn in (128, 256):
+        dw2 = torch.zeros(ne, E, 512, dtype=torch.float32, device="cuda")
+        G.gemm_grouped_reduce(y16, x2, seg, ne, dw2, accumulate=False, block_n=bn)
+        L.check_status(what="grouped reduce bn %d" % bn)
+        for e, c in enumerate(counts):
+            ref = y16[offs[e]:offs[e] + c].float().t() @ x2[offs[e]:offs[e] + c].float()
+            rel, ok = _close(dw2[e], ref, tol=5e-3)
+            assert ok, (bn, e, rel)
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(512, 768, 32000, 16), (100, 128, 600, 4)])
@@ -173,4 +186,19 @@ def test_large_gemm_matches():
     out = G.gemm(a, b, out_dtype=torch.float32)
     L.check_status(what="gemm")
     rel, ok = _close(out, a.float() @ b.float().t(), tol=5e-3)
+    assert ok, rel
+
+
+@pytest.mark.parametrize("M,N,K", [(768, 768, 8192), (1280, 768, 8192), (256, 128, 4096), (2560, 768, 2048), (128, 128, 1000)])
+def test_weight_gradient_split_over_tokens(M, N, K):
+    """gemm_wgrad splits the token dimension when the output has few tiles; either way grad += a^T b."""
+    G, L = _ops()
+    a = _rand(K, M, seed=70) * 0.2
+    b = _rand(K, N, seed=71) * 0.2
+    grad = torch.full((M, N), 0.5, dtype=torch.float32, device="cuda")
+    G.gemm_wgrad(a, b, grad)
+    G.gemm_wgrad(a, b, grad)                  # accumulates, and the cached plan is reused
+    L.check_status(what="wgrad")
+    ref = 0.5 + 2.0 * (a.float().t() @ b.float())
+    rel, ok = _close(grad, ref, tol=5e-3)
     assert ok, rel
