@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const uint8_t* __restr
                                                          const XT* __restrict__ x, long long ldx, int B,
                                                          void* __restrict__ out, long long ldo, int out_f32,
                                                          const float* __restrict__ addend, long long ld_add) {
+  pdl_wait();
   __shared__ float sm[GV_WARPS];
   const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
   const int row = blockIdx.x * (GV_WARPS / KS) + ric;
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(GV_THREADS) expert_swiglu_kernel(const uint8_t
                                                                   long long row_bytes, int ne, int E, int d,
                                                                   const XT* __restrict__ x, const int* __restrict__ idx,
                                                                   int top_k, int slots, XT* __restrict__ act) {
+  pdl_wait();
   __shared__ float sm[2 * GV_WARPS];
   const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
   const int j = blockIdx.x * (GV_WARPS / KS) + ric;
@@ -169,6 +171,7 @@ __global__ void __launch_bounds__(GV_THREADS) expert_down_kernel(const uint8_t* 
                                                                 int E, const XT* __restrict__ act, const int* __restrict__ idx,
                                                                 const float* __restrict__ w, int top_k, int slots,
                                                                 const float* __restrict__ resid, float* __restrict__ out) {
+  pdl_wait();
   __shared__ float sm[GV_WARPS];
   const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
   const int r = blockIdx.x * (GV_WARPS / KS) + ric;
@@ -198,6 +201,7 @@ template <typename XT>
 __global__ void __launch_bounds__(256) decode_route_kernel(const XT* __restrict__ x, const float* __restrict__ rw,
                                                           const float* __restrict__ bias, int d, int ne, int top_k,
                                                           int* __restrict__ idx, float* __restrict__ wout) {
+  pdl_wait();
   __shared__ float lg[64];
   const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const XT* xr = x + (long long)b * d;
@@ -248,6 +252,7 @@ template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ k, long long ld_k, const T* __restrict__ v, long long ld_v,
                                  T* __restrict__ cK, T* __restrict__ cV, int* __restrict__ slot_pos,
                                  const gb_seq_state* __restrict__ st, int cap, int pinned, int kv_dim) {
+  pdl_wait();
   const int b = blockIdx.x;
   const gb_seq_state s = st[b];
   const int slot = s.cache_len < cap ? s.cache_len : pinned + s.ring_start;
@@ -261,6 +266,7 @@ __global__ void kv_append_kernel(const T* __restrict__ k, long long ld_k, const 
 }
 
 __global__ void decode_advance_kernel(gb_seq_state* __restrict__ st, int* __restrict__ pos_out, int B, int cap, int pinned) {
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   gb_seq_state s = st[b];
@@ -279,7 +285,9 @@ template <typename T, int HD, int G>
 __global__ void __launch_bounds__(128) decode_attn_kernel(const T* __restrict__ q, long long ld_q, const T* __restrict__ cK,
                                                          const T* __restrict__ cV, const int* __restrict__ slot_pos,
                                                          const gb_seq_state* __restrict__ st, float* __restrict__ scratch,
-                                                         int splits, int H, int KV, int cap, int window, float scale) {
+                                                         int splits, int H, int KV, int cap, int window, float scale,
+                                                         int* __restrict__ ticket, T* __restrict__ out, long long ld_o) {
+  pdl_wait();
   constexpr int EPL = HD / 32;   // elements per lane
   const int b = blockIdx.x / KV, kvh = blockIdx.x % KV, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -346,10 +354,39 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const T* __restrict__ 
     dst[2 + c] = oo;
     if (c == 0) { dst[0] = mm; dst[1] = ll; }
   }
+  if (ticket == nullptr) return;            // the splits are merged by decode_attn_merge_kernel
+  // The last split of this (sequence, kv head) to get here merges all of them, in split order: same result whoever
+  // it is.  The ticket returns to zero for the next launch.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&ticket[blockIdx.x], 1);
+    s_last = (t == splits - 1);
+    if (s_last) ticket[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int t = threadIdx.x; t < G * HD; t += 128) {
+    const int g = t / HD, c = t % HD;
+    const float* base = scratch + ((long long)b * H + kvh * G + g) * splits * (HD + 2);
+    float mm = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) mm = fmaxf(mm, __ldcg(base + sp * (HD + 2)));
+    float ll = 0.f, oo = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float ms = __ldcg(base + sp * (HD + 2));
+      const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);
+      ll += __ldcg(base + sp * (HD + 2) + 1) * f;
+      oo += __ldcg(base + sp * (HD + 2) + 2 + c) * f;
+    }
+    out[b * ld_o + (long long)(kvh * G + g) * HD + c] = Cvt<T>::from_f(ll > 0.f ? oo / ll : 0.f);
+  }
 }
 
 template <typename T, int HD>
 __global__ void decode_attn_merge_kernel(const float* __restrict__ scratch, int splits, T* __restrict__ out, long long ld_o, int H) {
+  pdl_wait();
   const int b = blockIdx.x / H, h = blockIdx.x % H, c = threadIdx.x;
   const float* base = scratch + ((long long)b * H + h) * splits * (HD + 2);
   float mm = -INFINITY;
@@ -362,6 +399,219 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ scratch, int 
     oo += base[s * (HD + 2) + 2 + c] * f;
   }
   out[b * ld_o + (long long)h * HD + c] = Cvt<T>::from_f(ll > 0.f ? oo / ll : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------- fused decode step
+// Fewer, fatter kernels for the token step: at batch 1 every kernel costs a few microseconds however little it does.
+//   gemv_norm:            RMSNorm of the fp32 residual inside the GEMV (every block normalises the row it needs)
+//   swiglu_norm_route:    RMSNorm + router (soft-max, bias-steered top-k) + gate/up rows of the selected experts
+//   qk_rope_append:       QK-norm + RoPE; k heads land in the cache slot, v heads are copied beside them
+//   decode_attn (fused):  the last split to finish merges the partial results (ticket), no merge launch
+// Rounding points are those of the separate kernels (normalised activations pass through 16 bits), so both routes
+// give the same numbers.
+
+// Row b of x (fp32, d values) normalised into xs (16-bit) by one warp, as rmsnorm_fwd_kernel does it.
+template <typename XT>
+__device__ __forceinline__ void norm_row_to_smem(const float* __restrict__ x, const float* __restrict__ w, XT* __restrict__ xs,
+                                                 int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const float4* xr = reinterpret_cast<const float4*>(x);
+  float ss = 0.f;
+  for (int i = lane; i < d / 4; i += 32) {
+    const float4 v = xr[i];
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  float inv = rsqrtf(ss / (float)d + eps);
+  if (!isfinite(inv)) inv = 0.f;
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  for (int i = lane; i < d / 4; i += 32) {
+    const float4 v = xr[i], g = wr[i];
+    uint2 o;
+    o.x = Cvt<XT>::pack2(v.x * inv * g.x, v.y * inv * g.y);
+    o.y = Cvt<XT>::pack2(v.z * inv * g.z, v.w * inv * g.w);
+    *reinterpret_cast<uint2*>(xs + 4 * i) = o;
+  }
+}
+
+template <int FMT, int NB, int KS, typename XT>
+__global__ void __launch_bounds__(GV_THREADS) gemv_norm_kernel(const uint8_t* __restrict__ W, long long row_bytes, int N, int K,
+                                                              const float* __restrict__ x32, long long ldx32,
+                                                              const float* __restrict__ norm_w, float eps, int B,
+                                                              void* __restrict__ out, long long ldo, int out_f32) {
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t gv_dyn[];
+  XT* xs = reinterpret_cast<XT*>(gv_dyn);                 // [B][K]
+  __shared__ float sm[GV_WARPS];
+  const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
+  for (int b = warp; b < B; b += GV_WARPS) norm_row_to_smem<XT>(x32 + b * ldx32, norm_w, xs + (long long)b * K, K, eps);
+  __syncthreads();
+  const int row = blockIdx.x * (GV_WARPS / KS) + ric;
+  const bool live = row < N;
+  const uint8_t* wrow = W + (size_t)(live ? row : 0) * row_bytes;
+  for (int b0 = 0; b0 < B; b0 += NB) {
+    float acc[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) acc[j] = 0.f;
+    const int nb = min(NB, B - b0);
+    if (live) row_partial<FMT, NB, KS, XT>(wrow, K, xs + (long long)b0 * K, K, nb, ks, acc);
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const float v0 = row_finish<KS>(acc[j], sm, ric, ks);
+      if (live && j < nb && ks == 0 && (threadIdx.x & 31) == 0) {
+        if (out_f32) reinterpret_cast<float*>(out)[(long long)(b0 + j) * ldo + row] = v0;
+        else reinterpret_cast<XT*>(out)[(long long)(b0 + j) * ldo + row] = Cvt<XT>::from_f(v0);
+      }
+    }
+  }
+}
+
+// Router of one token from its normalised activations in shared memory (rules of decode_route_kernel).  All threads
+// of the block call it; the selection is left in esel / wsel (shared).
+template <typename XT>
+__device__ __forceinline__ void route_in_block(const XT* __restrict__ xs, const float* __restrict__ rw, const float* __restrict__ bias,
+                                               int d, int ne, int top_k, float* __restrict__ lg, int* __restrict__ esel,
+                                               float* __restrict__ wsel) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < ne; e += GV_WARPS) {
+    const float* wr = rw + (size_t)e * d;
+    float s = 0.f;
+    for (int i = lane * 2; i < d; i += 64) {
+      const float2 xv = Cvt<XT>::unpack2(*reinterpret_cast<const uint32_t*>(xs + i));
+      const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+      s += xv.x * wv.x + xv.y * wv.y;
+    }
+    s = warp_sum(s);
+    if (lane == 0) lg[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mx = -INFINITY;
+    for (int e = 0; e < ne; ++e) mx = fmaxf(mx, lg[e]);
+    float sum = 0.f;
+    for (int e = 0; e < ne; ++e) { lg[e] = __expf(lg[e] - mx); sum += lg[e]; }
+    const float inv = 1.f / sum;
+    unsigned long long taken = 0ull;
+    float psel[8], psum = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      float bv = -INFINITY;
+      int bi = 0;
+      for (int e = 0; e < ne; ++e) {
+        if (taken >> e & 1ull) continue;
+        const float sc = lg[e] * inv + (bias ? bias[e] : 0.f);
+        if (sc > bv) { bv = sc; bi = e; }
+      }
+      taken |= 1ull << bi;
+      esel[k] = bi;
+      psel[k] = lg[bi] * inv;
+      psum += psel[k];
+    }
+    const float invs = psum > 1e-8f ? 1.f / psum : 0.f;
+    for (int k = 0; k < top_k; ++k) wsel[k] = psel[k] * invs;
+  }
+  __syncthreads();
+}
+
+// grid (ceil(E / rows per block), B * slots).  rw == nullptr: dense feed-forward (one "expert" 0, no routing).
+template <int FMT, int KS, typename XT>
+__global__ void __launch_bounds__(GV_THREADS) swiglu_norm_route_kernel(
+    const uint8_t* __restrict__ Wg, const uint8_t* __restrict__ Wu, long long row_bytes, int ne, int E, int d,
+    const float* __restrict__ x32, const float* __restrict__ norm_w, float eps, const float* __restrict__ rw,
+    const float* __restrict__ bias, int top_k, int slots, int* __restrict__ idx_out, float* __restrict__ w_out,
+    XT* __restrict__ act) {
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t gv_dyn[];
+  XT* xs = reinterpret_cast<XT*>(gv_dyn);                 // [d]
+  __shared__ float sm[2 * GV_WARPS];
+  __shared__ float lg[64];
+  __shared__ int esel[8];
+  __shared__ float wsel[8];
+  const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
+  const int b = blockIdx.y / slots, slot = blockIdx.y % slots;
+  if (warp == 0) norm_row_to_smem<XT>(x32 + (long long)b * d, norm_w, xs, d, eps);
+  __syncthreads();
+  int e = 0;
+  if (rw) {
+    route_in_block<XT>(xs, rw, bias, d, ne, top_k, lg, esel, wsel);
+    e = slot < top_k ? esel[slot] : ne;
+    if (blockIdx.x == 0 && slot == 0 && threadIdx.x < top_k) {
+      idx_out[b * top_k + threadIdx.x] = esel[threadIdx.x];
+      w_out[b * top_k + threadIdx.x] = wsel[threadIdx.x];
+    }
+  }
+  const int j = blockIdx.x * (GV_WARPS / KS) + ric;
+  const bool live = j < E && e >= 0 && e <= ne;
+  float g[1] = {0.f}, u[1] = {0.f};
+  if (live) {
+    const size_t r = (size_t)e * E + j;
+    row_partial<FMT, 1, KS, XT>(Wg + r * row_bytes, d, xs, d, 1, ks, g);
+    row_partial<FMT, 1, KS, XT>(Wu + r * row_bytes, d, xs, d, 1, ks, u);
+  }
+  const float gs = row_finish<KS>(g[0], sm, ric, ks);
+  const float us = row_finish<KS>(u[0], sm + GV_WARPS, ric, ks);
+  if (live && ks == 0 && (threadIdx.x & 31) == 0)
+    act[((long long)b * slots + slot) * E + j] = Cvt<XT>::from_f(gs / (1.f + __expf(-gs)) * us);
+}
+
+// One warp per (sequence, head) over the q, k and v heads of the fused projection.  q heads: norm + rotation into
+// `q_out`.  k heads: norm + rotation straight into the cache slot of the step.  v heads: copied into the cache.
+template <typename T, int HD>
+__global__ void qk_rope_append_kernel(const T* __restrict__ qkv, long long ld_in, T* __restrict__ q_out, long long ld_q,
+                                      const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cs,
+                                      const int* __restrict__ pos, T* __restrict__ cK, T* __restrict__ cV,
+                                      int* __restrict__ slot_pos, const gb_seq_state* __restrict__ st, int B, int H, int KV,
+                                      int cap, int pinned, float eps, int rope_type) {
+  pdl_wait();
+  constexpr int PAIRS = HD / 2;
+  constexpr int PPL = (PAIRS + 31) / 32;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = H + 2 * KV;
+  if (gw >= B * heads) return;
+  const int b = gw / heads, h = gw - b * heads;
+  const gb_seq_state s = st[b];
+  const int slot = s.cache_len < cap ? s.cache_len : pinned + s.ring_start;
+  const long long kvd = (long long)KV * HD;
+  const T* src = qkv + b * ld_in + (long long)h * HD;
+  if (h >= H + KV) {                                         // v head: plain copy into the cache
+    T* dv = cV + ((long long)b * cap + slot) * kvd + (long long)(h - H - KV) * HD;
+    for (int i = lane * 2; i < HD; i += 64) *reinterpret_cast<uint32_t*>(dv + i) = *reinterpret_cast<const uint32_t*>(src + i);
+    return;
+  }
+  T* dst = h < H ? q_out + b * ld_q + (long long)h * HD : cK + ((long long)b * cap + slot) * kvd + (long long)(h - H) * HD;
+  if (h == H && lane == 0) slot_pos[(long long)b * cap + slot] = s.abs_pos;
+  const float* w = (h < H) ? qw : kw;
+  float a[PPL], c2[PPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PPL; ++k) {
+    const int p = lane + 32 * k;
+    if (p < PAIRS) {
+      const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+      a[k] = Cvt<T>::to_f(src[i0]);
+      c2[k] = Cvt<T>::to_f(src[i1]);
+      ss += a[k] * a[k] + c2[k] * c2[k];
+    }
+  }
+  float inv = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)HD + eps);
+    if (!isfinite(inv)) inv = 0.f;
+  }
+  const float* csr = cs + (size_t)pos[b] * HD;
+#pragma unroll
+  for (int k = 0; k < PPL; ++k) {
+    const int p = lane + 32 * k;
+    if (p < PAIRS) {
+      const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + PAIRS;
+      float x0 = a[k], x1 = c2[k];
+      if (w) { x0 *= inv * w[i0]; x1 *= inv * w[i1]; }
+      const float c = csr[p], sn = csr[PAIRS + p];
+      dst[i0] = Cvt<T>::from_f(x0 * c - x1 * sn);
+      dst[i1] = Cvt<T>::from_f(x0 * sn + x1 * c);
+    }
+  }
 }
 
 }  // namespace gb
@@ -397,8 +647,8 @@ extern "C" int gb_gemv(const void* W, int fmt, int N, int K, const void* x16, in
   const bool split = N <= 8192;   // few rows: spread each over four warps (latency bound); many rows fill the GPU anyway
   const uint8_t* w = static_cast<const uint8_t*>(W);
 #define GEMV_GO(F, NB, KS, XT)                                                                                     \
-  gemv_kernel<F, NB, KS, XT><<<dim3((N + GV_WARPS / KS - 1) / (GV_WARPS / KS)), GV_THREADS, 0, st>>>(                 \
-      w, rb, N, K, (const XT*)x16, ldx, B, out, ldo, out_f32, addend, ld_add)
+  GB_PDL_LAUNCH((gemv_kernel<F, NB, KS, XT>), dim3((N + GV_WARPS / KS - 1) / (GV_WARPS / KS)), dim3(GV_THREADS), st, \
+                w, rb, N, K, (const XT*)x16, (long long)ldx, B, out, (long long)ldo, out_f32, addend, (long long)ld_add)
 #define CALL(F)                                                                        \
   if (is_bf16) {                                                                       \
     if (B == 1 && split) GEMV_GO(F, 1, 4, __nv_bfloat16);                              \
@@ -423,8 +673,8 @@ extern "C" int gb_gemv_expert_swiglu(const void* Wg, const void* Wu, int fmt, in
   const uint8_t *g = static_cast<const uint8_t*>(Wg), *u = static_cast<const uint8_t*>(Wu);
   const bool split = B * slots <= 64;
 #define SW_GO(F, KS, XT)                                                                                              \
-  expert_swiglu_kernel<F, KS, XT><<<dim3((E + GV_WARPS / KS - 1) / (GV_WARPS / KS), B * slots), GV_THREADS, 0, st>>>( \
-      g, u, rb, ne, E, d, (const XT*)x16, idx, top_k, slots, (XT*)act16)
+  GB_PDL_LAUNCH((expert_swiglu_kernel<F, KS, XT>), dim3((E + GV_WARPS / KS - 1) / (GV_WARPS / KS), B * slots),       \
+                dim3(GV_THREADS), st, g, u, rb, ne, E, d, (const XT*)x16, idx, top_k, slots, (XT*)act16)
 #define CALL(F)                                                                                   \
   if (is_bf16) { if (split) SW_GO(F, 4, __nv_bfloat16); else SW_GO(F, 1, __nv_bfloat16); }        \
   else { if (split) SW_GO(F, 4, __half); else SW_GO(F, 1, __half); }
@@ -442,8 +692,8 @@ extern "C" int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E
   const uint8_t* wd = static_cast<const uint8_t*>(Wd);
   const bool split = B <= 16;
 #define DN_GO(F, KS, XT)                                                                                    \
-  expert_down_kernel<F, KS, XT><<<dim3((d + GV_WARPS / KS - 1) / (GV_WARPS / KS), B), GV_THREADS, 0, st>>>( \
-      wd, rb, ne, d, E, (const XT*)act16, idx, w, top_k, slots, resid, out)
+  GB_PDL_LAUNCH((expert_down_kernel<F, KS, XT>), dim3((d + GV_WARPS / KS - 1) / (GV_WARPS / KS), B), dim3(GV_THREADS), st, \
+                wd, rb, ne, d, E, (const XT*)act16, idx, w, top_k, slots, resid, out)
 #define CALL(F)                                                                                   \
   if (is_bf16) { if (split) DN_GO(F, 4, __nv_bfloat16); else DN_GO(F, 1, __nv_bfloat16); }        \
   else { if (split) DN_GO(F, 4, __half); else DN_GO(F, 1, __half); }
@@ -455,8 +705,8 @@ extern "C" int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E
 extern "C" int gb_decode_route(const void* x16, const float* router_w, const float* bias, int B, int d, int ne, int top_k,
                                int* idx, float* w, int is_bf16, cudaStream_t st) {
   if (!x16 || !router_w || !idx || !w || B <= 0 || ne <= 0 || ne > 64 || top_k <= 0 || top_k > 8 || top_k > ne || d % 2) return -1;
-  if (is_bf16) decode_route_kernel<__nv_bfloat16><<<B, 256, 0, st>>>((const __nv_bfloat16*)x16, router_w, bias, d, ne, top_k, idx, w);
-  else decode_route_kernel<__half><<<B, 256, 0, st>>>((const __half*)x16, router_w, bias, d, ne, top_k, idx, w);
+  if (is_bf16) GB_PDL_LAUNCH(decode_route_kernel<__nv_bfloat16>, dim3(B), dim3(256), st, (const __nv_bfloat16*)x16, router_w, bias, d, ne, top_k, idx, w);
+  else GB_PDL_LAUNCH(decode_route_kernel<__half>, dim3(B), dim3(256), st, (const __half*)x16, router_w, bias, d, ne, top_k, idx, w);
   return gb_launch_rc();
 }
 
@@ -465,26 +715,26 @@ extern "C" int gb_kv_append(const void* k16, long long ld_k, const void* v16, lo
   if (!k16 || !v16 || !cacheK || !cacheV || !slot_pos || !state || B <= 0 || cap <= pinned || kv_dim % 8 || ld_k % 8 || ld_v % 8)
     return -1;
   // 16-bit elements of either type are copied as raw bits
-  kv_append_kernel<__half><<<B, 128, 0, st>>>((const __half*)k16, ld_k, (const __half*)v16, ld_v, (__half*)cacheK,
+  GB_PDL_LAUNCH(kv_append_kernel<__half>, dim3(B), dim3(128), st, (const __half*)k16, ld_k, (const __half*)v16, ld_v, (__half*)cacheK,
                                               (__half*)cacheV, slot_pos, state, cap, pinned, kv_dim);
   return gb_launch_rc();
 }
 
 extern "C" int gb_decode_advance(gb_seq_state* state, int* pos_out, int B, int cap, int pinned, cudaStream_t st) {
   if (!state || !pos_out || B <= 0) return -1;
-  decode_advance_kernel<<<(B + 63) / 64, 64, 0, st>>>(state, pos_out, B, cap, pinned);
+  GB_PDL_LAUNCH(decode_advance_kernel, dim3((B + 63) / 64), dim3(64), st, state, pos_out, B, cap, pinned);
   return gb_launch_rc();
 }
 
 template <typename T, int HD>
 static int launch_decode_attn(const void* q, long long ld_q, const void* cK, const void* cV, const int* slot_pos,
                               const gb_seq_state* state, void* out, long long ld_o, float* scratch, int splits, int B, int H,
-                              int KV, int cap, int window, float scale, cudaStream_t st) {
+                              int KV, int cap, int window, float scale, int* ticket, cudaStream_t st) {
   const int G = H / KV;
   const dim3 grid(B * KV, splits);
 #define ATT(GG)                                                                                                   \
-  decode_attn_kernel<T, HD, GG><<<grid, 128, 0, st>>>((const T*)q, ld_q, (const T*)cK, (const T*)cV, slot_pos, state, \
-                                                      scratch, splits, H, KV, cap, window, scale)
+  GB_PDL_LAUNCH((decode_attn_kernel<T, HD, GG>), grid, dim3(128), st, (const T*)q, ld_q, (const T*)cK, (const T*)cV, slot_pos, \
+                state, scratch, splits, H, KV, cap, window, scale, ticket, (T*)out, ld_o)
   switch (G) {
     case 1: ATT(1); break;
     case 2: ATT(2); break;
@@ -495,19 +745,118 @@ static int launch_decode_attn(const void* q, long long ld_q, const void* cK, con
     default: return -3;
   }
 #undef ATT
-  decode_attn_merge_kernel<T, HD><<<B * H, HD, 0, st>>>(scratch, splits, (T*)out, ld_o, H);
+  if (!ticket) GB_PDL_LAUNCH((decode_attn_merge_kernel<T, HD>), dim3(B * H), dim3(HD), st, (const float*)scratch, splits, (T*)out, ld_o, H);
   return gb_launch_rc();
 }
 
-extern "C" int gb_decode_attn(const void* q16, long long ld_q, const void* cacheK, const void* cacheV, const int* slot_pos,
-                              const gb_seq_state* state, void* out16, long long ld_o, float* scratch, int splits, int B, int H,
-                              int KV, int hd, int cap, int window, float scale, int is_bf16, cudaStream_t st) {
+static int decode_attn_any(const void* q16, long long ld_q, const void* cacheK, const void* cacheV, const int* slot_pos,
+                           const gb_seq_state* state, void* out16, long long ld_o, float* scratch, int splits, int B, int H,
+                           int KV, int hd, int cap, int window, float scale, int is_bf16, int* ticket, cudaStream_t st) {
   if (!q16 || !cacheK || !cacheV || !slot_pos || !state || !out16 || !scratch || splits < 1 || B <= 0 || KV <= 0 || H % KV)
     return -1;
-#define GO(T, HD) return launch_decode_attn<T, HD>(q16, ld_q, cacheK, cacheV, slot_pos, state, out16, ld_o, scratch, splits, B, H, KV, cap, window, scale, st)
+#define GO(T, HD) return launch_decode_attn<T, HD>(q16, ld_q, cacheK, cacheV, slot_pos, state, out16, ld_o, scratch, splits, B, H, KV, cap, window, scale, ticket, st)
   if (hd == 64) { if (is_bf16) GO(__nv_bfloat16, 64); else GO(__half, 64); }
   if (hd == 128) { if (is_bf16) GO(__nv_bfloat16, 128); else GO(__half, 128); }
   if (hd == 32) { if (is_bf16) GO(__nv_bfloat16, 32); else GO(__half, 32); }
 #undef GO
   return -2;
+}
+
+extern "C" int gb_decode_attn(const void* q16, long long ld_q, const void* cacheK, const void* cacheV, const int* slot_pos,
+                              const gb_seq_state* state, void* out16, long long ld_o, float* scratch, int splits, int B, int H,
+                              int KV, int hd, int cap, int window, float scale, int is_bf16, cudaStream_t st) {
+  return decode_attn_any(q16, ld_q, cacheK, cacheV, slot_pos, state, out16, ld_o, scratch, splits, B, H, KV, hd, cap, window,
+                         scale, is_bf16, nullptr, st);
+}
+
+// The same with the merge of the splits done by the last block to finish; `ticket` is B*KV ints, zero before the first call.
+extern "C" int gb_decode_attn_fused(const void* q16, long long ld_q, const void* cacheK, const void* cacheV, const int* slot_pos,
+                                    const gb_seq_state* state, void* out16, long long ld_o, float* scratch, int splits, int B,
+                                    int H, int KV, int hd, int cap, int window, float scale, int is_bf16, int* ticket,
+                                    cudaStream_t st) {
+  if (!ticket) return -1;
+  return decode_attn_any(q16, ld_q, cacheK, cacheV, slot_pos, state, out16, ld_o, scratch, splits, B, H, KV, hd, cap, window,
+                         scale, is_bf16, ticket, st);
+}
+
+// RMSNorm of x32 [B, K] (fp32) fused into out = W @ norm(x32).  Shared memory holds the normalised rows: B*K*2 bytes.
+extern "C" int gb_gemv_norm(const void* W, int fmt, int N, int K, const float* x32, int ldx32, const float* norm_w, float eps,
+                            int B, void* out, int ldo, int out_f32, int is_bf16, cudaStream_t st) {
+  const long long rb = gb_wfmt_row_bytes(fmt, K);
+  if (!W || !x32 || !norm_w || !out || N <= 0 || B <= 0 || B > 32 || rb < 0 || (K % 8) || (ldx32 % 4)) return -1;
+  const size_t smem = (size_t)B * K * 2;
+  if (smem > 40 * 1024) return -2;                          // the caller takes the two-kernel route
+  const bool split = N <= 8192;
+  const uint8_t* w = static_cast<const uint8_t*>(W);
+#define GEMVN_GO(F, NB, KS, XT)                                                                                      \
+  do {                                                                                                               \
+    cudaLaunchAttribute gb_attr_;                                                                                    \
+    cudaLaunchConfig_t gb_cfg_ = gb_pdl_config(dim3((N + GV_WARPS / KS - 1) / (GV_WARPS / KS)), dim3(GV_THREADS), smem, st, &gb_attr_); \
+    (void)cudaLaunchKernelEx(&gb_cfg_, (gemv_norm_kernel<F, NB, KS, XT>), w, rb, N, K, x32, (long long)ldx32, norm_w, eps, B, \
+                             out, (long long)ldo, out_f32);                                                          \
+  } while (0)
+#define CALL(F)                                                                         \
+  if (is_bf16) {                                                                        \
+    if (B == 1 && split) GEMVN_GO(F, 1, 4, __nv_bfloat16);                              \
+    else if (B == 1) GEMVN_GO(F, 1, 1, __nv_bfloat16);                                  \
+    else GEMVN_GO(F, 4, 1, __nv_bfloat16);                                              \
+  } else {                                                                              \
+    if (B == 1 && split) GEMVN_GO(F, 1, 4, __half);                                     \
+    else if (B == 1) GEMVN_GO(F, 1, 1, __half);                                         \
+    else GEMVN_GO(F, 4, 1, __half);                                                     \
+  }
+  GB_FMT_SWITCH(fmt, CALL)
+#undef CALL
+#undef GEMVN_GO
+  return gb_launch_rc();
+}
+
+// RMSNorm + router + gate/up of the selected experts.  router_w == nullptr: dense feed-forward (weights hold one block).
+extern "C" int gb_swiglu_norm_route(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const float* x32,
+                                    const float* norm_w, float eps, const float* router_w, const float* bias, int B, int top_k,
+                                    int shared, int* idx_out, float* w_out, void* act16, int is_bf16, cudaStream_t st) {
+  const long long rb = gb_wfmt_row_bytes(fmt, d);
+  if (!Wg || !Wu || !x32 || !norm_w || !act16 || rb < 0 || B <= 0 || top_k <= 0 || top_k > 8 || (d % 8)) return -1;
+  if (router_w && (!idx_out || !w_out || ne <= 0 || ne > 64 || top_k > ne)) return -1;
+  const size_t smem = (size_t)d * 2;
+  if (smem > 40 * 1024) return -2;
+  const int slots = top_k + (shared ? 1 : 0);
+  const uint8_t *g = static_cast<const uint8_t*>(Wg), *u = static_cast<const uint8_t*>(Wu);
+  const bool split = B * slots <= 64;
+#define SWN_GO(F, KS, XT)                                                                                            \
+  do {                                                                                                               \
+    cudaLaunchAttribute gb_attr_;                                                                                    \
+    cudaLaunchConfig_t gb_cfg_ = gb_pdl_config(dim3((E + GV_WARPS / KS - 1) / (GV_WARPS / KS), B * slots), dim3(GV_THREADS), smem, st, &gb_attr_); \
+    (void)cudaLaunchKernelEx(&gb_cfg_, (swiglu_norm_route_kernel<F, KS, XT>), g, u, rb, ne, E, d, x32, norm_w, eps, router_w, \
+                             bias, top_k, slots, idx_out, w_out, (XT*)act16);                                        \
+  } while (0)
+#define CALL(F)                                                                                     \
+  if (is_bf16) { if (split) SWN_GO(F, 4, __nv_bfloat16); else SWN_GO(F, 1, __nv_bfloat16); }        \
+  else { if (split) SWN_GO(F, 4, __half); else SWN_GO(F, 1, __half); }
+  GB_FMT_SWITCH(fmt, CALL)
+#undef CALL
+#undef SWN_GO
+  return gb_launch_rc();
+}
+
+extern "C" int gb_qk_rope_append(const void* qkv, long long ld_in, void* q_out, long long ld_q, const float* qw, const float* kw,
+                                 const float* cos_sin, const int* pos, void* cacheK, void* cacheV, int* slot_pos,
+                                 const gb_seq_state* state, int B, int H, int KV, int hd, int cap, int pinned, float eps,
+                                 int rope_type, int is_bf16, cudaStream_t st) {
+  if (!qkv || !q_out || !cos_sin || !pos || !cacheK || !cacheV || !slot_pos || !state || B <= 0 || H <= 0 || KV <= 0 ||
+      cap <= pinned || (hd % 2) || (ld_in % 2))
+    return -1;
+  const int items = B * (H + 2 * KV);
+  const int wpb = 8;
+  const dim3 grid((items + wpb - 1) / wpb);
+#define QKA(T, HD)                                                                                                       \
+  GB_PDL_LAUNCH((qk_rope_append_kernel<T, HD>), grid, dim3(wpb * 32), st, (const T*)qkv, ld_in, (T*)q_out, ld_q, qw, kw, cos_sin, \
+                pos, (T*)cacheK, (T*)cacheV, slot_pos, state, B, H, KV, cap, pinned, eps, rope_type)
+  if (is_bf16) {
+    switch (hd) { case 32: QKA(__nv_bfloat16, 32); break; case 64: QKA(__nv_bfloat16, 64); break; case 128: QKA(__nv_bfloat16, 128); break; default: return -2; }
+  } else {
+    switch (hd) { case 32: QKA(__half, 32); break; case 64: QKA(__half, 64); break; case 128: QKA(__half, 128); break; default: return -2; }
+  }
+#undef QKA
+  return gb_launch_rc();
 }

@@ -27,6 +27,7 @@ __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
 // ------------------------------------------------------------------------------------------ embedding
 __global__ void embed_fwd_kernel(const int* __restrict__ ids, const float* __restrict__ table, float* __restrict__ out,
                                  int n_tok, int d, int vocab) {
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= n_tok) return;
   int id = ids[t];
@@ -53,6 +54,7 @@ __global__ void embed_bwd_kernel(const int* __restrict__ ids, const float* __res
 template <typename T>
 __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
                                    float* __restrict__ rrms, int rows, int d, float eps) {
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -165,6 +167,7 @@ __global__ void qk_norm_rope_fwd_kernel(const T* __restrict__ qkv, int ld_in, T*
                                         const float* __restrict__ qw, const float* __restrict__ kw,
                                         const float* __restrict__ cs, const int* __restrict__ pos, int n_tok, int H,
                                         int KV, float eps, int rope_type) {
+  pdl_wait();
   constexpr int PAIRS = HD / 2;
   constexpr int PPL = (PAIRS + 31) / 32;  // pairs per lane
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -316,7 +319,7 @@ using namespace gb;
 
 extern "C" int gb_embed_fwd(const int* ids, const float* table, float* out, int n_tok, int d, int vocab, cudaStream_t st) {
   if (d % 4) return -1;
-  embed_fwd_kernel<<<n_tok, 128, 0, st>>>(ids, table, out, n_tok, d, vocab);
+  GB_PDL_LAUNCH(embed_fwd_kernel, dim3(n_tok), dim3(128), st, ids, table, out, n_tok, d, vocab);
   return GB_LAUNCH_OK();
 }
 extern "C" int gb_embed_bwd(const int* ids, const float* dx, float* dtable, int n_tok, int d, int vocab, cudaStream_t st) {
@@ -329,8 +332,8 @@ extern "C" int gb_rmsnorm_fwd(const float* x, const float* w, void* y, float* rr
   if (d % 4) return -1;
   const int wpb = 8;
   dim3 grid((rows + wpb - 1) / wpb);
-  if (is_bf16) rmsnorm_fwd_kernel<__nv_bfloat16><<<grid, wpb * 32, 0, st>>>(x, w, (__nv_bfloat16*)y, rrms, rows, d, eps);
-  else rmsnorm_fwd_kernel<__half><<<grid, wpb * 32, 0, st>>>(x, w, (__half*)y, rrms, rows, d, eps);
+  if (is_bf16) GB_PDL_LAUNCH(rmsnorm_fwd_kernel<__nv_bfloat16>, dim3(grid), dim3(wpb * 32), st, x, w, (__nv_bfloat16*)y, rrms, rows, d, eps);
+  else GB_PDL_LAUNCH(rmsnorm_fwd_kernel<__half>, dim3(grid), dim3(wpb * 32), st, x, w, (__half*)y, rrms, rows, d, eps);
   return GB_LAUNCH_OK();
 }
 
@@ -376,7 +379,7 @@ static int qk_fwd_t(const void* qkv, int ld_in, void* out, int ld_out, const flo
   const int wpb = 8;
   dim3 grid((items + wpb - 1) / wpb);
 #define GB_QK_FWD(HD) \
-  qk_norm_rope_fwd_kernel<T, HD><<<grid, wpb * 32, 0, st>>>((const T*)qkv, ld_in, (T*)out, ld_out, qw, kw, cs, pos, n_tok, H, KV, eps, rope_type)
+  GB_PDL_LAUNCH((qk_norm_rope_fwd_kernel<T, HD>), dim3(grid), dim3(wpb * 32), st, (const T*)qkv, ld_in, (T*)out, ld_out, qw, kw, cs, pos, n_tok, H, KV, eps, rope_type)
   switch (hd) {
     case 32: GB_QK_FWD(32); break;
     case 64: GB_QK_FWD(64); break;

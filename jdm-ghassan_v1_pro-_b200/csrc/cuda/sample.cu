@@ -21,6 +21,7 @@ __device__ __forceinline__ unsigned int order_key(float f) {
 }
 
 __global__ void __launch_bounds__(SM_THREADS) sample_kernel(gb_sample_args a) {
+  pdl_wait();
   __shared__ unsigned int hist[256];
   __shared__ unsigned int s_prefix, s_need, s_count;
   __shared__ float cand_v[MAX_CAND];
@@ -202,7 +203,10 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(gb_sample_args a) {
   }
 }
 
-__global__ void step_inc_kernel(int* step) { step[0] += 1; }
+__global__ void step_inc_kernel(int* step) {
+  pdl_wait();
+  step[0] += 1;
+}
 
 }  // namespace gb
 
@@ -211,7 +215,7 @@ extern "C" int gb_sample(const gb_sample_args* a, cudaStream_t st) {
   const bool greedy = a->greedy || !(a->temperature > 0.f) || a->top_k == 1;
   if (!greedy && (!a->uniforms || a->top_k <= 0 || a->top_k > 1024)) return -2;   // unbounded / larger candidate sets: host sampler
   if (a->n_stop > 0 && !a->stop) return -1;
-  gb::sample_kernel<<<a->B, gb::SM_THREADS, 0, st>>>(*a);
-  if (a->tok_log && a->step) gb::step_inc_kernel<<<1, 1, 0, st>>>(const_cast<int*>(a->step));
+  GB_PDL_LAUNCH(gb::sample_kernel, dim3(a->B), dim3(gb::SM_THREADS), st, *a);
+  if (a->tok_log && a->step) GB_PDL_LAUNCH(gb::step_inc_kernel, dim3(1), dim3(1), st, const_cast<int*>(a->step));
   return gb_launch_rc();
 }

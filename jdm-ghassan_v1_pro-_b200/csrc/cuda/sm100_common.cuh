@@ -31,7 +31,38 @@ static inline int gb_launch_rc() {
   return e == cudaSuccess ? 0 : -(1000 + static_cast<int>(e));
 }
 
+// Programmatic dependent launch for chains of short kernels (the decode step): the next kernel's blocks are set up
+// while this one drains.  A kernel launched through GB_PDL_LAUNCH must call gb::pdl_wait() before it touches global
+// memory; until then nothing its predecessors wrote is guaranteed visible.  GB200_NO_PDL=1 turns the attribute off.
+#include <cstdlib>
+static inline cudaLaunchConfig_t gb_pdl_config(dim3 grid, dim3 block, size_t smem, cudaStream_t st, cudaLaunchAttribute* attr) {
+  static const int enabled = []() { const char* e = std::getenv("GB200_NO_PDL"); return (e && e[0] == '1') ? 0 : 1; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = enabled ? 1 : 0;
+  return cfg;
+}
+#define GB_PDL_LAUNCH(kernel, grid, block, st, ...)                                   \
+  do {                                                                                \
+    cudaLaunchAttribute gb_attr_;                                                     \
+    cudaLaunchConfig_t gb_cfg_ = gb_pdl_config(grid, block, 0, st, &gb_attr_);        \
+    (void)cudaLaunchKernelEx(&gb_cfg_, kernel, __VA_ARGS__);                          \
+  } while (0)
+
 namespace gb {
+
+// First statement of every kernel that GB_PDL_LAUNCH starts: wait until the kernels before it have finished and
+// their writes are visible, then let the kernel after it begin its own set-up.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -68,13 +68,17 @@ class InferenceEngine:
 
     def __init__(self, cfg: ModelConfig, named: Dict[str, np.ndarray], fmt: str = "f16", batch: int = 1,
                  max_len: int = 2048, prefill_chunk: int = 1024, moe_bias: Optional[Sequence] = None, device=None,
-                 compute_dtype=torch.float16, keep_f16_embeddings: bool = True, raw=None, raw_types=None):
+                 compute_dtype=torch.float16, keep_f16_embeddings: bool = True, raw=None, raw_types=None,
+                 fused_step: bool = True):
         """``named``: fp32 tensors by parameter name.  ``fmt``: decode weight format, or "auto" with ``raw`` (an object
         with ``tensor_raw(name)``, e.g. a GGUF file) and ``raw_types`` (name -> ggml type) to take the stored bytes."""
         cfg.validate()
         if cfg.head_dim not in (32, 64, 128):
             raise ValueError("decode attention supports head_dim 32, 64 and 128")
         self.cfg, self.B, self.cap = cfg, batch, max_len
+        # six launches per layer instead of eleven (norms, router, cache append and split merge folded into their
+        # consumers); the separate kernels remain for shapes whose rows do not fit the shared-memory budget
+        self.fused = bool(fused_step) and D.gemv_norm_fits(batch, cfg.hidden_size)
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.dt = compute_dtype
         raw_types = raw_types or {}
@@ -162,6 +166,7 @@ class InferenceEngine:
         # so at batch 1 the cache is cut fine (a few slots per warp) and the partial results merged afterwards
         self.splits = int(min(64, max(8, 512 // (B * cfg.num_kv_heads))))
         self.att_scratch = torch.zeros(B * cfg.num_heads * self.splits * (cfg.head_dim + 2), **f32)
+        self.att_ticket = torch.zeros(B * cfg.num_kv_heads, **i32)
         self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, max_len) + 1, self.dev)
         self.hist_cap = max_len + 8
         self.history = torch.zeros(B, self.hist_cap, **i32)
@@ -184,6 +189,24 @@ class InferenceEngine:
     def _layer_step(self, L: _Layer, x_in, x_out):
         cfg = self.cfg
         d, qd, kvd, Hh, KV, hd = cfg.hidden_size, cfg.q_dim, cfg.kv_dim, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        bf = self.dt == torch.bfloat16
+        if self.fused:
+            D.gemv_norm(L.wqkv, x_in, L.attn_norm, cfg.rms_eps, self.qkv, bf)
+            D.qk_rope_append(self.qkv, self.qk, L.qn, L.kn, self.cos_sin, self.pos, L.cK, L.cV, self.slot_pos, self.state,
+                             Hh, KV, hd, self.cap, PINNED_TOKENS, cfg.rms_eps, cfg.rope_type)
+            D.decode_attn_fused(self.qk[:, :qd], L.cK, L.cV, self.slot_pos, self.state, self.att, self.att_scratch,
+                                self.att_ticket, self.splits, Hh, KV, hd, self.cap, cfg.sliding_window, cfg.attn_scale())
+            D.gemv(L.wo, self.att, self.x_mid, addend=x_in)
+            if cfg.use_moe:
+                D.swiglu_norm_route(L.wg, L.wu, cfg.num_experts, self.E, d, self.x_mid, L.ffn_norm, cfg.rms_eps, L.router,
+                                    L.bias, cfg.moe_top_k, cfg.moe_shared, self.r_idx, self.r_w, self.act)
+                D.expert_down(L.wd, cfg.num_experts, d, self.E, self.act, self.r_idx, self.r_w, cfg.moe_top_k, cfg.moe_shared,
+                              self.x_mid, x_out)
+            else:
+                D.swiglu_norm_route(L.wg, L.wu, 0, self.E, d, self.x_mid, L.ffn_norm, cfg.rms_eps, None, None, 1, False,
+                                    None, None, self.act)
+                D.expert_down(L.wd, 0, d, self.E, self.act, self.dense_idx, self.dense_w, 1, False, self.x_mid, x_out)
+            return
         K.rmsnorm_fwd(x_in, L.attn_norm, self.xb, self.rr, cfg.rms_eps)
         D.gemv(L.wqkv, self.xb, self.qkv)
         K.qk_norm_rope_fwd(self.qkv, self.qk, L.qn, L.kn, self.cos_sin, self.pos, Hh, KV, hd, cfg.rms_eps, cfg.rope_type)
@@ -221,8 +244,11 @@ class InferenceEngine:
         for i, L in enumerate(self.layers):
             self._layer_step(L, self.x[i % 2], self.x[(i + 1) % 2])
         xf = self.x[cfg.num_layers % 2]
-        K.rmsnorm_fwd(xf, self.final_norm, self.xb, self.rr, cfg.rms_eps)
-        D.gemv(self.head, self.xb, self.logits)
+        if self.fused:
+            D.gemv_norm(self.head, xf, self.final_norm, cfg.rms_eps, self.logits, self.dt == torch.bfloat16)
+        else:
+            K.rmsnorm_fwd(xf, self.final_norm, self.xb, self.rr, cfg.rms_eps)
+            D.gemv(self.head, self.xb, self.logits)
         D.decode_advance(self.state, self.pos, self.cap, PINNED_TOKENS)
 
     def _step_eager(self, sp: Optional[SamplingParams]):

@@ -149,6 +149,52 @@ def decode_attn(q16, cacheK, cacheV, slot_pos, state, out16, scratch, splits, H,
     _lib.check_rc(rc, "gb_decode_attn")
 
 
+# ---------------------------------------------------------------------------------------------- fused token step
+def gemv_norm_fits(B: int, K: int) -> bool:
+    return B * K * 2 <= 40 * 1024
+
+
+def gemv_norm(w: QWeight, x32, norm_w, eps, out, is_bf16=False):
+    """``out[b, :] = W @ rmsnorm(x32[b, :]) `` with the normalisation done inside the GEMV (one launch)."""
+    B = x32.shape[0]
+    rc = _lib.lib().gb_gemv_norm(c_vp(w.data.data_ptr()), c_int(w.fmt), c_int(w.N), c_int(w.K), c_vp(x32.data_ptr()),
+                                 c_int(x32.stride(0)), c_vp(norm_w.data_ptr()), c_float(eps), c_int(B), c_vp(out.data_ptr()),
+                                 c_int(out.stride(0)), c_int(int(out.dtype == torch.float32)), c_int(int(is_bf16)),
+                                 _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_gemv_norm")
+    return out
+
+
+def swiglu_norm_route(wg: QWeight, wu: QWeight, ne, E, d, x32, norm_w, eps, router_w, bias, top_k, shared, idx, w, act):
+    """RMSNorm + router + gate/up of the selected experts in one launch; ``router_w=None`` for a dense block."""
+    rc = _lib.lib().gb_swiglu_norm_route(c_vp(wg.data.data_ptr()), c_vp(wu.data.data_ptr()), c_int(wg.fmt), c_int(ne), c_int(E),
+                                         c_int(d), c_vp(x32.data_ptr()), c_vp(norm_w.data_ptr()), c_float(eps),
+                                         _lib.ptr(router_w), _lib.ptr(bias), c_int(x32.shape[0]), c_int(top_k),
+                                         c_int(int(shared)), _lib.ptr(idx), _lib.ptr(w), c_vp(act.data_ptr()),
+                                         c_int(_bf(act)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_swiglu_norm_route")
+
+
+def qk_rope_append(qkv, q_out, qw, kw, cos_sin, pos, cacheK, cacheV, slot_pos, state, H, KV, hd, cap, pinned, eps, rope_type):
+    B = qkv.shape[0]
+    rc = _lib.lib().gb_qk_rope_append(c_vp(qkv.data_ptr()), c_ll(qkv.stride(0)), c_vp(q_out.data_ptr()), c_ll(q_out.stride(0)),
+                                      _lib.ptr(qw), _lib.ptr(kw), c_vp(cos_sin.data_ptr()), c_vp(pos.data_ptr()),
+                                      c_vp(cacheK.data_ptr()), c_vp(cacheV.data_ptr()), c_vp(slot_pos.data_ptr()),
+                                      c_vp(state.data_ptr()), c_int(B), c_int(H), c_int(KV), c_int(hd), c_int(cap),
+                                      c_int(pinned), c_float(eps), c_int(rope_type), c_int(_bf(qkv)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_qk_rope_append")
+
+
+def decode_attn_fused(q16, cacheK, cacheV, slot_pos, state, out16, scratch, ticket, splits, H, KV, hd, cap, window, scale):
+    B = q16.shape[0]
+    rc = _lib.lib().gb_decode_attn_fused(c_vp(q16.data_ptr()), c_ll(q16.stride(0)), c_vp(cacheK.data_ptr()),
+                                         c_vp(cacheV.data_ptr()), c_vp(slot_pos.data_ptr()), c_vp(state.data_ptr()),
+                                         c_vp(out16.data_ptr()), c_ll(out16.stride(0)), c_vp(scratch.data_ptr()), c_int(splits),
+                                         c_int(B), c_int(H), c_int(KV), c_int(hd), c_int(cap), c_int(window), c_float(scale),
+                                         c_int(_bf(q16)), c_vp(ticket.data_ptr()), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_decode_attn_fused")
+
+
 def decode_advance(state, pos_out, cap, pinned):
     rc = _lib.lib().gb_decode_advance(c_vp(state.data_ptr()), c_vp(pos_out.data_ptr()), c_int(state.shape[0]), c_int(cap),
                                       c_int(pinned), _lib.stream_ptr())

@@ -345,3 +345,34 @@ def test_inference_cli_runs_the_model(tmp_path, capsys):
     assert os.path.getsize(str(tmp_path / "l.f32")) == 400 * 4
     assert I.main(["eval", "--model", path, "--max-prompts", "2", "--max-tokens", "6", "--ctx", "128"]) == 0
     assert "items 2" in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("moe,fmt,B", [(True, "f16", 1), (True, "q4_0", 3), (False, "q8_0", 2)])
+def test_fused_token_step_equals_separate_kernels(moe, fmt, B):
+    """Norms, router, cache append and split merge folded into their consumers: same rounding points, same numbers."""
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.models.config import init_parameters
+    cfg = _tiny_cfg(use_moe=moe)
+    named = init_parameters(cfg, 31)
+    engines = [InferenceEngine(cfg, named, fmt=fmt, batch=B, max_len=48, prefill_chunk=32, fused_step=f) for f in (True, False)]
+    assert engines[0].fused and not engines[1].fused
+    seq = torch.randint(16, 512, (B, 60), generator=torch.Generator().manual_seed(9), dtype=torch.int32)
+    for e in engines:
+        e.reset(1)
+    for j in range(60):                                  # longer than the cache: the ring wraps
+        for e in engines:
+            e.cur_tok.copy_(seq[:, j])
+            e._forward_token()
+        assert torch.equal(engines[0].logits, engines[1].logits), (j, float((engines[0].logits - engines[1].logits).abs().max()))
+    for La, Lb in zip(engines[0].layers, engines[1].layers):
+        assert torch.equal(La.cK, Lb.cK) and torch.equal(La.cV, Lb.cV)
+    assert torch.equal(engines[0].slot_pos, engines[1].slot_pos) and int(engines[0].att_ticket.abs().sum()) == 0
+    sp = SamplingParams(seed=4, top_k=20)
+    outs = []
+    for e in engines:                                    # and through the captured graph with sampling
+        e.reset(1)
+        e.prefill(seq[:, :9].contiguous())
+        e.sample_first(sp)
+        e.decode_steps(12, sp)
+        outs.append(e.transcript(13))
+    assert np.array_equal(np.asarray(outs[0]), np.asarray(outs[1]))
