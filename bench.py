@@ -159,7 +159,7 @@ def recipe_label(path, mcfg, tcfg, world):
             "params": mcfg.count_parameters(),
             "global_batch": tcfg.batch_size * tcfg.grad_accum * world,
             "micro_batch": tcfg.batch_size, "grad_accum": tcfg.grad_accum, "seq_len": tcfg.seq_len,
-            "optimizer": tcfg.optimizer, "parallelism": "dp%d" % world,
+            "optimizer": tcfg.optimizer, "parallelism": ("dp%d" % world) + ("+ep%d" % tcfg.ep_size if tcfg.ep_size > 1 else ""),
             "l2": "per-step working set (weights, gradients, moments: several GB) exceeds the 126 MB L2"}
 
 

@@ -3,7 +3,8 @@
     data_pipeline parquet        --lake <dir|file.parquet> --tokenizer tok.gtok --out shards [--match s] [--domain d] [--mode auto|qa|text|chat]
     data_pipeline parquet-corpus --lake <dir> --out corpus.txt [--limit n]
     data_pipeline build          --tokenizer tok.gtok --out shards [--text path] [--chat file.jsonl] [--synth n]
-    data_pipeline synth          --out synth.jsonl --n 50000 [--english]
+    data_pipeline synth          --out synth.jsonl --n 50000 [--config configs/synthesis_large_200k.yaml [--section synth|sft_synth]]
+    data_pipeline synth-en       --out synth_en.jsonl --n 20000 [--seed 4321]
     data_pipeline inspect        --shards shards [--tokenizer tok.gtok]
     data_pipeline tok-info       --tokenizer tok.gtok
     data_pipeline csvs           --dir <csv-root> --out corpus_csv.txt [--with-english]
@@ -34,7 +35,7 @@ from ..data import synth as S
 from ..data import tokenizer as T
 from ..utils.log import human_count, log_error, log_info, log_warn
 
-COMMANDS = ["parquet", "parquet-corpus", "build", "synth", "inspect", "tok-info", "csvs", "csv2json", "jsons", "json",
+COMMANDS = ["parquet", "parquet-corpus", "build", "synth", "synth-en", "inspect", "tok-info", "csvs", "csv2json", "jsons", "json",
             "json-inspect", "dump-text", "retrieve"]
 
 
@@ -43,12 +44,12 @@ def _parser() -> argparse.ArgumentParser:
     ap.add_argument("command", choices=COMMANDS)
     ap.add_argument("rest", nargs="*")
     for n in ("lake", "dir", "match", "tokenizer", "out", "domain", "style-mode", "mode", "text", "chat", "shards", "index", "query",
-              "input", "blocklist"):
+              "input", "blocklist", "config", "section"):
         ap.add_argument("--" + n, default="")
     for n, d in (("val-ratio", 0.005), ("min-score", 0.0)):
         ap.add_argument("--" + n, type=float, default=d)
-    for n, d in (("shard-tokens", 50_000_000), ("seq-len", 4096), ("min-keep", 1), ("expect-vocab", 0), ("limit", 0), ("n", 50000),
-                 ("synth", 0), ("seed", 1), ("top", 3), ("docs-per-file", 20000), ("id-start", 1_000_000), ("min-chars", 2)):
+    for n, d in (("shard-tokens", 50_000_000), ("seq-len", 4096), ("min-keep", 1), ("expect-vocab", 0), ("limit", 0), ("n", None),
+                 ("synth", 0), ("seed", None), ("top", 3), ("docs-per-file", 20000), ("id-start", 1_000_000), ("min-chars", 2)):
         ap.add_argument("--" + n, type=int, default=d)
     for n in ("keep-robotic", "keep-case", "no-dedup", "probe", "with-english", "english"):
         ap.add_argument("--" + n, action="store_true")
@@ -214,6 +215,9 @@ def cmd_jsons(a) -> int:
 
 def main(argv: Optional[List[str]] = None) -> int:
     a = _parser().parse_args(argv)
+    a.n_given, a.seed_given = a.n is not None, a.seed is not None
+    a.n = a.n if a.n_given else 50000
+    a.seed = a.seed if a.seed_given else 1
     cmd = a.command
     if cmd in ("parquet", "parquet-corpus"):
         try:
@@ -269,11 +273,30 @@ def main(argv: Optional[List[str]] = None) -> int:
             return 1
         log_info("\n" + rep.summary())
         return 0
-    if cmd == "synth":
-        gen = S.english_conversations if a.english else S.darija_conversations
-        out = a.out or "data/synth.jsonl"
+    if cmd in ("synth", "synth-en"):
+        from ..utils.config import ConfigError
+        if cmd == "synth-en" or a.english:
+            out = a.out or "data/synth_en.jsonl"
+            rows = S.english_conversations(a.n if a.n_given else 20000, seed=a.seed if a.seed_given else 4321)
+        else:
+            try:
+                scfg = S.load_synth_config(a.config, a.section or "synth") if a.config else S.SynthConfig()
+            except ConfigError as e:
+                log_error(str(e))
+                return 1
+            if a.n_given or not a.config:
+                scfg.num_conversations = a.n
+            if a.seed_given:
+                scfg.seed = a.seed
+            out = a.out or scfg.output_path or "data/synth.jsonl"
+            if a.config:
+                log_info("[synth] config %s [%s]: %d conversations, seed %d, turns %d-%d" % (
+                    a.config, a.section or "synth", scfg.num_conversations, scfg.seed, scfg.min_turns, scfg.max_turns))
+            g = S.DarijaSynthGenerator(scfg)
+            rows = g.generate_many(scfg.num_conversations)
+            log_info("[synth] " + g.stats.summary())
         os.makedirs(os.path.dirname(os.path.abspath(out)), exist_ok=True)
-        n = S.write_jsonl(out, gen(a.n, seed=a.seed))
+        n = S.write_jsonl(out, rows)
         log_info("[synth] wrote %s conversations to %s" % (human_count(n), out))
         return 0
     if cmd == "inspect":

@@ -6,7 +6,7 @@
     python -m ghassan_b200.cli.infer quantize  --model in.gguf --out out.gguf --profile q4_0
     python -m ghassan_b200.cli.infer bench     --model model.gguf [--tokens 128] [--prompt-tokens 32] [--batch 1]
     python -m ghassan_b200.cli.infer tokenize  --model model.gguf --text "شنو خبارك"
-    python -m ghassan_b200.cli.infer export    --checkpoint last.ckpt --tokenizer tok.gtok --out model.gguf [--profile fp16|q8_k|q4_0]
+    python -m ghassan_b200.cli.infer export    --checkpoint last.ckpt --tokenizer tok.gtok --out model.gguf [--profile fp16|q8_k|q4_0] [--compat native|llama|llama_moe]
     python -m ghassan_b200.cli.infer eval      --model model.gguf [--suite dir] [--persona en]
     python -m ghassan_b200.cli.infer perplexity --model model.gguf (--text "held out" | --shards dir --prefix val_)
     python -m ghassan_b200.cli.infer devices
@@ -113,15 +113,17 @@ def main(argv: Optional[List[str]] = None) -> int:
         from ..training import checkpoint as C
         if not (a.checkpoint and a.tokenizer and a.out):
             raise SystemExit("export needs --checkpoint, --tokenizer and --out")
-        if (a.compat or "native") != "native":
-            raise SystemExit("only --compat native is written by this build")
         d = C.read(a.checkpoint, with_optimizer=False)
         cfg = C.config_from_dict(d["config"])
         st = d["state"]
-        info = export_gguf(a.out, cfg, dict(d["params"]), a.tokenizer, a.profile or "fp16", moe_bias=d["moe_bias"],
-                           extra_meta={"steps": str(st["step"]), "val_loss": "%.6f" % st["best_val"]})
-        print("[gguf] exported %s  profile=%s tensors=%d metadata=%d weights=%d bytes" % (
-            info["path"], info["profile"], info["tensors"], info["metadata"], info["weight_bytes"]))
+        try:
+            info = export_gguf(a.out, cfg, dict(d["params"]), a.tokenizer, a.profile or "fp16", moe_bias=d["moe_bias"],
+                               extra_meta={"steps": str(st["step"]), "val_loss": "%.6f" % st["best_val"]},
+                               compat=a.compat or "native")
+        except ValueError as e:
+            raise SystemExit("export: %s" % e)
+        print("[gguf] exported %s  profile=%s compat=%s tensors=%d metadata=%d weights=%d bytes" % (
+            info["path"], info["profile"], a.compat or "native", info["tensors"], info["metadata"], info["weight_bytes"]))
         return 0
     if cmd == "quantize":
         from ..formats.gguf import export_gguf

@@ -78,9 +78,61 @@ def _unescape_merge_piece(b: bytes) -> bytes:
     return bytes(out)
 
 
+def llama_compat_refusal(cfg: ModelConfig, compat: str) -> str:
+    """Why ``cfg`` cannot be written under a llama.cpp architecture name ("" = it can); the rules of the reference's
+    exporter (format/gguf_codec.cpp:966-997)."""
+    if compat == "llama":
+        if cfg.use_moe:
+            return ("MoE has no llama.cpp dense equivalent; export native GGUF for ghassan-ai, --compat llama_moe for MoE "
+                    "Ollama (needs moe_shared=false), or train a dense (use_moe=false) variant for ollama")
+    else:
+        if not cfg.use_moe:
+            return "llama_moe needs use_moe=true (use --compat llama for dense)"
+        if cfg.moe_shared:
+            return ("llama_moe has no shared-expert equivalent in llama.cpp; train with moe_shared=false for Ollama, or use "
+                    "native GGUF (full quality)")
+    if cfg.use_qk_norm:
+        return "use_qk_norm has no llama-arch equivalent; disable it for --compat " + compat
+    if cfg.rope_scale != 1.0:
+        return "rope_scale YaRN has no exact llama mapping here; use rope_scale=1"
+    if cfg.moe_aux_free:
+        return "moe_aux_free has no llama mapping; use native GGUF"
+    if cfg.sliding_window != 0:
+        return "sliding_window has no llama mapping here; use 0"
+    if cfg.rope_type != 0:
+        return "rope_type=neox mismatches the interleaved rotation of this export; use 0"
+    return ""
+
+
+def llama_tensor_name(internal: str, moe: bool = False) -> str:
+    """llama.cpp tensor name of a parameter ("" = none), format/gguf_codec.cpp:929-951 and :999-1024."""
+    top = {"tok_embeddings": "token_embd.weight", "final_norm": "output_norm.weight", "lm_head": "output.weight"}
+    if internal in top:
+        return top[internal]
+    if not internal.startswith("layers.") or internal.count(".") < 2:
+        return ""
+    _, layer, rest = internal.split(".", 2)
+    names = {"attn_norm": "attn_norm.weight", "wq": "attn_q.weight", "wk": "attn_k.weight", "wv": "attn_v.weight",
+             "wo": "attn_output.weight", "ffn_norm": "ffn_norm.weight"}
+    names.update({"moe_router": "ffn_gate_inp.weight", "moe_gate": "ffn_gate_exps.weight", "moe_up": "ffn_up_exps.weight",
+                  "moe_down": "ffn_down_exps.weight"} if moe else
+                 {"w_gate": "ffn_gate.weight", "w_up": "ffn_up.weight", "w_down": "ffn_down.weight"})
+    return ("blk.%s.%s" % (layer, names[rest])) if rest in names else ""
+
+
 def export_gguf(path: str, cfg: ModelConfig, named: Dict[str, np.ndarray], tokenizer_path: str, profile: str = "fp16",
-                moe_bias: Optional[Sequence[np.ndarray]] = None, extra_meta: Optional[Dict[str, str]] = None) -> dict:
-    """Write a self-contained native ("ghassan" architecture) GGUF file; returns a small summary."""
+                moe_bias: Optional[Sequence[np.ndarray]] = None, extra_meta: Optional[Dict[str, str]] = None,
+                compat: str = "native") -> dict:
+    """Write a self-contained GGUF file; returns a small summary.  ``compat``: "native" (architecture "ghassan", what
+    this framework loads), "llama" (dense models under llama.cpp names) or "llama_moe" (Mixtral-style names;
+    experimental in the reference too).  The compat forms are write-only: they drop what llama.cpp cannot express."""
+    if compat not in ("native", "llama", "llama_moe"):
+        raise ValueError(f"unknown compat '{compat}' (native|llama|llama_moe)")
+    want_llama, want_moe = compat == "llama", compat == "llama_moe"
+    if compat != "native":
+        why = llama_compat_refusal(cfg, compat)
+        if why:
+            raise ValueError(f"--compat {compat} refused: {why}")
     prof = profile_for(profile)
     tok = Tokenizer.load(tokenizer_path)
     if tok.vocab_size != cfg.vocab_size:
@@ -90,7 +142,7 @@ def export_gguf(path: str, cfg: ModelConfig, named: Dict[str, np.ndarray], token
     n_params = cfg.count_parameters()
     w = H.GgufWriter()
     s = lambda k, v: w.set_str(k, v.encode("utf-8") if isinstance(v, str) else v)
-    arch = "ghassan"
+    arch = "ghassan" if compat == "native" else "llama"
     a = lambda k: arch + "." + k
     s("general.architecture", arch)
     net = "MoE-%d" % cfg.num_experts if cfg.use_moe else "dense"
@@ -102,7 +154,7 @@ def export_gguf(path: str, cfg: ModelConfig, named: Dict[str, np.ndarray], token
     w.set_u64(a("vocab_size"), cfg.vocab_size)
     w.set_u64(a("embedding_length"), cfg.hidden_size)
     w.set_u64(a("block_count"), cfg.num_layers)
-    w.set_u64(a("feed_forward_length"), cfg.intermediate_size)
+    w.set_u64(a("feed_forward_length"), cfg.moe_expert_dim if want_moe else cfg.intermediate_size)
     w.set_u64(a("attention.head_count"), cfg.num_heads)
     w.set_u64(a("attention.head_count_kv"), cfg.num_kv_heads)
     w.set_f32(a("attention.layer_norm_rms_epsilon"), cfg.rms_eps)
@@ -110,25 +162,30 @@ def export_gguf(path: str, cfg: ModelConfig, named: Dict[str, np.ndarray], token
     w.set_f32(a("rope.freq_base"), cfg.rope_theta)
     w.set_u64(a("context_length"), cfg.max_seq_len)
     w.set_bool(a("tie_word_embeddings"), cfg.tie_embeddings)
-    w.set_bool(a("use_moe"), cfg.use_moe)
-    w.set_u64(a("moe.expert_count"), cfg.num_experts)
-    w.set_u64(a("moe.experts_used_count"), cfg.moe_top_k)
-    w.set_u64(a("moe.expert_feed_forward_length"), cfg.moe_expert_dim)
-    w.set_bool(a("moe.shared_expert"), cfg.moe_shared)
-    w.set_f32(a("rope.scale"), cfg.rope_scale)
-    w.set_f32(a("rope.yarn_mscale"), cfg.rope_yarn_mscale)
-    w.set_f32(a("rope.yarn_low"), cfg.rope_yarn_low)
-    w.set_f32(a("rope.yarn_high"), cfg.rope_yarn_high)
-    w.set_u64(a("sliding_window"), cfg.sliding_window)
-    w.set_u64(a("rope.type"), cfg.rope_type)
-    w.set_bool(a("moe.aux_free"), cfg.moe_aux_free)
-    w.set_f32(a("moe.aux_scale"), cfg.moe_aux_scale)
-    w.set_f32(a("moe.jitter"), cfg.moe_jitter)
-    w.set_f32(a("z_loss_scale"), cfg.z_loss_scale)
-    w.set_bool(a("use_qk_norm"), cfg.use_qk_norm)
-    s(a("norm_type"), "rmsnorm")
-    s(a("ffn_type"), "swiglu_moe" if cfg.use_moe else "swiglu")
-    s(a("attention.type"), "gqa_causal")
+    if want_moe:
+        w.set_u64(a("expert_count"), cfg.num_experts)
+        w.set_u64(a("expert_used_count"), cfg.moe_top_k)
+        w.set_u64(a("expert_feed_forward_length"), cfg.moe_expert_dim)
+    if compat == "native":
+        w.set_bool(a("use_moe"), cfg.use_moe)
+        w.set_u64(a("moe.expert_count"), cfg.num_experts)
+        w.set_u64(a("moe.experts_used_count"), cfg.moe_top_k)
+        w.set_u64(a("moe.expert_feed_forward_length"), cfg.moe_expert_dim)
+        w.set_bool(a("moe.shared_expert"), cfg.moe_shared)
+        w.set_f32(a("rope.scale"), cfg.rope_scale)
+        w.set_f32(a("rope.yarn_mscale"), cfg.rope_yarn_mscale)
+        w.set_f32(a("rope.yarn_low"), cfg.rope_yarn_low)
+        w.set_f32(a("rope.yarn_high"), cfg.rope_yarn_high)
+        w.set_u64(a("sliding_window"), cfg.sliding_window)
+        w.set_u64(a("rope.type"), cfg.rope_type)
+        w.set_bool(a("moe.aux_free"), cfg.moe_aux_free)
+        w.set_f32(a("moe.aux_scale"), cfg.moe_aux_scale)
+        w.set_f32(a("moe.jitter"), cfg.moe_jitter)
+        w.set_f32(a("z_loss_scale"), cfg.z_loss_scale)
+        w.set_bool(a("use_qk_norm"), cfg.use_qk_norm)
+        s(a("norm_type"), "rmsnorm")
+        s(a("ffn_type"), "swiglu_moe" if cfg.use_moe else "swiglu")
+        s(a("attention.type"), "gqa_causal")
     # ---- tokenizer, llama.cpp style + the authoritative .gtok image
     s("tokenizer.ggml.model", "gpt2")
     s("tokenizer.ggml.pre", "gpt-2")
@@ -166,9 +223,19 @@ def export_gguf(path: str, cfg: ModelConfig, named: Dict[str, np.ndarray], token
         is_emb = spec.name in ("tok_embeddings", "lm_head")
         t = prof.norm if is_norm else prof.embedding if is_emb else prof.default
         arr = np.ascontiguousarray(np.asarray(named[spec.name], dtype=np.float32).reshape(spec.shape))
-        w.add_tensor(spec.name, arr, t)
+        name = spec.name
+        if compat != "native":
+            name = llama_tensor_name(spec.name, moe=want_moe)
+            if not name:
+                raise ValueError(f"no llama.cpp name for tensor {spec.name} (use native GGUF)")
+            if want_moe and spec.name.endswith("moe_down"):          # [ne*d, E] -> [ne, E, d]
+                arr = np.ascontiguousarray(arr.reshape(cfg.num_experts, cfg.hidden_size, cfg.moe_expert_dim).transpose(0, 2, 1))
+        w.add_tensor(name, arr, t)
         total += H.ggml_tensor_nbytes(t, arr.size)
-    if cfg.moe_aux_free and moe_bias is not None:
+        if compat != "native" and spec.name == "tok_embeddings" and cfg.tie_embeddings:
+            w.add_tensor("output.weight", arr, t)                     # llama.cpp wants the head by name
+            total += H.ggml_tensor_nbytes(t, arr.size)
+    if compat == "native" and cfg.moe_aux_free and moe_bias is not None:
         for l, b in enumerate(moe_bias):
             b = np.asarray(b, dtype=np.float32).reshape(-1)
             if l < cfg.num_layers and b.size == cfg.num_experts:

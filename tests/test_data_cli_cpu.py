@@ -127,3 +127,37 @@ def test_data_pipeline_csv_json_retrieve_synth(tmp_path, capsys):
     assert capsys.readouterr().out.count("[chat]") == 3
     assert DP.main(["dump-text", "--input", sy, "--limit", "2"]) == 0
     assert "[chat]" not in capsys.readouterr().out
+
+
+def test_shipped_synthesis_recipes_drive_the_generator(tmp_path, capsys):
+    """The synthesis YAMLs are data_pipeline configs: both sections load, a typo in one is an error, knobs are obeyed."""
+    from ghassan_b200.cli import data_pipeline as DP
+    from ghassan_b200.data import synth as S
+    cfgs = os.path.join(os.path.dirname(__file__), "..", "configs")
+    for name, section in (("synthesis_large_200k", "synth"), ("synthesis_billion_scale", "synth"), ("synthesis_billion_scale", "sft_synth")):
+        out = str(tmp_path / (name + section + ".jsonl"))
+        assert DP.main(["synth", "--config", os.path.join(cfgs, name + ".yaml"), "--section", section, "--n", "6", "--out", out]) == 0
+        rows = [json.loads(ln) for ln in open(out, encoding="utf-8")]
+        assert len(rows) == 6 and all(r["messages"][-1]["role"] == "assistant" for r in rows)
+    typo = tmp_path / "typo.yaml"
+    src = open(os.path.join(cfgs, "synthesis_large_200k.yaml"), encoding="utf-8").read()
+    typo.write_text(src.replace("  min_turns:", "  p_bogus_typo: 0.5\n  min_turns:", 1), encoding="utf-8")
+    assert DP.main(["synth", "--config", str(typo), "--n", "2", "--out", str(tmp_path / "t.jsonl")]) == 1
+    assert "p_bogus_typo" in (lambda o: o.out + o.err)(capsys.readouterr())
+    assert DP.main(["synth", "--config", os.path.join(cfgs, "synthesis_large_200k.yaml"), "--section", "other", "--out", str(tmp_path / "x")]) == 1
+    cfg = S.load_synth_config(os.path.join(cfgs, "synthesis_billion_scale.yaml"), "sft_synth")
+    assert cfg.seed == 9999 and cfg.max_turns == 10
+    # knobs: script mix, system prompts, turn bounds, template cap, determinism
+    c = S.SynthConfig(seed=3, min_turns=4, max_turns=6, p_arabic_script=0.0, p_latin_script=1.0, p_msa=0.0, p_system=1.0,
+                      p_french_switch=0.0)
+    g = S.DarijaSynthGenerator(c)
+    rows = g.generate_many(40)
+    assert rows and all(r["lang"] == "ar-MA-latn" and r["messages"][0]["role"] == "system" for r in rows)
+    assert all(4 <= len(r["messages"]) - 1 <= 6 for r in rows) and len({json.dumps(r["messages"]) for r in rows}) == len(rows)
+    assert [r["messages"] for r in S.DarijaSynthGenerator(c).generate_many(40)] == [r["messages"] for r in rows]
+    capped = S.DarijaSynthGenerator(S.SynthConfig(seed=3, max_template_uses=1, max_attempts_multiplier=5))
+    few = capped.generate_many(500)
+    assert len(few) < 60 and capped.stats.rejected_template_cap > 0 and capped.stats.attempts <= 2500
+    assert DP.main(["synth-en", "--n", "7", "--out", str(tmp_path / "en.jsonl")]) == 0
+    assert len(open(tmp_path / "en.jsonl", encoding="utf-8").read().splitlines()) == 7
+    capsys.readouterr()

@@ -176,3 +176,29 @@ def test_graw_round_trip(ckpt, tmp_path):
     open(p, "r+b").write(b"XXXX")
     with pytest.raises(Exception):
         GA.load_raw(p, cfg)
+
+
+@pytest.mark.parametrize("ckpt,golden,profile,compat", [("dense_ref.ckpt", "dense_llama_fp16.gguf", "fp16", "llama"),
+                                                        ("dense_ref.ckpt", "dense_llama_q8.gguf", "q8_k", "llama"),
+                                                        ("moe_noshared_ref.ckpt", "moens_llamamoe_fp16.gguf", "fp16", "llama_moe")])
+def test_llama_compat_export_is_byte_identical_to_the_reference(tmp_path, ckpt, golden, profile, compat):
+    """Golden files: the reference's ``ghassan-ai export --compat llama|llama_moe`` on checkpoints its trainer wrote."""
+    from ghassan_b200.cli import infer as I
+    out = str(tmp_path / "m.gguf")
+    assert I.main(["export", "--checkpoint", os.path.join(GOLD, ckpt), "--tokenizer", os.path.join(GOLD, "tiny400.gtok"), "--out", out,
+                   "--profile", profile, "--compat", compat]) == 0
+    assert open(out, "rb").read() == open(os.path.join(GOLD, golden), "rb").read()
+
+
+def test_llama_compat_refusals_and_names(tmp_path):
+    from ghassan_b200.cli import infer as I
+    from ghassan_b200.formats import gguf as G
+    tok = os.path.join(GOLD, "tiny400.gtok")
+    for ckpt, compat in (("tiny_ref.ckpt", "llama"), ("tiny_ref.ckpt", "llama_moe"), ("dense_ref.ckpt", "llama_moe")):
+        with pytest.raises(SystemExit, match="refused"):            # MoE as dense, shared expert / QK-norm, dense as MoE
+            I.main(["export", "--checkpoint", os.path.join(GOLD, ckpt), "--tokenizer", tok, "--out", str(tmp_path / "x.gguf"), "--compat", compat])
+    with pytest.raises(SystemExit, match="unknown compat"):
+        I.main(["export", "--checkpoint", os.path.join(GOLD, "dense_ref.ckpt"), "--tokenizer", tok, "--out", str(tmp_path / "x.gguf"), "--compat", "gpt2"])
+    assert G.llama_tensor_name("layers.3.wq") == "blk.3.attn_q.weight" and G.llama_tensor_name("layers.0.w_down") == "blk.0.ffn_down.weight"
+    assert G.llama_tensor_name("layers.2.moe_gate", moe=True) == "blk.2.ffn_gate_exps.weight"
+    assert G.llama_tensor_name("layers.2.moe_sh_gate", moe=True) == "" and G.llama_tensor_name("layers.2.qk_qnorm") == ""
