@@ -37,16 +37,64 @@ __global__ void embed_fwd_kernel(const int* __restrict__ ids, const float* __res
   for (int i = threadIdx.x; i < d / 4; i += blockDim.x) dst[i] = src[i];
 }
 
-// dtable[ids[t]] += dx[t]  (fp32 atomics; rows of distinct ids never collide)
-__global__ void embed_bwd_kernel(const int* __restrict__ ids, const float* __restrict__ dx, float* __restrict__ dtable,
-                                 int n_tok, int d, int vocab) {
+// dtable[id] += sum over the tokens t with ids[t] == id of dx[t], added in increasing t: no atomics, so the embedding
+// gradient is the same bits on every run (the reference scatters with atomicAdd, cuda/kernels.cu:420-442, and is
+// not).  One block per token; the block of the FIRST occurrence of an id owns that id's row and walks the later
+// occurrences, every other block leaves after it has found an earlier one.  Matches are found 256 ids at a time
+// (one compare per thread, ballots into shared memory) and then added in index order.
+constexpr int EMB_THREADS = 256;
+constexpr int EMB_MAX_COLS = 32;     // columns per thread: d <= 8192
+
+__global__ void __launch_bounds__(EMB_THREADS) embed_bwd_kernel(const int* __restrict__ ids, const float* __restrict__ dx,
+                                                               float* __restrict__ dtable, int n_tok, int d, int vocab) {
+  __shared__ unsigned int mask[EMB_THREADS / 32];
+  __shared__ int s_earlier;
   const int t = blockIdx.x;
   if (t >= n_tok) return;
   const int id = ids[t];
   if (id < 0 || id >= vocab) return;
-  const float* src = dx + (size_t)t * d;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_earlier = 0;
+  __syncthreads();
+  for (int base = 0; base < t; base += EMB_THREADS) {          // does an earlier token carry the same id?
+    const int j = base + threadIdx.x;
+    if (j < t && ids[j] == id) s_earlier = 1;
+  }
+  __syncthreads();
+  if (s_earlier) return;
+  float acc[EMB_MAX_COLS];
+  const int ncol = (d + EMB_THREADS - 1) / EMB_THREADS;
+#pragma unroll
+  for (int c = 0; c < EMB_MAX_COLS; ++c) acc[c] = 0.f;
+  for (int base = t - (t % EMB_THREADS); base < n_tok; base += EMB_THREADS) {
+    const int j = base + threadIdx.x;
+    const bool hit = j >= t && j < n_tok && ids[j] == id;
+    const unsigned int b = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) mask[warp] = b;
+    __syncthreads();
+    for (int w = 0; w < EMB_THREADS / 32; ++w) {
+      unsigned int m = mask[w];
+      while (m) {
+        const int k = __ffs(m) - 1;
+        m &= m - 1;
+        const float* src = dx + (size_t)(base + w * 32 + k) * d;
+#pragma unroll
+        for (int c = 0; c < EMB_MAX_COLS; ++c)
+          if (c < ncol) {
+            const int col = c * EMB_THREADS + threadIdx.x;
+            if (col < d) acc[c] += src[col];
+          }
+      }
+    }
+    __syncthreads();
+  }
   float* dst = dtable + (size_t)id * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[i]);
+#pragma unroll
+  for (int c = 0; c < EMB_MAX_COLS; ++c)
+    if (c < ncol) {
+      const int col = c * EMB_THREADS + threadIdx.x;
+      if (col < d) dst[col] += acc[c];
+    }
 }
 
 // ------------------------------------------------------------------------------------------ RMSNorm
@@ -323,7 +371,8 @@ extern "C" int gb_embed_fwd(const int* ids, const float* table, float* out, int 
   return GB_LAUNCH_OK();
 }
 extern "C" int gb_embed_bwd(const int* ids, const float* dx, float* dtable, int n_tok, int d, int vocab, cudaStream_t st) {
-  embed_bwd_kernel<<<n_tok, 128, 0, st>>>(ids, dx, dtable, n_tok, d, vocab);
+  if (d > EMB_THREADS * EMB_MAX_COLS) return -1;
+  embed_bwd_kernel<<<n_tok, EMB_THREADS, 0, st>>>(ids, dx, dtable, n_tok, d, vocab);
   return GB_LAUNCH_OK();
 }
 

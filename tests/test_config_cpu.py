@@ -165,3 +165,41 @@ def test_trainer_config_rules():
     assert d == "artifacts/shards_en" and p.startswith("train")
     lion = TrainerConfig.from_config(Config.from_string(base + "  optimizer: lion\n  learning_rate: 0.001\n"))
     assert lion.effective_peak_lr() == pytest.approx(0.0001)      # Lion runs at a tenth of the recipe rate
+
+
+# "parameters : <total> (<total minus embedding tables> without embeddings)" as the reference's `gai_train --dry-run`
+# prints it for each shipped recipe (recorded from its CPU build)
+REFERENCE_DRY_RUN_PARAMETERS = {
+    "cpu_smoke_test": ("422.66K", "345.86K"), "flash_109m_compact_2xt4": ("109.25M", "92.86M"),
+    "flash_480m_2xt4": ("479.73M", "455.15M"), "flash_480m_ollama_compat": ("433.72M", "409.15M"),
+    "flash_480m_single": ("479.73M", "455.15M"), "pilot_moe_smoke": ("479.73M", "455.15M"),
+    "pro_1b_2xt4": ("1.04B", "1.01B"), "pro_1b_4xt4_legacy": ("1.04B", "1.01B"),
+    "pro_1b_auxfree_research": ("479.73M", "455.15M"), "pro_1b_single": ("1.04B", "1.01B"),
+    "sft_flash_109m_compact_2xt4": ("109.25M", "92.86M"), "sft_flash_480m_2xt4": ("479.73M", "455.15M"),
+    "sft_flash_480m_4xt4": ("479.73M", "455.15M"), "sft_flash_480m_single": ("479.73M", "455.15M"),
+    "sft_pro_1b_2xt4": ("1.04B", "1.01B"), "sft_pro_1b_single": ("1.04B", "1.01B"), "t4_en_120m_fast": ("100.09M", "75.52M"),
+}
+
+
+def test_parameter_totals_match_the_reference_dry_run():
+    import os
+    from ghassan_b200.models.config import ModelConfig
+    from ghassan_b200.utils.config import Config
+    from ghassan_b200.utils.log import human_count
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "configs")
+    for name, (total, no_emb) in REFERENCE_DRY_RUN_PARAMETERS.items():
+        m = ModelConfig.from_config(Config.from_file(os.path.join(root, name + ".yaml")))
+        n = m.count_parameters()
+        emb = m.vocab_size * m.hidden_size * (1 if m.tie_embeddings else 2)
+        assert human_count(n) == total, (name, human_count(n), total)
+        assert human_count(n - emb) == no_emb, (name, human_count(n - emb), no_emb)
+
+
+def test_every_training_recipe_passes_a_strict_dry_run(capsys):
+    import os
+    from ghassan_b200.cli import train as TR
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "configs")
+    for name in REFERENCE_DRY_RUN_PARAMETERS:
+        rc = TR.main(["--config", os.path.join(root, name + ".yaml"), "--dry-run", "--strict-config", "--output-budget-mb", "0"])
+        assert rc == 0, (name, capsys.readouterr())
+    capsys.readouterr()

@@ -365,3 +365,22 @@ def test_embedding_gather_scatter():
     k.embed_bwd(ids, dx, dt_)
     ref = torch.zeros(V, d, device="cuda").index_add_(0, ids.long(), dx)
     assert near(dt_, ref, 1e-5, 1e-6)[0]
+    # many repeats of few ids, a width that is no multiple of the block, invalid ids ignored; and the same bits every run
+    V, d, n = 37, 200, 5000
+    ids = torch.randint(-2, V + 2, (n,), device="cuda", dtype=torch.int32)
+    dx = rnd(n, d, seed=63)
+    runs = []
+    for _ in range(3):
+        g = torch.full((V, d), 0.25, device="cuda")
+        k.embed_bwd(ids, dx, g)
+        runs.append(g)
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+    ok = (ids >= 0) & (ids < V)
+    ref = torch.full((V, d), 0.25, device="cuda", dtype=torch.float64).index_add_(0, ids[ok].long(), dx[ok].double())
+    assert near(runs[0], ref.float(), 1e-5, 1e-5)[0]
+    # rows are added in token order: equal to a sequential fp32 sum for one id
+    first = int(ids[ok][0])
+    seq = torch.tensor(0.0, device="cuda").expand(d).clone()
+    for t in torch.nonzero(ids == first).flatten().tolist():
+        seq = seq + dx[t]
+    assert torch.equal(runs[0][first], 0.25 + seq) or near(runs[0][first], 0.25 + seq, 1e-6, 1e-6)[0]
