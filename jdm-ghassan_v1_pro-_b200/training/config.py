@@ -115,6 +115,7 @@ class TrainerConfig:
     weight_ema: float = 0.0           # > 0: keep an exponential moving average of the weights with this decay
     fuse_micro_batches: int = 0       # micro-batches run as one forward/backward pass (same gradient sum); 0 = choose
     cuda_graphs: bool = True
+    heartbeat_stale_s: float = 600.0  # multi-rank: a peer without progress for this long (or one that posted a failure) ends the run; 0 = off
     step_deadline_s: float = 0.0      # > 0: a host watchdog ends the process when no step finishes within this many seconds
     compute_dtype: str = ""           # "" = derive from precision/gemm_fp16; fp16 | bf16
 
@@ -281,6 +282,7 @@ class TrainerConfig:
         t.fuse_micro_batches = max(0, c.get_int("b200.fuse_micro_batches", t.fuse_micro_batches))
         t.cuda_graphs = c.get_bool("b200.cuda_graphs", t.cuda_graphs)
         t.step_deadline_s = max(0.0, c.get_float("b200.step_deadline_s", t.step_deadline_s))
+        t.heartbeat_stale_s = max(0.0, c.get_float("b200.heartbeat_stale_s", t.heartbeat_stale_s))
         t.compute_dtype = c.get_str("b200.compute_dtype", t.compute_dtype)
         if t.compute_dtype not in ("", "fp16", "bf16"):
             raise ConfigError("b200.compute_dtype must be fp16 or bf16")

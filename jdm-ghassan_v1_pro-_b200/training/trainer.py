@@ -20,7 +20,7 @@ import torch
 from ..data.loader import RANK_SEED_STRIDE, DataLoader, Prefetcher, state_from_dict, state_to_dict
 from ..models.config import ModelConfig
 from ..utils.log import (human_bytes, human_count, human_duration, log_debug, log_error, log_info, log_warn)
-from ..parallel.watchdog import StepWatchdog
+from ..parallel.watchdog import PeerFailure, StepWatchdog
 from ..utils.telemetry import PERF, STOP, PhaseTimers
 from . import checkpoint as C
 from .config import TrainerConfig
@@ -53,6 +53,7 @@ class Trainer:
         self.skipped_steps = 0
         self.total_steps = 0
         self.stopped_by_signal = False
+        self.heartbeat = None           # set by run() when there are peers (parallel/watchdog.py)
         self.phases = PhaseTimers(cuda=getattr(self.engine, "kind", "") == "cuda")
         self.writer = C.CheckpointWriter()
         self.jsonl_path = os.environ.get("GB200_JSONL", "")
@@ -521,8 +522,21 @@ class Trainer:
         watchdog = None
         if deadline > 0:                         # host thread: ends the process when a step (a peer) never arrives
             watchdog = StepWatchdog(deadline, describe=lambda: "rank %d step %d/%d" % (self.rank, self.state.step, self.total_steps)).start()
+        if self.world > 1 and c.heartbeat_stale_s > 0:
+            # liveness through the job's key-value store: a peer that failed or left is reported here, on the host,
+            # before this rank launches another collective towards it
+            import torch.distributed as tdist
+            from ..parallel.watchdog import Heartbeat
+            store = tdist.PrefixStore("gb200_heartbeat", tdist.distributed_c10d._get_default_store())
+            self.heartbeat = Heartbeat(store, self.rank, self.world, stale_s=c.heartbeat_stale_s)
         try:
             while self.state.step < self.total_steps:
+                if self.heartbeat is not None:
+                    self.heartbeat.beat()
+                    try:
+                        self.heartbeat.check()
+                    except PeerFailure as pf:
+                        raise TrainerError("peer failure before step %d: %s" % (self.state.step + 1, pf))
                 res, lr, dt = self.train_step()
                 loss = res.loss
                 if watchdog is not None:
@@ -574,6 +588,13 @@ class Trainer:
             elif not (c.save_every > 0 and self.state.step % c.save_every == 0):
                 self.save("last.ckpt")
             self.writer.wait()
+        except BaseException as e:
+            if self.heartbeat is not None and not isinstance(e, TrainerError):
+                try:
+                    self.heartbeat.fail("%s: %s" % (type(e).__name__, e))
+                except Exception:
+                    pass
+            raise
         finally:
             if watchdog is not None:
                 watchdog.stop()

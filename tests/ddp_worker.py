@@ -85,6 +85,33 @@ def main():
             code = 17
         tr.prefetch.stop()
         os._exit(code)
+    if mode == "peer_raises":
+        # rank 1 fails at the start of its third step (nothing of its own in flight); rank 0 dawdles after its second
+        # step, so its next look at the heartbeat store finds the failure before it launches another collective
+        import time
+        from ghassan_b200.training.trainer import TrainerError
+        orig = tr.train_step
+        calls = [0]
+
+        def step():
+            calls[0] += 1
+            if rank == 1 and calls[0] == 3:
+                raise RuntimeError("injected: device lost on rank 1")
+            r = orig()
+            if rank == 0 and calls[0] == 2:
+                time.sleep(1.5)
+            return r
+        tr.train_step = step
+        code = 0
+        try:
+            tr.run()
+        except TrainerError as e:
+            open(os.path.join(out, "rank%d.err" % rank), "w").write("TrainerError: " + str(e)[:300])
+            code = 22
+        except RuntimeError as e:
+            open(os.path.join(out, "rank%d.err" % rank), "w").write("RuntimeError: " + str(e)[:300])
+            code = 21
+        os._exit(code)
     if mode == "resume":
         tr.run()
     else:

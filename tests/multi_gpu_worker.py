@@ -229,6 +229,23 @@ def bench_sync(work, total=1_036_995_840):
     e1.record()
     torch.cuda.synchronize()
     fused_ms = e0.elapsed_time(e1) / iters
+    # the two phases on their own (events around each kernel of one more run of exchanges)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(iters)]
+    for k, e in enumerate(range(4 + iters, 4 + 2 * iters)):
+        a.epoch = e
+        be += 1
+        C.barrier(tC, rank, world, be)
+        ev[k][0].record()
+        C.reduce(a)
+        ev[k][1].record()
+        C.update(a)
+        ev[k][2].record()
+        be += 1
+        C.barrier(tC, rank, world, be)
+        ev[k][3].record()
+    torch.cuda.synchronize()
+    reduce_ms = sum(x[0].elapsed_time(x[1]) for x in ev) / iters
+    update_ms = sum(x[1].elapsed_time(x[2]) for x in ev) / iters
     g2 = torch.randn(total, device=dev)
     for _ in range(2):
         dist.all_reduce(g2)
@@ -240,9 +257,9 @@ def bench_sync(work, total=1_036_995_840):
     e1.record()
     torch.cuda.synchronize()
     nccl_ms = e0.elapsed_time(e1) / iters
-    t = torch.tensor([fused_ms, nccl_ms], device=dev, dtype=torch.float64)
+    t = torch.tensor([fused_ms, nccl_ms, reduce_ms, update_ms], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    fused_ms, nccl_ms = float(t[0]), float(t[1])
+    fused_ms, nccl_ms, reduce_ms, update_ms = (float(x) for x in t)
     # bytes that must cross NVLink per rank: read (W-1) peers' shard as fp32, write the shard as 16-bit to (W-1) peers
     nv_in = (world - 1) * shard * 4
     nv_out = (world - 1) * (shard * 2 + min(shard, a.f32_end) * 4 / world)
@@ -250,7 +267,8 @@ def bench_sync(work, total=1_036_995_840):
     roof_ms = max(nv_in, nv_out) / link * 1e3
     if rank == 0:
         print(json.dumps({"bench": "fused_grad_sync", "world": world, "elements": total, "fused_ms": fused_ms,
-                          "nccl_allreduce_only_ms": nccl_ms, "nvlink_in_bytes_per_rank": nv_in,
+                          "nccl_allreduce_only_ms": nccl_ms, "reduce_scatter_phase_ms": reduce_ms,
+                          "update_allgather_phase_ms": update_ms, "nvlink_in_bytes_per_rank": nv_in,
                           "nvlink_out_bytes_per_rank": nv_out, "roofline_ms_at_770GBs": roof_ms,
                           "fraction_of_roofline": roof_ms / fused_ms,
                           "note": "fused = barrier + reduce-scatter + norm + mailbox + Lion update + 16-bit all-gather + "

@@ -128,3 +128,15 @@ def test_a_rank_that_leaves_between_steps_is_an_error_not_a_hang(data_dir, tmp_p
     assert res[1][0] == 0                      # the leaving rank exits cleanly
     assert res[0][0] == 17, res[0][1][-1500:]  # the survivor got an exception from its next collective
     assert os.path.exists(os.path.join(out, "rank0.err"))
+
+
+def test_a_failed_rank_is_reported_through_the_heartbeat_before_the_next_collective(data_dir, tmp_path):
+    import time
+    out = str(tmp_path)
+    t0 = time.time()
+    res = _launch(2, [out, data_dir, 6, "peer_raises"], extra_env={"PG_TIMEOUT_S": "60"}, timeout=120)
+    assert res[1][0] == 21 and "injected" in open(os.path.join(out, "rank1.err")).read()
+    assert res[0][0] == 22, res[0][1][-1500:]
+    msg = open(os.path.join(out, "rank0.err")).read()
+    assert "peer failure before step 3" in msg and "rank 1" in msg and "device lost" in msg
+    assert time.time() - t0 < 45                      # learned on the host, not through the 60 s collective timeout
