@@ -72,7 +72,7 @@ def main():
             return 3
     if mode == "heartbeat":                 # rank 1 leaves between steps; rank 0 learns of it before its next collective
         e = init_process_group("gloo", timeout_s=30)
-        store = dist.TCPStore(e.master_addr, e.master_port + 1, world, rank == 0, timeout=datetime.timedelta(seconds=30))
+        store = dist.PrefixStore("hb_test", dist.distributed_c10d._get_default_store())    # the job's own store
         hb = Heartbeat(store, rank, world, stale_s=30)
         t = torch.ones(1)
         for step in range(3):
