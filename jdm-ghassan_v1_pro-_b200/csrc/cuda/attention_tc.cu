@@ -115,7 +115,20 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_co
                                                                  const AttnTcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t TILE = AT_M * HD * 2;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem;
+  if constexpr (HD == 64) {
+    // 112 KB of tiles + barriers and not a byte more: two CTAs of this kernel share an SM (143 registers, 256 TMEM
+    // columns each), which hides the latency of the short causal loops at T = 512.  That leaves no slack to align
+    // the base by hand; the kernel has no static shared memory, so the dynamic window starts 1024-aligned.  Checked,
+    // not assumed: a misaligned base reports and returns before any barrier or TMEM is touched.
+    if (smem_u32(smem_raw) & 1023u) {
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);
+      return;
+    }
+    smem = smem_raw;
+  } else {
+    smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE;            // 2 stages
   uint8_t* sV = sK + 2 * TILE;        // 2 stages
@@ -695,11 +708,13 @@ int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   AttnTcParams p{};
   p.B = a->B; p.T = a->T; p.H = a->H; p.KV = a->KV; p.window = a->window; p.scale = a->scale;
   p.lo = lo; p.o = a->o; p.ld_o = a->ld_o; p.lse = a->lse; p.status = status;
-  constexpr size_t smem = (size_t)AT_M * HD * 2 * 5 + AT_M * AT_N * 2 + 128 + 1024;
+  constexpr size_t smem = (size_t)AT_M * HD * 2 * 5 + AT_M * AT_N * 2 + 128 + (HD == 64 ? 0 : 1024);
   auto kern = attn_tc_fwd_kernel<T, HD>;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -10;
+    // the largest shared-memory carve-out, so that two 112 KB CTAs fit one SM
+    (void)cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr = true;
   }
   dim3 grid((a->T + AT_M - 1) / AT_M, a->H, a->B);

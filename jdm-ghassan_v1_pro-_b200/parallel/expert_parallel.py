@@ -27,7 +27,8 @@ from ..ops import gemm as G
 from ..ops import kernels as K
 from .grad_sync import LocalBuffers, SymmetricBuffers
 
-BARRIER_SPINS = 200 * 1000 * 1000        # ~10 s: ranks may drift by a data-loader stall, not by more
+BARRIER_SPINS = 20 * 1000 * 1000         # polls of roughly half a microsecond each: about ten seconds; ranks may drift by a
+                                         # data-loader stall, not by more
 
 
 class ExpertParallel:

@@ -53,10 +53,14 @@ class PhaseTimers:
         self.wall: Dict[str, float] = defaultdict(float)
         self._open: Dict[str, object] = {}
         self.enabled = True
+        # GB200_NVTX=1: every phase is also an NVTX range, so a timeline profiler shows the step's structure
+        self.nvtx = self.cuda and os.environ.get("GB200_NVTX", "") == "1"
 
     def start(self, phase: str):
         if not self.enabled:
             return
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(phase)
         if self.cuda and phase != "load":
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
@@ -67,6 +71,8 @@ class PhaseTimers:
     def stop(self, phase: str):
         if not self.enabled or phase not in self._open:
             return
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         t0 = self._open.pop(phase)
         if self.cuda and phase != "load":
             ev = torch.cuda.Event(enable_timing=True)
