@@ -8,7 +8,8 @@
     python -m ghassan_b200.cli.infer tokenize  --model model.gguf --text "شنو خبارك"
     python -m ghassan_b200.cli.infer export    --checkpoint last.ckpt --tokenizer tok.gtok --out model.gguf [--profile fp16|q8_k|q4_0] [--compat native|llama|llama_moe]
     python -m ghassan_b200.cli.infer eval      --model model.gguf [--suite dir] [--persona en]
-    python -m ghassan_b200.cli.infer perplexity --model model.gguf (--text "held out" | --shards dir --prefix val_)
+    python -m ghassan_b200.cli.infer perplexity --model model.gguf (--text "held out" | --shards dir --prefix val)
+                                                [--seq-len 512 --batches 20] [--rope-scale s] [--yarn-mscale m]
     python -m ghassan_b200.cli.infer devices
     python -m ghassan_b200.cli.infer logits    --model model.gguf --prompt "salam" [--out logits.f32]
 
@@ -36,7 +37,8 @@ def _parser() -> argparse.ArgumentParser:
         ap.add_argument("--" + name)
     for name, typ in (("temp", float), ("top-k", int), ("top-p", float), ("min-p", float), ("repeat", float),
                       ("no-repeat-ngram", int), ("max-tokens", int), ("seed", int), ("tokens", int), ("prompt-tokens", int),
-                      ("ctx", int), ("batch", int), ("max-prompts", int)):
+                      ("ctx", int), ("batch", int), ("max-prompts", int), ("seq-len", int), ("batches", int),
+                      ("batch-size", int), ("rope-scale", float), ("yarn-mscale", float)):
         ap.add_argument("--" + name, type=typ)
     for name in ("greedy", "no-adaptive", "no-stream", "retrieve-direct", "stats", "verbose"):
         ap.add_argument("--" + name, action="store_true")
@@ -70,6 +72,12 @@ def _load(a, batch=1, ctx=0):
     if not a.model:
         raise SystemExit("--model is required")
     m = IO.load_model(a.model, a.tokenizer or "")
+    if a.rope_scale is not None or a.yarn_mscale is not None:      # run-time context extension (perplexity sweeps)
+        if a.rope_scale is not None:
+            m.cfg.rope_scale = float(a.rope_scale)
+        if a.yarn_mscale is not None:
+            m.cfg.rope_yarn_mscale = float(a.yarn_mscale)
+        m.cfg.validate()
     eng = IO.build_engine(m, batch=batch, max_len=ctx or min(2048, m.cfg.max_seq_len), fmt=a.format or "auto")
     return m, Generator(eng, m.tokenizer)
 
@@ -186,8 +194,20 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 0
     if cmd == "perplexity":
         from ..inference import evaluate as E
-        r = E.perplexity_text(gen, a.text) if a.text else E.perplexity_shards(gen, a.shards, a.prefix or "val_")
-        print("  tokens %d | nll %.4f | perplexity %.3f" % (r["tokens"], r["nll"], r["perplexity"]))
+        seq_len, batches, bs = a.seq_len or 512, a.batches or 20, a.batch_size or 1
+        if seq_len <= 0 or batches <= 0 or bs <= 0:
+            raise SystemExit("perplexity options must be positive")
+        if a.text:
+            r = E.perplexity_text(gen, a.text)
+        elif a.shards:
+            r = E.perplexity_shards(gen, a.shards, a.prefix or "val", max_tokens=batches * bs * seq_len, window=seq_len)
+        else:
+            raise SystemExit("perplexity requires --text or --shards")
+        print("  rope_scale  : %.3f" % m.cfg.rope_scale)
+        print("  yarn_mscale : %.3f" % m.cfg.rope_mscale())
+        print("  mean_nll    : %.8f" % r["nll"])
+        print("  perplexity  : %.6f" % r["perplexity"])
+        print("  tokens      : %d" % r["tokens"])
         return 0
     if cmd == "eval":
         from ..data.tokenizer import SYSTEM_ENGLISH

@@ -404,9 +404,11 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ scratch, int 
 // ---------------------------------------------------------------------------------------------- fused decode step
 // Fewer, fatter kernels for the token step: at batch 1 every kernel costs a few microseconds however little it does.
 //   gemv_norm:            RMSNorm of the fp32 residual inside the GEMV (every block normalises the row it needs)
-//   swiglu_norm_route:    RMSNorm + router (soft-max, bias-steered top-k) + gate/up rows of the selected experts
+//   route_norm:           RMSNorm + router (soft-max, bias-steered top-k), one block per token
+//   swiglu_norm:          RMSNorm + gate/up rows of the selected experts
 //   qk_rope_append:       QK-norm + RoPE; k heads land in the cache slot, v heads are copied beside them
-//   decode_attn (fused):  the last split to finish merges the partial results (ticket), no merge launch
+//   decode_attn (ticket): the last split to finish merges the partial results; measured slower than the separate
+//                         merge launch (the merge is a serial tail of the longest block), so the engine does not use it
 // Rounding points are those of the separate kernels (normalised activations pass through 16 bits), so both routes
 // give the same numbers.
 
@@ -512,33 +514,45 @@ __device__ __forceinline__ void route_in_block(const XT* __restrict__ xs, const 
   __syncthreads();
 }
 
-// grid (ceil(E / rows per block), B * slots).  rw == nullptr: dense feed-forward (one "expert" 0, no routing).
+// Router of a token on its own: RMSNorm of the fp32 row + soft-max + bias-steered top-k; one block per token.  (Doing
+// this inside every gate/up block was measured: thousands of blocks re-reading the router weights cost more than
+// the launch it saved.)
+template <typename XT>
+__global__ void __launch_bounds__(GV_THREADS) route_norm_kernel(const float* __restrict__ x32, const float* __restrict__ norm_w,
+                                                               float eps, const float* __restrict__ rw,
+                                                               const float* __restrict__ bias, int d, int ne, int top_k,
+                                                               int* __restrict__ idx_out, float* __restrict__ w_out) {
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t gv_dyn[];
+  XT* xs = reinterpret_cast<XT*>(gv_dyn);
+  __shared__ float lg[64];
+  __shared__ int esel[8];
+  __shared__ float wsel[8];
+  const int b = blockIdx.x;
+  if ((threadIdx.x >> 5) == 0) norm_row_to_smem<XT>(x32 + (long long)b * d, norm_w, xs, d, eps);
+  __syncthreads();
+  route_in_block<XT>(xs, rw, bias, d, ne, top_k, lg, esel, wsel);
+  if (threadIdx.x < top_k) {
+    idx_out[b * top_k + threadIdx.x] = esel[threadIdx.x];
+    w_out[b * top_k + threadIdx.x] = wsel[threadIdx.x];
+  }
+}
+
+// grid (ceil(E / rows per block), B * slots).  idx == nullptr: dense feed-forward (one "expert" 0).
 template <int FMT, int KS, typename XT>
-__global__ void __launch_bounds__(GV_THREADS) swiglu_norm_route_kernel(
+__global__ void __launch_bounds__(GV_THREADS) swiglu_norm_kernel(
     const uint8_t* __restrict__ Wg, const uint8_t* __restrict__ Wu, long long row_bytes, int ne, int E, int d,
-    const float* __restrict__ x32, const float* __restrict__ norm_w, float eps, const float* __restrict__ rw,
-    const float* __restrict__ bias, int top_k, int slots, int* __restrict__ idx_out, float* __restrict__ w_out,
-    XT* __restrict__ act) {
+    const float* __restrict__ x32, const float* __restrict__ norm_w, float eps, const int* __restrict__ idx, int top_k,
+    int slots, XT* __restrict__ act) {
   pdl_wait();
   extern __shared__ __align__(16) uint8_t gv_dyn[];
   XT* xs = reinterpret_cast<XT*>(gv_dyn);                 // [d]
   __shared__ float sm[2 * GV_WARPS];
-  __shared__ float lg[64];
-  __shared__ int esel[8];
-  __shared__ float wsel[8];
   const int warp = threadIdx.x >> 5, ric = warp / KS, ks = warp % KS;
   const int b = blockIdx.y / slots, slot = blockIdx.y % slots;
   if (warp == 0) norm_row_to_smem<XT>(x32 + (long long)b * d, norm_w, xs, d, eps);
   __syncthreads();
-  int e = 0;
-  if (rw) {
-    route_in_block<XT>(xs, rw, bias, d, ne, top_k, lg, esel, wsel);
-    e = slot < top_k ? esel[slot] : ne;
-    if (blockIdx.x == 0 && slot == 0 && threadIdx.x < top_k) {
-      idx_out[b * top_k + threadIdx.x] = esel[threadIdx.x];
-      w_out[b * top_k + threadIdx.x] = wsel[threadIdx.x];
-    }
-  }
+  const int e = idx ? (slot < top_k ? idx[b * top_k + slot] : ne) : 0;
   const int j = blockIdx.x * (GV_WARPS / KS) + ric;
   const bool live = j < E && e >= 0 && e <= ne;
   float g[1] = {0.f}, u[1] = {0.f};
@@ -811,13 +825,27 @@ extern "C" int gb_gemv_norm(const void* W, int fmt, int N, int K, const float* x
   return gb_launch_rc();
 }
 
-// RMSNorm + router + gate/up of the selected experts.  router_w == nullptr: dense feed-forward (weights hold one block).
-extern "C" int gb_swiglu_norm_route(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const float* x32,
-                                    const float* norm_w, float eps, const float* router_w, const float* bias, int B, int top_k,
-                                    int shared, int* idx_out, float* w_out, void* act16, int is_bf16, cudaStream_t st) {
+// RMSNorm + router of x32 [B, d]: idx_out / w_out [B, top_k].
+extern "C" int gb_route_norm(const float* x32, const float* norm_w, float eps, const float* router_w, const float* bias, int B,
+                             int d, int ne, int top_k, int* idx_out, float* w_out, int is_bf16, cudaStream_t st) {
+  if (!x32 || !norm_w || !router_w || !idx_out || !w_out || B <= 0 || ne <= 0 || ne > 64 || top_k <= 0 || top_k > 8 ||
+      top_k > ne || (d % 8))
+    return -1;
+  const size_t smem = (size_t)d * 2;
+  if (smem > 40 * 1024) return -2;
+  cudaLaunchAttribute attr;
+  cudaLaunchConfig_t cfg = gb_pdl_config(dim3(B), dim3(GV_THREADS), smem, st, &attr);
+  if (is_bf16) (void)cudaLaunchKernelEx(&cfg, route_norm_kernel<__nv_bfloat16>, x32, norm_w, eps, router_w, bias, d, ne, top_k, idx_out, w_out);
+  else (void)cudaLaunchKernelEx(&cfg, route_norm_kernel<__half>, x32, norm_w, eps, router_w, bias, d, ne, top_k, idx_out, w_out);
+  return gb_launch_rc();
+}
+
+// RMSNorm + gate/up of the experts named by idx [B, top_k] (+ the shared one).  idx == nullptr: dense feed-forward.
+extern "C" int gb_swiglu_norm(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const float* x32, const float* norm_w,
+                              float eps, const int* idx, int B, int top_k, int shared, void* act16, int is_bf16,
+                              cudaStream_t st) {
   const long long rb = gb_wfmt_row_bytes(fmt, d);
   if (!Wg || !Wu || !x32 || !norm_w || !act16 || rb < 0 || B <= 0 || top_k <= 0 || top_k > 8 || (d % 8)) return -1;
-  if (router_w && (!idx_out || !w_out || ne <= 0 || ne > 64 || top_k > ne)) return -1;
   const size_t smem = (size_t)d * 2;
   if (smem > 40 * 1024) return -2;
   const int slots = top_k + (shared ? 1 : 0);
@@ -827,8 +855,8 @@ extern "C" int gb_swiglu_norm_route(const void* Wg, const void* Wu, int fmt, int
   do {                                                                                                               \
     cudaLaunchAttribute gb_attr_;                                                                                    \
     cudaLaunchConfig_t gb_cfg_ = gb_pdl_config(dim3((E + GV_WARPS / KS - 1) / (GV_WARPS / KS), B * slots), dim3(GV_THREADS), smem, st, &gb_attr_); \
-    (void)cudaLaunchKernelEx(&gb_cfg_, (swiglu_norm_route_kernel<F, KS, XT>), g, u, rb, ne, E, d, x32, norm_w, eps, router_w, \
-                             bias, top_k, slots, idx_out, w_out, (XT*)act16);                                        \
+    (void)cudaLaunchKernelEx(&gb_cfg_, (swiglu_norm_kernel<F, KS, XT>), g, u, rb, ne, E, d, x32, norm_w, eps, idx, top_k, slots, \
+                             (XT*)act16);                                                                            \
   } while (0)
 #define CALL(F)                                                                                     \
   if (is_bf16) { if (split) SWN_GO(F, 4, __nv_bfloat16); else SWN_GO(F, 1, __nv_bfloat16); }        \

@@ -129,7 +129,7 @@ typedef struct gb_moe_args {
   const float* dyn_aux_coef;         // device copy of aux_coef (overrides it)
   float* part2;                      // scratch [GB_ROUTER_WGRAD_CHUNKS, ne, d] for the router weight gradient, or NULL
 } gb_moe_args;
-#define GB_ROUTER_WGRAD_CHUNKS 32
+#define GB_ROUTER_WGRAD_CHUNKS 256
 int gb_moe_num_blocks(int n_tok);
 int gb_moe_capacity(int n_tok, int ne, int top_k, int shared);
 int gb_moe_route(const gb_moe_args* a, cudaStream_t st);          // router + top-k + histograms

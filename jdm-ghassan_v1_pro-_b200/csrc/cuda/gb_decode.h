@@ -82,11 +82,13 @@ int gb_sample(const gb_sample_args* a, cudaStream_t st);
 // out = W @ rmsnorm(x32) for fp32 rows x32 [B, K]; returns -2 when B*K*2 bytes do not fit the shared-memory budget.
 int gb_gemv_norm(const void* W, int fmt, int N, int K, const float* x32, int ldx32, const float* norm_w, float eps, int B,
                  void* out, int ldo, int out_f32, int is_bf16, cudaStream_t st);
-// act = SwiGLU(gate, up) of the experts the router picks for rmsnorm(x32); writes the picks to idx_out / w_out.
-// router_w == NULL: dense feed-forward block (no routing, nothing written to idx_out / w_out).
-int gb_swiglu_norm_route(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const float* x32, const float* norm_w,
-                         float eps, const float* router_w, const float* bias, int B, int top_k, int shared, int* idx_out,
-                         float* w_out, void* act16, int is_bf16, cudaStream_t st);
+// Router of rmsnorm(x32) [B, d]: picks to idx_out / w_out [B, top_k].
+int gb_route_norm(const float* x32, const float* norm_w, float eps, const float* router_w, const float* bias, int B, int d,
+                  int ne, int top_k, int* idx_out, float* w_out, int is_bf16, cudaStream_t st);
+// act = SwiGLU(gate, up) of the experts named by idx [B, top_k] (+ the shared one) applied to rmsnorm(x32).
+// idx == NULL: dense feed-forward block.
+int gb_swiglu_norm(const void* Wg, const void* Wu, int fmt, int ne, int E, int d, const float* x32, const float* norm_w, float eps,
+                   const int* idx, int B, int top_k, int shared, void* act16, int is_bf16, cudaStream_t st);
 // QK-norm + RoPE of the fused projection; q to q_out, k and v into the cache slot of the step (slot_pos updated).
 int gb_qk_rope_append(const void* qkv, long long ld_in, void* q_out, long long ld_q, const float* qw, const float* kw,
                       const float* cos_sin, const int* pos, void* cacheK, void* cacheV, int* slot_pos,

@@ -419,7 +419,18 @@ __global__ void moe_router_wgrad_kernel(const float* __restrict__ dlogit, const 
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  for (int t = ta; t < tb; ++t) {
+  int t = ta;
+  for (; t + 4 <= tb; t += 4) {        // four tokens' loads in flight; the additions keep token order
+    float xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) xv[u] = Cvt<T>::to_f(x16[(size_t)(t + u) * d + c]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (e0 + j < ne) acc[j] += dlogit[(size_t)(t + u) * ne + e0 + j] * xv[u];
+  }
+  for (; t < tb; ++t) {
     const float xv = Cvt<T>::to_f(x16[(size_t)t * d + c]);
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -523,7 +534,7 @@ extern "C" int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st) {
   if (rc) return rc;
   const int grid = (a->n_tok + 7) / 8;
   // token chunks for the router weight gradient: partials in part2 ([chunks, ne, d]) when it is provided
-  int chunks = a->part2 ? (a->n_tok + 31) / 32 : 1;
+  int chunks = a->part2 ? (a->n_tok + 31) / 32 : 1;   // 32 tokens per thread: 8192 tokens fill 1536 blocks
   if (chunks > GB_ROUTER_WGRAD_CHUNKS) chunks = GB_ROUTER_WGRAD_CHUNKS;
   dim3 g2((a->d + 127) / 128, chunks, (a->ne + 7) / 8);
   float* wout = chunks > 1 ? a->part2 : a->d_router_w;

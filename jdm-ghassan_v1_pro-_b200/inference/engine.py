@@ -76,8 +76,8 @@ class InferenceEngine:
         if cfg.head_dim not in (32, 64, 128):
             raise ValueError("decode attention supports head_dim 32, 64 and 128")
         self.cfg, self.B, self.cap = cfg, batch, max_len
-        # six launches per layer instead of eleven (norms, router, cache append and split merge folded into their
-        # consumers); the separate kernels remain for shapes whose rows do not fit the shared-memory budget
+        # eight launches per layer instead of eleven (both norms and the cache append folded into their consumers);
+        # the separate kernels remain for shapes whose rows do not fit the shared-memory budget
         self.fused = bool(fused_step) and D.gemv_norm_fits(batch, cfg.hidden_size)
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.dt = compute_dtype
@@ -194,17 +194,17 @@ class InferenceEngine:
             D.gemv_norm(L.wqkv, x_in, L.attn_norm, cfg.rms_eps, self.qkv, bf)
             D.qk_rope_append(self.qkv, self.qk, L.qn, L.kn, self.cos_sin, self.pos, L.cK, L.cV, self.slot_pos, self.state,
                              Hh, KV, hd, self.cap, PINNED_TOKENS, cfg.rms_eps, cfg.rope_type)
-            D.decode_attn_fused(self.qk[:, :qd], L.cK, L.cV, self.slot_pos, self.state, self.att, self.att_scratch,
-                                self.att_ticket, self.splits, Hh, KV, hd, self.cap, cfg.sliding_window, cfg.attn_scale())
+            D.decode_attn(self.qk[:, :qd], L.cK, L.cV, self.slot_pos, self.state, self.att, self.att_scratch, self.splits,
+                          Hh, KV, hd, self.cap, cfg.sliding_window, cfg.attn_scale())
             D.gemv(L.wo, self.att, self.x_mid, addend=x_in)
             if cfg.use_moe:
-                D.swiglu_norm_route(L.wg, L.wu, cfg.num_experts, self.E, d, self.x_mid, L.ffn_norm, cfg.rms_eps, L.router,
-                                    L.bias, cfg.moe_top_k, cfg.moe_shared, self.r_idx, self.r_w, self.act)
+                D.route_norm(self.x_mid, L.ffn_norm, cfg.rms_eps, L.router, L.bias, cfg.moe_top_k, self.r_idx, self.r_w, bf)
+                D.swiglu_norm(L.wg, L.wu, cfg.num_experts, self.E, d, self.x_mid, L.ffn_norm, cfg.rms_eps, self.r_idx,
+                              cfg.moe_top_k, cfg.moe_shared, self.act)
                 D.expert_down(L.wd, cfg.num_experts, d, self.E, self.act, self.r_idx, self.r_w, cfg.moe_top_k, cfg.moe_shared,
                               self.x_mid, x_out)
             else:
-                D.swiglu_norm_route(L.wg, L.wu, 0, self.E, d, self.x_mid, L.ffn_norm, cfg.rms_eps, None, None, 1, False,
-                                    None, None, self.act)
+                D.swiglu_norm(L.wg, L.wu, 0, self.E, d, self.x_mid, L.ffn_norm, cfg.rms_eps, None, 1, False, self.act)
                 D.expert_down(L.wd, 0, d, self.E, self.act, self.dense_idx, self.dense_w, 1, False, self.x_mid, x_out)
             return
         K.rmsnorm_fwd(x_in, L.attn_norm, self.xb, self.rr, cfg.rms_eps)

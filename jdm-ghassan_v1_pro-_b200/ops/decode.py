@@ -165,14 +165,22 @@ def gemv_norm(w: QWeight, x32, norm_w, eps, out, is_bf16=False):
     return out
 
 
-def swiglu_norm_route(wg: QWeight, wu: QWeight, ne, E, d, x32, norm_w, eps, router_w, bias, top_k, shared, idx, w, act):
-    """RMSNorm + router + gate/up of the selected experts in one launch; ``router_w=None`` for a dense block."""
-    rc = _lib.lib().gb_swiglu_norm_route(c_vp(wg.data.data_ptr()), c_vp(wu.data.data_ptr()), c_int(wg.fmt), c_int(ne), c_int(E),
-                                         c_int(d), c_vp(x32.data_ptr()), c_vp(norm_w.data_ptr()), c_float(eps),
-                                         _lib.ptr(router_w), _lib.ptr(bias), c_int(x32.shape[0]), c_int(top_k),
-                                         c_int(int(shared)), _lib.ptr(idx), _lib.ptr(w), c_vp(act.data_ptr()),
-                                         c_int(_bf(act)), _lib.stream_ptr())
-    _lib.check_rc(rc, "gb_swiglu_norm_route")
+def route_norm(x32, norm_w, eps, router_w, bias, top_k, idx, w, is_bf16=False):
+    """Router of ``rmsnorm(x32)``: one launch, one block per row."""
+    B, d = x32.shape
+    rc = _lib.lib().gb_route_norm(c_vp(x32.data_ptr()), c_vp(norm_w.data_ptr()), c_float(eps), c_vp(router_w.data_ptr()),
+                                  _lib.ptr(bias), c_int(B), c_int(d), c_int(router_w.shape[0]), c_int(top_k),
+                                  c_vp(idx.data_ptr()), c_vp(w.data_ptr()), c_int(int(is_bf16)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_route_norm")
+
+
+def swiglu_norm(wg: QWeight, wu: QWeight, ne, E, d, x32, norm_w, eps, idx, top_k, shared, act):
+    """RMSNorm + gate/up of the experts in ``idx`` (``None``: dense block) in one launch."""
+    rc = _lib.lib().gb_swiglu_norm(c_vp(wg.data.data_ptr()), c_vp(wu.data.data_ptr()), c_int(wg.fmt), c_int(ne), c_int(E),
+                                   c_int(d), c_vp(x32.data_ptr()), c_vp(norm_w.data_ptr()), c_float(eps), _lib.ptr(idx),
+                                   c_int(x32.shape[0]), c_int(top_k), c_int(int(shared)), c_vp(act.data_ptr()),
+                                   c_int(_bf(act)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_swiglu_norm")
 
 
 def qk_rope_append(qkv, q_out, qw, kw, cos_sin, pos, cacheK, cacheV, slot_pos, state, H, KV, hd, cap, pinned, eps, rope_type):

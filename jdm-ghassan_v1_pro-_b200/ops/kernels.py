@@ -47,7 +47,7 @@ class MoeArgs(ctypes.Structure):
                 ("aux_m", c_void_p), ("part", c_void_p), ("aux_acc", c_void_p), ("dyn_seed", c_void_p),
                 ("dyn_aux_coef", c_void_p), ("part2", c_void_p)]
 
-ROUTER_WGRAD_CHUNKS = 32
+ROUTER_WGRAD_CHUNKS = 256
 
 
 class OptArgs(ctypes.Structure):

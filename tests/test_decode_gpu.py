@@ -101,6 +101,8 @@ def test_kv_ring_and_decode_attention(hd, H, KV):
     pos = torch.zeros(B, dtype=torch.int32, device="cuda")
     scratch = torch.zeros(B * H * 4 * (hd + 2), device="cuda")
     out = torch.zeros(B, qd, device="cuda", dtype=torch.float16)
+    out_t, scratch_t = torch.zeros_like(out), torch.zeros_like(scratch)
+    ticket = torch.zeros(B * KV, dtype=torch.int32, device="cuda")
     ks, vs = [], []
     scale = 1.0 / math.sqrt(hd)
     for t in range(steps):
@@ -111,6 +113,9 @@ def test_kv_ring_and_decode_attention(hd, H, KV):
         vs.append(v)
         D.kv_append(k, v, cK, cV, slot_pos, state, cap, pinned)
         D.decode_attn(q, cK, cV, slot_pos, state, out, scratch, 4, H, KV, hd, cap, 0, scale)
+        # the variant whose last split merges the partial results gives the same bits
+        D.decode_attn_fused(q, cK, cV, slot_pos, state, out_t, scratch_t, ticket, 4, H, KV, hd, cap, 0, scale)
+        assert torch.equal(out, out_t) and int(ticket.abs().sum()) == 0
         D.decode_advance(state, pos, cap, pinned)
         # the cache must hold the first `pinned` tokens and the most recent cap - pinned ones
         live = list(range(min(t + 1, pinned))) + [j for j in range(max(pinned, t + 1 - (cap - pinned)), t + 1)]
