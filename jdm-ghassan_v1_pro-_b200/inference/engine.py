@@ -15,6 +15,8 @@ candidates back for every token.  Here:
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
@@ -78,7 +80,8 @@ class InferenceEngine:
         self.cfg, self.B, self.cap = cfg, batch, max_len
         # eight launches per layer instead of eleven (both norms and the cache append folded into their consumers);
         # the separate kernels remain for shapes whose rows do not fit the shared-memory budget
-        self.fused = bool(fused_step) and D.gemv_norm_fits(batch, cfg.hidden_size)
+        self.fused = (bool(fused_step) and os.environ.get("GB200_DECODE_UNFUSED", "") != "1"
+                      and D.gemv_norm_fits(batch, cfg.hidden_size))
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.dt = compute_dtype
         raw_types = raw_types or {}
