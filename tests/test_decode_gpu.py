@@ -42,23 +42,42 @@ def test_gemv_matches_dequantised_product(fmt, B):
     assert err < {"f16": 1e-3, "bf16": 1e-2, "q8_0": 0.02, "q8_64": 0.02, "q4_0": 0.25, "q4_1": 0.2}[fmt]
 
 
+@pytest.mark.parametrize("B", [3, 1])
 @pytest.mark.parametrize("fmt", ["f16", "q8_0", "q4_1"])
-def test_expert_kernels(fmt):
+def test_expert_kernels(fmt, B):
+    """B = 1 takes the whole-row-per-warp kernels, larger batches the split-row ones."""
     D = _D()
-    ne, E, d, B, top_k = 4, 64, 96, 3, 2
+    ne, E, d, top_k = 4, 64, 96, 2
     f = D.FMT_NAMES[fmt]
     wg, wu = _rand((ne + 1) * E, d, seed=4, scale=0.2), _rand((ne + 1) * E, d, seed=5, scale=0.2)
     wdn = _rand((ne + 1) * d, E, seed=6, scale=0.2)
     qg, qu, qd = (D.QWeight.from_f32(t, f, "cuda") for t in (wg, wu, wdn))
     g, u, dn = (q.dequantize().cuda() for q in (qg, qu, qd))
     x = _rand(B, d, seed=7).cuda().half()
-    idx = torch.tensor([[1, 3], [0, 2], [3, 3]], dtype=torch.int32, device="cuda")
-    wt = torch.tensor([[0.7, 0.3], [0.5, 0.5], [0.9, 0.1]], device="cuda")
+    idx = torch.tensor([[1, 3], [0, 2], [3, 3]], dtype=torch.int32, device="cuda")[:B].contiguous()
+    wt = torch.tensor([[0.7, 0.3], [0.5, 0.5], [0.9, 0.1]], device="cuda")[:B].contiguous()
     resid = _rand(B, d, seed=8).cuda()
     act = torch.zeros(B, top_k + 1, E, device="cuda", dtype=torch.float16)
     out = torch.zeros(B, d, device="cuda")
     D.expert_swiglu(qg, qu, ne, E, d, x, idx, top_k, True, act)
     D.expert_down(qd, ne, d, E, act, idx, wt, top_k, True, resid, out)
+    # the fused forms: RMSNorm of an fp32 row inside the kernel (unit weight: x is the normalised row's source)
+    x32 = _rand(B, d, seed=9).cuda()
+    nw = 1.0 + 0.1 * _rand(d, seed=10).cuda()
+    xn = torch.empty(B, d, device="cuda", dtype=torch.float16)
+    from ghassan_b200.ops import kernels as KK
+    KK.rmsnorm_fwd(x32, nw, xn, torch.empty(B, device="cuda"), 1e-5)
+    act_a = torch.zeros_like(act)
+    act_b = torch.zeros_like(act)
+    D.expert_swiglu(qg, qu, ne, E, d, xn, idx, top_k, True, act_a)
+    D.swiglu_norm(qg, qu, ne, E, d, x32, nw, 1e-5, idx, top_k, True, act_b)
+    assert torch.allclose(act_a.float(), act_b.float(), rtol=2e-3, atol=2e-3)
+    o_a = torch.zeros(B, 200, device="cuda")
+    o_b = torch.zeros(B, 200, device="cuda")
+    qh = D.QWeight.from_f32(_rand(200, d, seed=11, scale=0.3), f, "cuda")
+    D.gemv(qh, xn, o_a)
+    D.gemv_norm(qh, x32, nw, 1e-5, o_b)
+    assert torch.allclose(o_a, o_b, rtol=2e-3, atol=2e-3)
     ref = resid.clone()
     for b in range(B):
         for s in range(top_k + 1):
