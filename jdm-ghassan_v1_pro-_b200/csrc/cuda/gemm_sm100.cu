@@ -167,6 +167,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // 2 KB per epilogue warp: a 32 x 32 block of 16-bit results is turned from "one row per lane" into "four lanes per
+  // row" before it goes to a per-tile destination (another GPU's memory likes 64-byte pieces, not 16-byte ones)
+  uint8_t* stage = smem + STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -303,6 +306,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[b][i]);
             const int col = t.n0 + (c0 + b) * 32;
             const int nvalid = p.N - col;
+            if constexpr (sizeof(OutT) == 2) {
+              if (p.tile_out != nullptr && nvalid >= 32) {      // warp-uniform: col and N are
+                uint4* ws = reinterpret_cast<uint4*>(stage + warp * 2048);
+                __syncwarp();
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                  uint4 q;
+                  q.x = Cvt<OutT>::pack2(v[8 * pp + 0], v[8 * pp + 1]);
+                  q.y = Cvt<OutT>::pack2(v[8 * pp + 2], v[8 * pp + 3]);
+                  q.z = Cvt<OutT>::pack2(v[8 * pp + 4], v[8 * pp + 5]);
+                  q.w = Cvt<OutT>::pack2(v[8 * pp + 6], v[8 * pp + 7]);
+                  ws[lane * 4 + (pp ^ ((lane >> 1) & 3))] = q;      // swizzled: quarter-warps hit eight bank groups
+                }
+                __syncwarp();
+                OutT* tbase = reinterpret_cast<OutT*>(p.tile_out[t.tm]);
+#pragma unroll
+                for (int it = 0; it < 4; ++it) {
+                  const int rr = it * 8 + (lane >> 2), part = lane & 3;
+                  const uint4 q = ws[rr * 4 + (part ^ ((rr >> 1) & 3))];
+                  const int grow = quarter * 32 + rr;
+                  if (t.a_row0 + grow < p.M)
+                    *reinterpret_cast<uint4*>(tbase + (long long)grow * p.ldo + col + part * 8) = q;
+                }
+                continue;
+              }
+            }
             if (row_ok && nvalid > 0) {
               if (arow) {
                 float a[32];
@@ -395,7 +424,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 template <int BN, int STAGES>
 constexpr size_t gemm_smem_bytes() {
-  return size_t(STAGES) * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  return size_t(STAGES) * (BM * BK * 2 + BN * BK * 2) + 256 /* barriers */ + 8 * 2048 /* epilogue staging */ + 1024;
 }
 
 }  // namespace gb
