@@ -54,9 +54,9 @@ def pick_block_n(M, N, mn_major=False):
     """Tile width.  A 128 x 256 tile reads 1.5 operand bytes per MMA where 128 x 128 reads 2, and one CTA's
     tcgen05 pipe at 128 x 128 is bound by shared-memory bandwidth: measured 1.5x faster at 256 once there are tiles
     for every SM.  Narrow tiles only when the problem would otherwise leave most of the 148 SMs idle; operands that
-    are both stored MN-major (weight gradients) measured fastest at 128."""
+    are both stored MN-major (weight gradients) want one and a half waves of 256-wide tiles before they gain."""
     tiles_m = (M + 127) // 128
-    if not mn_major and N % 256 == 0 and tiles_m * (N // 256) >= 120:
+    if N % 256 == 0 and tiles_m * (N // 256) >= (222 if mn_major else 120):
         return 256
     tiles128 = tiles_m * ((N + 127) // 128)
     if tiles128 < 100 and N % 64 == 0:
