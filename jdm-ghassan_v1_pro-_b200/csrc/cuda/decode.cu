@@ -628,171 +628,6 @@ __global__ void qk_rope_append_kernel(const T* __restrict__ qkv, long long ld_in
   }
 }
 
-// ---------------------------------------------------------------------------------------------- batch-1 fast path
-// One token: every weight row is a few hundred bytes, so what matters is how many loads a lane has in flight before
-// it needs the first one.  Here a warp owns R whole rows (no cross-warp reduction, no block barrier in the dot
-// product) and issues the loads of all of them unit by unit before any arithmetic; a block covers 8*R rows, so the
-// grid shrinks by 4*R against the split-row kernels while the bytes in flight per SM grow.
-template <typename XT>
-__device__ __forceinline__ void unit_to_f8(const XT* __restrict__ x, float (&f)[8]) {
-  const uint4 q = *reinterpret_cast<const uint4*>(x);
-  if constexpr (std::is_same<XT, __half>::value) {
-    const __half2* h = reinterpret_cast<const __half2*>(&q);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
-  } else {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
-  }
-}
-
-// acc[r] += row r . x for R stored rows (nullptr = skip); lanes stride over the 8-value units, sums stay per lane.
-template <int FMT, int R, typename XT>
-__device__ __forceinline__ void rows_partial(const uint8_t* const (&wrow)[R], int K, const XT* __restrict__ x, float (&acc)[R]) {
-  const int lane = threadIdx.x & 31;
-#pragma unroll 2
-  for (int u = lane; u < (K >> 3); u += 32) {
-    float w[R][8], xf[8];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (wrow[r]) load8<FMT>(wrow[r], u, w[r]);
-    unit_to_f8<XT>(x + 8 * u, xf);
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (wrow[r]) {
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s += w[r][i] * xf[i];
-        acc[r] += s;
-      }
-  }
-}
-
-constexpr int B1_R = 4;                      // rows per warp
-constexpr int B1_ROWS = GV_WARPS * B1_R;     // rows per block
-
-// out[row] = W[row] . x (+ addend[row]); x is either 16-bit activations (x16) or the fp32 residual to normalise first.
-template <int FMT, typename XT>
-__global__ void __launch_bounds__(GV_THREADS) gemv_b1_kernel(const uint8_t* __restrict__ W, long long row_bytes, int N, int K,
-                                                            const XT* __restrict__ x16, const float* __restrict__ x32,
-                                                            const float* __restrict__ norm_w, float eps,
-                                                            void* __restrict__ out, int out_f32, const float* __restrict__ addend) {
-  pdl_wait();
-  extern __shared__ __align__(16) uint8_t gv_dyn[];
-  const XT* x = x16;
-  if (x32) {                                  // fused RMSNorm: the block normalises the row into shared memory
-    XT* xs = reinterpret_cast<XT*>(gv_dyn);
-    if ((threadIdx.x >> 5) == 0) norm_row_to_smem<XT>(x32, norm_w, xs, K, eps);
-    __syncthreads();
-    x = xs;
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * B1_ROWS + warp * B1_R;
-  const uint8_t* wrow[B1_R];
-  float acc[B1_R];
-#pragma unroll
-  for (int r = 0; r < B1_R; ++r) {
-    wrow[r] = (row0 + r < N) ? W + (size_t)(row0 + r) * row_bytes : nullptr;
-    acc[r] = 0.f;
-  }
-  rows_partial<FMT, B1_R, XT>(wrow, K, x, acc);
-#pragma unroll
-  for (int r = 0; r < B1_R; ++r) {
-    const float v0 = warp_sum(acc[r]);
-    if (lane == 0 && wrow[r]) {
-      float v = v0;
-      if (addend) v += addend[row0 + r];
-      if (out_f32) reinterpret_cast<float*>(out)[row0 + r] = v;
-      else reinterpret_cast<XT*>(out)[row0 + r] = Cvt<XT>::from_f(v);
-    }
-  }
-}
-
-// grid (ceil(E / (8 * R2)), slots): a warp owns R2 consecutive j, i.e. R2 gate rows and R2 up rows of one expert.
-constexpr int B1_R2 = 2;
-template <int FMT, typename XT>
-__global__ void __launch_bounds__(GV_THREADS) swiglu_b1_kernel(const uint8_t* __restrict__ Wg, const uint8_t* __restrict__ Wu,
-                                                              long long row_bytes, int ne, int E, int d,
-                                                              const float* __restrict__ x32, const float* __restrict__ norm_w,
-                                                              float eps, const int* __restrict__ idx, int top_k,
-                                                              XT* __restrict__ act) {
-  pdl_wait();
-  extern __shared__ __align__(16) uint8_t gv_dyn[];
-  XT* xs = reinterpret_cast<XT*>(gv_dyn);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == 0) norm_row_to_smem<XT>(x32, norm_w, xs, d, eps);
-  __syncthreads();
-  const int slot = blockIdx.y;
-  const int e = idx ? (slot < top_k ? idx[slot] : ne) : 0;
-  if (e < 0 || e > ne) return;
-  const int j0 = (blockIdx.x * GV_WARPS + warp) * B1_R2;
-  const uint8_t* wrow[2 * B1_R2];
-  float acc[2 * B1_R2];
-#pragma unroll
-  for (int r = 0; r < B1_R2; ++r) {
-    const bool ok = j0 + r < E;
-    const size_t row = (size_t)e * E + j0 + r;
-    wrow[r] = ok ? Wg + row * row_bytes : nullptr;
-    wrow[B1_R2 + r] = ok ? Wu + row * row_bytes : nullptr;
-    acc[r] = acc[B1_R2 + r] = 0.f;
-  }
-  rows_partial<FMT, 2 * B1_R2, XT>(wrow, d, xs, acc);
-#pragma unroll
-  for (int r = 0; r < B1_R2; ++r) {
-    const float gs = warp_sum(acc[r]), us = warp_sum(acc[B1_R2 + r]);
-    if (lane == 0 && wrow[r]) act[(long long)slot * E + j0 + r] = Cvt<XT>::from_f(gs / (1.f + __expf(-gs)) * us);
-  }
-}
-
-// out[r] = resid[r] + sum over slots of weight * (W_down[expert, r] . act[slot]); a warp owns one output row and reads
-// the rows of all its slots (at most 6) unit by unit, so that every slot's loads are in flight together.
-constexpr int B1_MAX_SLOTS = 6;
-template <int FMT, typename XT>
-__global__ void __launch_bounds__(GV_THREADS) down_b1_kernel(const uint8_t* __restrict__ Wd, long long row_bytes, int ne, int d,
-                                                            int E, const XT* __restrict__ act, const int* __restrict__ idx,
-                                                            const float* __restrict__ w, int top_k, int slots,
-                                                            const float* __restrict__ resid, float* __restrict__ out) {
-  pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.x * GV_WARPS + warp;
-  if (r >= d) return;
-  const uint8_t* wrow[B1_MAX_SLOTS];
-  float wgt[B1_MAX_SLOTS], part[B1_MAX_SLOTS];
-#pragma unroll
-  for (int s = 0; s < B1_MAX_SLOTS; ++s) {
-    wrow[s] = nullptr; wgt[s] = 0.f; part[s] = 0.f;
-    if (s < slots) {
-      const int e = s < top_k ? idx[s] : ne;
-      if (e >= 0 && e <= ne) {
-        wrow[s] = Wd + ((size_t)e * d + r) * row_bytes;
-        wgt[s] = s < top_k ? w[s] : 1.f;
-      }
-    }
-  }
-#pragma unroll 1
-  for (int u = lane; u < (E >> 3); u += 32) {
-    float wv[B1_MAX_SLOTS][8], xf[B1_MAX_SLOTS][8];
-#pragma unroll
-    for (int s = 0; s < B1_MAX_SLOTS; ++s)
-      if (wrow[s]) { load8<FMT>(wrow[s], u, wv[s]); unit_to_f8<XT>(act + (long long)s * E + 8 * u, xf[s]); }
-#pragma unroll
-    for (int s = 0; s < B1_MAX_SLOTS; ++s)
-      if (wrow[s]) {
-        float a = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a += wv[s][i] * xf[s][i];
-        part[s] += a;
-      }
-  }
-  float total = 0.f;                          // slot order fixed: reproducible
-#pragma unroll
-  for (int s = 0; s < B1_MAX_SLOTS; ++s)
-    if (wrow[s]) total += wgt[s] * part[s];
-  const float t = warp_sum(total);
-  if (lane == 0) out[r] = resid[r] + t;
-}
-
 }  // namespace gb
 
 using namespace gb;
@@ -819,39 +654,12 @@ extern "C" long long gb_wfmt_row_bytes(int fmt, int K) {
     default: return -1;                                   \
   }
 
-// batch-1 fast path launchers (see the kernels): return true when they took the call
-template <typename XT>
-static bool launch_gemv_b1(const uint8_t* w, long long rb, int fmt, int N, int K, const XT* x16, const float* x32,
-                           const float* norm_w, float eps, void* out, int out_f32, const float* addend, cudaStream_t st) {
-  const size_t smem = x32 ? (size_t)K * 2 : 0;
-  if (smem > 40 * 1024) return false;
-  cudaLaunchAttribute attr;
-  cudaLaunchConfig_t cfg = gb_pdl_config(dim3((N + B1_ROWS - 1) / B1_ROWS), dim3(GV_THREADS), smem, st, &attr);
-#define CALL(F) (void)cudaLaunchKernelEx(&cfg, (gemv_b1_kernel<F, XT>), w, rb, N, K, x16, x32, norm_w, eps, out, out_f32, addend);
-  switch (fmt) {
-    case GB_W_F16: CALL(GB_W_F16) break;
-    case GB_W_BF16: CALL(GB_W_BF16) break;
-    case GB_W_GGML_Q8_0: CALL(GB_W_GGML_Q8_0) break;
-    case GB_W_Q4_0: CALL(GB_W_Q4_0) break;
-    case GB_W_Q8_64: CALL(GB_W_Q8_64) break;
-    case GB_W_Q4_1: CALL(GB_W_Q4_1) break;
-    default: return false;
-  }
-#undef CALL
-  return true;
-}
-
 extern "C" int gb_gemv(const void* W, int fmt, int N, int K, const void* x16, int ldx, int B, void* out, int ldo, int out_f32,
                        const float* addend, int ld_add, int is_bf16, cudaStream_t st) {
   const long long rb = gb_wfmt_row_bytes(fmt, K);
   if (!W || !x16 || !out || N <= 0 || B <= 0 || B > 32 || rb < 0 || (ldx % 8)) return -1;
   const bool split = N <= 8192;   // few rows: spread each over four warps (latency bound); many rows fill the GPU anyway
   const uint8_t* w = static_cast<const uint8_t*>(W);
-  if (B == 1) {
-    const bool took = is_bf16 ? launch_gemv_b1<__nv_bfloat16>(w, rb, fmt, N, K, (const __nv_bfloat16*)x16, nullptr, nullptr, 0.f, out, out_f32, addend, st)
-                              : launch_gemv_b1<__half>(w, rb, fmt, N, K, (const __half*)x16, nullptr, nullptr, 0.f, out, out_f32, addend, st);
-    if (took) return gb_launch_rc();
-  }
 #define GEMV_GO(F, NB, KS, XT)                                                                                     \
   GB_PDL_LAUNCH((gemv_kernel<F, NB, KS, XT>), dim3((N + GV_WARPS / KS - 1) / (GV_WARPS / KS)), dim3(GV_THREADS), st, \
                 w, rb, N, K, (const XT*)x16, (long long)ldx, B, out, (long long)ldo, out_f32, addend, (long long)ld_add)
@@ -897,16 +705,6 @@ extern "C" int gb_gemv_expert_down(const void* Wd, int fmt, int ne, int d, int E
   const int slots = top_k + (shared ? 1 : 0);
   const uint8_t* wd = static_cast<const uint8_t*>(Wd);
   const bool split = B <= 16;
-  if (B == 1 && slots <= B1_MAX_SLOTS) {
-    cudaLaunchAttribute attr;
-    cudaLaunchConfig_t cfg = gb_pdl_config(dim3((d + GV_WARPS - 1) / GV_WARPS), dim3(GV_THREADS), 0, st, &attr);
-#define DNB(F)                                                                                                            \
-  if (is_bf16) (void)cudaLaunchKernelEx(&cfg, (down_b1_kernel<F, __nv_bfloat16>), wd, rb, ne, d, E, (const __nv_bfloat16*)act16, idx, w, top_k, slots, resid, out); \
-  else (void)cudaLaunchKernelEx(&cfg, (down_b1_kernel<F, __half>), wd, rb, ne, d, E, (const __half*)act16, idx, w, top_k, slots, resid, out);
-    GB_FMT_SWITCH(fmt, DNB)
-#undef DNB
-    return gb_launch_rc();
-  }
 #define DN_GO(F, KS, XT)                                                                                    \
   GB_PDL_LAUNCH((expert_down_kernel<F, KS, XT>), dim3((d + GV_WARPS / KS - 1) / (GV_WARPS / KS), B), dim3(GV_THREADS), st, \
                 wd, rb, ne, d, E, (const XT*)act16, idx, w, top_k, slots, resid, out)
@@ -1004,11 +802,6 @@ extern "C" int gb_gemv_norm(const void* W, int fmt, int N, int K, const float* x
   if (smem > 40 * 1024) return -2;                          // the caller takes the two-kernel route
   const bool split = N <= 8192;
   const uint8_t* w = static_cast<const uint8_t*>(W);
-  if (B == 1) {
-    const bool took = is_bf16 ? launch_gemv_b1<__nv_bfloat16>(w, rb, fmt, N, K, nullptr, x32, norm_w, eps, out, out_f32, nullptr, st)
-                              : launch_gemv_b1<__half>(w, rb, fmt, N, K, nullptr, x32, norm_w, eps, out, out_f32, nullptr, st);
-    if (took) return gb_launch_rc();
-  }
 #define GEMVN_GO(F, NB, KS, XT)                                                                                      \
   do {                                                                                                               \
     cudaLaunchAttribute gb_attr_;                                                                                    \
@@ -1058,16 +851,6 @@ extern "C" int gb_swiglu_norm(const void* Wg, const void* Wu, int fmt, int ne, i
   const int slots = top_k + (shared ? 1 : 0);
   const uint8_t *g = static_cast<const uint8_t*>(Wg), *u = static_cast<const uint8_t*>(Wu);
   const bool split = B * slots <= 64;
-  if (B == 1) {
-    cudaLaunchAttribute attr;
-    cudaLaunchConfig_t cfg = gb_pdl_config(dim3((E + GV_WARPS * B1_R2 - 1) / (GV_WARPS * B1_R2), slots), dim3(GV_THREADS), smem, st, &attr);
-#define SWB(F)                                                                                                              \
-  if (is_bf16) (void)cudaLaunchKernelEx(&cfg, (swiglu_b1_kernel<F, __nv_bfloat16>), g, u, rb, ne, E, d, x32, norm_w, eps, idx, top_k, (__nv_bfloat16*)act16); \
-  else (void)cudaLaunchKernelEx(&cfg, (swiglu_b1_kernel<F, __half>), g, u, rb, ne, E, d, x32, norm_w, eps, idx, top_k, (__half*)act16);
-    GB_FMT_SWITCH(fmt, SWB)
-#undef SWB
-    return gb_launch_rc();
-  }
 #define SWN_GO(F, KS, XT)                                                                                            \
   do {                                                                                                               \
     cudaLaunchAttribute gb_attr_;                                                                                    \

@@ -45,7 +45,7 @@ def test_gemv_matches_dequantised_product(fmt, B):
 @pytest.mark.parametrize("B", [3, 1])
 @pytest.mark.parametrize("fmt", ["f16", "q8_0", "q4_1"])
 def test_expert_kernels(fmt, B):
-    """B = 1 takes the whole-row-per-warp kernels, larger batches the split-row ones."""
+    """One sequence and several; the fused-norm forms must agree with norm followed by the plain kernels."""
     D = _D()
     ne, E, d, top_k = 4, 64, 96, 2
     f = D.FMT_NAMES[fmt]
@@ -389,7 +389,7 @@ def test_fused_token_step_equals_separate_kernels(moe, fmt, B):
             e._forward_token()
         if B > 1:
             assert torch.equal(engines[0].logits, engines[1].logits), (j, float((engines[0].logits - engines[1].logits).abs().max()))
-        else:      # one sequence: the fused step takes the whole-row-per-warp kernels, which group the sums differently
+        else:      # kept loose for one sequence so that batch-1 kernel variants may regroup the sums
             assert torch.allclose(engines[0].logits, engines[1].logits, rtol=2e-3, atol=2e-3), (j, float((engines[0].logits - engines[1].logits).abs().max()))
     for La, Lb in zip(engines[0].layers, engines[1].layers):
         if B > 1:
