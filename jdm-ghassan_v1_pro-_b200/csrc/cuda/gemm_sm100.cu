@@ -39,7 +39,8 @@ struct GemmParams {
   int* status;
 };
 
-enum { EPI_STORE = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2 };
+enum { EPI_STORE = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2,
+       EPI_STORE_TILED = 3 };   // EPI_STORE with per-tile destinations (16-bit output), chosen by the launcher
 
 __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, int* status, int code, volatile int* abort_flag) {
   long long t0 = clock64();
@@ -283,7 +284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int row = t.a_row0 + r_in_tile;
       const bool row_ok = row < p.M;
       const uint32_t taddr0 = tmem_base + ab * BN + (uint32_t(quarter * 32) << 16);
-      if constexpr (EPI == EPI_STORE) {
+      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_TILED) {
         // per-tile destinations: the rows of this tile go to wherever the table says (expert-parallel combine
         // writes them straight into the buffer of the GPU that owns the tokens)
         OutT* orow = p.tile_out ? reinterpret_cast<OutT*>(p.tile_out[t.tm]) + (long long)r_in_tile * p.ldo
@@ -306,8 +307,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[b][i]);
             const int col = t.n0 + (c0 + b) * 32;
             const int nvalid = p.N - col;
-            if constexpr (sizeof(OutT) == 2) {
-              if (p.tile_out != nullptr && nvalid >= 32) {      // warp-uniform: col and N are
+            if constexpr (EPI == EPI_STORE_TILED && sizeof(OutT) == 2) {
+              if (nvalid >= 32) {                               // warp-uniform: col and N are
                 uint4* ws = reinterpret_cast<uint4*>(stage + warp * 2048);
                 __syncwarp();
 #pragma unroll
@@ -538,6 +539,11 @@ extern "C" int gb_gemm(const gb_gemm_args* a, cudaStream_t st) {
   const int ot = a->out_dtype;  // 0 fp16, 1 bf16, 2 fp32
   switch (a->epilogue) {
     case gb::EPI_STORE:
+      if (p.tile_out) {   // expert-parallel combine: its own instantiation, so the plain store keeps its registers
+        if (ot == 2) return -1;
+        if (ot == 1) return dispatch_bn<gb::EPI_STORE_TILED, __nv_bfloat16, __nv_bfloat16>(bn, ta, tb, p, max_tiles, st);
+        return dispatch_bn<gb::EPI_STORE_TILED, __half, __half>(bn, ta, tb, p, max_tiles, st);
+      }
       if (ot == 2) return dispatch_bn<gb::EPI_STORE, float, __half>(bn, ta, tb, p, max_tiles, st);
       if (ot == 1) return dispatch_bn<gb::EPI_STORE, __nv_bfloat16, __nv_bfloat16>(bn, ta, tb, p, max_tiles, st);
       return dispatch_bn<gb::EPI_STORE, __half, __half>(bn, ta, tb, p, max_tiles, st);
