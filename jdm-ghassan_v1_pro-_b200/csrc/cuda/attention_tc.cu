@@ -145,7 +145,9 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_co
   int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * AT_M;
+  // the tile index is the slowest grid dimension and runs from the last query tile down: under a causal mask that tile
+  // has the most key tiles to visit, and CTAs are handed out in grid order, so the long ones start first
+  const int b = blockIdx.y, h = blockIdx.x, q0 = (int)(gridDim.z - 1 - blockIdx.z) * AT_M;
   const int kvh = h / (p.H / p.KV);
   const long long row_base = (long long)b * p.T;
 
@@ -333,7 +335,9 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
   int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * AT_M;
+  // the tile index is the slowest grid dimension and runs from the last query tile down: under a causal mask that tile
+  // has the most key tiles to visit, and CTAs are handed out in grid order, so the long ones start first
+  const int b = blockIdx.y, h = blockIdx.x, q0 = (int)(gridDim.z - 1 - blockIdx.z) * AT_M;
   const int kvh = h / (p.H / p.KV);
   const long long row_base = (long long)b * p.T;
   if (threadIdx.x == 0) {
@@ -501,7 +505,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, kvh = blockIdx.y, j0 = blockIdx.x * AT_N;
+  // slowest grid dimension = key tile, first tile first: it is read by every query tile, the longest loop
+  const int b = blockIdx.y, kvh = blockIdx.x, j0 = blockIdx.z * AT_N;
   const int group = p.H / p.KV;
   const long long row_base = (long long)b * p.T;
   if (threadIdx.x == 0) {
@@ -717,7 +722,8 @@ int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
     (void)cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr = true;
   }
-  dim3 grid((a->T + AT_M - 1) / AT_M, a->H, a->B);
+  if (a->B > 65535 || (a->T + AT_M - 1) / AT_M > 65535) return -1;   // grid y and z limits
+  dim3 grid(a->H, a->B, (a->T + AT_M - 1) / AT_M);
   kern<<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
   return gb_launch_rc();
 }
@@ -764,7 +770,8 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
     if (cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv) != cudaSuccess) return -10;
     attr = true;
   }
-  dim3 gq((a->T + AT_M - 1) / AT_M, a->H, a->B), gkv((a->T + AT_N - 1) / AT_N, a->KV, a->B);
+  if (a->B > 65535 || (a->T + AT_N - 1) / AT_N > 65535) return -1;   // grid y and z limits
+  dim3 gq(a->H, a->B, (a->T + AT_M - 1) / AT_M), gkv(a->KV, a->B, (a->T + AT_N - 1) / AT_N);
   kq<<<gq, AT_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
   kkv<<<gkv, AT_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
   return gb_launch_rc();
