@@ -37,55 +37,64 @@ __global__ void embed_fwd_kernel(const int* __restrict__ ids, const float* __res
   for (int i = threadIdx.x; i < d / 4; i += blockDim.x) dst[i] = src[i];
 }
 
-// dtable[id] += sum over the tokens t with ids[t] == id of dx[t], added in increasing t: no atomics, so the embedding
-// gradient is the same bits on every run (the reference scatters with atomicAdd, cuda/kernels.cu:420-442, and is
-// not).  One block per token; the block of the FIRST occurrence of an id owns that id's row and walks the later
-// occurrences, every other block leaves after it has found an earlier one.  Matches are found 256 ids at a time
-// (one compare per thread, ballots into shared memory) and then added in index order.
+// dtable[id] += sum over the tokens t with ids[t] == id of dx[t], added in increasing t: no atomics on the sums, so
+// the embedding gradient is the same bits on every run (the reference scatters with atomicAdd,
+// cuda/kernels.cu:420-442, and is not).  A first pass records the first token of every id (atomicMin on an index:
+// order-independent).  Then one block per token: the block of the FIRST occurrence owns that id's row and walks the
+// later tokens, 1024 ids per trip (four per thread, ballots into shared memory), adding the matches in index order;
+// every other block leaves at once.
 constexpr int EMB_THREADS = 256;
-constexpr int EMB_MAX_COLS = 32;     // columns per thread: d <= 8192
+constexpr int EMB_MAX_COLS = 32;           // columns per thread: d <= 8192
+constexpr int EMB_MAX_VOCAB = 1 << 19;     // ids covered by the first-occurrence table (2 MB of device memory)
+__device__ int g_emb_first[EMB_MAX_VOCAB];
+
+__global__ void embed_first_kernel(const int* __restrict__ ids, int n_tok, int vocab) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tok) return;
+  const int id = ids[t];
+  if (id >= 0 && id < vocab) atomicMin(&g_emb_first[id], t);
+}
 
 __global__ void __launch_bounds__(EMB_THREADS) embed_bwd_kernel(const int* __restrict__ ids, const float* __restrict__ dx,
                                                                float* __restrict__ dtable, int n_tok, int d, int vocab) {
-  __shared__ unsigned int mask[EMB_THREADS / 32];
-  __shared__ int s_earlier;
+  __shared__ unsigned int mask[4][EMB_THREADS / 32];
   const int t = blockIdx.x;
   if (t >= n_tok) return;
   const int id = ids[t];
   if (id < 0 || id >= vocab) return;
+  if (g_emb_first[id] != t) return;              // an earlier token owns this id
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) s_earlier = 0;
-  __syncthreads();
-  for (int base = 0; base < t; base += EMB_THREADS) {          // does an earlier token carry the same id?
-    const int j = base + threadIdx.x;
-    if (j < t && ids[j] == id) s_earlier = 1;
-  }
-  __syncthreads();
-  if (s_earlier) return;
   float acc[EMB_MAX_COLS];
   const int ncol = (d + EMB_THREADS - 1) / EMB_THREADS;
 #pragma unroll
   for (int c = 0; c < EMB_MAX_COLS; ++c) acc[c] = 0.f;
-  for (int base = t - (t % EMB_THREADS); base < n_tok; base += EMB_THREADS) {
-    const int j = base + threadIdx.x;
-    const bool hit = j >= t && j < n_tok && ids[j] == id;
-    const unsigned int b = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) mask[warp] = b;
-    __syncthreads();
-    for (int w = 0; w < EMB_THREADS / 32; ++w) {
-      unsigned int m = mask[w];
-      while (m) {
-        const int k = __ffs(m) - 1;
-        m &= m - 1;
-        const float* src = dx + (size_t)(base + w * 32 + k) * d;
+  constexpr int TRIP = 4 * EMB_THREADS;
+  for (int base = t - (t % TRIP); base < n_tok; base += TRIP) {
+    // thread i looks at ids base + k*256 + i for k = 0..3, so that mask[k] is in index order
 #pragma unroll
-        for (int c = 0; c < EMB_MAX_COLS; ++c)
-          if (c < ncol) {
-            const int col = c * EMB_THREADS + threadIdx.x;
-            if (col < d) acc[c] += src[col];
-          }
-      }
+    for (int k = 0; k < 4; ++k) {
+      const int j = base + k * EMB_THREADS + threadIdx.x;
+      const bool hit = j >= t && j < n_tok && ids[j] == id;
+      const unsigned int b = __ballot_sync(0xffffffffu, hit);
+      if (lane == 0) mask[k][warp] = b;
     }
+    __syncthreads();
+#pragma unroll 1
+    for (int k = 0; k < 4; ++k)
+      for (int w = 0; w < EMB_THREADS / 32; ++w) {
+        unsigned int m = mask[k][w];
+        while (m) {
+          const int bit = __ffs(m) - 1;
+          m &= m - 1;
+          const float* src = dx + (size_t)(base + k * EMB_THREADS + w * 32 + bit) * d;
+#pragma unroll
+          for (int c = 0; c < EMB_MAX_COLS; ++c)
+            if (c < ncol) {
+              const int col = c * EMB_THREADS + threadIdx.x;
+              if (col < d) acc[c] += src[col];
+            }
+        }
+      }
     __syncthreads();
   }
   float* dst = dtable + (size_t)id * d;
@@ -371,7 +380,11 @@ extern "C" int gb_embed_fwd(const int* ids, const float* table, float* out, int 
   return GB_LAUNCH_OK();
 }
 extern "C" int gb_embed_bwd(const int* ids, const float* dx, float* dtable, int n_tok, int d, int vocab, cudaStream_t st) {
-  if (d > EMB_THREADS * EMB_MAX_COLS) return -1;
+  if (d > EMB_THREADS * EMB_MAX_COLS || vocab > EMB_MAX_VOCAB || vocab <= 0) return -1;
+  void* first = nullptr;
+  if (cudaGetSymbolAddress(&first, g_emb_first) != cudaSuccess) return -12;
+  if (cudaMemsetAsync(first, 0x7f, (size_t)vocab * sizeof(int), st) != cudaSuccess) return -12;   // 0x7f7f7f7f > any token index
+  embed_first_kernel<<<(n_tok + 255) / 256, 256, 0, st>>>(ids, n_tok, vocab);
   embed_bwd_kernel<<<n_tok, EMB_THREADS, 0, st>>>(ids, dx, dtable, n_tok, d, vocab);
   return GB_LAUNCH_OK();
 }
