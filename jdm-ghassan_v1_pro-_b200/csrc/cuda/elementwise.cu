@@ -196,6 +196,84 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ g, const float* __restr
   }
 }
 
+// The same for d = 128 * NV with a whole row in registers: every load of a row (x, g, dres) is issued before the
+// first use, the row is read once, and the column sums stay in registers until the end.  The rolled loop above
+// waits for DRAM twelve times per row and ran at about half of the copy bandwidth.  8 warps per block.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_vec_kernel(const T* __restrict__ g, const float* __restrict__ x,
+                                                              const float* __restrict__ w, const float* __restrict__ rrms,
+                                                              const float* __restrict__ dres, float* __restrict__ dx_out,
+                                                              T* __restrict__ dx16, float* __restrict__ part, int rows,
+                                                              int rows_per_block) {
+  constexpr int D = NV * 128;
+  extern __shared__ float sm_dw_all[];  // [8][D] column sums of the warps, then [D] weights
+  float* s_w = sm_dw_all + 8 * D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) s_w[i] = w[i];
+  __syncthreads();
+  float acc[NV][4];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f;
+  const int row0 = blockIdx.x * rows_per_block;
+  const int row1 = min(rows, row0 + rows_per_block);
+  for (int row = row0 + warp; row < row1; row += 8) {
+    const float inv = rrms[row];
+    const float* xr = x + (size_t)row * D;
+    const T* gr = g + (size_t)row * D;
+    float4 xv[NV];
+    uint2 gq[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = k * 128 + lane * 4;
+      xv[k] = *reinterpret_cast<const float4*>(xr + i);
+      gq[k] = *reinterpret_cast<const uint2*>(gr + i);
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const float4 wv = *reinterpret_cast<const float4*>(s_w + k * 128 + lane * 4);
+      const float2 g01 = Cvt<T>::unpack2(gq[k].x), g23 = Cvt<T>::unpack2(gq[k].y);
+      dot += g01.x * wv.x * xv[k].x + g01.y * wv.y * xv[k].y + g23.x * wv.z * xv[k].z + g23.y * wv.w * xv[k].w;
+    }
+    dot = warp_sum(dot);
+    const float coef = inv * inv * inv * dot / (float)D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = k * 128 + lane * 4;
+      const float4 wv = *reinterpret_cast<const float4*>(s_w + i);
+      const float2 g01 = Cvt<T>::unpack2(gq[k].x), g23 = Cvt<T>::unpack2(gq[k].y);
+      const float4 rv = dres ? __ldcs(reinterpret_cast<const float4*>(dres + (size_t)row * D + i)) : make_float4(0, 0, 0, 0);
+      float4 o;
+      o.x = rv.x + g01.x * wv.x * inv - xv[k].x * coef;
+      o.y = rv.y + g01.y * wv.y * inv - xv[k].y * coef;
+      o.z = rv.z + g23.x * wv.z * inv - xv[k].z * coef;
+      o.w = rv.w + g23.y * wv.w * inv - xv[k].w * coef;
+      *reinterpret_cast<float4*>(dx_out + (size_t)row * D + i) = o;
+      if (dx16) {
+        uint2 q;
+        q.x = Cvt<T>::pack2(o.x, o.y);
+        q.y = Cvt<T>::pack2(o.z, o.w);
+        *reinterpret_cast<uint2*>(dx16 + (size_t)row * D + i) = q;
+      }
+      acc[k][0] += g01.x * xv[k].x * inv;
+      acc[k][1] += g01.y * xv[k].y * inv;
+      acc[k][2] += g23.x * xv[k].z * inv;
+      acc[k][3] += g23.y * xv[k].w * inv;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    *reinterpret_cast<float4*>(sm_dw_all + (size_t)warp * D + k * 128 + lane * 4) =
+        make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < 8; ++wv) s += sm_dw_all[(size_t)wv * D + i];
+    part[(size_t)blockIdx.x * D + i] = s;
+  }
+}
+
 // dw[c] += sum_b part[b, c]
 // 256 threads = 32 columns x 8 row lanes; fixed summation order (row lane, then lanes 0..7)
 __global__ void colsum_finalize_kernel(const float* __restrict__ part, float* __restrict__ dw, int nblocks, int d) {
@@ -354,6 +432,215 @@ __global__ void qk_norm_rope_bwd_kernel(const T* __restrict__ dout, int ld_dout,
     }
 }
 
+// The same backward with HD/8 lanes per (token, head) item: a lane owns four rotation pairs and moves them with
+// 16-byte (interleaved pairs) or 8-byte (half-split pairs) accesses, a warp works on 256/HD items at once and on
+// two such groups per trip, so that enough bytes are in flight to cover the DRAM latency (with one item per warp
+// the kernel ran at a fifth of the copy bandwidth).  Needs 16-byte aligned rows; HD in {32, 64, 128, 256}.
+template <typename T>
+__device__ __forceinline__ void qk_load8(const T* p, int j, int pairs, int rope_type, float (&a)[4], float (&b)[4]) {
+  if (rope_type == 0) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p + 8 * j);
+    const float2 e0 = Cvt<T>::unpack2(v.x), e1 = Cvt<T>::unpack2(v.y), e2 = Cvt<T>::unpack2(v.z), e3 = Cvt<T>::unpack2(v.w);
+    a[0] = e0.x; b[0] = e0.y; a[1] = e1.x; b[1] = e1.y; a[2] = e2.x; b[2] = e2.y; a[3] = e3.x; b[3] = e3.y;
+  } else {
+    const uint2 lo = *reinterpret_cast<const uint2*>(p + 4 * j);
+    const uint2 hi = *reinterpret_cast<const uint2*>(p + pairs + 4 * j);
+    const float2 l0 = Cvt<T>::unpack2(lo.x), l1 = Cvt<T>::unpack2(lo.y), h0 = Cvt<T>::unpack2(hi.x), h1 = Cvt<T>::unpack2(hi.y);
+    a[0] = l0.x; a[1] = l0.y; a[2] = l1.x; a[3] = l1.y; b[0] = h0.x; b[1] = h0.y; b[2] = h1.x; b[3] = h1.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void qk_store8(T* p, int j, int pairs, int rope_type, const float (&a)[4], const float (&b)[4]) {
+  if (rope_type == 0) {
+    uint4 v;
+    v.x = Cvt<T>::pack2(a[0], b[0]); v.y = Cvt<T>::pack2(a[1], b[1]);
+    v.z = Cvt<T>::pack2(a[2], b[2]); v.w = Cvt<T>::pack2(a[3], b[3]);
+    *reinterpret_cast<uint4*>(p + 8 * j) = v;
+  } else {
+    uint2 lo, hi;
+    lo.x = Cvt<T>::pack2(a[0], a[1]); lo.y = Cvt<T>::pack2(a[2], a[3]);
+    hi.x = Cvt<T>::pack2(b[0], b[1]); hi.y = Cvt<T>::pack2(b[2], b[3]);
+    *reinterpret_cast<uint2*>(p + 4 * j) = lo;
+    *reinterpret_cast<uint2*>(p + pairs + 4 * j) = hi;
+  }
+}
+// fp32 vector of the four first / second pair members a lane owns (weights)
+__device__ __forceinline__ void qk_loadw(const float* w, int j, int pairs, int rope_type, float (&a)[4], float (&b)[4]) {
+  if (rope_type == 0) {
+    const float4 u = *reinterpret_cast<const float4*>(w + 8 * j), v = *reinterpret_cast<const float4*>(w + 8 * j + 4);
+    a[0] = u.x; b[0] = u.y; a[1] = u.z; b[1] = u.w; a[2] = v.x; b[2] = v.y; a[3] = v.z; b[3] = v.w;
+  } else {
+    const float4 u = *reinterpret_cast<const float4*>(w + 4 * j), v = *reinterpret_cast<const float4*>(w + pairs + 4 * j);
+    a[0] = u.x; a[1] = u.y; a[2] = u.z; a[3] = u.w; b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
+  }
+}
+
+// Forward with the same lane layout: HD/8 lanes per (token, head) item, 256/HD items per warp.
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) qk_norm_rope_fwd_vec_kernel(
+    const T* __restrict__ qkv, int ld_in, T* __restrict__ out, int ld_out, const float* __restrict__ qw,
+    const float* __restrict__ kw, const float* __restrict__ cs, const int* __restrict__ pos, int n_tok, int H, int KV,
+    float eps, int rope_type) {
+  pdl_wait();
+  constexpr int PAIRS = HD / 2, LPI = HD / 8, IPW = 32 / LPI;
+  const int lane = threadIdx.x & 31, sub = lane / LPI, j = lane % LPI;
+  const int heads = H + KV;
+  const int item = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * IPW + sub;
+  const bool live = item < n_tok * heads;
+  const int t = live ? item / heads : 0, h = live ? item - t * heads : 0;
+  float a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+  float4 c = make_float4(1, 1, 1, 1), s = make_float4(0, 0, 0, 0);
+  if (live) {
+    const float* csr = cs + (size_t)pos[t] * HD;
+    qk_load8<T>(qkv + (size_t)t * ld_in + (size_t)h * HD, j, PAIRS, rope_type, a, b);
+    c = *reinterpret_cast<const float4*>(csr + 4 * j);
+    s = *reinterpret_cast<const float4*>(csr + PAIRS + 4 * j);
+  }
+  const float* w = (h < H) ? qw : kw;
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) ss += a[k] * a[k] + b[k] * b[k];
+#pragma unroll
+    for (int o = LPI / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float inv = rsqrtf(ss / (float)HD + eps);
+    if (!isfinite(inv)) inv = 0.f;
+    float w0[4], w1[4];
+    qk_loadw(w, j, PAIRS, rope_type, w0, w1);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { a[k] *= inv * w0[k]; b[k] *= inv * w1[k]; }
+  }
+  const float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+  float o0[4], o1[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    o0[k] = a[k] * cc[k] - b[k] * sn[k];
+    o1[k] = a[k] * sn[k] + b[k] * cc[k];
+  }
+  if (live) qk_store8<T>(out + (size_t)t * ld_out + (size_t)h * HD, j, PAIRS, rope_type, o0, o1);
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) qk_norm_rope_bwd_vec_kernel(
+    const T* __restrict__ dout, int ld_dout, const T* __restrict__ qkv, int ld_in, T* __restrict__ dqkv, int ld_dqkv,
+    const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ cs, const int* __restrict__ pos,
+    float* __restrict__ part_q, float* __restrict__ part_k, int n_tok, int H, int KV, float eps, int rope_type,
+    int items_per_block) {
+  constexpr int PAIRS = HD / 2, LPI = HD / 8, IPW = 32 / LPI, U = 2;
+  __shared__ __align__(16) float s_w[2][HD];        // q and k norm weights
+  __shared__ float s_dw[2][8][HD];                  // [q|k][warp][column], summed over the warp's items
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPI, j = lane % LPI;
+  const bool norm = qw != nullptr;
+  if (norm)
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) { s_w[0][i] = qw[i]; s_w[1][i] = kw[i]; }
+  __syncthreads();
+  float accq0[4] = {0, 0, 0, 0}, accq1[4] = {0, 0, 0, 0}, acck0[4] = {0, 0, 0, 0}, acck1[4] = {0, 0, 0, 0};
+  const int heads = H + KV;
+  const int total = n_tok * heads;
+  const int it0 = blockIdx.x * items_per_block, it1 = min(total, it0 + items_per_block);
+  for (int base = it0 + warp * (IPW * U); base < it1; base += 8 * IPW * U) {
+    float g0[U][4], g1[U][4], x0[U][4], x1[U][4];
+    bool live[U], isq[U];
+    int tt[U], hh[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int item = base + u * IPW + sub;
+      live[u] = item < it1;
+      const int t = live[u] ? item / heads : 0;
+      tt[u] = t;
+      hh[u] = live[u] ? item - t * heads : 0;
+      isq[u] = hh[u] < H;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float d0[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0};
+      float4 c = make_float4(1, 1, 1, 1), s = make_float4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { x0[u][k] = 0.f; x1[u][k] = 0.f; }
+      if (live[u]) {
+        const float* csr = cs + (size_t)pos[tt[u]] * HD;
+        qk_load8<T>(dout + (size_t)tt[u] * ld_dout + (size_t)hh[u] * HD, j, PAIRS, rope_type, d0, d1);
+        if (norm) qk_load8<T>(qkv + (size_t)tt[u] * ld_in + (size_t)hh[u] * HD, j, PAIRS, rope_type, x0[u], x1[u]);
+        c = *reinterpret_cast<const float4*>(csr + 4 * j);
+        s = *reinterpret_cast<const float4*>(csr + PAIRS + 4 * j);
+      }
+      const float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        g0[u][k] = d0[k] * cc[k] + d1[k] * sn[k];   // inverse rotation
+        g1[u][k] = -d0[k] * sn[k] + d1[k] * cc[k];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      T* dst = dqkv + (size_t)tt[u] * ld_dqkv + (size_t)hh[u] * HD;
+      if (!norm) {
+        if (live[u]) qk_store8<T>(dst, j, PAIRS, rope_type, g0[u], g1[u]);
+        continue;
+      }
+      float w0[4], w1[4];
+      qk_loadw(s_w[isq[u] ? 0 : 1], j, PAIRS, rope_type, w0, w1);
+      float ss = 0.f, dot = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        ss += x0[u][k] * x0[u][k] + x1[u][k] * x1[u][k];
+        dot += g0[u][k] * w0[k] * x0[u][k] + g1[u][k] * w1[k] * x1[u][k];
+      }
+#pragma unroll
+      for (int o = LPI / 2; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      }
+      float inv = rsqrtf(ss / (float)HD + eps);
+      if (!isfinite(inv)) inv = 0.f;
+      const float coef = inv * inv * inv * dot / (float)HD;
+      float o0[4], o1[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        o0[k] = g0[u][k] * w0[k] * inv - x0[u][k] * coef;
+        o1[k] = g1[u][k] * w1[k] * inv - x1[u][k] * coef;
+        const float a0 = live[u] ? g0[u][k] * x0[u][k] * inv : 0.f;
+        const float a1 = live[u] ? g1[u][k] * x1[u][k] * inv : 0.f;
+        accq0[k] += isq[u] ? a0 : 0.f;
+        accq1[k] += isq[u] ? a1 : 0.f;
+        acck0[k] += isq[u] ? 0.f : a0;
+        acck1[k] += isq[u] ? 0.f : a1;
+      }
+      if (live[u]) qk_store8<T>(dst, j, PAIRS, rope_type, o0, o1);
+    }
+  }
+  if (!part_q) return;
+  // lanes with the same j hold the same columns: fold the item groups of the warp, then the warps, in a fixed order
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+#pragma unroll
+    for (int o = LPI; o < 32; o <<= 1) {
+      accq0[k] += __shfl_xor_sync(0xffffffffu, accq0[k], o);
+      accq1[k] += __shfl_xor_sync(0xffffffffu, accq1[k], o);
+      acck0[k] += __shfl_xor_sync(0xffffffffu, acck0[k], o);
+      acck1[k] += __shfl_xor_sync(0xffffffffu, acck1[k], o);
+    }
+  }
+  if (sub == 0) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i0 = rope_type == 0 ? 8 * j + 2 * k : 4 * j + k;
+      const int i1 = rope_type == 0 ? 8 * j + 2 * k + 1 : PAIRS + 4 * j + k;
+      s_dw[0][warp][i0] = accq0[k]; s_dw[0][warp][i1] = accq1[k];
+      s_dw[1][warp][i0] = acck0[k]; s_dw[1][warp][i1] = acck1[k];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < 8; ++wv) { sq += s_dw[0][wv][i]; sk += s_dw[1][wv][i]; }
+    part_q[(size_t)blockIdx.x * HD + i] = sq;
+    part_k[(size_t)blockIdx.x * HD + i] = sk;
+  }
+}
+
 // ------------------------------------------------------------------------------------------ casts / fills
 template <typename T>
 __global__ void cast_f32_to_16_kernel(const float* __restrict__ src, T* __restrict__ dst, long long n) {
@@ -419,7 +706,23 @@ extern "C" int gb_rmsnorm_bwd(const void* g, const float* x, const float* w, con
   if (wpb < 1) return -1;
   const size_t smem = (size_t)d * wpb * sizeof(float);
   const int threads = wpb * 32;
-  if (is_bf16)
+  const bool vec = d % 256 == 0 && d <= 1024 &&
+                   (((uintptr_t)g | (uintptr_t)x | (uintptr_t)dres | (uintptr_t)dx_out | (uintptr_t)dx16) & 15) == 0;
+  if (vec) {
+    const size_t vsmem = (size_t)d * 9 * sizeof(float);
+#define GB_RMS_BWD_VEC(T, NV)                                                                                      \
+  rmsnorm_bwd_vec_kernel<T, NV><<<nb, 256, vsmem, st>>>((const T*)g, x, w, rrms, dres, dx_out, (T*)dx16, part, rows, rpb)
+#define GB_RMS_BWD_VEC_T(T)          \
+  switch (d / 128) {                 \
+    case 2: GB_RMS_BWD_VEC(T, 2); break; \
+    case 4: GB_RMS_BWD_VEC(T, 4); break; \
+    case 6: GB_RMS_BWD_VEC(T, 6); break; \
+    default: GB_RMS_BWD_VEC(T, 8); break; \
+  }
+    if (is_bf16) { GB_RMS_BWD_VEC_T(__nv_bfloat16) } else { GB_RMS_BWD_VEC_T(__half) }
+#undef GB_RMS_BWD_VEC_T
+#undef GB_RMS_BWD_VEC
+  } else if (is_bf16)
     rmsnorm_bwd_kernel<__nv_bfloat16><<<nb, threads, smem, st>>>((const __nv_bfloat16*)g, x, w, rrms, dres, dx_out,
                                                              (__nv_bfloat16*)dx16, part, rows, d, rpb);
   else
@@ -431,7 +734,7 @@ extern "C" int gb_rmsnorm_bwd(const void* g, const float* x, const float* w, con
 
 extern "C" int gb_qk_rope_blocks(int n_items) {
   int b = (n_items + 31) / 32;
-  return b > 592 ? 592 : (b < 1 ? 1 : b);
+  return b > 444 ? 444 : (b < 1 ? 1 : b);   // three 256-thread blocks of the backward kernel per SM
 }
 
 template <typename T>
@@ -439,6 +742,22 @@ static int qk_fwd_t(const void* qkv, int ld_in, void* out, int ld_out, const flo
                     const int* pos, int n_tok, int H, int KV, int hd, float eps, int rope_type, cudaStream_t st) {
   const int items = n_tok * (H + KV);
   const int wpb = 8;
+  const bool aligned = ld_in % 8 == 0 && ld_out % 8 == 0 && (qw == nullptr) == (kw == nullptr) &&
+                       (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)cs | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
+  if (aligned && (hd == 32 || hd == 64 || hd == 128 || hd == 256)) {
+    const int ipb = wpb * (256 / hd);   // items per block
+    dim3 vgrid((items + ipb - 1) / ipb);
+#define GB_QK_FWD_VEC(HD) \
+  GB_PDL_LAUNCH((qk_norm_rope_fwd_vec_kernel<T, HD>), dim3(vgrid), dim3(wpb * 32), st, (const T*)qkv, ld_in, (T*)out, ld_out, qw, kw, cs, pos, n_tok, H, KV, eps, rope_type)
+    switch (hd) {
+      case 32: GB_QK_FWD_VEC(32); break;
+      case 64: GB_QK_FWD_VEC(64); break;
+      case 128: GB_QK_FWD_VEC(128); break;
+      default: GB_QK_FWD_VEC(256); break;
+    }
+#undef GB_QK_FWD_VEC
+    return GB_LAUNCH_OK();
+  }
   dim3 grid((items + wpb - 1) / wpb);
 #define GB_QK_FWD(HD) \
   GB_PDL_LAUNCH((qk_norm_rope_fwd_kernel<T, HD>), dim3(grid), dim3(wpb * 32), st, (const T*)qkv, ld_in, (T*)out, ld_out, qw, kw, cs, pos, n_tok, H, KV, eps, rope_type)
@@ -470,9 +789,23 @@ static int qk_bwd_t(const void* dout, int ld_dout, const void* qkv, int ld_in, v
   const int ipb = (items + nb - 1) / nb;
   float* pq = part;
   float* pk = part ? part + (size_t)nb * hd : nullptr;
+  const bool aligned = ld_dout % 8 == 0 && ld_in % 8 == 0 && ld_dqkv % 8 == 0 && (qw == nullptr) == (kw == nullptr) &&
+                       (((uintptr_t)dout | (uintptr_t)qkv | (uintptr_t)dqkv | (uintptr_t)cs) & 15) == 0;
+#define GB_QK_BWD_VEC(HD)                                                                                        \
+  qk_norm_rope_bwd_vec_kernel<T, HD><<<nb, 256, 0, st>>>((const T*)dout, ld_dout, (const T*)qkv, ld_in, (T*)dqkv, \
+                                                         ld_dqkv, qw, kw, cs, pos, pq, pk, n_tok, H, KV, eps,   \
+                                                         rope_type, ipb)
 #define GB_QK_BWD(HD)                                                                                                 \
   qk_norm_rope_bwd_kernel<T, HD><<<nb, 256, 0, st>>>((const T*)dout, ld_dout, (const T*)qkv, ld_in, (T*)dqkv, ld_dqkv, \
                                                      qw, kw, cs, pos, pq, pk, n_tok, H, KV, eps, rope_type, ipb)
+  if (aligned && (hd == 32 || hd == 64 || hd == 128 || hd == 256)) {
+    switch (hd) {
+      case 32: GB_QK_BWD_VEC(32); break;
+      case 64: GB_QK_BWD_VEC(64); break;
+      case 128: GB_QK_BWD_VEC(128); break;
+      default: GB_QK_BWD_VEC(256); break;
+    }
+  } else
   switch (hd) {
     case 32: GB_QK_BWD(32); break;
     case 64: GB_QK_BWD(64); break;

@@ -42,7 +42,10 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-template <typename T>
+// NV8 > 0: d = 256 * NV8 and the activation row stays in registers (one 16-byte load per 256 columns and lane,
+// 16-byte weight loads); NV8 = 0 is the loop for any even d.  With the row re-read for every expert in 4-byte
+// pieces the kernel was bound by load instructions, at a tenth of the bandwidth its 2 bytes per element need.
+template <typename T, int NV8>
 __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
   __shared__ int s_hist[MAX_NE + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,18 +61,45 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
     const T* xr = x16 + (size_t)t * d;
     // lane holds the logits of experts `lane` and `lane + 32`
     float l0 = -INFINITY, l1 = -INFINITY;
-    for (int e = 0; e < ne; ++e) {
-      const float* wr = a.router_w + (size_t)e * d;
-      float s = 0.f;
-      for (int i = lane * 2; i < d; i += 64) {
-        const float2 xv = Cvt<T>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
-        const float2 wv = *reinterpret_cast<const float2*>(wr + i);
-        s += xv.x * wv.x + xv.y * wv.y;
+    if constexpr (NV8 > 0) {
+      float xf[NV8][8];
+#pragma unroll
+      for (int k = 0; k < NV8; ++k) {
+        const uint4 q = *reinterpret_cast<const uint4*>(xr + k * 256 + lane * 8);
+        const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+        xf[k][0] = v0.x; xf[k][1] = v0.y; xf[k][2] = v1.x; xf[k][3] = v1.y;
+        xf[k][4] = v2.x; xf[k][5] = v2.y; xf[k][6] = v3.x; xf[k][7] = v3.y;
       }
-      s = warp_sum(s);
-      if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, jseed);
-      if (e == lane) l0 = s;
-      if (e == lane + 32) l1 = s;
+#pragma unroll 2
+      for (int e = 0; e < ne; ++e) {
+        const float* wr = a.router_w + (size_t)e * d + lane * 8;
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV8; ++k) {
+          const float4 w0 = *reinterpret_cast<const float4*>(wr + k * 256);
+          const float4 w1 = *reinterpret_cast<const float4*>(wr + k * 256 + 4);
+          s += xf[k][0] * w0.x + xf[k][1] * w0.y + xf[k][2] * w0.z + xf[k][3] * w0.w +
+               xf[k][4] * w1.x + xf[k][5] * w1.y + xf[k][6] * w1.z + xf[k][7] * w1.w;
+        }
+        s = warp_sum(s);
+        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, jseed);
+        if (e == lane) l0 = s;
+        if (e == lane + 32) l1 = s;
+      }
+    } else {
+      for (int e = 0; e < ne; ++e) {
+        const float* wr = a.router_w + (size_t)e * d;
+        float s = 0.f;
+        for (int i = lane * 2; i < d; i += 64) {
+          const float2 xv = Cvt<T>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
+          const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+          s += xv.x * wv.x + xv.y * wv.y;
+        }
+        s = warp_sum(s);
+        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, jseed);
+        if (e == lane) l0 = s;
+        if (e == lane + 32) l1 = s;
+      }
     }
     const float mx = warp_max(fmaxf(l0, l1));
     const float e0 = lane < ne ? __expf(l0 - mx) : 0.f;
@@ -477,8 +507,17 @@ extern "C" int gb_moe_route(const gb_moe_args* a, cudaStream_t st) {
   int rc = moe_check(a);
   if (rc) return rc;
   const int nb = gb_moe_num_blocks(a->n_tok);
-  if (a->is_bf16) moe_route_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(*a);
-  else moe_route_kernel<__half><<<nb, 256, 0, st>>>(*a);
+  const bool vec = a->d % 256 == 0 && a->d <= 1024 && (((uintptr_t)a->x16 | (uintptr_t)a->router_w) & 15) == 0;
+#define GB_ROUTE(T)                                                           \
+  switch (vec ? a->d / 256 : 0) {                                             \
+    case 1: moe_route_kernel<T, 1><<<nb, 256, 0, st>>>(*a); break;            \
+    case 2: moe_route_kernel<T, 2><<<nb, 256, 0, st>>>(*a); break;            \
+    case 3: moe_route_kernel<T, 3><<<nb, 256, 0, st>>>(*a); break;            \
+    case 4: moe_route_kernel<T, 4><<<nb, 256, 0, st>>>(*a); break;            \
+    default: moe_route_kernel<T, 0><<<nb, 256, 0, st>>>(*a); break;           \
+  }
+  if (a->is_bf16) { GB_ROUTE(__nv_bfloat16) } else { GB_ROUTE(__half) }
+#undef GB_ROUTE
   if (a->aux_m) moe_colmean_kernel<<<a->ne, 256, 0, st>>>(a->probs, a->aux_m, a->n_tok, a->ne);
   return GB_OK();
 }

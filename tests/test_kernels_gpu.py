@@ -62,7 +62,8 @@ def test_rmsnorm_fwd_bwd(dt):
     assert torch.equal(dw, dw2)
 
 
-@pytest.mark.parametrize("hd,rope_type,use_norm", [(64, 0, True), (64, 1, True), (32, 0, False), (128, 1, True)])
+@pytest.mark.parametrize("hd,rope_type,use_norm", [(64, 0, True), (64, 1, True), (32, 0, False), (128, 1, True),
+                                                  (256, 0, True), (96, 1, True), (32, 1, True)])
 def test_qk_norm_rope(hd, rope_type, use_norm):
     k, r = K(), R()
     dt = torch.float16
@@ -161,12 +162,12 @@ def _moe_setup(n, d, ne, Kk, shared, seed=0, dt=torch.float16):
     return x16, rw
 
 
-@pytest.mark.parametrize("n,ne,Kk,shared,jit", [(300, 8, 2, True, 0.0), (513, 8, 4, True, 0.01), (64, 4, 2, False, 0.0),
-                                               (1000, 64, 8, True, 0.0)])
-def test_moe_route_group_matches_reference(n, ne, Kk, shared, jit):
+@pytest.mark.parametrize("n,ne,Kk,shared,jit,d", [(300, 8, 2, True, 0.0, 128), (513, 8, 4, True, 0.01, 128),
+                                                 (64, 4, 2, False, 0.0, 128), (1000, 64, 8, True, 0.0, 128),
+                                                 (777, 8, 4, True, 0.01, 768), (300, 16, 2, False, 0.0, 256)])
+def test_moe_route_group_matches_reference(n, ne, Kk, shared, jit, d):
     k, r = K(), R()
     from ghassan_b200.models.config import ModelConfig
-    d = 128
     dt = torch.float16
     x16, rw = _moe_setup(n, d, ne, Kk, shared)
     bias = rnd(ne, seed=9, scale=0.01)
