@@ -744,6 +744,30 @@ __global__ void attn_tc_delta_kernel(const T* __restrict__ d_o, long long ld_do,
   if (lane == 0) delta[gw] = s;
 }
 
+// The same with HD/8 lanes per (token, head) and one 16-byte load of each operand per lane: 256/HD rows per warp.
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) attn_tc_delta_vec_kernel(const T* __restrict__ d_o, long long ld_do,
+                                                                const T* __restrict__ o, long long ld_o,
+                                                                float* __restrict__ delta, long long n_tok, int H) {
+  constexpr int LPI = HD / 8, IPW = 32 / LPI;
+  const int lane = threadIdx.x & 31, sub = lane / LPI, j = lane % LPI;
+  const long long item = (blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5)) * IPW + sub;
+  const bool live = item < n_tok * H;
+  float s = 0.f;
+  if (live) {
+    const long long t = item / H;
+    const int h = (int)(item - t * H);
+    const uint4 qa = *reinterpret_cast<const uint4*>(d_o + t * ld_do + (long long)h * HD + 8 * j);
+    const uint4 qb = *reinterpret_cast<const uint4*>(o + t * ld_o + (long long)h * HD + 8 * j);
+    const float2 a0 = Cvt<T>::unpack2(qa.x), a1 = Cvt<T>::unpack2(qa.y), a2 = Cvt<T>::unpack2(qa.z), a3 = Cvt<T>::unpack2(qa.w);
+    const float2 b0 = Cvt<T>::unpack2(qb.x), b1 = Cvt<T>::unpack2(qb.y), b2 = Cvt<T>::unpack2(qb.z), b3 = Cvt<T>::unpack2(qb.w);
+    s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+  }
+#pragma unroll
+  for (int off = LPI / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (live && j == 0) delta[item] = s;
+}
+
 template <typename T, int HD>
 int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) {
   constexpr int STAGES = HD == 64 ? 2 : 1;
@@ -753,8 +777,14 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   if (gb_make_tmap_2d_16b(&tk, a->k, rows, (uint64_t)a->KV * HD, a->ld_k, AT_N, 64, a->is_bf16)) return -21;
   if (gb_make_tmap_2d_16b(&tv, a->v, rows, (uint64_t)a->KV * HD, a->ld_v, AT_N, 64, a->is_bf16)) return -22;
   if (gb_make_tmap_2d_16b(&tdo, a->d_o, rows, (uint64_t)a->H * HD, a->ld_do, AT_M, 64, a->is_bf16)) return -23;
-  attn_tc_delta_kernel<T><<<(unsigned)((rows * a->H + 7) / 8), 256, 0, st>>>(
-      reinterpret_cast<const T*>(a->d_o), a->ld_do, reinterpret_cast<const T*>(a->o), a->ld_o, a->delta, rows, a->H, HD);
+  if (a->ld_do % 8 == 0 && a->ld_o % 8 == 0 && (((uintptr_t)a->d_o | (uintptr_t)a->o) & 15) == 0) {
+    constexpr int per_block = 8 * (256 / HD);
+    attn_tc_delta_vec_kernel<T, HD><<<(unsigned)((rows * a->H + per_block - 1) / per_block), 256, 0, st>>>(
+        reinterpret_cast<const T*>(a->d_o), a->ld_do, reinterpret_cast<const T*>(a->o), a->ld_o, a->delta, rows, a->H);
+  } else {
+    attn_tc_delta_kernel<T><<<(unsigned)((rows * a->H + 7) / 8), 256, 0, st>>>(
+        reinterpret_cast<const T*>(a->d_o), a->ld_do, reinterpret_cast<const T*>(a->o), a->ld_o, a->delta, rows, a->H, HD);
+  }
   AttnTcParams p{};
   p.B = a->B; p.T = a->T; p.H = a->H; p.KV = a->KV; p.window = a->window; p.scale = a->scale;
   p.lo = lo; p.lse = a->lse; p.delta = a->delta; p.status = status;

@@ -744,7 +744,9 @@ static int qk_fwd_t(const void* qkv, int ld_in, void* out, int ld_out, const flo
   const int wpb = 8;
   const bool aligned = ld_in % 8 == 0 && ld_out % 8 == 0 && (qw == nullptr) == (kw == nullptr) &&
                        (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)cs | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
-  if (aligned && (hd == 32 || hd == 64 || hd == 128 || hd == 256)) {
+  // Up to 64 tokens (a decode step) keep the one-item-per-warp kernel: its sums are grouped exactly as in the
+  // token step's fused QK-norm + RoPE + cache-append kernel, so the two decode paths stay bit-identical.
+  if (aligned && n_tok > 64 && (hd == 32 || hd == 64 || hd == 128 || hd == 256)) {
     const int ipb = wpb * (256 / hd);   // items per block
     dim3 vgrid((items + ipb - 1) / ipb);
 #define GB_QK_FWD_VEC(HD) \

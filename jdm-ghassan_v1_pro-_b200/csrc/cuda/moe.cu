@@ -420,6 +420,7 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
         const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
         acc[0] += v0.x; acc[1] += v0.y; acc[2] += v1.x; acc[3] += v1.y; acc[4] += v2.x; acc[5] += v2.y; acc[6] += v3.x; acc[7] += v3.y;
       }
+#pragma unroll 4
     for (int e = 0; e < ne; ++e) {
       const float dl = __shfl_sync(0xffffffffu, e < 32 ? dl0 : dl1, e & 31);
       const float4 w0 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i);
