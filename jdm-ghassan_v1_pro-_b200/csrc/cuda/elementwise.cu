@@ -106,6 +106,44 @@ __global__ void __launch_bounds__(EMB_THREADS) embed_bwd_kernel(const int* __res
     }
 }
 
+__global__ void __launch_bounds__(EMB_THREADS) embed_bwd_sorted_kernel(const int* __restrict__ sid,
+                                                                      const long long* __restrict__ order,
+                                                                      const float* __restrict__ dx, float* __restrict__ dtable,
+                                                                      int n_tok, int d, int vocab) {
+  const int p = blockIdx.x;
+  if (p >= n_tok) return;
+  const int id = sid[p];
+  if (id < 0 || id >= vocab) return;
+  if (p > 0 && sid[p - 1] == id) return;          // not the first position of this id's run
+  float acc[EMB_MAX_COLS];
+  const int ncol = (d + EMB_THREADS - 1) / EMB_THREADS;
+#pragma unroll
+  for (int c = 0; c < EMB_MAX_COLS; ++c) acc[c] = 0.f;
+  long long tok = order[p];
+  for (int q = p; q < n_tok; ++q) {
+    const bool more = q + 1 < n_tok && sid[q + 1] == id;
+    const long long next_tok = more ? order[q + 1] : 0;   // fetched while this row is added
+    if (tok >= 0 && tok < n_tok) {
+      const float* src = dx + (size_t)tok * d;
+#pragma unroll
+      for (int c = 0; c < EMB_MAX_COLS; ++c)
+        if (c < ncol) {
+          const int col = c * EMB_THREADS + threadIdx.x;
+          if (col < d) acc[c] += src[col];
+        }
+    }
+    if (!more) break;
+    tok = next_tok;
+  }
+  float* dst = dtable + (size_t)id * d;
+#pragma unroll
+  for (int c = 0; c < EMB_MAX_COLS; ++c)
+    if (c < ncol) {
+      const int col = c * EMB_THREADS + threadIdx.x;
+      if (col < d) dst[col] += acc[c];
+    }
+}
+
 // ------------------------------------------------------------------------------------------ RMSNorm
 // One warp per row.  y16 = x * inv * w (16-bit), rrms[row] = inv;  inv = 0 when it is not finite.
 template <typename T>
@@ -673,6 +711,17 @@ extern "C" int gb_embed_bwd(const int* ids, const float* dx, float* dtable, int 
   if (cudaMemsetAsync(first, 0x7f, (size_t)vocab * sizeof(int), st) != cudaSuccess) return -12;   // 0x7f7f7f7f > any token index
   embed_first_kernel<<<(n_tok + 255) / 256, 256, 0, st>>>(ids, n_tok, vocab);
   embed_bwd_kernel<<<n_tok, EMB_THREADS, 0, st>>>(ids, dx, dtable, n_tok, d, vocab);
+  return GB_LAUNCH_OK();
+}
+
+// The same sums from ids that were sorted with a STABLE sort (sorted_ids ascending, order[p] = the token that
+// landed at p): the tokens of one id are neighbours and already in increasing token order, so the block at the
+// first position of a run adds that run's rows and every other block leaves.  Linear in the number of tokens,
+// where the unsorted form above walks the whole id list once per distinct id.
+extern "C" int gb_embed_bwd_sorted(const int* sorted_ids, const long long* order, const float* dx, float* dtable,
+                                   int n_tok, int d, int vocab, cudaStream_t st) {
+  if (d > EMB_THREADS * EMB_MAX_COLS || vocab <= 0 || n_tok <= 0) return -1;
+  embed_bwd_sorted_kernel<<<n_tok, EMB_THREADS, 0, st>>>(sorted_ids, order, dx, dtable, n_tok, d, vocab);
   return GB_LAUNCH_OK();
 }
 

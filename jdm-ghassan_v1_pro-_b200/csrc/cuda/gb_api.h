@@ -43,6 +43,8 @@ int gb_gemm(const gb_gemm_args* args, cudaStream_t stream);
 // ----------------------------------------------------------------------------- elementwise.cu
 int gb_embed_fwd(const int* ids, const float* table, float* out, int n_tok, int d, int vocab, cudaStream_t st);
 int gb_embed_bwd(const int* ids, const float* dx, float* dtable, int n_tok, int d, int vocab, cudaStream_t st);
+int gb_embed_bwd_sorted(const int* sorted_ids, const long long* order, const float* dx, float* dtable, int n_tok,
+                        int d, int vocab, cudaStream_t st);
 int gb_rmsnorm_fwd(const float* x, const float* w, void* y16, float* rrms, int rows, int d, float eps, int is_bf16,
                    cudaStream_t st);
 int gb_rmsnorm_bwd_blocks(int rows);

@@ -274,28 +274,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       TileInfo t = decode_tile<BN>(p, tile, tiles_m, tiles_n);
       const bool empty_k = (t.k_end <= t.k_begin);
-      // SwiGLU backward: the saved (gate, up) values of a 32-column chunk, still packed.  A chunk is fetched one
-      // chunk ahead -- the first one before the wait for the accumulator -- so that its DRAM round trip runs under
-      // the arithmetic of the chunk before it (fetched at the point of use, the eight epilogue warps kept too few
-      // bytes in flight and this epilogue, not the MMA, set the pace of the kernel).
-      uint4 ng[4], nu[4];
-      bool nfast = false;
-      auto fetch_gu = [&](int c) {
-        if constexpr (EPI == EPI_SWIGLU_BWD && sizeof(InT) == 2) {
-          const int j = t.n0 + c * 32;
-          const InT* src = reinterpret_cast<const InT*>(p.aux_in) + (long long)(t.a_row0 + r_in_tile) * p.ld_aux +
-                           (j >> 6) * 128 + (j & 63);
-          nfast = t.a_row0 + r_in_tile < p.M && p.N - j >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
-          if (nfast) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              ng[i] = reinterpret_cast<const uint4*>(src)[i];
-              nu[i] = reinterpret_cast<const uint4*>(src + 64)[i];
-            }
-          }
-        }
-      };
-      if constexpr (EPI == EPI_SWIGLU_BWD) fetch_gu((warp >> 2) * (BN / 64));
       uint32_t ab = 0;
       if (!empty_k) {
         ab = acc_it & 1;
@@ -402,11 +380,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         OutT* dgu = reinterpret_cast<OutT*>(p.out) + (long long)row * p.ldo;
 #pragma unroll 1
         for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-          uint4 cg[4], cu[4];
-          const bool cfast = nfast;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { cg[i] = ng[i]; cu[i] = nu[i]; }
-          if (c + 1 < (half + 1) * (BN / 64)) fetch_gu(c + 1);
           uint32_t r[32];
           tmem_ld_32x32(taddr0 + c * 32, r);
           tmem_ld_wait();
@@ -415,22 +388,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (row_ok && nvalid > 0) {
             const int base = (j >> 6) * 128 + (j & 63);
             float g[32], u[32], dg[32], du[32];
-            if (cfast) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 g0 = Cvt<InT>::unpack2(cg[i].x), g1 = Cvt<InT>::unpack2(cg[i].y);
-                const float2 g2 = Cvt<InT>::unpack2(cg[i].z), g3 = Cvt<InT>::unpack2(cg[i].w);
-                const float2 u0 = Cvt<InT>::unpack2(cu[i].x), u1 = Cvt<InT>::unpack2(cu[i].y);
-                const float2 u2 = Cvt<InT>::unpack2(cu[i].z), u3 = Cvt<InT>::unpack2(cu[i].w);
-                g[8 * i + 0] = g0.x; g[8 * i + 1] = g0.y; g[8 * i + 2] = g1.x; g[8 * i + 3] = g1.y;
-                g[8 * i + 4] = g2.x; g[8 * i + 5] = g2.y; g[8 * i + 6] = g3.x; g[8 * i + 7] = g3.y;
-                u[8 * i + 0] = u0.x; u[8 * i + 1] = u0.y; u[8 * i + 2] = u1.x; u[8 * i + 3] = u1.y;
-                u[8 * i + 4] = u2.x; u[8 * i + 5] = u2.y; u[8 * i + 6] = u3.x; u[8 * i + 7] = u3.y;
-              }
-            } else {
-              load_row32<InT>(gu + base, g, nvalid);
-              load_row32<InT>(gu + base + 64, u, nvalid);
-            }
+            load_row32<InT>(gu + base, g, nvalid);
+            load_row32<InT>(gu + base + 64, u, nvalid);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float da = __uint_as_float(r[i]);

@@ -68,6 +68,7 @@ def _protos():
                                 c_void_p, c_int, c_void_p]
     L.gb_embed_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     L.gb_embed_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    L.gb_embed_bwd_sorted.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     L.gb_rmsnorm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
     L.gb_rmsnorm_bwd.argtypes = [c_void_p] * 9 + [c_int, c_int, c_int, c_void_p]
     L.gb_qk_norm_rope_fwd.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -91,8 +92,18 @@ def embed_fwd(ids, table, out):
     return out
 
 
-def embed_bwd(ids, dx, dtable):
+def embed_bwd(ids, dx, dtable, presorted: bool = True):
+    """dtable[id] += the rows of dx whose token has that id, added in token order (bit-reproducible).
+
+    `presorted` (default): the ids go through a stable sort first (torch.sort on n int32 values: a library radix sort,
+    not a hot op) and the kernel adds each run of equal ids from its first position: linear in n.  Without it the
+    kernel finds the later occurrences of an id by walking the id list: no scratch memory, quadratic in n."""
     n, d = dx.shape
+    if presorted and n > 1:
+        sid, order = torch.sort(ids, stable=True)
+        check_rc(_protos().gb_embed_bwd_sorted(_p(sid), _p(order), _p(dx), _p(dtable), n, d, dtable.shape[0],
+                                               stream_ptr()), "embed_bwd_sorted")
+        return
     check_rc(_protos().gb_embed_bwd(_p(ids), _p(dx), _p(dtable), n, d, dtable.shape[0], stream_ptr()), "embed_bwd")
 
 

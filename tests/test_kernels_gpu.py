@@ -376,6 +376,9 @@ def test_embedding_gather_scatter():
         k.embed_bwd(ids, dx, g)
         runs.append(g)
     assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+    g = torch.full((V, d), 0.25, device="cuda")
+    k.embed_bwd(ids, dx, g, presorted=False)          # the scratch-free walk adds in the same order: same bits
+    assert torch.equal(runs[0], g)
     ok = (ids >= 0) & (ids < V)
     ref = torch.full((V, d), 0.25, device="cuda", dtype=torch.float64).index_add_(0, ids[ok].long(), dx[ok].double())
     assert near(runs[0], ref.float(), 1e-5, 1e-5)[0]
