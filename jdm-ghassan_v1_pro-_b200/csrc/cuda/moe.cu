@@ -369,6 +369,12 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
   if (t >= a.n_tok) return;
   const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
   // ---- router-logit gradient (lane e and e+32 hold expert e / e+32)
+  // the slot positions first: they do not depend on the router part, and after its stores the compiler could not
+  // move these loads up by itself
+  int pos[MAX_K + 1];
+#pragma unroll
+  for (int s = 0; s <= MAX_K; ++s)
+    if (s < S) pos[s] = a.slot_pos[(size_t)t * S + s];
   const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
   const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
   float dp0 = 0.f, dp1 = 0.f;
@@ -381,7 +387,7 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
   float ssum = 0.f, gbar = 0.f;
   for (int k = 0; k < K; ++k) {
     const int e = a.idx[(size_t)t * K + k];
-    const float pe = a.probs[(size_t)t * ne + e];
+    const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);   // probs[t, e], already in a lane
     ssum += pe;
     gbar += a.gdot[(size_t)t * K + k] * a.w[(size_t)t * K + k];
   }
@@ -405,10 +411,6 @@ __global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a
   // ---- input gradient
   const T* dxp = reinterpret_cast<const T*>(a.dx_perm);
   T* dx = reinterpret_cast<T*>(a.dx16);
-  int pos[MAX_K + 1];
-#pragma unroll
-  for (int s = 0; s <= MAX_K; ++s)
-    if (s < S) pos[s] = a.slot_pos[(size_t)t * S + s];
   for (int i = lane * 8; i < d; i += 256) {
     float acc[8];
 #pragma unroll
