@@ -235,10 +235,12 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ g, const float* __restr
 }
 
 // The same for d = 128 * NV with a whole row in registers: every load of a row (x, g, dres) is issued before the
-// first use, the row is read once, and the column sums stay in registers until the end.  The rolled loop above
-// waits for DRAM twelve times per row and ran at about half of the copy bandwidth.  8 warps per block.
+// first use and the row is read once.  The rolled loop above waits for DRAM twelve times per row and ran at about
+// half of the copy bandwidth.  The column sums of dw live in the warp's own slice of shared memory (lanes own
+// distinct columns), not in registers: that keeps the kernel at 64 registers and four blocks of 8 warps per SM,
+// and the number of rows in flight is what this kernel's speed depends on.
 template <typename T, int NV>
-__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_vec_kernel(const T* __restrict__ g, const float* __restrict__ x,
+__global__ void __launch_bounds__(256, 4) rmsnorm_bwd_vec_kernel(const T* __restrict__ g, const float* __restrict__ x,
                                                               const float* __restrict__ w, const float* __restrict__ rrms,
                                                               const float* __restrict__ dres, float* __restrict__ dx_out,
                                                               T* __restrict__ dx16, float* __restrict__ part, int rows,
@@ -248,10 +250,10 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_vec_kernel(const T* __rest
   float* s_w = sm_dw_all + 8 * D;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < D; i += blockDim.x) s_w[i] = w[i];
-  __syncthreads();
-  float acc[NV][4];
+  float* s_acc = sm_dw_all + (size_t)warp * D + lane * 4;
 #pragma unroll
-  for (int k = 0; k < NV; ++k) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f;
+  for (int k = 0; k < NV; ++k) *reinterpret_cast<float4*>(s_acc + k * 128) = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
   const int row0 = blockIdx.x * rows_per_block;
   const int row1 = min(rows, row0 + rows_per_block);
   for (int row = row0 + warp; row < row1; row += 8) {
@@ -293,16 +295,14 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_vec_kernel(const T* __rest
         q.y = Cvt<T>::pack2(o.z, o.w);
         *reinterpret_cast<uint2*>(dx16 + (size_t)row * D + i) = q;
       }
-      acc[k][0] += g01.x * xv[k].x * inv;
-      acc[k][1] += g01.y * xv[k].y * inv;
-      acc[k][2] += g23.x * xv[k].z * inv;
-      acc[k][3] += g23.y * xv[k].w * inv;
+      float4 a = *reinterpret_cast<float4*>(s_acc + k * 128);
+      a.x += g01.x * xv[k].x * inv;
+      a.y += g01.y * xv[k].y * inv;
+      a.z += g23.x * xv[k].z * inv;
+      a.w += g23.y * xv[k].w * inv;
+      *reinterpret_cast<float4*>(s_acc + k * 128) = a;
     }
   }
-#pragma unroll
-  for (int k = 0; k < NV; ++k)
-    *reinterpret_cast<float4*>(sm_dw_all + (size_t)warp * D + k * 128 + lane * 4) =
-        make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float s = 0.f;
@@ -738,7 +738,7 @@ extern "C" int gb_rmsnorm_fwd(const float* x, const float* w, void* y, float* rr
 // Number of row blocks (and rows of the partial buffer) gb_rmsnorm_bwd uses for `rows`.
 extern "C" int gb_rmsnorm_bwd_blocks(int rows) {
   int b = (rows + 7) / 8;   // one row per warp while that still fits a modest partial buffer
-  return b > 296 ? 296 : (b < 1 ? 1 : b);
+  return b > 592 ? 592 : (b < 1 ? 1 : b);   // four blocks of 8 warps per SM
 }
 
 // dw (fp32 [d]) is accumulated (+=).  `part` must hold gb_rmsnorm_bwd_blocks(rows) * d floats.

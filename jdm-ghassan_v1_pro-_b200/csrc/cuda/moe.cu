@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const gb_moe_args 
 // Per token: sum the sorted-order input gradients of its slots, add the router path, write 16-bit dx and the
 // router-logit gradients (into `part`, [n_tok, ne]).
 template <typename T>
-__global__ void __launch_bounds__(256) moe_router_bwd_kernel(const gb_moe_args a) {
+__global__ void __launch_bounds__(256, 4) moe_router_bwd_kernel(const gb_moe_args a) {
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= a.n_tok) return;
   const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
