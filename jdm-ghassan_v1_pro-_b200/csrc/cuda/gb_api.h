@@ -37,8 +37,14 @@ typedef struct gb_gemm_args {
   int* status;              // device status word
   const long long* tile_out;  // mode 1 + plain store, no addend: device table with the address of output row 0 of every
                               // 128-row tile (overrides out); destinations may be another GPU's mapped memory
+  int pair;                   // 1: two-CTA 256 x 256 tiles (gemm_pair_sm100.cu).  Needs a 16-byte aligned output whose
+                              // row pitch is a multiple of 16 bytes, no tile_out, an addend only with fp32 output, and
+                              // in mode 1 expert segments padded to GB_MOE_PAD rows; block_n is ignored
 } gb_gemm_args;
 int gb_gemm(const gb_gemm_args* args, cudaStream_t stream);
+int gb_gemm_pair(const gb_gemm_args* args, cudaStream_t stream);   // what gb_gemm calls when args->pair != 0
+// Expert segments of the sorted MoE buffers start at multiples of this many rows (two 128-row tiles: one pair tile).
+#define GB_MOE_PAD 256
 
 // ----------------------------------------------------------------------------- elementwise.cu
 int gb_embed_fwd(const int* ids, const float* table, float* out, int n_tok, int d, int vocab, cudaStream_t st);

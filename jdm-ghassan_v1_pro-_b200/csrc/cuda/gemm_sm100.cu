@@ -505,6 +505,7 @@ int dispatch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const gb::
 // Public launcher.  All pointers are device pointers; see gb_api.h for the argument contract.
 extern "C" int gb_gemm(const gb_gemm_args* a, cudaStream_t st) {
   if (!a || a->M <= 0 || a->N <= 0 || a->K < 0) return -1;
+  if (a->pair) return gb_gemm_pair(a, st);
   const int bn = a->block_n ? a->block_n : 128;
   if (bn != 64 && bn != 128 && bn != 256) return -1;
   gb::GemmParams p{};

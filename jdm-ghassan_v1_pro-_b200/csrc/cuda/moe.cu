@@ -182,7 +182,7 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks, int staged) {
     int off = 0;
     for (int i = 0; i < ne1; ++i) {
       s_off[i] = off;
-      off += (s_total[i] + 127) / 128 * 128;
+      off += (s_total[i] + GB_MOE_PAD - 1) / GB_MOE_PAD * GB_MOE_PAD;
     }
     s_off[ne1] = off;
     for (int i = 0; i <= ne1; ++i) a.seg_offsets[i] = s_off[i];
@@ -500,8 +500,8 @@ extern "C" int gb_moe_num_blocks(int n_tok) { return (n_tok + blk_tok(n_tok) - 1
 
 extern "C" int gb_moe_capacity(int n_tok, int ne, int top_k, int shared) {
   const long long slots = (long long)n_tok * (top_k + (shared ? 1 : 0));
-  const long long cap = slots + (long long)(ne + (shared ? 1 : 0)) * 127;
-  return (int)((cap + 127) / 128 * 128);
+  const long long cap = slots + (long long)(ne + (shared ? 1 : 0)) * (GB_MOE_PAD - 1);
+  return (int)((cap + GB_MOE_PAD - 1) / GB_MOE_PAD * GB_MOE_PAD);
 }
 
 #define GB_OK() (gb_launch_rc())

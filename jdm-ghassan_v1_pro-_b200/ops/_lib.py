@@ -38,6 +38,7 @@ class GemmArgs(ctypes.Structure):
         ("aux_out", c_vp), ("aux_in", c_vp), ("ld_aux", c_int),
         ("status", c_vp),
         ("tile_out", c_vp),
+        ("pair", c_int),
     ]
 
 
@@ -91,6 +92,7 @@ STATUS_NAMES = {
     102: "timeout waiting for a free shared-memory stage (empty barrier)",
     103: "timeout waiting for the accumulator (tmem full barrier)",
     104: "timeout waiting for an accumulator buffer (tmem empty barrier)",
+    105: "timeout waiting for an epilogue warp's own TMA load",
     201: "timeout waiting for a peer rank's flag",
     301: "bad argument detected on device",
     302: "expert parallelism: more rows were routed to this rank's experts than its buffers hold (raise b200.ep_capacity)",

@@ -8,12 +8,33 @@ bf16, accumulation is fp32, the output dtype is chosen by the caller.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from . import _lib
 
 EPI_STORE, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2
+
+# Two-CTA 256 x 256 tiles (csrc/cuda/gemm_pair_sm100.cu) are taken when the problem has at least this many of them
+# (74 CTA pairs on a B200); GB200_GEMM_PAIR=0 keeps every product on the one-CTA kernel.
+PAIR_ENABLED = os.environ.get("GB200_GEMM_PAIR", "1") != "0"
+PAIR_MIN_TILES = int(os.environ.get("GB200_GEMM_PAIR_MIN_TILES", "60"))
+
+
+def pair_tiles(M, N, groups=1):
+    return ((M + 255) // 256) * ((N + 255) // 256) * groups
+
+
+def pair_ok(M, N, out, groups=1, extra=()):
+    """True when the two-CTA kernel can and should run this product: enough 256 x 256 tiles, and every matrix that
+    its epilogue moves with TMA (the output, saved gate/up) 16-byte aligned with a 16-byte row pitch."""
+    if not PAIR_ENABLED or pair_tiles(M, N, groups) < PAIR_MIN_TILES:
+        return False
+    for t in (out,) + tuple(extra):
+        if t is not None and (t.data_ptr() % 16 or (t.stride(-2) * t.element_size()) % 16):
+            return False
+    return True
 
 
 def _check_operand(t, name):
@@ -64,18 +85,22 @@ def pick_block_n(M, N, mn_major=False):
     return 128
 
 
-def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, addend=None, block_n=0):
-    """``out = A @ B^T (+ addend)``; ``addend`` is fp32 and may alias an fp32 ``out`` (accumulate)."""
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, addend=None, block_n=0, pair=None):
+    """``out = A @ B^T (+ addend)``; ``addend`` is fp32 and may alias an fp32 ``out`` (accumulate).
+    ``pair``: force (True) or forbid (False) the two-CTA kernel; None picks by size."""
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     if K != Kb:
         raise ValueError(f"reduction dims differ: {K} vs {Kb}")
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    if pair is None:
+        pair = (block_n in (0, 256) and (addend is None or out.dtype == torch.float32) and pair_ok(M, N, out))
     if not block_n:
         block_n = pick_block_n(M, N, mn_major=a_mn and b_mn)
     g = _base_args(a, b, M, N, K, a_mn, b_mn, out, block_n)
     g.epilogue = EPI_STORE
+    g.pair = int(bool(pair))
     if addend is not None:
         if addend.dtype != torch.float32:
             raise ValueError("addend must be fp32")
@@ -84,7 +109,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, addend=None,
     return out
 
 
-def gemm_swiglu(a, w_gu, *, act_out=None, gu_out=None, tile_expert=None, num_m_tiles=None, group_rows=0):
+def gemm_swiglu(a, w_gu, *, act_out=None, gu_out=None, tile_expert=None, num_m_tiles=None, group_rows=0, pair=None):
     """Fused ``[gate|up]`` projection + SwiGLU.
 
     ``w_gu`` stores gate and up rows interleaved in blocks of 64 (``g0..g63,u0..u63,g64..``) so that one
@@ -100,6 +125,7 @@ def gemm_swiglu(a, w_gu, *, act_out=None, gu_out=None, tile_expert=None, num_m_t
         act_out = torch.empty(M, N // 2, dtype=a.dtype, device=a.device)
     g = _base_args(a, w_gu, M, N, K, False, False, act_out, 256 if (N % 256 == 0 and M >= 4096) else 128)
     g.epilogue = EPI_SWIGLU_FWD
+    g.pair = int(pair_ok(M, N, act_out, extra=(gu_out,)) if pair is None else bool(pair))
     if gu_out is not None:
         g.aux_out, g.ld_aux = gu_out.data_ptr(), gu_out.stride(0)
     if tile_expert is not None:
@@ -111,7 +137,7 @@ def gemm_swiglu(a, w_gu, *, act_out=None, gu_out=None, tile_expert=None, num_m_t
 
 
 def gemm_swiglu_bwd(dy, w_down, gu, *, dgu_out=None, b_mn=True, tile_expert=None, num_m_tiles=None, group_rows=0,
-                    n=None):
+                    n=None, pair=None):
     """``d_act = dy @ W_down`` fused with the SwiGLU derivative: writes interleaved ``(dg, du)``.
 
     ``w_down`` is the stored ``[d, E]`` matrix (``[ne*d, E]`` when grouped), i.e. B in ``[K, N]`` layout.
@@ -123,6 +149,7 @@ def gemm_swiglu_bwd(dy, w_down, gu, *, dgu_out=None, b_mn=True, tile_expert=None
     g = _base_args(dy, w_down, M, N, K, False, b_mn, dgu_out,
                    256 if (N % 256 == 0 and M >= 4096) else (128 if N % 128 == 0 else 64))
     g.epilogue = EPI_SWIGLU_BWD
+    g.pair = int((N % 64 == 0 and pair_ok(M, N, dgu_out, extra=(gu,))) if pair is None else bool(pair))
     g.aux_in, g.ld_aux = gu.data_ptr(), gu.stride(0)
     if tile_expert is not None:
         g.mode = 1
@@ -133,8 +160,9 @@ def gemm_swiglu_bwd(dy, w_down, gu, *, dgu_out=None, b_mn=True, tile_expert=None
 
 
 def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_rows, out=None, out_dtype=None,
-                      block_n=0, tile_out=None, ldo=None):
+                      block_n=0, tile_out=None, ldo=None, pair=None):
     """Expert-sorted rows: every 128-row tile of ``a`` multiplies the weight block of ``tile_expert[tile]``.
+    The two-CTA kernel (``pair``) needs tiles ``2i`` and ``2i+1`` to belong to one expert: segments padded to 256 rows.
 
     ``b`` stacks the per-expert matrices along its rows: ``group_rows`` stored rows per expert.
     ``tile_out`` (device int64 table, one entry per 128-row tile) redirects each tile's rows to the given address,
@@ -145,9 +173,12 @@ def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_ro
         out = torch.empty((M, n) if tile_out is None else (1, n), dtype=out_dtype or a.dtype, device=a.device)
     if not block_n:
         block_n = 256 if (n % 256 == 0 and M >= 4096) else 128
+    if pair is None:
+        pair = tile_out is None and pair_ok(M, n, out)
     g = _base_args(a, b, M, n, K, False, b_mn, out, block_n)
     g.epilogue = EPI_STORE
     g.mode = 1
+    g.pair = int(bool(pair))
     g.tile_expert, g.num_m_tiles = tile_expert.data_ptr(), num_m_tiles.data_ptr()
     g.b_group_rows = group_rows
     if tile_out is not None:
@@ -159,7 +190,7 @@ def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_ro
     return out
 
 
-def gemm_grouped_reduce(a, b, seg_offsets, groups, out, *, accumulate=True, block_n=0):
+def gemm_grouped_reduce(a, b, seg_offsets, groups, out, *, accumulate=True, block_n=0, pair=None):
     """Per-expert weight gradient: ``out[g] (+)= a[rows_g]^T @ b[rows_g]`` with ``rows_g`` given by the padded
     offsets ``seg_offsets[g] .. seg_offsets[g+1]`` (device int32, multiples of 128; pad rows must be zero).
     ``a`` is ``[rows, M]``, ``b`` is ``[rows, N]``, ``out`` is fp32 ``[groups, M, N]``.
@@ -169,9 +200,12 @@ def gemm_grouped_reduce(a, b, seg_offsets, groups, out, *, accumulate=True, bloc
         raise ValueError("out must be contiguous fp32 [groups, M, N]")
     if not block_n:    # 256-wide tiles measured 1.47x faster once the groups supply tiles for every SM
         block_n = 256 if (N % 256 == 0 and groups * ((M + 127) // 128) * (N // 256) >= 222) else 128
+    if pair is None:
+        pair = pair_ok(M, N, out, groups=groups)
     g = _base_args(a, b, M, N, 0, True, True, out, block_n)
     g.epilogue = EPI_STORE
     g.mode = 2
+    g.pair = int(bool(pair))
     g.seg_offsets = seg_offsets.data_ptr()
     g.groups = groups
     g.out_group_stride = M * N
@@ -227,10 +261,24 @@ def gemm_wgrad(a, b, grad):
     Everything else takes the plain accumulate path."""
     Kt, M = a.shape
     N = b.shape[1]
-    tiles = ((M + 127) // 128) * ((N + 127) // 128)
-    splits = min(8, 148 // max(1, tiles), Kt // 1024)
-    if splits < 2 or Kt % 64 or not grad.is_contiguous() or grad.shape != (M, N) or (M * N) % 4:
-        return gemm(a, b, a_mn=True, b_mn=True, out=grad, addend=grad)
+    splittable = not (Kt % 64 or not grad.is_contiguous() or grad.shape != (M, N) or (M * N) % 4)
+    use_pair = False
+    if PAIR_ENABLED and splittable and pair_tiles(M, N) < PAIR_MIN_TILES:
+        # two-CTA tiles: the split count that best fills the 74 CTA pairs (at most 8 partials, 1024 tokens or more each)
+        t, best = pair_tiles(M, N), (0.0, 1)
+        for sp in range(1, 9):
+            if sp > 1 and Kt // sp < 1024:
+                break
+            eff = t * sp / (-(-t * sp // 74) * 74.0)
+            if eff > best[0] + 0.04:
+                best = (eff, sp)
+        if best[1] >= 2 and t * best[1] >= 30:
+            use_pair, splits = True, best[1]
+    if not use_pair:
+        tiles = ((M + 127) // 128) * ((N + 127) // 128)
+        splits = min(8, 148 // max(1, tiles), Kt // 1024)
+        if splits < 2 or not splittable:
+            return gemm(a, b, a_mn=True, b_mn=True, out=grad, addend=grad)
     key = (M, N, Kt, splits, a.device.index)
     plan = _WGRAD_PLANS.get(key)
     if plan is None:
@@ -243,6 +291,7 @@ def gemm_wgrad(a, b, grad):
     g = _base_args(a, b, M, N, 0, True, True, part, 128)
     g.epilogue = EPI_STORE
     g.mode = 2
+    g.pair = int(use_pair)
     g.seg_offsets = offsets.data_ptr()
     g.groups = splits
     g.out_group_stride = M * N
