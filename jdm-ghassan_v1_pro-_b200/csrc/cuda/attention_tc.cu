@@ -25,6 +25,13 @@ template <typename T> struct OperandFmt { static constexpr int value = std::is_s
 constexpr int AT_M = 128;        // query rows per tile
 constexpr int AT_N = 128;        // keys per tile
 constexpr int AT_THREADS = 192;
+// Backward kernels: sixteen compute warps.  Warp w owns the 32 tile rows of TMEM lane quarter w % 4 and the 32-column
+// chunk w / 4, so a 128 x 128 score tile is one tcgen05.ld per thread and every scheduler has four warps to switch
+// between (with four compute warps in all, the exp / multiply / pack chain of a tile ran at one warp per scheduler
+// and its latencies were exposed: the tensor pipe sat idle 94 % of the time).  Warp 16 = TMA producer, 17 = MMA issuer.
+constexpr int AT_BWD_CW = 16;
+constexpr int AT_BWD_THREADS = (AT_BWD_CW + 2) * 32;
+constexpr int AT_BWD_W_TMA = AT_BWD_CW, AT_BWD_W_MMA = AT_BWD_CW + 1;
 
 struct AttnTcParams {
   int B, T, H, KV, window;
@@ -310,7 +317,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_co
 // dS = P o (dP - delta) * scale written to shared memory (16-bit operand layout), dQ += dS K accumulated in
 // tensor memory over the whole key loop and read out once.
 template <typename T, int HD, int STAGES>
-__global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                     const __grid_constant__ CUtensorMap tmK,
                                                                     const __grid_constant__ CUtensorMap tmV,
                                                                     const __grid_constant__ CUtensorMap tmDO,
@@ -344,34 +351,35 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 128);
+    mbar_init(ds_ready, AT_BWD_CW * 32);
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     *s_lo_min = 0x7fffffff;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == AT_BWD_W_MMA) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + AT_N, tmem_dQ = tmem_base + 2 * AT_N;
 
-  const int r = threadIdx.x;
+  const int cq = warp >> 2;                     // 32-column chunk of a compute warp
+  const int r = (warp & 3) * 32 + lane;         // query row of a compute thread (its TMEM lane)
   const int i = q0 + r;
-  const bool row_ok = r < AT_M && i < p.T;
+  const bool row_ok = warp < AT_BWD_CW && i < p.T;
   int lo_i = 0;
   if (row_ok) {
     if (p.lo) lo_i = p.lo[row_base + i];
     if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
-    atomicMin(s_lo_min, lo_i);
+    if (cq == 0) atomicMin(s_lo_min, lo_i);
   }
   __syncthreads();
   const int k_hi = min(p.T, q0 + AT_M);
   const int k_lo = (min(*s_lo_min, k_hi - 1) / AT_N) * AT_N;
   const int n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
 
-  if (warp == 4) {
+  if (warp == AT_BWD_W_TMA) {
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, 2 * TILE);
       load_tile<HD>(&tmQ, q_full, sQ, h * HD, (int)row_base + q0);
@@ -385,7 +393,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == AT_BWD_W_MMA) {
     if (lane == 0) {
       constexpr int fmt = OperandFmt<T>::value;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
@@ -407,7 +415,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
     }
     __syncwarp();
   } else {
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float sc = p.scale;
     float lse = INFINITY, dl = 0.f;
     if (row_ok) {
@@ -420,8 +428,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
       if (!at_wait(sdp_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
-#pragma unroll 1
-      for (int c = 0; c < AT_N / 32; ++c) {
+      {
+        const int c = cq;
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(tmem_S + lane_base + c * 32, rs);
         tmem_ld_32x32(tmem_dP + lane_base + c * 32, rp);
@@ -443,8 +451,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
     if (ok && at_wait(dq_full, 0, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) {
       tc_fence_after();
       T* dqp = reinterpret_cast<T*>(p.dq) + (row_base + i) * p.ld_dq + (long long)h * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      if (cq < HD / 32) {
+        const int c = cq;
         uint32_t rg[32];
         tmem_ld_32x32(tmem_dQ + lane_base + c * 32, rg);
         tmem_ld_wait();
@@ -468,7 +476,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
     for (int k = 0; k < 64; ++k) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // ============================================================================================ backward: dK, dV
@@ -477,7 +485,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dq_kernel(const __grid
 // keys, columns = queries), P^T and dS^T written to shared memory, dV += P^T dO and dK += dS^T Q accumulated in
 // tensor memory over all iterations (ordered, so the GQA reduction is deterministic) and read out once.
 template <typename T, int HD, int STAGES>
-__global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                      const __grid_constant__ CUtensorMap tmK,
                                                                      const __grid_constant__ CUtensorMap tmV,
                                                                      const __grid_constant__ CUtensorMap tmDO,
@@ -513,12 +521,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(st_full, 1);
-    mbar_init(pt_ready, 128);
+    mbar_init(pt_ready, AT_BWD_CW * 32);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == AT_BWD_W_MMA) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -532,7 +540,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
   const int n_qt = (i_hi - i_lo + AT_M - 1) / AT_M;
   const int n_it = group * n_qt;
 
-  if (warp == 4) {
+  if (warp == AT_BWD_W_TMA) {
     if (lane == 0) {
       mbar_arrive_expect_tx(kv_full, 2 * TILE);
       load_tile<HD>(&tmK, kv_full, sK, kvh * HD, (int)row_base + j0);
@@ -548,7 +556,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == AT_BWD_W_MMA) {
     if (lane == 0) {
       constexpr int fmt = OperandFmt<T>::value;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
@@ -571,17 +579,18 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
     }
     __syncwarp();
   } else {
-    const int r = threadIdx.x;          // key row of this thread
+    const int cq = warp >> 2;                  // 32-column (query) chunk of this warp
+    const int r = (warp & 3) * 32 + lane;      // key row of this thread (its TMEM lane)
     const int j = j0 + r;
     const bool row_ok = j < p.T;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float sc = p.scale;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const int h = kvh * group + it / n_qt;
       const int i0 = i_lo + (it % n_qt) * AT_M;
       const int bufi = it & 1;
-      {  // stage the per-query statistics of this tile (column r)
+      if (cq == 0) {  // stage the per-query statistics of this tile (column r)
         const int i = i0 + r;
         const bool in = i < p.T;
         sLse[bufi * AT_N + r] = in ? p.lse[(row_base + i) * p.H + h] : INFINITY;
@@ -591,7 +600,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
         if (in && p.window > 0) lo = max(lo, i - p.window + 1);
         sLo[bufi * AT_N + r] = in ? lo : 0x7fffffff;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 512;" ::: "memory");   // all AT_BWD_CW * 32 compute threads
       // after a failed wait the loop keeps running (without waiting or computing) so that every thread still
       // reaches the named barrier above in every iteration
       if (ok && !at_wait(st_full, it & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
@@ -600,8 +609,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
       const float* lse = sLse + bufi * AT_N;
       const float* dl = sDl + bufi * AT_N;
       const int* lo = sLo + bufi * AT_N;
-#pragma unroll 1
-      for (int c = 0; c < AT_M / 32; ++c) {
+      {
+        const int c = cq;
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(tmem_ST + lane_base + c * 32, rs);
         tmem_ld_32x32(tmem_dPT + lane_base + c * 32, rp);
@@ -627,8 +636,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
       tc_fence_after();
       T* dkp = reinterpret_cast<T*>(p.dk) + (row_base + j) * p.ld_dk + (long long)kvh * HD;
       T* dvp = reinterpret_cast<T*>(p.dv) + (row_base + j) * p.ld_dv + (long long)kvh * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      if (cq < HD / 32) {
+        const int c = cq;
         uint32_t rv[32], rk[32];
         tmem_ld_32x32(tmem_dV + lane_base + c * 32, rv);
         tmem_ld_32x32(tmem_dK + lane_base + c * 32, rk);
@@ -658,7 +667,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_bwd_dkv_kernel(const __gri
     for (int k = 0; k < 64; ++k) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // lo[i] = first position of the run of equal segment ids that contains i (per sequence); seg < 0 -> 0
@@ -802,8 +811,8 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   }
   if (a->B > 65535 || (a->T + AT_N - 1) / AT_N > 65535) return -1;   // grid y and z limits
   dim3 gq(a->H, a->B, (a->T + AT_M - 1) / AT_M), gkv(a->KV, a->B, (a->T + AT_N - 1) / AT_N);
-  kq<<<gq, AT_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
-  kkv<<<gkv, AT_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
+  kq<<<gq, AT_BWD_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
+  kkv<<<gkv, AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
   return gb_launch_rc();
 }
 

@@ -29,19 +29,19 @@ extern "C" {
 // sit in the static scratch.  g: device, 16-byte aligned, n floats; out: device, 2 floats.
 //
 // Returns 0, or: -1 bad arguments (null pointer, n < 0), -2 misaligned g, -3 n larger than GB_NOALLOC_MAX_ELEMS,
-// -4 the scratch symbol could not be resolved on the current device (the CUDA error is in gb_noalloc_last_cuda_error),
-// -11 launch error.  n == 0 writes {grad_scale, 0}.
+// -4 the scratch symbol could not be resolved on the current device, -11 launch error (for -4 and -11 the CUDA error
+// code is in gb_noalloc_last_cuda_error).  n == 0 writes {grad_scale, 0} and needs no scratch.
 //
 // Calls no cudaMalloc, cudaFree or any library routine that allocates.  The first call on each device resolves the
-// scratch address with cudaGetSymbolAddress and caches it; make that first call during set-up, before any stream
-// capture begins.  The arrival counter has to be zero when the kernel starts: every call clears it on `st` ahead of
+// scratch address with cudaGetSymbolAddress and caches it (the cache is atomic: host threads may make their first
+// calls concurrently); make that first call during set-up, before any stream capture begins.  The arrival counter has to be zero when the kernel starts: every call clears it on `st` ahead of
 // the kernel, and the last block clears it again on the way out.
 //
 // The scratch is one per device and is not locked: two calls that overlap in time on the same device (different
 // streams or threads) race on it and both results are garbage.  Serialise such calls on one stream.
 int gb_grad_norm_noalloc(const float* g, long long n, float grad_scale, float clip, float* out, cudaStream_t st);
 
-// CUDA error code of the last failed set-up (0 = none).
+// CUDA error code of the last failed set-up or launch of this entry point (0 = none).
 int gb_noalloc_last_cuda_error(void);
 
 #ifdef __cplusplus

@@ -1,6 +1,8 @@
 // Gradient norm and clip factor without any allocation: see gb_noalloc.h for who calls this and why.
 #include <stdint.h>
 
+#include <atomic>
+
 #include "gb_noalloc.h"
 
 namespace {
@@ -71,50 +73,64 @@ __global__ void grad_norm_empty_kernel(float grad_scale, float* __restrict__ out
   out[1] = 0.f;
 }
 
-unsigned char* g_ptr[NA_MAX_DEVICES];
-bool g_ready[NA_MAX_DEVICES];
-int g_last_err = 0;
+// Address of each device's copy of the scratch, published with release/acquire ordering: a second host thread that
+// makes its first call while another thread is inside the set-up either sees the finished pointer or resolves the
+// (identical) address itself; it never sees a half-written cache.
+std::atomic<unsigned char*> g_ptr[NA_MAX_DEVICES];
+std::atomic<int> g_last_err{0};
 
 // Resolve (once per device) where this device's copy of the scratch lives.
 unsigned char* scratch_for_current_device() {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= NA_MAX_DEVICES) {
-    g_last_err = e != cudaSuccess ? (int)e : (int)cudaErrorInvalidDevice;
+    g_last_err.store(e != cudaSuccess ? (int)e : (int)cudaErrorInvalidDevice, std::memory_order_relaxed);
     return nullptr;
   }
-  if (!g_ready[dev]) {
-    unsigned char* p = nullptr;
+  unsigned char* p = g_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     e = cudaGetSymbolAddress((void**)&p, g_scratch);
     if (e != cudaSuccess || p == nullptr) {
-      g_last_err = (int)e;
+      g_last_err.store((int)e, std::memory_order_relaxed);
       return nullptr;
     }
-    g_ptr[dev] = p;
-    g_ready[dev] = true;
+    g_ptr[dev].store(p, std::memory_order_release);
   }
-  return g_ptr[dev];
+  return p;
+}
+
+// Result of the launch just issued.  cudaPeekAtLastError leaves an earlier, unrelated sticky error for its owner
+// to find; a failure is recorded so that gb_noalloc_last_cuda_error() names it.
+int launch_result() {
+  const cudaError_t e = cudaPeekAtLastError();
+  if (e == cudaSuccess) return 0;
+  g_last_err.store((int)e, std::memory_order_relaxed);
+  return -11;
 }
 
 }  // namespace
 
-extern "C" int gb_noalloc_last_cuda_error(void) { return g_last_err; }
+extern "C" int gb_noalloc_last_cuda_error(void) { return g_last_err.load(std::memory_order_relaxed); }
 
 extern "C" int gb_grad_norm_noalloc(const float* g, long long n, float grad_scale, float clip, float* out,
                                     cudaStream_t st) {
   if (out == nullptr || n < 0 || (g == nullptr && n > 0)) return -1;
   if (reinterpret_cast<uintptr_t>(g) & 15) return -2;
   if (n > GB_NOALLOC_MAX_ELEMS) return -3;       // beyond the static scratch: refuse rather than truncate
+  if (n == 0) {                                  // needs no scratch at all
+    grad_norm_empty_kernel<<<1, 1, 0, st>>>(grad_scale, out);
+    return launch_result();
+  }
   unsigned char* sc = scratch_for_current_device();
   if (sc == nullptr) return -4;
-  if (n == 0) {
-    grad_norm_empty_kernel<<<1, 1, 0, st>>>(grad_scale, out);
-    return cudaGetLastError() == cudaSuccess ? 0 : -11;
-  }
   const int n_chunks = (int)((n + NA_CHUNK - 1) / NA_CHUNK);
   // The arrival counter must be zero when the first block takes its ticket.  A kernel that was interrupted could have
   // left it non-zero, so it is cleared here on the same stream, ahead of the kernel.
-  if (cudaMemsetAsync(sc, 0, sizeof(unsigned int), st) != cudaSuccess) return -11;
+  const cudaError_t me = cudaMemsetAsync(sc, 0, sizeof(unsigned int), st);
+  if (me != cudaSuccess) {
+    g_last_err.store((int)me, std::memory_order_relaxed);
+    return -11;
+  }
   grad_norm_static_kernel<<<n_chunks, NA_THREADS, 0, st>>>(g, n, sc, n_chunks, grad_scale, clip, out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return launch_result();
 }

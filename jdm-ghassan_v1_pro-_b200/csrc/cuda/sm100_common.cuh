@@ -249,6 +249,14 @@ __device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_
       : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(const CUtensorMap* map, uint32_t bar_cluster_addr, void* dst, int c0,
+                                                 int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
                : "memory");
@@ -385,5 +393,9 @@ int gb_make_tmap_2d_16b(CUtensorMap* out, const void* base, uint64_t rows, uint6
 // 3-D view [groups][rows][cols] of an output (or epilogue input) matrix for TMA stores / loads of 128-byte-wide boxes:
 // dtype 0 fp16, 1 bf16, 2 fp32; row pitch `ld` and group pitch `group_stride` in elements; box = [1, box_rows,
 // 128 / element size] with the 128-byte swizzle.  Returns 0 on success.
+// MN-major 16-bit operand stored [k_rows, mn] (mn a multiple of 64) viewed as [mn / 64][k_rows][64]: one box
+// [chunks, box_k, 64] lands as `chunks` consecutive 64-wide, 128-byte-swizzled column blocks.  Returns 0 on success.
+int gb_make_tmap_mn_chunks(CUtensorMap* out, const void* base, uint64_t k_rows, uint64_t mn, uint64_t ld, uint32_t box_k,
+                           uint32_t chunks, int is_bf16);
 int gb_make_tmap_3d_box128(CUtensorMap* out, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t groups,
                            uint64_t ld, uint64_t group_stride, uint32_t box_rows);

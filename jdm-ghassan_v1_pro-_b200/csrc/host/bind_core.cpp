@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include "core.hpp"
+#include "hostres.hpp"
 #include "shards.hpp"
 
 namespace py = pybind11;
@@ -66,6 +67,12 @@ PYBIND11_MODULE(_gb200_host, m) {
     return fnv1a64(s.data(), s.size());
   });
   m.def("splitmix64", &splitmix64);
+  m.def("physical_ram_bytes", &physical_ram_bytes);
+  m.def("free_disk_bytes", &free_disk_bytes);
+  m.def("tree_size_bytes", [](const std::string& root, const std::vector<std::string>& skip) {
+    const TreeSize t = tree_size_bytes(root, skip);
+    return py::make_tuple(t.bytes, t.unique_files);
+  }, py::arg("root"), py::arg("skip_dirs") = std::vector<std::string>());
   m.def("fingerprint_file", &fingerprint_file);
   m.def("fingerprint_hex", &fingerprint_hex);
 

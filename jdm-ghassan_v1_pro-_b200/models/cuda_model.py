@@ -206,6 +206,8 @@ class CudaModel:
         self.bias_counts = None
         if cfg.use_moe and cfg.moe_aux_free:
             self.moe_bias = torch.zeros(cfg.num_layers, cfg.num_experts, **f32)
+        if cfg.use_moe and train:
+            # routed slots per (layer, expert) of the current step: balancing input (aux-free) and expert-load report
             self.bias_counts = torch.zeros(cfg.num_layers, cfg.num_experts, **f32)
         self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, T), self.dev)
         self.pos = torch.arange(T, dtype=torch.int32, device=self.dev).repeat(B)

@@ -50,8 +50,8 @@ class ExpertParallel:
         cap_local = model.layers[0].ws.cap                                  # rows of one rank's grouped layout
         routed_all = self.world * (N * cfg.moe_top_k)
         want = int(min(self.world, max(1.0, capacity)) * N * cfg.moe_top_k) + (N if self.shared else 0)
-        want = min(want, routed_all + N) + 128 * ((ne // self.world) * self.world + 1)
-        self.cap = (want + 127) // 128 * 128
+        want = min(want, routed_all + N) + 256 * ((ne // self.world) * self.world + 1)   # segments are padded to 256 rows
+        self.cap = (want + 255) // 256 * 256
         nl = len(model.layers)
         esz = torch.empty(0, dtype=dt).element_size()
         # ---- symmetric: what peers read (grouped rows, their offsets) and what peers write (results)

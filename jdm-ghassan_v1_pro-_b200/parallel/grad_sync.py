@@ -20,6 +20,8 @@ Between steps a rank's fp32 master copy is current only for its own shard (and t
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import numpy as np
@@ -36,6 +38,10 @@ class SymmetricBuffers:
     """Symmetric-memory allocations of one process group and the peer pointer tables the kernels take."""
 
     def __init__(self, group=None):
+        # The kernels reach peers with plain loads and stores and never use a multicast address, so the buffers are not
+        # bound to an NVLink multicast object: a rank that dies while its memory is bound to one (the step watchdog
+        # exits hard, the launcher kills stragglers) can fault the other ranks' GPUs.  Set before the first rendezvous.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         self.symm = symm
         self.group = group if group is not None else dist.group.WORLD

@@ -147,7 +147,11 @@ class CheckpointWriter:
         self._pending: List[Snapshot] = []     # queued or being written (unique snapshots)
         self._err: Optional[BaseException] = None
         self._thread: Optional[threading.Thread] = None
-        self._written: Dict[int, str] = {}     # id(snapshot) -> first path it was written to
+        # (serial of the snapshot, first path it was written to) of the last full write.  Every snapshot gets a serial
+        # from this writer the first time it is submitted; id() is not used, because the id of a freed snapshot can be
+        # taken by a later one, which would then be published as a hard link to the earlier file.
+        self._written = None
+        self._serial = 0
 
     def start(self):
         if self._thread is None:
@@ -170,6 +174,7 @@ class CheckpointWriter:
     def submit(self, snap: Snapshot, path: str):
         """Blocks while the unique queued snapshots would exceed the RAM budget."""
         self.check_health()
+        self._serial_of(snap)
         if self._thread is None:
             self._write(snap, path)
             return
@@ -192,7 +197,8 @@ class CheckpointWriter:
         self._q.put((snap, path))
 
     def _write(self, snap: Snapshot, path: str):
-        prior = self._written.get(id(snap))
+        serial = self._serial_of(snap)
+        prior = self._written[1] if (self._written is not None and self._written[0] == serial) else None
         if prior and os.path.exists(prior) and os.path.abspath(prior) != os.path.abspath(path):
             # same step, second name: link (or copy) the file that is already on disk
             tmp = path + ".lnk"
@@ -209,7 +215,16 @@ class CheckpointWriter:
                 if os.path.exists(tmp):
                     os.remove(tmp)
         save_snapshot(snap, path)
-        self._written = {id(snap): path}
+        self._written = (serial, path)
+
+    def _serial_of(self, snap) -> int:
+        s = getattr(snap, "_writer_serial", None)
+        if s is None:
+            with self._cv:
+                self._serial += 1
+                s = self._serial
+            snap._writer_serial = s
+        return s
 
     def _run(self):
         while True:

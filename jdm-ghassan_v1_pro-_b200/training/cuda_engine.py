@@ -26,7 +26,8 @@ from ..ops import kernels as K
 from ..utils.log import log_info, log_warn
 from ..utils.telemetry import PERF
 from . import optim as O
-from .engine import MOE_BIAS_CLAMP, MOE_BIAS_LR, DistInfo, StepResult, jitter_seed_for, moe_bias_update
+from .engine import (MOE_BIAS_CLAMP, MOE_BIAS_LR, DistInfo, StepResult, format_balance_report, jitter_seed_for,
+                     moe_bias_update)
 
 _F32 = np.float32
 
@@ -99,7 +100,11 @@ class CudaEngine:
         self.ntok_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.aux_weighted = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.readback = torch.zeros(6, dtype=torch.float64).pin_memory()
-        self.dyn_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+        # per-launch scalars go through a pinned ring with one slot per micro-batch of a step (plus slack): the copy is
+        # asynchronous and nothing syncs the host between micro-batches, so a single pinned buffer would be rewritten
+        # before an earlier micro-batch's copy has run.  end_step() synchronises once per step.
+        self.dyn_ring = torch.zeros(max(4, tcfg.grad_accum + 2), 4, dtype=torch.float32).pin_memory()
+        self._dyn_slot = 0
         self.seed_host = torch.zeros(1, dtype=torch.int64).pin_memory()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.eval_graph: Optional[torch.cuda.CUDAGraph] = None
@@ -121,6 +126,9 @@ class CudaEngine:
             if tcfg.ep_size != self.dist.world:
                 raise ValueError("b200.ep_size must equal the number of ranks (%d): the expert group is the whole job" % self.dist.world)
             self.expert_parallel = self.model.enable_expert_parallel(capacity=tcfg.ep_capacity)
+        # routed slots per (layer, expert) since the last expert-load report (this rank's tokens)
+        self.load_acc = (torch.zeros(mcfg.num_layers, mcfg.num_experts, dtype=torch.float64, device=self.device)
+                         if mcfg.use_moe else None)
         self.last_step_ms = None
         self._ev0, self._ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         self.kernel_launches = 0
@@ -199,13 +207,20 @@ class CudaEngine:
     def micro_step(self, ids, targets, segments, B, T):
         m = self.model
         ntok = int((targets.view(-1) >= 0).sum()) if not targets.is_cuda else int((targets >= 0).sum().item())
-        if ntok == 0:
+        if ntok == 0 and self.expert_parallel is None:
             return 0.0, 0    # nothing supervised: no forward/backward, no router counts
+        # With experts divided among the ranks every layer holds peer barriers and row exchanges, so a rank may not
+        # skip on its own: an all-masked micro-batch runs anyway (zero loss and gradient; its rows still serve the
+        # peers' experts, and its routed slots do enter the balancing counts, unlike the skipped case above).
         cfg = self.mcfg
-        self.dyn_host[0] = self._loss_scale
-        self.dyn_host[1] = (cfg.moe_aux_scale * self._loss_scale * ntok / cfg.num_layers *
-                            cfg.num_experts / float(B * T)) if cfg.use_moe else 0.0
-        m.dyn.copy_(self.dyn_host, non_blocking=True)
+        dyn_host = self.dyn_ring[self._dyn_slot]
+        self._dyn_slot = (self._dyn_slot + 1) % self.dyn_ring.shape[0]
+        dyn_host[0] = self._loss_scale
+        dyn_host[1] = (cfg.moe_aux_scale * self._loss_scale * ntok / cfg.num_layers *
+                       cfg.num_experts / float(B * T)) if cfg.use_moe else 0.0
+        dyn_host[2] = 0.0
+        dyn_host[3] = 0.0
+        m.dyn.copy_(dyn_host, non_blocking=True)
         m.set_inputs(ids, targets, segments)
         PERF.add("h2d_bytes", ids.numel() * 4 * (3 if m.use_segments else 2))
         self._run_micro()
@@ -248,6 +263,8 @@ class CudaEngine:
                 K.sqnorm_partial(m.Gr, self.sq_partial)
                 K.finish_norm(self.sq_partial, self.sq_partial.numel(), None, grad_scale, self.tcfg.grad_clip, self.norm_out)
                 self.optimizer.launch(lr, self.norm_out[0:1])
+        if self.load_acc is not None and m.bias_counts is not None:
+            self.load_acc.add_(m.bias_counts)      # this rank's counts (the fused exchange keeps the global sum apart)
         # ---- the one host read-back of the step
         self._ev1.record()
         norm_src = self.grad_sync.out if fused else self.norm_out
@@ -292,7 +309,12 @@ class CudaEngine:
         return float(acc[0]), int(acc[1])
 
     def balance_report(self) -> str:
-        return ""
+        """Expert-load line for the evaluation log (model/model.cpp:107-127 in the reference); resets the counts."""
+        if self.load_acc is None:
+            return ""
+        rep = format_balance_report(self.load_acc, self.mcfg.num_experts)
+        self.load_acc.zero_()
+        return rep
 
     # ------------------------------------------------------------------ checkpoint state
     def prepare_export(self):

@@ -57,6 +57,24 @@ class StepResult:
     applied: bool          # False: skipped (non-finite norm) or all-masked step
 
 
+def format_balance_report(acc, num_experts: int) -> str:
+    """``expert load (share of routed slots): L0[min..max] L1[..]!`` from per-layer routed-slot counts accumulated
+    since the last report; ``!`` marks a layer whose least (most) loaded expert is below a quarter of (above four
+    times) the even share.  Same text as the reference prints at evaluation (model/model.cpp:107-127)."""
+    if acc is None:
+        return ""
+    rows = acc.detach().double().cpu().tolist()
+    out = []
+    for l, row in enumerate(rows):
+        tot = sum(row)
+        if tot <= 0:
+            continue
+        mn, mx = min(row) / tot, max(row) / tot
+        flag = "!" if (mn < 0.25 / num_experts or mx > 4.0 / num_experts) else ""
+        out.append(" L%d[%.2f..%.2f]%s" % (l, mn, mx, flag))
+    return ("expert load (share of routed slots):" + "".join(out)) if out else ""
+
+
 class DistInfo:
     """Rank / world size and the small host-side collectives the engines need."""
 
@@ -99,6 +117,7 @@ class TorchEngine:
                            for n, p in self.model.named_parameters()]
         self.optimizer = O.make_optimizer(tcfg, self.opt_params)
         self._bias_counts: Optional[torch.Tensor] = None
+        self._load_acc: Optional[torch.Tensor] = None     # routed slots per (layer, expert) since the last report
         self._loss_num = 0.0
         self._ntok = 0
         self._loss_scale = 1.0
@@ -131,9 +150,11 @@ class TorchEngine:
         (res.objective(self.mcfg) * self._loss_scale).backward()
         if self.tcfg.freeze_embeddings:
             self.model.params["tok_embeddings"].grad = None
-        if self.model.moe_bias is not None and res.slot_counts is not None:
+        if res.slot_counts is not None:
             c = res.slot_counts.detach()
-            self._bias_counts = c if self._bias_counts is None else self._bias_counts + c
+            self._load_acc = c.double() if self._load_acc is None else self._load_acc + c.double()
+            if self.model.moe_bias is not None:
+                self._bias_counts = c if self._bias_counts is None else self._bias_counts + c
         loss = res.reported_loss(self.mcfg)
         self._loss_num += loss * res.ntok
         self._ntok += res.ntok
@@ -169,6 +190,12 @@ class TorchEngine:
                 for n, p in self.model.named_parameters():
                     self.weight_ema[n].mul_(beta).add_(p.detach(), alpha=1.0 - beta)
         return StepResult(loss, self._ntok, ntok_global, gnorm, applied)
+
+    def balance_report(self) -> str:
+        """Expert-load line for the evaluation log; resets the accumulation."""
+        rep = format_balance_report(self._load_acc, self.mcfg.num_experts) if self.mcfg.use_moe else ""
+        self._load_acc = None
+        return rep
 
     @torch.no_grad()
     def eval_batch(self, ids, targets, segments, B, T):

@@ -40,6 +40,7 @@ class Trainer:
         self.mcfg, self.cfg = mcfg, tcfg
         self._check_ranges()
         self.fuse = 1
+        self.segments = 1          # row slices a micro-batch is run in (training.ckpt_segments), see _pick_segments
         self.engine = engine if engine is not None else self._make_engine(device)
         self.dist = self.engine.dist
         self.rank, self.world = self.dist.rank, self.dist.world
@@ -59,6 +60,7 @@ class Trainer:
         self.jsonl_path = os.environ.get("GB200_JSONL", "")
         self._snapshot_cache = None
         self._open_loaders()
+        self._preflight()
         self._resume()
 
     # ------------------------------------------------------------------ construction helpers
@@ -73,6 +75,18 @@ class Trainer:
         if not (0.0 < c.sched_decay_frac <= 1.0):
             raise TrainerError("training.sched_decay_frac must be in (0,1]")
 
+    def _preflight(self, probe=None):
+        """Host RAM, free disk and output quota before anything is trained (training/guards.py); the device-memory
+        guard ran in _make_engine, ahead of the allocations."""
+        from . import guards
+        c = self.cfg
+        try:
+            guards.preflight(self.mcfg.count_parameters(), c.optimizer, c.checkpoint_dir, c.output_budget_mb,
+                             self.writer.budget, probe=probe, main=self.is_main(),
+                             pretrained=c.pretrained_checkpoint if c.stage == "sft" else "")
+        except guards.GuardError as e:
+            raise TrainerError(str(e)) from None
+
     def _make_engine(self, device):
         dev = device or self.cfg.device
         if dev == "auto":
@@ -80,17 +94,50 @@ class Trainer:
         if dev == "cuda":
             from .cuda_engine import CudaEngine
             self.fuse = self._pick_fuse()
+            self.segments = self._pick_segments()
             ecfg = self.cfg
+            if self.segments > 1:
+                ecfg = dataclasses.replace(self.cfg, batch_size=self.cfg.batch_size // self.segments,
+                                           grad_accum=self.cfg.grad_accum * self.segments)
             if self.fuse > 1:
                 ecfg = dataclasses.replace(self.cfg, batch_size=self.cfg.batch_size * self.fuse,
                                            grad_accum=self.cfg.grad_accum // self.fuse)
                 log_info("[cuda] %d micro-batches of %d x %d tokens run as one pass of %d tokens (%d passes per step)" % (
                     self.fuse, self.cfg.batch_size, self.cfg.seq_len, ecfg.batch_size * ecfg.seq_len, ecfg.grad_accum))
+            from . import guards
+            from .memory_plan import memory_plan
+            world = int(os.environ.get("WORLD_SIZE", "1") or 1)
+            try:
+                guards.check_device_memory(memory_plan(self.mcfg, self.cfg, world, self.fuse)["total"],
+                                           int(torch.cuda.memory_allocated()), world, guards.Probe(), True)
+            except guards.GuardError as e:
+                raise TrainerError(str(e)) from None
             return CudaEngine(self.mcfg, ecfg)
         if dev != "cpu":
             log_warn(f"device '{dev}' is not supported; falling back to cpu")
         from .engine import TorchEngine
+        self.segments = self._pick_segments()
         return TorchEngine(self.mcfg, self.cfg, "cpu")
+
+    def _pick_segments(self) -> int:
+        """``training.activation_checkpointing`` with ``ckpt_segments: S`` runs every micro-batch as S row slices one
+        after another (the reference's "checkpointing" is this segmenting, not recomputation:
+        training/trainer.cpp:1122-1146): same gradient sum, 1/S of the activation memory.  When micro-batches are
+        fused into larger passes instead, the pass size is already chosen by the memory plan and the key has nothing
+        left to do; that is logged, not silent."""
+        c = self.cfg
+        if not c.activation_checkpointing or c.ckpt_segments <= 1:
+            return 1
+        if self.fuse > 1:
+            log_info("[ckpt] ckpt_segments=%d not applied: %d micro-batches already run as one pass whose size the "
+                     "memory plan chose (b200.fuse_micro_batches: 1 brings segmenting back)" % (c.ckpt_segments, self.fuse))
+            return 1
+        if c.batch_size % c.ckpt_segments:
+            log_warn("[ckpt] ckpt_segments=%d does not divide batch_size=%d: micro-batches run unsegmented" % (
+                c.ckpt_segments, c.batch_size))
+            return 1
+        log_info("[ckpt] every micro-batch runs as %d slices of %d sequences" % (c.ckpt_segments, c.batch_size // c.ckpt_segments))
+        return c.ckpt_segments
 
     def _pick_fuse(self) -> int:
         """How many of the recipe's micro-batches one forward/backward pass covers.  The gradient of a step is a sum
@@ -104,7 +151,7 @@ class Trainer:
             # auto: the largest divisor of grad_accum whose pass stays within a token cap and whose predicted memory
             # (closed form of cli/train.py) fits the device with room to spare.  Measured on pro_1b, one B200:
             # 113.6 k tokens/s at 8192 tokens per pass, 122.7 k at 16384, 126.7 k at 32768 (activations 80 GB).
-            from ..cli.train import memory_plan
+            from .memory_plan import memory_plan
             total = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory if torch.cuda.is_available() else 0
             cap = 32768 if total >= 120 * (1 << 30) else 8192
             if c.ep_size > 1:
@@ -499,7 +546,14 @@ class Trainer:
             self.phases.start("load")
             group = [self.prefetch.get() for _ in range(self.fuse)]
             self.phases.stop("load")
-            self.engine.micro_step(*self._fused(group))
+            ids, tg, sg, Bm, Tm = self._fused(group)
+            if self.segments == 1:
+                self.engine.micro_step(ids, tg, sg, Bm, Tm)
+            else:
+                rows = Bm // self.segments
+                cut = lambda t, k: None if t is None else t.view(Bm, Tm)[k * rows:(k + 1) * rows]
+                for k in range(self.segments):
+                    self.engine.micro_step(cut(ids, k), cut(tg, k), cut(sg, k), rows, Tm)
         lr = self.sched.lr_at(self.state.step)
         res = self.engine.end_step(lr)
         loss = res.loss

@@ -42,7 +42,7 @@ def test_emulated_ranks_equal_local_experts(W, shared):
     t_seg = C.pointer_table([w.seg_offsets.data_ptr() for w in ws], dev)
     t_x = C.pointer_table([x.data_ptr() for x in xperm], dev)
     base_y = C.pointer_table([y.data_ptr() for y in y_ep], dev)
-    cap = (W * N * top_k + N + 128 * (ne + 1) + 127) // 128 * 128
+    cap = (W * N * top_k + N + 256 * (ne + 1) + 255) // 256 * 256
     routed = 0
     for r in range(W):                                    # the owner's phase of every emulated rank, one after another
         plan = EP.Plan(ne1, cap, dev)

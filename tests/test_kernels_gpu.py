@@ -186,12 +186,12 @@ def test_moe_route_group_matches_reference(n, ne, Kk, shared, jit, d):
     assert torch.equal(counts, ref_counts)
     assert near(ws.f_frac, ref_counts / (n * Kk), 1e-5, 1e-6)[0]
     assert near(ws.aux_m, ws.probs.mean(0), 1e-4, 1e-5)[0]
-    # segments: padded to 128, rows stable in token order, pads zero
+    # segments: padded to 256 rows (one two-CTA tile), rows stable in token order, pads zero
     so = ws.seg_offsets.cpu().tolist()
     tot = ref_counts.cpu().long().tolist() + ([n] if shared else [])
     ne1 = ne + int(shared)
     for e in range(ne1):
-        assert so[e] % 128 == 0 and so[e + 1] - so[e] == (tot[e] + 127) // 128 * 128
+        assert so[e] % 256 == 0 and so[e + 1] - so[e] == (tot[e] + 255) // 256 * 256
     assert int(ws.num_tiles[0]) == so[ne1] // 128
     te = ws.tile_expert.cpu().tolist()
     for e in range(ne1):

@@ -274,6 +274,43 @@ def test_writer_links_second_name_and_applies_back_pressure(tmp_path):
     assert written == ["a1", "a2", "b1"]
 
 
+def test_writer_never_links_a_new_snapshot_to_an_old_file(tmp_path, monkeypatch):
+    """last.ckpt at step A, snapshot freed, best.ckpt from a new snapshot at step B: best must hold step B even when
+    the new object reuses the old one's id()."""
+    import gc
+    from ghassan_b200.training import checkpoint as C
+
+    saved = {}
+
+    def fake_save(snap, path):
+        with open(path, "w") as f:
+            f.write(str(snap.state["step"]))
+        saved[path] = snap.state["step"]
+
+    monkeypatch.setattr(C, "save_snapshot", fake_save)
+
+    class Snap:
+        def __init__(self, step):
+            self.state = {"step": step}
+
+        def nbytes(self):
+            return 8
+
+    for trial in range(20):
+        w = C.CheckpointWriter(ram_budget=1 << 20)
+        last, best = str(tmp_path / ("last%d" % trial)), str(tmp_path / ("best%d" % trial))
+        a = Snap(100 + trial)
+        w.submit(a, last)
+        del a
+        gc.collect()
+        b = Snap(200 + trial)              # often gets the id of the freed object
+        w.submit(b, best)
+        w.submit(b, last + ".second")      # the same snapshot under a second name is still a link to its own file
+        assert open(best).read() == str(200 + trial)
+        assert open(last + ".second").read() == str(200 + trial)
+        assert os.path.samefile(best, last + ".second")
+
+
 def test_latest_in_order(tmp_path):
     from ghassan_b200.training import checkpoint as C
     d = str(tmp_path)
@@ -285,3 +322,20 @@ def test_latest_in_order(tmp_path):
     assert C.latest_in(d).endswith("last.ckpt.bak")
     open(os.path.join(d, "last.ckpt"), "w").close()
     assert C.latest_in(d).endswith("last.ckpt")
+
+
+def test_expert_load_report_text_and_reset(data_dir, tmp_path):
+    """The evaluation log's expert-load line: shares of routed slots per layer, '!' on a lopsided layer
+    (model/model.cpp:107-127 in the reference), accumulated over training steps and reset by the report."""
+    import torch
+    from ghassan_b200.training.engine import format_balance_report
+    acc = torch.tensor([[10.0, 10.0, 10.0, 10.0], [1.0, 0.0, 30.0, 9.0], [0.0, 0.0, 0.0, 0.0]])
+    assert format_balance_report(acc, 4) == "expert load (share of routed slots): L0[0.25..0.25] L1[0.00..0.75]!"
+    assert format_balance_report(None, 4) == "" and format_balance_report(acc[2:], 4) == ""
+    tr = _trainer(_recipe(data_dir, str(tmp_path / "ck"), eval_every=0))
+    tr.prepare()
+    tr.train_step()
+    tr.prefetch.stop()
+    rep = tr.engine.balance_report()
+    assert rep.startswith("expert load (share of routed slots): L0[") and " L1[" in rep
+    assert tr.engine.balance_report() == ""            # reset by the report
