@@ -4,6 +4,11 @@ uniform token data, random-initialised weights.
 
     python bench.py --gpus N --steps K --warmup W                  # this framework
     python bench.py --impl reference --gpus N --steps K --warmup W  # the unmodified reference binary
+    python bench.py --profile-passes 2 [--fuse F] [--layers L] [--end-step]   # a few eager passes, for use under ncu
+    python bench.py --sync-only                                     # the gradient exchange alone (one process per GPU)
+
+With one GPU the JSON line also carries a ``decode`` object: batch-1 decode tokens/s of the same model for f16, q8_0 and
+q4_0 weights (device-timed; ``--no-decode`` skips it, ``bench_decode.py`` has the full table with batch 32).
 
 For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...``; rank,
 world size and rendezvous come from the environment.  A "step" is one optimizer step of the recipe
@@ -258,11 +263,217 @@ def run_ours(args):
            "gpu_launches": int(launches), "optimizer_steps_applied": applied, "settle_steps": settle,
            "loss_first": losses[0], "loss_last": losses[-1],
            "supervised_tokens_per_step": toks / args.steps}
+    if world == 1 and not args.no_decode:
+        del tr, eng
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            out["decode"] = run_decode(args, local)
+        except Exception as e:        # the training number stands on its own
+            out["decode"] = {"error": "%s: %s" % (type(e).__name__, str(e)[:200])}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return 0
+
+
+def run_decode(args, local):
+    """Batch-1 decode of the recipe's model (random-initialised) for three weight formats: tokens/s with CUDA events
+    around the decode steps, SM clocks sampled meanwhile.  Runs after the training measurement has released the GPU."""
+    import torch
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.inference.generator import Generator
+    from ghassan_b200.models.config import ModelConfig, init_parameters
+    from ghassan_b200.utils.config import Config
+    cfg = ModelConfig.from_config(Config.from_file(args.config))
+    named = init_parameters(cfg, 1234)
+    sp = SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, repetition_penalty=1.0, seed=1234)
+    out = {"batch": 1, "prompt_len": args.decode_prompt, "new_tokens": args.decode_new, "kv_cache": "fp16",
+           "sampling": "top_p 0.9 top_k 40 temperature 0.8 seed 1234", "timing": "CUDA events around the decode steps"}
+    sampler = ClockSampler(local)
+    sampler.start()
+    for fmt in ("f16", "q8_0", "q4_0"):
+        eng = InferenceEngine(cfg, named, fmt=fmt, batch=1, max_len=args.decode_prompt + args.decode_new + 8,
+                              prefill_chunk=args.decode_prompt)
+        r = Generator(eng).benchmark(args.decode_prompt, args.decode_new, sp, 1234)
+        out[fmt] = {"tokens_per_s": r["decode_tokens_per_s"], "ms_per_token": r["decode_ms_per_token"],
+                    "stored_weight_bytes": r["stored_weight_bytes"], "prefill_ms": r["prefill_ms"]}
+        del eng
+        torch.cuda.empty_cache()
+    out["clocks"] = sampler.stop()
+    return out
+
+
+def run_sync(args):
+    """The gradient exchange alone on buffers of the recipe's size (default: the 1.04 G parameters of pro_1b), one
+    process per GPU: barrier, reduce-scatter + norm by peer loads, Lion update of the own shard, barrier, all-gather of
+    the 16-bit weights and the fp32 prefix by peer loads.  Device time, max over ranks, against one NCCL all-reduce of
+    the same fp32 gradient (which does no norm and no optimizer).  Launch like the training bench:
+
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --sync-only
+    """
+    import torch
+    import torch.distributed as dist
+    from ghassan_b200.ops import _lib, comm as C
+    from ghassan_b200.parallel.grad_sync import SymmetricBuffers
+    rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    torch.cuda.set_device(local)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    total = (args.sync_elements + 63) // 64 * 64
+    buf = SymmetricBuffers()
+    shard = ((total + world - 1) // world + 63) // 64 * 64
+    pad = shard * world
+    P, tP = buf.alloc(pad, torch.float32)
+    W16, tW = buf.alloc(pad, torch.float16)
+    Gr, tG = buf.alloc(pad, torch.float32)
+    ctl, tC = buf.alloc(C.CTL_WORDS, torch.int32)
+    Gr.normal_()
+    m = torch.zeros(pad, device=dev)
+    partial = torch.zeros(C.SYNC_BLOCKS, dtype=torch.float64, device=dev)
+    ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(4, device=dev)
+    hyper = torch.tensor([1e-5, 0.1, 0.01], device=dev)
+    f32_end = min(total, 25_400_000 // 64 * 64)
+    a = C.SyncArgs()
+    a.rank, a.world, a.shard, a.total = rank, world, shard, total
+    a.decay_start, a.f32_end = min(total, 25_000_000 // 64 * 64), f32_end
+    a.peer_grad, a.peer_master, a.peer_w16, a.peer_ctl = tG.data_ptr(), tP.data_ptr(), tW.data_ptr(), tC.data_ptr()
+    a.m, a.v, a.kind = m.data_ptr(), None, 1
+    a.beta1, a.beta2, a.eps, a.wd = 0.9, 0.99, 1e-8, 0.1
+    a.hyper, a.loss_scale, a.clip, a.ntok_local = hyper.data_ptr(), 1024.0, 1.0, 32768.0
+    a.partial, a.ticket, a.out = partial.data_ptr(), ticket.data_ptr(), out.data_ptr()
+    a.status = _lib.status_word(dev).data_ptr()
+    a.is_bf16, a.no_wait, a.local_only = 0, 0, 1
+    state = {"be": 0}
+
+    def bar():
+        state["be"] += 1
+        C.barrier(tC, rank, world, state["be"])
+
+    def exchange(epoch, ev=None):
+        a.epoch = epoch
+        bar()
+        if ev: ev[0].record()
+        C.reduce(a)
+        if ev: ev[1].record()
+        C.update(a)
+        if ev: ev[2].record()
+        bar()
+        if ev: ev[3].record()
+        C.gather(tW, W16, shard, total, rank, world)
+        C.gather(tP, P, shard, f32_end, rank, world)
+        if ev: ev[4].record()
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    for e in range(1, 4):
+        exchange(e)
+    torch.cuda.synchronize()
+    _lib.check_status(dev, "exchange")
+    dist.barrier()
+    iters = max(3, args.steps)
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for e in range(4, 4 + iters):
+        exchange(e)
+    bar()                         # the barrier that opens the next exchange belongs to the cycle
+    e1.record()
+    torch.cuda.synchronize()
+    fused_ms = e0.elapsed_time(e1) / iters
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(iters)]
+    for k in range(iters):
+        exchange(4 + iters + k, evs[k])
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    phase = lambda i, j: sum(x[i].elapsed_time(x[j]) for x in evs) / iters
+    reduce_ms, update_ms, gather_ms = phase(0, 1), phase(1, 2), phase(3, 4)
+    g2 = torch.randn(total, device=dev)
+    for _ in range(2):
+        dist.all_reduce(g2)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for _ in range(iters):
+        dist.all_reduce(g2)
+    e1.record()
+    torch.cuda.synchronize()
+    nccl_ms = e0.elapsed_time(e1) / iters
+    t = torch.tensor([fused_ms, nccl_ms, reduce_ms, update_ms, gather_ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    fused_ms, nccl_ms, reduce_ms, update_ms, gather_ms = (float(x) for x in t)
+    # Bytes that cross each direction of a GPU's NVLink per exchange: it reads W-1 peer shards of fp32 gradient and
+    # W-1 peer shards of new weights (16-bit everywhere, fp32 below f32_end), and serves the same amounts to its peers.
+    per_dir = (world - 1) * (shard * 4 + shard * 2) + max(0, min(f32_end, total) - shard) * 4
+    roof_ms = per_dir / 770e9 * 1e3
+    if rank == 0:
+        print(json.dumps({"bench": "fused_grad_sync", "world": world, "elements": total, "fused_ms": fused_ms,
+                          "reduce_scatter_phase_ms": reduce_ms, "update_phase_ms": update_ms,
+                          "allgather_phase_ms": gather_ms, "nccl_allreduce_only_ms": nccl_ms,
+                          "nvlink_bytes_per_direction": per_dir, "roofline_ms_at_770GBs_per_direction": roof_ms,
+                          "fraction_of_roofline": roof_ms / fused_ms if world > 1 else None, "clocks": clocks,
+                          "note": "fused = barrier + reduce-scatter + norm + mailbox + Lion update + barrier + all-gather "
+                                  "of 16-bit weights and fp32 prefix by peer loads; the NCCL figure is the all-reduce "
+                                  "alone (no norm, no optimizer, fp32 result only)"}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+def run_profile_passes(args):
+    """A few training passes launched eagerly (no CUDA graph) so that a profiler sees every kernel:
+
+        CMD="python bench.py --profile-passes 2 --fuse 64"
+        $CMD > plain.log 2>&1 && ncu --metrics gpu__time_duration.sum --clock-control none -c 6000 --csv \
+            --log-file launches.csv $CMD
+
+    Prints the launches and device milliseconds per pass.  ``--layers`` shrinks the model for ``--set full`` captures."""
+    import torch
+    from ghassan_b200.models.config import ModelConfig
+    from ghassan_b200.training.config import TrainerConfig
+    from ghassan_b200.training.trainer import Trainer
+    from ghassan_b200.utils import log as L
+    from ghassan_b200.utils.config import Config
+    L.set_log_level(L.WARN)
+    torch.cuda.set_device(env_int("LOCAL_RANK", 0))
+    base = Config.from_file(args.config)
+    work = os.path.join(args.workdir, "profile")
+    data, tok = make_data(work, ModelConfig.from_config(base).vocab_size, TrainerConfig.from_config(base).mix)
+    c = load_recipe(args.config, data, os.path.join(work, "ckpt"), tok, 10)
+    c.set("b200.cuda_graphs", "true" if args.graphs else "false")
+    c.set("b200.fuse_micro_batches", args.fuse)
+    if args.layers > 0:
+        c.set("model.num_layers", args.layers)
+    for k, v in (args.set or []):
+        c.set(k, v)
+    tr = Trainer(ModelConfig.from_config(c), TrainerConfig.from_config(c), device="cuda")
+    tr.prepare()
+    eng = tr.engine
+    eng.begin_step(0, 64.0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(args.profile_passes):
+        fused = tr._fused([tr.prefetch.get() for _ in range(tr.fuse)])
+        e0.record()
+        eng.micro_step(*fused)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    print("launches per pass: %d | tokens per pass: %d | device ms per pass: %s" % (
+        eng.model.launches_per_micro_batch(), eng.model.N, " ".join("%.2f" % t for t in times)), flush=True)
+    if args.end_step:
+        e0.record()
+        r = eng.end_step(1e-5)
+        e1.record()
+        torch.cuda.synchronize()
+        print("end_step: %.2f ms %s" % (e0.elapsed_time(e1), r), flush=True)
+    tr.prefetch.stop()
     return 0
 
 
@@ -366,7 +577,21 @@ def main():
     ap.add_argument("--settle-max", type=int, default=12,
                     help="untimed steps allowed before warm-up for the dynamic loss scale to stop overflowing")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the batch-1 decode measurement of the 1-GPU run")
+    ap.add_argument("--decode-prompt", type=int, default=1024)
+    ap.add_argument("--decode-new", type=int, default=256)
+    ap.add_argument("--profile-passes", type=int, default=0, help="run this many eager passes and exit (for profilers)")
+    ap.add_argument("--fuse", type=int, default=0, help="--profile-passes: micro-batches per pass (0 = automatic)")
+    ap.add_argument("--layers", type=int, default=0, help="--profile-passes: override model.num_layers")
+    ap.add_argument("--graphs", action="store_true", help="--profile-passes: replay CUDA graphs instead of eager launches")
+    ap.add_argument("--end-step", action="store_true", help="--profile-passes: also run the optimizer step")
+    ap.add_argument("--sync-only", action="store_true", help="time the gradient exchange alone (see run_sync)")
+    ap.add_argument("--sync-elements", type=int, default=1_036_995_840)
     args = ap.parse_args()
+    if args.profile_passes > 0:
+        return run_profile_passes(args)
+    if args.sync_only:
+        return run_sync(args)
     world = env_int("WORLD_SIZE", 1)
     if world != args.gpus and env_int("RANK", 0) == 0:
         sys.stderr.write("[bench] note: --gpus %d but WORLD_SIZE=%d; using WORLD_SIZE\n" % (args.gpus, world))

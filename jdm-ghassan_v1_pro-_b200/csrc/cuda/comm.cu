@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(256) sync_update_kernel(gb_sync_args a) {
   __syncthreads();
   const float scale = s_scale;
   if (scale == 0.f) return;   // skipped step (overflow, nothing supervised, or a peer that never answered)
+  if (KIND == 2) return;      // norm and skip decision only: the optimizer runs elsewhere (Muon)
   const float lr = a.hyper[0], bc1 = a.hyper[1], bc2 = a.hyper[2];
   const long long lo = (long long)a.rank * a.shard;
   const long long hi = min(a.total, lo + a.shard);
@@ -246,12 +247,48 @@ __global__ void __launch_bounds__(256) sync_update_kernel(gb_sync_args a) {
     q16.y = Cvt<T>::pack2(wv[2], wv[3]);
     q16.z = Cvt<T>::pack2(wv[4], wv[5]);
     q16.w = Cvt<T>::pack2(wv[6], wv[7]);
+    if (a.local_only) {                   // peers fetch the new values themselves afterwards (gb_sync_gather)
+      *reinterpret_cast<uint4*>(wp[a.rank] + i) = q16;
+      *reinterpret_cast<float4*>(w + i) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+      *reinterpret_cast<float4*>(w + i + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
+      continue;
+    }
     const bool also_f32 = i < a.f32_end;
     for (int r = 0; r < a.world; ++r) {   // all-gather: the new values go straight into every rank's buffers
       *reinterpret_cast<uint4*>(wp[r] + i) = q16;
       if (also_f32 || r == a.rank) {
         *reinterpret_cast<float4*>(mp[r] + i) = make_float4(wv[0], wv[1], wv[2], wv[3]);
         *reinterpret_cast<float4*>(mp[r] + i + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
+      }
+    }
+  }
+}
+
+// All-gather by peer loads: every rank copies the other ranks' shards of a flat buffer into its own copy.  Bytes
+// [r * shard_bytes, (r + 1) * shard_bytes) clipped to limit_bytes come from rank r.  A thread keeps U 16-byte loads in
+// flight; consecutive blocks take consecutive pieces of one peer's shard, and the peer index is the outer loop, rotated
+// by the rank so that at any moment the ranks read from different peers.
+template <int U>
+__global__ void __launch_bounds__(256) sync_gather_kernel(const unsigned char* const* __restrict__ peer,
+                                                          unsigned char* __restrict__ local, long long shard_bytes,
+                                                          long long limit_bytes, int rank, int world) {
+  const long long tile = 256LL * 16 * U;
+  for (int k = 1; k < world; ++k) {
+    const int r = (rank + k) % world;
+    const long long lo = (long long)r * shard_bytes;
+    const long long hi = min(limit_bytes, lo + shard_bytes);
+    const unsigned char* src = peer[r];
+    for (long long base = lo + (long long)blockIdx.x * tile; base < hi; base += (long long)gridDim.x * tile) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + ((long long)u * 256 + threadIdx.x) * 16;
+        if (i < hi) v[u] = *reinterpret_cast<const uint4*>(src + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + ((long long)u * 256 + threadIdx.x) * 16;
+        if (i < hi) *reinterpret_cast<uint4*>(local + i) = v[u];
       }
     }
   }
@@ -286,9 +323,10 @@ extern "C" int gb_sync_barrier_auto(unsigned int* const* peer_ctl, int rank, int
 
 static int check_sync_args(const gb_sync_args* a) {
   if (!a || a->world < 1 || a->world > GB_MAX_RANKS || a->rank < 0 || a->rank >= a->world) return -1;
-  if (!a->peer_grad || !a->peer_master || !a->peer_w16 || !a->peer_ctl || !a->m || !a->hyper || !a->partial ||
-      !a->ticket || !a->out || !a->status)
+  if (!a->peer_grad || !a->peer_master || !a->peer_w16 || !a->peer_ctl || !a->partial || !a->ticket || !a->out ||
+      !a->status)
     return -1;
+  if (a->kind != 2 && (!a->m || !a->hyper)) return -1;
   if (a->kind == 0 && !a->v) return -1;
   if (a->shard <= 0 || a->shard % 64 || a->total % 8 || a->decay_start % 8 || a->f32_end % 8) return -2;
   return 0;
@@ -309,6 +347,10 @@ extern "C" int gb_sync_reduce(const gb_sync_args* a, cudaStream_t st) {
 extern "C" int gb_sync_update(const gb_sync_args* a, cudaStream_t st) {
   if (int rc = check_sync_args(a)) return rc;
   const int blocks = 148 * 4;
+  if (a->kind == 2) {       // wait for the mailboxes, fold the norm, publish {scale, gnorm, tokens}: no update
+    sync_update_kernel<__half, 2><<<1, 256, 0, st>>>(*a);
+    return gb_launch_rc();
+  }
   if (a->is_bf16) {
     if (a->kind == 0) sync_update_kernel<__nv_bfloat16, 0><<<blocks, 256, 0, st>>>(*a);
     else sync_update_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, st>>>(*a);
@@ -316,6 +358,17 @@ extern "C" int gb_sync_update(const gb_sync_args* a, cudaStream_t st) {
     if (a->kind == 0) sync_update_kernel<__half, 0><<<blocks, 256, 0, st>>>(*a);
     else sync_update_kernel<__half, 1><<<blocks, 256, 0, st>>>(*a);
   }
+  return gb_launch_rc();
+}
+
+extern "C" int gb_sync_gather(const void* const* peer, void* local, long long shard_bytes, long long limit_bytes, int rank,
+                              int world, cudaStream_t st) {
+  if (!peer || !local || world < 1 || world > GB_MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if (shard_bytes <= 0 || (shard_bytes & 15) || (limit_bytes & 15) || (reinterpret_cast<uintptr_t>(local) & 15)) return -2;
+  if (world == 1 || limit_bytes <= 0) return 0;
+  sync_gather_kernel<4><<<GB_SYNC_BLOCKS, 256, 0, st>>>(reinterpret_cast<const unsigned char* const*>(peer),
+                                                        reinterpret_cast<unsigned char*>(local), shard_bytes, limit_bytes,
+                                                        rank, world);
   return gb_launch_rc();
 }
 

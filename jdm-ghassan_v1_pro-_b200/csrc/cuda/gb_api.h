@@ -176,6 +176,23 @@ int gb_finish_norm(const double* partial, int n_partial, const float* grad_scale
                    float* out, cudaStream_t st);
 int gb_fill_f32(float* p, float v, long long n, cudaStream_t st);
 
+// ----------------------------------------------------------------------------- muon.cu
+// Elementwise parts of Muon over "class" buffers: all matrices of one shape stacked as [n * rows_per_mat, C] fp32,
+// rows_per_mat a multiple of 256 (pad rows zero).  row_src[r] = offset of class row r in the flat parameter / gradient
+// buffers, -1 for a pad row.  scale_dev[0] = grad_scale * clip factor of the step; 0 makes every kernel a no-op.
+int gb_muon_blocks(long long rows);                       // entries of `partial` that gb_muon_momentum fills
+int gb_muon_momentum(float* m, const float* g, const long long* row_src, long long rows, int C, float beta1,
+                     const float* scale_dev, double* partial, cudaStream_t st);
+// Y = m / |m|_F per matrix, Y16 = bf16(Y), T = 1.5 Y; skip_flag[mat] = 1 when the norm is unusable
+int gb_muon_normalize(const float* m, float* Y, float* T, void* Y16, const double* partial, long long rows,
+                      int rows_per_mat, int C, const float* scale_dev, int* skip_flag, cudaStream_t st);
+int gb_muon_gram_cast(const float* A, void* B16, long long n, const float* scale_dev, cudaStream_t st);   // bf16(-0.5 A)
+int gb_muon_refresh(float* Y, float* T, void* Y16, long long rows, int rows_per_mat, int C, const float* scale_dev,
+                    const int* skip_flag, cudaStream_t st);
+// w <- (w - lr Y)(1 - lr wd) through row_src, plus the 16-bit shadow (w16 may be NULL); lr_dev[0] = learning rate
+int gb_muon_apply(float* w, void* w16, int is_bf16, const float* Y, const long long* row_src, long long rows, int C,
+                  const float* lr_dev, float wd, const float* scale_dev, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,11 +2,14 @@
 // device pointers, one per rank, obtained from symmetric memory; entry r of a rank's own array is its local buffer.
 // Peers are read with plain loads and written with plain stores; no TMA, no multicast.
 //
-// One gradient exchange = gb_sync_barrier, gb_sync_reduce, gb_sync_update, gb_sync_barrier on the same stream of
-// every rank.  It replaces the reference's per-parameter ncclAllReduce + host-side norm + per-tensor optimizer
-// launches (training/trainer.cpp:1835-1876, 1476-1536) by: reduce-scatter through peer loads in rank order,
-// Sum g^2 of the owned shard, a mailbox exchange of {Sum g^2, token count}, and on each owner the unscale / clip /
-// inf-check / optimizer update of its shard followed by the all-gather of the new 16-bit weights through peer stores.
+// One gradient exchange = gb_sync_barrier, gb_sync_reduce, gb_sync_update (local_only), gb_sync_barrier, gb_sync_gather
+// of the 16-bit weights (and of the fp32 part that kernels read in fp32) on the same stream of every rank; the barrier
+// that opens the next exchange keeps a rank from overwriting its shard while a peer still reads it.
+// It replaces the reference's per-parameter ncclAllReduce + host-side norm + per-tensor optimizer launches
+// (training/trainer.cpp:1835-1876, 1476-1536) by: reduce-scatter through peer loads in rank order, Sum g^2 of the owned
+// shard, a mailbox exchange of {Sum g^2, token count}, on each owner the unscale / clip / inf-check / optimizer update
+// of its shard, and an all-gather of the new 16-bit weights by peer loads.  With kind = 2 (Muon) the update is left
+// out and the ranks gather the reduced fp32 gradient instead.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -33,7 +36,7 @@ typedef struct gb_sync_args {
   void* const* peer_w16;            // 16-bit shadows of every rank
   unsigned int* const* peer_ctl;    // control blocks
   float* m; float* v;               // local moments, indexed like the flat buffers (only the own shard is touched)
-  int kind;                         // 0 AdamW, 1 Lion
+  int kind;                         // 0 AdamW, 1 Lion, 2 none: gb_sync_update only folds the norm and publishes `out`
   float beta1, beta2, eps, wd;
   const float* hyper;               // device {lr, bc1, bc2}
   float loss_scale, clip;
@@ -45,6 +48,9 @@ typedef struct gb_sync_args {
   int* status;                      // device status word (ST_TIMEOUT_PEER on a wait that ran out)
   int is_bf16;
   int no_wait;                      // 1: all ranks' kernels run back to back on one device (tests): never spin
+  int local_only;                   // 1: gb_sync_update writes the new values of the own shard locally only; the ranks
+                                    //    then fetch each other's shards with gb_sync_gather (peer loads ran 1.8x faster
+                                    //    than peer stores on NVSwitch here)
 } gb_sync_args;
 
 // All ranks have reached this point, and their earlier writes are visible to peer loads issued after it.
@@ -55,6 +61,11 @@ int gb_sync_barrier_auto(unsigned int* const* peer_ctl, int rank, int world, uns
                          int* status, cudaStream_t st);
 int gb_sync_reduce(const gb_sync_args* a, cudaStream_t st);
 int gb_sync_update(const gb_sync_args* a, cudaStream_t st);
+// All-gather by peer loads of a flat buffer that every rank holds a copy of: bytes [r*shard_bytes, (r+1)*shard_bytes)
+// below limit_bytes are copied from rank r's buffer (peer[r]) into `local`, for every r != rank.  Call between two
+// barriers: after the owners have written, and before anyone overwrites its shard again.
+int gb_sync_gather(const void* const* peer, void* local, long long shard_bytes, long long limit_bytes, int rank, int world,
+                   cudaStream_t st);
 // dst[i] = sum over ranks (in rank order) of peer_src[r][i]: replicated small tensors (routing counts).
 int gb_sync_small_allreduce(const float* const* peer_src, float* dst, int n, int world, cudaStream_t st);
 

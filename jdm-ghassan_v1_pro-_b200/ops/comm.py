@@ -26,7 +26,7 @@ class SyncArgs(ctypes.Structure):
         ("ntok_local", c_double),
         ("epoch", c_uint),
         ("partial", c_vp), ("ticket", c_vp), ("out", c_vp), ("status", c_vp),
-        ("is_bf16", c_int), ("no_wait", c_int),
+        ("is_bf16", c_int), ("no_wait", c_int), ("local_only", c_int),
     ]
 
 
@@ -47,6 +47,14 @@ def reduce(args: SyncArgs):
 
 def update(args: SyncArgs):
     _lib.check_rc(_lib.lib().gb_sync_update(ctypes.byref(args), _lib.stream_ptr()), "gb_sync_update")
+
+
+def gather(peer_table: torch.Tensor, local: torch.Tensor, shard_elems: int, limit_elems: int, rank: int, world: int):
+    """All-gather by peer loads: ``local[r*shard : (r+1)*shard]`` (below ``limit_elems``) from every other rank ``r``."""
+    es = local.element_size()
+    rc = _lib.lib().gb_sync_gather(c_vp(peer_table.data_ptr()), c_vp(local.data_ptr()), c_ll(shard_elems * es),
+                                   c_ll(limit_elems * es), c_int(rank), c_int(world), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_sync_gather")
 
 
 def small_allreduce(src_table: torch.Tensor, dst: torch.Tensor, n: int, world: int):

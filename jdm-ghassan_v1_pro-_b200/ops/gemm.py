@@ -160,25 +160,30 @@ def gemm_swiglu_bwd(dy, w_down, gu, *, dgu_out=None, b_mn=True, tile_expert=None
 
 
 def gemm_grouped_rows(a, b, tile_expert, num_m_tiles, *, n, b_mn=False, group_rows, out=None, out_dtype=None,
-                      block_n=0, tile_out=None, ldo=None, pair=None):
+                      block_n=0, tile_out=None, ldo=None, pair=None, addend=None):
     """Expert-sorted rows: every 128-row tile of ``a`` multiplies the weight block of ``tile_expert[tile]``.
     The two-CTA kernel (``pair``) needs tiles ``2i`` and ``2i+1`` to belong to one expert: segments padded to 256 rows.
 
     ``b`` stacks the per-expert matrices along its rows: ``group_rows`` stored rows per expert.
     ``tile_out`` (device int64 table, one entry per 128-row tile) redirects each tile's rows to the given address,
     row pitch ``ldo`` elements; the destinations may be buffers of other GPUs mapped into this process.
+    ``addend`` (fp32 ``[M, n]``, fp32 ``out`` only, not with ``tile_out``): ``out = product + addend``.
     """
     M, K = a.shape
     if out is None:
         out = torch.empty((M, n) if tile_out is None else (1, n), dtype=out_dtype or a.dtype, device=a.device)
     if not block_n:
         block_n = 256 if (n % 256 == 0 and M >= 4096) else 128
+    if addend is not None and (addend.dtype != torch.float32 or out.dtype != torch.float32 or tile_out is not None):
+        raise ValueError("addend needs fp32 addend and output and no tile_out")
     if pair is None:
         pair = tile_out is None and pair_ok(M, n, out)
     g = _base_args(a, b, M, n, K, False, b_mn, out, block_n)
     g.epilogue = EPI_STORE
     g.mode = 1
     g.pair = int(bool(pair))
+    if addend is not None:
+        g.addend, g.ld_add = addend.data_ptr(), addend.stride(0)
     g.tile_expert, g.num_m_tiles = tile_expert.data_ptr(), num_m_tiles.data_ptr()
     g.b_group_rows = group_rows
     if tile_out is not None:

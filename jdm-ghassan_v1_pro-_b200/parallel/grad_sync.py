@@ -117,7 +117,7 @@ class FusedGradSync:
             dist.barrier()
 
     # ------------------------------------------------------------------ one exchange
-    def _args(self, lr_hyper: torch.Tensor, loss_scale: float, ntok_local: int, no_wait=False) -> C.SyncArgs:
+    def _args(self, lr_hyper: Optional[torch.Tensor], loss_scale: float, ntok_local: int, no_wait=False) -> C.SyncArgs:
         e, m, opt, t = self.engine, self.engine.model, self.engine.optimizer, self.engine.tcfg
         a = C.SyncArgs()
         a.rank, a.world = self.rank, self.world
@@ -125,11 +125,14 @@ class FusedGradSync:
         a.decay_start, a.f32_end = m.layout.decay_start, m.layout.f32_end
         a.peer_grad, a.peer_master = self.t_grad.data_ptr(), self.t_master.data_ptr()
         a.peer_w16, a.peer_ctl = self.t_w16.data_ptr(), self.t_ctl.data_ptr()
-        a.m = opt.m_flat.data_ptr()
-        a.v = opt.v_flat.data_ptr() if opt.v_flat is not None else None
-        a.kind = 0 if opt.kind == "adamw" else 1
+        if opt.kind == "muon":           # norm and skip decision only; Muon itself runs after the gradient gather
+            a.m, a.v, a.kind, a.hyper = None, None, 2, None
+        else:
+            a.m = opt.m_flat.data_ptr()
+            a.v = opt.v_flat.data_ptr() if opt.v_flat is not None else None
+            a.kind = 0 if opt.kind == "adamw" else 1
+            a.hyper = lr_hyper.data_ptr()
         a.beta1, a.beta2, a.eps, a.wd = opt.beta1, opt.beta2, opt.eps, opt.weight_decay
-        a.hyper = lr_hyper.data_ptr()
         a.loss_scale, a.clip = loss_scale, t.grad_clip
         a.ntok_local = float(ntok_local)
         a.epoch = self.epoch & 0xFFFFFFFF
@@ -137,6 +140,7 @@ class FusedGradSync:
         a.status = _lib.status_word(m.dev).data_ptr()
         a.is_bf16 = int(m.dtype == torch.bfloat16)
         a.no_wait = int(no_wait)
+        a.local_only = 1                 # new values reach the peers by gb_sync_gather (loads), not by stores
         return a
 
     def _barrier(self):
@@ -145,21 +149,38 @@ class FusedGradSync:
             C.barrier(self.t_ctl, self.rank, self.world, self.barrier_epoch)
 
     def step(self, lr: float, loss_scale: float, ntok_local: int):
-        """Enqueue the whole exchange on the current stream; results land in ``self.out`` (scale, gnorm, ntok)."""
+        """Enqueue the whole exchange on the current stream; results land in ``self.out`` (scale, gnorm, ntok).
+
+        AdamW / Lion: barrier, reduce-scatter + norm, update of the own shard, barrier, all-gather of the new 16-bit
+        weights (and of the fp32 prefix) by peer loads; the next exchange's opening barrier is what keeps a rank from
+        rewriting its shard under a peer that still reads it.  Muon: barrier, reduce-scatter + norm, barrier, all-gather
+        of the reduced fp32 gradient, barrier (the next step zeroes the gradient buffer), then Muon on every rank: the
+        Newton-Schulz matrices need whole gradients, and identical inputs give identical weights everywhere."""
         opt = self.engine.optimizer
-        t = opt.t + 1
-        bc1 = float(_F32(1.0) - np.power(_F32(opt.beta1), _F32(t), dtype=_F32))
-        bc2 = float(_F32(1.0) - np.power(_F32(opt.beta2), _F32(t), dtype=_F32))
-        opt.hyper_host[0], opt.hyper_host[1], opt.hyper_host[2] = lr, bc1, bc2
-        opt.hyper_dev.copy_(opt.hyper_host, non_blocking=True)
+        muon = opt.kind == "muon"
+        hyper = None
+        if not muon:
+            t = opt.t + 1
+            bc1 = float(_F32(1.0) - np.power(_F32(opt.beta1), _F32(t), dtype=_F32))
+            bc2 = float(_F32(1.0) - np.power(_F32(opt.beta2), _F32(t), dtype=_F32))
+            opt.hyper_host[0], opt.hyper_host[1], opt.hyper_host[2] = lr, bc1, bc2
+            opt.hyper_dev.copy_(opt.hyper_host, non_blocking=True)
+            hyper = opt.hyper_dev
         self.epoch += 1
-        a = self._args(opt.hyper_dev, loss_scale, ntok_local)
+        a = self._args(hyper, loss_scale, ntok_local)
         self._barrier()
         if self.counts_local is not None:
             C.small_allreduce(self.t_counts, self.counts_global, self.counts_global.numel(), self.world)
         C.reduce(a)
         C.update(a)
         self._barrier()
+        if muon:
+            C.gather(self.t_grad, self._Gr_pad, self.shard, self.total, self.rank, self.world)
+            self._barrier()
+            opt.launch(lr, self.out[0:1])
+        else:
+            C.gather(self.t_w16, self._W16_pad, self.shard, self.total, self.rank, self.world)
+            C.gather(self.t_master, self._P_pad, self.shard, self.engine.model.layout.f32_end, self.rank, self.world)
         self._keep = a     # the struct is read at launch; kept only so that debugging can inspect the last call
 
     # ------------------------------------------------------------------ full state for checkpoints
@@ -169,6 +190,8 @@ class FusedGradSync:
             return
         opt = self.engine.optimizer
         own = slice(self.lo, self.lo + self.shard)
+        if opt.kind == "muon":           # every rank ran the whole update: masters and state are complete already
+            return
         dist.all_gather_into_tensor(self._P_pad, self._P_pad[own].clone())
         for flat in (opt.m_flat, opt.v_flat, getattr(self.engine, "weight_ema", None)):
             if flat is None:

@@ -113,7 +113,7 @@ class CudaEngine:
         self._loss_scale = 1.0
         self.weight_ema = torch.empty_like(self.model.P).copy_(self.model.P) if tcfg.weight_ema > 0 else None
         self.grad_sync = None
-        fused_ok = tcfg.optimizer != "muon" and tcfg.tokens_per_step_global(self.dist.world) < (1 << 24)
+        fused_ok = tcfg.tokens_per_step_global(self.dist.world) < (1 << 24)
         if fused_ok and ((self.dist.world > 1 and tcfg.grad_sync == "fused") or fused_sync_single):
             from ..parallel.grad_sync import FusedGradSync
             self.grad_sync = FusedGradSync(self)   # moves P / W16 / Gr (and routing counts) into symmetric memory
@@ -144,30 +144,10 @@ class CudaEngine:
                 self.dist.broadcast_(self.model.moe_bias, 0)
             self.model.refresh_shadows()
 
-    # ------------------------------------------------------------------ muon (matrix-wise, reference arithmetic)
+    # ------------------------------------------------------------------ muon (training/muon_cuda.py)
     def _make_muon(self):
-        t = self.tcfg
-        specs = {s.name: s for s in self.mcfg.param_specs()}
-        named = self.model.layout.from_internal(self.model.P)
-        self._muon_w = {n: named[n].clone() for n in specs}
-        params = [O.OptParam(s.name, self._muon_w[s.name], s.decay) for s in self.mcfg.param_specs()]
-        return O.Muon(params, t.learning_rate, t.muon_vec_ratio, t.beta1, t.beta2, t.eps, t.weight_decay, t.grad_clip,
-                      t.muon_ns_steps, t.muon_min_ns_dim)
-
-    def _muon_step(self, lr, grad_scale):
-        m = self.model
-        named_g = m.layout.from_internal(m.Gr)
-        named_w = m.layout.from_internal(m.P)
-        for p in self.optimizer.params:
-            p.w.copy_(named_w[p.name])
-            p.w.grad = named_g[p.name].contiguous()
-        gnorm = self.optimizer.step(lr, grad_scale)
-        if math.isfinite(gnorm):
-            m.layout.to_internal({p.name: p.w for p in self.optimizer.params}, m.P)
-            m.refresh_shadows()
-        for p in self.optimizer.params:
-            p.w.grad = None
-        return gnorm
+        from .muon_cuda import MuonCuda
+        return MuonCuda(self.model, self.mcfg, self.tcfg)
 
     # ------------------------------------------------------------------ step protocol
     def begin_step(self, step: int, loss_scale: float):
@@ -252,17 +232,11 @@ class CudaEngine:
             grad_scale = float(_F32(1.0) / (_F32(ntok_global) * _F32(self._loss_scale)))
             if self.tcfg.freeze_embeddings:
                 m.g("tok_embeddings").zero_()
-            if self.tcfg.optimizer == "muon":
-                if d.world > 1:
-                    d.all_reduce_sum_(m.Gr)
-                gnorm = self._muon_step(lr, grad_scale)
-                self.norm_out[1] = gnorm if math.isfinite(gnorm) else float("nan")
-            else:
-                if d.world > 1:
-                    d.all_reduce_sum_(m.Gr)
-                K.sqnorm_partial(m.Gr, self.sq_partial)
-                K.finish_norm(self.sq_partial, self.sq_partial.numel(), None, grad_scale, self.tcfg.grad_clip, self.norm_out)
-                self.optimizer.launch(lr, self.norm_out[0:1])
+            if d.world > 1:
+                d.all_reduce_sum_(m.Gr)
+            K.sqnorm_partial(m.Gr, self.sq_partial)
+            K.finish_norm(self.sq_partial, self.sq_partial.numel(), None, grad_scale, self.tcfg.grad_clip, self.norm_out)
+            self.optimizer.launch(lr, self.norm_out[0:1])      # AdamW / Lion flat kernel, or Muon (NS on the GEMM)
         if self.load_acc is not None and m.bias_counts is not None:
             self.load_acc.add_(m.bias_counts)      # this rank's counts (the fused exchange keeps the global sum apart)
         # ---- the one host read-back of the step
@@ -281,7 +255,7 @@ class CudaEngine:
         if ntok_global > 0:
             gnorm = gn
             applied = math.isfinite(gnorm)
-            if applied and self.tcfg.optimizer != "muon":
+            if applied:
                 self.optimizer.t += 1
         loss = 0.0
         if self._ntok > 0:
@@ -291,7 +265,7 @@ class CudaEngine:
         if m.moe_bias is not None and applied:
             moe_bias_update(m.moe_bias, self.grad_sync.counts_global if fused else m.bias_counts)
         if applied and self.weight_ema is not None:
-            if fused:   # the master copy is current on the owned shard only; checkpoints gather the rest
+            if fused and self.tcfg.optimizer != "muon":   # master current on the owned shard only; checkpoints gather
                 own = slice(self.grad_sync.lo, self.grad_sync.hi)
                 self.weight_ema[own].lerp_(m.P[own], 1.0 - self.tcfg.weight_ema)
             else:
@@ -346,10 +320,7 @@ class CudaEngine:
         opt = self.optimizer
         specs = self.mcfg.param_specs()
         if self.tcfg.optimizer == "muon":
-            cpu = lambda t: None if t is None else np.ascontiguousarray(t.detach().cpu().numpy().reshape(-1))
-            return {"kind": "muon", "t": int(opt.t), "hyper": {k: (int(v) if isinstance(v, int) else float(v))
-                                                               for k, v in opt.hyper().items()},
-                    "m": [cpu(t) for t in opt.m], "v": [cpu(t) for t in opt.v], "fmt": 1}
+            return opt.export_state()
         m_named = self.model.export_named(opt.m_flat)
         v_named = self.model.export_named(opt.v_flat) if opt.v_flat is not None else None
         return {"kind": opt.kind, "t": int(opt.t), "hyper": {k: float(v) for k, v in opt.hyper().items()},
@@ -362,11 +333,7 @@ class CudaEngine:
         if blob is None or blob.get("kind") != opt.kind or len(blob["m"]) != len(specs):
             return False
         if self.tcfg.optimizer == "muon":
-            for i, (mm, vv) in enumerate(zip(blob["m"], blob["v"])):
-                if mm is not None and opt.m[i] is not None:
-                    opt.m[i].copy_(torch.from_numpy(np.asarray(mm)).view_as(opt.m[i]))
-                if vv is not None and opt.v[i] is not None:
-                    opt.v[i].copy_(torch.from_numpy(np.asarray(vv)).view_as(opt.v[i]))
+            return opt.import_state(blob)
         else:
             for i, s in enumerate(specs):
                 if blob["m"][i] is not None and blob["m"][i].size != s.numel:

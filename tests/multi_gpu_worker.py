@@ -4,8 +4,6 @@ parity      train a small MoE model for a few steps twice, once with the fused p
             once with the NCCL all-reduce path, from the same seed and data; weights must agree.
 ep_parity   the same model trained with the routed experts divided among the ranks (peer-memory dispatch, combine in
             the GEMM epilogue) and with replicated experts: same losses, same weights.
-bench_sync  time the exchange alone on buffers of the pro_1b size (device time, max over ranks) against one NCCL
-            all-reduce of the same gradient buffer.
 """
 import json
 import os
@@ -175,116 +173,13 @@ def ep_parity(work):
     return 0 if int(flag) else 1
 
 
-def bench_sync(work, total=1_036_995_840):
-    from ghassan_b200.ops import _lib, comm as C
-    from ghassan_b200.parallel.grad_sync import SymmetricBuffers
-    rank, world = dist.get_rank(), dist.get_world_size()
-    dev = torch.device("cuda", torch.cuda.current_device())
-    total = (total + 63) // 64 * 64
-    buf = SymmetricBuffers()
-    shard = ((total + world - 1) // world + 63) // 64 * 64
-    pad = shard * world
-    P, tP = buf.alloc(pad, torch.float32)
-    W16, tW = buf.alloc(pad, torch.float16)
-    Gr, tG = buf.alloc(pad, torch.float32)
-    ctl, tC = buf.alloc(C.CTL_WORDS, torch.int32)
-    Gr.normal_()
-    m = torch.zeros(pad, device=dev)
-    partial = torch.zeros(C.SYNC_BLOCKS, dtype=torch.float64, device=dev)
-    ticket = torch.zeros(1, dtype=torch.int32, device=dev)
-    out = torch.zeros(4, device=dev)
-    hyper = torch.tensor([1e-5, 0.1, 0.01], device=dev)
-    a = C.SyncArgs()
-    a.rank, a.world, a.shard, a.total = rank, world, shard, total
-    a.decay_start, a.f32_end = 25_000_000 // 64 * 64, 25_400_000 // 64 * 64
-    a.peer_grad, a.peer_master, a.peer_w16, a.peer_ctl = tG.data_ptr(), tP.data_ptr(), tW.data_ptr(), tC.data_ptr()
-    a.m, a.v, a.kind = m.data_ptr(), None, 1
-    a.beta1, a.beta2, a.eps, a.wd = 0.9, 0.99, 1e-8, 0.1
-    a.hyper, a.loss_scale, a.clip, a.ntok_local = hyper.data_ptr(), 1024.0, 1.0, 32768.0
-    a.partial, a.ticket, a.out = partial.data_ptr(), ticket.data_ptr(), out.data_ptr()
-    a.status = _lib.status_word(dev).data_ptr()
-    a.is_bf16, a.no_wait = 0, 0
-    be = 0
-
-    def exchange(epoch):
-        nonlocal be
-        a.epoch = epoch
-        be += 1
-        C.barrier(tC, rank, world, be)
-        C.reduce(a)
-        C.update(a)
-        be += 1
-        C.barrier(tC, rank, world, be)
-
-    torch.cuda.synchronize()
-    dist.barrier()
-    for e in range(1, 4):
-        exchange(e)
-    torch.cuda.synchronize()
-    _lib.check_status(dev, "bench exchange")
-    dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    iters = 5
-    e0.record()
-    for e in range(4, 4 + iters):
-        exchange(e)
-    e1.record()
-    torch.cuda.synchronize()
-    fused_ms = e0.elapsed_time(e1) / iters
-    # the two phases on their own (events around each kernel of one more run of exchanges)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(iters)]
-    for k, e in enumerate(range(4 + iters, 4 + 2 * iters)):
-        a.epoch = e
-        be += 1
-        C.barrier(tC, rank, world, be)
-        ev[k][0].record()
-        C.reduce(a)
-        ev[k][1].record()
-        C.update(a)
-        ev[k][2].record()
-        be += 1
-        C.barrier(tC, rank, world, be)
-        ev[k][3].record()
-    torch.cuda.synchronize()
-    reduce_ms = sum(x[0].elapsed_time(x[1]) for x in ev) / iters
-    update_ms = sum(x[1].elapsed_time(x[2]) for x in ev) / iters
-    g2 = torch.randn(total, device=dev)
-    for _ in range(2):
-        dist.all_reduce(g2)
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0.record()
-    for _ in range(iters):
-        dist.all_reduce(g2)
-    e1.record()
-    torch.cuda.synchronize()
-    nccl_ms = e0.elapsed_time(e1) / iters
-    t = torch.tensor([fused_ms, nccl_ms, reduce_ms, update_ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    fused_ms, nccl_ms, reduce_ms, update_ms = (float(x) for x in t)
-    # bytes that must cross NVLink per rank: read (W-1) peers' shard as fp32, write the shard as 16-bit to (W-1) peers
-    nv_in = (world - 1) * shard * 4
-    nv_out = (world - 1) * (shard * 2 + min(shard, a.f32_end) * 4 / world)
-    link = 770e9
-    roof_ms = max(nv_in, nv_out) / link * 1e3
-    if rank == 0:
-        print(json.dumps({"bench": "fused_grad_sync", "world": world, "elements": total, "fused_ms": fused_ms,
-                          "nccl_allreduce_only_ms": nccl_ms, "reduce_scatter_phase_ms": reduce_ms,
-                          "update_allgather_phase_ms": update_ms, "nvlink_in_bytes_per_rank": nv_in,
-                          "nvlink_out_bytes_per_rank": nv_out, "roofline_ms_at_770GBs": roof_ms,
-                          "fraction_of_roofline": roof_ms / fused_ms,
-                          "note": "fused = barrier + reduce-scatter + norm + mailbox + Lion update + 16-bit all-gather + "
-                                  "barrier; the NCCL figure is the all-reduce alone (no norm, no optimizer)"}), flush=True)
-    return 0
-
-
 def main():
     mode, work = sys.argv[1], sys.argv[2]
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    rc = {"parity": parity, "ep_parity": ep_parity, "bench_sync": bench_sync}[mode](work)
+    rc = {"parity": parity, "ep_parity": ep_parity}[mode](work)
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(rc)

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _emulated_exchange(W, total, kind, dtype, seed, inf_at=None, clip=1.0, ntok=(37, 41, 11, 5)):
+def _emulated_exchange(W, total, kind, dtype, seed, inf_at=None, clip=1.0, ntok=(37, 41, 11, 5), pull=False):
     from ghassan_b200.ops import _lib, comm as C
     dev = torch.device("cuda")
     g = torch.Generator(device="cuda").manual_seed(seed)
@@ -49,7 +49,8 @@ def _emulated_exchange(W, total, kind, dtype, seed, inf_at=None, clip=1.0, ntok=
         a.peer_grad, a.peer_master, a.peer_w16, a.peer_ctl = (t_grad.data_ptr(), t_master.data_ptr(), t_w16.data_ptr(),
                                                               t_ctl.data_ptr())
         a.m, a.v = ranks[r]["m"].data_ptr(), ranks[r]["v"].data_ptr()
-        a.kind, a.beta1, a.beta2, a.eps, a.wd = (0 if kind == "adamw" else 1), b1, b2, eps, wd
+        a.kind, a.beta1, a.beta2, a.eps, a.wd = {"adamw": 0, "lion": 1, "none": 2}[kind], b1, b2, eps, wd
+        a.local_only = int(pull)
         a.hyper = hyper.data_ptr()
         a.loss_scale, a.clip, a.ntok_local, a.epoch = loss_scale, clip, float(ntok[r]), 7
         a.partial, a.ticket, a.out = ranks[r]["partial"].data_ptr(), ranks[r]["ticket"].data_ptr(), ranks[r]["out"].data_ptr()
@@ -60,6 +61,13 @@ def _emulated_exchange(W, total, kind, dtype, seed, inf_at=None, clip=1.0, ntok=
         C.reduce(a)
     for a in args:
         C.update(a)
+    if pull:          # every rank fetches the other ranks' shards: 16-bit weights everywhere, fp32 below f32_end
+        for r in range(W):
+            C.gather(t_w16, ranks[r]["W16"], shard, total, r, W)
+            C.gather(t_master, ranks[r]["P"], shard, f32_end, r, W)
+    if kind == "none":  # the optimizer runs elsewhere: every rank fetches the reduced gradient shards instead
+        for r in range(W):
+            C.gather(t_grad, ranks[r]["Gr"], shard, total, r, W)
     torch.cuda.synchronize()
     _lib.check_status(dev, "emulated exchange")
     # ---- plain PyTorch reference
@@ -89,12 +97,13 @@ def _emulated_exchange(W, total, kind, dtype, seed, inf_at=None, clip=1.0, ntok=
     return ranks, ref, dict(shard=shard, total=total, f32_end=f32_end, gnorm=gnorm, scale=scale, nt=nt, P0=P0, W=W)
 
 
+@pytest.mark.parametrize("pull", [False, True])
 @pytest.mark.parametrize("W", [1, 2, 4])
 @pytest.mark.parametrize("kind", ["adamw", "lion"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_emulated_ranks_match_reference(W, kind, dtype):
+def test_emulated_ranks_match_reference(W, kind, dtype, pull):
     total = 64 * 37 + 8 * 3          # not a multiple of the shard size: the last shard is short
-    ranks, ref, info = _emulated_exchange(W, total, kind, dtype, seed=W * 10 + (kind == "lion"))
+    ranks, ref, info = _emulated_exchange(W, total, kind, dtype, seed=W * 10 + (kind == "lion"), pull=pull)
     T, S = info["total"], info["shard"]
     for r, x in enumerate(ranks):
         assert float(x["out"][1]) == pytest.approx(info["gnorm"], rel=1e-5)
@@ -135,6 +144,21 @@ def test_overflow_skips_on_every_rank():
     for x in ranks:
         assert float(x["out"][0]) == 0.0 and not math.isfinite(float(x["out"][1]))
         assert torch.equal(x["P"], info["P0"]) and torch.equal(x["W16"], info["P0"].to(torch.float16))
+
+
+@pytest.mark.parametrize("W", [1, 2, 4])
+def test_norm_only_exchange_gathers_the_reduced_gradient(W):
+    """The form Muon uses: reduce-scatter + norm, no update, then every rank pulls the other ranks' reduced shards."""
+    total = 64 * 41 + 16
+    ranks, ref, info = _emulated_exchange(W, total, "none", torch.float16, seed=21 + W)
+    gsum = None
+    for x in ranks:
+        assert float(x["out"][1]) == pytest.approx(info["gnorm"], rel=1e-5)
+        assert float(x["out"][0]) == pytest.approx(info["scale"], rel=1e-5)
+        assert torch.equal(x["P"], info["P0"])                       # nothing was updated
+        gsum = x["Gr"][:total] if gsum is None else gsum
+        assert torch.equal(x["Gr"][:total], gsum)                    # the same complete sum on every rank
+    assert float(gsum.double().pow(2).sum().sqrt()) / (info["nt"] * 64.0) == pytest.approx(info["gnorm"], rel=1e-6)
 
 
 def test_small_allreduce():
