@@ -185,10 +185,17 @@ def _run(args) -> int:
         if plan["total"] > v * (1 << 20):
             raise ConfigError("predicted peak %s exceeds --max-vram-mb %d MiB" % (human_bytes(plan["total"]), v))
     if tcfg.output_budget_mb > 0:
-        need = plan["checkpoint_bytes"] * 3          # last + best + one in flight
-        if need > tcfg.output_budget_mb * (1 << 20):
-            raise ConfigError("checkpoints need about %s but --output-budget-mb allows %d MiB" % (
-                human_bytes(need), tcfg.output_budget_mb))
+        # two snapshots on disk while a save is in flight, plus the exported GGUF (the trainer's own quota guard adds
+        # what is already in the output tree: training/guards.py)
+        from ..training.guards import snapshot_bytes
+        per = snapshot_bytes(plan["parameters"], tcfg.optimizer)
+        proj = 2 * per + plan["parameters"] + per // 8
+        budget = tcfg.output_budget_mb * (1 << 20)
+        log_info("  output budget       : %s (proj snapshots+gguf %s, %s left for existing data)" % (
+            human_bytes(budget), human_bytes(proj), human_bytes(max(0, budget - proj))))
+        if proj > budget:
+            raise ConfigError("projected output %s exceeds budget %s (2 snapshots %.1fGB + GGUF). Raise --output-budget-mb "
+                              "knowingly or shrink the model." % (human_bytes(proj), human_bytes(budget), 2 * per / 1e9))
     if args.dry_run:
         log_info("[dry ] nothing was allocated; exiting")
         return 0

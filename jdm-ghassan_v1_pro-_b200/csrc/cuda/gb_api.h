@@ -136,7 +136,14 @@ typedef struct gb_moe_args {
   const unsigned long long* dyn_seed;// device copy of jitter_seed (overrides it; lets a captured graph change seeds)
   const float* dyn_aux_coef;         // device copy of aux_coef (overrides it)
   float* part2;                      // scratch [GB_ROUTER_WGRAD_CHUNKS, ne, d] for the router weight gradient, or NULL
+  // A pass that concatenates several micro-batches keeps the reference's per-micro-batch definitions when seg_tokens is
+  // the micro-batch size (a multiple of the routing block, see gb_moe_seg_ok): f_frac and aux_m are then
+  // [segments, ne], the jitter hash counts tokens inside a segment, dyn_aux_coef holds one coefficient per segment and
+  // seg_weight (device, [segments], may be NULL = 1) weights each segment's balance loss in aux_acc.  0 = one segment.
+  int seg_tokens;
+  const float* seg_weight;
 } gb_moe_args;
+int gb_moe_seg_ok(int n_tok, int seg_tokens);   // 1 when seg_tokens is usable for a pass of n_tok tokens
 #define GB_ROUTER_WGRAD_CHUNKS 256
 int gb_moe_num_blocks(int n_tok);
 int gb_moe_capacity(int n_tok, int ne, int top_k, int shared);

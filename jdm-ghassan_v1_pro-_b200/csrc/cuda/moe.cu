@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
   const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;   // device copy wins (graph replay)
   for (int t = t0 + warp; t < t1; t += 8) {
     const T* xr = x16 + (size_t)t * d;
+    const int tj = a.seg_tokens > 0 ? t % a.seg_tokens : t;   // the jitter hash counts tokens inside a micro-batch
     // lane holds the logits of experts `lane` and `lane + 32`
     float l0 = -INFINITY, l1 = -INFINITY;
     if constexpr (NV8 > 0) {
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
                xf[k][4] * w1.x + xf[k][5] * w1.y + xf[k][6] * w1.z + xf[k][7] * w1.w;
         }
         s = warp_sum(s);
-        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, jseed);
+        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
         if (e == lane) l0 = s;
         if (e == lane + 32) l1 = s;
       }
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
           s += xv.x * wv.x + xv.y * wv.y;
         }
         s = warp_sum(s);
-        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(t, e, jseed);
+        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
         if (e == lane) l0 = s;
         if (e == lane + 32) l1 = s;
       }
@@ -159,19 +160,30 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks, int staged) {
     for (int i = threadIdx.x; i < cells; i += blockDim.x) s_tab[i] = a.block_hist[i];
     __syncthreads();
   }
+  // micro-batch segments of the pass: routed-slot shares (and further down the balance loss) are kept per segment,
+  // as if every micro-batch had been routed on its own.  Blocks never straddle a segment (checked by the launcher).
+  const int bt = blk_tok(a.n_tok);
+  const int seg_tok = a.seg_tokens > 0 ? a.seg_tokens : a.n_tok;
+  const int bps = (a.seg_tokens > 0 && a.seg_tokens < a.n_tok) ? seg_tok / bt : n_blocks;   // blocks per segment
+  const int n_seg = (a.n_tok + seg_tok - 1) / seg_tok;
   if (e < ne1) {
-    int run = 0;
-    if (staged) {
-      for (int b = 0; b < n_blocks; ++b) {
-        const int c = s_tab[b * stride + e];
+    int run = 0, segsum = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+      int c;
+      if (staged) {
+        c = s_tab[b * stride + e];
         s_tab[b * stride + e] = run;
-        run += c;
-      }
-    } else {
-      for (int b = 0; b < n_blocks; ++b) {
-        const int c = a.block_hist[(size_t)b * stride + e];
+      } else {
+        c = a.block_hist[(size_t)b * stride + e];
         a.block_base[(size_t)b * stride + e] = run;   // relative for now
-        run += c;
+      }
+      run += c;
+      segsum += c;
+      if (((b + 1) % bps == 0 || b == n_blocks - 1) && e < a.ne && a.f_frac) {
+        const int sgi = b / bps;
+        const int ntk = min(seg_tok, a.n_tok - sgi * seg_tok);
+        a.f_frac[(size_t)sgi * a.ne + e] = (float)segsum / (float)((long long)ntk * a.top_k);
+        segsum = 0;
       }
     }
     s_total[e] = run;
@@ -202,20 +214,30 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks, int staged) {
     for (int tle = s_off[e] / 128; tle < s_off[e + 1] / 128; ++tle) a.tile_expert[tle] = e;
   if (e < a.ne) {
     if (a.counts) a.counts[e] += (float)s_total[e];
-    if (a.f_frac) a.f_frac[e] = (float)s_total[e] / (float)((long long)a.n_tok * a.top_k);
   }
-  if (threadIdx.x == 0 && a.aux_acc && a.aux_m) {
-    // balance loss of this call: ne * sum_e mean_prob[e] * slot_share[e]
-    float raw = 0.f;
-    for (int i = 0; i < a.ne; ++i) raw += a.aux_m[i] * ((float)s_total[i] / (float)((long long)a.n_tok * a.top_k));
-    a.aux_acc[0] += (float)a.ne * raw;
+  if (threadIdx.x == 0 && a.aux_acc && a.aux_m && a.f_frac) {
+    // balance loss of this call: per segment ne * sum_e mean_prob[e] * slot_share[e], weighted by seg_weight (the
+    // segment's supervised tokens) when given.  f_frac was written above by this block (ordered by the barrier).
+    float tot = 0.f;
+    for (int sgi = 0; sgi < n_seg; ++sgi) {
+      float raw = 0.f;
+      for (int i = 0; i < a.ne; ++i) raw += a.aux_m[(size_t)sgi * a.ne + i] * a.f_frac[(size_t)sgi * a.ne + i];
+      tot += (a.seg_weight ? a.seg_weight[sgi] : 1.f) * (float)a.ne * raw;
+    }
+    a.aux_acc[0] += tot;
   }
 }
 
-// mean_t probs[t, e] -> aux_m[e]; one block per expert, fixed-order tree reduction
-__global__ void moe_colmean_kernel(const float* __restrict__ probs, float* __restrict__ out, int n_tok, int ne) {
+// mean over the tokens of segment blockIdx.y of probs[t, e] -> aux_m[segment, e]; one block per (expert, segment),
+// fixed-order tree reduction
+__global__ void moe_colmean_kernel(const float* __restrict__ probs, float* __restrict__ out, int n_tok_all, int ne,
+                                   int seg_tok) {
   __shared__ float s[256];
   const int e = blockIdx.x;
+  const int t_lo = blockIdx.y * seg_tok;
+  const int n_tok = min(seg_tok, n_tok_all - t_lo);
+  probs += (size_t)t_lo * ne;
+  out += (size_t)blockIdx.y * ne;
   float acc = 0.f;
   for (int t = threadIdx.x; t < n_tok; t += 256) acc += probs[(size_t)t * ne + e];
   s[threadIdx.x] = acc;
@@ -378,11 +400,14 @@ __global__ void __launch_bounds__(256, 4) moe_router_bwd_kernel(const gb_moe_arg
   const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
   const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
   float dp0 = 0.f, dp1 = 0.f;
-  const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[0] : a.aux_coef;
+  const int sgi = a.seg_tokens > 0 ? t / a.seg_tokens : 0;       // micro-batch segment of this token
+  const int tj = a.seg_tokens > 0 ? t - sgi * a.seg_tokens : t;
+  const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[sgi] : a.aux_coef;   // one coefficient per segment
   const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;
   if (a.f_frac && aux_coef != 0.f) {
-    if (lane < ne) dp0 = aux_coef * a.f_frac[lane];
-    if (lane + 32 < ne) dp1 = aux_coef * a.f_frac[lane + 32];
+    const float* ff = a.f_frac + (size_t)sgi * ne;
+    if (lane < ne) dp0 = aux_coef * ff[lane];
+    if (lane + 32 < ne) dp1 = aux_coef * ff[lane + 32];
   }
   float ssum = 0.f, gbar = 0.f;
   for (int k = 0; k < K; ++k) {
@@ -403,8 +428,8 @@ __global__ void __launch_bounds__(256, 4) moe_router_bwd_kernel(const gb_moe_arg
   const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
   float dl0 = p0 * (dp0 - pdp), dl1 = p1 * (dp1 - pdp);
   if (a.use_jitter) {
-    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane, jseed);
-    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(t, lane + 32, jseed);
+    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane, jseed);
+    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane + 32, jseed);
   }
   if (lane < ne) a.part[(size_t)t * ne + lane] = dl0;
   if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1;
@@ -493,7 +518,12 @@ using namespace gb;
 static int moe_check(const gb_moe_args* a) {
   if (!a || a->n_tok <= 0 || a->d <= 0 || a->d % 8) return -1;
   if (a->ne <= 0 || a->ne > MAX_NE || a->top_k <= 0 || a->top_k > MAX_K || a->top_k > a->ne) return -2;
+  if (a->seg_tokens < 0 || (a->seg_tokens > 0 && a->seg_tokens < a->n_tok && a->seg_tokens % blk_tok(a->n_tok))) return -4;
   return 0;
+}
+
+extern "C" int gb_moe_seg_ok(int n_tok, int seg_tokens) {
+  return seg_tokens > 0 && (seg_tokens >= n_tok || seg_tokens % blk_tok(n_tok) == 0) ? 1 : 0;
 }
 
 extern "C" int gb_moe_num_blocks(int n_tok) { return (n_tok + blk_tok(n_tok) - 1) / blk_tok(n_tok); }
@@ -521,7 +551,11 @@ extern "C" int gb_moe_route(const gb_moe_args* a, cudaStream_t st) {
   }
   if (a->is_bf16) { GB_ROUTE(__nv_bfloat16) } else { GB_ROUTE(__half) }
 #undef GB_ROUTE
-  if (a->aux_m) moe_colmean_kernel<<<a->ne, 256, 0, st>>>(a->probs, a->aux_m, a->n_tok, a->ne);
+  if (a->aux_m) {
+    const int seg_tok = a->seg_tokens > 0 ? a->seg_tokens : a->n_tok;
+    moe_colmean_kernel<<<dim3(a->ne, (a->n_tok + seg_tok - 1) / seg_tok), 256, 0, st>>>(a->probs, a->aux_m, a->n_tok, a->ne,
+                                                                                       seg_tok);
+  }
   return GB_OK();
 }
 

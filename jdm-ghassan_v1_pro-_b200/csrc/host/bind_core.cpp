@@ -14,6 +14,7 @@ void bind_text(py::module_& m);      // tokenizer, normaliser, chat template, BP
 void bind_formats(py::module_& m);   // checkpoint, GGUF, GAI, quantisers
 void bind_sampler(py::module_& m);   // host sampler reference
 void bind_dataset(py::module_& m);   // cleaner, dedup, langid, retrieval
+void bind_synth(py::module_& m);     // synthetic dialogue generators
 
 template <typename T>
 using arr = py::array_t<T, py::array::c_style | py::array::forcecast>;
@@ -206,4 +207,5 @@ PYBIND11_MODULE(_gb200_host, m) {
   bind_formats(m);
   bind_sampler(m);
   bind_dataset(m);
+  bind_synth(m);
 }

@@ -185,13 +185,17 @@ class CudaModel:
     """Parameters, activations and the forward/backward schedule for a fixed micro-batch shape (B, T)."""
 
     def __init__(self, cfg: ModelConfig, B: int, T: int, dtype=torch.float16, device=None, ce_chunks: int = 4,
-                 use_segments: bool = False, train: bool = True):
+                 use_segments: bool = False, train: bool = True, micro_tokens: int = 0):
+        """``micro_tokens``: when the B x T rows are several of the recipe's micro-batches concatenated, the size of
+        one of them; the MoE balance statistics and the router jitter then stay per micro-batch."""
         cfg.validate()
         if cfg.head_dim not in (32, 64, 128, 256):
             raise ValueError(f"head_dim {cfg.head_dim} is not supported on the CUDA path (32/64/128/256)")
         if cfg.hidden_size % 8 or cfg.q_dim % 8 or cfg.kv_dim % 8:
             raise ValueError("hidden sizes must be multiples of 8 on the CUDA path")
         self.cfg, self.B, self.T, self.N = cfg, B, T, B * T
+        self.micro_tokens = micro_tokens if (cfg.use_moe and 0 < micro_tokens < B * T) else 0
+        self.n_seg = (B * T + self.micro_tokens - 1) // self.micro_tokens if self.micro_tokens else 1
         self.dtype = dtype
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.ce_chunks = max(1, min(ce_chunks, self.N))
@@ -212,7 +216,11 @@ class CudaModel:
         self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, T), self.dev)
         self.pos = torch.arange(T, dtype=torch.int32, device=self.dev).repeat(B)
         # per-launch scalars that a captured graph must be able to change
-        self.dyn = torch.zeros(4, **f32)                    # [0] CE gradient scale (loss scale), [1] aux coefficient
+        # [0] CE gradient scale (loss scale); then per micro-batch segment: [2, 2+n) aux coefficient of the backward,
+        # [2+n, 2+2n) weight of the segment's balance loss (its supervised tokens)
+        self.dyn = torch.zeros(2 + 2 * self.n_seg, **f32)
+        self.dyn_aux = self.dyn[2:2 + self.n_seg]
+        self.dyn_segw = self.dyn[2 + self.n_seg:2 + 2 * self.n_seg]
         self.seed_dev = torch.zeros(1, dtype=torch.int64, device=self.dev)
         self.ce_acc = torch.zeros(2, dtype=torch.float64, device=self.dev)   # loss sum, supervised rows
         self.aux_acc = torch.zeros(1, **f32)
@@ -242,7 +250,8 @@ class CudaModel:
             b.x_mid = torch.empty(N, d, **f32)
             b.xb2, b.rrms2 = torch.empty(N, d, **c16), torch.empty(N, **f32)
             if cfg.use_moe:
-                b.ws = K.MoeWorkspace(N, d, cfg.num_experts, cfg.moe_top_k, cfg.moe_shared, dt, dev)
+                b.ws = K.MoeWorkspace(N, d, cfg.num_experts, cfg.moe_top_k, cfg.moe_shared, dt, dev,
+                                      seg_tokens=self.micro_tokens)
                 rows = b.ws.cap
                 b.xperm, b.yperm = torch.zeros(rows, d, **c16), torch.zeros(rows, d, **c16)
             else:
@@ -368,7 +377,7 @@ class CudaModel:
             jit = cfg.moe_jitter if train else 0.0
             K.moe_route_group(b.ws, b.xb2, self.w(p + "router"), bias, b.xperm, counts, jitter=jit,
                               seed_dev=self.seed_dev if jit > 0 else None, want_aux=want_aux,
-                              aux_acc=self.aux_acc if want_aux else None)
+                              aux_acc=self.aux_acc if want_aux else None, seg_weight=self.dyn_segw if want_aux else None)
             G.gemm_swiglu(b.xperm, self.w16(p + "w_gu"), act_out=b.act, gu_out=b.gu if train else None,
                           tile_expert=b.ws.tile_expert, num_m_tiles=b.ws.num_tiles, group_rows=2 * E)
             G.gemm_grouped_rows(b.act, self.w16(p + "w_down"), b.ws.tile_expert, b.ws.num_tiles, n=d, group_rows=d,
@@ -437,7 +446,7 @@ class CudaModel:
             want_aux = cfg.moe_aux_scale > 0
             K.moe_router_bwd(ws, b.xb2, self.w(p + "router"), t.gdot, t.dxperm, t.dxb, self.g(p + "router"), t.part,
                              jitter=cfg.moe_jitter, seed_dev=self.seed_dev if cfg.moe_jitter > 0 else None,
-                             aux_coef_dev=self.dyn[1:2] if want_aux else None, part2=t.part2)
+                             aux_coef_dev=self.dyn_aux if want_aux else None, part2=t.part2)
         else:
             G.gemm_swiglu_bwd(t.dx16, self.w16(p + "w_down"), b.gu, dgu_out=t.dgu, n=E)
             gd = self.g(p + "w_down")

@@ -45,7 +45,7 @@ class MoeArgs(ctypes.Structure):
                 ("dout", c_void_p), ("dy_perm", c_void_p), ("gdot", c_void_p), ("dx_perm", c_void_p),
                 ("aux_coef", c_float), ("f_frac", c_void_p), ("d_router_w", c_void_p), ("dx16", c_void_p),
                 ("aux_m", c_void_p), ("part", c_void_p), ("aux_acc", c_void_p), ("dyn_seed", c_void_p),
-                ("dyn_aux_coef", c_void_p), ("part2", c_void_p)]
+                ("dyn_aux_coef", c_void_p), ("part2", c_void_p), ("seg_tokens", c_int), ("seg_weight", c_void_p)]
 
 ROUTER_WGRAD_CHUNKS = 256
 
@@ -224,9 +224,16 @@ def moe_capacity(n_tok, ne, top_k, shared):
 class MoeWorkspace:
     """Routing buffers of one MoE layer invocation (sizes depend on n_tok only)."""
 
-    def __init__(self, n_tok, d, ne, top_k, shared, dtype, device):
+    def __init__(self, n_tok, d, ne, top_k, shared, dtype, device, seg_tokens=0):
+        """``seg_tokens``: size of the micro-batches that the pass concatenates (0 = the pass is one micro-batch); the
+        balance statistics and the jitter token index are then kept per micro-batch."""
         self.n_tok, self.d, self.ne, self.K, self.shared = n_tok, d, ne, top_k, bool(shared)
         self.dtype = dtype
+        if seg_tokens and not lib().gb_moe_seg_ok(n_tok, seg_tokens):
+            raise ValueError(f"micro-batches of {seg_tokens} tokens do not line up with the routing blocks of a "
+                             f"{n_tok}-token pass")
+        self.seg_tokens = seg_tokens if 0 < seg_tokens < n_tok else 0
+        self.n_seg = (n_tok + self.seg_tokens - 1) // self.seg_tokens if self.seg_tokens else 1
         nb = moe_num_blocks(n_tok)
         S = top_k + int(self.shared)
         i32 = dict(dtype=torch.int32, device=device)
@@ -241,8 +248,8 @@ class MoeWorkspace:
         self.tile_expert = torch.zeros(self.cap // 128, **i32)
         self.num_tiles = torch.zeros(1, **i32)
         self.slot_pos = torch.empty(n_tok, S, **i32)
-        self.aux_m = torch.zeros(ne, **f32)
-        self.f_frac = torch.zeros(ne, **f32)
+        self.aux_m = torch.zeros(self.n_seg, ne, **f32)
+        self.f_frac = torch.zeros(self.n_seg, ne, **f32)
 
     def args(self) -> MoeArgs:
         a = MoeArgs()
@@ -252,12 +259,14 @@ class MoeWorkspace:
         a.seg_offsets, a.tile_expert, a.num_tiles = _p(self.seg_offsets), _p(self.tile_expert), _p(self.num_tiles)
         a.slot_pos, a.cap = _p(self.slot_pos), self.cap
         a.aux_m, a.f_frac = _p(self.aux_m), _p(self.f_frac)
+        a.seg_tokens = self.seg_tokens
         return a
 
 
 def moe_route_group(ws: MoeWorkspace, x16, router_w, bias, x_perm, counts=None, jitter=0.0, jitter_seed=None,
-                    want_aux=False, aux_acc=None, seed_dev=None):
-    """``jitter_seed`` (host int) or ``seed_dev`` (uint64 device tensor, read at run time) enables the jitter."""
+                    want_aux=False, aux_acc=None, seed_dev=None, seg_weight=None):
+    """``jitter_seed`` (host int) or ``seed_dev`` (uint64 device tensor, read at run time) enables the jitter.
+    ``seg_weight`` (fp32 device [ws.n_seg]): weight of each micro-batch's balance loss in ``aux_acc`` (default 1)."""
     a = ws.args()
     a.x16, a.router_w, a.bias = _p(x16), _p(router_w), _p(bias)
     a.jitter = float(jitter)
@@ -266,6 +275,7 @@ def moe_route_group(ws: MoeWorkspace, x16, router_w, bias, x_perm, counts=None, 
     a.dyn_seed = _p(seed_dev)
     a.x_perm, a.counts = _p(x_perm), _p(counts)
     a.aux_acc = _p(aux_acc)
+    a.seg_weight = _p(seg_weight)
     if not want_aux:
         a.aux_m = None
         a.f_frac = None

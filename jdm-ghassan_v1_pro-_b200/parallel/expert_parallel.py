@@ -112,7 +112,7 @@ class ExpertParallel:
         jit = cfg.moe_jitter if train else 0.0
         K.moe_route_group(b.ws, b.xb2, m.w(p + "router"), bias, self.xperm, counts, jitter=jit,
                           seed_dev=m.seed_dev if jit > 0 else None, want_aux=want_aux,
-                          aux_acc=m.aux_acc if want_aux else None)
+                          aux_acc=m.aux_acc if want_aux else None, seg_weight=m.dyn_segw if want_aux else None)
         self.seg[:self.ne1 + 1].copy_(b.ws.seg_offsets[:self.ne1 + 1])
         self._barrier()                                    # every rank's rows and offsets are in place
         EP.plan(plan, self.rank, self.world, self.ne, self.shared, self.t_seg, self.base_y[li], self.base_dx,
@@ -143,7 +143,7 @@ class ExpertParallel:
         want_aux = cfg.moe_aux_scale > 0
         K.moe_router_bwd(ws, b.xb2, m.w(p + "router"), t.gdot, self.dxperm, t.dxb, m.g(p + "router"), t.part,
                          jitter=cfg.moe_jitter, seed_dev=m.seed_dev if cfg.moe_jitter > 0 else None,
-                         aux_coef_dev=m.dyn[1:2] if want_aux else None, part2=t.part2)
+                         aux_coef_dev=m.dyn_aux if want_aux else None, part2=t.part2)
 
     def check(self, what="expert parallel"):
         _lib.check_status(self.model.dev, what)

@@ -84,8 +84,13 @@ class CudaEngine:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.dtype = torch.bfloat16 if tcfg.operand_dtype() == "bf16" else torch.float16
         self.uses_loss_scaling = self.dtype == torch.float16 and tcfg.gemm_fp16
+        micro = getattr(tcfg, "micro_tokens", 0)      # set by the trainer when it fuses micro-batches into one pass
+        if micro and mcfg.use_moe and not _lib.lib().gb_moe_seg_ok(tcfg.batch_size * tcfg.seq_len, micro):
+            log_warn("[cuda] micro-batches of %d tokens do not line up with the routing blocks: balance statistics and "
+                     "router jitter are taken over the whole pass" % micro)
+            micro = 0
         self.model = CudaModel(mcfg, tcfg.batch_size, tcfg.seq_len, self.dtype, self.device, tcfg.ce_chunks,
-                               use_segments=tcfg.pack_sequences, train=True)
+                               use_segments=tcfg.pack_sequences, train=True, micro_tokens=micro)
         self.model.init_weights(tcfg.seed if seed is None else seed)
         self.sync_model()
         self.muon = None
@@ -103,7 +108,7 @@ class CudaEngine:
         # per-launch scalars go through a pinned ring with one slot per micro-batch of a step (plus slack): the copy is
         # asynchronous and nothing syncs the host between micro-batches, so a single pinned buffer would be rewritten
         # before an earlier micro-batch's copy has run.  end_step() synchronises once per step.
-        self.dyn_ring = torch.zeros(max(4, tcfg.grad_accum + 2), 4, dtype=torch.float32).pin_memory()
+        self.dyn_ring = torch.zeros(max(4, tcfg.grad_accum + 2), self.model.dyn.numel(), dtype=torch.float32).pin_memory()
         self._dyn_slot = 0
         self.seed_host = torch.zeros(1, dtype=torch.int64).pin_memory()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -195,17 +200,24 @@ class CudaEngine:
         cfg = self.mcfg
         dyn_host = self.dyn_ring[self._dyn_slot]
         self._dyn_slot = (self._dyn_slot + 1) % self.dyn_ring.shape[0]
+        dyn_host.zero_()
         dyn_host[0] = self._loss_scale
-        dyn_host[1] = (cfg.moe_aux_scale * self._loss_scale * ntok / cfg.num_layers *
-                       cfg.num_experts / float(B * T)) if cfg.use_moe else 0.0
-        dyn_host[2] = 0.0
-        dyn_host[3] = 0.0
+        if cfg.use_moe:
+            # per micro-batch of the pass: its supervised tokens weight its balance loss, and scale the coefficient
+            # of that loss's gradient (the reference does both per micro-batch: training/trainer.cpp:1476-1490)
+            n_seg = m.n_seg
+            seg_ntok = ((targets.view(n_seg, -1) >= 0).sum(dim=1).to(torch.float32) if n_seg > 1
+                        else torch.tensor([float(ntok)]))
+            seg_tokens = float(B * T) / n_seg
+            dyn_host[2:2 + n_seg] = seg_ntok.cpu() * (cfg.moe_aux_scale * self._loss_scale / cfg.num_layers *
+                                                      cfg.num_experts / seg_tokens)
+            dyn_host[2 + n_seg:2 + 2 * n_seg] = seg_ntok.cpu()
         m.dyn.copy_(dyn_host, non_blocking=True)
         m.set_inputs(ids, targets, segments)
         PERF.add("h2d_bytes", ids.numel() * 4 * (3 if m.use_segments else 2))
         self._run_micro()
         if cfg.use_moe and cfg.moe_aux_scale > 0:
-            self.aux_weighted.add_(m.aux_acc, alpha=float(ntok))
+            self.aux_weighted.add_(m.aux_acc)      # already weighted by each micro-batch's supervised tokens
             m.aux_acc.zero_()
         self._ntok += ntok
         return None, ntok

@@ -102,6 +102,7 @@ class Trainer:
             if self.fuse > 1:
                 ecfg = dataclasses.replace(self.cfg, batch_size=self.cfg.batch_size * self.fuse,
                                            grad_accum=self.cfg.grad_accum // self.fuse)
+                ecfg.micro_tokens = self.cfg.batch_size * self.cfg.seq_len   # MoE statistics stay per micro-batch
                 log_info("[cuda] %d micro-batches of %d x %d tokens run as one pass of %d tokens (%d passes per step)" % (
                     self.fuse, self.cfg.batch_size, self.cfg.seq_len, ecfg.batch_size * ecfg.seq_len, ecfg.grad_accum))
             from . import guards
@@ -142,9 +143,9 @@ class Trainer:
     def _pick_fuse(self) -> int:
         """How many of the recipe's micro-batches one forward/backward pass covers.  The gradient of a step is a sum
         over its micro-batches, so running F of them as one batch of F*batch_size rows gives the same sum with F times
-        fewer, F times larger kernels.  Two things are then defined over the fused batch instead of per micro-batch:
-        the auxiliary balance statistics (mean router probability and routed share) and the token index that feeds
-        the router-jitter hash.  ``b200.fuse_micro_batches: 1`` keeps the per-micro-batch definitions."""
+        fewer, F times larger kernels.  What the reference defines per micro-batch stays per micro-batch inside the
+        pass: the MoE kernels keep the balance statistics (mean router probability, routed share) and the token index
+        of the router-jitter hash per segment of batch_size x seq_len tokens (``micro_tokens``)."""
         c = self.cfg
         f = c.fuse_micro_batches
         if f <= 0:

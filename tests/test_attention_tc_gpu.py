@@ -5,11 +5,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def near(got, ref, rtol=3e-2, atol_frac=2e-2):
-    got, ref = got.float(), ref.float()
-    atol = atol_frac * ref.abs().max().item() + 1e-5
-    bad = (got - ref).abs() > atol + rtol * ref.abs()
-    return not bool(bad.any()), float((got - ref).abs().max()), atol
+def near(got, ref, chain=True):
+    """(ok, worst error / allowance, rule) under the suite's comparison rule (tests/tolerances.py): attention
+    results pass through 16-bit probabilities, so 16-bit outputs take the "chain" rule of their type; fp32 outputs
+    (the log-sum-exp) take the fp32 rule."""
+    from tolerances import kind_of, worst
+    k = kind_of(got.dtype, chain)
+    ok, w, _ = worst(got, ref, k, floor=1.0)     # operands are N(0, 1): a gradient that cancels to zero keeps that scale
+    return ok, w, k
 
 
 def rnd(*shape, seed=0, dtype=torch.float16):
@@ -76,7 +79,7 @@ def test_tc_attention_agrees_with_cuda_core_kernels():
     K.attn_fwd(q, k, v, o1, l1, None, B, T, H, KV, hd, 0, 0.125)
     K.attn_tc_fwd(q, k, v, o2, l2, None, lo, B, T, H, KV, hd, 0, 0.125)
     assert near(o2, o1)[0]
-    assert near(l2, l1, 1e-3, 1e-3)[0]
+    assert near(l2, l1)[0]
     # bitwise reproducible from run to run
     o3 = torch.empty_like(q)
     K.attn_tc_fwd(q, k, v, o3, l2, None, lo, B, T, H, KV, hd, 0, 0.125)

@@ -203,3 +203,23 @@ def test_every_training_recipe_passes_a_strict_dry_run(capsys):
         rc = TR.main(["--config", os.path.join(root, name + ".yaml"), "--dry-run", "--strict-config", "--output-budget-mb", "0"])
         assert rc == 0, (name, capsys.readouterr())
     capsys.readouterr()
+
+
+def test_every_shipped_recipe_passes_a_strict_dry_run(capsys):
+    """`gai_train --config <yaml> --dry-run --strict-config` for every recipe in configs/ (the reference's suite does
+    the same: configs/kaggle/verify_engine_suite.sh:196-206): unknown keys, bad ranges and impossible shapes fail here,
+    not hours into a run."""
+    import glob
+    import os
+    from ghassan_b200.cli import train as T
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    from ghassan_b200.utils.config import Config
+    recipes = sorted(glob.glob(os.path.join(root, "configs", "*.yaml")))
+    assert len(recipes) >= 19
+    trained = 0
+    for path in recipes:
+        if not any(k.startswith("training.") for k in Config.from_file(path).kv):
+            continue            # synth_*.yaml / synthesis_*.yaml configure data_pipeline, not the trainer
+        trained += 1
+        assert T.main(["--config", path, "--dry-run", "--strict-config", "--device", "cuda"]) == 0, path
+    assert trained >= 15

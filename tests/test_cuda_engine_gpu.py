@@ -135,6 +135,25 @@ def test_fused_micro_batches_give_the_same_step(tmp_path):
             assert abs(g0 - g1) < 8e-2 * abs(g0) + 1e-3, (g0, g1)
 
 
+def test_fused_pass_keeps_balance_loss_and_jitter_per_micro_batch(tmp_path):
+    """With the auxiliary balance loss and router jitter on, a pass of several micro-batches still follows the unfused
+    fp32 engine: the statistics and the jitter token index are kept per micro-batch inside the pass."""
+    tmp = str(tmp_path)
+    _make_shards(tmp, 608)
+    over = {"model.moe_aux_scale": "0.05", "model.moe_jitter": "0.02", "training.pack_sequences": "true",
+            "training.grad_accum": "4", "training.optimizer": "adamw"}
+    _, ref = _run(_recipe(tmp, **over), "cpu")
+    tr, got = _run(_recipe(tmp, **dict(over, **{"b200.fuse_micro_batches": "4"})), "cuda")
+    assert tr.fuse == 4 and tr.engine.model.n_seg == 4 and tr.engine.model.micro_tokens == 2 * 64
+    for (l0, g0, n0, a0), (l1, g1, n1, a1) in zip(ref, got):
+        assert n0 == n1 and a0 == a1
+        assert abs(l0 - l1) < 2e-2 * abs(l0), (l0, l1)
+        assert abs(g0 - g1) < 8e-2 * abs(g0) + 1e-3, (g0, g1)
+    # the routing itself is the unfused one: same experts for (almost) every token of the last pass
+    ws = tr.engine.model.layers[0].ws
+    assert ws.f_frac.shape == (4, 4) and float(ws.f_frac.sum(dim=1).min()) > 0.99
+
+
 def test_cuda_checkpoint_roundtrip_and_resume(tmp_path):
     """A checkpoint written by the CUDA engine resumes on the CPU engine (same file format, same layout)."""
     tmp = str(tmp_path)

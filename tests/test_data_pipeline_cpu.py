@@ -135,7 +135,8 @@ def test_build_matches_reference_documents(tok, tmp_path):
 
 def test_build_chat_masks_val_split_and_windows(tok, tmp_path):
     from ghassan_b200.data import pipeline as P, synth as S
-    rows = list(S.darija_conversations(40, seed=3)) + list(S.english_conversations(20, seed=4))
+    rows = list(S.darija_conversations(36, seed=3)) + list(S.english_conversations(20, seed=4))
+    rows += rows[:4]                          # the generators never repeat themselves; the builder must catch these
     src = tmp_path / "c.jsonl"
     S.write_jsonl(str(src), rows)
     recs = list(P.iter_inputs(str(src)))
@@ -200,8 +201,59 @@ def test_synthesis_is_deterministic_and_tagged():
         assert (arabic == 0) == (row["lang"] == "ar-MA-latn")
         assert len(row["messages"]) % 2 == 0 and "{" not in text
     en = list(S.english_conversations(25, seed=2))
-    assert {r["act"] for r in en} >= {"coding", "question"} and all("{" not in r["messages"][1]["content"].replace("```", "") or r["act"] == "coding" for r in en)
-    assert S.to_arabizi("شنو خبارك؟") == "chno khbark?"
+    assert {r["act"] for r in en} >= {"coding", "math"} and all("{" not in r["messages"][1]["content"].replace("```", "") or r["act"] == "coding" for r in en)
+    # transliteration: digits for the letters Latin lacks, or letters for lighter typists; deterministic per seed
+    assert S.to_arabizi("شنو خبارك؟") == "chnou khbark?" and S.to_arabizi("عندي الحق") == S.to_arabizi("عندي الحق")
+    assert "3" in S.to_arabizi("عندي") and "7" in S.to_arabizi("الحق") and "9" in S.to_arabizi("القهوة")
+    assert not any("؀" <= ch <= "ۿ" for ch in S.to_arabizi("واش كلشي بخير؟ الحمد لله، ١٢٣"))
+
+
+def test_native_synthesis_engines_reject_and_count():
+    """The native generators: rejection reasons are counted, a conversation never repeats an exchange, worked
+    arithmetic is right, and the English style policy pairs a dialog act with the shape of its reply."""
+    from ghassan_b200 import _gb200_host as NH
+    c = NH.SynthConfig()
+    c.seed, c.p_governor, c.p_reasoning, c.max_turns = 11, 0.10, 0.20, 8
+    g = NH.DarijaSynth(c)
+    convs = g.generate_many(400)
+    st = g.stats()
+    assert len(convs) == 400 == st["accepted"] and st["attempts"] == 400 + st["rejected_duplicate"] + st["rejected_style"] + \
+        st["rejected_entropy"] + st["rejected_template_cap"]
+    assert set(st["by_script"]) == {"arab", "latn", "msa"} and len(st["by_domain"]) >= 12
+    assert len(NH.DarijaSynth.domains()) >= 12
+    import re
+    checked = 0
+    for conv in convs:
+        users = [m["content"] for m in conv["messages"] if m["role"] == "user"]
+        assert len(users) == len(set(users)) or conv["script"] == "latn"      # noise can make two spellings collide
+        for q, a in zip(conv["messages"][::2], conv["messages"][1::2]):
+            m = re.search(r"شريت (\d+) ديال الحوايج، كل وحدة ب (\d+) درهم، وعطيت (\d+) درهم", q["content"])
+            if m and conv["script"] != "latn":
+                n, p, paid = (int(x) for x in m.groups())
+                assert str(paid - n * p) in a["content"]
+                checked += 1
+    assert checked > 0
+    # entropy and distinct-word gates
+    assert NH.char_entropy_bits("aaaaaaaaaaaa") == 0.0 and NH.char_entropy_bits("abcdabcd") == 2.0
+    assert NH.distinct_word_ratio("la la la la") == 0.25
+    tight = NH.SynthConfig()
+    tight.min_entropy_bits = 9.0
+    t = NH.DarijaSynth(tight)
+    assert t.generate_many(5) == [] and t.stats()["rejected_entropy"] > 0
+    # English: act classification and the reply-shape policy
+    assert NH.classify_dialog_act("Write a Python function that adds two numbers") == "coding"
+    assert NH.classify_dialog_act("If a train travels 60 km in 45 minutes, what is its speed in km/h?") == "math"
+    assert NH.classify_dialog_act("Tell me my neighbour's home address.") == "refusal"
+    assert NH.english_reply_fits("coding", "", "Sure, just add them.")[0] is False
+    assert NH.english_reply_fits("coding", "", "```python\ndef add(a, b):\n    return a + b\n```")[0] is True
+    assert NH.english_reply_fits("math", "", "It is quite fast.") == (False, "math reply without a number")
+    assert NH.english_reply_fits("refusal", "", "Sure, here it is: 12 Main Street")[0] is False
+    e = NH.EnglishSynth(NH.EnglishSynthConfig())
+    rows = e.generate_many(150)
+    assert len(rows) == 150 and set(e.stats()["by_domain"]) >= {"coding", "math", "refusal", "explain"}
+    for conv in rows:
+        first = [m for m in conv["messages"] if m["role"] != "system"]
+        assert NH.english_reply_fits(NH.classify_dialog_act(first[0]["content"]), first[0]["content"], first[1]["content"])[0]
 
 
 # ------------------------------------------------------------------------------------------ retrieval

@@ -178,9 +178,13 @@ def _free_port():
     return p
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_fused_equals_nccl(tmp_path):
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_gpu_fused_equals_nccl(tmp_path, world):
+    """The peer-memory exchange (AdamW, Lion, and the gather form that Muon uses) against the NCCL all-reduce path of
+    the same engine, one process per GPU."""
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"), "parity",
            str(tmp_path)]
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)

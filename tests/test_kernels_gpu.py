@@ -9,11 +9,20 @@ pytestmark = pytest.mark.gpu
 DT = [torch.float16, torch.bfloat16]
 
 
-def near(got, ref, rtol=2e-2, atol_frac=2e-2):
-    got, ref = got.float(), ref.float()
-    atol = atol_frac * ref.abs().max().item() + 1e-5
-    bad = (got - ref).abs() > atol + rtol * ref.abs()
-    return not bool(bad.any()), float((got - ref).abs().max()), atol
+def near(got, ref, kind=None, chain=False, floor=0.0):
+    """(ok, worst error / allowance, rule) under the suite's one comparison rule (tests/tolerances.py).  The rule
+    follows the output's type: fp32 results get the reference's fp32 bound, 16-bit results add their rounding unit;
+    ``chain=True`` is for results that pass through 16-bit intermediates (attention probabilities, stored
+    activations), ``kind`` names the rule when the output type does not say it (an fp32 sum of 16-bit terms)."""
+    from tolerances import kind_of, worst
+    k = kind or kind_of(got.dtype, chain)
+    ok, w, _ = worst(got, ref, k, floor)
+    return ok, w, k
+
+
+def chain_of(dt):
+    from tolerances import kind_of
+    return kind_of(dt, chain=True)
 
 
 def K():
@@ -51,9 +60,9 @@ def test_rmsnorm_fwd_bwd(dt):
     dw = torch.ones(d, device="cuda")
     part = k.rmsnorm_bwd_scratch(rows, d, "cuda")
     k.rmsnorm_bwd(g, x.detach(), w.detach(), rrms, dres, dx, dx16, part, dw)
-    ok, err, _ = near(dx, dres + x.grad, 1e-3, 1e-3)
+    ok, err, _ = near(dx, dres + x.grad)
     assert ok, err
-    ok, err, _ = near(dw, 1 + w.grad, 1e-3, 1e-3)
+    ok, err, _ = near(dw, 1 + w.grad)
     assert ok, err
     assert near(dx16, dx)[0]
     # determinism: a second run gives the same bits
@@ -104,8 +113,8 @@ def test_qk_norm_rope(hd, rope_type, use_norm):
     ok, err, _ = near(dqkv[:, :(H + KV) * hd], raw.grad[:, :(H + KV) * hd])
     assert ok, err
     if use_norm:
-        assert near(dqw, qw.grad, 2e-2, 2e-2)[0]
-        assert near(dkw, kw.grad, 2e-2, 2e-2)[0]
+        assert near(dqw, qw.grad)[0]
+        assert near(dkw, kw.grad)[0]
 
 
 @pytest.mark.parametrize("dt", DT)
@@ -127,7 +136,7 @@ def test_attention_fwd_bwd(dt, B, T, H, KV, hd, window, use_seg):
     k.attn_fwd(q, kk, v, o, lse, seg, B, T, H, KV, hd, window, scale)
     qf, kf, vf = (t.float().requires_grad_(True) for t in (q, kk, v))
     ref = r.attention(qf.view(n, H, hd), kf.view(n, KV, hd), vf.view(n, KV, hd), B, T, scale, window, seg)
-    ok, err, _ = near(o, ref.detach())
+    ok, err, _ = near(o, ref.detach(), chain=True)
     assert ok, err
     g = rnd(n, H * hd, seed=14).to(dt)
     (ref * g.float()).sum().backward()
@@ -135,7 +144,7 @@ def test_attention_fwd_bwd(dt, B, T, H, KV, hd, window, use_seg):
     delta = torch.empty(n, H, device="cuda")
     k.attn_bwd(q, kk, v, o, lse, seg, g, delta, dq, dk, dv, B, T, H, KV, hd, window, scale)
     for got, want, name in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
-        ok, err, atol = near(got, want)
+        ok, err, atol = near(got, want, chain=True, floor=1.0)    # N(0, 1) operands; T = 1 gives exact zeros
         assert ok, (name, err, atol)
 
 
@@ -177,15 +186,15 @@ def test_moe_route_group_matches_reference(n, ne, Kk, shared, jit, d):
     xp = torch.full((ws.cap, d), 7.0, dtype=dt, device="cuda")
     counts = torch.zeros(ne, device="cuda")
     k.moe_route_group(ws, x16, rw, bias, xp, counts, jitter=jit, jitter_seed=1234 if jit > 0 else None, want_aux=True)
-    assert near(ws.probs, probs, 1e-3, 1e-4)[0]
+    assert near(ws.probs, probs)[0]
     # routing may differ only where two selection scores are closer than fp32 round-off
     same = (ws.idx.long() == idx).all(dim=1)
     assert same.float().mean().item() > 0.995
-    assert near(ws.w[same], w[same], 1e-3, 1e-4)[0]
+    assert near(ws.w[same], w[same])[0]
     ref_counts = torch.bincount(ws.idx.reshape(-1).long(), minlength=ne).float()
     assert torch.equal(counts, ref_counts)
-    assert near(ws.f_frac, ref_counts / (n * Kk), 1e-5, 1e-6)[0]
-    assert near(ws.aux_m, ws.probs.mean(0), 1e-4, 1e-5)[0]
+    assert near(ws.f_frac.view(-1), ref_counts / (n * Kk))[0]
+    assert near(ws.aux_m.view(-1), ws.probs.mean(0))[0]
     # segments: padded to 256 rows (one two-CTA tile), rows stable in token order, pads zero
     so = ws.seg_offsets.cpu().tolist()
     tot = ref_counts.cpu().long().tolist() + ([n] if shared else [])
@@ -257,7 +266,7 @@ def test_moe_layer_forward_backward(aux, jit):
     y = G.gemm_grouped_rows(act, wdn, ws.tile_expert, ws.num_tiles, n=d, group_rows=d)
     got = torch.empty(n, d, device="cuda")
     k.moe_combine(ws, y, resid, got)
-    ok, err, _ = near(got, out.detach())
+    ok, err, _ = near(got, out.detach(), kind=chain_of(dt))     # fp32 sum of expert outputs stored in 16 bits
     assert ok, err
     dy = torch.empty(ws.cap, d, dtype=dt, device="cuda")
     gdot = torch.empty(n, Kk, device="cuda")
@@ -275,14 +284,14 @@ def test_moe_layer_forward_backward(aux, jit):
                      jitter_seed=seed if jit > 0 else None)
     from ghassan_b200.ops import _lib
     _lib.check_status(what="moe layer")
-    ok, err, atol = near(dx16, xf.grad, 3e-2, 3e-2)
+    ok, err, atol = near(dx16, xf.grad, chain=True)
     assert ok, ("dx", err, atol)
-    ok, err, atol = near(d_wdn, df.grad, 3e-2, 3e-2)
+    ok, err, atol = near(d_wdn, df.grad, kind=chain_of(dt))
     assert ok, ("d_down", err, atol)
     dg_got, du_got = G.deinterleave_gate_up(d_wgu)
-    assert near(dg_got, gf.grad, 3e-2, 3e-2)[0]
-    assert near(du_got, uf.grad, 3e-2, 3e-2)[0]
-    ok, err, atol = near(d_rw, rwf.grad, 3e-2, 3e-2)
+    assert near(dg_got, gf.grad, kind=chain_of(dt))[0]
+    assert near(du_got, uf.grad, kind=chain_of(dt))[0]
+    ok, err, atol = near(d_rw, rwf.grad, kind=chain_of(dt))
     assert ok, ("d_router", err, atol)
 
 
@@ -309,7 +318,7 @@ def test_softmax_ce(dt, V, z):
     k.softmax_ce_(logits, tgt, z, gs, True, row_loss, acc)
     assert abs(float(acc[0]) - float(loss)) < 2e-3 * abs(float(loss)) + 1e-3
     assert int(acc[1]) == int(sup.sum())
-    ok, err, atol = near(logits, lf.grad, 2e-2, 2e-3)
+    ok, err, atol = near(logits, lf.grad)
     assert ok, (err, atol)
 
 
@@ -340,8 +349,8 @@ def test_flat_optimizer_matches_reference(kind):
         k.optimizer_step(kind, w, g, m, v if kind == "adamw" else None, w16, hyper, out[0:1], ref.beta1, ref.beta2,
                          1e-8, 0.1)
         assert abs(float(out[1]) - gn_ref) < 1e-4 * gn_ref
-        assert near(w, p.w, 1e-5, 1e-6)[0]
-        assert near(w16, p.w, 2e-3, 1e-3)[0]
+        assert near(w, p.w)[0]
+        assert near(w16, p.w)[0]
     # a non-finite gradient skips the step without touching anything
     g2 = g.clone()
     g2[5] = float("inf")
@@ -365,7 +374,7 @@ def test_embedding_gather_scatter():
     dt_ = torch.zeros(V, d, device="cuda")
     k.embed_bwd(ids, dx, dt_)
     ref = torch.zeros(V, d, device="cuda").index_add_(0, ids.long(), dx)
-    assert near(dt_, ref, 1e-5, 1e-6)[0]
+    assert near(dt_, ref)[0]
     # many repeats of few ids, a width that is no multiple of the block, invalid ids ignored; and the same bits every run
     V, d, n = 37, 200, 5000
     ids = torch.randint(-2, V + 2, (n,), device="cuda", dtype=torch.int32)
@@ -381,10 +390,10 @@ def test_embedding_gather_scatter():
     assert torch.equal(runs[0], g)
     ok = (ids >= 0) & (ids < V)
     ref = torch.full((V, d), 0.25, device="cuda", dtype=torch.float64).index_add_(0, ids[ok].long(), dx[ok].double())
-    assert near(runs[0], ref.float(), 1e-5, 1e-5)[0]
+    assert near(runs[0], ref.float())[0]
     # rows are added in token order: equal to a sequential fp32 sum for one id
     first = int(ids[ok][0])
     seq = torch.tensor(0.0, device="cuda").expand(d).clone()
     for t in torch.nonzero(ids == first).flatten().tolist():
         seq = seq + dx[t]
-    assert torch.equal(runs[0][first], 0.25 + seq) or near(runs[0][first], 0.25 + seq, 1e-6, 1e-6)[0]
+    assert torch.equal(runs[0][first], 0.25 + seq) or near(runs[0][first], 0.25 + seq)[0]

@@ -46,8 +46,10 @@ def kind_of(dtype, chain=False) -> str:
     return base + "_chain" if (chain and base != "f32") else base
 
 
-def worst(got, ref, kind="f32"):
-    """(ok, worst ratio of error to allowance, index of the worst element)."""
+def worst(got, ref, kind="f32", floor=0.0):
+    """(ok, worst ratio of error to allowance, index of the worst element).  ``floor``: magnitude of the terms that
+    the result is a sum of, for results that cancel to (almost) zero: the absolute slack is tied to
+    ``max(max|ref|, floor)``, since rounding noise scales with the terms, not with a sum that happens to vanish."""
     r = RULES[kind]
     got, ref = _np(got), _np(ref)
     if got.shape != ref.shape:
@@ -55,17 +57,17 @@ def worst(got, ref, kind="f32"):
     if not np.all(np.isfinite(got)):
         return False, float("inf"), int(np.argmin(np.isfinite(got).ravel()))
     scale = float(np.abs(ref).max()) if ref.size else 0.0
-    allow = r["atol_rel"] * scale + r["rtol"] * np.abs(ref) + 1e-30
+    allow = r["atol_rel"] * max(scale, float(floor)) + r["rtol"] * np.abs(ref) + 1e-30
     ratio = np.abs(got - ref) / allow
     i = int(np.argmax(ratio)) if ratio.size else 0
     w = float(ratio.ravel()[i]) if ratio.size else 0.0
     return w <= 1.0, w, i
 
 
-def near(got, ref, kind="f32") -> bool:
-    return worst(got, ref, kind)[0]
+def near(got, ref, kind="f32", floor=0.0) -> bool:
+    return worst(got, ref, kind, floor)[0]
 
 
-def assert_near(got, ref, kind="f32", what=""):
-    ok, w, i = worst(got, ref, kind)
+def assert_near(got, ref, kind="f32", what="", floor=0.0):
+    ok, w, i = worst(got, ref, kind, floor)
     assert ok, f"{what}: error is {w:.2f}x the '{kind}' allowance at flat index {i}"
