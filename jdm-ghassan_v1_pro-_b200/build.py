@@ -64,6 +64,18 @@ def _run(cmd, log_path=None):
     return p.stdout
 
 
+def _link(cmd, target, inputs):
+    """Link to a temporary name and rename: a reader (an import in another process, a copy of the tree) sees the old
+    library or the new one, never a half-written file."""
+    tmp = target + ".tmp%d" % os.getpid()
+    try:
+        _run(cmd + ["-o", tmp] + inputs)
+        os.replace(tmp, target)
+    finally:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+
+
 def _sources(sub, ext):
     d = os.path.join(CSRC, sub)
     return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(ext))
@@ -88,7 +100,7 @@ def build_host(verbose=False, force=False):
             if verbose and out.strip():
                 print(out)
     if jobs or not os.path.exists(HOST_SO):
-        _run([CXX, "-shared", "-o", HOST_SO] + objs + ["-pthread"])
+        _link([CXX, "-shared"], HOST_SO, objs + ["-pthread"])
     return HOST_SO
 
 
@@ -109,8 +121,7 @@ def build_cuda(verbose=False, force=False):
             if verbose and out.strip():
                 print(out)
     if jobs or not os.path.exists(CUDA_SO):
-        _run([NVCC, "-shared", "-o", CUDA_SO] + objs +
-             ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"])
+        _link([NVCC, "-shared"], CUDA_SO, objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"])
     return CUDA_SO
 
 

@@ -40,9 +40,38 @@ def _parser() -> argparse.ArgumentParser:
                       ("ctx", int), ("batch", int), ("max-prompts", int), ("seq-len", int), ("batches", int),
                       ("batch-size", int), ("rope-scale", float), ("yarn-mscale", float)):
         ap.add_argument("--" + name, type=typ)
-    for name in ("greedy", "no-adaptive", "no-stream", "retrieve-direct", "stats", "verbose"):
+    for name in ("greedy", "no-adaptive", "no-stream", "retrieve-direct", "stats", "verbose", "measure"):
         ap.add_argument("--" + name, action="store_true")
     return ap
+
+
+def worst_q4_probe(named, profile: str):
+    """``quantize --measure``: how much a 4-bit block format would cost each matrix.  Every non-norm tensor is
+    quantised to Q4_0 and expanded again (embeddings and the output head only to fp16, unless the profile's default
+    type is 8-bit, when they are probed in 4 bits too: tools/inference_cli.cpp:531-549 in the reference); returns
+    (name, relative RMS error) of the worst one."""
+    from .. import _gb200_host as H
+    worst, worst_name = 0.0, ""
+    all_q4 = profile in ("q8_k", "q8_0", "int8")
+    for name, w in named.items():
+        if "norm" in name:
+            continue
+        x = np.ascontiguousarray(np.asarray(w, dtype=np.float32)).reshape(-1)
+        if x.size == 0:
+            continue
+        if name in ("tok_embeddings", "lm_head") and not all_q4:
+            y = x.astype(np.float16).astype(np.float32)
+        elif x.size % 32 == 0:
+            y = np.asarray(H.ggml_dequantize(np.asarray(H.ggml_quantize(x, 2)), 2, x.size), dtype=np.float32)
+        else:
+            continue
+        ok = np.isfinite(x) & np.isfinite(y)
+        n = max(1, int(ok.sum()))
+        rms = float(np.sqrt(np.sum((x[ok].astype(np.float64)) ** 2) / n))
+        rel = float(np.sqrt(np.sum((x[ok].astype(np.float64) - y[ok]) ** 2) / n)) / rms if rms > 0 else 0.0
+        if rel > worst:
+            worst, worst_name = rel, name
+    return worst_name, worst
 
 
 def _sampling(a):
@@ -145,12 +174,19 @@ def main(argv: Optional[List[str]] = None) -> int:
         with tempfile.NamedTemporaryFile(suffix=".gtok", delete=False) as tf:
             tf.write(m.tokenizer.to_bytes())
             tok_path = tf.name
+        if a.measure:
+            name, rel = worst_q4_probe(m.named, a.profile or "q8_k")
+            print("[quant] worst rel RMSE (Q4 probe): %.4f%% on %s" % (rel * 100.0, name))
         try:
             keep = {k: (v.decode() if isinstance(v, bytes) else str(v)) for k, v in m.metadata.items() if k in ("steps", "val_loss")}
-            info = export_gguf(a.out, m.cfg, m.named, tok_path, a.profile or "q8_k", moe_bias=m.moe_bias or None, extra_meta=keep)
+            info = export_gguf(a.out, m.cfg, m.named, tok_path, a.profile or "q8_k", moe_bias=m.moe_bias or None, extra_meta=keep,
+                               compat=a.compat or "native")
+        except ValueError as e:
+            raise SystemExit("quantize: %s" % e)
         finally:
             os.unlink(tok_path)
-        print("[quant] %s -> %s   profile=%s (%d bytes of weights)" % (a.model, a.out, info["profile"], info["weight_bytes"]))
+        print("[quant] %s -> %s   profile=%s compat=%s (%d bytes of weights)" % (
+            a.model, a.out, info["profile"], a.compat or "native", info["weight_bytes"]))
         return 0
 
     # ---- commands that run the model

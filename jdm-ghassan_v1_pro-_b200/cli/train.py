@@ -123,6 +123,15 @@ def _run(args) -> int:
         if args.scheduler not in ("cosine", "wsd"):
             raise ConfigError("unknown --scheduler (cosine|wsd)")
         tcfg.scheduler = args.scheduler
+    v = _num(args, "ckpt-segments", strict)
+    if v is not None:
+        if v < 1:
+            raise ConfigError("--ckpt-segments must be >= 1")
+        tcfg.ckpt_segments, tcfg.activation_checkpointing = v, v > 1
+    v = _num(args, "threads", strict)
+    if v is not None and v > 0:
+        import torch as _torch
+        _torch.set_num_threads(v)
     v = _num(args, "ce-chunks", strict)
     if v is not None:
         tcfg.ce_chunks = min(32, max(1, v))

@@ -6,64 +6,12 @@
 
 #include "sm100_common.cuh"
 #include "gb_decode.h"
+#include "decode_fmt.cuh"
 
 namespace gb {
 
 constexpr int GV_WARPS = 8;            // output rows per CTA
 constexpr int GV_THREADS = GV_WARPS * 32;
-
-__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
-__device__ __forceinline__ uint16_t ld_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
-
-// Expand unit u (values 8u .. 8u+7) of one stored row into floats.
-template <int FMT>
-__device__ __forceinline__ void load8(const uint8_t* __restrict__ row, int u, float (&w)[8]) {
-  if constexpr (FMT == GB_W_F16) {
-    const uint4 q = *reinterpret_cast<const uint4*>(row + 16 * (size_t)u);
-    const __half2* h = reinterpret_cast<const __half2*>(&q);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); w[2 * i] = f.x; w[2 * i + 1] = f.y; }
-  } else if constexpr (FMT == GB_W_BF16) {
-    const uint4 q = *reinterpret_cast<const uint4*>(row + 16 * (size_t)u);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); w[2 * i] = f.x; w[2 * i + 1] = f.y; }
-  } else if constexpr (FMT == GB_W_GGML_Q8_0) {
-    const uint8_t* p = row + (size_t)(u >> 2) * 34;
-    const float d = h2f(ld_u16(p));
-    const uint8_t* q = p + 2 + (u & 3) * 8;           // 2-byte aligned: blocks are 34 bytes
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint16_t v = ld_u16(q + 2 * i);
-      w[2 * i] = d * (float)(int8_t)(v & 0xFF);
-      w[2 * i + 1] = d * (float)(int8_t)(v >> 8);
-    }
-  } else if constexpr (FMT == GB_W_Q4_0) {
-    const uint8_t* p = row + (size_t)(u >> 2) * 18;
-    const float d = h2f(ld_u16(p));
-    const uint8_t* q = p + 2 + (u & 3) * 4;
-    const uint32_t v = (uint32_t)ld_u16(q) | ((uint32_t)ld_u16(q + 2) << 16);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = d * (float)((int)((v >> (4 * i)) & 0xF) - 8);   // byte i: low nibble = value 2i
-  } else if constexpr (FMT == GB_W_Q8_64) {
-    const uint8_t* p = row + (size_t)(u >> 3) * 68;
-    const float d = *reinterpret_cast<const float*>(p);
-    // blocks are 68 bytes: the quants are 4-byte aligned but not 8-byte aligned, so two 32-bit loads
-    const uint32_t* qp = reinterpret_cast<const uint32_t*>(p + 4 + (u & 7) * 8);
-    const uint32_t vx = qp[0], vy = qp[1];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w[i] = d * (float)(int8_t)((vx >> (8 * i)) & 0xFF);
-      w[4 + i] = d * (float)(int8_t)((vy >> (8 * i)) & 0xFF);
-    }
-  } else {   // GB_W_Q4_1
-    const uint8_t* p = row + (size_t)(u >> 2) * 20;
-    const float d = h2f(ld_u16(p)), m = h2f(ld_u16(p + 2));
-    const uint32_t v = *reinterpret_cast<const uint32_t*>(p + 4 + (u & 3) * 4);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = d * (float)((v >> (4 * i)) & 0xF) + m;
-  }
-}
 
 template <typename XT>
 __device__ __forceinline__ float dot8(const float (&w)[8], const XT* __restrict__ x) {
@@ -384,20 +332,38 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const T* __restrict__ 
   }
 }
 
+// One block of HD threads per (sequence, head).  The split maxima and sums are read by one thread per split and the
+// per-split factors go through shared memory, so that the long loop over the splits carries no dependent load: the
+// earlier form (every thread walking all splits twice, each step waiting for its load) took 12 us per launch, a
+// fifth of a token step, for a few kilobytes.
 template <typename T, int HD>
 __global__ void decode_attn_merge_kernel(const float* __restrict__ scratch, int splits, T* __restrict__ out, long long ld_o, int H) {
+  __shared__ float s_f[128];
+  __shared__ float s_red[4];
   pdl_wait();
   const int b = blockIdx.x / H, h = blockIdx.x % H, c = threadIdx.x;
   const float* base = scratch + ((long long)b * H + h) * splits * (HD + 2);
-  float mm = -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, base[s * (HD + 2)]);
-  float ll = 0.f, oo = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = base[s * (HD + 2)];
-    const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);
-    ll += base[s * (HD + 2) + 1] * f;
-    oo += base[s * (HD + 2) + 2 + c] * f;
-  }
+  // maximum over the splits (splits <= 128: up to two per thread)
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  if (c < splits) { m0 = base[c * (HD + 2)]; l0 = base[c * (HD + 2) + 1]; }
+  if (c + HD < splits) { m1 = base[(c + HD) * (HD + 2)]; l1 = base[(c + HD) * (HD + 2) + 1]; }
+  float mm = warp_max(fmaxf(m0, m1));
+  if ((c & 31) == 0) s_red[c >> 5] = mm;
+  __syncthreads();
+  mm = s_red[0];
+  for (int w = 1; w < HD / 32; ++w) mm = fmaxf(mm, s_red[w]);
+  const float f0 = m0 == -INFINITY ? 0.f : __expf(m0 - mm), f1 = m1 == -INFINITY ? 0.f : __expf(m1 - mm);
+  if (c < splits) s_f[c] = f0;
+  if (c + HD < splits) s_f[c + HD] = f1;
+  __syncthreads();                       // also orders the reads of s_red above against the writes below
+  float ll = warp_sum(l0 * f0 + l1 * f1);
+  if ((c & 31) == 0) s_red[c >> 5] = ll;
+  __syncthreads();
+  ll = 0.f;
+  for (int w = 0; w < HD / 32; ++w) ll += s_red[w];
+  float oo = 0.f;
+#pragma unroll 8
+  for (int s = 0; s < splits; ++s) oo += base[s * (HD + 2) + 2 + c] * s_f[s];
   out[b * ld_o + (long long)h * HD + c] = Cvt<T>::from_f(ll > 0.f ? oo / ll : 0.f);
 }
 
@@ -745,6 +711,7 @@ static int launch_decode_attn(const void* q, long long ld_q, const void* cK, con
                               const gb_seq_state* state, void* out, long long ld_o, float* scratch, int splits, int B, int H,
                               int KV, int cap, int window, float scale, int* ticket, cudaStream_t st) {
   const int G = H / KV;
+  if (!ticket && splits > 2 * HD) return -4;      // the merge kernel reads at most two splits per thread
   const dim3 grid(B * KV, splits);
 #define ATT(GG)                                                                                                   \
   GB_PDL_LAUNCH((decode_attn_kernel<T, HD, GG>), grid, dim3(128), st, (const T*)q, ld_q, (const T*)cK, (const T*)cV, slot_pos, \

@@ -1,0 +1,781 @@
+// The whole token step of one sequence as ONE cooperative kernel: embedding row, every layer (RMSNorm + fused QKV
+// projection, QK-norm + RoPE + cache append + split-KV attention, merge + output projection + residual, RMSNorm +
+// router + gate/up + SwiGLU of the selected experts, down projection + residual), final norm and the vocabulary
+// projection.  One CTA of 16 warps per SM; the phases of a layer are separated by grid-wide barriers (five per layer)
+// instead of kernel boundaries (eight per layer in decode.cu), and every warp issues the weight loads of its next
+// piece of work BEFORE it arrives at the barrier: the weights do not depend on the activations, so their DRAM round
+// trip hides behind the barrier instead of following it.  The reference's decode loop (inference/generator.cpp:97-193,
+// cuda/kernels.cu:876-1019) launches about fifteen kernels per layer.
+//
+// Work split.  Output rows of a projection are dealt to the CTAs round robin (row r belongs to CTA r mod grid); inside
+// a CTA a row goes to one warp, or, when the CTA has fewer rows than warps, to KS warps that split the row's K range
+// and meet in shared memory.  Rows are read in "super-units" of 256 stored values: a whole number of quantisation
+// blocks in every format (512 B fp16/bf16, 272 B Q8_0, 144 B Q4_0, 272 B Q8_0(64), 160 B Q4_1) and a multiple of 16 bytes,
+// so one lane loads one 16-byte word of a super-unit, coalesced.  16-bit formats are expanded from that register;
+// block formats go through a per-warp staging slot in shared memory, from which lane l expands values 8l..8l+7.
+//
+// Every barrier wait is bounded (about two seconds): on expiry the CTA writes status 401 and skips the rest of the
+// step, and so do the others when their own wait runs out.  The launch is cooperative, so either all CTAs are
+// resident or the launch fails.
+#include <algorithm>
+#include <type_traits>
+
+#include "sm100_common.cuh"
+#include "gb_decode.h"
+#include "decode_fmt.cuh"
+
+namespace gb {
+namespace mg {
+
+constexpr int WARPS = 16;
+constexpr int THREADS = WARPS * 32;
+constexpr int GROUP = 4;              // super-units a warp keeps in flight
+constexpr int SU = 256;               // values per super-unit
+constexpr int MAX_SLOTS = 9;          // top_k <= 8 routed experts plus the shared one
+constexpr int MAX_HEADS = 128;
+constexpr int ST_TIMEOUT_GRID = 401;
+
+template <int FMT> struct Fmt {
+  static constexpr bool k16 = FMT == GB_W_F16 || FMT == GB_W_BF16;
+  static constexpr int bytes = k16 ? 512 : FMT == GB_W_GGML_Q8_0 ? 272 : FMT == GB_W_Q4_0 ? 144 : FMT == GB_W_Q8_64 ? 272 : 160;
+  static constexpr int words = bytes / 16;    // 16-byte words per super-unit (<= 32: one per lane)
+};
+
+__device__ __forceinline__ uint4 ld_stream(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+template <typename XT> __device__ __forceinline__ float ld16(const XT* p) {       // L2 read of one 16-bit activation
+  const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(p));
+  if constexpr (std::is_same<XT, __half>::value) return __half2float(__ushort_as_half(u));
+  else return __bfloat162float(__ushort_as_bfloat16(u));
+}
+
+// ------------------------------------------------------------------------------------------------ grid barrier
+// Arrivals are counted in sync[0], which only ever grows; barrier k of a launch opens at base + k * grid, where base
+// (sync[1]) is the count the previous launch left behind.
+struct GridBar {
+  unsigned* cnt;
+  int* status;
+  int* dead;          // shared memory: set once a wait of this CTA ran out
+  unsigned next;      // count at which the next barrier opens
+};
+
+__device__ __forceinline__ bool grid_sync(GridBar& gb) {
+  __syncthreads();
+  if (threadIdx.x == 0 && !*gb.dead) {
+    __threadfence();
+    atomicAdd(gb.cnt, 1u);
+    unsigned it = 0;
+    unsigned long long t0 = 0;
+    for (;;) {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(gb.cnt) : "memory");
+      if ((int)(v - gb.next) >= 0) break;
+      ++it;
+      if (it == 2048) t0 = globaltimer_ns();
+      if (it > 2048) {
+        __nanosleep(64);
+        if ((it & 1023) == 0 && globaltimer_ns() - t0 > 2000000000ull) {
+          *gb.dead = 1;
+          atomicCAS(gb.status, 0, ST_TIMEOUT_GRID);
+          break;
+        }
+      }
+    }
+  }
+  gb.next += gridDim.x;
+  __syncthreads();
+  return !*gb.dead;
+}
+
+// ------------------------------------------------------------------------------------------------ row engine
+// One projection phase: every output is a sum over P super-units.  Super-unit p of an output lives at
+//   W + row_off(output) + off[p / nsu] + (p % nsu) * bytes,
+// is multiplied with the 256 activations at xs + (x_mod ? p % nsu : p) * 256, weighted by wt[p / nsu], and added to
+// accumulator (acc_split ? p / nsu : 0).  That covers a plain row (off, wt absent), a gate/up pair (two rows, two
+// accumulators) and the down projection of several experts into one output (one stored row per slot, weighted).
+struct Phase {
+  const uint8_t* W;
+  const long long* off;
+  const float* wt;
+  int nsu, P;
+  bool x_mod, acc_split;
+};
+
+// Which outputs of the CTA a warp computes: local output i = first + k * stride for k < n, super-units [pb, pe).
+struct Plan {
+  int n, first, stride, KS, rows, pb, pe;
+};
+__device__ __forceinline__ Plan make_plan(int N, int P) {
+  const int warp = threadIdx.x >> 5;
+  const int grid = gridDim.x, cta = blockIdx.x;
+  Plan pl;
+  pl.rows = N > cta ? (N - cta + grid - 1) / grid : 0;
+  pl.KS = 1; pl.first = warp; pl.stride = WARPS; pl.pb = 0; pl.pe = P; pl.n = 0;
+  if (pl.rows == 0) return pl;
+  const int ks = min(P, WARPS / pl.rows);
+  if (ks >= 2) {
+    pl.KS = ks;
+    pl.first = warp / ks;
+    const int k = warp - pl.first * ks;
+    pl.pb = k * P / ks;
+    pl.pe = (k + 1) * P / ks;
+    pl.n = pl.first < pl.rows ? 1 : 0;
+  } else {
+    pl.n = warp < pl.rows ? (pl.rows - warp + WARPS - 1) / WARPS : 0;
+  }
+  return pl;
+}
+
+template <int FMT>
+__device__ __forceinline__ void load_group(const Phase& ph, const uint8_t* row, int p0, int pe, uint4 (&r)[GROUP]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    const int p = p0 + i;
+    if (p < pe && lane < Fmt<FMT>::words) {
+      const int s = p / ph.nsu, su = p - s * ph.nsu;
+      r[i] = ld_stream(row + (ph.off ? ph.off[s] : 0ll) + (long long)su * Fmt<FMT>::bytes + 16 * lane);
+    }
+  }
+}
+
+template <int FMT, typename XT>
+__device__ __forceinline__ float su_dot(const uint4& q, const uint8_t* slot, const XT* __restrict__ x) {
+  const int lane = threadIdx.x & 31;
+  float w[8];
+  if constexpr (FMT == GB_W_F16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); w[2 * i] = f.x; w[2 * i + 1] = f.y; }
+  } else if constexpr (FMT == GB_W_BF16) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); w[2 * i] = f.x; w[2 * i + 1] = f.y; }
+  } else {
+    load8<FMT>(slot, lane, w);
+  }
+  const uint4 xv = *reinterpret_cast<const uint4*>(x + 8 * lane);
+  float s = 0.f;
+  const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = Cvt<XT>::unpack2(xu[i]); s += w[2 * i] * f.x + w[2 * i + 1] * f.y; }
+  return s;
+}
+
+template <int FMT, typename XT>
+__device__ __forceinline__ void dot_group(const Phase& ph, const XT* xs, int p0, int pe, const uint4 (&r)[GROUP], uint8_t* stage,
+                                          float (&acc)[2]) {
+  const int lane = threadIdx.x & 31;
+  if constexpr (!Fmt<FMT>::k16) {
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i)
+      if (p0 + i < pe && lane < Fmt<FMT>::words) *reinterpret_cast<uint4*>(stage + i * Fmt<FMT>::bytes + 16 * lane) = r[i];
+    __syncwarp();
+  }
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    const int p = p0 + i;
+    if (p < pe) {
+      const int s = p / ph.nsu, su = p - s * ph.nsu;
+      const float v = su_dot<FMT, XT>(r[i], stage + i * Fmt<FMT>::bytes, xs + (ph.x_mod ? su : p) * SU);
+      if (ph.acc_split && s == 1) acc[1] += v;
+      else acc[0] += (ph.wt ? ph.wt[s] : 1.f) * v;
+    }
+  }
+  if constexpr (!Fmt<FMT>::k16) __syncwarp();
+}
+
+// The first group of the warp's first output, issued before the barrier that precedes the phase.
+template <int FMT, class RowOff>
+__device__ __forceinline__ void preload(const Phase& ph, const Plan& pl, RowOff row_off, uint4 (&cur)[GROUP]) {
+  if (pl.n > 0) load_group<FMT>(ph, ph.W + row_off(blockIdx.x + pl.first * (int)gridDim.x), pl.pb, pl.pe, cur);
+}
+
+// Runs the warp's outputs.  row_off(o): byte offset of output o's stored row; epi(o, a0, a1): called by one thread
+// per finished output.  `cur` holds the preloaded first group.
+template <int FMT, typename XT, class RowOff, class Epi>
+__device__ __forceinline__ void run_phase(const Phase& ph, const Plan& pl, const XT* xs, uint8_t* stage, float (*red)[WARPS],
+                                          uint4 (&cur)[GROUP], RowOff row_off, Epi epi) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grid = gridDim.x, cta = blockIdx.x;
+  const int gpi = (pl.pe - pl.pb + GROUP - 1) / GROUP;
+  const int total = pl.n * gpi;
+  float acc[2] = {0.f, 0.f};
+  int k = 0, g = 0;
+  for (int t = 0; t < total; ++t) {
+    uint4 nxt[GROUP];
+    int k2 = k, g2 = g + 1;
+    if (g2 == gpi) { g2 = 0; ++k2; }
+    if (t + 1 < total)
+      load_group<FMT>(ph, ph.W + row_off(cta + (pl.first + k2 * pl.stride) * grid), pl.pb + GROUP * g2, pl.pe, nxt);
+    dot_group<FMT, XT>(ph, xs, pl.pb + GROUP * g, pl.pe, cur, stage, acc);
+    if (g == gpi - 1) {
+      const float a0 = warp_sum(acc[0]);
+      const float a1 = ph.acc_split ? warp_sum(acc[1]) : 0.f;
+      if (lane == 0) {
+        if (pl.KS == 1) epi(cta + (pl.first + k * pl.stride) * grid, a0, a1);
+        else { red[0][warp] = a0; red[1][warp] = a1; }
+      }
+      acc[0] = acc[1] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) cur[i] = nxt[i];
+    k = k2; g = g2;
+  }
+  if (pl.KS > 1) {                        // uniform over the CTA: rows and P are
+    __syncthreads();
+    if ((int)threadIdx.x < pl.rows) {
+      float a0 = 0.f, a1 = 0.f;
+      for (int j = 0; j < pl.KS; ++j) { a0 += red[0][threadIdx.x * pl.KS + j]; a1 += red[1][threadIdx.x * pl.KS + j]; }
+      epi(cta + (int)threadIdx.x * grid, a0, a1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ pieces
+// RMSNorm of an fp32 row in global memory into 16-bit shared memory, by the whole CTA.
+template <typename XT>
+__device__ __forceinline__ void block_norm(const float* x, const float* __restrict__ w, XT* xs, int d, float eps, float* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d / 4; i += THREADS) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + i);
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < WARPS; ++i) tot += red[i];
+  float inv = rsqrtf(tot / (float)d + eps);
+  if (!isfinite(inv)) inv = 0.f;
+  for (int i = threadIdx.x; i < d / 4; i += THREADS) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + i);
+    const float4 g = reinterpret_cast<const float4*>(w)[i];
+    uint2 o;
+    o.x = Cvt<XT>::pack2(v.x * inv * g.x, v.y * inv * g.y);
+    o.y = Cvt<XT>::pack2(v.z * inv * g.z, v.w * inv * g.w);
+    *reinterpret_cast<uint2*>(xs + 4 * i) = o;
+  }
+  __syncthreads();
+}
+
+// QK-norm + rotation of one head by one warp (the arithmetic of qk_rope_append_kernel in decode.cu); st(i, value).
+template <typename XT, class Store>
+__device__ __forceinline__ void rope_head(const XT* src, const float* __restrict__ w, const float* __restrict__ csr, int hd, int rope_type,
+                                          float eps, Store st) {
+  const int lane = threadIdx.x & 31;
+  const int pairs = hd / 2;
+  float a[2], b[2];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int p = lane + 32 * k;
+    a[k] = b[k] = 0.f;
+    if (p < pairs) {
+      const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + pairs;
+      a[k] = ld16<XT>(src + i0);
+      b[k] = ld16<XT>(src + i1);
+      ss += a[k] * a[k] + b[k] * b[k];
+    }
+  }
+  float inv = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)hd + eps);
+    if (!isfinite(inv)) inv = 0.f;
+  }
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int p = lane + 32 * k;
+    if (p < pairs) {
+      const int i0 = rope_type == 0 ? 2 * p : p, i1 = rope_type == 0 ? 2 * p + 1 : p + pairs;
+      float x0 = a[k], x1 = b[k];
+      if (w) { x0 *= inv * w[i0]; x1 *= inv * w[i1]; }
+      const float c = csr[p], sn = csr[pairs + p];
+      st(i0, x0 * c - x1 * sn);
+      st(i1, x0 * sn + x1 * c);
+    }
+  }
+}
+
+// epl (1, 2 or 4) consecutive 16-bit values of a cache row
+template <typename XT>
+__device__ __forceinline__ void ld_epl(const XT* p, int epl, float (&f)[4]) {
+  if (epl == 2) {
+    const float2 v = Cvt<XT>::unpack2(__ldcg(reinterpret_cast<const unsigned int*>(p)));
+    f[0] = v.x; f[1] = v.y;
+  } else if (epl == 4) {
+    const uint2 u = __ldcg(reinterpret_cast<const uint2*>(p));
+    const float2 v0 = Cvt<XT>::unpack2(u.x), v1 = Cvt<XT>::unpack2(u.y);
+    f[0] = v0.x; f[1] = v0.y; f[2] = v1.x; f[3] = v1.y;
+  } else {
+    f[0] = ld16<XT>(p);
+  }
+}
+
+struct Smem {          // static shared memory of the kernel
+  float red[2][WARPS];
+  float lg[64];
+  float linv[MAX_HEADS];
+  float q[4][128];
+  long long off_e[MAX_SLOTS];
+  long long off_gu[2];
+  float wsel[MAX_SLOTS];
+  int esel[MAX_SLOTS];
+  int dead;
+};
+
+// ------------------------------------------------------------------------------------------------ attention
+// CTA `item` < KV * S serves key/value head item % KV over slots [lo, hi) of the cache (split item / KV): all query
+// heads of the group in one walk.  The CTA whose range holds the step's own slot writes the new K (normalised,
+// rotated) and V there first.  Partial (max, sum, output) per (head, split) go to `scratch`.
+template <typename XT>
+__device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_mega_layer& L, int S, Smem& sm, float* amerge) {
+  const int item = blockIdx.x;
+  if (item >= a.KV * S) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hd = a.hd, G = a.H / a.KV, epl = hd / 32;
+  const int kvh = item % a.KV, split = item / a.KV;
+  const gb_seq_state s = a.state[0];
+  const int n_slots = min(a.cap, s.cache_len + 1);
+  const int slot_new = s.cache_len < a.cap ? s.cache_len : a.pinned + s.ring_start;
+  const int per = (n_slots + S - 1) / S;
+  const int lo = split * per, hi = min(n_slots, lo + per);
+  const bool owner = slot_new >= lo && slot_new < hi;
+  const XT* qkv = reinterpret_cast<const XT*>(a.qkv);
+  const long long kvd = (long long)a.KV * hd;
+  XT* cK = reinterpret_cast<XT*>(L.cache_k);
+  XT* cV = reinterpret_cast<XT*>(L.cache_v);
+  const float* csr = a.cos_sin + (size_t)a.pos[0] * hd;
+  float* am = amerge;                         // [WARPS][4]
+  float* al = amerge + WARPS * 4;             // [WARPS][4]
+  float* ao = amerge + WARPS * 8;             // [WARPS][4][hd]
+
+  for (int g0 = 0; g0 < G; g0 += 4) {
+    const int gc = min(4, G - g0);
+    if (warp < gc) {
+      float* qd = sm.q[warp];
+      const float scale = a.scale;
+      rope_head<XT>(qkv + (size_t)(kvh * G + g0 + warp) * hd, L.q_norm, csr, hd, a.rope_type, a.eps,
+                    [&](int i, float v) { qd[i] = Cvt<XT>::to_f(Cvt<XT>::from_f(v)) * scale; });
+    } else if (g0 == 0 && owner && warp == 4) {
+      XT* dk = cK + (size_t)slot_new * kvd + (size_t)kvh * hd;
+      rope_head<XT>(qkv + (size_t)(a.H + kvh) * hd, L.k_norm, csr, hd, a.rope_type, a.eps,
+                    [&](int i, float v) { dk[i] = Cvt<XT>::from_f(v); });
+      if (kvh == 0 && lane == 0) a.slot_pos[slot_new] = s.abs_pos;
+    } else if (g0 == 0 && owner && warp == 5) {
+      const XT* sv = qkv + (size_t)(a.H + a.KV + kvh) * hd;
+      XT* dv = cV + (size_t)slot_new * kvd + (size_t)kvh * hd;
+      for (int i = lane * 2; i < hd; i += 64)
+        *reinterpret_cast<unsigned int*>(dv + i) = __ldcg(reinterpret_cast<const unsigned int*>(sv + i));
+    }
+    __syncthreads();
+
+    float qv[4][4], m[4], l[4], o[4][4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[g][e] = 0.f;
+        qv[g][e] = (g < gc && e < epl) ? sm.q[g][lane * epl + e] : 0.f;
+      }
+    }
+    auto visit = [&](const float (&kf)[4], const float (&vf)[4]) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (g < gc) {
+          float dsum = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) if (e < epl) dsum += qv[g][e] * kf[e];
+          dsum = warp_sum(dsum);
+          const float mn = fmaxf(m[g], dsum);
+          const float c = __expf(m[g] - mn), p = __expf(dsum - mn);
+          l[g] = l[g] * c + p;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) if (e < epl) o[g][e] = o[g][e] * c + p * vf[e];
+          m[g] = mn;
+        }
+      }
+    };
+    auto live = [&](int j) {
+      if (j >= hi) return false;
+      if (a.window <= 0 || j == slot_new) return true;
+      return s.abs_pos - a.slot_pos[j] < a.window;
+    };
+    for (int j = lo + warp; j < hi; j += 2 * WARPS) {
+      const int j1 = j + WARPS;
+      const bool v0 = live(j), v1 = live(j1);
+      float k0[4], w0[4], k1[4], w1[4];
+      if (v0) {
+        ld_epl<XT>(cK + (size_t)j * kvd + (size_t)kvh * hd + lane * epl, epl, k0);
+        ld_epl<XT>(cV + (size_t)j * kvd + (size_t)kvh * hd + lane * epl, epl, w0);
+      }
+      if (v1) {
+        ld_epl<XT>(cK + (size_t)j1 * kvd + (size_t)kvh * hd + lane * epl, epl, k1);
+        ld_epl<XT>(cV + (size_t)j1 * kvd + (size_t)kvh * hd + lane * epl, epl, w1);
+      }
+      if (v0) visit(k0, w0);
+      if (v1) visit(k1, w1);
+    }
+    // the sixteen warps meet in shared memory, in warp order
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g < gc) {
+        if (lane == 0) { am[warp * 4 + g] = m[g]; al[warp * 4 + g] = l[g]; }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) if (e < epl) ao[(size_t)(warp * 4 + g) * hd + lane * epl + e] = o[g][e];
+      }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < gc * hd; t += THREADS) {
+      const int g = t / hd, c = t - g * hd;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, am[w * 4 + g]);
+      float ll = 0.f, oo = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float mw = am[w * 4 + g];
+        const float f = mw == -INFINITY ? 0.f : __expf(mw - mm);
+        ll += al[w * 4 + g] * f;
+        oo += ao[(size_t)(w * 4 + g) * hd + c] * f;
+      }
+      float* dst = a.att_scratch + ((size_t)(kvh * G + g0 + g) * S + split) * (hd + 2);
+      dst[2 + c] = oo;
+      if (c == 0) { dst[0] = mm; dst[1] = ll; }
+    }
+    __syncthreads();
+  }
+}
+
+// Every CTA merges the S partial results of all heads into the 16-bit attention output in shared memory.
+template <typename XT>
+__device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& sm, float* ftab, XT* xs) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hd = a.hd, st = hd + 2;
+  for (int h = warp; h < a.H; h += WARPS) {
+    const float* base = a.att_scratch + (size_t)h * S * st;
+    float ml = -INFINITY;
+    for (int s = lane; s < S; s += 32) ml = fmaxf(ml, __ldcg(base + (size_t)s * st));
+    const float M = warp_max(ml);
+    float ls = 0.f;
+    for (int s = lane; s < S; s += 32) {
+      const float ms = __ldcg(base + (size_t)s * st);
+      const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
+      ftab[h * S + s] = f;
+      ls += __ldcg(base + (size_t)s * st + 1) * f;
+    }
+    ls = warp_sum(ls);
+    if (lane == 0) sm.linv[h] = ls;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < a.H * hd; c += THREADS) {
+    const int h = c / hd, cc = c - h * hd;
+    const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
+    float oo = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < S; ++s) oo += __ldcg(base + (size_t)s * st) * ftab[h * S + s];
+    const float ll = sm.linv[h];
+    xs[c] = Cvt<XT>::from_f(ll > 0.f ? oo / ll : 0.f);
+  }
+  __syncthreads();
+}
+
+// Router of the normalised activations in shared memory (rules of route_in_block in decode.cu), then the tables the
+// expert phases index by slot: expert, weight, byte offset of the expert's down-projection block.
+template <typename XT>
+__device__ __forceinline__ void route_phase(const gb_mega_args& a, const gb_mega_layer& L, const XT* xs, Smem& sm, long long rb_E) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d = a.d, ne = a.ne, top_k = a.top_k;
+  if (ne > 0) {
+    for (int e = warp; e < ne; e += WARPS) {
+      const float* wr = L.router + (size_t)e * d;
+      float s = 0.f;
+      for (int i = lane * 2; i < d; i += 64) {
+        const float2 xv = Cvt<XT>::unpack2(*reinterpret_cast<const uint32_t*>(xs + i));
+        const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+        s += xv.x * wv.x + xv.y * wv.y;
+      }
+      s = warp_sum(s);
+      if (lane == 0) sm.lg[e] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float mx = -INFINITY;
+      for (int e = 0; e < ne; ++e) mx = fmaxf(mx, sm.lg[e]);
+      float sum = 0.f;
+      for (int e = 0; e < ne; ++e) { sm.lg[e] = __expf(sm.lg[e] - mx); sum += sm.lg[e]; }
+      const float inv = 1.f / sum;
+      unsigned long long taken = 0ull;
+      float psum = 0.f;
+      for (int k = 0; k < top_k; ++k) {
+        float bv = -INFINITY;
+        int bi = 0;
+        for (int e = 0; e < ne; ++e) {
+          if (taken >> e & 1ull) continue;
+          const float sc = sm.lg[e] * inv + (L.bias ? L.bias[e] : 0.f);
+          if (sc > bv) { bv = sc; bi = e; }
+        }
+        taken |= 1ull << bi;
+        sm.esel[k] = bi;
+        sm.wsel[k] = sm.lg[bi] * inv;
+        psum += sm.wsel[k];
+      }
+      const float invs = psum > 1e-8f ? 1.f / psum : 0.f;
+      for (int k = 0; k < top_k; ++k) sm.wsel[k] *= invs;
+      if (a.shared) { sm.esel[top_k] = ne; sm.wsel[top_k] = 1.f; }
+      if (blockIdx.x == 0 && a.r_idx)
+        for (int k = 0; k < top_k; ++k) { a.r_idx[k] = sm.esel[k]; a.r_w[k] = sm.wsel[k]; }
+    }
+  } else if (threadIdx.x == 0) {
+    sm.esel[0] = 0;
+    sm.wsel[0] = 1.f;
+  }
+  __syncthreads();
+  const int slots = ne > 0 ? top_k + (a.shared ? 1 : 0) : 1;
+  if ((int)threadIdx.x < slots) sm.off_e[threadIdx.x] = (long long)sm.esel[threadIdx.x] * d * rb_E;
+  __syncthreads();
+}
+
+template <int FMT, typename XT>
+__device__ __forceinline__ void head_phase(const gb_mega_args& a, const XT* xs, uint8_t* stage, Smem& sm, uint4 (&cur)[GROUP],
+                                           bool preloaded) {
+  const long long rb = (long long)(a.d / SU) * Fmt<FMT>::bytes;
+  Phase ph{reinterpret_cast<const uint8_t*>(a.head), nullptr, nullptr, a.d / SU, a.d / SU, false, false};
+  const Plan pl = make_plan(a.V, ph.P);
+  auto row = [&](int o) { return (long long)o * rb; };
+  if (!preloaded) preload<FMT>(ph, pl, row, cur);
+  run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, row, [&](int o, float v, float) { a.logits[o] = v; });
+}
+
+// ------------------------------------------------------------------------------------------------ the kernel
+template <int FMT, typename XT>
+__global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_constant__ gb_mega_args a) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  __shared__ Smem sm;
+  const int d = a.d, hd = a.hd, qd = a.H * hd, kvd = a.KV * hd, E = a.E;
+  const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
+  const int xs_vals = max(max(d, qd), slots * E);
+  XT* xs = reinterpret_cast<XT*>(dyn);
+  uint8_t* stage_all = dyn + (((size_t)xs_vals * 2 + 15) & ~(size_t)15);
+  uint8_t* stage = stage_all + (size_t)(threadIdx.x >> 5) * GROUP * 512;
+  float* ftab = reinterpret_cast<float*>(stage_all + (size_t)WARPS * GROUP * 512);
+  float* amerge = ftab + a.H * a.max_splits;
+  const int nsu_d = d / SU, nsu_q = qd / SU, nsu_E = E / SU;
+  const long long rb_d = (long long)nsu_d * Fmt<FMT>::bytes, rb_q = (long long)nsu_q * Fmt<FMT>::bytes,
+                  rb_E = (long long)nsu_E * Fmt<FMT>::bytes;
+
+  if (threadIdx.x == 0) sm.dead = 0;
+  GridBar gb{a.sync, a.status, &sm.dead, a.sync[1] + gridDim.x};
+  __syncthreads();
+
+  int tok = a.cur_tok[0];
+  if (tok < 0 || tok >= a.V) tok = 0;
+  const float* x_in = a.emb + (size_t)tok * d;
+  float* x_mid = a.xbuf;
+  float* x_out = a.xbuf + d;
+  XT* qkv = reinterpret_cast<XT*>(a.qkv);
+  XT* act = reinterpret_cast<XT*>(a.act);
+
+  // number of cache splits: about 128 slots per CTA, at most what the grid and the scratch hold
+  const gb_seq_state s0 = a.state[0];
+  const int n_slots = min(a.cap, s0.cache_len + 1);
+  const int S = max(1, min(min(a.max_splits, (int)gridDim.x / a.KV), (n_slots + 127) / 128));
+
+  uint4 cur[GROUP];
+  bool ok = true;
+  {   // first projection of the first layer: nothing to wait for
+    const gb_mega_layer& L = a.layers[0];
+    Phase ph{reinterpret_cast<const uint8_t*>(L.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
+    preload<FMT>(ph, make_plan(qd + 2 * kvd, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
+  }
+  for (int li = 0; li < a.n_layers && ok; ++li) {
+    const gb_mega_layer& L = a.layers[li];
+    // ---- A: RMSNorm + fused QKV projection
+    {
+      block_norm<XT>(x_in, L.attn_norm, xs, d, a.eps, sm.red[0]);
+      Phase ph{reinterpret_cast<const uint8_t*>(L.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
+      const Plan pl = make_plan(qd + 2 * kvd, nsu_d);
+      run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, [&](int o) { return (long long)o * rb_d; },
+                         [&](int o, float v, float) { qkv[o] = Cvt<XT>::from_f(v); });
+    }
+    if (!(ok = grid_sync(gb))) break;
+    // ---- B: attention over the cache (a few CTAs); the others go straight on to fetch their rows of wo
+    attention_phase<XT>(a, L, S, sm, amerge);
+    Phase phC{reinterpret_cast<const uint8_t*>(L.wo), nullptr, nullptr, nsu_q, nsu_q, false, false};
+    const Plan plC = make_plan(d, nsu_q);
+    auto rowC = [&](int o) { return (long long)o * rb_q; };
+    preload<FMT>(phC, plC, rowC, cur);
+    if (!(ok = grid_sync(gb))) break;
+    // ---- C: merge of the splits + output projection + residual
+    merge_phase<XT>(a, S, sm, ftab, xs);
+    run_phase<FMT, XT>(phC, plC, xs, stage, sm.red, cur, rowC,
+                       [&](int o, float v, float) { x_mid[o] = __ldcg(x_in + o) + v; });
+    if (!(ok = grid_sync(gb))) break;
+    // ---- D: RMSNorm + router + gate/up of the chosen experts + SwiGLU
+    {
+      block_norm<XT>(x_mid, L.ffn_norm, xs, d, a.eps, sm.red[0]);
+      route_phase<XT>(a, L, xs, sm, rb_E);
+      if (threadIdx.x == 0) {
+        sm.off_gu[0] = 0;
+        sm.off_gu[1] = reinterpret_cast<const uint8_t*>(L.wu) - reinterpret_cast<const uint8_t*>(L.wg);
+      }
+      __syncthreads();
+      Phase ph{reinterpret_cast<const uint8_t*>(L.wg), sm.off_gu, nullptr, nsu_d, 2 * nsu_d, true, true};
+      const Plan pl = make_plan(slots * E, ph.P);
+      auto row = [&](int o) {
+        const int slot = o / E, j = o - slot * E;
+        return ((long long)sm.esel[slot] * E + j) * rb_d;
+      };
+      preload<FMT>(ph, pl, row, cur);
+      run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, row,
+                         [&](int o, float g, float u) { act[o] = Cvt<XT>::from_f(g / (1.f + __expf(-g)) * u); });
+    }
+    // ---- E: down projection of the chosen experts, weighted, + residual
+    Phase phE{reinterpret_cast<const uint8_t*>(L.wd), sm.off_e, sm.wsel, nsu_E, slots * nsu_E, false, false};
+    const Plan plE = make_plan(d, phE.P);
+    auto rowE = [&](int o) { return (long long)o * rb_E; };
+    preload<FMT>(phE, plE, rowE, cur);
+    if (!(ok = grid_sync(gb))) break;
+    for (int i = threadIdx.x; i < slots * E / 8; i += THREADS)
+      reinterpret_cast<uint4*>(xs)[i] = __ldcg(reinterpret_cast<const uint4*>(act) + i);
+    __syncthreads();
+    run_phase<FMT, XT>(phE, plE, xs, stage, sm.red, cur, rowE,
+                       [&](int o, float v, float) { x_out[o] = __ldcg(x_mid + o) + v; });
+    // ---- the next projection's first rows, then the barrier that publishes x_out
+    const bool last = li + 1 == a.n_layers;
+    bool head_pre = false;
+    if (!last) {
+      const gb_mega_layer& Ln = a.layers[li + 1];
+      Phase ph{reinterpret_cast<const uint8_t*>(Ln.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
+      preload<FMT>(ph, make_plan(qd + 2 * kvd, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
+    } else if (a.head_fmt == FMT) {
+      Phase ph{reinterpret_cast<const uint8_t*>(a.head), nullptr, nullptr, nsu_d, nsu_d, false, false};
+      preload<FMT>(ph, make_plan(a.V, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
+      head_pre = true;
+    }
+    if (!(ok = grid_sync(gb))) break;
+    x_in = x_out;
+    if (last) {
+      // ---- final norm + vocabulary projection
+      block_norm<XT>(x_in, a.final_norm, xs, d, a.eps, sm.red[0]);
+      if (a.head_fmt == FMT) head_phase<FMT, XT>(a, xs, stage, sm, cur, head_pre);
+      else if (a.head_fmt == GB_W_F16) head_phase<GB_W_F16, XT>(a, xs, stage, sm, cur, false);
+      else head_phase<GB_W_BF16, XT>(a, xs, stage, sm, cur, false);
+    }
+  }
+  // ---- bookkeeping: the last CTA out records where the arrival count stands; CTA 0 advances the sequence state
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0 && ok) {
+      gb_seq_state s = a.state[0];
+      if (s.cache_len < a.cap) s.cache_len += 1;
+      else s.ring_start = (s.ring_start + 1) % max(1, a.cap - a.pinned);
+      s.abs_pos += 1;
+      a.state[0] = s;
+      a.pos[0] = s.abs_pos;
+    }
+    __threadfence();
+    const unsigned t = atomicAdd(&a.sync[2], 1u);
+    if (t == gridDim.x - 1) {
+      a.sync[1] = atomicAdd(&a.sync[0], 0u);
+      a.sync[2] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+static size_t dyn_bytes(const gb_mega_args& a) {
+  const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
+  const int xs_vals = std::max(std::max(a.d, a.H * a.hd), slots * a.E);
+  size_t b = ((size_t)xs_vals * 2 + 15) & ~(size_t)15;
+  b += (size_t)WARPS * GROUP * 512;
+  b += (size_t)a.H * a.max_splits * 4;
+  b += (size_t)(WARPS * 8 + WARPS * 4 * a.hd) * 4;
+  return b;
+}
+
+}  // namespace mg
+}  // namespace gb
+
+using namespace gb;
+
+extern "C" int gb_decode_mega_ok(const gb_mega_args* a) {
+  if (!a || a->n_layers <= 0) return -1;
+  if (a->d % mg::SU || (a->H * a->hd) % mg::SU || a->E % mg::SU) return -2;          // whole super-units per stored row
+  if (a->hd != 32 && a->hd != 64 && a->hd != 128) return -3;
+  if (a->KV <= 0 || a->H % a->KV || a->H > mg::MAX_HEADS) return -3;
+  if (a->ne > 64 || a->ne < 0 || (a->ne > 0 && (a->top_k < 1 || a->top_k > 8 || a->top_k > a->ne))) return -4;
+  if (a->fmt < GB_W_F16 || a->fmt > GB_W_Q4_1) return -5;
+  if (a->head_fmt != a->fmt && a->head_fmt != GB_W_F16 && a->head_fmt != GB_W_BF16) return -5;
+  if (a->max_splits < 1 || a->cap < 1 || a->pinned < 0 || a->pinned >= a->cap) return -6;
+  if (mg::dyn_bytes(*a) > 200 * 1024) return -7;
+  return 0;
+}
+
+// Number of CTAs of the launch: one per SM (a cooperative launch needs all of them resident at once).
+extern "C" int gb_decode_mega_grid() {
+  static const int n = []() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+  }();
+  return n;
+}
+
+template <int FMT, typename XT>
+static int launch_mega(const gb_mega_args& a, cudaStream_t st) {
+  auto kern = mg::decode_mega_kernel<FMT, XT>;
+  const size_t smem = mg::dyn_bytes(a);
+  static bool attr_done = false;                 // one process drives one device
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -8;
+    attr_done = true;
+  }
+  const int grid = gb_decode_mega_grid();
+  if (grid <= 0 || grid < a.KV) return -9;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeCooperative;
+  attr.val.cooperative = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(mg::THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return -(1000 + (int)e); }
+  return 0;
+}
+
+extern "C" int gb_decode_mega(const gb_mega_args* a, cudaStream_t st) {
+  const int rc = gb_decode_mega_ok(a);
+  if (rc) return rc;
+#define GB_MEGA_CASE(F)                                                    \
+  case F:                                                                  \
+    return a->is_bf16 ? launch_mega<F, __nv_bfloat16>(*a, st) : launch_mega<F, __half>(*a, st);
+  switch (a->fmt) {
+    GB_MEGA_CASE(GB_W_F16)
+    GB_MEGA_CASE(GB_W_BF16)
+    GB_MEGA_CASE(GB_W_GGML_Q8_0)
+    GB_MEGA_CASE(GB_W_Q4_0)
+    GB_MEGA_CASE(GB_W_Q8_64)
+    GB_MEGA_CASE(GB_W_Q4_1)
+  }
+#undef GB_MEGA_CASE
+  return -5;
+}

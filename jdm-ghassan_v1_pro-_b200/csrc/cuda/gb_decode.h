@@ -99,6 +99,38 @@ int gb_decode_attn_fused(const void* q16, long long ld_q, const void* cacheK, co
                          const gb_seq_state* state, void* out16, long long ld_o, float* scratch, int splits, int B, int H,
                          int KV, int hd, int cap, int window, float scale, int is_bf16, int* ticket, cudaStream_t st);
 
+// ---- the whole token step of ONE sequence as one cooperative kernel (decode_mega.cu)
+typedef struct gb_mega_layer {
+  const float* attn_norm; const float* ffn_norm;
+  const float* q_norm; const float* k_norm;      // NULL: no QK-norm
+  const void* wqkv; const void* wo;              // stored rows, format `fmt`
+  const float* router; const float* bias;        // NULL for a dense block / no balancing bias
+  const void* wg; const void* wu; const void* wd;   // experts stacked, the shared one last
+  void* cache_k; void* cache_v;                  // [cap, KV * hd] 16-bit
+} gb_mega_layer;
+
+typedef struct gb_mega_args {
+  const gb_mega_layer* layers;                   // device array [n_layers]
+  int n_layers, d, H, KV, hd, ne, top_k, shared, E, V;   // ne == 0: dense feed-forward of width E
+  int fmt, head_fmt, is_bf16, rope_type;         // head_fmt: fmt, GB_W_F16 or GB_W_BF16
+  float eps, scale;
+  const float* emb; const int* cur_tok;          // fp32 embedding rows; the token to run
+  const float* final_norm; const void* head; float* logits;   // logits: [V] fp32
+  const float* cos_sin; int* pos;                // RoPE table [positions, hd]; pos[0] = position of the token
+  gb_seq_state* state; int* slot_pos;            // advanced by the kernel at the end of the step
+  int cap, pinned, window;
+  float* xbuf;                                   // 2 * d floats
+  void* qkv;                                     // (H + 2 KV) * hd 16-bit
+  float* att_scratch; int max_splits;            // H * max_splits * (hd + 2) floats
+  void* act;                                     // slots * E 16-bit
+  int* r_idx; float* r_w;                        // router choice of the last layer (may be NULL)
+  unsigned* sync;                                // 4 words, zero before the first launch, owned by the kernel afterwards
+  int* status;                                   // set to 401 when a grid-wide wait ran out
+} gb_mega_args;
+int gb_decode_mega_ok(const gb_mega_args* a);    // 0 when the shapes are covered, else a negative code
+int gb_decode_mega_grid(void);                   // CTAs of the launch (one per SM)
+int gb_decode_mega(const gb_mega_args* a, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

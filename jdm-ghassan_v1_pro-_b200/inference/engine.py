@@ -33,6 +33,11 @@ from ..ops import kernels as K
 PINNED_TOKENS = 8
 
 
+def _lib_status(dev):
+    from ..ops import _lib
+    return _lib.status_word(dev)
+
+
 @dataclass
 class SamplingParams:
     temperature: float = 0.8
@@ -71,9 +76,11 @@ class InferenceEngine:
     def __init__(self, cfg: ModelConfig, named: Dict[str, np.ndarray], fmt: str = "f16", batch: int = 1,
                  max_len: int = 2048, prefill_chunk: int = 1024, moe_bias: Optional[Sequence] = None, device=None,
                  compute_dtype=torch.float16, keep_f16_embeddings: bool = True, raw=None, raw_types=None,
-                 fused_step: bool = True):
+                 fused_step: bool = True, single_kernel: Optional[bool] = None):
         """``named``: fp32 tensors by parameter name.  ``fmt``: decode weight format, or "auto" with ``raw`` (an object
-        with ``tensor_raw(name)``, e.g. a GGUF file) and ``raw_types`` (name -> ggml type) to take the stored bytes."""
+        with ``tensor_raw(name)``, e.g. a GGUF file) and ``raw_types`` (name -> ggml type) to take the stored bytes.
+        ``single_kernel``: run the token step of a batch of one as one cooperative kernel (``csrc/cuda/decode_mega.cu``)
+        when the shapes allow it; None takes the default (``GB200_DECODE_MEGA``)."""
         cfg.validate()
         if cfg.head_dim not in (32, 64, 128):
             raise ValueError("decode attention supports head_dim 32, 64 and 128")
@@ -181,12 +188,60 @@ class InferenceEngine:
         self.n_stop = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._graph_key = None
+        self.mega: Optional[D.MegaArgs] = None
+        if single_kernel is None:
+            single_kernel = os.environ.get("GB200_DECODE_MEGA", "0") == "1"
+        if single_kernel and batch == 1:
+            self._build_mega()
         self.prefill_chunk = min(prefill_chunk, max_len)
         self._prefill_model: Optional[CudaModel] = None
         self._named = named
         self.rng = H.Rng(1)
         self._uni_host = torch.zeros(max_len, B, dtype=torch.float32).pin_memory()
         self._host_step = 0
+
+    # ------------------------------------------------------------------ single-kernel step
+    def _build_mega(self):
+        """Argument block of the one-kernel token step; leaves ``self.mega`` None when the kernel does not cover the
+        model (row lengths that are not whole 256-value units, head sizes, expert counts: ``gb_decode_mega_ok``)."""
+        cfg = self.cfg
+        p = lambda t: None if t is None else t.data_ptr()
+        rows = []
+        for L in self.layers:
+            m = D.MegaLayer()
+            m.attn_norm, m.ffn_norm, m.q_norm, m.k_norm = p(L.attn_norm), p(L.ffn_norm), p(L.qn), p(L.kn)
+            m.wqkv, m.wo = L.wqkv.data.data_ptr(), L.wo.data.data_ptr()
+            m.router = p(L.router) if cfg.use_moe else None
+            m.bias = p(L.bias) if cfg.use_moe else None
+            m.wg, m.wu, m.wd = L.wg.data.data_ptr(), L.wu.data.data_ptr(), L.wd.data.data_ptr()
+            m.cache_k, m.cache_v = L.cK.data_ptr(), L.cV.data_ptr()
+            rows.append(m)
+        self._mega_layers = D.mega_layer_table(rows, self.dev)
+        grid = D.mega_grid()
+        a = D.MegaArgs()
+        a.layers = self._mega_layers.data_ptr()
+        a.n_layers, a.d, a.H, a.KV, a.hd = cfg.num_layers, cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        a.ne = cfg.num_experts if cfg.use_moe else 0
+        a.top_k = cfg.moe_top_k if cfg.use_moe else 1
+        a.shared = int(bool(cfg.use_moe and cfg.moe_shared))
+        a.E, a.V = self.E, cfg.vocab_size
+        a.fmt, a.head_fmt, a.is_bf16, a.rope_type = self.fmt, self.head.fmt, int(self.dt == torch.bfloat16), cfg.rope_type
+        a.eps, a.scale = cfg.rms_eps, cfg.attn_scale()
+        a.emb, a.cur_tok = self.emb.data_ptr(), self.cur_tok.data_ptr()
+        a.final_norm, a.head, a.logits = self.final_norm.data_ptr(), self.head.data.data_ptr(), self.logits.data_ptr()
+        a.cos_sin, a.pos = self.cos_sin.data_ptr(), self.pos.data_ptr()
+        a.state, a.slot_pos = self.state.data_ptr(), self.slot_pos.data_ptr()
+        a.cap, a.pinned, a.window = self.cap, PINNED_TOKENS, cfg.sliding_window
+        self._mega_x = torch.zeros(2 * cfg.hidden_size, dtype=torch.float32, device=self.dev)
+        a.xbuf, a.qkv = self._mega_x.data_ptr(), self.qkv.data_ptr()
+        a.max_splits = max(1, min(64, grid // max(1, cfg.num_kv_heads)))
+        self._mega_scratch = torch.zeros(cfg.num_heads * a.max_splits * (cfg.head_dim + 2), dtype=torch.float32, device=self.dev)
+        a.att_scratch, a.act = self._mega_scratch.data_ptr(), self.act.data_ptr()
+        a.r_idx, a.r_w = self.r_idx.data_ptr(), self.r_w.data_ptr()
+        self._mega_sync = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        a.sync, a.status = self._mega_sync.data_ptr(), _lib_status(self.dev).data_ptr()
+        if grid > 0 and D.mega_ok(a) == 0:
+            self.mega = a
 
     # ------------------------------------------------------------------ one decode step (captured)
     def _layer_step(self, L: _Layer, x_in, x_out):
@@ -243,6 +298,9 @@ class InferenceEngine:
     def _forward_token(self):
         """Embedding of ``cur_tok`` through all layers to fp32 logits; advances the per-sequence state."""
         cfg = self.cfg
+        if self.mega is not None:
+            D.decode_mega(self.mega)
+            return
         K.embed_fwd(self.cur_tok, self.emb, self.x[0])
         for i, L in enumerate(self.layers):
             self._layer_step(L, self.x[i % 2], self.x[(i + 1) % 2])

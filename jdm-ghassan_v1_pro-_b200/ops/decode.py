@@ -212,3 +212,50 @@ def decode_advance(state, pos_out, cap, pinned):
 def sample(args: SampleArgs):
     rc = _lib.lib().gb_sample(ctypes.byref(args), _lib.stream_ptr())
     _lib.check_rc(rc, "gb_sample")
+
+
+# ------------------------------------------------------------------------------ single-kernel token step
+class MegaLayer(ctypes.Structure):
+    _fields_ = [(n, c_vp) for n in ("attn_norm", "ffn_norm", "q_norm", "k_norm", "wqkv", "wo", "router", "bias",
+                                    "wg", "wu", "wd", "cache_k", "cache_v")]
+
+
+class MegaArgs(ctypes.Structure):
+    _fields_ = [
+        ("layers", c_vp),
+        ("n_layers", c_int), ("d", c_int), ("H", c_int), ("KV", c_int), ("hd", c_int), ("ne", c_int), ("top_k", c_int),
+        ("shared", c_int), ("E", c_int), ("V", c_int),
+        ("fmt", c_int), ("head_fmt", c_int), ("is_bf16", c_int), ("rope_type", c_int),
+        ("eps", c_float), ("scale", c_float),
+        ("emb", c_vp), ("cur_tok", c_vp),
+        ("final_norm", c_vp), ("head", c_vp), ("logits", c_vp),
+        ("cos_sin", c_vp), ("pos", c_vp),
+        ("state", c_vp), ("slot_pos", c_vp),
+        ("cap", c_int), ("pinned", c_int), ("window", c_int),
+        ("xbuf", c_vp), ("qkv", c_vp),
+        ("att_scratch", c_vp), ("max_splits", c_int),
+        ("act", c_vp),
+        ("r_idx", c_vp), ("r_w", c_vp),
+        ("sync", c_vp), ("status", c_vp),
+    ]
+
+
+def mega_layer_table(layers, device) -> torch.Tensor:
+    """Device copy of a list of :class:`MegaLayer` (the kernel indexes it by layer)."""
+    arr = (MegaLayer * len(layers))(*layers)
+    raw = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8)
+    return raw.to(device)
+
+
+def mega_grid() -> int:
+    return int(_lib.lib().gb_decode_mega_grid())
+
+
+def mega_ok(a: MegaArgs) -> int:
+    """0 when the single-kernel step covers these shapes and formats, else the negative code that says why not."""
+    return int(_lib.lib().gb_decode_mega_ok(ctypes.byref(a)))
+
+
+def decode_mega(a: MegaArgs):
+    rc = _lib.lib().gb_decode_mega(ctypes.byref(a), _lib.stream_ptr())
+    _lib.check_rc(rc, "gb_decode_mega")

@@ -159,8 +159,12 @@ def test_english_discipline_and_repetition_metrics():
 def test_suites_round_trip_and_summary(tok, tmp_path):
     from ghassan_b200.inference import evaluate as E
     items = E.builtin_suite()
-    assert len(items) >= 10 and len({i.id for i in items}) == len(items) and len({i.category for i in items}) >= 4
-    assert all(i.expect_lang == "en" for i in E.builtin_suite_en())
+    from ghassan_b200.inference import eval_suites as ES
+    assert len(items) >= 50 and len({i.id for i in items}) == len(items)
+    assert {i.category for i in items} == set(ES.CATEGORIES) and len(ES.CATEGORIES) == 14      # every category has items
+    en = E.builtin_suite_en()
+    assert len(en) >= 25 and all(i.expect_lang in ("en", "") for i in en) and len({i.category for i in en}) >= 10
+    assert ES.category_from_name("Code-Switching") == "code_switching" and ES.category_from_name("nope") == "basic_conversation"
     E.write_suite(str(tmp_path / "suite.jsonl"), items)
     back = E.load_suite(str(tmp_path))
     assert [(i.id, i.prompt, i.expect_any, i.max_words) for i in back] == [(i.id, i.prompt, i.expect_any, i.max_words) for i in items]
@@ -221,6 +225,17 @@ def test_infer_cli_export_info_quantize_tokenize(tmp_path, capsys):
     assert os.path.getsize(q) < os.path.getsize(out)
     capsys.readouterr()
     assert I.main(["info", "--model", q]) == 0 and "Q4_0" in capsys.readouterr().out
+    # --measure: the 4-bit probe names a matrix and a plausible error; --compat writes the llama-style names
+    q2 = str(tmp_path / "q2.gguf")
+    assert I.main(["quantize", "--model", out, "--out", q2, "--profile", "q8_k", "--measure", "--compat", "native"]) == 0
+    msg = capsys.readouterr().out
+    assert "worst rel RMSE (Q4 probe):" in msg and "compat=native" in msg
+    pct = float(msg.split("worst rel RMSE (Q4 probe):")[1].split("%")[0])
+    assert 1.0 < pct < 30.0
+    with pytest.raises(SystemExit, match="unknown compat"):
+        I.main(["quantize", "--model", out, "--out", q2, "--compat", "nonsense"])
+    with pytest.raises(SystemExit, match="refused"):      # this model has a shared expert and QK-norm: no llama.cpp form
+        I.main(["quantize", "--model", out, "--out", q2, "--compat", "llama_moe"])
     assert I.main(["tokenize", "--model", out, "--text", "salam"]) == 0
     t = capsys.readouterr().out
     assert "tokens  :" in t and "ids     :" in t

@@ -409,3 +409,101 @@ def test_fused_token_step_equals_separate_kernels(moe, fmt, B):
         assert np.array_equal(np.asarray(outs[0]), np.asarray(outs[1]))
     else:
         assert np.asarray(outs[0]).shape == np.asarray(outs[1]).shape
+
+
+# ------------------------------------------------------------------------------ the token step as one cooperative kernel
+_MEGA_CASES = [
+    dict(moe=True, fmt="f16"),
+    dict(moe=True, fmt="q8_0"),
+    dict(moe=True, fmt="q4_0"),
+    dict(moe=False, fmt="q4_1"),
+    dict(moe=True, fmt="q8_64", dtype="bf16"),
+    dict(moe=False, fmt="bf16", dtype="bf16"),
+    dict(moe=True, fmt="f16", num_heads=2, num_kv_heads=1),                    # head_dim 128
+    dict(moe=True, fmt="q8_0", num_heads=8, num_kv_heads=1),                   # head_dim 32, eight heads per group
+    dict(moe=True, fmt="f16", sliding_window=16),
+    dict(moe=True, fmt="q4_0", rope_type=1, use_qk_norm=False),
+]
+
+
+@pytest.mark.parametrize("case", _MEGA_CASES, ids=lambda c: "-".join(f"{k}={v}" for k, v in c.items()))
+def test_single_kernel_step_matches_kernel_chain(case):
+    """One cooperative launch per token against the chain of per-operation kernels: same cache contents, positions and
+    state, logits equal up to the order of the fp32 sums (the two split rows and cache ranges differently)."""
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.models.config import init_parameters
+    from ghassan_b200.ops import _lib
+    case = dict(case)
+    moe, fmt = case.pop("moe"), case.pop("fmt")
+    dt = torch.bfloat16 if case.pop("dtype", "f16") == "bf16" else torch.float16
+    cfg = _tiny_cfg(use_moe=moe, moe_expert_dim=256, intermediate_size=512, **case)
+    named = init_parameters(cfg, 31)
+    one = InferenceEngine(cfg, named, fmt=fmt, batch=1, max_len=48, prefill_chunk=32, compute_dtype=dt, single_kernel=True)
+    chain = InferenceEngine(cfg, named, fmt=fmt, batch=1, max_len=48, prefill_chunk=32, compute_dtype=dt, single_kernel=False)
+    assert one.mega is not None and chain.mega is None
+    seq = torch.randint(16, 512, (1, 60), generator=torch.Generator().manual_seed(9), dtype=torch.int32)
+    for e in (one, chain):
+        e.reset(1)
+    tol = 4e-3 if dt == torch.float16 else 3e-2
+    for j in range(60):                                  # longer than the cache: the ring wraps
+        for e in (one, chain):
+            e.cur_tok.copy_(seq[:, j])
+            e._forward_token()
+        scale = float(chain.logits.abs().max())
+        err = float((one.logits - chain.logits).abs().max())
+        assert err <= tol * max(1.0, scale), (j, err, scale)
+        assert one.state.cpu().tolist() == chain.state.cpu().tolist(), j
+    _lib.check_status(what="single-kernel decode step")
+    assert torch.equal(one.slot_pos, chain.slot_pos) and torch.equal(one.pos, chain.pos)
+    for La, Lb in zip(one.layers, chain.layers):
+        assert torch.allclose(La.cK.float(), Lb.cK.float(), atol=8 * tol) and torch.allclose(La.cV.float(), Lb.cV.float(), atol=8 * tol)
+    sp = SamplingParams(greedy=True, repetition_penalty=1.0)
+    outs = []
+    for e in (one, chain):                               # through the captured graph, with the device sampler
+        e.reset(1)
+        e.prefill(seq[:, :9].contiguous())
+        e.sample_first(sp)
+        e.decode_steps(12, sp)
+        outs.append(np.asarray(e.transcript(13)))
+    _lib.check_status(what="single-kernel decode step (graph)")
+    assert outs[0].shape == outs[1].shape and int(one.state[0, 0]) == int(chain.state[0, 0])
+    same = int((outs[0] == outs[1]).sum())
+    assert outs[0][0, 0] == outs[1][0, 0] and same >= 1, (outs[0], outs[1])
+
+
+def test_single_kernel_step_is_refused_for_uncovered_shapes():
+    from ghassan_b200.inference.engine import InferenceEngine
+    from ghassan_b200.models.config import init_parameters
+    cfg = _tiny_cfg()                                     # expert width 128: not a whole 256-value unit
+    eng = InferenceEngine(cfg, init_parameters(cfg, 3), fmt="f16", batch=1, max_len=32, single_kernel=True)
+    assert eng.mega is None and eng.fused
+    eng2 = InferenceEngine(_tiny_cfg(moe_expert_dim=256), init_parameters(_tiny_cfg(moe_expert_dim=256), 3), fmt="f16", batch=2,
+                           max_len=32, single_kernel=True)
+    assert eng2.mega is None                              # more than one sequence: the kernel chain
+
+
+def test_single_kernel_barrier_wait_runs_out_with_a_status():
+    """A barrier that cannot open (its opening count is set far ahead of the arrivals) ends after its time limit with
+    status 401; the step is skipped, the context stays usable and the next step runs."""
+    from ghassan_b200.inference.engine import InferenceEngine
+    from ghassan_b200.models.config import init_parameters
+    from ghassan_b200.ops import _lib
+    cfg = _tiny_cfg(moe_expert_dim=256)
+    eng = InferenceEngine(cfg, init_parameters(cfg, 3), fmt="f16", batch=1, max_len=32, single_kernel=True)
+    assert eng.mega is not None
+    eng.reset(1)
+    eng.cur_tok.fill_(20)
+    eng._forward_token()
+    torch.cuda.synchronize()
+    _lib.check_status(what="warm-up step")
+    before = eng.state.cpu().tolist()
+    eng._mega_sync[1] += 1 << 30                          # the count this launch starts from: nothing ever reaches it
+    eng._forward_token()
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="401"):
+        _lib.check_status(what="step with a closed barrier")
+    assert eng.state.cpu().tolist() == before             # the step did not advance the sequence
+    eng._forward_token()                                  # the kernel left its counters consistent
+    torch.cuda.synchronize()
+    _lib.check_status(what="step after the expired wait")
+    assert int(eng.state[0, 0]) == before[0][0] + 1 and bool(torch.isfinite(eng.logits).all())
