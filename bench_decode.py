@@ -86,6 +86,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-args", default="", help="extra arguments for the reference binary (default: none)")
     ap.add_argument("--workdir", default=os.environ.get("GB200_BENCH_DIR", "/tmp/gb200_bench_decode"))
+    ap.add_argument("--single-kernel", type=int, default=-1, help="1 / 0: force the one-kernel token step on or off (default: the engine's)")
+    ap.add_argument("--trace-phases", type=int, default=0,
+                    help="with the one-kernel step: print the mean time of each phase and barrier over this many tokens")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference(a)
@@ -101,8 +104,13 @@ def main():
     sp = SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, repetition_penalty=1.0, seed=a.seed)
     for fmt in a.formats.split(","):
         for B in (int(x) for x in a.batches.split(",")):
-            eng = InferenceEngine(cfg, named, fmt=fmt, batch=B, max_len=a.prompt + a.new + 8, prefill_chunk=a.prompt)
+            eng = InferenceEngine(cfg, named, fmt=fmt, batch=B, max_len=a.prompt + a.new + 8, prefill_chunk=a.prompt,
+                                  single_kernel=None if a.single_kernel < 0 else bool(a.single_kernel))
             r = Generator(eng).benchmark(a.prompt, a.new, sp, a.seed)
+            r["token_step"] = ("one cooperative kernel" if eng.mega is not None else
+                               "tensor-core GEMMs over 16-bit weight copies" if eng.batched else "GEMV kernel chain over the stored bytes")
+            if a.trace_phases > 0 and eng.mega is not None:
+                r["phase_us"] = eng.trace_phases(a.trace_phases)
             r.update({"metric": "decode tokens/s", "model": os.path.splitext(os.path.basename(a.config))[0],
                       "params": cfg.count_parameters(), "weight_format": fmt, "kv_cache": "fp16",
                       "sampling": "top_p 0.9 top_k 40 temperature 0.8 seed %d" % a.seed, "data": "synthetic"})

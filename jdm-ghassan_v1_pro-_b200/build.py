@@ -104,6 +104,41 @@ def build_host(verbose=False, force=False):
     return HOST_SO
 
 
+SANITIZERS = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "thread": ["-fsanitize=thread"]}
+
+
+def build_host_sanitized(kind: str, verbose=False) -> str:
+    """The host library compiled with AddressSanitizer + UBSan (``address``) or ThreadSanitizer (``thread``) into
+    ``build/host_<kind>/_gb200_host.so``.  Run the CPU tests against it with
+
+        GB200_HOST_SO=<that file> LD_PRELOAD=$(g++ -print-file-name=lib{a,t}san.so) python -m pytest tests -m "not gpu"
+
+    (the interpreter itself is not instrumented, so the sanitizer runtime has to be loaded first).  The compiler must
+    ship the runtime it links against: set ``CXX=/usr/bin/g++`` when the default one is a wrapper without it."""
+    import pybind11
+    if kind not in SANITIZERS:
+        raise ValueError("sanitizer must be one of " + ", ".join(SANITIZERS))
+    out_dir = os.path.join(BUILD, "host_" + kind)
+    os.makedirs(out_dir, exist_ok=True)
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + ["-O1", "-g", "-fno-omit-frame-pointer"] + SANITIZERS[kind]
+    inc = ["-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], "-I" + os.path.join(CSRC, "host")]
+    hdrs = _headers("host")
+    jobs, objs = [], []
+    for s in _sources("host", ".cpp"):
+        o = os.path.join(out_dir, os.path.basename(s) + ".o")
+        objs.append(o)
+        if _newer([s] + hdrs, o):
+            jobs.append([CXX] + flags + inc + ["-c", s, "-o", o])
+    with cf.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
+        for out in ex.map(_run, jobs):
+            if verbose and out.strip():
+                print(out)
+    target = os.path.join(out_dir, "_gb200_host.so")
+    if jobs or not os.path.exists(target):
+        _link([CXX, "-shared"] + SANITIZERS[kind], target, objs + ["-pthread"])
+    return target
+
+
 def build_cuda(verbose=False, force=False):
     os.makedirs(os.path.join(BUILD, "cuda"), exist_ok=True)
     srcs = _sources("cuda", ".cu")
@@ -145,5 +180,8 @@ def ptxas_report():
 
 
 if __name__ == "__main__":
-    force = "--force" in sys.argv
-    print(build_all(verbose="-v" in sys.argv, force=force))
+    if "--sanitize" in sys.argv:
+        print(build_host_sanitized(sys.argv[sys.argv.index("--sanitize") + 1], verbose="-v" in sys.argv))
+    else:
+        force = "--force" in sys.argv
+        print(build_all(verbose="-v" in sys.argv, force=force))

@@ -89,8 +89,11 @@ class Suite:
 
     def call(self, fn: Callable[[List[str]], int], argv: List[str]) -> Tuple[int, str]:
         """Run a command-line entry point in-process; returns (exit code, everything it printed)."""
+        from ..utils import log as LOG
         buf = io.StringIO()
         rc = 0
+        level = LOG.log_level()
+        LOG.set_log_level(LOG.INFO)                     # the gates read step lines and resume messages
         with contextlib.redirect_stdout(buf), contextlib.redirect_stderr(buf):
             try:
                 rc = fn(argv)
@@ -101,6 +104,8 @@ class Suite:
             except Exception as e:                                   # a crash is a failed gate, not a crashed suite
                 rc = 99
                 print("%s: %s" % (type(e).__name__, e))
+            finally:
+                LOG.set_log_level(level)
         text = buf.getvalue()
         self.logs.append(text)
         return int(rc or 0), text

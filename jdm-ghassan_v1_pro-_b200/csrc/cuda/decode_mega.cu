@@ -70,8 +70,7 @@ struct GridBar {
 __device__ __forceinline__ bool grid_sync(GridBar& gb) {
   __syncthreads();
   if (threadIdx.x == 0 && !*gb.dead) {
-    __threadfence();
-    atomicAdd(gb.cnt, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(gb.cnt), "r"(1u) : "memory");
     unsigned it = 0;
     unsigned long long t0 = 0;
     for (;;) {
@@ -245,10 +244,21 @@ __device__ __forceinline__ void run_phase(const Phase& ph, const Plan& pl, const
 template <typename XT>
 __device__ __forceinline__ void block_norm(const float* x, const float* __restrict__ w, XT* xs, int d, float eps, float* red) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // d <= 4 * THREADS * 2: at most two float4 per thread, read once and kept
+  float4 v[2];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d / 4; i += THREADS) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + i);
-    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < d / 4) v[k] = __ldcg(reinterpret_cast<const float4*>(x) + i);
+    ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  }
+  float4 g[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    g[k] = i < d / 4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   ss = warp_sum(ss);
   if (lane == 0) red[warp] = ss;
@@ -258,13 +268,15 @@ __device__ __forceinline__ void block_norm(const float* x, const float* __restri
   for (int i = 0; i < WARPS; ++i) tot += red[i];
   float inv = rsqrtf(tot / (float)d + eps);
   if (!isfinite(inv)) inv = 0.f;
-  for (int i = threadIdx.x; i < d / 4; i += THREADS) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + i);
-    const float4 g = reinterpret_cast<const float4*>(w)[i];
-    uint2 o;
-    o.x = Cvt<XT>::pack2(v.x * inv * g.x, v.y * inv * g.y);
-    o.y = Cvt<XT>::pack2(v.z * inv * g.z, v.w * inv * g.w);
-    *reinterpret_cast<uint2*>(xs + 4 * i) = o;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    if (i < d / 4) {
+      uint2 o;
+      o.x = Cvt<XT>::pack2(v[k].x * inv * g[k].x, v[k].y * inv * g[k].y);
+      o.y = Cvt<XT>::pack2(v[k].z * inv * g[k].z, v[k].w * inv * g[k].w);
+      *reinterpret_cast<uint2*>(xs + 4 * i) = o;
+    }
   }
   __syncthreads();
 }
@@ -414,20 +426,21 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
       if (a.window <= 0 || j == slot_new) return true;
       return s.abs_pos - a.slot_pos[j] < a.window;
     };
-    for (int j = lo + warp; j < hi; j += 2 * WARPS) {
-      const int j1 = j + WARPS;
-      const bool v0 = live(j), v1 = live(j1);
-      float k0[4], w0[4], k1[4], w1[4];
-      if (v0) {
-        ld_epl<XT>(cK + (size_t)j * kvd + (size_t)kvh * hd + lane * epl, epl, k0);
-        ld_epl<XT>(cV + (size_t)j * kvd + (size_t)kvh * hd + lane * epl, epl, w0);
+    for (int j = lo + warp; j < hi; j += 4 * WARPS) {
+      bool ok[4];
+      float kf[4][4], vf[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int ju = j + u * WARPS;
+        ok[u] = live(ju);
+        if (ok[u]) {
+          ld_epl<XT>(cK + (size_t)ju * kvd + (size_t)kvh * hd + lane * epl, epl, kf[u]);
+          ld_epl<XT>(cV + (size_t)ju * kvd + (size_t)kvh * hd + lane * epl, epl, vf[u]);
+        }
       }
-      if (v1) {
-        ld_epl<XT>(cK + (size_t)j1 * kvd + (size_t)kvh * hd + lane * epl, epl, k1);
-        ld_epl<XT>(cV + (size_t)j1 * kvd + (size_t)kvh * hd + lane * epl, epl, w1);
-      }
-      if (v0) visit(k0, w0);
-      if (v1) visit(k1, w1);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (ok[u]) visit(kf[u], vf[u]);
     }
     // the sixteen warps meet in shared memory, in warp order
 #pragma unroll
@@ -467,17 +480,15 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
   const int hd = a.hd, st = hd + 2;
   for (int h = warp; h < a.H; h += WARPS) {
     const float* base = a.att_scratch + (size_t)h * S * st;
-    float ml = -INFINITY;
-    for (int s = lane; s < S; s += 32) ml = fmaxf(ml, __ldcg(base + (size_t)s * st));
-    const float M = warp_max(ml);
-    float ls = 0.f;
-    for (int s = lane; s < S; s += 32) {
-      const float ms = __ldcg(base + (size_t)s * st);
-      const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
-      ftab[h * S + s] = f;
-      ls += __ldcg(base + (size_t)s * st + 1) * f;
-    }
-    ls = warp_sum(ls);
+    // S <= 64: at most two splits per lane, (max, sum) read once
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (lane < S) { const float2 t = __ldcg(reinterpret_cast<const float2*>(base + (size_t)lane * st)); m0 = t.x; l0 = t.y; }
+    if (lane + 32 < S) { const float2 t = __ldcg(reinterpret_cast<const float2*>(base + (size_t)(lane + 32) * st)); m1 = t.x; l1 = t.y; }
+    const float M = warp_max(fmaxf(m0, m1));
+    const float f0 = m0 == -INFINITY ? 0.f : __expf(m0 - M), f1 = m1 == -INFINITY ? 0.f : __expf(m1 - M);
+    if (lane < S) ftab[h * S + lane] = f0;
+    if (lane + 32 < S) ftab[h * S + lane + 32] = f1;
+    const float ls = warp_sum(l0 * f0 + l1 * f1);
     if (lane == 0) sm.linv[h] = ls;
   }
   __syncthreads();
@@ -485,7 +496,7 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
     const int h = c / hd, cc = c - h * hd;
     const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
     float oo = 0.f;
-#pragma unroll 4
+#pragma unroll 16
     for (int s = 0; s < S; ++s) oo += __ldcg(base + (size_t)s * st) * ftab[h * S + s];
     const float ll = sm.linv[h];
     xs[c] = Cvt<XT>::from_f(ll > 0.f ? oo / ll : 0.f);
@@ -589,10 +600,16 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   XT* qkv = reinterpret_cast<XT*>(a.qkv);
   XT* act = reinterpret_cast<XT*>(a.act);
 
-  // number of cache splits: about 128 slots per CTA, at most what the grid and the scratch hold
+  // number of cache splits: about 64 slots per CTA (four per warp, fetched in one trip), at most what the grid and
+  // the scratch hold
   const gb_seq_state s0 = a.state[0];
   const int n_slots = min(a.cap, s0.cache_len + 1);
-  const int S = max(1, min(min(a.max_splits, (int)gridDim.x / a.KV), (n_slots + 127) / 128));
+  const int S = max(1, min(min(a.max_splits, (int)gridDim.x / a.KV), (n_slots + 63) / 64));
+
+  // optional trace: CTA 0 records the global timer before and after every barrier (10 marks per layer + start and end)
+  unsigned long long* prof = (blockIdx.x == 0 && threadIdx.x == 0) ? a.prof : nullptr;
+  auto mark = [&]() { if (prof) *prof++ = globaltimer_ns(); };
+  mark();
 
   uint4 cur[GROUP];
   bool ok = true;
@@ -611,19 +628,25 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, [&](int o) { return (long long)o * rb_d; },
                          [&](int o, float v, float) { qkv[o] = Cvt<XT>::from_f(v); });
     }
+    mark();
     if (!(ok = grid_sync(gb))) break;
+    mark();
     // ---- B: attention over the cache (a few CTAs); the others go straight on to fetch their rows of wo
     attention_phase<XT>(a, L, S, sm, amerge);
     Phase phC{reinterpret_cast<const uint8_t*>(L.wo), nullptr, nullptr, nsu_q, nsu_q, false, false};
     const Plan plC = make_plan(d, nsu_q);
     auto rowC = [&](int o) { return (long long)o * rb_q; };
     preload<FMT>(phC, plC, rowC, cur);
+    mark();
     if (!(ok = grid_sync(gb))) break;
+    mark();
     // ---- C: merge of the splits + output projection + residual
     merge_phase<XT>(a, S, sm, ftab, xs);
     run_phase<FMT, XT>(phC, plC, xs, stage, sm.red, cur, rowC,
                        [&](int o, float v, float) { x_mid[o] = __ldcg(x_in + o) + v; });
+    mark();
     if (!(ok = grid_sync(gb))) break;
+    mark();
     // ---- D: RMSNorm + router + gate/up of the chosen experts + SwiGLU
     {
       block_norm<XT>(x_mid, L.ffn_norm, xs, d, a.eps, sm.red[0]);
@@ -648,7 +671,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     const Plan plE = make_plan(d, phE.P);
     auto rowE = [&](int o) { return (long long)o * rb_E; };
     preload<FMT>(phE, plE, rowE, cur);
+    mark();
     if (!(ok = grid_sync(gb))) break;
+    mark();
     for (int i = threadIdx.x; i < slots * E / 8; i += THREADS)
       reinterpret_cast<uint4*>(xs)[i] = __ldcg(reinterpret_cast<const uint4*>(act) + i);
     __syncthreads();
@@ -666,7 +691,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       preload<FMT>(ph, make_plan(a.V, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
       head_pre = true;
     }
+    mark();
     if (!(ok = grid_sync(gb))) break;
+    mark();
     x_in = x_out;
     if (last) {
       // ---- final norm + vocabulary projection
@@ -676,6 +703,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       else head_phase<GB_W_BF16, XT>(a, xs, stage, sm, cur, false);
     }
   }
+  mark();
   // ---- bookkeeping: the last CTA out records where the arrival count stands; CTA 0 advances the sequence state
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -720,6 +748,7 @@ extern "C" int gb_decode_mega_ok(const gb_mega_args* a) {
   if (a->ne > 64 || a->ne < 0 || (a->ne > 0 && (a->top_k < 1 || a->top_k > 8 || a->top_k > a->ne))) return -4;
   if (a->fmt < GB_W_F16 || a->fmt > GB_W_Q4_1) return -5;
   if (a->head_fmt != a->fmt && a->head_fmt != GB_W_F16 && a->head_fmt != GB_W_BF16) return -5;
+  if (a->d > 8 * mg::THREADS || a->max_splits > 64) return -6;
   if (a->max_splits < 1 || a->cap < 1 || a->pinned < 0 || a->pinned >= a->cap) return -6;
   if (mg::dyn_bytes(*a) > 200 * 1024) return -7;
   return 0;

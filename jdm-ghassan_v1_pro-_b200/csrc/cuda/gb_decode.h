@@ -126,6 +126,9 @@ typedef struct gb_mega_args {
   int* r_idx; float* r_w;                        // router choice of the last layer (may be NULL)
   unsigned* sync;                                // 4 words, zero before the first launch, owned by the kernel afterwards
   int* status;                                   // set to 401 when a grid-wide wait ran out
+  unsigned long long* prof;                      // NULL, or 10 * n_layers + 2 words: CTA 0's global-timer marks in
+                                                 // nanoseconds (start; per layer the end of a phase and the start of
+                                                 // the next, i.e. both sides of each of the five barriers; end)
 } gb_mega_args;
 int gb_decode_mega_ok(const gb_mega_args* a);    // 0 when the shapes are covered, else a negative code
 int gb_decode_mega_grid(void);                   // CTAs of the launch (one per SM)

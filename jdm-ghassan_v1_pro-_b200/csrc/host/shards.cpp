@@ -182,7 +182,7 @@ bool ShardFile::open(const std::string& path, std::string* why) {
   wide_ = dtype == 1;
   if (wide_) tok32_ = reinterpret_cast<const u32*>(base + 32);
   else tok16_ = reinterpret_cast<const u16*>(base + 32);
-  docs_ = reinterpret_cast<const u64*>(base + 32 + tok_bytes);
+  docs_ = base + 32 + tok_bytes;
   if (flags & 1u) mask_ = base + 32 + tok_bytes + nd * 8;
   n_tokens_ = nt;
   n_docs_ = nd;
@@ -193,7 +193,7 @@ bool ShardFile::open(const std::string& path, std::string* why) {
     u64 prev = 0;
     for (u64 d = 0; d < nd; ++d) {
       u64 v;
-      std::memcpy(&v, reinterpret_cast<const u8*>(docs_) + d * 8, 8);
+      std::memcpy(&v, docs_ + d * 8, 8);
       if ((d == 0 && v != 0) || (d > 0 && v <= prev) || v >= nt) return bad("bad document offsets");
       prev = v;
     }
@@ -209,9 +209,13 @@ bool ShardFile::open(const std::string& path, std::string* why) {
 
 u64 ShardFile::doc_end_after(u64 i) const {
   if (n_docs_ == 0) return n_tokens_;
-  const u64* end = docs_ + n_docs_;
-  const u64* it = std::upper_bound(docs_, end, i);
-  return it == end ? n_tokens_ : *it;
+  u64 lo = 0, hi = n_docs_;                  // first document whose start is > i
+  while (lo < hi) {
+    const u64 mid = lo + (hi - lo) / 2;
+    if (doc_at(mid) <= i) lo = mid + 1;
+    else hi = mid;
+  }
+  return lo == n_docs_ ? n_tokens_ : doc_at(lo);
 }
 
 std::vector<std::string> list_shards(const std::string& dir, const std::string& prefix) {

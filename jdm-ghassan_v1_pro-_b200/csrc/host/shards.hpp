@@ -7,6 +7,7 @@
 // training/dataloader.cpp:117-153, 475-756), so a (seed, batch index) pair names the same batch in
 // both engines and checkpoints carry over.
 #pragma once
+#include <cstring>
 #include <map>
 #include <memory>
 #include <string>
@@ -55,7 +56,7 @@ class ShardFile {
   bool has_mask() const { return mask_ != nullptr; }
   i32 token(u64 i) const { return wide_ ? static_cast<i32>(tok32_[i]) : static_cast<i32>(tok16_[i]); }
   u8 mask(u64 i) const { return mask_ ? mask_[i] : 1; }
-  u64 doc_start(u64 d) const { return d < n_docs_ ? docs_[d] : 0; }
+  u64 doc_start(u64 d) const { return d < n_docs_ ? doc_at(d) : 0; }
   // first document boundary strictly after position i (n_tokens when i is in the last document)
   u64 doc_end_after(u64 i) const;
 
@@ -68,7 +69,13 @@ class ShardFile {
   bool wide_ = false;
   const u16* tok16_ = nullptr;
   const u32* tok32_ = nullptr;
-  const u64* docs_ = nullptr;
+  // the offsets follow the token array, so they sit on a 2- or 4-byte boundary: read them byte-wise
+  u64 doc_at(u64 d) const {
+    u64 v;
+    std::memcpy(&v, docs_ + d * 8, 8);
+    return v;
+  }
+  const u8* docs_ = nullptr;
   const u8* mask_ = nullptr;
 };
 

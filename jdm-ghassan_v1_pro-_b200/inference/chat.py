@@ -92,8 +92,8 @@ class ChatOptions:
 
 
 class ChatSession:
-    def __init__(self, gen: Generator, opts: Optional[ChatOptions] = None, out=sys.stdout):
-        self.gen, self.o, self.out = gen, opts or ChatOptions(), out
+    def __init__(self, gen: Generator, opts: Optional[ChatOptions] = None, out=None):
+        self.gen, self.o, self.out = gen, opts or ChatOptions(), (sys.stdout if out is None else out)
         if self.o.max_history_turns < 0 or self.o.retrieve_top_k < 0 or self.o.max_new_tokens < 0:
             raise ValueError("chat options must be non-negative")
         self.english = self.o.persona in ("en", "english")
@@ -175,7 +175,8 @@ class ChatSession:
         self.history.append(T.Message("assistant", reply))
         return reply
 
-    def run_repl(self, inp=sys.stdin):
+    def run_repl(self, inp=None):
+        inp = sys.stdin if inp is None else inp          # looked up at call time: callers may have replaced it
         w = lambda s="": print(s, file=self.out, flush=True)
         w("\n  Ghassan AI - chat" + (" (English)" if self.english else ""))
         w("  Type your message. Commands: /help /clear /system <text> /temp <f> /stats /quit" if self.english else

@@ -76,15 +76,22 @@ class InferenceEngine:
     def __init__(self, cfg: ModelConfig, named: Dict[str, np.ndarray], fmt: str = "f16", batch: int = 1,
                  max_len: int = 2048, prefill_chunk: int = 1024, moe_bias: Optional[Sequence] = None, device=None,
                  compute_dtype=torch.float16, keep_f16_embeddings: bool = True, raw=None, raw_types=None,
-                 fused_step: bool = True, single_kernel: Optional[bool] = None):
+                 fused_step: bool = True, single_kernel: Optional[bool] = None, gemm_min_batch: Optional[int] = None):
         """``named``: fp32 tensors by parameter name.  ``fmt``: decode weight format, or "auto" with ``raw`` (an object
         with ``tensor_raw(name)``, e.g. a GGUF file) and ``raw_types`` (name -> ggml type) to take the stored bytes.
         ``single_kernel``: run the token step of a batch of one as one cooperative kernel (``csrc/cuda/decode_mega.cu``)
-        when the shapes allow it; None takes the default (``GB200_DECODE_MEGA``)."""
+        when the shapes allow it; None takes the default (``GB200_DECODE_MEGA``).  ``gemm_min_batch``: from this many
+        sequences on, the token step runs its projections and experts as tensor-core GEMMs over 16-bit copies of the
+        weights (the ones the prompt pass keeps) instead of per-sequence GEMV kernels over the stored bytes; None
+        takes ``GB200_DECODE_GEMM_MIN_BATCH`` (default 8), 0 turns it off."""
         cfg.validate()
         if cfg.head_dim not in (32, 64, 128):
             raise ValueError("decode attention supports head_dim 32, 64 and 128")
-        self.cfg, self.B, self.cap = cfg, batch, max_len
+        self.cfg, self.B, self.cap, self.pinned = cfg, batch, max_len, PINNED_TOKENS
+        if gemm_min_batch is None:
+            gemm_min_batch = int(os.environ.get("GB200_DECODE_GEMM_MIN_BATCH", "8") or 0)
+        self.batched = gemm_min_batch > 0 and batch >= gemm_min_batch
+        self._step_model: Optional[CudaModel] = None
         # eight launches per layer instead of eleven (both norms and the cache append folded into their consumers);
         # the separate kernels remain for shapes whose rows do not fit the shared-memory budget
         self.fused = (bool(fused_step) and os.environ.get("GB200_DECODE_UNFUSED", "") != "1"
@@ -243,6 +250,32 @@ class InferenceEngine:
         if grid > 0 and D.mega_ok(a) == 0:
             self.mega = a
 
+    def trace_phases(self, n_tokens: int = 16) -> Dict[str, float]:
+        """Mean microseconds that CTA 0 of the one-kernel step spends in each phase of a layer and at the barrier
+        behind it, over ``n_tokens`` eager steps from the current state (the marks come from the device's global
+        timer).  Keys: A (norm + QKV), B (attention), C (merge + output projection), D (norm + router + gate/up), E
+        (down projection), ``wait_X`` for the barrier after phase X, ``head`` and ``step``."""
+        assert self.mega is not None, "the one-kernel token step is not in use"
+        nl = self.cfg.num_layers
+        buf = torch.zeros(10 * nl + 2, dtype=torch.int64, device=self.dev)
+        self.mega.prof = buf.data_ptr()
+        acc = np.zeros(10 * nl + 1)
+        try:
+            for _ in range(n_tokens):
+                self._forward_token()
+                torch.cuda.synchronize()
+                acc += np.diff(buf.cpu().numpy().astype(np.float64))
+        finally:
+            self.mega.prof = None
+        acc /= n_tokens * 1e3
+        per = acc[:10 * nl].reshape(nl, 10)              # A, wait, B, wait, C, wait, D, wait, E, wait
+        names = ["A", "wait_A", "B", "wait_B", "C", "wait_C", "D", "wait_D", "E", "wait_E"]
+        out = {k: float(per[:, i].mean()) for i, k in enumerate(names)}
+        out["layer"] = float(per.sum(1).mean())
+        out["head"] = float(acc[10 * nl])
+        out["step"] = float(acc.sum())
+        return out
+
     # ------------------------------------------------------------------ one decode step (captured)
     def _layer_step(self, L: _Layer, x_in, x_out):
         cfg = self.cfg
@@ -300,6 +333,10 @@ class InferenceEngine:
         cfg = self.cfg
         if self.mega is not None:
             D.decode_mega(self.mega)
+            return
+        if self.batched:
+            self._step_net().decode_forward(self)
+            D.decode_advance(self.state, self.pos, self.cap, PINNED_TOKENS)
             return
         K.embed_fwd(self.cur_tok, self.emb, self.x[0])
         for i, L in enumerate(self.layers):
@@ -370,8 +407,19 @@ class InferenceEngine:
         if self._prefill_model is None:
             m = CudaModel(self.cfg, self.B, self.prefill_chunk, self.dt, self.dev, ce_chunks=1, use_segments=False, train=False)
             m.load_named(self._named)
+            if m.moe_bias is not None:                     # selection bias of aux-free balancing, as the token step uses it
+                for i, L in enumerate(self.layers):
+                    if getattr(L, "bias", None) is not None:
+                        m.moe_bias[i].copy_(L.bias)
             self._prefill_model = m
         return self._prefill_model
+
+    def _step_net(self) -> CudaModel:
+        """Activation buffers for one token per sequence over the prompt model's weights (tensor-core token step)."""
+        if self._step_model is None:
+            self._step_model = CudaModel(self.cfg, self.B, 1, self.dt, self.dev, ce_chunks=1, use_segments=False, train=False,
+                                         share_weights=self._prefill_net())
+        return self._step_model
 
     def prefill(self, prompts: torch.Tensor):
         """``prompts``: int32 [B, n] (same length for every sequence).  The first ``prefill_chunk`` tokens go through

@@ -185,9 +185,11 @@ class CudaModel:
     """Parameters, activations and the forward/backward schedule for a fixed micro-batch shape (B, T)."""
 
     def __init__(self, cfg: ModelConfig, B: int, T: int, dtype=torch.float16, device=None, ce_chunks: int = 4,
-                 use_segments: bool = False, train: bool = True, micro_tokens: int = 0):
+                 use_segments: bool = False, train: bool = True, micro_tokens: int = 0, share_weights=None):
         """``micro_tokens``: when the B x T rows are several of the recipe's micro-batches concatenated, the size of
-        one of them; the MoE balance statistics and the router jitter then stay per micro-batch."""
+        one of them; the MoE balance statistics and the router jitter then stay per micro-batch.  ``share_weights``:
+        another (inference) model of the same configuration whose parameter buffers this one uses instead of
+        allocating its own: a second activation shape over one set of weights."""
         cfg.validate()
         if cfg.head_dim not in (32, 64, 128, 256):
             raise ValueError(f"head_dim {cfg.head_dim} is not supported on the CUDA path (32/64/128/256)")
@@ -203,12 +205,19 @@ class CudaModel:
         self.layout = ParamLayout(cfg)
         L = self.layout
         f32 = dict(dtype=torch.float32, device=self.dev)
-        self.P = torch.zeros(L.total, **f32)                # fp32 master weights
-        self.W16 = torch.zeros(L.total, dtype=dtype, device=self.dev)   # 16-bit shadows (GEMM operands)
+        if share_weights is not None:
+            if train or share_weights.layout.total != L.total or share_weights.dtype != dtype:
+                raise ValueError("share_weights needs an inference model of the same configuration and dtype")
+            self.P, self.W16 = share_weights.P, share_weights.W16
+        else:
+            self.P = torch.zeros(L.total, **f32)                # fp32 master weights
+            self.W16 = torch.zeros(L.total, dtype=dtype, device=self.dev)   # 16-bit shadows (GEMM operands)
         self.Gr = torch.zeros(L.total, **f32) if train else None        # fp32 gradients
         self.moe_bias = None
         self.bias_counts = None
-        if cfg.use_moe and cfg.moe_aux_free:
+        if share_weights is not None:
+            self.moe_bias = share_weights.moe_bias
+        elif cfg.use_moe and cfg.moe_aux_free:
             self.moe_bias = torch.zeros(cfg.num_layers, cfg.num_experts, **f32)
         if cfg.use_moe and train:
             # routed slots per (layer, expert) of the current step: balancing input (aux-free) and expert-load report
@@ -355,6 +364,24 @@ class CudaModel:
         G.gemm(b.xb, self.w16(p + "wqkv"), out=b.qkv)
         qw = self.w(p + "qk_qnorm") if cfg.use_qk_norm else None
         kw = self.w(p + "qk_knorm") if cfg.use_qk_norm else None
+        dec = getattr(self, "decode_engine", None)
+        if dec is not None:    # token step of the inference engine (T == 1): this token's k/v go into the cache, the
+            #                    query attends over the cache; everything else in this layer is the batched pass
+            from ..ops import decode as D
+            Lc = dec.layers[l]
+            D.qk_rope_append(b.qkv, b.qk, qw, kw, dec.cos_sin, dec.pos, Lc.cK, Lc.cV, dec.slot_pos, dec.state, H, KV, hd,
+                             dec.cap, dec.pinned, cfg.rms_eps, cfg.rope_type)
+            D.decode_attn(b.qk[:, :qd], Lc.cK, Lc.cV, dec.slot_pos, dec.state, b.att, dec.att_scratch, dec.splits, H, KV, hd,
+                          dec.cap, cfg.sliding_window, cfg.attn_scale())
+        else:
+            self._attention_forward(l, b, qw, kw)
+        G.gemm(b.att, self.w16(p + "wo"), out=b.x_mid, addend=x_in)
+        K.rmsnorm_fwd(b.x_mid, self.w(p + "ffn_norm"), b.xb2, b.rrms2, cfg.rms_eps)
+        self._ffn_forward(l, p, b, x_out, train, want_aux)
+
+    def _attention_forward(self, l: int, b: _LayerBuf, qw, kw):
+        cfg = self.cfg
+        qd, kvd, H, KV, hd = cfg.q_dim, cfg.kv_dim, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         K.qk_norm_rope_fwd(b.qkv, b.qk, qw, kw, self.cos_sin, self.pos, H, KV, hd, cfg.rms_eps, cfg.rope_type)
         sink = getattr(self, "kv_sink", None)
         if sink is not None:   # prompt pass of the inference engine: keep this layer's keys (after RoPE) and values
@@ -367,8 +394,10 @@ class CudaModel:
         else:
             K.attn_fwd(b.qk[:, :qd], b.qk[:, qd:], b.qkv[:, qd + kvd:], b.att, b.lse, self._seg(), self.B, self.T, H,
                        KV, hd, cfg.sliding_window, cfg.attn_scale())
-        G.gemm(b.att, self.w16(p + "wo"), out=b.x_mid, addend=x_in)
-        K.rmsnorm_fwd(b.x_mid, self.w(p + "ffn_norm"), b.xb2, b.rrms2, cfg.rms_eps)
+
+    def _ffn_forward(self, l: int, p: str, b: _LayerBuf, x_out, train: bool, want_aux: bool):
+        cfg = self.cfg
+        d, E = cfg.hidden_size, self.layout.Eff
         if cfg.use_moe and self.ep is not None:     # experts divided among the ranks (parallel/expert_parallel.py)
             self.ep.forward(l, b, x_out, train, want_aux)
         elif cfg.use_moe:
@@ -386,6 +415,23 @@ class CudaModel:
         else:
             G.gemm_swiglu(b.xb2, self.w16(p + "w_gu"), act_out=b.act, gu_out=b.gu if train else None)
             G.gemm(b.act, self.w16(p + "w_down"), out=x_out, addend=b.x_mid)
+
+    def decode_forward(self, eng):
+        """One token per sequence for the inference engine ``eng`` (this model has T == 1 and B == eng.B): embedding of
+        ``eng.cur_tok``, all layers with the projections and experts on the tensor cores and the attention over the
+        engine's cache, final norm, fp32 logits into ``eng.logits``.  Reads every weight once for the whole batch,
+        where the per-sequence GEMV kernels read it once per four sequences."""
+        cfg = self.cfg
+        assert self.T == 1 and self.B == eng.B
+        self.decode_engine = eng
+        try:
+            K.embed_fwd(eng.cur_tok, self.w("tok_embeddings"), self.x[0])
+            for l in range(cfg.num_layers):
+                self._layer_forward(l, self.x[l % 2], self.x[(l + 1) % 2], self.layers[0], False, False)
+        finally:
+            self.decode_engine = None
+        K.rmsnorm_fwd(self.x[cfg.num_layers % 2], self.w("final_norm"), self.h16, self.rrms_f, cfg.rms_eps)
+        G.gemm(self.h16, self._head_weight16(), out=eng.logits, block_n=256 if cfg.vocab_size >= 4096 else 0)
 
     def _head_weight16(self):
         return self.w16("tok_embeddings") if self.cfg.tie_embeddings else self.w16("lm_head")

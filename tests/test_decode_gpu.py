@@ -132,9 +132,9 @@ def test_kv_ring_and_decode_attention(hd, H, KV):
         vs.append(v)
         D.kv_append(k, v, cK, cV, slot_pos, state, cap, pinned)
         D.decode_attn(q, cK, cV, slot_pos, state, out, scratch, 4, H, KV, hd, cap, 0, scale)
-        # the variant whose last split merges the partial results gives the same bits
+        # the variant whose last split merges the partial results agrees up to the order of the sums over the splits
         D.decode_attn_fused(q, cK, cV, slot_pos, state, out_t, scratch_t, ticket, 4, H, KV, hd, cap, 0, scale)
-        assert torch.equal(out, out_t) and int(ticket.abs().sum()) == 0
+        assert torch.allclose(out.float(), out_t.float(), rtol=2e-3, atol=2e-3) and int(ticket.abs().sum()) == 0
         D.decode_advance(state, pos, cap, pinned)
         # the cache must hold the first `pinned` tokens and the most recent cap - pinned ones
         live = list(range(min(t + 1, pinned))) + [j for j in range(max(pinned, t + 1 - (cap - pinned)), t + 1)]
@@ -507,3 +507,37 @@ def test_single_kernel_barrier_wait_runs_out_with_a_status():
     torch.cuda.synchronize()
     _lib.check_status(what="step after the expired wait")
     assert int(eng.state[0, 0]) == before[0][0] + 1 and bool(torch.isfinite(eng.logits).all())
+
+
+@pytest.mark.parametrize("moe,fmt,B", [(True, "f16", 3), (True, "q4_0", 8), (False, "q8_0", 5)])
+def test_tensor_core_token_step_matches_gemv_chain(moe, fmt, B):
+    """Batches from ``gemm_min_batch`` sequences on run the token step's projections and experts as GEMMs over the
+    16-bit weights; against the per-sequence GEMV kernels over the same (fp16) or the quantised stored bytes."""
+    from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
+    from ghassan_b200.models.config import init_parameters
+    cfg = _tiny_cfg(use_moe=moe, moe_aux_free=moe, moe_aux_scale=0.0 if moe else 0.01)
+    named = init_parameters(cfg, 31)
+    bias = [np.linspace(-0.02, 0.02, cfg.num_experts).astype(np.float32) for _ in range(cfg.num_layers)] if moe else None
+    gemm = InferenceEngine(cfg, named, fmt=fmt, batch=B, max_len=48, prefill_chunk=32, moe_bias=bias, gemm_min_batch=2)
+    gemv = InferenceEngine(cfg, named, fmt="f16", batch=B, max_len=48, prefill_chunk=32, moe_bias=bias, gemm_min_batch=0)
+    assert gemm.batched and not gemv.batched
+    seq = torch.randint(16, 512, (B, 60), generator=torch.Generator().manual_seed(9), dtype=torch.int32)
+    for e in (gemm, gemv):
+        e.reset(1)
+    for j in range(60):                                  # longer than the cache: the ring wraps
+        for e in (gemm, gemv):
+            e.cur_tok.copy_(seq[:, j])
+            e._forward_token()
+        scale = float(gemv.logits.abs().max())
+        err = float((gemm.logits - gemv.logits).abs().max())
+        assert err <= 1e-2 * max(1.0, scale), (j, err, scale)
+    assert gemm.state.cpu().tolist() == gemv.state.cpu().tolist() and torch.equal(gemm.slot_pos, gemv.slot_pos)
+    for La, Lb in zip(gemm.layers, gemv.layers):
+        assert torch.allclose(La.cK.float(), Lb.cK.float(), atol=3e-2) and torch.allclose(La.cV.float(), Lb.cV.float(), atol=3e-2)
+    sp = SamplingParams(seed=4, top_k=20)
+    gemm.reset(1)
+    gemm.prefill(seq[:, :9].contiguous())
+    gemm.sample_first(sp)
+    gemm.decode_steps(12, sp)                             # through the captured graph
+    out = np.asarray(gemm.transcript(13))
+    assert out.shape == (B, 13) and int(gemm.state[0, 0]) == 9 + 12
