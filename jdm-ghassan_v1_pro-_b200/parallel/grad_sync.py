@@ -112,6 +112,19 @@ class FusedGradSync:
         self.barrier_epoch = 0
         self.lo = self.rank * self.shard
         self.hi = min(self.total, self.lo + self.shard)
+        # ZeRO-1 for real: only the owner ever touches the moments of a shard, so only the owner keeps them.  The
+        # kernels index moments by global element, so they get the shard's address moved back by the shard's offset.
+        self.m_own = self.v_own = None
+        opt = engine.optimizer
+        if self.world > 1 and opt.kind != "muon":
+            own = slice(self.lo, self.hi)
+            self.m_own = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+            self.m_own[:self.hi - self.lo].copy_(opt.m_flat[own])
+            opt.m_flat = None
+            if opt.v_flat is not None:
+                self.v_own = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+                self.v_own[:self.hi - self.lo].copy_(opt.v_flat[own])
+                opt.v_flat = None
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier()
@@ -128,8 +141,12 @@ class FusedGradSync:
         if opt.kind == "muon":           # norm and skip decision only; Muon itself runs after the gradient gather
             a.m, a.v, a.kind, a.hyper = None, None, 2, None
         else:
-            a.m = opt.m_flat.data_ptr()
-            a.v = opt.v_flat.data_ptr() if opt.v_flat is not None else None
+            if self.m_own is not None:
+                a.m = self.m_own.data_ptr() - 4 * self.lo
+                a.v = self.v_own.data_ptr() - 4 * self.lo if self.v_own is not None else None
+            else:
+                a.m = opt.m_flat.data_ptr()
+                a.v = opt.v_flat.data_ptr() if opt.v_flat is not None else None
             a.kind = 0 if opt.kind == "adamw" else 1
             a.hyper = lr_hyper.data_ptr()
         a.beta1, a.beta2, a.eps, a.wd = opt.beta1, opt.beta2, opt.eps, opt.weight_decay
@@ -185,7 +202,9 @@ class FusedGradSync:
 
     # ------------------------------------------------------------------ full state for checkpoints
     def gather_full_state(self):
-        """Complete the master weights and moments on every rank (collective: all ranks must call it)."""
+        """Complete the master weights on every rank and the moments on rank 0, which writes the checkpoint
+        (collective: all ranks must call it).  The full moments live in ``optimizer.m_flat`` / ``v_flat`` until
+        :meth:`release_full_state`."""
         if self.world == 1:
             return
         opt = self.engine.optimizer
@@ -193,10 +212,30 @@ class FusedGradSync:
         if opt.kind == "muon":           # every rank ran the whole update: masters and state are complete already
             return
         dist.all_gather_into_tensor(self._P_pad, self._P_pad[own].clone())
-        for flat in (opt.m_flat, opt.v_flat, getattr(self.engine, "weight_ema", None)):
-            if flat is None:
+        for name, mine in (("m_flat", self.m_own), ("v_flat", self.v_own)):
+            if mine is None:
                 continue
-            pad = torch.zeros(self.shard * self.world, dtype=flat.dtype, device=flat.device)
-            pad[:self.total].copy_(flat)
+            pad = None
+            if self.rank == 0:
+                pad = torch.empty(self.shard * self.world, dtype=torch.float32, device=mine.device)
+            dist.gather(mine, list(pad.view(self.world, self.shard).unbind(0)) if self.rank == 0 else None, dst=0)
+            setattr(opt, name, pad[:self.total] if self.rank == 0 else None)
+        ema = getattr(self.engine, "weight_ema", None)
+        if ema is not None:
+            pad = torch.zeros(self.shard * self.world, dtype=ema.dtype, device=ema.device)
+            pad[:self.total].copy_(ema)
             dist.all_gather_into_tensor(pad, pad[own].clone())
-            flat.copy_(pad[:self.total])
+            ema.copy_(pad[:self.total])
+
+    def release_full_state(self):
+        """Drop the gathered copy of the moments (after the checkpoint snapshot was taken)."""
+        if self.m_own is not None:
+            self.engine.optimizer.m_flat = None
+            self.engine.optimizer.v_flat = None
+
+    def load_full_moments(self, m_full: torch.Tensor, v_full: Optional[torch.Tensor]):
+        """Resume: keep this rank's slice of moments read from a checkpoint (full, flat layout)."""
+        n = self.hi - self.lo
+        self.m_own[:n].copy_(m_full[self.lo:self.hi])
+        if self.v_own is not None and v_full is not None:
+            self.v_own[:n].copy_(v_full[self.lo:self.hi])

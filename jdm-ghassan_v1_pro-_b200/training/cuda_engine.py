@@ -308,6 +308,11 @@ class CudaEngine:
         if self.grad_sync is not None:
             self.grad_sync.gather_full_state()
 
+    def finish_export(self):
+        """After the snapshot was captured: drop what prepare_export() gathered only for it."""
+        if self.grad_sync is not None:
+            self.grad_sync.release_full_state()
+
     def export_weights(self) -> List:
         named = self.model.export_named()
         return [(s.name, named[s.name]) for s in self.mcfg.param_specs()]
@@ -333,8 +338,12 @@ class CudaEngine:
         specs = self.mcfg.param_specs()
         if self.tcfg.optimizer == "muon":
             return opt.export_state()
+        if opt.m_flat is None:
+            raise RuntimeError("the moments are sharded over the ranks: prepare_export() must run first (rank 0 exports)")
         m_named = self.model.export_named(opt.m_flat)
         v_named = self.model.export_named(opt.v_flat) if opt.v_flat is not None else None
+        if self.grad_sync is not None:
+            self.grad_sync.release_full_state()
         return {"kind": opt.kind, "t": int(opt.t), "hyper": {k: float(v) for k, v in opt.hyper().items()},
                 "m": [m_named[s.name].reshape(-1) for s in specs],
                 "v": [v_named[s.name].reshape(-1) if v_named is not None else None for s in specs], "fmt": 1}
@@ -350,11 +359,18 @@ class CudaEngine:
             for i, s in enumerate(specs):
                 if blob["m"][i] is not None and blob["m"][i].size != s.numel:
                     return False
+            sharded = self.grad_sync is not None and self.grad_sync.m_own is not None
+            n = self.model.layout.total
+            m_flat = torch.zeros(n, dtype=torch.float32, device=self.device) if sharded else opt.m_flat
+            has_v = opt.kind == "adamw"
+            v_flat = (torch.zeros(n, dtype=torch.float32, device=self.device) if sharded else opt.v_flat) if has_v else None
             self.model.layout.to_internal({s.name: blob["m"][i].reshape(s.shape) for i, s in enumerate(specs)
-                                           if blob["m"][i] is not None}, opt.m_flat, missing_ok=True)
-            if opt.v_flat is not None:
+                                           if blob["m"][i] is not None}, m_flat, missing_ok=True)
+            if v_flat is not None:
                 self.model.layout.to_internal({s.name: blob["v"][i].reshape(s.shape) for i, s in enumerate(specs)
-                                               if blob["v"][i] is not None}, opt.v_flat, missing_ok=True)
+                                               if blob["v"][i] is not None}, v_flat, missing_ok=True)
+            if sharded:                  # every rank reads the whole state and keeps its own slice
+                self.grad_sync.load_full_moments(m_flat, v_flat)
         opt.t = int(blob["t"])
         h = blob["hyper"]
         opt.beta1, opt.beta2 = float(h["beta1"]), float(h["beta2"])

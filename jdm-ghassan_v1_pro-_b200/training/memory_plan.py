@@ -17,9 +17,11 @@ def memory_plan(m: ModelConfig, t: TrainerConfig, world: int = 1, fuse: int = 1)
     rows = N * (m.moe_top_k + int(m.moe_shared)) + 256 * (m.num_experts + 1) if m.use_moe else N   # segments padded to 256 rows
     weights = n * 4 + n * 2                       # fp32 master + 16-bit shadow
     grads = n * 4
-    moments = n * 4 * (2 if t.optimizer == "adamw" else 1)
-    # With the fused gradient sync each rank updates only its shard, but the buffers are allocated full-size (a
-    # checkpoint gathers them in place), so the per-GPU figure does not shrink with the world size.
+    moments_full = n * 4 * (2 if t.optimizer == "adamw" else 1)
+    # With the fused gradient exchange a rank keeps only the moments of the shard it updates (AdamW / Lion; Muon runs
+    # whole on every rank).  Rank 0 gathers them for the moment a checkpoint snapshot is taken.
+    sharded = world > 1 and getattr(t, "grad_sync", "fused") == "fused" and t.optimizer != "muon"
+    moments = (moments_full + world - 1) // world if sharded else moments_full
     per_layer = (N * d * 4 * 2                    # residual stream in and mid (fp32)
                  + N * d * 2 * 2                  # normalised activations (16-bit)
                  + N * (qd + 2 * kvd) * 2 + N * (qd + kvd) * 2 + N * qd * 2 + N * H * 4
@@ -29,7 +31,7 @@ def memory_plan(m: ModelConfig, t: TrainerConfig, world: int = 1, fuse: int = 1)
     head = chunk * ((m.vocab_size + 7) // 8 * 8) * 2 + N * d * 2
     temps = N * d * (4 + 2 * 3) + N * (2 * qd + 2 * kvd + qd + kvd) * 2 + rows * (2 * E + 2 * d) * 2
     acts = per_layer * m.num_layers + head + temps
-    ckpt = n * 4 + moments + 4096
+    ckpt = n * 4 + moments_full + 4096
     return {"parameters": n, "active_per_token": m.active_parameters_per_token(), "tokens_per_pass": N,
             "weights": weights, "gradients": grads, "optimizer": moments, "activations": acts,
             "total": weights + grads + moments + acts, "checkpoint_bytes": ckpt}

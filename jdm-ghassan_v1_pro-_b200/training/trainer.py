@@ -502,6 +502,9 @@ class Trainer:
         else:
             self.prefetch.quiesce()
             self.prefetch.start()
+        fin = getattr(self.engine, "finish_export", None)
+        if fin is not None:
+            fin()           # what prepare_export gathered only for the snapshot is dropped again
         if self.world > 1:
             dev = getattr(self.engine, "device", torch.device("cpu"))
             flag = ok.to(dev) if dev.type == "cuda" else ok

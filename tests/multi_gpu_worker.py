@@ -86,6 +86,8 @@ def run_engine(work, sync, steps=5, opt="adamw", extra=None):
     tr.engine.prepare_export()
     named = dict(tr.engine.export_weights())
     bias = tr.engine.export_moe_bias()
+    tr.moments = tr.engine.export_optimizer() if dist.get_rank() == 0 else None   # rank 0 writes checkpoints
+    tr.engine.finish_export()
     tr.prefetch.stop()
     return out, named, bias, tr
 
@@ -104,7 +106,29 @@ def parity(work):
         steps = 2 if opt == "adamw" else (3 if opt == "muon" else 5)
         a, wa, ba, tra = run_engine(work, "fused", steps=steps, opt=opt)
         assert tra.engine.grad_sync is not None, "fused path not taken"
-        b, wb, bb, _ = run_engine(work, "nccl", steps=steps, opt=opt)
+        b, wb, bb, trb = run_engine(work, "nccl", steps=steps, opt=opt)
+        if opt != "muon":
+            # the owner-only moments: a shard per rank while training, whole on rank 0 for the snapshot, and the same
+            # numbers as the replicated moments of the NCCL path; reading them back leaves every rank with its slice
+            gs = tra.engine.grad_sync
+            if gs.m_own is None or gs.m_own.numel() != gs.shard or tra.engine.optimizer.m_flat is not None:
+                print(rank, opt, "moments are not sharded", flush=True)
+                ok = False
+            if rank == 0:
+                for key in ("m", "v"):
+                    for x, y in zip(tra.moments[key], trb.moments[key]):
+                        if (x is None) != (y is None):
+                            ok = False
+                        elif x is not None and float(np.abs(x - y).max()) > 2e-2 * (float(np.abs(y).max()) + 1e-12):
+                            print(rank, opt, "moments differ", key, float(np.abs(x - y).max()), flush=True)
+                            ok = False
+            blob = [tra.moments]
+            dist.broadcast_object_list(blob, 0)
+            before = gs.m_own.clone()
+            gs.m_own.zero_()
+            if not tra.engine.import_optimizer(blob[0]) or not torch.equal(gs.m_own, before):
+                print(rank, opt, "moments did not survive export -> import", flush=True)
+                ok = False
         for (la, ga, na, apa), (lb, gb_, nb, apb) in zip(a, b):
             if na != nb or apa != apb or abs(la - lb) > 2e-3 * max(1.0, abs(lb)) or abs(ga - gb_) > 2e-2 * max(1e-3, abs(gb_)):
                 print(rank, opt, "step mismatch", (la, ga, na, apa), (lb, gb_, nb, apb), flush=True)

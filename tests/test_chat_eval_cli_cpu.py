@@ -205,8 +205,13 @@ def test_memory_plan_scales_with_sharding():
     m, t = ModelConfig.from_config(cfg), TrainerConfig.from_config(cfg)
     one, eight = memory_plan(m, t, 1, 16), memory_plan(m, t, 8, 16)
     assert one["parameters"] == m.count_parameters() == eight["parameters"]
-    assert eight["total"] == one["total"]                  # buffers are full-size on every rank; only the update is sharded
+    # moments live only on the rank that updates their shard (fused exchange); weights and gradients stay whole
+    assert eight["optimizer"] == (one["optimizer"] + 7) // 8 and eight["total"] == one["total"] - one["optimizer"] + eight["optimizer"]
+    assert eight["checkpoint_bytes"] == one["checkpoint_bytes"]        # a checkpoint still holds all of them
     assert one["optimizer"] == 4 * one["parameters"] and one["weights"] == 6 * one["parameters"]       # lion: one moment
+    t2 = TrainerConfig.from_config(cfg)
+    t2.optimizer = "muon"                                  # Muon runs whole on every rank: nothing to shard
+    assert memory_plan(m, t2, 8, 16)["optimizer"] == memory_plan(m, t2, 1, 16)["optimizer"]
     assert eight["activations"] == one["activations"] and memory_plan(m, t, 1, 1)["activations"] < one["activations"]
 
 
