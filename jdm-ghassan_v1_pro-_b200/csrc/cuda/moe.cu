@@ -57,51 +57,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
   const int t1 = min(a.n_tok, t0 + bt);
   const T* x16 = reinterpret_cast<const T*>(a.x16);
   const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;   // device copy wins (graph replay)
-  for (int t = t0 + warp; t < t1; t += 8) {
-    const T* xr = x16 + (size_t)t * d;
-    const int tj = a.seg_tokens > 0 ? t % a.seg_tokens : t;   // the jitter hash counts tokens inside a micro-batch
-    // lane holds the logits of experts `lane` and `lane + 32`
-    float l0 = -INFINITY, l1 = -INFINITY;
-    if constexpr (NV8 > 0) {
-      float xf[NV8][8];
-#pragma unroll
-      for (int k = 0; k < NV8; ++k) {
-        const uint4 q = *reinterpret_cast<const uint4*>(xr + k * 256 + lane * 8);
-        const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
-        xf[k][0] = v0.x; xf[k][1] = v0.y; xf[k][2] = v1.x; xf[k][3] = v1.y;
-        xf[k][4] = v2.x; xf[k][5] = v2.y; xf[k][6] = v3.x; xf[k][7] = v3.y;
-      }
-#pragma unroll 2
-      for (int e = 0; e < ne; ++e) {
-        const float* wr = a.router_w + (size_t)e * d + lane * 8;
-        float s = 0.f;
-#pragma unroll
-        for (int k = 0; k < NV8; ++k) {
-          const float4 w0 = *reinterpret_cast<const float4*>(wr + k * 256);
-          const float4 w1 = *reinterpret_cast<const float4*>(wr + k * 256 + 4);
-          s += xf[k][0] * w0.x + xf[k][1] * w0.y + xf[k][2] * w0.z + xf[k][3] * w0.w +
-               xf[k][4] * w1.x + xf[k][5] * w1.y + xf[k][6] * w1.z + xf[k][7] * w1.w;
-        }
-        s = warp_sum(s);
-        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
-        if (e == lane) l0 = s;
-        if (e == lane + 32) l1 = s;
-      }
-    } else {
-      for (int e = 0; e < ne; ++e) {
-        const float* wr = a.router_w + (size_t)e * d;
-        float s = 0.f;
-        for (int i = lane * 2; i < d; i += 64) {
-          const float2 xv = Cvt<T>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
-          const float2 wv = *reinterpret_cast<const float2*>(wr + i);
-          s += xv.x * wv.x + xv.y * wv.y;
-        }
-        s = warp_sum(s);
-        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
-        if (e == lane) l0 = s;
-        if (e == lane + 32) l1 = s;
-      }
-    }
+  // The rest of a token after its logits: soft-max, bias-steered top-k, outputs and the block histogram.
+  auto finish = [&](int t, float l0, float l1) {
     const float mx = warp_max(fmaxf(l0, l1));
     const float e0 = lane < ne ? __expf(l0 - mx) : 0.f;
     const float e1 = lane + 32 < ne ? __expf(l1 - mx) : 0.f;
@@ -139,6 +96,72 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
           atomicAdd(&s_hist[esel[k]], 1);
         }
       if (a.shared) atomicAdd(&s_hist[ne], 1);
+    }
+  };
+  if constexpr (NV8 > 0) {
+    // Two tokens per warp and trip: the router rows (ne x d fp32, the same for every token) come through L1 once
+    // for the pair.  With one token per trip the kernel moved 24 KB of router weights per token through L1 and ran
+    // at a tenth of what its 1.5 KB of activations per token need.
+    for (int t = t0 + 2 * warp; t < t1; t += 16) {
+      const bool two = t + 1 < t1;
+      float xf[2][NV8][8];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const T* xr = x16 + (size_t)(t + (u && two ? 1 : 0)) * d;
+#pragma unroll
+        for (int k = 0; k < NV8; ++k) {
+          const uint4 q = *reinterpret_cast<const uint4*>(xr + k * 256 + lane * 8);
+          const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+          xf[u][k][0] = v0.x; xf[u][k][1] = v0.y; xf[u][k][2] = v1.x; xf[u][k][3] = v1.y;
+          xf[u][k][4] = v2.x; xf[u][k][5] = v2.y; xf[u][k][6] = v3.x; xf[u][k][7] = v3.y;
+        }
+      }
+      float l0[2] = {-INFINITY, -INFINITY}, l1[2] = {-INFINITY, -INFINITY};
+#pragma unroll 2
+      for (int e = 0; e < ne; ++e) {
+        const float* wr = a.router_w + (size_t)e * d + lane * 8;
+        float s[2] = {0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < NV8; ++k) {
+          const float4 w0 = *reinterpret_cast<const float4*>(wr + k * 256);
+          const float4 w1 = *reinterpret_cast<const float4*>(wr + k * 256 + 4);
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+            s[u] += xf[u][k][0] * w0.x + xf[u][k][1] * w0.y + xf[u][k][2] * w0.z + xf[u][k][3] * w0.w +
+                    xf[u][k][4] * w1.x + xf[u][k][5] * w1.y + xf[u][k][6] * w1.z + xf[u][k][7] * w1.w;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          s[u] = warp_sum(s[u]);
+          const int tt = t + u;
+          const int tj = a.seg_tokens > 0 ? tt % a.seg_tokens : tt;   // the jitter hash counts tokens inside a micro-batch
+          if (a.use_jitter) s[u] *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
+          if (e == lane) l0[u] = s[u];
+          if (e == lane + 32) l1[u] = s[u];
+        }
+      }
+      finish(t, l0[0], l1[0]);
+      if (two) finish(t + 1, l0[1], l1[1]);
+    }
+  } else {
+    for (int t = t0 + warp; t < t1; t += 8) {
+      const T* xr = x16 + (size_t)t * d;
+      const int tj = a.seg_tokens > 0 ? t % a.seg_tokens : t;
+      float l0 = -INFINITY, l1 = -INFINITY;   // lane holds the logits of experts `lane` and `lane + 32`
+      for (int e = 0; e < ne; ++e) {
+        const float* wr = a.router_w + (size_t)e * d;
+        float s = 0.f;
+        for (int i = lane * 2; i < d; i += 64) {
+          const float2 xv = Cvt<T>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
+          const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+          s += xv.x * wv.x + xv.y * wv.y;
+        }
+        s = warp_sum(s);
+        if (a.use_jitter) s *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
+        if (e == lane) l0 = s;
+        if (e == lane + 32) l1 = s;
+      }
+      finish(t, l0, l1);
     }
   }
   __syncthreads();
@@ -386,79 +409,101 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const gb_moe_args 
 // Per token: sum the sorted-order input gradients of its slots, add the router path, write 16-bit dx and the
 // router-logit gradients (into `part`, [n_tok, ne]).
 template <typename T>
-__global__ void __launch_bounds__(256, 4) moe_router_bwd_kernel(const gb_moe_args a) {
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (t >= a.n_tok) return;
+__global__ void __launch_bounds__(256, 2) moe_router_bwd_kernel(const gb_moe_args a) {
+  // Two tokens per warp: the router rows (ne x d fp32) pass through L1 once for the pair.
+  const int tb = blockIdx.x * 16 + 2 * (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (tb >= a.n_tok) return;
   const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
-  // ---- router-logit gradient (lane e and e+32 hold expert e / e+32)
-  // the slot positions first: they do not depend on the router part, and after its stores the compiler could not
-  // move these loads up by itself
-  int pos[MAX_K + 1];
-#pragma unroll
-  for (int s = 0; s <= MAX_K; ++s)
-    if (s < S) pos[s] = a.slot_pos[(size_t)t * S + s];
-  const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
-  const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
-  float dp0 = 0.f, dp1 = 0.f;
-  const int sgi = a.seg_tokens > 0 ? t / a.seg_tokens : 0;       // micro-batch segment of this token
-  const int tj = a.seg_tokens > 0 ? t - sgi * a.seg_tokens : t;
-  const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[sgi] : a.aux_coef;   // one coefficient per segment
+  const bool two = tb + 1 < a.n_tok;
   const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;
-  if (a.f_frac && aux_coef != 0.f) {
-    const float* ff = a.f_frac + (size_t)sgi * ne;
-    if (lane < ne) dp0 = aux_coef * ff[lane];
-    if (lane + 32 < ne) dp1 = aux_coef * ff[lane + 32];
-  }
-  float ssum = 0.f, gbar = 0.f;
-  for (int k = 0; k < K; ++k) {
-    const int e = a.idx[(size_t)t * K + k];
-    const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);   // probs[t, e], already in a lane
-    ssum += pe;
-    gbar += a.gdot[(size_t)t * K + k] * a.w[(size_t)t * K + k];
-  }
-  if (ssum > 1e-8f) {
-    const float invs = 1.f / ssum;
+  int pos[2][MAX_K + 1];
+  float dl0[2], dl1[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int t = tb + ((u && two) ? 1 : 0);
+    // ---- router-logit gradient (lane e and e+32 hold expert e / e+32)
+    // the slot positions first: they do not depend on the router part, and after its stores the compiler could not
+    // move these loads up by itself
+#pragma unroll
+    for (int s = 0; s <= MAX_K; ++s)
+      if (s < S) pos[u][s] = a.slot_pos[(size_t)t * S + s];
+    const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
+    const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
+    float dp0 = 0.f, dp1 = 0.f;
+    const int sgi = a.seg_tokens > 0 ? t / a.seg_tokens : 0;       // micro-batch segment of this token
+    const int tj = a.seg_tokens > 0 ? t - sgi * a.seg_tokens : t;
+    const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[sgi] : a.aux_coef;   // one coefficient per segment
+    if (a.f_frac && aux_coef != 0.f) {
+      const float* ff = a.f_frac + (size_t)sgi * ne;
+      if (lane < ne) dp0 = aux_coef * ff[lane];
+      if (lane + 32 < ne) dp1 = aux_coef * ff[lane + 32];
+    }
+    float ssum = 0.f, gbar = 0.f;
     for (int k = 0; k < K; ++k) {
       const int e = a.idx[(size_t)t * K + k];
-      const float v = (a.gdot[(size_t)t * K + k] - gbar) * invs;
-      if (e == lane) dp0 += v;
-      if (e == lane + 32) dp1 += v;
+      const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);   // probs[t, e], already in a lane
+      ssum += pe;
+      gbar += a.gdot[(size_t)t * K + k] * a.w[(size_t)t * K + k];
+    }
+    if (ssum > 1e-8f) {
+      const float invs = 1.f / ssum;
+      for (int k = 0; k < K; ++k) {
+        const int e = a.idx[(size_t)t * K + k];
+        const float v = (a.gdot[(size_t)t * K + k] - gbar) * invs;
+        if (e == lane) dp0 += v;
+        if (e == lane + 32) dp1 += v;
+      }
+    }
+    const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
+    dl0[u] = p0 * (dp0 - pdp);
+    dl1[u] = p1 * (dp1 - pdp);
+    if (a.use_jitter) {
+      dl0[u] *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane, jseed);
+      dl1[u] *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane + 32, jseed);
+    }
+    if (u == 0 || two) {
+      if (lane < ne) a.part[(size_t)t * ne + lane] = dl0[u];
+      if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1[u];
     }
   }
-  const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
-  float dl0 = p0 * (dp0 - pdp), dl1 = p1 * (dp1 - pdp);
-  if (a.use_jitter) {
-    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane, jseed);
-    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane + 32, jseed);
-  }
-  if (lane < ne) a.part[(size_t)t * ne + lane] = dl0;
-  if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1;
   // ---- input gradient
   const T* dxp = reinterpret_cast<const T*>(a.dx_perm);
   T* dx = reinterpret_cast<T*>(a.dx16);
   for (int i = lane * 8; i < d; i += 256) {
-    float acc[8];
+    float acc[2][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int u = 0; u < 2; ++u) {
 #pragma unroll
-    for (int s = 0; s <= MAX_K; ++s)
-      if (s < S) {
-        const uint4 q = *reinterpret_cast<const uint4*>(dxp + (size_t)pos[s] * d + i);
-        const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
-        acc[0] += v0.x; acc[1] += v0.y; acc[2] += v1.x; acc[3] += v1.y; acc[4] += v2.x; acc[5] += v2.y; acc[6] += v3.x; acc[7] += v3.y;
-      }
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+#pragma unroll
+      for (int s = 0; s <= MAX_K; ++s)
+        if (s < S) {
+          const uint4 q = *reinterpret_cast<const uint4*>(dxp + (size_t)pos[u][s] * d + i);
+          const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+          acc[u][0] += v0.x; acc[u][1] += v0.y; acc[u][2] += v1.x; acc[u][3] += v1.y;
+          acc[u][4] += v2.x; acc[u][5] += v2.y; acc[u][6] += v3.x; acc[u][7] += v3.y;
+        }
+    }
 #pragma unroll 4
     for (int e = 0; e < ne; ++e) {
-      const float dl = __shfl_sync(0xffffffffu, e < 32 ? dl0 : dl1, e & 31);
       const float4 w0 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i);
       const float4 w1 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i + 4);
-      acc[0] += dl * w0.x; acc[1] += dl * w0.y; acc[2] += dl * w0.z; acc[3] += dl * w0.w;
-      acc[4] += dl * w1.x; acc[5] += dl * w1.y; acc[6] += dl * w1.z; acc[7] += dl * w1.w;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float dl = __shfl_sync(0xffffffffu, e < 32 ? dl0[u] : dl1[u], e & 31);
+        acc[u][0] += dl * w0.x; acc[u][1] += dl * w0.y; acc[u][2] += dl * w0.z; acc[u][3] += dl * w0.w;
+        acc[u][4] += dl * w1.x; acc[u][5] += dl * w1.y; acc[u][6] += dl * w1.z; acc[u][7] += dl * w1.w;
+      }
     }
-    uint4 o;
-    o.x = Cvt<T>::pack2(acc[0], acc[1]); o.y = Cvt<T>::pack2(acc[2], acc[3]);
-    o.z = Cvt<T>::pack2(acc[4], acc[5]); o.w = Cvt<T>::pack2(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(dx + (size_t)t * d + i) = o;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u == 0 || two) {
+        uint4 o;
+        o.x = Cvt<T>::pack2(acc[u][0], acc[u][1]); o.y = Cvt<T>::pack2(acc[u][2], acc[u][3]);
+        o.z = Cvt<T>::pack2(acc[u][4], acc[u][5]); o.w = Cvt<T>::pack2(acc[u][6], acc[u][7]);
+        *reinterpret_cast<uint4*>(dx + (size_t)(tb + u) * d + i) = o;
+      }
+    }
   }
 }
 
@@ -608,7 +653,7 @@ extern "C" int gb_moe_combine_bwd(const gb_moe_args* a, cudaStream_t st) {
 extern "C" int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st) {
   int rc = moe_check(a);
   if (rc) return rc;
-  const int grid = (a->n_tok + 7) / 8;
+  const int grid = (a->n_tok + 15) / 16;      // two tokens per warp, eight warps per block
   // token chunks for the router weight gradient: partials in part2 ([chunks, ne, d]) when it is provided
   int chunks = a->part2 ? (a->n_tok + 31) / 32 : 1;   // 32 tokens per thread: 8192 tokens fill 1536 blocks
   if (chunks > GB_ROUTER_WGRAD_CHUNKS) chunks = GB_ROUTER_WGRAD_CHUNKS;

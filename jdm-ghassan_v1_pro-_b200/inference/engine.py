@@ -29,6 +29,7 @@ from ..models.config import ModelConfig
 from ..models.cuda_model import CudaModel
 from ..ops import decode as D
 from ..ops import kernels as K
+from ..utils import canary as CA
 
 PINNED_TOKENS = 8
 
@@ -154,44 +155,44 @@ class InferenceEngine:
                 L.ws = K.MoeWorkspace(batch, d, cfg.num_experts, cfg.moe_top_k, cfg.moe_shared, self.dt, self.dev)
             else:
                 L.wg, L.wu, L.wd = q(r + "w_gate"), q(r + "w_up"), q(r + "w_down")
-            L.cK = torch.zeros(batch, max_len, kvd, **c16)
-            L.cV = torch.zeros(batch, max_len, kvd, **c16)
+            L.cK = CA.zeros(batch, max_len, kvd, **c16)
+            L.cV = CA.zeros(batch, max_len, kvd, **c16)
             self.layers.append(L)
         self.weight_bytes = sum(w.nbytes for L in self.layers for w in (L.wqkv, L.wo, L.wg, L.wu, L.wd)) + self.head.nbytes
         # ---- decode state and buffers (all static: one graph serves every step)
         B = batch
-        self.state = torch.zeros(B, D.STATE_INTS, **i32)
-        self.slot_pos = torch.zeros(B, max_len, **i32)
-        self.pos = torch.zeros(B, **i32)
-        self.cur_tok = torch.zeros(B, **i32)
-        self.x = [torch.zeros(B, d, **f32) for _ in range(2)]
-        self.x_mid = torch.zeros(B, d, **f32)
-        self.xb = torch.zeros(B, d, **c16)
-        self.rr = torch.zeros(B, **f32)
-        self.qkv = torch.zeros(B, qd + 2 * kvd, **c16)
-        self.qk = torch.zeros(B, qd + kvd, **c16)
-        self.att = torch.zeros(B, qd, **c16)
+        self.state = CA.zeros(B, D.STATE_INTS, **i32)
+        self.slot_pos = CA.zeros(B, max_len, **i32)
+        self.pos = CA.zeros(B, **i32)
+        self.cur_tok = CA.zeros(B, **i32)
+        self.x = [CA.zeros(B, d, **f32) for _ in range(2)]
+        self.x_mid = CA.zeros(B, d, **f32)
+        self.xb = CA.zeros(B, d, **c16)
+        self.rr = CA.zeros(B, **f32)
+        self.qkv = CA.zeros(B, qd + 2 * kvd, **c16)
+        self.qk = CA.zeros(B, qd + kvd, **c16)
+        self.att = CA.zeros(B, qd, **c16)
         slots = (cfg.moe_top_k + int(cfg.moe_shared)) if cfg.use_moe else 1
         self.slots = slots
-        self.act = torch.zeros(B, slots, E, **c16)
-        self.r_idx = torch.zeros(B, max(1, cfg.moe_top_k), **i32)      # router output of the current layer
-        self.r_w = torch.zeros(B, max(1, cfg.moe_top_k), **f32)
-        self.dense_idx = torch.zeros(B, 1, **i32)          # dense FFN = one "expert" with weight 1
+        self.act = CA.zeros(B, slots, E, **c16)
+        self.r_idx = CA.zeros(B, max(1, cfg.moe_top_k), **i32)      # router output of the current layer
+        self.r_w = CA.zeros(B, max(1, cfg.moe_top_k), **f32)
+        self.dense_idx = CA.zeros(B, 1, **i32)          # dense FFN = one "expert" with weight 1
         self.dense_w = torch.ones(B, 1, **f32)
-        self.logits = torch.zeros(B, V, **f32)
+        self.logits = CA.zeros(B, V, **f32)
         # split-KV: enough (sequence, kv head, split) blocks to cover the GPU; a warp walks its slots one by one,
         # so at batch 1 the cache is cut fine (a few slots per warp) and the partial results merged afterwards
         self.splits = int(min(64, max(8, 512 // (B * cfg.num_kv_heads))))
-        self.att_scratch = torch.zeros(B * cfg.num_heads * self.splits * (cfg.head_dim + 2), **f32)
-        self.att_ticket = torch.zeros(B * cfg.num_kv_heads, **i32)
+        self.att_scratch = CA.zeros(B * cfg.num_heads * self.splits * (cfg.head_dim + 2), **f32)
+        self.att_ticket = CA.zeros(B * cfg.num_kv_heads, **i32)
         self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, max_len) + 1, self.dev)
         self.hist_cap = max_len + 8
-        self.history = torch.zeros(B, self.hist_cap, **i32)
-        self.hist_len = torch.zeros(B, **i32)
-        self.uniforms = torch.zeros(max_len, B, **f32)      # one row of draws per sampling step
-        self.tok_log = torch.zeros(B, max_len, **i32)
-        self.step = torch.zeros(1, **i32)
-        self.stop = torch.zeros(8, **i32)
+        self.history = CA.zeros(B, self.hist_cap, **i32)
+        self.hist_len = CA.zeros(B, **i32)
+        self.uniforms = CA.zeros(max_len, B, **f32)      # one row of draws per sampling step
+        self.tok_log = CA.zeros(B, max_len, **i32)
+        self.step = CA.zeros(1, **i32)
+        self.stop = CA.zeros(8, **i32)
         self.n_stop = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._graph_key = None

@@ -24,6 +24,7 @@ import torch
 
 from ..ops import gemm as G
 from ..ops import kernels as K
+from ..utils import canary as CA
 from .config import ModelConfig, init_parameters
 
 ALIGN = 64  # elements; keeps every segment 16-byte aligned in both the fp32 and the 16-bit buffer
@@ -210,34 +211,34 @@ class CudaModel:
                 raise ValueError("share_weights needs an inference model of the same configuration and dtype")
             self.P, self.W16 = share_weights.P, share_weights.W16
         else:
-            self.P = torch.zeros(L.total, **f32)                # fp32 master weights
-            self.W16 = torch.zeros(L.total, dtype=dtype, device=self.dev)   # 16-bit shadows (GEMM operands)
-        self.Gr = torch.zeros(L.total, **f32) if train else None        # fp32 gradients
+            self.P = CA.zeros(L.total, **f32)                # fp32 master weights
+            self.W16 = CA.zeros(L.total, dtype=dtype, device=self.dev)   # 16-bit shadows (GEMM operands)
+        self.Gr = CA.zeros(L.total, **f32) if train else None        # fp32 gradients
         self.moe_bias = None
         self.bias_counts = None
         if share_weights is not None:
             self.moe_bias = share_weights.moe_bias
         elif cfg.use_moe and cfg.moe_aux_free:
-            self.moe_bias = torch.zeros(cfg.num_layers, cfg.num_experts, **f32)
+            self.moe_bias = CA.zeros(cfg.num_layers, cfg.num_experts, **f32)
         if cfg.use_moe and train:
             # routed slots per (layer, expert) of the current step: balancing input (aux-free) and expert-load report
-            self.bias_counts = torch.zeros(cfg.num_layers, cfg.num_experts, **f32)
+            self.bias_counts = CA.zeros(cfg.num_layers, cfg.num_experts, **f32)
         self.cos_sin = K.rope_table(torch.from_numpy(cfg.rope_inv_freq()), max(cfg.max_seq_len, T), self.dev)
         self.pos = torch.arange(T, dtype=torch.int32, device=self.dev).repeat(B)
         # per-launch scalars that a captured graph must be able to change
         # [0] CE gradient scale (loss scale); then per micro-batch segment: [2, 2+n) aux coefficient of the backward,
         # [2+n, 2+2n) weight of the segment's balance loss (its supervised tokens)
-        self.dyn = torch.zeros(2 + 2 * self.n_seg, **f32)
+        self.dyn = CA.zeros(2 + 2 * self.n_seg, **f32)
         self.dyn_aux = self.dyn[2:2 + self.n_seg]
         self.dyn_segw = self.dyn[2 + self.n_seg:2 + 2 * self.n_seg]
-        self.seed_dev = torch.zeros(1, dtype=torch.int64, device=self.dev)
-        self.ce_acc = torch.zeros(2, dtype=torch.float64, device=self.dev)   # loss sum, supervised rows
-        self.aux_acc = torch.zeros(1, **f32)
-        self.ids = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
+        self.seed_dev = CA.zeros(1, dtype=torch.int64, device=self.dev)
+        self.ce_acc = CA.zeros(2, dtype=torch.float64, device=self.dev)   # loss sum, supervised rows
+        self.aux_acc = CA.zeros(1, **f32)
+        self.ids = CA.zeros(self.N, dtype=torch.int32, device=self.dev)
         self.targets = torch.full((self.N,), -100, dtype=torch.int32, device=self.dev)
-        self.segs = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
+        self.segs = CA.zeros(self.N, dtype=torch.int32, device=self.dev)
         self.attn_tc = K.attn_tc_supported(cfg.head_dim)
-        self.seg_lo = torch.zeros(self.N, dtype=torch.int32, device=self.dev)
+        self.seg_lo = CA.zeros(self.N, dtype=torch.int32, device=self.dev)
         self.ep = None                                      # set by enable_expert_parallel()
         self._alloc_activations(train)
 
@@ -249,31 +250,31 @@ class CudaModel:
         f32 = dict(dtype=torch.float32, device=dev)
         c16 = dict(dtype=dt, device=dev)
         nl = cfg.num_layers if train else 1     # evaluation reuses one layer's buffers
-        self.x = [torch.empty(N, d, **f32) for _ in range((cfg.num_layers + 1) if train else 2)]
+        self.x = [CA.empty(N, d, **f32) for _ in range((cfg.num_layers + 1) if train else 2)]
         self.layers: List[_LayerBuf] = []
         for _ in range(nl):
             b = _LayerBuf()
-            b.xb, b.rrms1 = torch.empty(N, d, **c16), torch.empty(N, **f32)
-            b.qkv, b.qk = torch.empty(N, qd + 2 * kvd, **c16), torch.empty(N, qd + kvd, **c16)
-            b.att, b.lse = torch.empty(N, qd, **c16), torch.empty(N, H, **f32)
-            b.x_mid = torch.empty(N, d, **f32)
-            b.xb2, b.rrms2 = torch.empty(N, d, **c16), torch.empty(N, **f32)
+            b.xb, b.rrms1 = CA.empty(N, d, **c16), CA.empty(N, **f32)
+            b.qkv, b.qk = CA.empty(N, qd + 2 * kvd, **c16), CA.empty(N, qd + kvd, **c16)
+            b.att, b.lse = CA.empty(N, qd, **c16), CA.empty(N, H, **f32)
+            b.x_mid = CA.empty(N, d, **f32)
+            b.xb2, b.rrms2 = CA.empty(N, d, **c16), CA.empty(N, **f32)
             if cfg.use_moe:
                 b.ws = K.MoeWorkspace(N, d, cfg.num_experts, cfg.moe_top_k, cfg.moe_shared, dt, dev,
                                       seg_tokens=self.micro_tokens)
                 rows = b.ws.cap
-                b.xperm, b.yperm = torch.zeros(rows, d, **c16), torch.zeros(rows, d, **c16)
+                b.xperm, b.yperm = CA.zeros(rows, d, **c16), CA.zeros(rows, d, **c16)
             else:
                 rows = N
-            b.gu, b.act = torch.zeros(rows, 2 * E, **c16), torch.zeros(rows, E, **c16)
+            b.gu, b.act = CA.zeros(rows, 2 * E, **c16), CA.zeros(rows, E, **c16)
             self.layers.append(b)
         rows = self.layers[0].ws.cap if cfg.use_moe else N
-        self.h16, self.rrms_f = torch.empty(N, d, **c16), torch.empty(N, **f32)
+        self.h16, self.rrms_f = CA.empty(N, d, **c16), CA.empty(N, **f32)
         # ce_chunks bounds the logits buffer (rows x vocab, 16-bit); chunks below 2048 rows only add launches
         self.chunk_rows = max((N + self.ce_chunks - 1) // self.ce_chunks, min(N, 2048))
         self.Vpad = (cfg.vocab_size + 7) // 8 * 8
-        self.logits = torch.zeros(self.chunk_rows, self.Vpad, **c16)
-        self.row_loss = torch.empty(self.chunk_rows, **f32)
+        self.logits = CA.zeros(self.chunk_rows, self.Vpad, **c16)
+        self.row_loss = CA.empty(self.chunk_rows, **f32)
         self.head_splitk = None
         if not train:
             return
@@ -282,17 +283,17 @@ class CudaModel:
             splits = max(2, min(32, 296 // tiles, cfg.vocab_size // 512))
             self.head_splitk = G.SplitK(self.chunk_rows, d, cfg.vocab_size, splits, dt, dev)
         t = _LayerBuf()   # backward temporaries shared by all layers
-        t.dx, t.dx16 = torch.empty(N, d, **f32), torch.empty(N, d, **c16)
-        t.dxb, t.dh16 = torch.empty(N, d, **c16), torch.empty(N, d, **c16)
-        t.datt, t.delta = torch.empty(N, qd, **c16), torch.empty(N, H, **f32)
-        t.dqkv, t.dqk = torch.zeros(N, qd + 2 * kvd, **c16), torch.empty(N, qd + kvd, **c16)
-        t.dgu = torch.zeros(rows, 2 * E, **c16)
+        t.dx, t.dx16 = CA.empty(N, d, **f32), CA.empty(N, d, **c16)
+        t.dxb, t.dh16 = CA.empty(N, d, **c16), CA.empty(N, d, **c16)
+        t.datt, t.delta = CA.empty(N, qd, **c16), CA.empty(N, H, **f32)
+        t.dqkv, t.dqk = CA.zeros(N, qd + 2 * kvd, **c16), CA.empty(N, qd + kvd, **c16)
+        t.dgu = CA.zeros(rows, 2 * E, **c16)
         if cfg.use_moe:
-            t.dy_perm, t.dxperm = torch.zeros(rows, d, **c16), torch.zeros(rows, d, **c16)
-            t.gdot, t.part = torch.empty(N, cfg.moe_top_k, **f32), torch.empty(N, cfg.num_experts, **f32)
-            t.part2 = torch.empty(K.ROUTER_WGRAD_CHUNKS * cfg.num_experts * d, **f32)
+            t.dy_perm, t.dxperm = CA.zeros(rows, d, **c16), CA.zeros(rows, d, **c16)
+            t.gdot, t.part = CA.empty(N, cfg.moe_top_k, **f32), CA.empty(N, cfg.num_experts, **f32)
+            t.part2 = CA.empty(K.ROUTER_WGRAD_CHUNKS * cfg.num_experts * d, **f32)
         else:
-            t.dact = torch.empty(N, E, **c16)
+            t.dact = CA.empty(N, E, **c16)
         t.norm_part = K.rmsnorm_bwd_scratch(N, d, dev)
         t.qk_part = K.qk_rope_scratch(N, H + cfg.num_kv_heads, cfg.head_dim, dev)
         self.tmp = t

@@ -11,6 +11,8 @@ from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
+from ..utils import canary as CA
+
 from . import _lib
 from ._lib import check_rc, lib, stream_ptr
 
@@ -239,17 +241,17 @@ class MoeWorkspace:
         i32 = dict(dtype=torch.int32, device=device)
         f32 = dict(dtype=torch.float32, device=device)
         self.cap = moe_capacity(n_tok, ne, top_k, shared)
-        self.probs = torch.empty(n_tok, ne, **f32)
-        self.idx = torch.empty(n_tok, top_k, **i32)
-        self.w = torch.empty(n_tok, top_k, **f32)
-        self.block_hist = torch.empty(nb, ne + 1, **i32)
-        self.block_base = torch.empty(nb + 1, ne + 1, **i32)
-        self.seg_offsets = torch.zeros(ne + 2, **i32)
-        self.tile_expert = torch.zeros(self.cap // 128, **i32)
-        self.num_tiles = torch.zeros(1, **i32)
-        self.slot_pos = torch.empty(n_tok, S, **i32)
-        self.aux_m = torch.zeros(self.n_seg, ne, **f32)
-        self.f_frac = torch.zeros(self.n_seg, ne, **f32)
+        self.probs = CA.empty(n_tok, ne, **f32)
+        self.idx = CA.empty(n_tok, top_k, **i32)
+        self.w = CA.empty(n_tok, top_k, **f32)
+        self.block_hist = CA.empty(nb, ne + 1, **i32)
+        self.block_base = CA.empty(nb + 1, ne + 1, **i32)
+        self.seg_offsets = CA.zeros(ne + 2, **i32)
+        self.tile_expert = CA.zeros(self.cap // 128, **i32)
+        self.num_tiles = CA.zeros(1, **i32)
+        self.slot_pos = CA.empty(n_tok, S, **i32)
+        self.aux_m = CA.zeros(self.n_seg, ne, **f32)
+        self.f_frac = CA.zeros(self.n_seg, ne, **f32)
 
     def args(self) -> MoeArgs:
         a = MoeArgs()

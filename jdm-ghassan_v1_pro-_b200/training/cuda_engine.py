@@ -23,6 +23,7 @@ from ..models.config import ModelConfig
 from ..models.cuda_model import CudaModel
 from ..ops import _lib
 from ..ops import kernels as K
+from ..utils import canary as CA
 from ..utils.log import log_info, log_warn
 from ..utils.telemetry import PERF
 from . import optim as O
@@ -43,8 +44,8 @@ class _FlatOptimizer:
         self.weight_decay, self.grad_clip = tcfg.weight_decay, tcfg.grad_clip
         self.lr = tcfg.effective_peak_lr()
         n = model.layout.total
-        self.m_flat = torch.zeros(n, dtype=torch.float32, device=model.dev)
-        self.v_flat = torch.zeros(n, dtype=torch.float32, device=model.dev) if kind == "adamw" else None
+        self.m_flat = CA.zeros(n, dtype=torch.float32, device=model.dev, name="moment m")
+        self.v_flat = CA.zeros(n, dtype=torch.float32, device=model.dev, name="moment v") if kind == "adamw" else None
         self.hyper_dev = torch.zeros(3, dtype=torch.float32, device=model.dev)
         self.hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory()
 
