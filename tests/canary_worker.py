@@ -31,7 +31,7 @@ def main():
         docs.append(a + 16)
     write_shard(os.path.join(work, "train_0000.gbin"), docs, 600, None)
     bad = []
-    # sizes that are not multiples of the tile shapes: vocabulary 600, expert width 192, 3 + 1 experts, odd batch
+    # sizes that are not multiples of the tile shapes: vocabulary 600, expert width 192, 5 + 1 experts, odd batch
     for opt, moe, B, T in (("adamw", True, 3, 96), ("lion", False, 2, 160), ("muon", True, 1, 128)):
         c = Config.from_string("""
 model:
@@ -43,7 +43,7 @@ model:
   intermediate_size: 320
   max_seq_len: 160
   use_moe: %s
-  num_experts: 3
+  num_experts: 5
   moe_top_k: 2
   moe_expert_dim: 192
   moe_shared: true
@@ -74,7 +74,7 @@ training:
     for kw, moe, E in ((dict(batch=1, fmt="q4_0"), True, 192), (dict(batch=3, fmt="q8_0", gemm_min_batch=2), True, 192),
                        (dict(batch=1, fmt="f16", single_kernel=True), True, 256)):
         cfg = ModelConfig(vocab_size=600, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, intermediate_size=320,
-                          max_seq_len=96, use_moe=moe, num_experts=3, moe_top_k=2, moe_expert_dim=E, moe_shared=True, use_qk_norm=True)
+                          max_seq_len=96, use_moe=moe, num_experts=5, moe_top_k=2, moe_expert_dim=E, moe_shared=True, use_qk_norm=True)
         cfg.validate()
         eng = InferenceEngine(cfg, init_parameters(cfg, 5), max_len=40, prefill_chunk=32, **kw)
         eng.reset(1)
