@@ -255,7 +255,8 @@ def run_ours(args):
            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "bf16" if tcfg.operand_dtype() == "bf16" else "fp16", "data": "synthetic",
            "impl": "ours", "config": dict(recipe_label(args.config, mcfg, tcfg, world), fuse_micro_batches=tr.fuse,
-                                            grad_sync=("fused peer-memory" if eng.grad_sync is not None else
+                                            grad_sync=(("fused NVSwitch multicast" if getattr(eng.grad_sync, "nvls", False)
+                                                        else "fused peer-memory") if eng.grad_sync is not None else
                                                        ("nccl" if world > 1 else "none"))), "clocks": clocks,
            "e2e": {"value": toks_e / sec_e, "unit": "tokens/s",
                    "h2d_bytes_per_step": tcfg.grad_accum * tcfg.batch_size * tcfg.seq_len * 4 * n_in + 64,
@@ -325,7 +326,7 @@ def run_sync(args):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     total = (args.sync_elements + 63) // 64 * 64
-    buf = SymmetricBuffers()
+    buf = SymmetricBuffers(multicast=bool(args.nvls))
     shard = ((total + world - 1) // world + 63) // 64 * 64
     pad = shard * world
     P, tP = buf.alloc(pad, torch.float32)
@@ -349,6 +350,11 @@ def run_sync(args):
     a.partial, a.ticket, a.out = partial.data_ptr(), ticket.data_ptr(), out.data_ptr()
     a.status = _lib.status_word(dev).data_ptr()
     a.is_bf16, a.no_wait, a.local_only = 0, 0, 1
+    nvls = bool(args.nvls) and all(buf.mc_ptrs[:3])
+    if nvls:                       # reduce in the switch, distribute with multicast stores: no gather afterwards
+        a.mc_master, a.mc_w16, a.mc_grad = buf.mc_ptrs[0], buf.mc_ptrs[1], buf.mc_ptrs[2]
+    elif args.nvls and rank == 0:
+        print("[sync] no multicast address for the symmetric buffers: peer loads", file=sys.stderr, flush=True)
     state = {"be": 0}
 
     def bar():
@@ -365,8 +371,9 @@ def run_sync(args):
         if ev: ev[2].record()
         bar()
         if ev: ev[3].record()
-        C.gather(tW, W16, shard, total, rank, world)
-        C.gather(tP, P, shard, f32_end, rank, world)
+        if not nvls:
+            C.gather(tW, W16, shard, total, rank, world)
+            C.gather(tP, P, shard, f32_end, rank, world)
         if ev: ev[4].record()
 
     torch.cuda.synchronize()
@@ -411,9 +418,11 @@ def run_sync(args):
     # Bytes that cross each direction of a GPU's NVLink per exchange: it reads W-1 peer shards of fp32 gradient and
     # W-1 peer shards of new weights (16-bit everywhere, fp32 below f32_end), and serves the same amounts to its peers.
     per_dir = (world - 1) * (shard * 4 + shard * 2) + max(0, min(f32_end, total) - shard) * 4
+    if nvls:                       # the switch adds and copies: a GPU receives one reduced shard and every new weight once
+        per_dir = shard * 4 + (world - 1) * shard * 2 + max(0, min(f32_end, total) - shard) * 4
     roof_ms = per_dir / 770e9 * 1e3
     if rank == 0:
-        print(json.dumps({"bench": "fused_grad_sync", "world": world, "elements": total, "fused_ms": fused_ms,
+        print(json.dumps({"bench": "fused_grad_sync", "world": world, "path": "NVSwitch multicast (multimem)" if nvls else "peer loads", "elements": total, "fused_ms": fused_ms,
                           "reduce_scatter_phase_ms": reduce_ms, "update_phase_ms": update_ms,
                           "allgather_phase_ms": gather_ms, "nccl_allreduce_only_ms": nccl_ms,
                           "nvlink_bytes_per_direction": per_dir, "roofline_ms_at_770GBs_per_direction": roof_ms,
@@ -586,6 +595,7 @@ def main():
     ap.add_argument("--graphs", action="store_true", help="--profile-passes: replay CUDA graphs instead of eager launches")
     ap.add_argument("--end-step", action="store_true", help="--profile-passes: also run the optimizer step")
     ap.add_argument("--sync-only", action="store_true", help="time the gradient exchange alone (see run_sync)")
+    ap.add_argument("--nvls", action="store_true", help="--sync-only: reduce and distribute through NVSwitch multicast")
     ap.add_argument("--sync-elements", type=int, default=1_036_995_840)
     args = ap.parse_args()
     if args.profile_passes > 0:

@@ -69,6 +69,20 @@ __global__ void sync_barrier_auto_kernel(unsigned int* const* __restrict__ peer_
   __syncthreads();
 }
 
+// ---------------------------------------------------------------------------------------------- NVSwitch multicast
+// One load that the switch answers with the sum over all ranks' copies, and one store that the switch delivers to all
+// of them.  Only with a multicast address (the symmetric buffer bound to a multicast object); never in a test where a
+// rank leaves.
+__device__ __forceinline__ float4 mc_ld_reduce_f32x4(const float* p) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_16B(void* p, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------- reduce-scatter
 template <int W>
 __device__ __forceinline__ float4 sum_peers(float* const* __restrict__ g, long long i, int world) {
@@ -102,7 +116,8 @@ __global__ void __launch_bounds__(256) sync_reduce_kernel(gb_sync_args a) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long i = base + ((long long)u * 256 + threadIdx.x) * 4;
-      s[u] = i < hi ? sum_peers<W>(gp, i, a.world) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s[u] = i >= hi ? make_float4(0.f, 0.f, 0.f, 0.f)
+                     : (a.mc_grad ? mc_ld_reduce_f32x4(a.mc_grad + i) : sum_peers<W>(gp, i, a.world));
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -247,6 +262,18 @@ __global__ void __launch_bounds__(256) sync_update_kernel(gb_sync_args a) {
     q16.y = Cvt<T>::pack2(wv[2], wv[3]);
     q16.z = Cvt<T>::pack2(wv[4], wv[5]);
     q16.w = Cvt<T>::pack2(wv[6], wv[7]);
+    if (a.mc_w16) {                       // one store per 16 bytes, delivered to every rank (this one included)
+      mc_st_16B(reinterpret_cast<T*>(a.mc_w16) + i, make_float4(__uint_as_float(q16.x), __uint_as_float(q16.y),
+                                                                   __uint_as_float(q16.z), __uint_as_float(q16.w)));
+      if (i < a.f32_end && a.mc_master) {
+        mc_st_16B(a.mc_master + i, make_float4(wv[0], wv[1], wv[2], wv[3]));
+        mc_st_16B(a.mc_master + i + 4, make_float4(wv[4], wv[5], wv[6], wv[7]));
+      } else {
+        *reinterpret_cast<float4*>(w + i) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+        *reinterpret_cast<float4*>(w + i + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
+      }
+      continue;
+    }
     if (a.local_only) {                   // peers fetch the new values themselves afterwards (gb_sync_gather)
       *reinterpret_cast<uint4*>(wp[a.rank] + i) = q16;
       *reinterpret_cast<float4*>(w + i) = make_float4(wv[0], wv[1], wv[2], wv[3]);

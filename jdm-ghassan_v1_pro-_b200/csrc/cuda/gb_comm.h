@@ -51,6 +51,10 @@ typedef struct gb_sync_args {
   int local_only;                   // 1: gb_sync_update writes the new values of the own shard locally only; the ranks
                                     //    then fetch each other's shards with gb_sync_gather (peer loads ran 1.8x faster
                                     //    than peer stores on NVSwitch here)
+  // NVSwitch multicast addresses of the same three buffers (NULL: not used).  With mc_grad the reduce-scatter is one
+  // multimem.ld_reduce per 16 bytes (the switch adds the ranks' values); with mc_w16 / mc_master the new values of
+  // the own shard go to every rank with one multimem.st each and no gather follows.
+  float* mc_grad; float* mc_master; void* mc_w16;
 } gb_sync_args;
 
 // All ranks have reached this point, and their earlier writes are visible to peer loads issued after it.

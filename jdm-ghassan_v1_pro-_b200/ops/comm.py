@@ -27,6 +27,7 @@ class SyncArgs(ctypes.Structure):
         ("epoch", c_uint),
         ("partial", c_vp), ("ticket", c_vp), ("out", c_vp), ("status", c_vp),
         ("is_bf16", c_int), ("no_wait", c_int), ("local_only", c_int),
+        ("mc_grad", c_vp), ("mc_master", c_vp), ("mc_w16", c_vp),
     ]
 
 

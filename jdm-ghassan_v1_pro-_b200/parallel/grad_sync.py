@@ -37,11 +37,18 @@ _F32 = np.float32
 class SymmetricBuffers:
     """Symmetric-memory allocations of one process group and the peer pointer tables the kernels take."""
 
-    def __init__(self, group=None):
-        # The kernels reach peers with plain loads and stores and never use a multicast address, so the buffers are not
-        # bound to an NVLink multicast object: a rank that dies while its memory is bound to one (the step watchdog
-        # exits hard, the launcher kills stragglers) can fault the other ranks' GPUs.  Set before the first rendezvous.
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    def __init__(self, group=None, multicast: bool = False):
+        # By default the kernels reach peers with plain loads and stores and never use a multicast address, so the
+        # buffers are not bound to an NVLink multicast object: a rank that dies while its memory is bound to one (the
+        # step watchdog exits hard, the launcher kills stragglers) can fault the other ranks' GPUs.  ``multicast``
+        # (recipe key ``b200.grad_sync_nvls``) asks for the binding; it takes effect only if no buffer of this process
+        # was created without it.  Set before the first rendezvous.
+        if multicast:
+            os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "0"
+        else:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.multicast = multicast
+        self.mc_ptrs = []
         import torch.distributed._symmetric_memory as symm
         self.symm = symm
         self.group = group if group is not None else dist.group.WORLD
@@ -56,6 +63,7 @@ class SymmetricBuffers:
         t.zero_()
         h = self.symm.rendezvous(t, self.group.group_name)
         self.handles.append(h)          # keeps the mapping alive
+        self.mc_ptrs.append(int(getattr(h, "multicast_ptr", 0) or 0) if self.multicast else 0)
         table = C.pointer_table(h.buffer_ptrs, self.device)
         return t, table
 
@@ -66,6 +74,7 @@ class LocalBuffers:
     def __init__(self):
         self.rank, self.world = 0, 1
         self.device = torch.device("cuda", torch.cuda.current_device())
+        self.multicast, self.mc_ptrs = False, []
 
     def alloc(self, numel: int, dtype):
         t = torch.zeros(numel, dtype=dtype, device=self.device)
@@ -73,13 +82,15 @@ class LocalBuffers:
 
 
 class FusedGradSync:
-    def __init__(self, engine, buffers=None):
+    def __init__(self, engine, buffers=None, nvls: bool = False):
+        """``nvls``: reduce and distribute through NVSwitch multicast (``multimem.ld_reduce`` / ``multimem.st``) when the
+        symmetric buffers could be bound to a multicast object; otherwise, and by default, plain peer loads."""
         self.engine = engine
         m = engine.model
         L = m.layout
         if buffers is None:
-            buffers = SymmetricBuffers() if (dist.is_available() and dist.is_initialized() and
-                                             dist.get_world_size() > 1) else LocalBuffers()
+            buffers = SymmetricBuffers(multicast=nvls) if (dist.is_available() and dist.is_initialized() and
+                                                           dist.get_world_size() > 1) else LocalBuffers()
         self.buf = buffers
         self.rank, self.world = buffers.rank, buffers.world
         if self.world > C.MAX_RANKS:
@@ -91,6 +102,12 @@ class FusedGradSync:
         P, self.t_master = buffers.alloc(padded, torch.float32)
         W16, self.t_w16 = buffers.alloc(padded, m.dtype)
         Gr, self.t_grad = buffers.alloc(padded, torch.float32)
+        mc = list(buffers.mc_ptrs[-3:]) if getattr(buffers, "multicast", False) else [0, 0, 0]
+        self.mc_master, self.mc_w16, self.mc_grad = mc if all(mc) else (0, 0, 0)
+        self.nvls = bool(self.mc_grad)
+        if nvls and not self.nvls and buffers.rank == 0:
+            from ..utils.log import log_warn
+            log_warn("[sync] b200.grad_sync_nvls: no multicast address for the symmetric buffers; using peer loads")
         P[:self.total].copy_(m.P)
         W16[:self.total].copy_(m.W16)
         self._P_pad, self._W16_pad, self._Gr_pad = P, W16, Gr
@@ -158,6 +175,10 @@ class FusedGradSync:
         a.is_bf16 = int(m.dtype == torch.bfloat16)
         a.no_wait = int(no_wait)
         a.local_only = 1                 # new values reach the peers by gb_sync_gather (loads), not by stores
+        if self.nvls:
+            a.mc_grad = self.mc_grad
+            if opt.kind != "muon":       # Muon's update does not run in these kernels: only its reduction uses the switch
+                a.mc_master, a.mc_w16 = self.mc_master, self.mc_w16
         return a
 
     def _barrier(self):
@@ -195,7 +216,7 @@ class FusedGradSync:
             C.gather(self.t_grad, self._Gr_pad, self.shard, self.total, self.rank, self.world)
             self._barrier()
             opt.launch(lr, self.out[0:1])
-        else:
+        elif not self.nvls:              # with multicast stores the new values are everywhere already
             C.gather(self.t_w16, self._W16_pad, self.shard, self.total, self.rank, self.world)
             C.gather(self.t_master, self._P_pad, self.shard, self.engine.model.layout.f32_end, self.rank, self.world)
         self._keep = a     # the struct is read at launch; kept only so that debugging can inspect the last call

@@ -112,6 +112,7 @@ class TrainerConfig:
     ep_size: int = 1                  # expert-parallel degree (num_experts % ep_size == 0; 1 or the number of ranks)
     ep_capacity: float = 2.0          # receive-buffer rows per rank, in units of its own routed rows (balanced load = 1)
     grad_sync: str = "fused"          # fused (peer-memory reduce-scatter + optimizer + all-gather) | nccl
+    grad_sync_nvls: bool = False      # fused exchange through NVSwitch multicast (multimem) where the buffers allow it
     weight_ema: float = 0.0           # > 0: keep an exponential moving average of the weights with this decay
     fuse_micro_batches: int = 0       # micro-batches run as one forward/backward pass (same gradient sum); 0 = choose
     cuda_graphs: bool = True
@@ -276,6 +277,7 @@ class TrainerConfig:
         t.ep_size = max(1, c.get_int("b200.ep_size", t.ep_size))
         t.ep_capacity = max(1.0, c.get_float("b200.ep_capacity", t.ep_capacity))
         t.grad_sync = c.get_str("b200.grad_sync", t.grad_sync)
+        t.grad_sync_nvls = c.get_bool("b200.grad_sync_nvls", t.grad_sync_nvls)
         if t.grad_sync not in ("fused", "nccl"):
             raise ConfigError(f"unknown b200.grad_sync '{t.grad_sync}' (fused|nccl)")
         t.weight_ema = c.get_float("b200.weight_ema", t.weight_ema)

@@ -122,7 +122,8 @@ class CudaEngine:
         fused_ok = tcfg.tokens_per_step_global(self.dist.world) < (1 << 24)
         if fused_ok and ((self.dist.world > 1 and tcfg.grad_sync == "fused") or fused_sync_single):
             from ..parallel.grad_sync import FusedGradSync
-            self.grad_sync = FusedGradSync(self)   # moves P / W16 / Gr (and routing counts) into symmetric memory
+            # moves P / W16 / Gr (and routing counts) into symmetric memory
+            self.grad_sync = FusedGradSync(self, nvls=bool(getattr(tcfg, "grad_sync_nvls", False)))
             if self.weight_ema is not None:
                 self.weight_ema = torch.empty_like(self.model.P).copy_(self.model.P)
         self.expert_parallel = None

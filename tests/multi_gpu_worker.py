@@ -162,6 +162,34 @@ def parity(work):
     return 0 if int(flag) else 1
 
 
+def nvls_parity(work):
+    """The exchange through NVSwitch multicast (multimem.ld_reduce / multimem.st) against NCCL.  No rank leaves in this
+    test; the switch's summation order is not the rank order, hence the tolerance of the Lion row."""
+    rank = dist.get_rank()
+    if rank == 0:
+        os.makedirs(work, exist_ok=True)
+        make_shards(work, 608)
+    dist.barrier()
+    ok = True
+    a, wa, _, tra = run_engine(work, "fused", steps=5, opt="lion", extra={"b200.grad_sync_nvls": "true"})
+    used = bool(tra.engine.grad_sync is not None and tra.engine.grad_sync.nvls)
+    b, wb, _, _ = run_engine(work, "nccl", steps=5, opt="lion")
+    for (la, ga, na, apa), (lb, gb_, nb, apb) in zip(a, b):
+        if na != nb or apa != apb or abs(la - lb) > 2e-3 * max(1.0, abs(lb)) or abs(ga - gb_) > 2e-2 * max(1e-3, abs(gb_)):
+            print(rank, "nvls step mismatch", (la, ga, na, apa), (lb, gb_, nb, apb), flush=True)
+            ok = False
+    worst = max(float(np.abs(wa[n] - wb[n]).max()) / (float(np.abs(wb[n]).max()) + 1e-9) for n in wb)
+    if worst > 2e-2:
+        print(rank, "nvls weights differ", worst, flush=True)
+        ok = False
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(("NVLS PARITY OK" if int(flag) else "NVLS PARITY FAILED") + (" (multicast in use)" if used else " (no multicast address: peer loads)"),
+              "worst rel weight diff", worst, flush=True)
+    return 0 if int(flag) else 1
+
+
 def ep_parity(work):
     rank, world = dist.get_rank(), dist.get_world_size()
     if rank == 0:
@@ -205,7 +233,7 @@ def main():
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    rc = {"parity": parity, "ep_parity": ep_parity}[mode](work)
+    rc = {"parity": parity, "ep_parity": ep_parity, "nvls_parity": nvls_parity}[mode](work)
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(rc)

@@ -200,3 +200,17 @@ def test_two_gpu_expert_parallel_equals_replicated(tmp_path):
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert p.returncode == 0, p.stdout[-3000:]
     assert "EP PARITY OK" in p.stdout, p.stdout[-3000:]
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_multi_gpu_exchange_through_nvswitch_multicast(tmp_path, world):
+    """`b200.grad_sync_nvls`: the reduce-scatter as multimem.ld_reduce and the distribution of the new weights as
+    multimem.st, against the NCCL path.  All ranks stay for the whole test."""
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "multi_gpu_worker.py"), "nvls_parity",
+           str(tmp_path)]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-3000:]
+    assert "NVLS PARITY OK" in p.stdout, p.stdout[-3000:]
