@@ -2,20 +2,21 @@
 // projection, QK-norm + RoPE + cache append + split-KV attention, merge + output projection + residual, RMSNorm +
 // router + gate/up + SwiGLU of the selected experts, down projection + residual), final norm and the vocabulary
 // projection.  One CTA of 16 warps per SM; the phases of a layer are separated by grid-wide barriers (five per layer)
-// instead of kernel boundaries (eight per layer in decode.cu), and every warp issues the weight loads of its next
-// piece of work BEFORE it arrives at the barrier: the weights do not depend on the activations, so their DRAM round
-// trip hides behind the barrier instead of following it.  The reference's decode loop (inference/generator.cpp:97-193,
+// instead of kernel boundaries (eight per layer in decode.cu), and every warp starts the bulk asynchronous copies of
+// the weight rows of its next piece of work into shared memory BEFORE it arrives at the barrier: the weights do not
+// depend on the activations, so their DRAM round trip hides behind the barrier instead of following it.  The reference's decode loop (inference/generator.cpp:97-193,
 // cuda/kernels.cu:876-1019) launches about fifteen kernels per layer.
 //
 // Work split.  Output rows of a projection are dealt to the CTAs round robin (row r belongs to CTA r mod grid); inside
 // a CTA a row goes to one warp, or, when the CTA has fewer rows than warps, to KS warps that split the row's K range
 // and meet in shared memory.  Rows are read in "super-units" of 256 stored values: a whole number of quantisation
 // blocks in every format (512 B fp16/bf16, 272 B Q8_0, 144 B Q4_0, 272 B Q8_0(64), 160 B Q4_1) and a multiple of 16 bytes,
-// so one lane loads one 16-byte word of a super-unit, coalesced.  16-bit formats are expanded from that register;
-// block formats go through a per-warp staging slot in shared memory, from which lane l expands values 8l..8l+7.
+// so a run of super-units is one bulk copy and lane l expands values 8l..8l+7 of a super-unit from shared memory.
+// (The vocabulary projection, too many rows per CTA to stage, pulls its rows through registers instead.)
 //
-// Every barrier wait is bounded (about two seconds): on expiry the CTA writes status 401 and skips the rest of the
-// step, and so do the others when their own wait runs out.  The launch is cooperative, so either all CTAs are
+// Every wait is bounded: a grid barrier that does not open within about two seconds writes status 401, a copy that
+// never signals its mbarrier 402; the CTA then skips the rest of the step (the others follow when their own waits run
+// out) and waits, again bounded, for its copies in flight before it leaves.  The launch is cooperative, so either all CTAs are
 // resident or the launch fails.
 #include <algorithm>
 #include <type_traits>
@@ -34,6 +35,7 @@ constexpr int SU = 256;               // values per super-unit
 constexpr int MAX_SLOTS = 9;          // top_k <= 8 routed experts plus the shared one
 constexpr int MAX_HEADS = 128;
 constexpr int ST_TIMEOUT_GRID = 401;
+constexpr int ST_TIMEOUT_COPY = 402;      // a bulk copy of weight rows never signalled its barrier
 
 template <int FMT> struct Fmt {
   static constexpr bool k16 = FMT == GB_W_F16 || FMT == GB_W_BF16;
@@ -230,6 +232,106 @@ __device__ __forceinline__ void run_phase(const Phase& ph, const Plan& pl, const
     k = k2; g = g2;
   }
   if (pl.KS > 1) {                        // uniform over the CTA: rows and P are
+    __syncthreads();
+    if ((int)threadIdx.x < pl.rows) {
+      float a0 = 0.f, a1 = 0.f;
+      for (int j = 0; j < pl.KS; ++j) { a0 += red[0][threadIdx.x * pl.KS + j]; a1 += red[1][threadIdx.x * pl.KS + j]; }
+      epi(cta + (int)threadIdx.x * grid, a0, a1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ row streaming
+// The layer phases do not pull their rows through registers: lane 0 of a warp issues one bulk asynchronous copy per
+// contiguous run of super-units of ALL the warp's work in the phase into the warp's own slice of shared memory (no
+// other warp touches it), signalled on the warp's own mbarriers, and it does so right after the warp has finished the
+// phase before: the weights of a phase are in flight while the previous phase's results cross the grid barrier.
+constexpr int MAXI = 4;               // outputs a warp stages at once (checked on the host)
+constexpr int MAX_DYN = 220 * 1024;   // dynamic shared memory the kernel may ask for (227 KB per CTA, 3 KB static)
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+struct Stage {
+  uint8_t* base;        // this warp's slice
+  uint64_t* bars;       // this warp's MAXI barriers
+  uint32_t parity;      // bit k: parity that the next completion of bars[k] is waited with
+  uint32_t pending;     // bit k: a copy onto bars[k] was issued and not yet waited for
+  int* dead;
+  int* status;
+};
+
+// Per-warp bytes of the staging slice for one phase: N outputs of P super-units each, dealt as make_plan does.
+__host__ __device__ inline long long stage_need(long long N, int P, int grid, int su_bytes, int* items_out) {
+  const long long rows = (N + grid - 1) / grid;
+  long long items = 1, sus = P;
+  if (rows == 0) { if (items_out) *items_out = 0; return 0; }
+  const int ks = (int)(WARPS / rows) < P ? (int)(WARPS / rows) : P;
+  if (ks >= 2) sus = (P + ks - 1) / ks;
+  else items = (rows + WARPS - 1) / WARPS;
+  if (items_out) *items_out = (int)items;
+  return items * sus * su_bytes;
+}
+
+template <int FMT, class RowOff>
+__device__ __forceinline__ void stream_issue(const Phase& ph, const Plan& pl, Stage& st, RowOff row_off) {
+  constexpr int SB = Fmt<FMT>::bytes;
+  __syncwarp();                                  // every lane has finished reading the slice
+  if (pl.n > 0 && !*st.dead) st.pending |= (1u << pl.n) - 1u;
+  if ((threadIdx.x & 31) == 0 && !*st.dead) {
+    fence_proxy_async();                         // those reads are ordered before the copies that overwrite them
+    const int item_bytes = (pl.pe - pl.pb) * SB;
+    for (int k = 0; k < pl.n; ++k) {
+      const uint8_t* row = ph.W + row_off((int)blockIdx.x + (pl.first + k * pl.stride) * (int)gridDim.x);
+      uint8_t* dst = st.base + (size_t)k * item_bytes;
+      mbar_arrive_expect_tx(st.bars + k, (uint32_t)item_bytes);
+      for (int p = pl.pb; p < pl.pe;) {
+        const int s = p / ph.nsu, su = p - s * ph.nsu;
+        const int run = min(pl.pe - p, ph.nsu - su);
+        bulk_g2s(smem_u32(dst + (size_t)(p - pl.pb) * SB), row + (ph.off ? ph.off[s] : 0ll) + (long long)su * SB,
+                 (uint32_t)(run * SB), smem_u32(st.bars + k));
+        p += run;
+      }
+    }
+  }
+}
+
+template <int FMT, typename XT, class Epi>
+__device__ __forceinline__ void stream_run(const Phase& ph, const Plan& pl, const XT* xs, Stage& st, float (*red)[WARPS], Epi epi) {
+  constexpr int SB = Fmt<FMT>::bytes;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grid = gridDim.x, cta = blockIdx.x;
+  const int item_bytes = (pl.pe - pl.pb) * SB;
+  for (int k = 0; k < pl.n; ++k) {
+    const bool got = mbar_wait(st.bars + k, (st.parity >> k) & 1u);
+    if (!got) {                                  // bounded: the copy never landed
+      if (lane == 0) { *st.dead = 1; atomicCAS(st.status, 0, ST_TIMEOUT_COPY); }
+      break;
+    }
+    st.parity ^= 1u << k;
+    st.pending &= ~(1u << k);
+    const uint8_t* src = st.base + (size_t)k * item_bytes;
+    float acc[2] = {0.f, 0.f};
+    for (int p = pl.pb; p < pl.pe; ++p) {
+      const int s = p / ph.nsu, su = p - s * ph.nsu;
+      const uint8_t* slot = src + (size_t)(p - pl.pb) * SB;
+      uint4 q = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (Fmt<FMT>::k16) q = *reinterpret_cast<const uint4*>(slot + 16 * lane);
+      const float v = su_dot<FMT, XT>(q, slot, xs + (ph.x_mod ? su : p) * SU);
+      if (ph.acc_split && s == 1) acc[1] += v;
+      else acc[0] += (ph.wt ? ph.wt[s] : 1.f) * v;
+    }
+    const float a0 = warp_sum(acc[0]);
+    const float a1 = ph.acc_split ? warp_sum(acc[1]) : 0.f;
+    if (lane == 0) {
+      if (pl.KS == 1) epi(cta + (pl.first + k * pl.stride) * grid, a0, a1);
+      else { red[0][warp] = a0; red[1][warp] = a1; }
+    }
+  }
+  if (pl.KS > 1) {                               // uniform over the CTA
     __syncthreads();
     if ((int)threadIdx.x < pl.rows) {
       float a0 = 0.f, a1 = 0.f;
@@ -583,7 +685,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   uint8_t* stage_all = dyn + (((size_t)xs_vals * 2 + 15) & ~(size_t)15);
   uint8_t* stage = stage_all + (size_t)(threadIdx.x >> 5) * GROUP * 512;
   float* ftab = reinterpret_cast<float*>(stage_all + (size_t)WARPS * GROUP * 512);
-  float* amerge = ftab + a.H * a.max_splits;
+  float* amerge = ftab + ((a.H * a.max_splits + 3) & ~3);
+  uint8_t* wstage = reinterpret_cast<uint8_t*>(amerge + WARPS * 8 + WARPS * 4 * hd);   // 16-byte aligned: see dyn_bytes
   const int nsu_d = d / SU, nsu_q = qd / SU, nsu_E = E / SU;
   const long long rb_d = (long long)nsu_d * Fmt<FMT>::bytes, rb_q = (long long)nsu_q * Fmt<FMT>::bytes,
                   rb_E = (long long)nsu_E * Fmt<FMT>::bytes;
@@ -611,43 +714,53 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   auto mark = [&]() { if (prof) *prof++ = globaltimer_ns(); };
   mark();
 
+  // per-warp staging slice and barriers
+  __shared__ __align__(8) uint64_t bars[WARPS * MAXI];
+  const int warp_id = threadIdx.x >> 5;
+  Stage st{wstage + (size_t)warp_id * a.stage_bytes, bars + warp_id * MAXI, 0u, 0u, &sm.dead, a.status};
+  if ((threadIdx.x & 31) == 0) {
+    for (int k = 0; k < MAXI; ++k) mbar_init(st.bars + k, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+
   uint4 cur[GROUP];
   bool ok = true;
-  {   // first projection of the first layer: nothing to wait for
-    const gb_mega_layer& L = a.layers[0];
-    Phase ph{reinterpret_cast<const uint8_t*>(L.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
-    preload<FMT>(ph, make_plan(qd + 2 * kvd, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
+  const int n_qkv = qd + 2 * kvd;
+  auto rowA = [&](int o) { return (long long)o * rb_d; };
+  auto rowC = [&](int o) { return (long long)o * rb_q; };
+  auto rowE = [&](int o) { return (long long)o * rb_E; };
+  const Plan plA = make_plan(n_qkv, nsu_d), plC = make_plan(d, nsu_q), plE = make_plan(d, slots * nsu_E);
+  {   // rows of the first projection of the first layer: nothing to wait for
+    Phase ph{reinterpret_cast<const uint8_t*>(a.layers[0].wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
+    stream_issue<FMT>(ph, plA, st, rowA);
   }
   for (int li = 0; li < a.n_layers && ok; ++li) {
     const gb_mega_layer& L = a.layers[li];
-    // ---- A: RMSNorm + fused QKV projection
+    Phase phC{reinterpret_cast<const uint8_t*>(L.wo), nullptr, nullptr, nsu_q, nsu_q, false, false};
+    // ---- A: RMSNorm + fused QKV projection; then this warp's rows of wo start to arrive
     {
       block_norm<XT>(x_in, L.attn_norm, xs, d, a.eps, sm.red[0]);
       Phase ph{reinterpret_cast<const uint8_t*>(L.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
-      const Plan pl = make_plan(qd + 2 * kvd, nsu_d);
-      run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, [&](int o) { return (long long)o * rb_d; },
-                         [&](int o, float v, float) { qkv[o] = Cvt<XT>::from_f(v); });
+      stream_run<FMT, XT>(ph, plA, xs, st, sm.red, [&](int o, float v, float) { qkv[o] = Cvt<XT>::from_f(v); });
+      stream_issue<FMT>(phC, plC, st, rowC);
     }
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
-    // ---- B: attention over the cache (a few CTAs); the others go straight on to fetch their rows of wo
+    // ---- B: attention over the cache
     attention_phase<XT>(a, L, S, sm, amerge);
-    Phase phC{reinterpret_cast<const uint8_t*>(L.wo), nullptr, nullptr, nsu_q, nsu_q, false, false};
-    const Plan plC = make_plan(d, nsu_q);
-    auto rowC = [&](int o) { return (long long)o * rb_q; };
-    preload<FMT>(phC, plC, rowC, cur);
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
     // ---- C: merge of the splits + output projection + residual
     merge_phase<XT>(a, S, sm, ftab, xs);
-    run_phase<FMT, XT>(phC, plC, xs, stage, sm.red, cur, rowC,
-                       [&](int o, float v, float) { x_mid[o] = __ldcg(x_in + o) + v; });
+    stream_run<FMT, XT>(phC, plC, xs, st, sm.red, [&](int o, float v, float) { x_mid[o] = __ldcg(x_in + o) + v; });
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
-    // ---- D: RMSNorm + router + gate/up of the chosen experts + SwiGLU
+    // ---- D: RMSNorm + router + gate/up of the chosen experts + SwiGLU; then the down-projection rows start to arrive
+    Phase phE{reinterpret_cast<const uint8_t*>(L.wd), sm.off_e, sm.wsel, nsu_E, slots * nsu_E, false, false};
     {
       block_norm<XT>(x_mid, L.ffn_norm, xs, d, a.eps, sm.red[0]);
       route_phase<XT>(a, L, xs, sm, rb_E);
@@ -662,33 +775,27 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
         const int slot = o / E, j = o - slot * E;
         return ((long long)sm.esel[slot] * E + j) * rb_d;
       };
-      preload<FMT>(ph, pl, row, cur);
-      run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, row,
-                         [&](int o, float g, float u) { act[o] = Cvt<XT>::from_f(g / (1.f + __expf(-g)) * u); });
+      stream_issue<FMT>(ph, pl, st, row);
+      stream_run<FMT, XT>(ph, pl, xs, st, sm.red,
+                          [&](int o, float g, float u) { act[o] = Cvt<XT>::from_f(g / (1.f + __expf(-g)) * u); });
+      stream_issue<FMT>(phE, plE, st, rowE);
     }
-    // ---- E: down projection of the chosen experts, weighted, + residual
-    Phase phE{reinterpret_cast<const uint8_t*>(L.wd), sm.off_e, sm.wsel, nsu_E, slots * nsu_E, false, false};
-    const Plan plE = make_plan(d, phE.P);
-    auto rowE = [&](int o) { return (long long)o * rb_E; };
-    preload<FMT>(phE, plE, rowE, cur);
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
+    // ---- E: down projection of the chosen experts, weighted, + residual; then the next layer's QKV rows
     for (int i = threadIdx.x; i < slots * E / 8; i += THREADS)
       reinterpret_cast<uint4*>(xs)[i] = __ldcg(reinterpret_cast<const uint4*>(act) + i);
     __syncthreads();
-    run_phase<FMT, XT>(phE, plE, xs, stage, sm.red, cur, rowE,
-                       [&](int o, float v, float) { x_out[o] = __ldcg(x_mid + o) + v; });
-    // ---- the next projection's first rows, then the barrier that publishes x_out
+    stream_run<FMT, XT>(phE, plE, xs, st, sm.red, [&](int o, float v, float) { x_out[o] = __ldcg(x_mid + o) + v; });
     const bool last = li + 1 == a.n_layers;
     bool head_pre = false;
     if (!last) {
-      const gb_mega_layer& Ln = a.layers[li + 1];
-      Phase ph{reinterpret_cast<const uint8_t*>(Ln.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
-      preload<FMT>(ph, make_plan(qd + 2 * kvd, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
-    } else if (a.head_fmt == FMT) {
+      Phase ph{reinterpret_cast<const uint8_t*>(a.layers[li + 1].wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
+      stream_issue<FMT>(ph, plA, st, rowA);
+    } else if (a.head_fmt == FMT) {       // the vocabulary projection has too many rows per CTA to stage: registers
       Phase ph{reinterpret_cast<const uint8_t*>(a.head), nullptr, nullptr, nsu_d, nsu_d, false, false};
-      preload<FMT>(ph, make_plan(a.V, nsu_d), [&](int o) { return (long long)o * rb_d; }, cur);
+      preload<FMT>(ph, make_plan(a.V, nsu_d), rowA, cur);
       head_pre = true;
     }
     mark();
@@ -703,6 +810,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       else head_phase<GB_W_BF16, XT>(a, xs, stage, sm, cur, false);
     }
   }
+  // a step that was given up: the copies this warp still has in flight must land (or run out of time) before the
+  // shared memory they target goes away
+  for (int k = 0; k < MAXI; ++k)
+    if (st.pending >> k & 1u) (void)mbar_wait(st.bars + k, (st.parity >> k) & 1u);
   mark();
   // ---- bookkeeping: the last CTA out records where the arrival count stands; CTA 0 advances the sequence state
   __syncthreads();
@@ -725,14 +836,40 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   }
 }
 
-static size_t dyn_bytes(const gb_mega_args& a) {
+// Bytes of one warp's staging slice (the largest of the four layer phases), or -1 when a warp would have to stage more
+// than MAXI outputs at once.
+static long long stage_bytes_per_warp(const gb_mega_args& a, int grid, int su_bytes) {
+  const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
+  const int nsu_d = a.d / SU, nsu_q = a.H * a.hd / SU, nsu_E = a.E / SU;
+  const long long n[4] = {(long long)(a.H + 2 * a.KV) * a.hd, a.d, (long long)slots * a.E, a.d};
+  const int P[4] = {nsu_d, nsu_q, 2 * nsu_d, slots * nsu_E};
+  long long need = 16;
+  for (int i = 0; i < 4; ++i) {
+    int items = 0;
+    need = std::max(need, stage_need(n[i], P[i], grid, su_bytes, &items));
+    if (items > MAXI) return -1;
+  }
+  return (need + 15) & ~15ll;
+}
+
+static size_t dyn_bytes(const gb_mega_args& a, long long stage_per_warp) {
   const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
   const int xs_vals = std::max(std::max(a.d, a.H * a.hd), slots * a.E);
   size_t b = ((size_t)xs_vals * 2 + 15) & ~(size_t)15;
   b += (size_t)WARPS * GROUP * 512;
-  b += (size_t)a.H * a.max_splits * 4;
+  b += (size_t)((a.H * a.max_splits + 3) & ~3) * 4;
   b += (size_t)(WARPS * 8 + WARPS * 4 * a.hd) * 4;
+  b += (size_t)WARPS * (size_t)stage_per_warp;
   return b;
+}
+
+static int su_bytes_of(int fmt) {
+  switch (fmt) {
+    case GB_W_F16: case GB_W_BF16: return 512;
+    case GB_W_GGML_Q8_0: case GB_W_Q8_64: return 272;
+    case GB_W_Q4_0: return 144;
+    default: return 160;
+  }
 }
 
 }  // namespace mg
@@ -750,7 +887,10 @@ extern "C" int gb_decode_mega_ok(const gb_mega_args* a) {
   if (a->head_fmt != a->fmt && a->head_fmt != GB_W_F16 && a->head_fmt != GB_W_BF16) return -5;
   if (a->d > 8 * mg::THREADS || a->max_splits > 64) return -6;
   if (a->max_splits < 1 || a->cap < 1 || a->pinned < 0 || a->pinned >= a->cap) return -6;
-  if (mg::dyn_bytes(*a) > 200 * 1024) return -7;
+  const int grid = gb_decode_mega_grid();
+  if (grid <= 0 || grid < a->KV) return -9;
+  const long long per_warp = mg::stage_bytes_per_warp(*a, grid, mg::su_bytes_of(a->fmt));
+  if (per_warp < 0 || mg::dyn_bytes(*a, per_warp) > mg::MAX_DYN) return -7;
   return 0;
 }
 
@@ -766,16 +906,18 @@ extern "C" int gb_decode_mega_grid() {
 }
 
 template <int FMT, typename XT>
-static int launch_mega(const gb_mega_args& a, cudaStream_t st) {
+static int launch_mega(const gb_mega_args& a_in, cudaStream_t st) {
   auto kern = mg::decode_mega_kernel<FMT, XT>;
-  const size_t smem = mg::dyn_bytes(a);
+  const int grid = gb_decode_mega_grid();
+  if (grid <= 0 || grid < a_in.KV) return -9;
+  gb_mega_args a = a_in;
+  a.stage_bytes = (int)mg::stage_bytes_per_warp(a, grid, mg::Fmt<FMT>::bytes);
+  const size_t smem = mg::dyn_bytes(a, a.stage_bytes);
   static bool attr_done = false;                 // one process drives one device
   if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -8;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mg::MAX_DYN) != cudaSuccess) return -8;
     attr_done = true;
   }
-  const int grid = gb_decode_mega_grid();
-  if (grid <= 0 || grid < a.KV) return -9;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeCooperative;
   attr.val.cooperative = 1;

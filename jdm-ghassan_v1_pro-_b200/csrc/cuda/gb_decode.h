@@ -129,6 +129,7 @@ typedef struct gb_mega_args {
   unsigned long long* prof;                      // NULL, or 10 * n_layers + 2 words: CTA 0's global-timer marks in
                                                  // nanoseconds (start; per layer the end of a phase and the start of
                                                  // the next, i.e. both sides of each of the five barriers; end)
+  int stage_bytes;                               // filled in by the launcher: shared-memory bytes per warp for staged rows
 } gb_mega_args;
 int gb_decode_mega_ok(const gb_mega_args* a);    // 0 when the shapes are covered, else a negative code
 int gb_decode_mega_grid(void);                   // CTAs of the launch (one per SM)

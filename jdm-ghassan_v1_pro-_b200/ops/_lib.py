@@ -96,6 +96,7 @@ STATUS_NAMES = {
     201: "timeout waiting for a peer rank's flag",
     301: "bad argument detected on device",
     401: "decode step: a grid-wide barrier wait ran out",
+    402: "decode step: a bulk copy of weight rows never signalled its barrier",
     302: "expert parallelism: more rows were routed to this rank's experts than its buffers hold (raise b200.ep_capacity)",
 }
 

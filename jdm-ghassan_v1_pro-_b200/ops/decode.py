@@ -236,7 +236,7 @@ class MegaArgs(ctypes.Structure):
         ("att_scratch", c_vp), ("max_splits", c_int),
         ("act", c_vp),
         ("r_idx", c_vp), ("r_w", c_vp),
-        ("sync", c_vp), ("status", c_vp), ("prof", c_vp),
+        ("sync", c_vp), ("status", c_vp), ("prof", c_vp), ("stage_bytes", c_int),
     ]
 
 
