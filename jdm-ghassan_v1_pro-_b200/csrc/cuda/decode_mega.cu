@@ -753,9 +753,13 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
-    // ---- C: merge of the splits + output projection + residual
+    // ---- C: merge of the splits + output projection + residual (the residual value is fetched ahead of the merge by
+    // the thread that will write the output)
+    const bool ownC = plC.KS > 1 && (int)threadIdx.x < plC.rows;
+    const float resC = ownC ? __ldcg(x_in + blockIdx.x + threadIdx.x * gridDim.x) : 0.f;
     merge_phase<XT>(a, S, sm, ftab, xs);
-    stream_run<FMT, XT>(phC, plC, xs, st, sm.red, [&](int o, float v, float) { x_mid[o] = __ldcg(x_in + o) + v; });
+    stream_run<FMT, XT>(phC, plC, xs, st, sm.red,
+                        [&](int o, float v, float) { x_mid[o] = (ownC ? resC : __ldcg(x_in + o)) + v; });
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
@@ -784,10 +788,13 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     if (!(ok = grid_sync(gb))) break;
     mark();
     // ---- E: down projection of the chosen experts, weighted, + residual; then the next layer's QKV rows
+    const bool ownE = plE.KS > 1 && (int)threadIdx.x < plE.rows;
+    const float resE = ownE ? __ldcg(x_mid + blockIdx.x + threadIdx.x * gridDim.x) : 0.f;
     for (int i = threadIdx.x; i < slots * E / 8; i += THREADS)
       reinterpret_cast<uint4*>(xs)[i] = __ldcg(reinterpret_cast<const uint4*>(act) + i);
     __syncthreads();
-    stream_run<FMT, XT>(phE, plE, xs, st, sm.red, [&](int o, float v, float) { x_out[o] = __ldcg(x_mid + o) + v; });
+    stream_run<FMT, XT>(phE, plE, xs, st, sm.red,
+                        [&](int o, float v, float) { x_out[o] = (ownE ? resE : __ldcg(x_mid + o)) + v; });
     const bool last = li + 1 == a.n_layers;
     bool head_pre = false;
     if (!last) {
