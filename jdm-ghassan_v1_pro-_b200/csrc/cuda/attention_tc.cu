@@ -1,10 +1,11 @@
 // Causal flash attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head_dim 64 or 128.
 //
-// Forward, one CTA per (batch, head, 128 query rows): a TMA producer warp, an MMA issuer warp (S = Q K^T into one of
-// two S buffers in tensor memory, O_part = P V with P read from shared memory) and sixteen softmax warps (tcgen05.ld
-// of S, scale + causal/window/segment mask, online softmax across four column chunks per row, P (16-bit) written to
-// shared memory in the 128-byte-swizzled operand layout, O rescaled and accumulated in registers, final
-// normalisation, O and log-sum-exp stored); details at the kernel.
+// Forward, one CTA per (batch, head, 128 query rows):
+//   warp 4 : TMA producer  - Q tile once, then K/V tiles of 128 keys through a 2-stage ring
+//   warp 5 : MMA issuer    - S = Q K^T into tensor memory, then O_part = P V (P read from shared memory)
+//   warps 0-3 (one thread per query row): tcgen05.ld of S, scale + causal/window/segment mask, online softmax,
+//            P (16-bit) written to shared memory in the 128-byte-swizzled operand layout, O rescaled and
+//            accumulated in registers, final normalisation, O and log-sum-exp stored.
 // The backward pass (further down) uses the same tile machinery: a dQ kernel per query tile and a dK/dV kernel
 // per key tile that loops over the query heads of its group, both recomputing P from the saved log-sum-exp.
 // Scores are never written to global memory (the reference materialises B*H*T^2 floats and re-runs the forward
@@ -23,6 +24,7 @@ template <typename T> struct OperandFmt { static constexpr int value = std::is_s
 
 constexpr int AT_M = 128;        // query rows per tile
 constexpr int AT_N = 128;        // keys per tile
+constexpr int AT_THREADS = 192;
 // Backward kernels: sixteen compute warps.  Warp w owns the 32 tile rows of TMEM lane quarter w % 4 and the 32-column
 // chunk w / 4, so a 128 x 128 score tile is one tcgen05.ld per thread and every scheduler has four warps to switch
 // between (with four compute warps in all, the exp / multiply / pack chain of a tile ran at one warp per scheduler
@@ -113,42 +115,39 @@ __device__ __forceinline__ void mma_kmajor_mnmajor(uint32_t tmem_d, uint32_t sa,
 }
 
 // ============================================================================================ forward
-// One CTA per (batch, head, 128 query rows), 18 warps:
-//   warp 16 : TMA producer - Q tile once, then K/V tiles of 128 keys through a ring of FWD_STAGES stages
-//   warp 17 : MMA issuer   - S(t+1) = Q K^T goes into the other of two S buffers in tensor memory while the softmax
-//             of tile t is still running; O_part(t) = P(t) V(t) once P(t) is in shared memory
-//   warps 0-15: warp w owns the 32 query rows of TMEM lane quarter w % 4 and the 32 key columns of chunk w / 4.
-//             Per tile: one tcgen05.ld of its 32 scores, local row maximum, exchange of the four chunk maxima of a
-//             row through shared memory (one named barrier), probabilities to shared memory in operand layout,
-//             then the PREVIOUS tile's P V (long finished by now) is folded into the output registers; each thread
-//             keeps HD / 4 output columns.  With four compute warps and one S buffer the exp / pack chain of a tile
-//             ran at one warp per scheduler and the tensor pipe idled through all of it.
-template <int HD> struct FwdStages { static constexpr int value = HD == 64 ? 3 : 2; };   // K/V ring depth
-
 template <typename T, int HD>
-__global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
-                                                                     const __grid_constant__ CUtensorMap tmK,
-                                                                     const __grid_constant__ CUtensorMap tmV,
-                                                                     const AttnTcParams p) {
+__global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                 const __grid_constant__ CUtensorMap tmK,
+                                                                 const __grid_constant__ CUtensorMap tmV,
+                                                                 const AttnTcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t TILE = AT_M * HD * 2;
-  constexpr int FWD_STAGES = FwdStages<HD>::value;
-  constexpr int OC = HD / 4;          // output columns per compute thread
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem;
+  if constexpr (HD == 64) {
+    // 112 KB of tiles + barriers and not a byte more: two CTAs of this kernel share an SM (143 registers, 256 TMEM
+    // columns each), which hides the latency of the short causal loops at T = 512.  That leaves no slack to align
+    // the base by hand; the kernel has no static shared memory, so the dynamic window starts 1024-aligned.  Checked,
+    // not assumed: a misaligned base reports and returns before any barrier or TMEM is touched.
+    if (smem_u32(smem_raw) & 1023u) {
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);
+      return;
+    }
+    smem = smem_raw;
+  } else {
+    smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  }
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE;                    // FWD_STAGES
-  uint8_t* sV = sK + FWD_STAGES * TILE;       // FWD_STAGES
-  uint8_t* sP = sV + FWD_STAGES * TILE;       // [128 x 128] 16-bit
-  float* sMax = reinterpret_cast<float*>(sP + AT_M * AT_N * 2);   // [2][4][128] chunk maxima, double-buffered by tile
-  float* sL = sMax + 2 * 4 * AT_M;                                // [4][128] chunk sums at the end
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + 4 * AT_M);
-  uint64_t* q_full = bars;                    // 1
-  uint64_t* kv_full = bars + 1;               // FWD_STAGES
-  uint64_t* kv_empty = kv_full + FWD_STAGES;  // FWD_STAGES
-  uint64_t* s_full = kv_empty + FWD_STAGES;   // 2 (one per S buffer)
-  uint64_t* p_ready = s_full + 2;
-  uint64_t* o_full = p_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint8_t* sK = sQ + TILE;            // 2 stages
+  uint8_t* sV = sK + 2 * TILE;        // 2 stages
+  uint8_t* sP = sV + 2 * TILE;        // [128 x 128] 16-bit
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + AT_M * AT_N * 2);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -161,44 +160,42 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_fwd_kernel(const __gri
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < FWD_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
-    mbar_init(p_ready, AT_BWD_CW * 32);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
     mbar_init(o_full, 1);
     *abort_flag = 0;
     *s_lo_min = 0x7fffffff;
     fence_barrier_init();
   }
-  if (warp == AT_BWD_W_MMA) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 5) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_O = tmem_base + 2 * AT_N;      // S buffers at columns [0, 128) and [128, 256)
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + AT_N;
 
   // visible key range of this tile: [k_lo, k_hi)
-  const int cq = warp >> 2;                     // 32-column chunk of a compute warp
-  const int r = (warp & 3) * 32 + lane;         // query row of a compute thread (its TMEM lane)
+  const int r = threadIdx.x;                  // query row for the first 128 threads
   const int i = q0 + r;
-  const bool row_ok = warp < AT_BWD_CW && i < p.T;
+  const bool row_ok = r < AT_M && i < p.T;
   int lo_i = 0;
   if (row_ok) {
     if (p.lo) lo_i = p.lo[row_base + i];
     if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
-    if (cq == 0) atomicMin(s_lo_min, lo_i);
+    atomicMin(s_lo_min, lo_i);
   }
   __syncthreads();
   const int k_hi = min(p.T, q0 + AT_M);
   const int k_lo = (min(*s_lo_min, k_hi - 1) / AT_N) * AT_N;
   const int n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
 
-  if (warp == AT_BWD_W_TMA) {
+  if (warp == 4) {
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, TILE);
       load_tile<HD>(&tmQ, q_full, sQ, h * HD, (int)row_base + q0);
       for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % FWD_STAGES, ph = (t / FWD_STAGES) & 1;
+        const int s = t & 1, ph = (t >> 1) & 1;
         if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
         mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
         load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
@@ -206,33 +203,21 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_fwd_kernel(const __gri
       }
     }
     __syncwarp();
-  } else if (warp == AT_BWD_W_MMA) {
+  } else if (warp == 5) {
     if (lane == 0) {
       constexpr int fmt = OperandFmt<T>::value;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
       const uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, AT_M, HD);
       bool ok = at_wait(q_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
-      if (ok && n_tiles > 0) {
-        ok = at_wait(&kv_full[0], 0, p.status, ST_TIMEOUT_FULL, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          mma_kmajor_kmajor<HD>(tmem_base, smem_u32(sQ), smem_u32(sK), idesc_s, false);
-          umma_commit(&s_full[0]);
-        }
-      }
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t % FWD_STAGES;
-        if (t + 1 < n_tiles) {
-          // S(t+1) into the other buffer: its previous content, S(t-1), was consumed before p_ready(t-1), waited below
-          const int s1 = (t + 1) % FWD_STAGES, ph1 = ((t + 1) / FWD_STAGES) & 1;
-          if (!at_wait(&kv_full[s1], ph1, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
-          tc_fence_after();
-          mma_kmajor_kmajor<HD>(tmem_base + ((t + 1) & 1) * AT_N, smem_u32(sQ), smem_u32(sK + s1 * TILE), idesc_s, false);
-          umma_commit(&s_full[(t + 1) & 1]);
-        }
+        const int s = t & 1, ph = (t >> 1) & 1;
+        if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        tc_fence_after();
+        // S(t) may overwrite S(t-1) only after the softmax threads have read it: p_ready(t-1) was waited below
+        mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
+        umma_commit(s_full);
         if (!at_wait(p_ready, t & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) break;
         tc_fence_after();
-        // p_ready(t) also says that O_part(t-1) has been read out of tensor memory
         mma_kmajor_mnmajor<AT_N>(tmem_O, smem_u32(sP), smem_u32(sV + s * TILE), idesc_o, false);
         umma_commit(o_full);
         umma_commit(&kv_empty[s]);
@@ -240,90 +225,75 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_fwd_kernel(const __gri
     }
     __syncwarp();
   } else {
-    float o[OC];
+    float o[HD];
 #pragma unroll
-    for (int d = 0; d < OC; ++d) o[d] = 0.f;
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const float sc = p.scale;
     bool ok = true;
-    // fold O_part of tile `u` (finished long ago) into the output registers
-    auto fold = [&](int u) -> bool {
-      if (!at_wait(o_full, u & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) return false;
-      tc_fence_after();
-      if constexpr (OC == 16) {
-        uint32_t rg[16];
-        tmem_ld_32x16(tmem_O + lane_base + cq * OC, rg);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 16; ++k) o[k] += __uint_as_float(rg[k]);
-      } else {
-        uint32_t rg[32];
-        tmem_ld_32x32(tmem_O + lane_base + cq * OC, rg);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 32; ++k) o[k] += __uint_as_float(rg[k]);
-      }
-      return true;
-    };
     for (int t = 0; t < n_tiles; ++t) {
       const int j0 = k_lo + t * AT_N;
-      if (!at_wait(&s_full[t & 1], (t >> 1) & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
-      float sv[32];
-      float mx = -INFINITY;
+      if (!at_wait(s_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
       const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
-      if (ok) {
-        tc_fence_after();
+      // pass A: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < AT_N / 32; ++c) {
         uint32_t rg[32];
-        tmem_ld_32x32(tmem_base + (t & 1) * AT_N + lane_base + cq * 32, rg);
+        tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const int j = j0 + cq * 32 + k;
-          const bool vis = row_ok && (!need_mask || (j <= i && j >= lo_i));
-          sv[k] = vis ? __uint_as_float(rg[k]) * sc : -INFINITY;
-          mx = fmaxf(mx, sv[k]);
+          const int j = j0 + c * 32 + k;
+          const bool vis = !need_mask || (j <= i && j >= lo_i);
+          if (vis) mx = fmaxf(mx, __uint_as_float(rg[k]) * sc);
         }
       }
-      float* mx_buf = sMax + (t & 1) * 4 * AT_M;
-      mx_buf[cq * AT_M + r] = mx;
-      // every compute thread reaches this barrier in every tile, also after a failed wait
-      asm volatile("bar.sync 1, 512;" ::: "memory");
-      if (!ok) continue;
-      float m_new = fmaxf(fmaxf(mx_buf[r], mx_buf[AT_M + r]), fmaxf(mx_buf[2 * AT_M + r], mx_buf[3 * AT_M + r]));
-      m_new = fmaxf(m, m_new);
-      if (!row_ok) m_new = 0.f;
+      if (!row_ok) mx = 0.f;
+      const float m_new = mx;
       const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
       float lsum = 0.f;
+      // pass B: probabilities -> shared memory (operand layout)
+#pragma unroll 1
+      for (int c = 0; c < AT_N / 32; ++c) {
+        uint32_t rg[32];
+        tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
+        tmem_ld_wait();
+        float pv[32];
 #pragma unroll
-      for (int k = 0; k < 32; ++k) {          // probabilities replace the scores in place
-        const float e = (m_new != -INFINITY && sv[k] != -INFINITY) ? __expf(sv[k] - m_new) : 0.f;
-        sv[k] = e;
-        lsum += e;
+        for (int k = 0; k < 32; ++k) {
+          const int j = j0 + c * 32 + k;
+          const bool vis = row_ok && (!need_mask || (j <= i && j >= lo_i));
+          const float e = (vis && m_new != -INFINITY) ? __expf(__uint_as_float(rg[k]) * sc - m_new) : 0.f;
+          pv[k] = e;
+          lsum += e;
+        }
+        store_p_chunk<T>(sP, r, c * 32, pv);
       }
-      // P(t) overwrites P(t-1): the P V product of tile t-1 must have finished reading it
-      if (t > 0 && !fold(t - 1)) { ok = false; }
-      if (ok) {
-#pragma unroll
-        for (int d = 0; d < OC; ++d) o[d] *= corr;      // everything gathered so far is relative to the old maximum
-        store_p_chunk<T>(sP, r, cq * 32, sv);
-        l = l * corr + lsum;
-        m = m_new;
-      }
+      l = l * corr + lsum;
+      m = m_new;
       tc_fence_before();
       fence_proxy_async();          // generic-proxy writes of P must be visible to the tensor core
       mbar_arrive(p_ready);
-    }
-    if (ok && n_tiles > 0 && !fold(n_tiles - 1)) ok = false;
-    tc_fence_before();
-    sL[cq * AT_M + r] = l;
-    asm volatile("bar.sync 1, 512;" ::: "memory");
-    if (ok && row_ok) {
-      const float lt = sL[r] + sL[AT_M + r] + sL[2 * AT_M + r] + sL[3 * AT_M + r];
-      const float inv_l = lt > 0.f ? 1.f / lt : 0.f;
-      T* op = reinterpret_cast<T*>(p.o) + (row_base + i) * p.ld_o + (long long)h * HD + cq * OC;
+      if (!at_wait(o_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < OC / 8; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t rg[32];
+        tmem_ld_32x32(tmem_O + lane_base + c * 32, rg);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) o[c * 32 + k] = o[c * 32 + k] * corr + __uint_as_float(rg[k]);
+      }
+      tc_fence_before();
+    }
+    if (ok && row_ok) {
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      T* op = reinterpret_cast<T*>(p.o) + (row_base + i) * p.ld_o + (long long)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
         uint4 q;
         q.x = Cvt<T>::pack2(o[8 * c + 0] * inv_l, o[8 * c + 1] * inv_l);
         q.y = Cvt<T>::pack2(o[8 * c + 2] * inv_l, o[8 * c + 3] * inv_l);
@@ -331,7 +301,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_fwd_kernel(const __gri
         q.w = Cvt<T>::pack2(o[8 * c + 6] * inv_l, o[8 * c + 7] * inv_l);
         reinterpret_cast<uint4*>(op)[c] = q;
       }
-      if (cq == 0 && p.lse) p.lse[(row_base + i) * p.H + h] = lt > 0.f ? m + __logf(lt) : INFINITY;
+      if (p.lse) p.lse[(row_base + i) * p.H + h] = l > 0.f ? m + __logf(l) : INFINITY;
     }
   }
   __syncthreads();
@@ -339,7 +309,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_fwd_kernel(const __gri
     for (int k = 0; k < 64; ++k) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
 }
 
 // ============================================================================================ backward: dQ
@@ -752,17 +722,18 @@ int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   AttnTcParams p{};
   p.B = a->B; p.T = a->T; p.H = a->H; p.KV = a->KV; p.window = a->window; p.scale = a->scale;
   p.lo = lo; p.o = a->o; p.ld_o = a->ld_o; p.lse = a->lse; p.status = status;
-  constexpr size_t smem = (size_t)AT_M * HD * 2 * (1 + 2 * FwdStages<HD>::value) + AT_M * AT_N * 2 + (2 * 4 + 4) * AT_M * 4 + 256 + 1024;
-  static_assert(smem <= 232448, "forward attention tiles exceed the shared memory of an SM");
+  constexpr size_t smem = (size_t)AT_M * HD * 2 * 5 + AT_M * AT_N * 2 + 128 + (HD == 64 ? 0 : 1024);
   auto kern = attn_tc_fwd_kernel<T, HD>;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -10;
+    // the largest shared-memory carve-out, so that two 112 KB CTAs fit one SM
+    (void)cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr = true;
   }
   if (a->B > 65535 || (a->T + AT_M - 1) / AT_M > 65535) return -1;   // grid y and z limits
   dim3 grid(a->H, a->B, (a->T + AT_M - 1) / AT_M);
-  kern<<<grid, AT_BWD_THREADS, smem, st>>>(tq, tk, tv, p);
+  kern<<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
   return gb_launch_rc();
 }
 

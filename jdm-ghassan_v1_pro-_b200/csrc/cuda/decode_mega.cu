@@ -454,9 +454,13 @@ struct Smem {          // static shared memory of the kernel
 // heads of the group in one walk.  The CTA whose range holds the step's own slot writes the new K (normalised,
 // rotated) and V there first.  Partial (max, sum, output) per (head, split) go to `scratch`.
 template <typename XT>
-__device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_mega_layer& L, int S, Smem& sm, float* amerge) {
+__device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_mega_layer& L, int S, Smem& sm, float* amerge,
+                                             unsigned long long*& prof) {
   const int item = blockIdx.x;
-  if (item >= a.KV * S) return;
+  if (item >= a.KV * S) {
+    if (prof) { const unsigned long long t = globaltimer_ns(); *prof++ = t; *prof++ = t; }
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hd = a.hd, G = a.H / a.KV, epl = hd / 32;
   const int kvh = item % a.KV, split = item / a.KV;
@@ -494,6 +498,7 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
         *reinterpret_cast<unsigned int*>(dv + i) = __ldcg(reinterpret_cast<const unsigned int*>(sv + i));
     }
     __syncthreads();
+    if (prof && g0 == 0) *prof++ = globaltimer_ns();          // queries rotated, the step's key and value stored
 
     float qv[4][4], m[4], l[4], o[4][4];
 #pragma unroll
@@ -506,23 +511,6 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
         qv[g][e] = (g < gc && e < epl) ? sm.q[g][lane * epl + e] : 0.f;
       }
     }
-    auto visit = [&](const float (&kf)[4], const float (&vf)[4]) {
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        if (g < gc) {
-          float dsum = 0.f;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) if (e < epl) dsum += qv[g][e] * kf[e];
-          dsum = warp_sum(dsum);
-          const float mn = fmaxf(m[g], dsum);
-          const float c = __expf(m[g] - mn), p = __expf(dsum - mn);
-          l[g] = l[g] * c + p;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) if (e < epl) o[g][e] = o[g][e] * c + p * vf[e];
-          m[g] = mn;
-        }
-      }
-    };
     auto live = [&](int j) {
       if (j >= hi) return false;
       if (a.window <= 0 || j == slot_new) return true;
@@ -535,15 +523,49 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
       for (int u = 0; u < 4; ++u) {
         const int ju = j + u * WARPS;
         ok[u] = live(ju);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) kf[u][e] = vf[u][e] = 0.f;
         if (ok[u]) {
           ld_epl<XT>(cK + (size_t)ju * kvd + (size_t)kvh * hd + lane * epl, epl, kf[u]);
           ld_epl<XT>(cV + (size_t)ju * kvd + (size_t)kvh * hd + lane * epl, epl, vf[u]);
         }
       }
+      // the dot products of all four slots with all heads of the group first, reduced over the lanes together (sixteen
+      // independent shuffles per step instead of one chain per slot and head), then the soft-max updates in slot order
+      float dots[4][4];
 #pragma unroll
       for (int u = 0; u < 4; ++u)
-        if (ok[u]) visit(kf[u], vf[u]);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float dsum = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) if (e < epl) dsum += qv[g][e] * kf[u][e];
+          dots[u][g] = dsum;
+        }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int g = 0; g < 4; ++g) dots[u][g] += __shfl_xor_sync(0xffffffffu, dots[u][g], off);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (!ok[u]) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (g < gc) {
+            const float dsum = dots[u][g];
+            const float mn = fmaxf(m[g], dsum);
+            const float c = __expf(m[g] - mn), p = __expf(dsum - mn);
+            l[g] = l[g] * c + p;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) if (e < epl) o[g][e] = o[g][e] * c + p * vf[u][e];
+            m[g] = mn;
+          }
+        }
+      }
     }
+    if (prof && g0 == 0) *prof++ = globaltimer_ns();          // this warp's slots walked
     // the sixteen warps meet in shared memory, in warp order
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -577,7 +599,8 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
 
 // Every CTA merges the S partial results of all heads into the 16-bit attention output in shared memory.
 template <typename XT>
-__device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& sm, float* ftab, XT* xs) {
+__device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& sm, float* ftab, XT* xs, float* part,
+                                            unsigned long long*& prof) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hd = a.hd, st = hd + 2;
   for (int h = warp; h < a.H; h += WARPS) {
@@ -594,14 +617,50 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
     if (lane == 0) sm.linv[h] = ls;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < a.H * hd; c += THREADS) {
-    const int h = c / hd, cc = c - h * hd;
-    const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
-    float oo = 0.f;
-#pragma unroll 16
-    for (int s = 0; s < S; ++s) oo += __ldcg(base + (size_t)s * st) * ftab[h * S + s];
-    const float ll = sm.linv[h];
-    xs[c] = Cvt<XT>::from_f(ll > 0.f ? oo / ll : 0.f);
+  if (prof) *prof++ = globaltimer_ns();                       // factors of every (head, split)
+  const int qd = a.H * hd;
+  if (2 * qd <= WARPS * 8 + WARPS * 4 * hd) {
+    // two threads per output, each over half of the splits, all loads of a half in flight at once; the halves meet in
+    // shared memory (the attention phase's merge area, free by now)
+    const int half = (S + 1) / 2;
+    for (int it = threadIdx.x; it < 2 * qd; it += THREADS) {
+      const int hf = it >= qd ? 1 : 0, c = it - hf * qd;
+      const int h = c / hd, cc = c - h * hd;
+      const int s0 = hf * half, s1 = min(S, s0 + half);
+      const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
+      // a rolled loop would wait for each load before it issued the next: fetch 16 splits at a time, then add
+      float oo = 0.f;
+      for (int sc = s0; sc < s1; sc += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = sc + j < s1 ? __ldcg(base + (size_t)(sc + j) * st) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (sc + j < s1) oo += v[j] * ftab[h * S + sc + j];
+      }
+      part[it] = oo;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < qd; c += THREADS) {
+      const float ll = sm.linv[c / hd];
+      xs[c] = Cvt<XT>::from_f(ll > 0.f ? (part[c] + part[qd + c]) / ll : 0.f);
+    }
+  } else {
+    for (int c = threadIdx.x; c < qd; c += THREADS) {
+      const int h = c / hd, cc = c - h * hd;
+      const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
+      float oo = 0.f;
+      for (int sc = 0; sc < S; sc += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = sc + j < S ? __ldcg(base + (size_t)(sc + j) * st) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (sc + j < S) oo += v[j] * ftab[h * S + sc + j];
+      }
+      const float ll = sm.linv[h];
+      xs[c] = Cvt<XT>::from_f(ll > 0.f ? oo / ll : 0.f);
+    }
   }
   __syncthreads();
 }
@@ -613,18 +672,47 @@ __device__ __forceinline__ void route_phase(const gb_mega_args& a, const gb_mega
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = a.d, ne = a.ne, top_k = a.top_k;
   if (ne > 0) {
-    for (int e = warp; e < ne; e += WARPS) {
-      const float* wr = L.router + (size_t)e * d;
+    // logits: `split` warps per expert, each over a contiguous part of the row with all its 16-byte loads in flight
+    // (a rolled loop of 8-byte loads per expert was most of this phase's time)
+    const int split = (2 * ne <= WARPS && d % 256 == 0) ? 2 : 1;
+    float* lg2 = sm.q[0];                                   // partial sums of the second halves (free in this phase)
+    for (int t = warp; t < ne * split; t += WARPS) {
+      const int e = t / split, hf = t - e * split;
+      const int len = d / split;                            // multiple of 128 when split == 2
+      const float* wr = L.router + (size_t)e * d + hf * len;
+      const XT* xr = xs + hf * len;
       float s = 0.f;
-      for (int i = lane * 2; i < d; i += 64) {
-        const float2 xv = Cvt<XT>::unpack2(*reinterpret_cast<const uint32_t*>(xs + i));
-        const float2 wv = *reinterpret_cast<const float2*>(wr + i);
-        s += xv.x * wv.x + xv.y * wv.y;
+      if (d % 256 == 0) {
+        float4 w[4];
+        uint2 xq[4];
+        const int n4 = len / 128;                           // 16-byte weight loads per lane (<= 4 per trip)
+        for (int c0 = 0; c0 < n4; c0 += 4) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c0 + j < n4) {
+              w[j] = *reinterpret_cast<const float4*>(wr + (size_t)(c0 + j) * 128 + lane * 4);
+              xq[j] = *reinterpret_cast<const uint2*>(xr + (size_t)(c0 + j) * 128 + lane * 4);
+            }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (c0 + j < n4) {
+              const float2 x0 = Cvt<XT>::unpack2(xq[j].x), x1 = Cvt<XT>::unpack2(xq[j].y);
+              s += x0.x * w[j].x + x0.y * w[j].y + x1.x * w[j].z + x1.y * w[j].w;
+            }
+        }
+      } else {
+        for (int i = lane * 2; i < len; i += 64) {
+          const float2 xv = Cvt<XT>::unpack2(*reinterpret_cast<const uint32_t*>(xr + i));
+          const float2 wv = *reinterpret_cast<const float2*>(wr + i);
+          s += xv.x * wv.x + xv.y * wv.y;
+        }
       }
       s = warp_sum(s);
-      if (lane == 0) sm.lg[e] = s;
+      if (lane == 0) { if (hf == 0) sm.lg[e] = s; else lg2[e] = s; }
     }
     __syncthreads();
+    if (split == 2 && (int)threadIdx.x < ne) sm.lg[threadIdx.x] += lg2[threadIdx.x];
+    if (split == 2) __syncthreads();
     if (threadIdx.x == 0) {
       float mx = -INFINITY;
       for (int e = 0; e < ne; ++e) mx = fmaxf(mx, sm.lg[e]);
@@ -709,7 +797,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   const int n_slots = min(a.cap, s0.cache_len + 1);
   const int S = max(1, min(min(a.max_splits, (int)gridDim.x / a.KV), (n_slots + 63) / 64));
 
-  // optional trace: CTA 0 records the global timer before and after every barrier (10 marks per layer + start and end)
+  // optional trace: CTA 0 records the global timer before and after every barrier and at six points inside the phases
+  // (16 marks per layer + start and end)
   unsigned long long* prof = (blockIdx.x == 0 && threadIdx.x == 0) ? a.prof : nullptr;
   auto mark = [&]() { if (prof) *prof++ = globaltimer_ns(); };
   mark();
@@ -749,7 +838,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     if (!(ok = grid_sync(gb))) break;
     mark();
     // ---- B: attention over the cache
-    attention_phase<XT>(a, L, S, sm, amerge);
+    attention_phase<XT>(a, L, S, sm, amerge, prof);
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
@@ -757,7 +846,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     // the thread that will write the output)
     const bool ownC = plC.KS > 1 && (int)threadIdx.x < plC.rows;
     const float resC = ownC ? __ldcg(x_in + blockIdx.x + threadIdx.x * gridDim.x) : 0.f;
-    merge_phase<XT>(a, S, sm, ftab, xs);
+    merge_phase<XT>(a, S, sm, ftab, xs, amerge, prof);
+    mark();                                                     // merged attention output in shared memory
     stream_run<FMT, XT>(phC, plC, xs, st, sm.red,
                         [&](int o, float v, float) { x_mid[o] = (ownC ? resC : __ldcg(x_in + o)) + v; });
     mark();
@@ -767,7 +857,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     Phase phE{reinterpret_cast<const uint8_t*>(L.wd), sm.off_e, sm.wsel, nsu_E, slots * nsu_E, false, false};
     {
       block_norm<XT>(x_mid, L.ffn_norm, xs, d, a.eps, sm.red[0]);
+      mark();
       route_phase<XT>(a, L, xs, sm, rb_E);
+      mark();
       if (threadIdx.x == 0) {
         sm.off_gu[0] = 0;
         sm.off_gu[1] = reinterpret_cast<const uint8_t*>(L.wu) - reinterpret_cast<const uint8_t*>(L.wg);

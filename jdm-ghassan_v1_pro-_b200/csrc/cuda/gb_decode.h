@@ -126,9 +126,9 @@ typedef struct gb_mega_args {
   int* r_idx; float* r_w;                        // router choice of the last layer (may be NULL)
   unsigned* sync;                                // 4 words, zero before the first launch, owned by the kernel afterwards
   int* status;                                   // set to 401 when a grid-wide wait ran out
-  unsigned long long* prof;                      // NULL, or 10 * n_layers + 2 words: CTA 0's global-timer marks in
-                                                 // nanoseconds (start; per layer the end of a phase and the start of
-                                                 // the next, i.e. both sides of each of the five barriers; end)
+  unsigned long long* prof;                      // NULL, or 16 * n_layers + 2 words: CTA 0's global-timer marks in
+                                                 // nanoseconds (start; per layer both sides of each of the five
+                                                 // barriers and six points inside the phases; end)
   int stage_bytes;                               // filled in by the launcher: shared-memory bytes per warp for staged rows
 } gb_mega_args;
 int gb_decode_mega_ok(const gb_mega_args* a);    // 0 when the shapes are covered, else a negative code

@@ -238,16 +238,30 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks, int staged) {
   if (e < a.ne) {
     if (a.counts) a.counts[e] += (float)s_total[e];
   }
-  if (threadIdx.x == 0 && a.aux_acc && a.aux_m && a.f_frac) {
+  if (a.aux_acc && a.aux_m && a.f_frac) {                      // uniform over the block
     // balance loss of this call: per segment ne * sum_e mean_prob[e] * slot_share[e], weighted by seg_weight (the
-    // segment's supervised tokens) when given.  f_frac was written above by this block (ordered by the barrier).
-    float tot = 0.f;
-    for (int sgi = 0; sgi < n_seg; ++sgi) {
+    // segment's supervised tokens) when given.  f_frac was written above by this block (ordered by the barriers).
+    // One thread per segment fetches its 2 * ne values (64 segments read by one thread were 1024 dependent loads, most
+    // of this kernel's time); thread 0 then adds the segments in order, so the sum is the same as a serial loop's.
+    __shared__ float s_seg[256];
+    auto seg_term = [&](int sgi) {
       float raw = 0.f;
       for (int i = 0; i < a.ne; ++i) raw += a.aux_m[(size_t)sgi * a.ne + i] * a.f_frac[(size_t)sgi * a.ne + i];
-      tot += (a.seg_weight ? a.seg_weight[sgi] : 1.f) * (float)a.ne * raw;
+      return (a.seg_weight ? a.seg_weight[sgi] : 1.f) * (float)a.ne * raw;
+    };
+    if (n_seg <= 256) {
+      if ((int)threadIdx.x < n_seg) s_seg[threadIdx.x] = seg_term(threadIdx.x);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int sgi = 0; sgi < n_seg; ++sgi) tot += s_seg[sgi];
+        a.aux_acc[0] += tot;
+      }
+    } else if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int sgi = 0; sgi < n_seg; ++sgi) tot += seg_term(sgi);
+      a.aux_acc[0] += tot;
     }
-    a.aux_acc[0] += tot;
   }
 }
 
@@ -409,101 +423,79 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const gb_moe_args 
 // Per token: sum the sorted-order input gradients of its slots, add the router path, write 16-bit dx and the
 // router-logit gradients (into `part`, [n_tok, ne]).
 template <typename T>
-__global__ void __launch_bounds__(256, 2) moe_router_bwd_kernel(const gb_moe_args a) {
-  // Two tokens per warp: the router rows (ne x d fp32) pass through L1 once for the pair.
-  const int tb = blockIdx.x * 16 + 2 * (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (tb >= a.n_tok) return;
+__global__ void __launch_bounds__(256, 4) moe_router_bwd_kernel(const gb_moe_args a) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= a.n_tok) return;
   const int ne = a.ne, K = a.top_k, S = K + (a.shared ? 1 : 0), d = a.d;
-  const bool two = tb + 1 < a.n_tok;
+  // ---- router-logit gradient (lane e and e+32 hold expert e / e+32)
+  // the slot positions first: they do not depend on the router part, and after its stores the compiler could not
+  // move these loads up by itself
+  int pos[MAX_K + 1];
+#pragma unroll
+  for (int s = 0; s <= MAX_K; ++s)
+    if (s < S) pos[s] = a.slot_pos[(size_t)t * S + s];
+  const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
+  const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
+  float dp0 = 0.f, dp1 = 0.f;
+  const int sgi = a.seg_tokens > 0 ? t / a.seg_tokens : 0;       // micro-batch segment of this token
+  const int tj = a.seg_tokens > 0 ? t - sgi * a.seg_tokens : t;
+  const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[sgi] : a.aux_coef;   // one coefficient per segment
   const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;
-  int pos[2][MAX_K + 1];
-  float dl0[2], dl1[2];
-#pragma unroll
-  for (int u = 0; u < 2; ++u) {
-    const int t = tb + ((u && two) ? 1 : 0);
-    // ---- router-logit gradient (lane e and e+32 hold expert e / e+32)
-    // the slot positions first: they do not depend on the router part, and after its stores the compiler could not
-    // move these loads up by itself
-#pragma unroll
-    for (int s = 0; s <= MAX_K; ++s)
-      if (s < S) pos[u][s] = a.slot_pos[(size_t)t * S + s];
-    const float p0 = lane < ne ? a.probs[(size_t)t * ne + lane] : 0.f;
-    const float p1 = lane + 32 < ne ? a.probs[(size_t)t * ne + lane + 32] : 0.f;
-    float dp0 = 0.f, dp1 = 0.f;
-    const int sgi = a.seg_tokens > 0 ? t / a.seg_tokens : 0;       // micro-batch segment of this token
-    const int tj = a.seg_tokens > 0 ? t - sgi * a.seg_tokens : t;
-    const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[sgi] : a.aux_coef;   // one coefficient per segment
-    if (a.f_frac && aux_coef != 0.f) {
-      const float* ff = a.f_frac + (size_t)sgi * ne;
-      if (lane < ne) dp0 = aux_coef * ff[lane];
-      if (lane + 32 < ne) dp1 = aux_coef * ff[lane + 32];
-    }
-    float ssum = 0.f, gbar = 0.f;
+  if (a.f_frac && aux_coef != 0.f) {
+    const float* ff = a.f_frac + (size_t)sgi * ne;
+    if (lane < ne) dp0 = aux_coef * ff[lane];
+    if (lane + 32 < ne) dp1 = aux_coef * ff[lane + 32];
+  }
+  float ssum = 0.f, gbar = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int e = a.idx[(size_t)t * K + k];
+    const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);   // probs[t, e], already in a lane
+    ssum += pe;
+    gbar += a.gdot[(size_t)t * K + k] * a.w[(size_t)t * K + k];
+  }
+  if (ssum > 1e-8f) {
+    const float invs = 1.f / ssum;
     for (int k = 0; k < K; ++k) {
       const int e = a.idx[(size_t)t * K + k];
-      const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);   // probs[t, e], already in a lane
-      ssum += pe;
-      gbar += a.gdot[(size_t)t * K + k] * a.w[(size_t)t * K + k];
-    }
-    if (ssum > 1e-8f) {
-      const float invs = 1.f / ssum;
-      for (int k = 0; k < K; ++k) {
-        const int e = a.idx[(size_t)t * K + k];
-        const float v = (a.gdot[(size_t)t * K + k] - gbar) * invs;
-        if (e == lane) dp0 += v;
-        if (e == lane + 32) dp1 += v;
-      }
-    }
-    const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
-    dl0[u] = p0 * (dp0 - pdp);
-    dl1[u] = p1 * (dp1 - pdp);
-    if (a.use_jitter) {
-      dl0[u] *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane, jseed);
-      dl1[u] *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane + 32, jseed);
-    }
-    if (u == 0 || two) {
-      if (lane < ne) a.part[(size_t)t * ne + lane] = dl0[u];
-      if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1[u];
+      const float v = (a.gdot[(size_t)t * K + k] - gbar) * invs;
+      if (e == lane) dp0 += v;
+      if (e == lane + 32) dp1 += v;
     }
   }
+  const float pdp = warp_sum(p0 * dp0 + p1 * dp1);
+  float dl0 = p0 * (dp0 - pdp), dl1 = p1 * (dp1 - pdp);
+  if (a.use_jitter) {
+    dl0 *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane, jseed);
+    dl1 *= 1.0f + a.jitter * 2.0f * jitter_u(tj, lane + 32, jseed);
+  }
+  if (lane < ne) a.part[(size_t)t * ne + lane] = dl0;
+  if (lane + 32 < ne) a.part[(size_t)t * ne + lane + 32] = dl1;
   // ---- input gradient
   const T* dxp = reinterpret_cast<const T*>(a.dx_perm);
   T* dx = reinterpret_cast<T*>(a.dx16);
   for (int i = lane * 8; i < d; i += 256) {
-    float acc[2][8];
+    float acc[8];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
-#pragma unroll
-      for (int s = 0; s <= MAX_K; ++s)
-        if (s < S) {
-          const uint4 q = *reinterpret_cast<const uint4*>(dxp + (size_t)pos[u][s] * d + i);
-          const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
-          acc[u][0] += v0.x; acc[u][1] += v0.y; acc[u][2] += v1.x; acc[u][3] += v1.y;
-          acc[u][4] += v2.x; acc[u][5] += v2.y; acc[u][6] += v3.x; acc[u][7] += v3.y;
-        }
-    }
+    for (int s = 0; s <= MAX_K; ++s)
+      if (s < S) {
+        const uint4 q = *reinterpret_cast<const uint4*>(dxp + (size_t)pos[s] * d + i);
+        const float2 v0 = Cvt<T>::unpack2(q.x), v1 = Cvt<T>::unpack2(q.y), v2 = Cvt<T>::unpack2(q.z), v3 = Cvt<T>::unpack2(q.w);
+        acc[0] += v0.x; acc[1] += v0.y; acc[2] += v1.x; acc[3] += v1.y; acc[4] += v2.x; acc[5] += v2.y; acc[6] += v3.x; acc[7] += v3.y;
+      }
 #pragma unroll 4
     for (int e = 0; e < ne; ++e) {
+      const float dl = __shfl_sync(0xffffffffu, e < 32 ? dl0 : dl1, e & 31);
       const float4 w0 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i);
       const float4 w1 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + i + 4);
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const float dl = __shfl_sync(0xffffffffu, e < 32 ? dl0[u] : dl1[u], e & 31);
-        acc[u][0] += dl * w0.x; acc[u][1] += dl * w0.y; acc[u][2] += dl * w0.z; acc[u][3] += dl * w0.w;
-        acc[u][4] += dl * w1.x; acc[u][5] += dl * w1.y; acc[u][6] += dl * w1.z; acc[u][7] += dl * w1.w;
-      }
+      acc[0] += dl * w0.x; acc[1] += dl * w0.y; acc[2] += dl * w0.z; acc[3] += dl * w0.w;
+      acc[4] += dl * w1.x; acc[5] += dl * w1.y; acc[6] += dl * w1.z; acc[7] += dl * w1.w;
     }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      if (u == 0 || two) {
-        uint4 o;
-        o.x = Cvt<T>::pack2(acc[u][0], acc[u][1]); o.y = Cvt<T>::pack2(acc[u][2], acc[u][3]);
-        o.z = Cvt<T>::pack2(acc[u][4], acc[u][5]); o.w = Cvt<T>::pack2(acc[u][6], acc[u][7]);
-        *reinterpret_cast<uint4*>(dx + (size_t)(tb + u) * d + i) = o;
-      }
-    }
+    uint4 o;
+    o.x = Cvt<T>::pack2(acc[0], acc[1]); o.y = Cvt<T>::pack2(acc[2], acc[3]);
+    o.z = Cvt<T>::pack2(acc[4], acc[5]); o.w = Cvt<T>::pack2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(dx + (size_t)t * d + i) = o;
   }
 }
 
@@ -653,7 +645,7 @@ extern "C" int gb_moe_combine_bwd(const gb_moe_args* a, cudaStream_t st) {
 extern "C" int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st) {
   int rc = moe_check(a);
   if (rc) return rc;
-  const int grid = (a->n_tok + 15) / 16;      // two tokens per warp, eight warps per block
+  const int grid = (a->n_tok + 7) / 8;
   // token chunks for the router weight gradient: partials in part2 ([chunks, ne, d]) when it is provided
   int chunks = a->part2 ? (a->n_tok + 31) / 32 : 1;   // 32 tokens per thread: 8192 tokens fill 1536 blocks
   if (chunks > GB_ROUTER_WGRAD_CHUNKS) chunks = GB_ROUTER_WGRAD_CHUNKS;

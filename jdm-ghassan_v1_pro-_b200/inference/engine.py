@@ -254,13 +254,14 @@ class InferenceEngine:
     def trace_phases(self, n_tokens: int = 16) -> Dict[str, float]:
         """Mean microseconds that CTA 0 of the one-kernel step spends in each phase of a layer and at the barrier
         behind it, over ``n_tokens`` eager steps from the current state (the marks come from the device's global
-        timer).  Keys: A (norm + QKV), B (attention), C (merge + output projection), D (norm + router + gate/up), E
-        (down projection), ``wait_X`` for the barrier after phase X, ``head`` and ``step``."""
+        timer).  Keys: A (norm + QKV), B (attention: ``B_rope``, ``B_walk``, ``B_merge``), C (``C_factors``, ``C_sum``,
+        ``C_proj``), D (``D_norm``, ``D_route``, ``D_experts``), E (down projection), ``wait_X`` for the barrier after
+        phase X, ``head`` and ``step``."""
         assert self.mega is not None, "the one-kernel token step is not in use"
-        nl = self.cfg.num_layers
-        buf = torch.zeros(10 * nl + 2, dtype=torch.int64, device=self.dev)
+        nl, M = self.cfg.num_layers, 16
+        buf = torch.zeros(M * nl + 2, dtype=torch.int64, device=self.dev)
         self.mega.prof = buf.data_ptr()
-        acc = np.zeros(10 * nl + 1)
+        acc = np.zeros(M * nl + 1)
         try:
             for _ in range(n_tokens):
                 self._forward_token()
@@ -269,11 +270,14 @@ class InferenceEngine:
         finally:
             self.mega.prof = None
         acc /= n_tokens * 1e3
-        per = acc[:10 * nl].reshape(nl, 10)              # A, wait, B, wait, C, wait, D, wait, E, wait
-        names = ["A", "wait_A", "B", "wait_B", "C", "wait_C", "D", "wait_D", "E", "wait_E"]
+        per = acc[:M * nl].reshape(nl, M)
+        names = ["A", "wait_A", "B_rope", "B_walk", "B_merge", "wait_B", "C_factors", "C_sum", "C_proj", "wait_C", "D_norm",
+                 "D_route", "D_experts", "wait_D", "E", "wait_E"]
         out = {k: float(per[:, i].mean()) for i, k in enumerate(names)}
+        for ph in "BCD":
+            out[ph] = sum(v for k, v in out.items() if k.startswith(ph + "_"))
         out["layer"] = float(per.sum(1).mean())
-        out["head"] = float(acc[10 * nl])
+        out["head"] = float(acc[M * nl])
         out["step"] = float(acc.sum())
         return out
 
