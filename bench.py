@@ -49,11 +49,17 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index=0, period_ms=200):
+    def __init__(self, index=0, period_ms=100):
         self.index, self.period_ms = index, period_ms
         self.proc = None
-        self.lines = []
+        self.lines = []            # (host time of arrival, line)
         self._t = None
+        self._begin = 0.0
+
+    def begin(self):
+        """The timed region starts now: samples that arrived earlier (the tool takes a few hundred milliseconds to
+        print its first line, so it is started ahead of the region) are not counted."""
+        self._begin = time.time()
 
     def start(self):
         smi = shutil.which("nvidia-smi")
@@ -71,7 +77,7 @@ class ClockSampler:
 
     def _read(self):
         for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+            self.lines.append((time.time(), ln.strip()))
 
     def stop(self):
         if self.proc is not None:
@@ -83,7 +89,9 @@ class ClockSampler:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for at, ln in self.lines:
+            if at < self._begin:
+                continue
             p = [x.strip() for x in ln.split(",")]
             if len(p) < 7:
                 continue
@@ -207,7 +215,10 @@ def run_ours(args):
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if float(ok) > 0:
             break
-    for _ in range(args.warmup):
+    sampler = ClockSampler(local)
+    for i in range(args.warmup):
+        if i == args.warmup - 1:
+            sampler.start()        # running by the time the timed region starts
         tr.train_step()
 
     def fence():
@@ -216,9 +227,10 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- phase A: device-timed
-    sampler = ClockSampler(local)
     fence()
-    sampler.start()
+    if sampler.proc is None:
+        sampler.start()
+    sampler.begin()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = eng.kernel_launches
     ev0.record()

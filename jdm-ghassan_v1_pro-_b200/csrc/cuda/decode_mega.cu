@@ -455,7 +455,7 @@ struct Smem {          // static shared memory of the kernel
 // rotated) and V there first.  Partial (max, sum, output) per (head, split) go to `scratch`.
 template <typename XT>
 __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_mega_layer& L, int S, Smem& sm, float* amerge,
-                                             unsigned long long*& prof) {
+                                             const gb_seq_state s, int pos_now, unsigned long long*& prof) {
   const int item = blockIdx.x;
   if (item >= a.KV * S) {
     if (prof) { const unsigned long long t = globaltimer_ns(); *prof++ = t; *prof++ = t; }
@@ -464,8 +464,7 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hd = a.hd, G = a.H / a.KV, epl = hd / 32;
   const int kvh = item % a.KV, split = item / a.KV;
-  const gb_seq_state s = a.state[0];
-  const int n_slots = min(a.cap, s.cache_len + 1);
+  const int n_slots = min(a.cap, s.cache_len + 1);       // s: the sequence state, read once per step by the caller
   const int slot_new = s.cache_len < a.cap ? s.cache_len : a.pinned + s.ring_start;
   const int per = (n_slots + S - 1) / S;
   const int lo = split * per, hi = min(n_slots, lo + per);
@@ -474,7 +473,7 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
   const long long kvd = (long long)a.KV * hd;
   XT* cK = reinterpret_cast<XT*>(L.cache_k);
   XT* cV = reinterpret_cast<XT*>(L.cache_v);
-  const float* csr = a.cos_sin + (size_t)a.pos[0] * hd;
+  const float* csr = a.cos_sin + (size_t)pos_now * hd;
   float* am = amerge;                         // [WARPS][4]
   float* al = amerge + WARPS * 4;             // [WARPS][4]
   float* ao = amerge + WARPS * 8;             // [WARPS][4][hd]
@@ -623,22 +622,35 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
     // two threads per output, each over half of the splits, all loads of a half in flight at once; the halves meet in
     // shared memory (the attention phase's merge area, free by now)
     const int half = (S + 1) / 2;
-    for (int it = threadIdx.x; it < 2 * qd; it += THREADS) {
-      const int hf = it >= qd ? 1 : 0, c = it - hf * qd;
-      const int h = c / hd, cc = c - h * hd;
-      const int s0 = hf * half, s1 = min(S, s0 + half);
-      const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
-      // a rolled loop would wait for each load before it issued the next: fetch 16 splits at a time, then add
-      float oo = 0.f;
-      for (int sc = s0; sc < s1; sc += 16) {
-        float v[16];
+    // a thread's items are THREADS apart; the partial outputs of up to three items (twelve splits each) are fetched
+    // before any is used, so that one memory round trip covers them all; larger cases go through the loops again
+    for (int it0 = threadIdx.x; it0 < 2 * qd; it0 += 3 * THREADS) {
+      for (int sc = 0; sc < half; sc += 12) {
+        float v[3][12];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = sc + j < s1 ? __ldcg(base + (size_t)(sc + j) * st) : 0.f;
+        for (int k = 0; k < 3; ++k) {
+          const int it = it0 + k * THREADS;
+          const int hf = it >= qd ? 1 : 0, c = it - hf * qd;
+          const int h = c / hd, cc = c - h * hd;
+          const int s0 = hf * half + sc, s1 = min(S, hf * half + half);
+          const float* base = a.att_scratch + (size_t)h * S * st + 2 + cc;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (sc + j < s1) oo += v[j] * ftab[h * S + sc + j];
+          for (int j = 0; j < 12; ++j) v[k][j] = (it < 2 * qd && s0 + j < s1) ? __ldcg(base + (size_t)(s0 + j) * st) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+          const int it = it0 + k * THREADS;
+          if (it >= 2 * qd) continue;
+          const int hf = it >= qd ? 1 : 0, c = it - hf * qd;
+          const int h = c / hd;
+          const int s0 = hf * half + sc, s1 = min(S, hf * half + half);
+          float oo = sc == 0 ? 0.f : part[it];
+#pragma unroll
+          for (int j = 0; j < 12; ++j)
+            if (s0 + j < s1) oo += v[k][j] * ftab[h * S + s0 + j];
+          part[it] = oo;
+        }
       }
-      part[it] = oo;
     }
     __syncthreads();
     for (int c = threadIdx.x; c < qd; c += THREADS) {
@@ -668,7 +680,8 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
 // Router of the normalised activations in shared memory (rules of route_in_block in decode.cu), then the tables the
 // expert phases index by slot: expert, weight, byte offset of the expert's down-projection block.
 template <typename XT>
-__device__ __forceinline__ void route_phase(const gb_mega_args& a, const gb_mega_layer& L, const XT* xs, Smem& sm, long long rb_E) {
+__device__ __forceinline__ void route_phase(const gb_mega_args& a, const gb_mega_layer& L, const XT* xs, Smem& sm, long long rb_E,
+                                            const float* router_rows) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = a.d, ne = a.ne, top_k = a.top_k;
   if (ne > 0) {
@@ -679,7 +692,7 @@ __device__ __forceinline__ void route_phase(const gb_mega_args& a, const gb_mega
     for (int t = warp; t < ne * split; t += WARPS) {
       const int e = t / split, hf = t - e * split;
       const int len = d / split;                            // multiple of 128 when split == 2
-      const float* wr = L.router + (size_t)e * d + hf * len;
+      const float* wr = router_rows + (size_t)e * d + hf * len;    // shared memory when staged, else the global rows
       const XT* xr = xs + hf * len;
       float s = 0.f;
       if (d % 256 == 0) {
@@ -794,6 +807,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   // number of cache splits: about 64 slots per CTA (four per warp, fetched in one trip), at most what the grid and
   // the scratch hold
   const gb_seq_state s0 = a.state[0];
+  const int pos_now = a.pos[0];
   const int n_slots = min(a.cap, s0.cache_len + 1);
   const int S = max(1, min(min(a.max_splits, (int)gridDim.x / a.KV), (n_slots + 63) / 64));
 
@@ -805,6 +819,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
 
   // per-warp staging slice and barriers
   __shared__ __align__(8) uint64_t bars[WARPS * MAXI];
+  // the router rows of a layer (ne x d fp32, the same for every token) are staged a phase and a half ahead too, into the
+  // area that only the vocabulary projection of block formats uses
+  __shared__ __align__(8) uint64_t rbar;
+  const uint32_t router_bytes = a.ne > 0 ? (uint32_t)a.ne * (uint32_t)d * 4u : 0u;
+  const bool router_staged = router_bytes > 0 && router_bytes <= (uint32_t)(WARPS * GROUP * 512);
+  uint32_t rparity = 0;
+  bool rpending = false;
+  if (threadIdx.x == 0) mbar_init(&rbar, 1);
   const int warp_id = threadIdx.x >> 5;
   Stage st{wstage + (size_t)warp_id * a.stage_bytes, bars + warp_id * MAXI, 0u, 0u, &sm.dead, a.status};
   if ((threadIdx.x & 31) == 0) {
@@ -833,12 +855,20 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       Phase ph{reinterpret_cast<const uint8_t*>(L.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
       stream_run<FMT, XT>(ph, plA, xs, st, sm.red, [&](int o, float v, float) { qkv[o] = Cvt<XT>::from_f(v); });
       stream_issue<FMT>(phC, plC, st, rowC);
+      if (router_staged) {
+        if (threadIdx.x == THREADS - 32) {       // every thread's reads of the previous layer's rows lie barriers back
+          fence_proxy_async();
+          mbar_arrive_expect_tx(&rbar, router_bytes);
+          bulk_g2s(smem_u32(stage_all), L.router, router_bytes, smem_u32(&rbar));
+        }
+        rpending = true;
+      }
     }
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
     // ---- B: attention over the cache
-    attention_phase<XT>(a, L, S, sm, amerge, prof);
+    attention_phase<XT>(a, L, S, sm, amerge, s0, pos_now, prof);
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
@@ -858,7 +888,17 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     {
       block_norm<XT>(x_mid, L.ffn_norm, xs, d, a.eps, sm.red[0]);
       mark();
-      route_phase<XT>(a, L, xs, sm, rb_E);
+      const float* router_rows = L.router;
+      if (rpending) {
+        if (!mbar_wait(&rbar, rparity)) {
+          if (threadIdx.x == 0) { sm.dead = 1; atomicCAS(a.status, 0, ST_TIMEOUT_COPY); }
+        } else {
+          router_rows = reinterpret_cast<const float*>(stage_all);
+        }
+        rparity ^= 1u;
+        rpending = false;
+      }
+      route_phase<XT>(a, L, xs, sm, rb_E, router_rows);
       mark();
       if (threadIdx.x == 0) {
         sm.off_gu[0] = 0;
@@ -913,6 +953,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   // shared memory they target goes away
   for (int k = 0; k < MAXI; ++k)
     if (st.pending >> k & 1u) (void)mbar_wait(st.bars + k, (st.parity >> k) & 1u);
+  if (rpending) (void)mbar_wait(&rbar, rparity);
   mark();
   // ---- bookkeeping: the last CTA out records where the arrival count stands; CTA 0 advances the sequence state
   __syncthreads();

@@ -138,8 +138,11 @@ def parity(work):
             d = float(np.abs(wa[n] - wb[n]).max()) / (float(np.abs(wb[n]).max()) + 1e-9)
             worst = max(worst, d)
         # sign updates (Lion) and the bf16 operands of Newton-Schulz (Muon) amplify last-bit differences of the reduced
-        # gradient; AdamW after two steps does not
-        tol = 2e-3 if opt == "adamw" else 2e-2
+        # gradient.  AdamW in its first steps divides every element by its own |g| (v is about g^2), so an element whose
+        # reduced gradient is near zero moves by about +-lr whichever sign the summation order (rank order here, NCCL's
+        # ring there) left it with: the bound is a few lr relative to the largest weight, and it grows with the number of
+        # ranks whose partial sums can differ.
+        tol = (2e-3 if dist.get_world_size() <= 2 else 6e-3) if opt == "adamw" else 2e-2
         if worst > tol:
             print(rank, opt, "weights differ", worst, flush=True)
             ok = False
