@@ -855,6 +855,22 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       Phase ph{reinterpret_cast<const uint8_t*>(L.wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
       stream_run<FMT, XT>(ph, plA, xs, st, sm.red, [&](int o, float v, float) { qkv[o] = Cvt<XT>::from_f(v); });
       stream_issue<FMT>(phC, plC, st, rowC);
+      if ((int)blockIdx.x < a.KV * S) {
+        // this CTA's slice of the cache is known before the queries are: ask L2 for its rows now (a cache row was last
+        // touched a token ago, 1.2 GB of weights back, so it would otherwise come from DRAM inside the walk)
+        const int kvh = blockIdx.x % a.KV, split = blockIdx.x / a.KV;
+        const int per = (n_slots + S - 1) / S;
+        const int lo = split * per, hi = min(n_slots, lo + per);
+        const int lane = threadIdx.x & 31;
+        const size_t row_elems = (size_t)a.KV * hd;
+        if (lane * 64 < hd)                                    // one 128-byte line per 64 values
+          for (int j = lo + warp_id; j < hi; j += WARPS) {
+            const XT* kp = reinterpret_cast<const XT*>(L.cache_k) + (size_t)j * row_elems + (size_t)kvh * hd + lane * 64;
+            const XT* vp = reinterpret_cast<const XT*>(L.cache_v) + (size_t)j * row_elems + (size_t)kvh * hd + lane * 64;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(kp));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vp));
+          }
+      }
       if (router_staged) {
         if (threadIdx.x == THREADS - 32) {       // every thread's reads of the previous layer's rows lie barriers back
           fence_proxy_async();
