@@ -294,8 +294,9 @@ def run_ours(args):
 
 
 def run_decode(args, local):
-    """Batch-1 decode of the recipe's model (random-initialised) for three weight formats: tokens/s with CUDA events
-    around the decode steps, SM clocks sampled meanwhile.  Runs after the training measurement has released the GPU."""
+    """Decode of the recipe's model (random-initialised): one sequence for three weight formats and 32 sequences for
+    two, tokens/s with CUDA events around the decode steps, SM clocks sampled meanwhile.  Runs after the training
+    measurement has released the GPU."""
     import torch
     from ghassan_b200.inference.engine import InferenceEngine, SamplingParams
     from ghassan_b200.inference.generator import Generator
@@ -314,6 +315,17 @@ def run_decode(args, local):
         r = Generator(eng).benchmark(args.decode_prompt, args.decode_new, sp, 1234)
         out[fmt] = {"tokens_per_s": r["decode_tokens_per_s"], "ms_per_token": r["decode_ms_per_token"],
                     "stored_weight_bytes": r["stored_weight_bytes"], "prefill_ms": r["prefill_ms"]}
+        del eng
+        torch.cuda.empty_cache()
+    # 32 sequences: the token step runs its projections and experts as tensor-core GEMMs over 16-bit weight copies
+    out["batch_32"] = {"token_step": "tcgen05 GEMMs over 16-bit weight copies, attention per sequence over the cache",
+                       "new_tokens": min(args.decode_new, 128)}
+    for fmt in ("f16", "q4_0"):
+        eng = InferenceEngine(cfg, named, fmt=fmt, batch=32, max_len=args.decode_prompt + args.decode_new + 8,
+                              prefill_chunk=args.decode_prompt)
+        r = Generator(eng).benchmark(args.decode_prompt, min(args.decode_new, 128), sp, 1234)
+        out["batch_32"][fmt] = {"tokens_per_s": r["decode_tokens_per_s"], "ms_per_step": r["decode_ms_per_token"],
+                                "prefill_ms": r["prefill_ms"]}
         del eng
         torch.cuda.empty_cache()
     out["clocks"] = sampler.stop()
