@@ -314,7 +314,8 @@ def run_decode(args, local):
                               prefill_chunk=args.decode_prompt)
         r = Generator(eng).benchmark(args.decode_prompt, args.decode_new, sp, 1234)
         out[fmt] = {"tokens_per_s": r["decode_tokens_per_s"], "ms_per_token": r["decode_ms_per_token"],
-                    "stored_weight_bytes": r["stored_weight_bytes"], "prefill_ms": r["prefill_ms"]}
+                    "stored_weight_bytes": r["stored_weight_bytes"], "prefill_ms": r["prefill_ms"],
+                    "token_step": "one cooperative kernel" if eng.mega is not None else "kernel chain"}
         del eng
         torch.cuda.empty_cache()
     # 32 sequences: the token step runs its projections and experts as tensor-core GEMMs over 16-bit weight copies

@@ -347,7 +347,7 @@ def app_suite(dev: str, work: str, suite: Optional[Suite] = None) -> Suite:
             rc, out = s.call(INF.main, ["chat", "--model", f16, "--max-tokens", "12", "--no-stream"])
         finally:
             sys.stdin = old
-        (s.ok if rc == 0 else s.bad)("chat session ended cleanly")
+        (s.ok if rc == 0 else s.bad)("chat session ended cleanly" + ("" if rc == 0 else ": " + out.strip()[-300:]))
         rc, out = s.call(INF.main, ["bench", "--model", f16, "--prompt-tokens", "16", "--tokens", "24", "--greedy"])
         try:
             r = json.loads(out.strip().splitlines()[-1])

@@ -624,12 +624,17 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
     const int half = (S + 1) / 2;
     // a thread's items are THREADS apart; the partial outputs of up to three items (twelve splits each) are fetched
     // before any is used, so that one memory round trip covers them all; larger cases go through the loops again
+    // Every CTA reads all partial outputs.  Walking them in the same order at the same time would put all 148 SMs on
+    // the same few L2 lines at every moment, so each CTA starts at its own offset into the item list.
+    const int rot = (int)((blockIdx.x * 53u) % (unsigned)(2 * qd));
+    auto item_of = [&](int i) { const int r = i + rot; return r >= 2 * qd ? r - 2 * qd : r; };
     for (int it0 = threadIdx.x; it0 < 2 * qd; it0 += 3 * THREADS) {
       for (int sc = 0; sc < half; sc += 12) {
         float v[3][12];
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
-          const int it = it0 + k * THREADS;
+          const int iu = it0 + k * THREADS;
+          const int it = iu < 2 * qd ? item_of(iu) : iu;
           const int hf = it >= qd ? 1 : 0, c = it - hf * qd;
           const int h = c / hd, cc = c - h * hd;
           const int s0 = hf * half + sc, s1 = min(S, hf * half + half);
@@ -639,8 +644,9 @@ __device__ __forceinline__ void merge_phase(const gb_mega_args& a, int S, Smem& 
         }
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
-          const int it = it0 + k * THREADS;
-          if (it >= 2 * qd) continue;
+          const int iu = it0 + k * THREADS;
+          if (iu >= 2 * qd) continue;
+          const int it = item_of(iu);
           const int hf = it >= qd ? 1 : 0, c = it - hf * qd;
           const int h = c / hd;
           const int s0 = hf * half + sc, s1 = min(S, hf * half + half);

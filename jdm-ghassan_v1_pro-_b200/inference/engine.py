@@ -81,7 +81,7 @@ class InferenceEngine:
         """``named``: fp32 tensors by parameter name.  ``fmt``: decode weight format, or "auto" with ``raw`` (an object
         with ``tensor_raw(name)``, e.g. a GGUF file) and ``raw_types`` (name -> ggml type) to take the stored bytes.
         ``single_kernel``: run the token step of a batch of one as one cooperative kernel (``csrc/cuda/decode_mega.cu``)
-        when the shapes allow it; None takes the default (``GB200_DECODE_MEGA``).  ``gemm_min_batch``: from this many
+        when the shapes allow it; None takes the default (on; ``GB200_DECODE_MEGA=0`` turns it off).  ``gemm_min_batch``: from this many
         sequences on, the token step runs its projections and experts as tensor-core GEMMs over 16-bit copies of the
         weights (the ones the prompt pass keeps) instead of per-sequence GEMV kernels over the stored bytes; None
         takes ``GB200_DECODE_GEMM_MIN_BATCH`` (default 8), 0 turns it off."""
@@ -198,7 +198,7 @@ class InferenceEngine:
         self._graph_key = None
         self.mega: Optional[D.MegaArgs] = None
         if single_kernel is None:
-            single_kernel = os.environ.get("GB200_DECODE_MEGA", "0") == "1"
+            single_kernel = os.environ.get("GB200_DECODE_MEGA", "1") != "0"
         if single_kernel and batch == 1:
             self._build_mega()
         self.prefill_chunk = min(prefill_chunk, max_len)
@@ -337,8 +337,13 @@ class InferenceEngine:
         """Embedding of ``cur_tok`` through all layers to fp32 logits; advances the per-sequence state."""
         cfg = self.cfg
         if self.mega is not None:
-            D.decode_mega(self.mega)
-            return
+            try:
+                D.decode_mega(self.mega)
+                return
+            except RuntimeError as e:      # the launch itself was refused (e.g. no cooperative launch): use the kernel chain
+                from ..utils.log import log_warn
+                log_warn("[decode] one-kernel token step not available (%s); using the kernel chain" % e)
+                self.mega = None
         if self.batched:
             self._step_net().decode_forward(self)
             D.decode_advance(self.state, self.pos, self.cap, PINNED_TOKENS)
@@ -431,11 +436,15 @@ class InferenceEngine:
         the batched forward pass, whose K/V land in the cache; the rest (and the last prompt token, which produces
         the first logits) go through the decode step."""
         B, n = prompts.shape
-        assert B == self.B and n >= 1 and n <= self.cap
+        if B != self.B or n < 1:
+            raise ValueError("prefill needs [%d, n >= 1] token ids, got %s" % (self.B, tuple(prompts.shape)))
         prompts = prompts.to(self.dev, dtype=torch.int32)
-        self.history[:, :n].copy_(prompts)
-        self.hist_len.fill_(n)
-        head = min(n - 1, self.prefill_chunk) if n - 1 >= 64 else 0    # short prompts are cheaper token by token
+        keep = min(n, self.hist_cap)                       # the penalty window looks at the most recent tokens only
+        self.history[:, :keep].copy_(prompts[:, n - keep:])
+        self.hist_len.fill_(keep)
+        # A prompt longer than the cache goes token by token: the ring keeps the first tokens and the most recent ones
+        # (inference/kv_cache.h:11-106 in the reference), which the batched pass cannot express.
+        head = min(n - 1, self.prefill_chunk) if (n - 1 >= 64 and n <= self.cap) else 0
         if head > 0:
             m = self._prefill_net()
             T = self.prefill_chunk
