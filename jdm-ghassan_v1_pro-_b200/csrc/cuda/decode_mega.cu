@@ -76,8 +76,13 @@ __device__ __forceinline__ bool grid_sync(GridBar& gb) {
     unsigned it = 0;
     unsigned long long t0 = 0;
     for (;;) {
+      // A relaxed load on purpose.  An acquire at GPU scope empties this SM's L1, and with it the registers the kernel
+      // has spilled to local memory: every phase then began with their reload from L2 (ncu: 65 % of the local loads
+      // missed L1).  What other CTAs wrote before they arrived is read with ld.global.cg or by bulk copies, both of
+      // which go to L2 and never to this L1, and the writers release (red.release.gpu) after their stores; the
+      // __syncthreads below keeps every thread's reads behind thread 0's observation of the count.
       unsigned v;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(gb.cnt) : "memory");
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(gb.cnt) : "memory");
       if ((int)(v - gb.next) >= 0) break;
       ++it;
       if (it == 2048) t0 = globaltimer_ns();
@@ -513,7 +518,7 @@ __device__ __noinline__ void attention_phase(const gb_mega_args& a, const gb_meg
     auto live = [&](int j) {
       if (j >= hi) return false;
       if (a.window <= 0 || j == slot_new) return true;
-      return s.abs_pos - a.slot_pos[j] < a.window;
+      return s.abs_pos - __ldcg(a.slot_pos + j) < a.window;
     };
     for (int j = lo + warp; j < hi; j += 4 * WARPS) {
       bool ok[4];
