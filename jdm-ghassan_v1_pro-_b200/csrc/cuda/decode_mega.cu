@@ -735,54 +735,131 @@ __device__ __forceinline__ void route_phase(const gb_mega_args& a, const gb_mega
       if (lane == 0) { if (hf == 0) sm.lg[e] = s; else lg2[e] = s; }
     }
     __syncthreads();
-    if (split == 2 && (int)threadIdx.x < ne) sm.lg[threadIdx.x] += lg2[threadIdx.x];
-    if (split == 2) __syncthreads();
-    if (threadIdx.x == 0) {
-      float mx = -INFINITY;
-      for (int e = 0; e < ne; ++e) mx = fmaxf(mx, sm.lg[e]);
-      float sum = 0.f;
-      for (int e = 0; e < ne; ++e) { sm.lg[e] = __expf(sm.lg[e] - mx); sum += sm.lg[e]; }
-      const float inv = 1.f / sum;
-      unsigned long long taken = 0ull;
-      float psum = 0.f;
+    // softmax and the top_k picks by one warp, lane e holding experts e and e + 32 in registers (a single thread
+    // walking the table in shared memory took most of this phase); ties go to the lower index, as in the serial rule
+    if (warp == 0) {
+      const unsigned full = 0xffffffffu;
+      const bool h0 = lane < ne, h1 = lane + 32 < ne;
+      const float l0 = h0 ? sm.lg[lane] + (split == 2 ? lg2[lane] : 0.f) : -INFINITY;
+      const float l1 = h1 ? sm.lg[lane + 32] + (split == 2 ? lg2[lane + 32] : 0.f) : -INFINITY;
+      float mx = fmaxf(l0, l1);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
+      float p0 = h0 ? __expf(l0 - mx) : 0.f, p1 = h1 ? __expf(l1 - mx) : 0.f;
+      const float inv = 1.f / warp_sum(p0 + p1);
+      p0 *= inv;
+      p1 *= inv;
+      float s0 = h0 ? p0 + (L.bias ? L.bias[lane] : 0.f) : -INFINITY;
+      float s1 = h1 ? p1 + (L.bias ? L.bias[lane + 32] : 0.f) : -INFINITY;
+      float psum = 0.f, my_w = 0.f;
+      int my_e = 0;
       for (int k = 0; k < top_k; ++k) {
-        float bv = -INFINITY;
-        int bi = 0;
-        for (int e = 0; e < ne; ++e) {
-          if (taken >> e & 1ull) continue;
-          const float sc = sm.lg[e] * inv + (L.bias ? L.bias[e] : 0.f);
-          if (sc > bv) { bv = sc; bi = e; }
+        float bv = s0;
+        int bi = lane;
+        if (s1 > bv) { bv = s1; bi = lane + 32; }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+          const float ov = __shfl_xor_sync(full, bv, o);
+          const int oi = __shfl_xor_sync(full, bi, o);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        taken |= 1ull << bi;
-        sm.esel[k] = bi;
-        sm.wsel[k] = sm.lg[bi] * inv;
-        psum += sm.wsel[k];
+        bi = min(bi, ne - 1);
+        const float w0 = __shfl_sync(full, p0, bi & 31), w1 = __shfl_sync(full, p1, bi & 31);
+        const float w = bi < 32 ? w0 : w1;
+        if (lane == k) { my_e = bi; my_w = w; }
+        psum += w;
+        if (bi == lane) s0 = -INFINITY;
+        if (bi == lane + 32) s1 = -INFINITY;
       }
       const float invs = psum > 1e-8f ? 1.f / psum : 0.f;
-      for (int k = 0; k < top_k; ++k) sm.wsel[k] *= invs;
-      if (a.shared) { sm.esel[top_k] = ne; sm.wsel[top_k] = 1.f; }
-      if (blockIdx.x == 0 && a.r_idx)
-        for (int k = 0; k < top_k; ++k) { a.r_idx[k] = sm.esel[k]; a.r_w[k] = sm.wsel[k]; }
+      if (lane < top_k) {
+        sm.esel[lane] = my_e;
+        sm.wsel[lane] = my_w * invs;
+        sm.off_e[lane] = (long long)my_e * d * rb_E;
+        if (blockIdx.x == 0 && a.r_idx) { a.r_idx[lane] = my_e; a.r_w[lane] = my_w * invs; }
+      }
+      if (a.shared && lane == top_k) { sm.esel[top_k] = ne; sm.wsel[top_k] = 1.f; sm.off_e[top_k] = (long long)ne * d * rb_E; }
     }
   } else if (threadIdx.x == 0) {
     sm.esel[0] = 0;
     sm.wsel[0] = 1.f;
+    sm.off_e[0] = 0;
   }
-  __syncthreads();
-  const int slots = ne > 0 ? top_k + (a.shared ? 1 : 0) : 1;
-  if ((int)threadIdx.x < slots) sm.off_e[threadIdx.x] = (long long)sm.esel[threadIdx.x] * d * rb_E;
+  if (threadIdx.x == THREADS - 1) {      // byte offsets of the gate and the up block, for the projection that follows
+    sm.off_gu[0] = 0;
+    sm.off_gu[1] = reinterpret_cast<const uint8_t*>(L.wu) - reinterpret_cast<const uint8_t*>(L.wg);
+  }
   __syncthreads();
 }
 
-template <int FMT, typename XT>
-__device__ __forceinline__ void head_phase(const gb_mega_args& a, const XT* xs, uint8_t* stage, Smem& sm, uint4 (&cur)[GROUP],
-                                           bool preloaded) {
+// Vocabulary projection.  A warp has far more rows here than its staging slice holds, so the slice is a ring of
+// `items` row slots (as many whole rows as fit, at most MAXI): row k lands in slot k % items, and the slot is refilled
+// with row k + items as soon as the warp has read it.  head_issue before the last grid barrier starts the first rows.
+// (Pulling the rows through registers one group ahead ran this phase at a fifth of the memory bandwidth.)
+template <int FMT>
+__device__ __forceinline__ int head_items(const gb_mega_args& a) {
   const long long rb = (long long)(a.d / SU) * Fmt<FMT>::bytes;
-  Phase ph{reinterpret_cast<const uint8_t*>(a.head), nullptr, nullptr, a.d / SU, a.d / SU, false, false};
+  const long long fit = a.stage_bytes / rb;
+  return (int)(fit < MAXI ? fit : MAXI);
+}
+
+template <int FMT>
+__device__ __forceinline__ void head_issue(const gb_mega_args& a, const Plan& pl, Stage& st, int items, int k0, int k1) {
+  const uint32_t rb = (uint32_t)(a.d / SU) * Fmt<FMT>::bytes;
+  k1 = min(k1, pl.n);
+  if (k0 >= k1 || *st.dead) return;
+  __syncwarp();                                  // every lane has finished reading the slots that are refilled
+  for (int k = k0; k < k1; ++k) st.pending |= 1u << (k % items);
+  if ((threadIdx.x & 31) == 0) {
+    fence_proxy_async();
+    for (int k = k0; k < k1; ++k) {
+      const int slot = k % items;
+      const long long o = (long long)blockIdx.x + (long long)(pl.first + k * pl.stride) * gridDim.x;
+      mbar_arrive_expect_tx(st.bars + slot, rb);
+      bulk_g2s(smem_u32(st.base + (size_t)slot * rb), reinterpret_cast<const uint8_t*>(a.head) + o * rb, rb,
+               smem_u32(st.bars + slot));
+    }
+  }
+}
+
+template <int FMT, typename XT>
+__device__ __noinline__ void head_phase(const gb_mega_args& a, const XT* xs, uint8_t* stage, Smem& sm, Stage& st,
+                                           int issued) {
+  constexpr int SB = Fmt<FMT>::bytes;
+  const int nsu = a.d / SU;
+  const long long rb = (long long)nsu * SB;
+  Phase ph{reinterpret_cast<const uint8_t*>(a.head), nullptr, nullptr, nsu, nsu, false, false};
   const Plan pl = make_plan(a.V, ph.P);
-  auto row = [&](int o) { return (long long)o * rb; };
-  if (!preloaded) preload<FMT>(ph, pl, row, cur);
-  run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, row, [&](int o, float v, float) { a.logits[o] = v; });
+  const int items = head_items<FMT>(a);
+  if (items < 1) {                               // a row does not fit the slice: through registers
+    auto row = [&](int o) { return (long long)o * rb; };
+    uint4 cur[GROUP];
+    preload<FMT>(ph, pl, row, cur);
+    run_phase<FMT, XT>(ph, pl, xs, stage, sm.red, cur, row, [&](int o, float v, float) { a.logits[o] = v; });
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  head_issue<FMT>(a, pl, st, items, issued, items);
+  for (int k = 0; k < pl.n; ++k) {
+    const int slot = k % items;
+    if (!mbar_wait(st.bars + slot, (st.parity >> slot) & 1u)) {
+      if (lane == 0) { *st.dead = 1; atomicCAS(st.status, 0, ST_TIMEOUT_COPY); }
+      break;
+    }
+    st.parity ^= 1u << slot;
+    st.pending &= ~(1u << slot);
+    const uint8_t* src = st.base + (size_t)slot * rb;
+    float acc = 0.f;
+    for (int p = 0; p < nsu; ++p) {
+      const uint8_t* su = src + (size_t)p * SB;
+      uint4 q = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (Fmt<FMT>::k16) q = *reinterpret_cast<const uint4*>(su + 16 * lane);
+      acc += su_dot<FMT, XT>(q, su, xs + p * SU);
+    }
+    head_issue<FMT>(a, pl, st, items, k + items, k + items + 1);
+    acc = warp_sum(acc);
+    if (lane == 0) a.logits[blockIdx.x + (pl.first + k * pl.stride) * (int)gridDim.x] = acc;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
@@ -846,7 +923,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   }
   __syncthreads();
 
-  uint4 cur[GROUP];
   bool ok = true;
   const int n_qkv = qd + 2 * kvd;
   auto rowA = [&](int o) { return (long long)o * rb_d; };
@@ -895,7 +971,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     if (!(ok = grid_sync(gb))) break;
     mark();
     // ---- B: attention over the cache
-    attention_phase<XT>(a, L, S, sm, amerge, s0, pos_now, prof);
+    {   // a copy for the call: the cursor itself must not have its address taken, or it lives in local memory
+      unsigned long long* pp = prof;
+      attention_phase<XT>(a, L, S, sm, amerge, s0, pos_now, pp);
+      prof = pp;
+    }
     mark();
     if (!(ok = grid_sync(gb))) break;
     mark();
@@ -927,11 +1007,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       }
       route_phase<XT>(a, L, xs, sm, rb_E, router_rows);
       mark();
-      if (threadIdx.x == 0) {
-        sm.off_gu[0] = 0;
-        sm.off_gu[1] = reinterpret_cast<const uint8_t*>(L.wu) - reinterpret_cast<const uint8_t*>(L.wg);
-      }
-      __syncthreads();
       Phase ph{reinterpret_cast<const uint8_t*>(L.wg), sm.off_gu, nullptr, nsu_d, 2 * nsu_d, true, true};
       const Plan pl = make_plan(slots * E, ph.P);
       auto row = [&](int o) {
@@ -955,14 +1030,16 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     stream_run<FMT, XT>(phE, plE, xs, st, sm.red,
                         [&](int o, float v, float) { x_out[o] = (ownE ? resE : __ldcg(x_mid + o)) + v; });
     const bool last = li + 1 == a.n_layers;
-    bool head_pre = false;
+    int head_pre = 0;
     if (!last) {
       Phase ph{reinterpret_cast<const uint8_t*>(a.layers[li + 1].wqkv), nullptr, nullptr, nsu_d, nsu_d, false, false};
       stream_issue<FMT>(ph, plA, st, rowA);
-    } else if (a.head_fmt == FMT) {       // the vocabulary projection has too many rows per CTA to stage: registers
-      Phase ph{reinterpret_cast<const uint8_t*>(a.head), nullptr, nullptr, nsu_d, nsu_d, false, false};
-      preload<FMT>(ph, make_plan(a.V, nsu_d), rowA, cur);
-      head_pre = true;
+    } else {                              // the first rows of the vocabulary projection
+      const Plan plH = make_plan(a.V, nsu_d);
+      if (a.head_fmt == FMT) { head_pre = head_items<FMT>(a); head_issue<FMT>(a, plH, st, head_pre, 0, head_pre); }
+      else if (a.head_fmt == GB_W_F16) { head_pre = head_items<GB_W_F16>(a); head_issue<GB_W_F16>(a, plH, st, head_pre, 0, head_pre); }
+      else { head_pre = head_items<GB_W_BF16>(a); head_issue<GB_W_BF16>(a, plH, st, head_pre, 0, head_pre); }
+      head_pre = max(0, min(head_pre, plH.n));
     }
     mark();
     if (!(ok = grid_sync(gb))) break;
@@ -971,9 +1048,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     if (last) {
       // ---- final norm + vocabulary projection
       block_norm<XT>(x_in, a.final_norm, xs, d, a.eps, sm.red[0]);
-      if (a.head_fmt == FMT) head_phase<FMT, XT>(a, xs, stage, sm, cur, head_pre);
-      else if (a.head_fmt == GB_W_F16) head_phase<GB_W_F16, XT>(a, xs, stage, sm, cur, false);
-      else head_phase<GB_W_BF16, XT>(a, xs, stage, sm, cur, false);
+      Stage sh = st;                      // a copy for the call, as above
+      if (a.head_fmt == FMT) head_phase<FMT, XT>(a, xs, stage, sm, sh, head_pre);
+      else if (a.head_fmt == GB_W_F16) head_phase<GB_W_F16, XT>(a, xs, stage, sm, sh, head_pre);
+      else head_phase<GB_W_BF16, XT>(a, xs, stage, sm, sh, head_pre);
+      st = sh;
     }
   }
   // a step that was given up: the copies this warp still has in flight must land (or run out of time) before the
@@ -1003,22 +1082,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   }
 }
 
-// Bytes of one warp's staging slice (the largest of the four layer phases), or -1 when a warp would have to stage more
-// than MAXI outputs at once.
-static long long stage_bytes_per_warp(const gb_mega_args& a, int grid, int su_bytes) {
-  const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
-  const int nsu_d = a.d / SU, nsu_q = a.H * a.hd / SU, nsu_E = a.E / SU;
-  const long long n[4] = {(long long)(a.H + 2 * a.KV) * a.hd, a.d, (long long)slots * a.E, a.d};
-  const int P[4] = {nsu_d, nsu_q, 2 * nsu_d, slots * nsu_E};
-  long long need = 16;
-  for (int i = 0; i < 4; ++i) {
-    int items = 0;
-    need = std::max(need, stage_need(n[i], P[i], grid, su_bytes, &items));
-    if (items > MAXI) return -1;
-  }
-  return (need + 15) & ~15ll;
-}
-
 static size_t dyn_bytes(const gb_mega_args& a, long long stage_per_warp) {
   const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
   const int xs_vals = std::max(std::max(a.d, a.H * a.hd), slots * a.E);
@@ -1037,6 +1100,28 @@ static int su_bytes_of(int fmt) {
     case GB_W_Q4_0: return 144;
     default: return 160;
   }
+}
+
+// Bytes of one warp's staging slice (the largest of the four layer phases and of the vocabulary ring), or -1 when a
+// warp would have to stage more than MAXI outputs at once.
+static long long stage_bytes_per_warp(const gb_mega_args& a, int grid, int su_bytes) {
+  const int slots = a.ne > 0 ? a.top_k + (a.shared ? 1 : 0) : 1;
+  const int nsu_d = a.d / SU, nsu_q = a.H * a.hd / SU, nsu_E = a.E / SU;
+  const long long n[4] = {(long long)(a.H + 2 * a.KV) * a.hd, a.d, (long long)slots * a.E, a.d};
+  const int P[4] = {nsu_d, nsu_q, 2 * nsu_d, slots * nsu_E};
+  long long need = 16;
+  for (int i = 0; i < 4; ++i) {
+    int items = 0;
+    need = std::max(need, stage_need(n[i], P[i], grid, su_bytes, &items));
+    if (items > MAXI) return -1;
+  }
+  need = (need + 15) & ~15ll;
+  // room for a ring of up to MAXI rows of the vocabulary projection, as far as the shared memory allows
+  const long long head_row = (long long)nsu_d * su_bytes_of(a.head_fmt);
+  const long long head_rows = ((long long)a.V + (long long)grid * WARPS - 1) / ((long long)grid * WARPS);
+  for (long long r = std::min<long long>(MAXI, head_rows); r >= 1; --r)
+    if (dyn_bytes(a, std::max(need, r * head_row)) <= (size_t)MAX_DYN) { need = std::max(need, r * head_row); break; }
+  return need;
 }
 
 }  // namespace mg
