@@ -13,6 +13,7 @@
 //
 // Segment masks are passed as `lo[i]` = first key position visible to query i (start of its packed document,
 // or 0): visible(i, j) <=> max(lo[i], i - window + 1) <= j <= i.  Every wait is bounded (status word on expiry).
+#include <algorithm>
 #include <type_traits>
 
 #include "sm100_common.cuh"
@@ -147,25 +148,28 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_co
   uint64_t* s_full = bars + 5;
   uint64_t* p_ready = bars + 6;
   uint64_t* o_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_empty = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the tile index is the slowest grid dimension and runs from the last query tile down: under a causal mask that tile
-  // has the most key tiles to visit, and CTAs are handed out in grid order, so the long ones start first
-  const int b = blockIdx.y, h = blockIdx.x, q0 = (int)(gridDim.z - 1 - blockIdx.z) * AT_M;
-  const int kvh = h / (p.H / p.KV);
-  const long long row_base = (long long)b * p.T;
+  // Work items: (query tile, batch, head), the query tile slowest and from the last one down: under a causal mask that
+  // tile visits the most key tiles, so the long items are dealt first and the short ones fill the tail.  A CTA stays
+  // on its SM and walks items blockIdx.x, blockIdx.x + gridDim.x, ...: tensor memory, barriers and tensor maps are set
+  // up once, the producer warp runs ahead into the next item's Q, K and V while the soft-max warps finish the current
+  // one, and the first score tile of the next item is computed under the current item's output store.
+  const int n_qt = (p.T + AT_M - 1) / AT_M, BH = p.B * p.H;
+  const int n_items = n_qt * BH;
+  const int rep = p.H / p.KV;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(p_ready, 128);
     mbar_init(o_full, 1);
     *abort_flag = 0;
-    *s_lo_min = 0x7fffffff;
     fence_barrier_init();
   }
   if (warp == 5) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
@@ -175,31 +179,40 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_co
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + AT_N;
 
-  // visible key range of this tile: [k_lo, k_hi)
-  const int r = threadIdx.x;                  // query row for the first 128 threads
-  const int i = q0 + r;
-  const bool row_ok = r < AT_M && i < p.T;
-  int lo_i = 0;
-  if (row_ok) {
-    if (p.lo) lo_i = p.lo[row_base + i];
-    if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
-    atomicMin(s_lo_min, lo_i);
-  }
-  __syncthreads();
-  const int k_hi = min(p.T, q0 + AT_M);
-  const int k_lo = (min(*s_lo_min, k_hi - 1) / AT_N) * AT_N;
-  const int n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
+  // Visible key tiles of an item: [k_lo, k_lo + n_tiles * AT_N).  `lo` (start of the packed document) and the window
+  // bound are both non-decreasing along a sequence, so the first row of the tile has the smallest of them.
+  auto item_range = [&](int item, int& b, int& h, int& q0, int& k_lo, int& n_tiles) {
+    const int zt = item / BH, bh = item - zt * BH;
+    b = bh / p.H;
+    h = bh - b * p.H;
+    q0 = (n_qt - 1 - zt) * AT_M;
+    int lo0 = p.lo ? p.lo[(long long)b * p.T + q0] : 0;
+    if (p.window > 0) lo0 = max(lo0, q0 - p.window + 1);
+    const int k_hi = min(p.T, q0 + AT_M);
+    k_lo = (min(lo0, k_hi - 1) / AT_N) * AT_N;
+    n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
+  };
 
   if (warp == 4) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, TILE);
-      load_tile<HD>(&tmQ, q_full, sQ, h * HD, (int)row_base + q0);
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t & 1, ph = (t >> 1) & 1;
-        if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
-        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
-        load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
-        load_tile<HD>(&tmV, &kv_full[s], sV + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
+      uint32_t kv_it = 0, q_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++q_it) {
+        int b, h, q0, k_lo, n_tiles;
+        item_range(item, b, h, q0, k_lo, n_tiles);
+        const int kvh = h / rep;
+        const int row_base = b * p.T;
+        // the tensor core has read the previous item's Q (committed after its last score tile)
+        if (!at_wait(q_empty, (q_it & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(q_full, TILE);
+        load_tile<HD>(&tmQ, q_full, sQ, h * HD, row_base + q0);
+        for (int t = 0; t < n_tiles; ++t, ++kv_it) {
+          const int s = kv_it & 1, ph = (kv_it >> 1) & 1;
+          if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
+          load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, row_base + k_lo + t * AT_N);
+          load_tile<HD>(&tmV, &kv_full[s], sV + s * TILE, kvh * HD, row_base + k_lo + t * AT_N);
+        }
       }
     }
     __syncwarp();
@@ -208,100 +221,159 @@ __global__ void __launch_bounds__(AT_THREADS) attn_tc_fwd_kernel(const __grid_co
       constexpr int fmt = OperandFmt<T>::value;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
       const uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, AT_M, HD);
-      bool ok = at_wait(q_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t & 1, ph = (t >> 1) & 1;
-        if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
-        tc_fence_after();
-        // S(t) may overwrite S(t-1) only after the softmax threads have read it: p_ready(t-1) was waited below
-        mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
-        umma_commit(s_full);
-        if (!at_wait(p_ready, t & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) break;
-        tc_fence_after();
-        mma_kmajor_mnmajor<AT_N>(tmem_O, smem_u32(sP), smem_u32(sV + s * TILE), idesc_o, false);
-        umma_commit(o_full);
-        umma_commit(&kv_empty[s]);
+      uint32_t kv_it = 0, q_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++q_it) {
+        int b, h, q0, k_lo, n_tiles;
+        item_range(item, b, h, q0, k_lo, n_tiles);
+        if (!at_wait(q_full, q_it & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        for (int t = 0; t < n_tiles; ++t, ++kv_it) {
+          const int s = kv_it & 1, ph = (kv_it >> 1) & 1;
+          if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          // S(t) may overwrite S(t-1) only after the softmax threads have read it: p_ready(t-1) was waited below
+          mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
+          umma_commit(s_full);
+          if (t == n_tiles - 1) umma_commit(q_empty);
+          if (!at_wait(p_ready, kv_it & 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_mnmajor<AT_N>(tmem_O, smem_u32(sP), smem_u32(sV + s * TILE), idesc_o, t > 0);
+          umma_commit(o_full);
+          umma_commit(&kv_empty[s]);
+        }
       }
     }
     __syncwarp();
   } else {
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    // Soft-max warps, one thread per query row.  The output accumulates in tensor memory over the key tiles of an item
+    // (the P V product adds to it), so a thread touches it only at the end of the item, and in the rare tile where the
+    // running maximum of a row of its warp has grown by more than 2^8: only then are the accumulator rows rescaled
+    // (until then the probabilities are taken against the older, smaller maximum, at most 256 times larger than with the
+    // true one; the final division by the row sum, kept against the same maximum, is exact either way).
+    const int r = threadIdx.x;                  // query row of the tile
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const float sc = p.scale;
+    const float sc2 = p.scale * 1.4426950408889634f;       // scores in log2 units: exp(x * scale) = 2^(x * sc2)
+    uint32_t tile_it = 0;
     bool ok = true;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int j0 = k_lo + t * AT_N;
-      if (!at_wait(s_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
-      // pass A: row maximum
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < AT_N / 32; ++c) {
-        uint32_t rg[32];
-        tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int j = j0 + c * 32 + k;
-          const bool vis = !need_mask || (j <= i && j >= lo_i);
-          if (vis) mx = fmaxf(mx, __uint_as_float(rg[k]) * sc);
-        }
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      int b, h, q0, k_lo, n_tiles;
+      item_range(item, b, h, q0, k_lo, n_tiles);
+      const long long row_base = (long long)b * p.T;
+      const int i = q0 + r;
+      const bool row_ok = i < p.T;
+      int lo_i = 0;
+      if (row_ok) {
+        if (p.lo) lo_i = p.lo[row_base + i];
+        if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
       }
-      if (!row_ok) mx = 0.f;
-      const float m_new = mx;
-      const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
-      float lsum = 0.f;
-      // pass B: probabilities -> shared memory (operand layout)
+      float m2 = -INFINITY, l = 0.f;            // maximum in use (log2 units) and the row sum against it
+      for (int t = 0; t < n_tiles; ++t, ++tile_it) {
+        const int j0 = k_lo + t * AT_N;
+        if (!at_wait(s_full, tile_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
+        // pass A: row maximum of the raw scores (the scale is positive: checked by the launcher)
+        float mr[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-      for (int c = 0; c < AT_N / 32; ++c) {
-        uint32_t rg[32];
-        tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
-        tmem_ld_wait();
-        float pv[32];
+        for (int c = 0; c < AT_N / 32; ++c) {
+          uint32_t rg[32];
+          tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
+          tmem_ld_wait();
+          if (!need_mask) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int j = j0 + c * 32 + k;
-          const bool vis = row_ok && (!need_mask || (j <= i && j >= lo_i));
-          const float e = (vis && m_new != -INFINITY) ? __expf(__uint_as_float(rg[k]) * sc - m_new) : 0.f;
-          pv[k] = e;
-          lsum += e;
+            for (int k = 0; k < 32; ++k) mr[k & 3] = fmaxf(mr[k & 3], __uint_as_float(rg[k]));
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int j = j0 + c * 32 + k;
+              if (j <= i && j >= lo_i) mr[k & 3] = fmaxf(mr[k & 3], __uint_as_float(rg[k]));
+            }
+          }
         }
-        store_p_chunk<T>(sP, r, c * 32, pv);
+        float mt = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sc2;
+        if (!row_ok) mt = 0.f;
+        // a new maximum is taken when some row of the warp needs it (the accumulator rows are reached by warp-wide
+        // tensor-memory loads and stores, so the decision is the warp's)
+        const bool grow = mt > m2 + 8.f || (m2 == -INFINITY && mt != -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m2, mt);
+          if (t > 0) {
+            const float corr = (m2 == -INFINITY) ? 1.f : exp2f(m2 - m_new);   // nothing accumulated yet on a -inf row
+            l *= corr;
+            // the previous tile's P V has to be in the accumulator before it is rescaled
+            if (!at_wait(o_full, (tile_it - 1u) & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 16; ++c) {
+              uint32_t rg[16];
+              tmem_ld_32x16(tmem_O + lane_base + c * 16, rg);
+              tmem_ld_wait();
+#pragma unroll
+              for (int k = 0; k < 16; ++k) rg[k] = __float_as_uint(__uint_as_float(rg[k]) * corr);
+              tmem_st_32x16(tmem_O + lane_base + c * 16, rg);
+            }
+            tmem_st_wait();
+          }
+          m2 = m_new;
+        }
+        float ls[2] = {0.f, 0.f};
+        const bool dead = m2 == -INFINITY;       // no visible key so far in this row
+        // pass B: probabilities -> shared memory (operand layout)
+#pragma unroll 1
+        for (int c = 0; c < AT_N / 32; ++c) {
+          uint32_t rg[32];
+          tmem_ld_32x32(tmem_S + lane_base + c * 32, rg);
+          tmem_ld_wait();
+          float pv[32];
+          if (!need_mask) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const float e = exp2f(fmaf(__uint_as_float(rg[k]), sc2, -m2));
+              pv[k] = e;
+              ls[k & 1] += e;
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int j = j0 + c * 32 + k;
+              const bool vis = row_ok && !dead && j <= i && j >= lo_i;
+              const float e = vis ? exp2f(fmaf(__uint_as_float(rg[k]), sc2, -m2)) : 0.f;
+              pv[k] = e;
+              ls[k & 1] += e;
+            }
+          }
+          store_p_chunk<T>(sP, r, c * 32, pv);
+        }
+        l += ls[0] + ls[1];
+        tc_fence_before();
+        fence_proxy_async();          // generic-proxy writes of P must be visible to the tensor core
+        mbar_arrive(p_ready);
       }
-      l = l * corr + lsum;
-      m = m_new;
-      tc_fence_before();
-      fence_proxy_async();          // generic-proxy writes of P must be visible to the tensor core
-      mbar_arrive(p_ready);
-      if (!at_wait(o_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      if (!ok) break;
+      // the item's last P V
+      if (!at_wait(o_full, (tile_it - 1u) & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      T* op = reinterpret_cast<T*>(p.o) + (row_base + i) * p.ld_o + (long long)h * HD;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t rg[32];
         tmem_ld_32x32(tmem_O + lane_base + c * 32, rg);
         tmem_ld_wait();
+        if (row_ok) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k) o[c * 32 + k] = o[c * 32 + k] * corr + __uint_as_float(rg[k]);
+          for (int k = 0; k < 4; ++k) {
+            uint4 q;
+            q.x = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 0]) * inv_l, __uint_as_float(rg[8 * k + 1]) * inv_l);
+            q.y = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 2]) * inv_l, __uint_as_float(rg[8 * k + 3]) * inv_l);
+            q.z = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 4]) * inv_l, __uint_as_float(rg[8 * k + 5]) * inv_l);
+            q.w = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 6]) * inv_l, __uint_as_float(rg[8 * k + 7]) * inv_l);
+            reinterpret_cast<uint4*>(op)[c * 4 + k] = q;
+          }
+        }
       }
-      tc_fence_before();
-    }
-    if (ok && row_ok) {
-      const float inv_l = l > 0.f ? 1.f / l : 0.f;
-      T* op = reinterpret_cast<T*>(p.o) + (row_base + i) * p.ld_o + (long long)h * HD;
-#pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        uint4 q;
-        q.x = Cvt<T>::pack2(o[8 * c + 0] * inv_l, o[8 * c + 1] * inv_l);
-        q.y = Cvt<T>::pack2(o[8 * c + 2] * inv_l, o[8 * c + 3] * inv_l);
-        q.z = Cvt<T>::pack2(o[8 * c + 4] * inv_l, o[8 * c + 5] * inv_l);
-        q.w = Cvt<T>::pack2(o[8 * c + 6] * inv_l, o[8 * c + 7] * inv_l);
-        reinterpret_cast<uint4*>(op)[c] = q;
-      }
-      if (p.lse) p.lse[(row_base + i) * p.H + h] = l > 0.f ? m + __logf(l) : INFINITY;
+      tc_fence_before();              // the next item's first P V overwrites the accumulator
+      if (row_ok && p.lse) p.lse[(row_base + i) * p.H + h] = l > 0.f ? (m2 + log2f(l)) * 0.6931471805599453f : INFINITY;
     }
   }
   __syncthreads();
@@ -719,6 +791,7 @@ int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   if (gb_make_tmap_2d_16b(&tq, a->q, rows, (uint64_t)a->H * HD, a->ld_q, AT_M, 64, a->is_bf16)) return -20;
   if (gb_make_tmap_2d_16b(&tk, a->k, rows, (uint64_t)a->KV * HD, a->ld_k, AT_N, 64, a->is_bf16)) return -21;
   if (gb_make_tmap_2d_16b(&tv, a->v, rows, (uint64_t)a->KV * HD, a->ld_v, AT_N, 64, a->is_bf16)) return -22;
+  if (!(a->scale > 0.f)) return -1;            // the row maximum is taken on raw scores
   AttnTcParams p{};
   p.B = a->B; p.T = a->T; p.H = a->H; p.KV = a->KV; p.window = a->window; p.scale = a->scale;
   p.lo = lo; p.o = a->o; p.ld_o = a->ld_o; p.lse = a->lse; p.status = status;
@@ -731,8 +804,20 @@ int launch_tc_fwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
     (void)cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr = true;
   }
-  if (a->B > 65535 || (a->T + AT_M - 1) / AT_M > 65535) return -1;   // grid y and z limits
-  dim3 grid(a->H, a->B, (a->T + AT_M - 1) / AT_M);
+  // persistent: as many CTAs as fit the device at once (two per SM at head_dim 64), each walking its share of the items
+  static int resident = 0;
+  if (!resident) {
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      return -10;
+    // two 112 KB CTAs share an SM at head_dim 64 (the carve-out preference above); the occupancy query does not see
+    // that preference, so the count is stated here
+    per_sm = HD == 64 ? 2 : 1;
+    resident = sms * per_sm;
+  }
+  const long long n_items = (long long)((a->T + AT_M - 1) / AT_M) * a->B * a->H;
+  if (n_items > 0x7fffffffll - resident) return -1;
+  const unsigned grid = (unsigned)std::min<long long>(n_items, resident);
   kern<<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
   return gb_launch_rc();
 }

@@ -29,6 +29,8 @@ CASES = [
     (1, 260, 2, 1, 128, 0, True),
     (1, 1, 2, 2, 64, 0, False),
     (1, 1024, 4, 4, 64, 0, False),
+    (8, 512, 12, 4, 64, 0, True),       # more work items than resident CTAs: every CTA walks several
+    (8, 384, 16, 4, 64, 100, True),
 ]
 
 
