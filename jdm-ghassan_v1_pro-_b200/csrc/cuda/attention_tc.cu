@@ -409,24 +409,25 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
   uint64_t* sdp_full = bars + 5;
   uint64_t* ds_ready = bars + 6;
   uint64_t* dq_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_empty = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_lo_min = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the tile index is the slowest grid dimension and runs from the last query tile down: under a causal mask that tile
-  // has the most key tiles to visit, and CTAs are handed out in grid order, so the long ones start first
-  const int b = blockIdx.y, h = blockIdx.x, q0 = (int)(gridDim.z - 1 - blockIdx.z) * AT_M;
-  const int kvh = h / (p.H / p.KV);
-  const long long row_base = (long long)b * p.T;
+  // Persistent, like the forward kernel: items are (query tile, batch, head) with the last query tile (the longest key
+  // loop) first; a CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ... with tensor memory and barriers set up once,
+  // the producer running ahead into the next item and the next item's first S / dP under the current dQ read-out.
+  const int n_qt = (p.T + AT_M - 1) / AT_M, BH = p.B * p.H;
+  const int n_items = n_qt * BH;
+  const int rep = p.H / p.KV;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(sdp_full, 1);
     mbar_init(ds_ready, AT_BWD_CW * 32);
     mbar_init(dq_full, 1);
     *abort_flag = 0;
-    *s_lo_min = 0x7fffffff;
     fence_barrier_init();
   }
   if (warp == AT_BWD_W_MMA) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -436,32 +437,41 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + AT_N, tmem_dQ = tmem_base + 2 * AT_N;
 
-  const int cq = warp >> 2;                     // 32-column chunk of a compute warp
-  const int r = (warp & 3) * 32 + lane;         // query row of a compute thread (its TMEM lane)
-  const int i = q0 + r;
-  const bool row_ok = warp < AT_BWD_CW && i < p.T;
-  int lo_i = 0;
-  if (row_ok) {
-    if (p.lo) lo_i = p.lo[row_base + i];
-    if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
-    if (cq == 0) atomicMin(s_lo_min, lo_i);
-  }
-  __syncthreads();
-  const int k_hi = min(p.T, q0 + AT_M);
-  const int k_lo = (min(*s_lo_min, k_hi - 1) / AT_N) * AT_N;
-  const int n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
+  // visible key tiles of an item (`lo` and the window bound are non-decreasing along a sequence: the first row of the
+  // tile has the smallest)
+  auto item_range = [&](int item, int& b, int& h, int& q0, int& k_lo, int& n_tiles) {
+    const int zt = item / BH, bh = item - zt * BH;
+    b = bh / p.H;
+    h = bh - b * p.H;
+    q0 = (n_qt - 1 - zt) * AT_M;
+    int lo0 = p.lo ? p.lo[(long long)b * p.T + q0] : 0;
+    if (p.window > 0) lo0 = max(lo0, q0 - p.window + 1);
+    const int k_hi = min(p.T, q0 + AT_M);
+    k_lo = (min(lo0, k_hi - 1) / AT_N) * AT_N;
+    n_tiles = (k_hi - k_lo + AT_N - 1) / AT_N;
+  };
 
   if (warp == AT_BWD_W_TMA) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, 2 * TILE);
-      load_tile<HD>(&tmQ, q_full, sQ, h * HD, (int)row_base + q0);
-      load_tile<HD>(&tmDO, q_full, sDO, h * HD, (int)row_base + q0);
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % STAGES, ph = (t / STAGES) & 1;
-        if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
-        mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
-        load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
-        load_tile<HD>(&tmV, &kv_full[s], sV + s * TILE, kvh * HD, (int)row_base + k_lo + t * AT_N);
+      uint32_t kv_it = 0, q_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++q_it) {
+        int b, h, q0, k_lo, n_tiles;
+        item_range(item, b, h, q0, k_lo, n_tiles);
+        const int kvh = h / rep;
+        const int row_base = b * p.T;
+        // Q and dO of the previous item have been read (committed after its last S / dP)
+        if (!at_wait(q_empty, (q_it & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(q_full, 2 * TILE);
+        load_tile<HD>(&tmQ, q_full, sQ, h * HD, row_base + q0);
+        load_tile<HD>(&tmDO, q_full, sDO, h * HD, row_base + q0);
+        for (int t = 0; t < n_tiles; ++t, ++kv_it) {
+          const int s = kv_it % STAGES, ph = (kv_it / STAGES) & 1;
+          if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
+          load_tile<HD>(&tmK, &kv_full[s], sK + s * TILE, kvh * HD, row_base + k_lo + t * AT_N);
+          load_tile<HD>(&tmV, &kv_full[s], sV + s * TILE, kvh * HD, row_base + k_lo + t * AT_N);
+        }
       }
     }
     __syncwarp();
@@ -470,57 +480,87 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
       constexpr int fmt = OperandFmt<T>::value;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
       const uint32_t idesc_dq = make_idesc_f16(fmt, 0, 1, AT_M, HD);
-      bool ok = at_wait(q_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t % STAGES, ph = (t / STAGES) & 1;
-        if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
-        mma_kmajor_kmajor<HD>(tmem_dP, smem_u32(sDO), smem_u32(sV + s * TILE), idesc_s, false);
-        umma_commit(sdp_full);
-        if (!at_wait(ds_ready, t & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        mma_kmajor_mnmajor<AT_N>(tmem_dQ, smem_u32(sDS), smem_u32(sK + s * TILE), idesc_dq, t > 0);
-        umma_commit(&kv_empty[s]);
+      uint32_t kv_it = 0, q_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++q_it) {
+        int b, h, q0, k_lo, n_tiles;
+        item_range(item, b, h, q0, k_lo, n_tiles);
+        if (!at_wait(q_full, q_it & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        for (int t = 0; t < n_tiles; ++t, ++kv_it) {
+          const int s = kv_it % STAGES, ph = (kv_it / STAGES) & 1;
+          if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * TILE), idesc_s, false);
+          mma_kmajor_kmajor<HD>(tmem_dP, smem_u32(sDO), smem_u32(sV + s * TILE), idesc_s, false);
+          umma_commit(sdp_full);
+          if (t == n_tiles - 1) umma_commit(q_empty);
+          if (!at_wait(ds_ready, kv_it & 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          // the first dQ of an item overwrites the accumulator: the compute warps have read the previous item's dQ
+          // before they arrived on ds_ready for this tile
+          mma_kmajor_mnmajor<AT_N>(tmem_dQ, smem_u32(sDS), smem_u32(sK + s * TILE), idesc_dq, t > 0);
+          umma_commit(&kv_empty[s]);
+        }
+        if (ok) umma_commit(dq_full);
       }
-      if (ok) umma_commit(dq_full);
     }
     __syncwarp();
   } else {
+    const int cq = warp >> 2;                     // 32-column chunk of a compute warp
+    const int r = (warp & 3) * 32 + lane;         // query row of a compute thread (its TMEM lane)
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float sc = p.scale;
-    float lse = INFINITY, dl = 0.f;
-    if (row_ok) {
-      lse = p.lse[(row_base + i) * p.H + h];
-      dl = p.delta[(row_base + i) * p.H + h];
-    }
+    const float sc2 = sc * 1.4426950408889634f;   // exp(x * scale - lse) = 2^(x * sc2 - lse * log2 e)
+    uint32_t tile_it = 0, item_it = 0;
     bool ok = true;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int j0 = k_lo + t * AT_N;
-      if (!at_wait(sdp_full, t & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      const bool need_mask = (j0 + AT_N - 1 > q0) || (j0 < lo_i);
-      {
-        const int c = cq;
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_S + lane_base + c * 32, rs);
-        tmem_ld_32x32(tmem_dP + lane_base + c * 32, rp);
-        tmem_ld_wait();
-        float ds[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int j = j0 + c * 32 + k;
-          const bool vis = row_ok && (!need_mask || (j <= i && j >= lo_i));
-          const float pr = vis ? __expf(__uint_as_float(rs[k]) * sc - lse) : 0.f;
-          ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
-        }
-        store_p_chunk<T>(sDS, r, c * 32, ds);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+      int b, h, q0, k_lo, n_tiles;
+      item_range(item, b, h, q0, k_lo, n_tiles);
+      const long long row_base = (long long)b * p.T;
+      const int i = q0 + r;
+      const bool row_ok = i < p.T;
+      int lo_i = 0;
+      float lse2 = INFINITY, dl = 0.f;
+      if (row_ok) {
+        if (p.lo) lo_i = p.lo[row_base + i];
+        if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
+        lse2 = p.lse[(row_base + i) * p.H + h] * 1.4426950408889634f;
+        dl = p.delta[(row_base + i) * p.H + h];
       }
-      tc_fence_before();
-      fence_proxy_async();
-      mbar_arrive(ds_ready);
-    }
-    if (ok && at_wait(dq_full, 0, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) {
+      for (int t = 0; t < n_tiles; ++t, ++tile_it) {
+        const int j0 = k_lo + t * AT_N;
+        if (!at_wait(sdp_full, tile_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const bool need_mask = !row_ok || (j0 + AT_N - 1 > q0) || (j0 < lo_i);
+        {
+          const int c = cq;
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32(tmem_S + lane_base + c * 32, rs);
+          tmem_ld_32x32(tmem_dP + lane_base + c * 32, rp);
+          tmem_ld_wait();
+          float ds[32];
+          if (!need_mask) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2));
+              ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int j = j0 + c * 32 + k;
+              const bool vis = row_ok && j <= i && j >= lo_i;
+              const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2)) : 0.f;
+              ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+            }
+          }
+          store_p_chunk<T>(sDS, r, c * 32, ds);
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        mbar_arrive(ds_ready);
+      }
+      if (!ok || !at_wait(dq_full, item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
       tc_fence_after();
       T* dqp = reinterpret_cast<T*>(p.dq) + (row_base + i) * p.ld_dq + (long long)h * HD;
       if (cq < HD / 32) {
@@ -581,16 +621,19 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
   uint64_t* st_full = bars + 5;
   uint64_t* pt_ready = bars + 6;
   uint64_t* dkv_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* kv_empty = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // slowest grid dimension = key tile, first tile first: it is read by every query tile, the longest loop
-  const int b = blockIdx.y, kvh = blockIdx.x, j0 = blockIdx.z * AT_N;
+  // Persistent: items are (key tile, batch, kv head), the first key tile first (every query tile reads it: the longest
+  // loop); a CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ... with tensor memory and barriers set up once.
   const int group = p.H / p.KV;
-  const long long row_base = (long long)b * p.T;
+  const int n_kt = (p.T + AT_N - 1) / AT_N, BKV = p.B * p.KV;
+  const int n_items = n_kt * BKV;
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     mbar_init(st_full, 1);
     mbar_init(pt_ready, AT_BWD_CW * 32);
@@ -606,25 +649,40 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
   const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + AT_M, tmem_dV = tmem_base + 2 * AT_M,
                  tmem_dK = tmem_base + 2 * AT_M + HD;
 
-  const int i_lo = j0;   // key tile and query tiles share the 128-row grid
-  int i_hi = p.T;
-  if (p.window > 0) i_hi = min(p.T, j0 + AT_N - 1 + p.window);
-  const int n_qt = (i_hi - i_lo + AT_M - 1) / AT_M;
-  const int n_it = group * n_qt;
+  // key tile and query tiles share the 128-row grid: the query tiles of an item start at its key tile
+  auto item_range = [&](int item, int& b, int& kvh, int& j0, int& n_qt) {
+    const int jt = item / BKV, bk = item - jt * BKV;
+    b = bk / p.KV;
+    kvh = bk - b * p.KV;
+    j0 = jt * AT_N;
+    int i_hi = p.T;
+    if (p.window > 0) i_hi = min(p.T, j0 + AT_N - 1 + p.window);
+    n_qt = (i_hi - j0 + AT_M - 1) / AT_M;
+  };
 
   if (warp == AT_BWD_W_TMA) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(kv_full, 2 * TILE);
-      load_tile<HD>(&tmK, kv_full, sK, kvh * HD, (int)row_base + j0);
-      load_tile<HD>(&tmV, kv_full, sV, kvh * HD, (int)row_base + j0);
-      for (int it = 0; it < n_it; ++it) {
-        const int s = it % STAGES, ph = (it / STAGES) & 1;
-        const int h = kvh * group + it / n_qt;
-        const int i0 = i_lo + (it % n_qt) * AT_M;
-        if (!at_wait(&q_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
-        mbar_arrive_expect_tx(&q_full[s], 2 * TILE);
-        load_tile<HD>(&tmQ, &q_full[s], sQ + s * TILE, h * HD, (int)row_base + i0);
-        load_tile<HD>(&tmDO, &q_full[s], sDO + s * TILE, h * HD, (int)row_base + i0);
+      uint32_t g_it = 0, item_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+        int b, kvh, j0, n_qt;
+        item_range(item, b, kvh, j0, n_qt);
+        const int row_base = b * p.T;
+        // K and V of the previous item have been read (committed after its last S^T / dP^T)
+        if (!at_wait(kv_empty, (item_it & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(kv_full, 2 * TILE);
+        load_tile<HD>(&tmK, kv_full, sK, kvh * HD, row_base + j0);
+        load_tile<HD>(&tmV, kv_full, sV, kvh * HD, row_base + j0);
+        const int n_it = group * n_qt;
+        for (int it = 0; it < n_it; ++it, ++g_it) {
+          const int s = g_it % STAGES, ph = (g_it / STAGES) & 1;
+          const int h = kvh * group + it / n_qt;
+          const int i0 = j0 + (it % n_qt) * AT_M;
+          if (!at_wait(&q_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&q_full[s], 2 * TILE);
+          load_tile<HD>(&tmQ, &q_full[s], sQ + s * TILE, h * HD, row_base + i0);
+          load_tile<HD>(&tmDO, &q_full[s], sDO + s * TILE, h * HD, row_base + i0);
+        }
       }
     }
     __syncwarp();
@@ -633,78 +691,132 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
       constexpr int fmt = OperandFmt<T>::value;
       const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, AT_N);
       const uint32_t idesc_d = make_idesc_f16(fmt, 0, 1, AT_M, HD);
-      bool ok = at_wait(kv_full, 0, p.status, ST_TIMEOUT_FULL, abort_flag);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!at_wait(&q_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        mma_kmajor_kmajor<HD>(tmem_ST, smem_u32(sK), smem_u32(sQ + s * TILE), idesc_s, false);
-        mma_kmajor_kmajor<HD>(tmem_dPT, smem_u32(sV), smem_u32(sDO + s * TILE), idesc_s, false);
-        umma_commit(st_full);
-        if (!at_wait(pt_ready, it & 1, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        mma_kmajor_mnmajor<AT_M>(tmem_dV, smem_u32(sPT), smem_u32(sDO + s * TILE), idesc_d, it > 0);
-        mma_kmajor_mnmajor<AT_M>(tmem_dK, smem_u32(sDST), smem_u32(sQ + s * TILE), idesc_d, it > 0);
-        umma_commit(&q_empty[s]);
+      uint32_t g_it = 0, item_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+        int b, kvh, j0, n_qt;
+        item_range(item, b, kvh, j0, n_qt);
+        if (!at_wait(kv_full, item_it & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        const int n_it = group * n_qt;
+        for (int it = 0; it < n_it; ++it, ++g_it) {
+          const int s = g_it % STAGES, ph = (g_it / STAGES) & 1;
+          if (!at_wait(&q_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_kmajor<HD>(tmem_ST, smem_u32(sK), smem_u32(sQ + s * TILE), idesc_s, false);
+          mma_kmajor_kmajor<HD>(tmem_dPT, smem_u32(sV), smem_u32(sDO + s * TILE), idesc_s, false);
+          umma_commit(st_full);
+          if (it == n_it - 1) umma_commit(kv_empty);
+          if (!at_wait(pt_ready, g_it & 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          // the first dV / dK of an item overwrite the accumulators: the compute warps have read the previous item's
+          // before they arrived on pt_ready for this iteration
+          mma_kmajor_mnmajor<AT_M>(tmem_dV, smem_u32(sPT), smem_u32(sDO + s * TILE), idesc_d, it > 0);
+          mma_kmajor_mnmajor<AT_M>(tmem_dK, smem_u32(sDST), smem_u32(sQ + s * TILE), idesc_d, it > 0);
+          umma_commit(&q_empty[s]);
+        }
+        if (ok) umma_commit(dkv_full);
       }
-      if (ok) umma_commit(dkv_full);
     }
     __syncwarp();
   } else {
     const int cq = warp >> 2;                  // 32-column (query) chunk of this warp
     const int r = (warp & 3) * 32 + lane;      // key row of this thread (its TMEM lane)
-    const int j = j0 + r;
-    const bool row_ok = j < p.T;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float sc = p.scale;
+    const float sc2 = sc * 1.4426950408889634f;
+    constexpr float LOG2E = 1.4426950408889634f;
+    uint32_t g_it = 0, item_it = 0;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int h = kvh * group + it / n_qt;
-      const int i0 = i_lo + (it % n_qt) * AT_M;
-      const int bufi = it & 1;
-      if (cq == 0) {  // stage the per-query statistics of this tile (column r)
-        const int i = i0 + r;
-        const bool in = i < p.T;
-        sLse[bufi * AT_N + r] = in ? p.lse[(row_base + i) * p.H + h] : INFINITY;
-        sDl[bufi * AT_N + r] = in ? p.delta[(row_base + i) * p.H + h] : 0.f;
-        int lo = 0;
-        if (in && p.lo) lo = p.lo[row_base + i];
-        if (in && p.window > 0) lo = max(lo, i - p.window + 1);
-        sLo[bufi * AT_N + r] = in ? lo : 0x7fffffff;
-      }
-      asm volatile("bar.sync 1, 512;" ::: "memory");   // all AT_BWD_CW * 32 compute threads
-      // after a failed wait the loop keeps running (without waiting or computing) so that every thread still
-      // reaches the named barrier above in every iteration
-      if (ok && !at_wait(st_full, it & 1, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
-      if (!ok) continue;
-      tc_fence_after();
-      const float* lse = sLse + bufi * AT_N;
-      const float* dl = sDl + bufi * AT_N;
-      const int* lo = sLo + bufi * AT_N;
-      {
-        const int c = cq;
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_ST + lane_base + c * 32, rs);
-        tmem_ld_32x32(tmem_dPT + lane_base + c * 32, rp);
-        tmem_ld_wait();
-        float pt[32], ds[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int col = c * 32 + k;
-          const int i = i0 + col;
-          const bool vis = row_ok && j <= i && j >= lo[col];
-          const float pr = vis ? __expf(__uint_as_float(rs[k]) * sc - lse[col]) : 0.f;
-          pt[k] = pr;
-          ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
-        }
-        store_p_chunk<T>(sPT, r, c * 32, pt);
-        store_p_chunk<T>(sDST, r, c * 32, ds);
-      }
-      tc_fence_before();
-      fence_proxy_async();
-      mbar_arrive(pt_ready);
+    // Per-query statistics of an iteration (log-sum-exp in log2 units, delta, first visible key), fetched by the four
+    // cq == 0 warps (thread r = column r) one iteration ahead, the next item's first iteration included: the loads
+    // of iteration n + 1 are in flight while iteration n is computed.
+    float n_lse = INFINITY, n_dl = 0.f;
+    int n_lo = 0x7fffffff;
+    auto fetch_stats = [&](int b, int h, int i0) {
+      const int i = i0 + r;
+      const bool in = i < p.T;
+      const long long row = (long long)b * p.T + i;
+      n_lse = in ? p.lse[row * p.H + h] * LOG2E : INFINITY;
+      n_dl = in ? p.delta[row * p.H + h] : 0.f;
+      int lo = 0;
+      if (in && p.lo) lo = p.lo[row];
+      if (in && p.window > 0) lo = max(lo, i - p.window + 1);
+      n_lo = in ? lo : 0x7fffffff;
+    };
+    if (cq == 0 && (int)blockIdx.x < n_items) {
+      int b, kvh, j0, n_qt;
+      item_range(blockIdx.x, b, kvh, j0, n_qt);
+      fetch_stats(b, kvh * group, j0);
     }
-    if (ok && at_wait(dkv_full, 0, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) {
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_it) {
+      int b, kvh, j0, n_qt;
+      item_range(item, b, kvh, j0, n_qt);
+      const long long row_base = (long long)b * p.T;
+      const int j = j0 + r;
+      const bool row_ok = j < p.T;
+      const int n_it = group * n_qt;
+      for (int it = 0; it < n_it; ++it, ++g_it) {
+        const int i0 = j0 + (it % n_qt) * AT_M;
+        const int bufi = g_it & 1;
+        if (cq == 0) {
+          sLse[bufi * AT_N + r] = n_lse;
+          sDl[bufi * AT_N + r] = n_dl;
+          sLo[bufi * AT_N + r] = n_lo;
+          if (it + 1 < n_it) {
+            fetch_stats(b, kvh * group + (it + 1) / n_qt, j0 + ((it + 1) % n_qt) * AT_M);
+          } else if (item + (int)gridDim.x < n_items) {
+            int b2, kvh2, j02, n_qt2;
+            item_range(item + gridDim.x, b2, kvh2, j02, n_qt2);
+            fetch_stats(b2, kvh2 * group, j02);
+          }
+        }
+        asm volatile("bar.sync 1, 512;" ::: "memory");   // all AT_BWD_CW * 32 compute threads
+        // after a failed wait the loops keep running (without waiting or computing) so that every thread still
+        // reaches the named barrier above in every iteration
+        if (ok && !at_wait(st_full, g_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
+        if (!ok) continue;
+        tc_fence_after();
+        const float* lse = sLse + bufi * AT_N;
+        const float* dl = sDl + bufi * AT_N;
+        const int* lo = sLo + bufi * AT_N;
+        // every (key, query) pair of the tile visible: a query tile after the key tile, whole tiles, and the largest
+        // `lo` of the tile (its last column: lo does not decrease along a sequence) at or before the first key
+        const bool full = i0 > j0 && j0 + AT_N <= p.T && i0 + AT_M <= p.T && lo[AT_M - 1] <= j0;
+        {
+          const int c = cq;
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32(tmem_ST + lane_base + c * 32, rs);
+          tmem_ld_32x32(tmem_dPT + lane_base + c * 32, rp);
+          tmem_ld_wait();
+          float pt[32], ds[32];
+          if (full) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int col = c * 32 + k;
+              const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col]));
+              pt[k] = pr;
+              ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int col = c * 32 + k;
+              const int i = i0 + col;
+              const bool vis = row_ok && j <= i && j >= lo[col];
+              const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col])) : 0.f;
+              pt[k] = pr;
+              ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+            }
+          }
+          store_p_chunk<T>(sPT, r, c * 32, pt);
+          store_p_chunk<T>(sDST, r, c * 32, ds);
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        mbar_arrive(pt_ready);
+      }
+      if (ok && !at_wait(dkv_full, item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
+      if (!ok) continue;
       tc_fence_after();
       T* dkp = reinterpret_cast<T*>(p.dk) + (row_base + j) * p.ld_dk + (long long)kvh * HD;
       T* dvp = reinterpret_cast<T*>(p.dv) + (row_base + j) * p.ld_dv + (long long)kvh * HD;
@@ -894,10 +1006,21 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
     if (cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv) != cudaSuccess) return -10;
     attr = true;
   }
-  if (a->B > 65535 || (a->T + AT_N - 1) / AT_N > 65535) return -1;   // grid y and z limits
-  dim3 gq(a->H, a->B, (a->T + AT_M - 1) / AT_M), gkv(a->KV, a->B, (a->T + AT_N - 1) / AT_N);
-  kq<<<gq, AT_BWD_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
-  kkv<<<gkv, AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
+  // persistent: one CTA per SM (each holds all 512 tensor-memory columns), walking its share of the items
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms < 1) {
+      sms = 0;
+      return -10;
+    }
+  }
+  const long long tiles = (a->T + AT_M - 1) / AT_M;
+  const long long items_q = tiles * a->B * a->H, items_kv = tiles * a->B * a->KV;
+  if (items_q > 0x7fffffffll - sms) return -1;
+  kq<<<(unsigned)std::min<long long>(items_q, sms), AT_BWD_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
+  kkv<<<(unsigned)std::min<long long>(items_kv, sms), AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
   return gb_launch_rc();
 }
 

@@ -31,6 +31,7 @@ CASES = [
     (1, 1024, 4, 4, 64, 0, False),
     (8, 512, 12, 4, 64, 0, True),       # more work items than resident CTAs: every CTA walks several
     (8, 384, 16, 4, 64, 100, True),
+    (16, 512, 8, 4, 64, 0, True),       # more key-tile items than SMs too (the dK/dV kernel walks several per CTA)
 ]
 
 
@@ -86,3 +87,41 @@ def test_tc_attention_agrees_with_cuda_core_kernels():
     o3 = torch.empty_like(q)
     K.attn_tc_fwd(q, k, v, o3, l2, None, lo, B, T, H, KV, hd, 0, 0.125)
     assert torch.equal(o2, o3)
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("use_seg", [False, True])
+def test_tc_attention_forward_rescales_when_the_row_maximum_jumps(dt, use_seg):
+    """The forward kernel keeps the output in tensor memory and rescales it only when a row's maximum has grown by
+    more than 2^8 since it was last taken.  Keys that grow in magnitude along the sequence force that path in every
+    later tile (unit-variance inputs never do); a second case makes only some rows of a warp jump."""
+    from ghassan_b200.models import reference as R
+    from ghassan_b200.ops import _lib, kernels as K
+    B, T, H, KV, hd = 2, 512, 4, 2, 64
+    n = B * T
+    scale = hd ** -0.5
+    for variant in range(2):
+        q, k, v = rnd(n, H * hd, seed=11, dtype=dt), rnd(n, KV * hd, seed=12, dtype=dt), rnd(n, KV * hd, seed=13, dtype=dt)
+        pos = torch.arange(T, device="cuda").repeat(B)
+        if variant == 0:
+            k = (k.float() * (1.0 + 5.0 * (pos // 128).float())[:, None]).to(dt)          # every tile louder than the last
+        else:
+            q = (q.float() * torch.where(pos % 7 == 0, 8.0, 1.0)[:, None]).to(dt)         # a few rows of each warp jump
+            k = (k.float() * torch.where(pos >= 256, 4.0, 1.0)[:, None]).to(dt)
+        seg = (pos // 200).to(torch.int32) if use_seg else None
+        lo = torch.empty(n, dtype=torch.int32, device="cuda")
+        o = torch.empty(n, H * hd, dtype=dt, device="cuda")
+        lse = torch.empty(n, H, device="cuda")
+        K.attn_tc_fwd(q, k, v, o, lse, seg, lo, B, T, H, KV, hd, 0, scale)
+        _lib.check_status(what="attn_tc_fwd")
+        ref = R.attention(q.float().view(n, H, hd), k.float().view(n, KV, hd), v.float().view(n, KV, hd), B, T, scale, 0, seg)
+        ok, err, rule = near(o, ref)
+        assert ok, ("o", variant, err, rule)
+        sc = torch.einsum("bihd,bjhd->bhij", q.float().view(B, T, H, hd),
+                          k.float().view(B, T, KV, hd).repeat_interleave(H // KV, dim=2)) * scale
+        vis = pos[:T][None, :] <= pos[:T][:, None]
+        if use_seg:
+            vis = vis & ((pos[:T] // 200)[None, :] == (pos[:T] // 200)[:, None])
+        want = torch.logsumexp(sc.masked_fill(~vis, float("-inf")), dim=-1).permute(0, 2, 1).reshape(n, H)
+        ok, err, rule = near(lse, want, chain=False)
+        assert ok, ("lse", variant, err, rule)
