@@ -593,6 +593,213 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
   if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// ============================================================================================ backward: dQ (head_dim 64)
+// The same product with key steps of 64 instead of 128.  A step is then S 64 + dP 64 + dQ 64 = 192 tensor-memory
+// columns and 96 KB of shared memory, so two CTAs (8 compute warps each) share an SM: what bounds these kernels is the
+// round trip tensor core -> barrier -> compute warps -> barrier -> tensor core of every step, not arithmetic, and two
+// independent chains per SM hide each other's waits (the forward kernel gets its rate the same way).
+constexpr int AT_DQ64_CW = 8;
+constexpr int AT_DQ64_THREADS = (AT_DQ64_CW + 2) * 32;
+constexpr int AT_DQ64_STAGES = 3;
+
+template <typename T>
+__global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                          const __grid_constant__ CUtensorMap tmK,
+                                                                          const __grid_constant__ CUtensorMap tmV,
+                                                                          const __grid_constant__ CUtensorMap tmDO,
+                                                                          const AttnTcParams p) {
+  constexpr int HD = 64, KN = 64, ST = AT_DQ64_STAGES;
+  constexpr int W_TMA = AT_DQ64_CW, W_MMA = AT_DQ64_CW + 1;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t TILE = AT_M * HD * 2;          // Q, dO and dS: [128 x 64] 16-bit
+  constexpr uint32_t KTILE = KN * HD * 2;           // K, V of a step: [64 x 64]
+  // no static shared memory: the dynamic window starts 1024-aligned (checked, as in the forward kernel)
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sQ = smem_raw;
+  uint8_t* sDO = sQ + TILE;
+  uint8_t* sDS = sDO + TILE;
+  uint8_t* sK = sDS + TILE;                 // ST
+  uint8_t* sV = sK + ST * KTILE;            // ST
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + ST * KTILE);
+  uint64_t* q_full = bars;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* sdp_full = bars + 2;
+  uint64_t* ds_ready = bars + 3;
+  uint64_t* dq_full = bars + 4;
+  uint64_t* kv_full = bars + 5;             // ST
+  uint64_t* kv_empty = bars + 5 + ST;       // ST
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 + 2 * ST);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.T + AT_M - 1) / AT_M, BH = p.B * p.H;
+  const int n_items = n_qt * BH;
+  const int rep = p.H / p.KV;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, AT_DQ64_CW);
+    mbar_init(dq_full, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == W_MMA) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + KN, tmem_dQ = tmem_base + 2 * KN;
+
+  // visible key steps of an item: [k_lo, k_lo + n_steps * 64)
+  auto item_range = [&](int item, int& b, int& h, int& q0, int& k_lo, int& n_steps) {
+    const int zt = item / BH, bh = item - zt * BH;
+    b = bh / p.H;
+    h = bh - b * p.H;
+    q0 = (n_qt - 1 - zt) * AT_M;
+    int lo0 = p.lo ? p.lo[(long long)b * p.T + q0] : 0;
+    if (p.window > 0) lo0 = max(lo0, q0 - p.window + 1);
+    const int k_hi = min(p.T, q0 + AT_M);
+    k_lo = (min(lo0, k_hi - 1) / KN) * KN;
+    n_steps = (k_hi - k_lo + KN - 1) / KN;
+  };
+
+  if (warp == W_TMA) {
+    if (lane == 0) {
+      uint32_t kv_it = 0, q_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++q_it) {
+        int b, h, q0, k_lo, n_steps;
+        item_range(item, b, h, q0, k_lo, n_steps);
+        const int kvh = h / rep;
+        const int row_base = b * p.T;
+        if (!at_wait(q_empty, (q_it & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(q_full, 2 * TILE);
+        load_tile<HD>(&tmQ, q_full, sQ, h * HD, row_base + q0);
+        load_tile<HD>(&tmDO, q_full, sDO, h * HD, row_base + q0);
+        for (int t = 0; t < n_steps; ++t, ++kv_it) {
+          const int s = kv_it % ST, ph = (kv_it / ST) & 1;
+          if (!at_wait(&kv_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&kv_full[s], 2 * KTILE);
+          tma_load_2d(&tmK, &kv_full[s], sK + s * KTILE, kvh * HD, row_base + k_lo + t * KN);
+          tma_load_2d(&tmV, &kv_full[s], sV + s * KTILE, kvh * HD, row_base + k_lo + t * KN);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == W_MMA) {
+    if (lane == 0) {
+      constexpr int fmt = OperandFmt<T>::value;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, KN);
+      const uint32_t idesc_dq = make_idesc_f16(fmt, 0, 1, AT_M, HD);
+      uint32_t kv_it = 0, q_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++q_it) {
+        int b, h, q0, k_lo, n_steps;
+        item_range(item, b, h, q0, k_lo, n_steps);
+        if (!at_wait(q_full, q_it & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        for (int t = 0; t < n_steps; ++t, ++kv_it) {
+          const int s = kv_it % ST, ph = (kv_it / ST) & 1;
+          if (!at_wait(&kv_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_kmajor<HD>(tmem_S, smem_u32(sQ), smem_u32(sK + s * KTILE), idesc_s, false);
+          mma_kmajor_kmajor<HD>(tmem_dP, smem_u32(sDO), smem_u32(sV + s * KTILE), idesc_s, false);
+          umma_commit(sdp_full);
+          if (t == n_steps - 1) umma_commit(q_empty);
+          if (!at_wait(ds_ready, kv_it & 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_mnmajor<KN>(tmem_dQ, smem_u32(sDS), smem_u32(sK + s * KTILE), idesc_dq, t > 0);
+          umma_commit(&kv_empty[s]);
+        }
+        if (ok) umma_commit(dq_full);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int cq = warp >> 2;                     // 32-column chunk (of the 64 keys of a step, of the 64 of dQ)
+    const int r = (warp & 3) * 32 + lane;         // query row of a compute thread (its TMEM lane)
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const float sc = p.scale;
+    const float sc2 = sc * 1.4426950408889634f;
+    uint32_t step_it = 0, item_it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+      int b, h, q0, k_lo, n_steps;
+      item_range(item, b, h, q0, k_lo, n_steps);
+      const long long row_base = (long long)b * p.T;
+      const int i = q0 + r;
+      const bool row_ok = i < p.T;
+      int lo_i = 0;
+      float lse2 = INFINITY, dl = 0.f;
+      if (row_ok) {
+        if (p.lo) lo_i = p.lo[row_base + i];
+        if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
+        lse2 = p.lse[(row_base + i) * p.H + h] * 1.4426950408889634f;
+        dl = p.delta[(row_base + i) * p.H + h];
+      }
+      for (int t = 0; t < n_steps; ++t, ++step_it) {
+        const int j0 = k_lo + t * KN;
+        if (!at_wait(sdp_full, step_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const bool need_mask = !row_ok || (j0 + KN - 1 > q0) || (j0 < lo_i);
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_S + lane_base + cq * 32, rs);
+        tmem_ld_32x32(tmem_dP + lane_base + cq * 32, rp);
+        tmem_ld_wait();
+        float ds[32];
+        if (!need_mask) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2));
+            ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int j = j0 + cq * 32 + k;
+            const bool vis = row_ok && j <= i && j >= lo_i;
+            const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2)) : 0.f;
+            ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+          }
+        }
+        store_p_chunk<T>(sDS, r, cq * 32, ds);
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();                 // every lane's writes and fences, then one arrival for the warp
+        if (lane == 0) mbar_arrive(ds_ready);
+      }
+      if (!ok || !at_wait(dq_full, item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      T* dqp = reinterpret_cast<T*>(p.dq) + (row_base + i) * p.ld_dq + (long long)h * HD;
+      uint32_t rg[32];
+      tmem_ld_32x32(tmem_dQ + lane_base + cq * 32, rg);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 q;
+          q.x = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 0]), __uint_as_float(rg[8 * k + 1]));
+          q.y = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 2]), __uint_as_float(rg[8 * k + 3]));
+          q.z = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 4]), __uint_as_float(rg[8 * k + 5]));
+          q.w = Cvt<T>::pack2(__uint_as_float(rg[8 * k + 6]), __uint_as_float(rg[8 * k + 7]));
+          reinterpret_cast<uint4*>(dqp + cq * 32)[k] = q;
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
 // ============================================================================================ backward: dK, dV
 // One CTA per (batch, kv head, 128 key rows).  Loops over the query heads that share the kv head and over the
 // query tiles at or after the key tile.  Per iteration: S^T = K Q^T and dP^T = V dO^T into tensor memory (rows =
@@ -857,315 +1064,6 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
   if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
-// ============================================================================================ backward: dK, dV (head_dim 64)
-// The same product as attn_tc_bwd_dkv_kernel, pipelined.  An iteration (one query tile of one head) is cut into two
-// half-steps of 64 queries, and the tensor memory holds two sets of S^T / dP^T halves (2 x 2 x 64 columns beside the
-// two accumulators): while the compute warps turn half-step g into P^T and dS^T, the tensor core already holds the
-// scores of half-step g + 1, and it receives dV / dK of g and S^T / dP^T of g + 2 as soon as g is handed over.  K and V
-// are double-buffered across items, so the run-ahead crosses item boundaries.  Needs two Q / dO stages (the scores run
-// one iteration ahead of the accumulation), which is why head_dim 128 stays on the kernel above.
-struct DkvWalk {
-  int BKV, KV, T, window, group, n_items, stride;
-  int item, it, hs, b, kvh, j0, n_qt, n_it;
-  uint32_t g_it, item_it;
-  __device__ __forceinline__ bool valid() const { return item < n_items; }
-  __device__ __forceinline__ void load_item() {
-    const int jt = item / BKV, bk = item - jt * BKV;
-    b = bk / KV;
-    kvh = bk - b * KV;
-    j0 = jt * AT_N;
-    int i_hi = T;
-    if (window > 0) i_hi = min(T, j0 + AT_N - 1 + window);
-    n_qt = (i_hi - j0 + AT_M - 1) / AT_M;
-    n_it = group * n_qt;
-  }
-  __device__ __forceinline__ void start(const AttnTcParams& p) {
-    KV = p.KV; BKV = p.B * p.KV; T = p.T; window = p.window; group = p.H / p.KV;
-    n_items = ((p.T + AT_N - 1) / AT_N) * BKV;
-    stride = gridDim.x;
-    item = blockIdx.x; it = 0; hs = 0; g_it = 0; item_it = 0;
-    b = kvh = j0 = n_qt = n_it = 0;
-    if (valid()) load_item();
-  }
-  __device__ __forceinline__ void next_iter() {
-    hs = 0;
-    ++it;
-    ++g_it;
-    if (it == n_it) {
-      it = 0;
-      item += stride;
-      ++item_it;
-      if (valid()) load_item();
-    }
-  }
-  __device__ __forceinline__ void next_half() {
-    if (hs == 0) hs = 1;
-    else next_iter();
-  }
-  __device__ __forceinline__ uint32_t g_hs() const { return 2u * g_it + (uint32_t)hs; }
-  __device__ __forceinline__ bool first_half() const { return it == 0 && hs == 0; }
-  __device__ __forceinline__ bool last_half() const { return it == n_it - 1 && hs == 1; }
-  __device__ __forceinline__ int head() const { return kvh * group + it / n_qt; }
-  __device__ __forceinline__ int i0() const { return j0 + (it % n_qt) * AT_M; }
-};
-
-template <typename T>
-__global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv64_kernel(const __grid_constant__ CUtensorMap tmQ,
-                                                                       const __grid_constant__ CUtensorMap tmK,
-                                                                       const __grid_constant__ CUtensorMap tmV,
-                                                                       const __grid_constant__ CUtensorMap tmDO,
-                                                                       const AttnTcParams p) {
-  constexpr int HD = 64, QH = 64;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  constexpr uint32_t TILE = AT_M * HD * 2;        // 16 KB: a [128 x 64] 16-bit tile, also a [128 keys x 64 queries] half
-  constexpr uint32_t HALF_ROWS = QH * 128;        // byte offset of query row 64 inside a Q / dO tile
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;                       // 2 (items)
-  uint8_t* sV = sK + 2 * TILE;              // 2
-  uint8_t* sQ = sV + 2 * TILE;              // 2 (iterations)
-  uint8_t* sDO = sQ + 2 * TILE;             // 2
-  uint8_t* sPT = sDO + 2 * TILE;            // 2 (half-steps)
-  uint8_t* sDST = sPT + 2 * TILE;           // 2
-  float* sLse = reinterpret_cast<float*>(sDST + 2 * TILE);   // [2][128]
-  float* sDl = sLse + 2 * AT_N;
-  int* sLo = reinterpret_cast<int*>(sDl + 2 * AT_N);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sLo + 2 * AT_N);
-  uint64_t* kv_full = bars;                 // 2
-  uint64_t* kv_empty = bars + 2;            // 2
-  uint64_t* q_full = bars + 4;              // 2
-  uint64_t* q_empty = bars + 6;             // 2
-  uint64_t* st_full = bars + 8;             // 2: S^T / dP^T of a half-step are in tensor memory
-  uint64_t* pt_ready = bars + 10;           // 2: P^T / dS^T of a half-step are in shared memory, its scores are read
-  uint64_t* ps_empty = bars + 12;           // 2: dV / dK of a half-step have read its P^T / dS^T
-  uint64_t* dkv_full = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-      mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1);
-      mbar_init(&st_full[s], 1); mbar_init(&pt_ready[s], AT_BWD_CW); mbar_init(&ps_empty[s], 1);
-    }
-    mbar_init(dkv_full, 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == AT_BWD_W_MMA) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 2 * QH, tmem_dV = tmem_base + 4 * QH,
-                 tmem_dK = tmem_base + 4 * QH + HD;
-
-  if (warp == AT_BWD_W_TMA) {
-    if (lane == 0) {
-      DkvWalk c;
-      c.start(p);
-      while (c.valid()) {
-        const int row_base = c.b * p.T;
-        if (c.it == 0) {
-          const int kb = c.item_it & 1;
-          if (!at_wait(&kv_empty[kb], ((c.item_it >> 1) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
-          mbar_arrive_expect_tx(&kv_full[kb], 2 * TILE);
-          load_tile<HD>(&tmK, &kv_full[kb], sK + kb * TILE, c.kvh * HD, row_base + c.j0);
-          load_tile<HD>(&tmV, &kv_full[kb], sV + kb * TILE, c.kvh * HD, row_base + c.j0);
-        }
-        const int s = c.g_it & 1;
-        if (!at_wait(&q_empty[s], ((c.g_it >> 1) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
-        mbar_arrive_expect_tx(&q_full[s], 2 * TILE);
-        load_tile<HD>(&tmQ, &q_full[s], sQ + s * TILE, c.head() * HD, row_base + c.i0());
-        load_tile<HD>(&tmDO, &q_full[s], sDO + s * TILE, c.head() * HD, row_base + c.i0());
-        c.next_iter();
-      }
-    }
-    __syncwarp();
-  } else if (warp == AT_BWD_W_MMA) {
-    if (lane == 0) {
-      constexpr int fmt = OperandFmt<T>::value;
-      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_M, QH);
-      const uint32_t idesc_d = make_idesc_f16(fmt, 0, 1, AT_M, HD);
-      // scores of one half-step: S^T = K Q^T and dP^T = V dO^T for 64 queries
-      auto issue_scores = [&](const DkvWalk& c) -> bool {
-        const uint32_t g = c.g_hs();
-        const int bf = g & 1, s = c.g_it & 1, kb = c.item_it & 1;
-        if (c.first_half() && !at_wait(&kv_full[kb], (c.item_it >> 1) & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) return false;
-        if (c.hs == 0 && !at_wait(&q_full[s], (c.g_it >> 1) & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) return false;
-        tc_fence_after();
-        mma_kmajor_kmajor<HD>(tmem_ST + bf * QH, smem_u32(sK + kb * TILE), smem_u32(sQ + s * TILE + c.hs * HALF_ROWS), idesc_s, false);
-        mma_kmajor_kmajor<HD>(tmem_dPT + bf * QH, smem_u32(sV + kb * TILE), smem_u32(sDO + s * TILE + c.hs * HALF_ROWS), idesc_s,
-                              false);
-        umma_commit(&st_full[bf]);
-        if (c.last_half()) umma_commit(&kv_empty[kb]);
-        return true;
-      };
-      DkvWalk cs, cd;                      // cs: the half-step whose scores are issued next; cd: whose dV / dK are
-      cs.start(p);
-      cd.start(p);
-      bool ok = true;
-      for (int n = 0; n < 2 && ok && cs.valid(); ++n) {
-        ok = issue_scores(cs);
-        cs.next_half();
-      }
-      while (ok && cd.valid()) {
-        const uint32_t g = cd.g_hs();
-        const int bf = g & 1, s = cd.g_it & 1;
-        if (!at_wait(&pt_ready[bf], (g >> 1) & 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) break;
-        tc_fence_after();
-        // the first dV / dK of an item overwrite the accumulators: the compute warps read out the previous item before
-        // they handed over this half-step
-        const bool acc = !cd.first_half();
-        mma_kmajor_mnmajor<QH>(tmem_dV, smem_u32(sPT + bf * TILE), smem_u32(sDO + s * TILE + cd.hs * HALF_ROWS), idesc_d, acc);
-        mma_kmajor_mnmajor<QH>(tmem_dK, smem_u32(sDST + bf * TILE), smem_u32(sQ + s * TILE + cd.hs * HALF_ROWS), idesc_d, acc);
-        umma_commit(&ps_empty[bf]);
-        if (cd.hs == 1) umma_commit(&q_empty[s]);
-        if (cd.last_half()) umma_commit(dkv_full);
-        cd.next_half();
-        // the score buffers of half-step g are free (pt_ready above): half-step g + 2 goes there
-        if (cs.valid()) {
-          ok = issue_scores(cs);
-          cs.next_half();
-        }
-      }
-    }
-    __syncwarp();
-  } else {
-    const int cq = warp >> 2;                  // 16-column (query) chunk of a half-step
-    const int r = (warp & 3) * 32 + lane;      // key row of this thread (its TMEM lane)
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const float sc = p.scale;
-    const float sc2 = sc * 1.4426950408889634f;
-    constexpr float LOG2E = 1.4426950408889634f;
-    bool ok = true;
-    float n_lse = INFINITY, n_dl = 0.f;        // statistics of the next iteration (see the kernel above)
-    int n_lo = 0x7fffffff;
-    auto fetch_stats = [&](int b, int h, int i0) {
-      const int i = i0 + r;
-      const bool in = i < p.T;
-      const long long row = (long long)b * p.T + i;
-      n_lse = in ? p.lse[row * p.H + h] * LOG2E : INFINITY;
-      n_dl = in ? p.delta[row * p.H + h] : 0.f;
-      int lo = 0;
-      if (in && p.lo) lo = p.lo[row];
-      if (in && p.window > 0) lo = max(lo, i - p.window + 1);
-      n_lo = in ? lo : 0x7fffffff;
-    };
-    DkvWalk c, cn;
-    c.start(p);
-    cn.start(p);
-    if (cq == 0 && cn.valid()) fetch_stats(cn.b, cn.head(), cn.i0());
-    if (cn.valid()) cn.next_iter();
-    while (c.valid()) {
-      const int j = c.j0 + r;
-      const bool row_ok = j < p.T;
-      const int i0 = c.i0();
-      const int bufi = c.g_it & 1;
-      if (cq == 0) {
-        sLse[bufi * AT_N + r] = n_lse;
-        sDl[bufi * AT_N + r] = n_dl;
-        sLo[bufi * AT_N + r] = n_lo;
-        if (cn.valid()) fetch_stats(cn.b, cn.head(), cn.i0());
-      }
-      if (cn.valid()) cn.next_iter();
-      asm volatile("bar.sync 1, 512;" ::: "memory");   // all AT_BWD_CW * 32 compute threads
-      const float* lse = sLse + bufi * AT_N;
-      const float* dl = sDl + bufi * AT_N;
-      const int* lo = sLo + bufi * AT_N;
-      const bool full = i0 > c.j0 && c.j0 + AT_N <= p.T && i0 + AT_M <= p.T && lo[AT_M - 1] <= c.j0;
-      // after a failed wait the loops keep running (without waiting or computing) so that every thread still reaches
-      // the named barrier above in every iteration
-      for (int hs = 0; hs < 2 && ok; ++hs) {
-        const uint32_t g = 2u * c.g_it + (uint32_t)hs;
-        const int bf = g & 1;
-        if (!at_wait(&st_full[bf], (g >> 1) & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        uint32_t rs[16], rp[16];
-        tmem_ld_32x16(tmem_ST + bf * QH + lane_base + cq * 16, rs);
-        tmem_ld_32x16(tmem_dPT + bf * QH + lane_base + cq * 16, rp);
-        tmem_ld_wait();
-        float pt[16], ds[16];
-        const int col0 = hs * QH + cq * 16;
-        if (full) {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col0 + k]));
-            pt[k] = pr;
-            ds[k] = pr * (__uint_as_float(rp[k]) - dl[col0 + k]) * sc;
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const int i = i0 + col0 + k;
-            const bool vis = row_ok && j <= i && j >= lo[col0 + k];
-            const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col0 + k])) : 0.f;
-            pt[k] = pr;
-            ds[k] = pr * (__uint_as_float(rp[k]) - dl[col0 + k]) * sc;
-          }
-        }
-        // the tensor core has read the P^T / dS^T that this buffer held two half-steps ago
-        if (!at_wait(&ps_empty[bf], ((g >> 1) & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) { ok = false; break; }
-        uint8_t* bp = sPT + bf * TILE;
-        uint8_t* bd = sDST + bf * TILE;
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          uint4 a, d;
-          a.x = Cvt<T>::pack2(pt[8 * q + 0], pt[8 * q + 1]); a.y = Cvt<T>::pack2(pt[8 * q + 2], pt[8 * q + 3]);
-          a.z = Cvt<T>::pack2(pt[8 * q + 4], pt[8 * q + 5]); a.w = Cvt<T>::pack2(pt[8 * q + 6], pt[8 * q + 7]);
-          d.x = Cvt<T>::pack2(ds[8 * q + 0], ds[8 * q + 1]); d.y = Cvt<T>::pack2(ds[8 * q + 2], ds[8 * q + 3]);
-          d.z = Cvt<T>::pack2(ds[8 * q + 4], ds[8 * q + 5]); d.w = Cvt<T>::pack2(ds[8 * q + 6], ds[8 * q + 7]);
-          *reinterpret_cast<uint4*>(bp + sw128_off(r, cq * 16 + 8 * q)) = a;
-          *reinterpret_cast<uint4*>(bd + sw128_off(r, cq * 16 + 8 * q)) = d;
-        }
-        tc_fence_before();
-        fence_proxy_async();
-        __syncwarp();                 // every lane's writes and fences, then one arrival for the warp
-        if (lane == 0) mbar_arrive(&pt_ready[bf]);
-      }
-      const bool item_done = c.it == c.n_it - 1;
-      if (item_done && ok) {
-        if (!at_wait(dkv_full, c.item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
-        if (ok) {
-          tc_fence_after();
-          const long long row_base = (long long)c.b * p.T;
-          T* dkp = reinterpret_cast<T*>(p.dk) + (row_base + j) * p.ld_dk + (long long)c.kvh * HD;
-          T* dvp = reinterpret_cast<T*>(p.dv) + (row_base + j) * p.ld_dv + (long long)c.kvh * HD;
-          // 16 warps over 2 x 64 accumulator columns: warp chunk cq reads 16 columns of dV and of dK
-          uint32_t rv[16], rk[16];
-          tmem_ld_32x16(tmem_dV + lane_base + cq * 16, rv);
-          tmem_ld_32x16(tmem_dK + lane_base + cq * 16, rk);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              uint4 qv, qk;
-              qv.x = Cvt<T>::pack2(__uint_as_float(rv[8 * q + 0]), __uint_as_float(rv[8 * q + 1]));
-              qv.y = Cvt<T>::pack2(__uint_as_float(rv[8 * q + 2]), __uint_as_float(rv[8 * q + 3]));
-              qv.z = Cvt<T>::pack2(__uint_as_float(rv[8 * q + 4]), __uint_as_float(rv[8 * q + 5]));
-              qv.w = Cvt<T>::pack2(__uint_as_float(rv[8 * q + 6]), __uint_as_float(rv[8 * q + 7]));
-              qk.x = Cvt<T>::pack2(__uint_as_float(rk[8 * q + 0]), __uint_as_float(rk[8 * q + 1]));
-              qk.y = Cvt<T>::pack2(__uint_as_float(rk[8 * q + 2]), __uint_as_float(rk[8 * q + 3]));
-              qk.z = Cvt<T>::pack2(__uint_as_float(rk[8 * q + 4]), __uint_as_float(rk[8 * q + 5]));
-              qk.w = Cvt<T>::pack2(__uint_as_float(rk[8 * q + 6]), __uint_as_float(rk[8 * q + 7]));
-              reinterpret_cast<uint4*>(dvp + cq * 16)[q] = qv;
-              reinterpret_cast<uint4*>(dkp + cq * 16)[q] = qk;
-            }
-          }
-          tc_fence_before();
-        }
-      }
-      c.next_iter();
-    }
-  }
-  __syncthreads();
-  if (*abort_flag) {
-    for (int k = 0; k < 64; ++k) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
-}
-
 // lo[i] = first position of the run of equal segment ids that contains i (per sequence); seg < 0 -> 0
 // One block of 1024 threads per sequence: running maximum of the run-start positions (chunked inclusive scan).
 __global__ void __launch_bounds__(1024) attn_seg_lo_kernel(const int* __restrict__ seg, int* __restrict__ lo, int B, int T) {
@@ -1331,19 +1229,24 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   const long long tiles = (a->T + AT_M - 1) / AT_M;
   const long long items_q = tiles * a->B * a->H, items_kv = tiles * a->B * a->KV;
   if (items_q > 0x7fffffffll - sms) return -1;
-  kq<<<(unsigned)std::min<long long>(items_q, sms), AT_BWD_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
   if constexpr (HD == 64) {
-    auto kkv64 = attn_tc_bwd_dkv64_kernel<T>;
-    constexpr size_t smem_kv64 = TILE * 12 + 6 * AT_N * 4 + 256 + 1024;
+    // key steps of 64, two CTAs per SM
+    CUtensorMap tk64, tv64;
+    if (gb_make_tmap_2d_16b(&tk64, a->k, rows, (uint64_t)a->KV * HD, a->ld_k, 64, 64, a->is_bf16)) return -21;
+    if (gb_make_tmap_2d_16b(&tv64, a->v, rows, (uint64_t)a->KV * HD, a->ld_v, 64, 64, a->is_bf16)) return -22;
+    auto kq64 = attn_tc_bwd_dq64_kernel<T>;
+    constexpr size_t smem_q64 = TILE * 3 + (size_t)64 * HD * 2 * 2 * AT_DQ64_STAGES + 128;
     static bool attr64 = false;
     if (!attr64) {
-      if (cudaFuncSetAttribute(kkv64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv64) != cudaSuccess) return -10;
+      if (cudaFuncSetAttribute(kq64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q64) != cudaSuccess) return -10;
+      (void)cudaFuncSetAttribute(kq64, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
       attr64 = true;
     }
-    kkv64<<<(unsigned)std::min<long long>(items_kv, sms), AT_BWD_THREADS, smem_kv64, st>>>(tq, tk, tv, tdo, p);
+    kq64<<<(unsigned)std::min<long long>(items_q, 2ll * sms), AT_DQ64_THREADS, smem_q64, st>>>(tq, tk64, tv64, tdo, p);
   } else {
-    kkv<<<(unsigned)std::min<long long>(items_kv, sms), AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
+    kq<<<(unsigned)std::min<long long>(items_q, sms), AT_BWD_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
   }
+  kkv<<<(unsigned)std::min<long long>(items_kv, sms), AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
   return gb_launch_rc();
 }
 
