@@ -1064,6 +1064,261 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
   if (warp == AT_BWD_W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// ============================================================================================ backward: dK, dV (head_dim 64)
+// The same product in query steps of 64 instead of 128: S^T 64 + dP^T 64 + dV 64 + dK 64 = 256 tensor-memory columns
+// and under 100 KB of shared memory, so two CTAs of 8 compute warps share an SM (see the dQ kernel above for why).
+template <typename T>
+__global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dkv64_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                           const __grid_constant__ CUtensorMap tmK,
+                                                                           const __grid_constant__ CUtensorMap tmV,
+                                                                           const __grid_constant__ CUtensorMap tmDO,
+                                                                           const AttnTcParams p) {
+  constexpr int HD = 64, QN = 64, ST = 2;
+  constexpr int W_TMA = AT_DQ64_CW, W_MMA = AT_DQ64_CW + 1;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t TILE = AT_N * HD * 2;          // K, V: [128 x 64]; P^T, dS^T of a step: [128 keys x 64 queries]
+  constexpr uint32_t QTILE = QN * HD * 2;           // Q, dO of a step: [64 x 64]
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sK = smem_raw;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sPT = sV + TILE;
+  uint8_t* sDST = sPT + TILE;
+  uint8_t* sQ = sDST + TILE;                // ST
+  uint8_t* sDO = sQ + ST * QTILE;           // ST
+  float* sLse = reinterpret_cast<float*>(sDO + ST * QTILE);   // [2][64]
+  float* sDl = sLse + 2 * QN;
+  int* sLo = reinterpret_cast<int*>(sDl + 2 * QN);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sLo + 2 * QN);
+  uint64_t* kv_full = bars;
+  uint64_t* kv_empty = bars + 1;
+  uint64_t* st_full = bars + 2;
+  uint64_t* pt_ready = bars + 3;
+  uint64_t* dkv_full = bars + 4;
+  uint64_t* q_full = bars + 5;              // ST
+  uint64_t* q_empty = bars + 5 + ST;        // ST
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 + 2 * ST);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = p.H / p.KV;
+  const int n_kt = (p.T + AT_N - 1) / AT_N, BKV = p.B * p.KV;
+  const int n_items = n_kt * BKV;
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
+    mbar_init(st_full, 1);
+    mbar_init(pt_ready, AT_DQ64_CW);
+    mbar_init(dkv_full, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == W_MMA) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + QN, tmem_dV = tmem_base + 2 * QN, tmem_dK = tmem_base + 2 * QN + HD;
+
+  // the query steps of an item start at its key tile: n_qs steps of 64 queries for each head of the group
+  auto item_range = [&](int item, int& b, int& kvh, int& j0, int& n_qs) {
+    const int jt = item / BKV, bk = item - jt * BKV;
+    b = bk / p.KV;
+    kvh = bk - b * p.KV;
+    j0 = jt * AT_N;
+    int i_hi = p.T;
+    if (p.window > 0) i_hi = min(p.T, j0 + AT_N - 1 + p.window);
+    n_qs = (i_hi - j0 + QN - 1) / QN;
+  };
+
+  if (warp == W_TMA) {
+    if (lane == 0) {
+      uint32_t g_it = 0, item_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+        int b, kvh, j0, n_qs;
+        item_range(item, b, kvh, j0, n_qs);
+        const int row_base = b * p.T;
+        if (!at_wait(kv_empty, (item_it & 1u) ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        mbar_arrive_expect_tx(kv_full, 2 * TILE);
+        load_tile<HD>(&tmK, kv_full, sK, kvh * HD, row_base + j0);
+        load_tile<HD>(&tmV, kv_full, sV, kvh * HD, row_base + j0);
+        const int n_it = group * n_qs;
+        for (int it = 0; it < n_it; ++it, ++g_it) {
+          const int s = g_it % ST, ph = (g_it / ST) & 1;
+          const int h = kvh * group + it / n_qs;
+          const int i0 = j0 + (it % n_qs) * QN;
+          if (!at_wait(&q_empty[s], ph ^ 1, p.status, ST_TIMEOUT_EMPTY, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&q_full[s], 2 * QTILE);
+          tma_load_2d(&tmQ, &q_full[s], sQ + s * QTILE, h * HD, row_base + i0);
+          tma_load_2d(&tmDO, &q_full[s], sDO + s * QTILE, h * HD, row_base + i0);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == W_MMA) {
+    if (lane == 0) {
+      constexpr int fmt = OperandFmt<T>::value;
+      const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AT_N, QN);
+      const uint32_t idesc_d = make_idesc_f16(fmt, 0, 1, AT_N, HD);
+      uint32_t g_it = 0, item_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++item_it) {
+        int b, kvh, j0, n_qs;
+        item_range(item, b, kvh, j0, n_qs);
+        if (!at_wait(kv_full, item_it & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        const int n_it = group * n_qs;
+        for (int it = 0; it < n_it; ++it, ++g_it) {
+          const int s = g_it % ST, ph = (g_it / ST) & 1;
+          if (!at_wait(&q_full[s], ph, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_kmajor<HD>(tmem_ST, smem_u32(sK), smem_u32(sQ + s * QTILE), idesc_s, false);
+          mma_kmajor_kmajor<HD>(tmem_dPT, smem_u32(sV), smem_u32(sDO + s * QTILE), idesc_s, false);
+          umma_commit(st_full);
+          if (it == n_it - 1) umma_commit(kv_empty);
+          if (!at_wait(pt_ready, g_it & 1u, p.status, ST_TIMEOUT_TMEM_EMPTY, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          mma_kmajor_mnmajor<QN>(tmem_dV, smem_u32(sPT), smem_u32(sDO + s * QTILE), idesc_d, it > 0);
+          mma_kmajor_mnmajor<QN>(tmem_dK, smem_u32(sDST), smem_u32(sQ + s * QTILE), idesc_d, it > 0);
+          umma_commit(&q_empty[s]);
+        }
+        if (ok) umma_commit(dkv_full);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int cq = warp >> 2;                  // 32-column chunk: of the 64 queries of a step, of the 64 of dV / dK
+    const int r = (warp & 3) * 32 + lane;      // key row of this thread (its TMEM lane)
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const float sc = p.scale;
+    const float sc2 = sc * 1.4426950408889634f;
+    constexpr float LOG2E = 1.4426950408889634f;
+    uint32_t g_it = 0, item_it = 0;
+    bool ok = true;
+    // statistics of the next step's 64 queries, fetched one step ahead by the first 64 compute threads
+    const bool stat_thread = threadIdx.x < QN;
+    float n_lse = INFINITY, n_dl = 0.f;
+    int n_lo = 0x7fffffff;
+    auto fetch_stats = [&](int b, int h, int i0) {
+      const int i = i0 + (int)threadIdx.x;
+      const bool in = i < p.T;
+      const long long row = (long long)b * p.T + i;
+      n_lse = in ? p.lse[row * p.H + h] * LOG2E : INFINITY;
+      n_dl = in ? p.delta[row * p.H + h] : 0.f;
+      int lo = 0;
+      if (in && p.lo) lo = p.lo[row];
+      if (in && p.window > 0) lo = max(lo, i - p.window + 1);
+      n_lo = in ? lo : 0x7fffffff;
+    };
+    if (stat_thread && (int)blockIdx.x < n_items) {
+      int b, kvh, j0, n_qs;
+      item_range(blockIdx.x, b, kvh, j0, n_qs);
+      fetch_stats(b, kvh * group, j0);
+    }
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++item_it) {
+      int b, kvh, j0, n_qs;
+      item_range(item, b, kvh, j0, n_qs);
+      const long long row_base = (long long)b * p.T;
+      const int j = j0 + r;
+      const bool row_ok = j < p.T;
+      const int n_it = group * n_qs;
+      for (int it = 0; it < n_it; ++it, ++g_it) {
+        const int i0 = j0 + (it % n_qs) * QN;
+        const int bufi = g_it & 1;
+        if (stat_thread) {
+          sLse[bufi * QN + threadIdx.x] = n_lse;
+          sDl[bufi * QN + threadIdx.x] = n_dl;
+          sLo[bufi * QN + threadIdx.x] = n_lo;
+          if (it + 1 < n_it) {
+            fetch_stats(b, kvh * group + (it + 1) / n_qs, j0 + ((it + 1) % n_qs) * QN);
+          } else if (item + (int)gridDim.x < n_items) {
+            int b2, kvh2, j02, n_qs2;
+            item_range(item + gridDim.x, b2, kvh2, j02, n_qs2);
+            fetch_stats(b2, kvh2 * group, j02);
+          }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // all AT_DQ64_CW * 32 compute threads
+        // after a failed wait the loops keep running (without waiting or computing) so that every thread still
+        // reaches the named barrier above in every step
+        if (ok && !at_wait(st_full, g_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
+        if (!ok) continue;
+        tc_fence_after();
+        const float* lse = sLse + bufi * QN;
+        const float* dl = sDl + bufi * QN;
+        const int* lo = sLo + bufi * QN;
+        // every (key, query) pair of the step visible: queries after the whole key tile, whole tiles, and the largest
+        // `lo` of the step (its last query) at or before the first key
+        const bool full = i0 >= j0 + AT_N && j0 + AT_N <= p.T && i0 + QN <= p.T && lo[QN - 1] <= j0;
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_ST + lane_base + cq * 32, rs);
+        tmem_ld_32x32(tmem_dPT + lane_base + cq * 32, rp);
+        tmem_ld_wait();
+        float pt[32], ds[32];
+        if (full) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int col = cq * 32 + k;
+            const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col]));
+            pt[k] = pr;
+            ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int col = cq * 32 + k;
+            const int i = i0 + col;
+            const bool vis = row_ok && j <= i && j >= lo[col];
+            const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col])) : 0.f;
+            pt[k] = pr;
+            ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+          }
+        }
+        store_p_chunk<T>(sPT, r, cq * 32, pt);
+        store_p_chunk<T>(sDST, r, cq * 32, ds);
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();                 // every lane's writes and fences, then one arrival for the warp
+        if (lane == 0) mbar_arrive(pt_ready);
+      }
+      if (ok && !at_wait(dkv_full, item_it & 1u, p.status, ST_TIMEOUT_TMEM_FULL, abort_flag)) ok = false;
+      if (!ok) continue;
+      tc_fence_after();
+      T* dkp = reinterpret_cast<T*>(p.dk) + (row_base + j) * p.ld_dk + (long long)kvh * HD;
+      T* dvp = reinterpret_cast<T*>(p.dv) + (row_base + j) * p.ld_dv + (long long)kvh * HD;
+      uint32_t rv[32], rk[32];
+      tmem_ld_32x32(tmem_dV + lane_base + cq * 32, rv);
+      tmem_ld_32x32(tmem_dK + lane_base + cq * 32, rk);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 qv, qk;
+          qv.x = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 0]), __uint_as_float(rv[8 * k + 1]));
+          qv.y = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 2]), __uint_as_float(rv[8 * k + 3]));
+          qv.z = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 4]), __uint_as_float(rv[8 * k + 5]));
+          qv.w = Cvt<T>::pack2(__uint_as_float(rv[8 * k + 6]), __uint_as_float(rv[8 * k + 7]));
+          qk.x = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 0]), __uint_as_float(rk[8 * k + 1]));
+          qk.y = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 2]), __uint_as_float(rk[8 * k + 3]));
+          qk.z = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 4]), __uint_as_float(rk[8 * k + 5]));
+          qk.w = Cvt<T>::pack2(__uint_as_float(rk[8 * k + 6]), __uint_as_float(rk[8 * k + 7]));
+          reinterpret_cast<uint4*>(dvp + cq * 32)[k] = qv;
+          reinterpret_cast<uint4*>(dkp + cq * 32)[k] = qk;
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
+}
+
 // lo[i] = first position of the run of equal segment ids that contains i (per sequence); seg < 0 -> 0
 // One block of 1024 threads per sequence: running maximum of the run-start positions (chunked inclusive scan).
 __global__ void __launch_bounds__(1024) attn_seg_lo_kernel(const int* __restrict__ seg, int* __restrict__ lo, int B, int T) {
@@ -1246,7 +1501,23 @@ int launch_tc_bwd(const gb_attn_args* a, int* lo, int* status, cudaStream_t st) 
   } else {
     kq<<<(unsigned)std::min<long long>(items_q, sms), AT_BWD_THREADS, smem_q, st>>>(tq, tk, tv, tdo, p);
   }
-  kkv<<<(unsigned)std::min<long long>(items_kv, sms), AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
+  if constexpr (HD == 64) {
+    // query steps of 64, two CTAs per SM
+    CUtensorMap tq64, tdo64;
+    if (gb_make_tmap_2d_16b(&tq64, a->q, rows, (uint64_t)a->H * HD, a->ld_q, 64, 64, a->is_bf16)) return -20;
+    if (gb_make_tmap_2d_16b(&tdo64, a->d_o, rows, (uint64_t)a->H * HD, a->ld_do, 64, 64, a->is_bf16)) return -23;
+    auto kkv64 = attn_tc_bwd_dkv64_kernel<T>;
+    constexpr size_t smem_kv64 = TILE * 4 + (size_t)64 * HD * 2 * 2 * 2 + 6 * 64 * 4 + 128;
+    static bool attr_kv64 = false;
+    if (!attr_kv64) {
+      if (cudaFuncSetAttribute(kkv64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv64) != cudaSuccess) return -10;
+      (void)cudaFuncSetAttribute(kkv64, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      attr_kv64 = true;
+    }
+    kkv64<<<(unsigned)std::min<long long>(items_kv, 2ll * sms), AT_DQ64_THREADS, smem_kv64, st>>>(tq64, tk, tv, tdo64, p);
+  } else {
+    kkv<<<(unsigned)std::min<long long>(items_kv, sms), AT_BWD_THREADS, smem_kv, st>>>(tq, tk, tv, tdo, p);
+  }
   return gb_launch_rc();
 }
 
