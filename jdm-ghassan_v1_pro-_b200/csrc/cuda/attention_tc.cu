@@ -1257,23 +1257,34 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dkv64_kernel(c
         tmem_ld_32x32(tmem_dPT + lane_base + cq * 32, rp);
         tmem_ld_wait();
         float pt[32], ds[32];
-        if (full) {
+        // the statistics of this warp's 32 queries come as 16-byte loads (every lane reads the same words), four
+        // queries at a time
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const int col = cq * 32 + k;
-            const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col]));
-            pt[k] = pr;
-            ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
-          }
-        } else {
+        for (int k4 = 0; k4 < 8; ++k4) {
+          const float4 a4 = reinterpret_cast<const float4*>(lse + cq * 32)[k4];
+          const float4 d4 = reinterpret_cast<const float4*>(dl + cq * 32)[k4];
+          const float lv[4] = {a4.x, a4.y, a4.z, a4.w};
+          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          if (full) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const int col = cq * 32 + k;
-            const int i = i0 + col;
-            const bool vis = row_ok && j <= i && j >= lo[col];
-            const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col])) : 0.f;
-            pt[k] = pr;
-            ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+            for (int e = 0; e < 4; ++e) {
+              const int k = 4 * k4 + e;
+              const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lv[e]));
+              pt[k] = pr;
+              ds[k] = pr * (__uint_as_float(rp[k]) - dv[e]) * sc;
+            }
+          } else {
+            const int4 l4 = reinterpret_cast<const int4*>(lo + cq * 32)[k4];
+            const int lov[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int k = 4 * k4 + e;
+              const int i = i0 + cq * 32 + k;
+              const bool vis = row_ok && j <= i && j >= lov[e];
+              const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lv[e])) : 0.f;
+              pt[k] = pr;
+              ds[k] = pr * (__uint_as_float(rp[k]) - dv[e]) * sc;
+            }
           }
         }
         store_p_chunk<T>(sPT, r, cq * 32, pt);
