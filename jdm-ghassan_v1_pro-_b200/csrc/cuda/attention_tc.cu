@@ -521,12 +521,12 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
       const int i = q0 + r;
       const bool row_ok = i < p.T;
       int lo_i = 0;
-      float lse2 = INFINITY, dl = 0.f;
+      float lse2 = INFINITY, dls = 0.f;
       if (row_ok) {
         if (p.lo) lo_i = p.lo[row_base + i];
         if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
         lse2 = p.lse[(row_base + i) * p.H + h] * 1.4426950408889634f;
-        dl = p.delta[(row_base + i) * p.H + h];
+        dls = p.delta[(row_base + i) * p.H + h] * sc;      // delta times the scale: dS = P (dP * scale - dls)
       }
       for (int t = 0; t < n_tiles; ++t, ++tile_it) {
         const int j0 = k_lo + t * AT_N;
@@ -544,7 +544,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
               const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2));
-              ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+              ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dls);
             }
           } else {
 #pragma unroll
@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dq_kernel(const __
               const int j = j0 + c * 32 + k;
               const bool vis = row_ok && j <= i && j >= lo_i;
               const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2)) : 0.f;
-              ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+              ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dls);
             }
           }
           store_p_chunk<T>(sDS, r, c * 32, ds);
@@ -734,12 +734,12 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dq64_kernel(co
       const int i = q0 + r;
       const bool row_ok = i < p.T;
       int lo_i = 0;
-      float lse2 = INFINITY, dl = 0.f;
+      float lse2 = INFINITY, dls = 0.f;
       if (row_ok) {
         if (p.lo) lo_i = p.lo[row_base + i];
         if (p.window > 0) lo_i = max(lo_i, i - p.window + 1);
         lse2 = p.lse[(row_base + i) * p.H + h] * 1.4426950408889634f;
-        dl = p.delta[(row_base + i) * p.H + h];
+        dls = p.delta[(row_base + i) * p.H + h] * sc;      // delta times the scale: dS = P (dP * scale - dls)
       }
       for (int t = 0; t < n_steps; ++t, ++step_it) {
         const int j0 = k_lo + t * KN;
@@ -755,7 +755,7 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dq64_kernel(co
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
             const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2));
-            ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+            ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dls);
           }
         } else {
 #pragma unroll
@@ -763,7 +763,7 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dq64_kernel(co
             const int j = j0 + cq * 32 + k;
             const bool vis = row_ok && j <= i && j >= lo_i;
             const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse2)) : 0.f;
-            ds[k] = pr * (__uint_as_float(rp[k]) - dl) * sc;
+            ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dls);
           }
         }
         store_p_chunk<T>(sDS, r, cq * 32, ds);
@@ -946,7 +946,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
       const bool in = i < p.T;
       const long long row = (long long)b * p.T + i;
       n_lse = in ? p.lse[row * p.H + h] * LOG2E : INFINITY;
-      n_dl = in ? p.delta[row * p.H + h] : 0.f;
+      n_dl = in ? p.delta[row * p.H + h] * sc : 0.f;       // delta times the scale: dS = P (dP * scale - that)
       int lo = 0;
       if (in && p.lo) lo = p.lo[row];
       if (in && p.window > 0) lo = max(lo, i - p.window + 1);
@@ -1004,7 +1004,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
               const int col = c * 32 + k;
               const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col]));
               pt[k] = pr;
-              ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+              ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dl[col]);
             }
           } else {
 #pragma unroll
@@ -1014,7 +1014,7 @@ __global__ void __launch_bounds__(AT_BWD_THREADS) attn_tc_bwd_dkv_kernel(const _
               const bool vis = row_ok && j <= i && j >= lo[col];
               const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lse[col])) : 0.f;
               pt[k] = pr;
-              ds[k] = pr * (__uint_as_float(rp[k]) - dl[col]) * sc;
+              ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dl[col]);
             }
           }
           store_p_chunk<T>(sPT, r, c * 32, pt);
@@ -1207,7 +1207,7 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dkv64_kernel(c
       const bool in = i < p.T;
       const long long row = (long long)b * p.T + i;
       n_lse = in ? p.lse[row * p.H + h] * LOG2E : INFINITY;
-      n_dl = in ? p.delta[row * p.H + h] : 0.f;
+      n_dl = in ? p.delta[row * p.H + h] * sc : 0.f;       // delta times the scale: dS = P (dP * scale - that)
       int lo = 0;
       if (in && p.lo) lo = p.lo[row];
       if (in && p.window > 0) lo = max(lo, i - p.window + 1);
@@ -1271,7 +1271,7 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dkv64_kernel(c
               const int k = 4 * k4 + e;
               const float pr = exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lv[e]));
               pt[k] = pr;
-              ds[k] = pr * (__uint_as_float(rp[k]) - dv[e]) * sc;
+              ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dv[e]);
             }
           } else {
             const int4 l4 = reinterpret_cast<const int4*>(lo + cq * 32)[k4];
@@ -1283,7 +1283,7 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dkv64_kernel(c
               const bool vis = row_ok && j <= i && j >= lov[e];
               const float pr = vis ? exp2f(fmaf(__uint_as_float(rs[k]), sc2, -lv[e])) : 0.f;
               pt[k] = pr;
-              ds[k] = pr * (__uint_as_float(rp[k]) - dv[e]) * sc;
+              ds[k] = pr * fmaf(__uint_as_float(rp[k]), sc, -dv[e]);
             }
           }
         }
