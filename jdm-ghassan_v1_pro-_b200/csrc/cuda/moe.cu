@@ -11,6 +11,8 @@
 // structure is not: the reference syncs the host once per layer per pass to read group offsets and loops
 // over experts with one cuBLAS call each.
 #include "sm100_common.cuh"
+#include <algorithm>
+
 #include "gb_api.h"
 
 namespace gb {
@@ -189,17 +191,45 @@ __global__ void moe_scan_kernel(const gb_moe_args a, int n_blocks, int staged) {
   const int seg_tok = a.seg_tokens > 0 ? a.seg_tokens : a.n_tok;
   const int bps = (a.seg_tokens > 0 && a.seg_tokens < a.n_tok) ? seg_tok / bt : n_blocks;   // blocks per segment
   const int n_seg = (a.n_tok + seg_tok - 1) / seg_tok;
-  if (e < ne1) {
+  if (staged) {
+    // one warp per expert: exclusive scan of its column over the blocks, 32 blocks per trip (one thread per expert
+    // walking all blocks was a chain of a thousand dependent shared-memory round trips, most of this kernel's time)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int ex = warp; ex < ne1; ex += n_warps) {
+      int run = 0;
+      for (int b0 = 0; b0 < n_blocks; b0 += 32) {
+        const int b = b0 + lane;
+        const int c = b < n_blocks ? s_tab[b * stride + ex] : 0;
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int n = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += n;
+        }
+        if (b < n_blocks) s_tab[b * stride + ex] = run + inc - c;
+        run += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) {
+        s_total[ex] = run;
+        a.block_base[(size_t)n_blocks * stride + ex] = run;  // last row: totals
+      }
+    }
+    __syncthreads();
+    // routed-slot share of every (segment, expert): a difference of two scanned values
+    if (a.f_frac)
+      for (int idx = threadIdx.x; idx < n_seg * a.ne; idx += blockDim.x) {
+        const int sgi = idx / a.ne, ex = idx - sgi * a.ne;
+        const int b_lo = sgi * bps, b_hi = min(n_blocks, b_lo + bps);
+        const int lo = s_tab[b_lo * stride + ex];
+        const int hi = b_hi < n_blocks ? s_tab[b_hi * stride + ex] : s_total[ex];
+        const int ntk = min(seg_tok, a.n_tok - sgi * seg_tok);
+        a.f_frac[(size_t)sgi * a.ne + ex] = (float)(hi - lo) / (float)((long long)ntk * a.top_k);
+      }
+  } else if (e < ne1) {
     int run = 0, segsum = 0;
     for (int b = 0; b < n_blocks; ++b) {
-      int c;
-      if (staged) {
-        c = s_tab[b * stride + e];
-        s_tab[b * stride + e] = run;
-      } else {
-        c = a.block_hist[(size_t)b * stride + e];
-        a.block_base[(size_t)b * stride + e] = run;   // relative for now
-      }
+      const int c = a.block_hist[(size_t)b * stride + e];
+      a.block_base[(size_t)b * stride + e] = run;   // relative for now
       run += c;
       segsum += c;
       if (((b + 1) % bps == 0 || b == n_blocks - 1) && e < a.ne && a.f_frac) {
@@ -499,6 +529,144 @@ __global__ void __launch_bounds__(256, 4) moe_router_bwd_kernel(const gb_moe_arg
   }
 }
 
+// The same for at most 8 experts, in two kernels.  moe_router_dlogit_kernel is the router-logit part above (one thread
+// per token, a few hundred bytes); moe_router_dx_kernel then streams the input gradient with the router rows held in
+// registers: a lane owns 8 columns of all (<= 8) experts for the life of the block, 4 token groups x 96 lanes per
+// block, blocks walk the tokens with a grid stride.  Per token a lane issues its slot rows' 16-byte loads and two
+// broadcast loads of the logit gradients; the 24 KB of router rows are no longer re-read from L1 for every token
+// (sixteen 16-byte loads per 8 columns, three quarters of the one-kernel form's load instructions).
+__global__ void __launch_bounds__(256) moe_router_dlogit_kernel(const gb_moe_args a) {
+  // one thread per token: with at most 8 experts everything of a token fits a thread's registers, and its dozen
+  // loads are independent (a warp per token waited for them in sequence, round after round)
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= a.n_tok) return;
+  const int ne = a.ne, K = a.top_k;
+  float p[8], dp[8];
+  int idx[MAX_K];
+  float gd[MAX_K], wk[MAX_K];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) p[e] = e < ne ? a.probs[(size_t)t * ne + e] : 0.f;
+#pragma unroll
+  for (int k = 0; k < MAX_K; ++k)
+    if (k < K) { idx[k] = a.idx[(size_t)t * K + k]; gd[k] = a.gdot[(size_t)t * K + k]; wk[k] = a.w[(size_t)t * K + k]; }
+  const int sgi = a.seg_tokens > 0 ? t / a.seg_tokens : 0;       // micro-batch segment of this token
+  const int tj = a.seg_tokens > 0 ? t - sgi * a.seg_tokens : t;
+  const float aux_coef = a.dyn_aux_coef ? a.dyn_aux_coef[sgi] : a.aux_coef;
+  const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;
+  const bool aux = a.f_frac && aux_coef != 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) dp[e] = (aux && e < ne) ? aux_coef * a.f_frac[(size_t)sgi * ne + e] : 0.f;
+  float ssum = 0.f, gbar = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAX_K; ++k)
+    if (k < K) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ssum += idx[k] == e ? p[e] : 0.f;
+      gbar += gd[k] * wk[k];
+    }
+  if (ssum > 1e-8f) {
+    const float invs = 1.f / ssum;
+#pragma unroll
+    for (int k = 0; k < MAX_K; ++k)
+      if (k < K) {
+        const float v = (gd[k] - gbar) * invs;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dp[e] += idx[k] == e ? v : 0.f;
+      }
+  }
+  float pdp = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) pdp += p[e] * dp[e];
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    if (e < ne) {
+      float dl = p[e] * (dp[e] - pdp);
+      if (a.use_jitter) dl *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
+      a.part[(size_t)t * ne + e] = dl;
+    }
+}
+
+constexpr int RD_LANES = 96, RD_GROUPS = 4;
+template <typename T, int NS>       // NS = slots per token (top_k + shared), so that the row buffers are exactly that long
+__global__ void __launch_bounds__(RD_LANES * RD_GROUPS) moe_router_dx_kernel(const gb_moe_args a) {
+  const int g = threadIdx.x / RD_LANES, l = threadIdx.x - g * RD_LANES;
+  const int c0 = (blockIdx.y * RD_LANES + l) * 8;
+  const int ne = a.ne, d = a.d;
+  constexpr int S = NS;
+  if (c0 >= d) return;                            // no block-wide barrier below
+  float w[8][8];                                  // router rows of this lane's 8 columns (zero beyond ne)
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+    if (e < ne) {
+      w0 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + c0);
+      w1 = *reinterpret_cast<const float4*>(a.router_w + (size_t)e * d + c0 + 4);
+    }
+    w[e][0] = w0.x; w[e][1] = w0.y; w[e][2] = w0.z; w[e][3] = w0.w;
+    w[e][4] = w1.x; w[e][5] = w1.y; w[e][6] = w1.z; w[e][7] = w1.w;
+  }
+  const T* dxp = reinterpret_cast<const T*>(a.dx_perm);
+  T* dx = reinterpret_cast<T*>(a.dx16);
+  const bool vec = ne == 8;
+  // Two tokens in flight: a token's slot rows depend on its slot positions, a chain of two global loads.  The positions
+  // are fetched two tokens ahead and the rows one token ahead, so that every trip waits for one load, not two.
+  const int stride = gridDim.x * RD_GROUPS;
+  auto load_pos = [&](int t, int (&pos)[NS]) {
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+      pos[s] = t < a.n_tok ? a.slot_pos[(size_t)t * S + s] : 0;
+  };
+  auto load_rows = [&](int t, const int (&pos)[NS], uint4 (&q)[NS], float (&dl)[8]) {
+    if (t >= a.n_tok) return;
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+      q[s] = *reinterpret_cast<const uint4*>(dxp + (size_t)pos[s] * d + c0);
+    if (vec) {
+      const float4 a4 = *reinterpret_cast<const float4*>(a.part + (size_t)t * 8);
+      const float4 b4 = *reinterpret_cast<const float4*>(a.part + (size_t)t * 8 + 4);
+      dl[0] = a4.x; dl[1] = a4.y; dl[2] = a4.z; dl[3] = a4.w; dl[4] = b4.x; dl[5] = b4.y; dl[6] = b4.z; dl[7] = b4.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dl[e] = e < ne ? a.part[(size_t)t * ne + e] : 0.f;
+    }
+  };
+  int t0 = blockIdx.x * RD_GROUPS + g;
+  int pos0[NS], pos1[NS];
+  uint4 q0[NS], q1[NS];
+  float dl0[8], dl1[8];
+  load_pos(t0, pos0);
+  load_pos(t0 + stride, pos1);
+  load_rows(t0, pos0, q0, dl0);
+  for (; t0 < a.n_tok; t0 += stride) {
+    load_rows(t0 + stride, pos1, q1, dl1);          // the next token's rows
+    load_pos(t0 + 2 * stride, pos0);                // positions of the one after (pos0 is free: its rows are loaded)
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+      {
+        const float2 v0 = Cvt<T>::unpack2(q0[s].x), v1 = Cvt<T>::unpack2(q0[s].y), v2 = Cvt<T>::unpack2(q0[s].z),
+                     v3 = Cvt<T>::unpack2(q0[s].w);
+        acc[0] += v0.x; acc[1] += v0.y; acc[2] += v1.x; acc[3] += v1.y; acc[4] += v2.x; acc[5] += v2.y; acc[6] += v3.x; acc[7] += v3.y;
+      }
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += dl0[e] * w[e][j];
+    uint4 o;
+    o.x = Cvt<T>::pack2(acc[0], acc[1]); o.y = Cvt<T>::pack2(acc[2], acc[3]);
+    o.z = Cvt<T>::pack2(acc[4], acc[5]); o.w = Cvt<T>::pack2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(dx + (size_t)t0 * d + c0) = o;
+    // hand over: next token's rows become current, the freshly loaded positions become next
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+      { q0[s] = q1[s]; const int tmp = pos0[s]; pos0[s] = pos1[s]; pos1[s] = tmp; }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dl0[e] = dl1[e];
+  }
+}
+
 // d_router_w[e, c] += sum_t dlogit[t, e] * x16[t, c], in a fixed order (deterministic).
 // grid (column groups / 96, token chunks, expert groups of 8), 384 threads = 4 token groups x 96 lanes.  A lane owns 8
 // columns (one 16-byte load of the activations per token) and 8 experts, 64 sums in registers; token group g takes
@@ -624,6 +792,18 @@ __global__ void __launch_bounds__(256) moe_router_wgrad_fold_kernel(const float*
 
 using namespace gb;
 
+template <typename T>
+static void launch_router_dx(const gb_moe_args& a, int n_slots, dim3 grid, cudaStream_t st) {
+  switch (n_slots) {
+    case 1: moe_router_dx_kernel<T, 1><<<grid, RD_LANES * RD_GROUPS, 0, st>>>(a); break;
+    case 2: moe_router_dx_kernel<T, 2><<<grid, RD_LANES * RD_GROUPS, 0, st>>>(a); break;
+    case 3: moe_router_dx_kernel<T, 3><<<grid, RD_LANES * RD_GROUPS, 0, st>>>(a); break;
+    case 4: moe_router_dx_kernel<T, 4><<<grid, RD_LANES * RD_GROUPS, 0, st>>>(a); break;
+    case 5: moe_router_dx_kernel<T, 5><<<grid, RD_LANES * RD_GROUPS, 0, st>>>(a); break;
+    default: moe_router_dx_kernel<T, 6><<<grid, RD_LANES * RD_GROUPS, 0, st>>>(a); break;
+  }
+}
+
 static int moe_check(const gb_moe_args* a) {
   if (!a || a->n_tok <= 0 || a->d <= 0 || a->d % 8) return -1;
   if (a->ne <= 0 || a->ne > MAX_NE || a->top_k <= 0 || a->top_k > MAX_K || a->top_k > a->ne) return -2;
@@ -723,13 +903,30 @@ extern "C" int gb_moe_router_bwd(const gb_moe_args* a, cudaStream_t st) {
   if (chunks > GB_ROUTER_WGRAD_CHUNKS) chunks = GB_ROUTER_WGRAD_CHUNKS;
   dim3 g2((a->d / 8 + RW_LANES - 1) / RW_LANES, chunks, (a->ne + 7) / 8);
   float* wout = chunks > 1 ? a->part2 : a->d_router_w;
+  // up to 8 experts: logit gradients first, then the input gradient with the router rows in registers
+  const int n_slots = a->top_k + (a->shared ? 1 : 0);
+  const bool split = a->ne <= 8 && n_slots <= 6;
+  int sms = 0, dev = 0;
+  if (split && (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess))
+    return -10;
+  dim3 gdx(std::max(1, std::min(sms, (a->n_tok + RD_GROUPS - 1) / RD_GROUPS)), (a->d / 8 + RD_LANES - 1) / RD_LANES);   // one resident block per SM
   if (a->is_bf16) {
-    moe_router_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*a);
+    if (split) {
+      moe_router_dlogit_kernel<<<(a->n_tok + 255) / 256, 256, 0, st>>>(*a);
+      launch_router_dx<__nv_bfloat16>(*a, n_slots, gdx, st);
+    } else {
+      moe_router_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*a);
+    }
     if (a->d_router_w)
       moe_router_wgrad_kernel<__nv_bfloat16><<<g2, RW_LANES * RW_GROUPS, 0, st>>>(a->part, (const __nv_bfloat16*)a->x16, wout, a->n_tok,
                                                                  a->ne, a->d);
   } else {
-    moe_router_bwd_kernel<__half><<<grid, 256, 0, st>>>(*a);
+    if (split) {
+      moe_router_dlogit_kernel<<<(a->n_tok + 255) / 256, 256, 0, st>>>(*a);
+      launch_router_dx<__half>(*a, n_slots, gdx, st);
+    } else {
+      moe_router_bwd_kernel<__half><<<grid, 256, 0, st>>>(*a);
+    }
     if (a->d_router_w)
       moe_router_wgrad_kernel<__half><<<g2, RW_LANES * RW_GROUPS, 0, st>>>(a->part, (const __half*)a->x16, wout, a->n_tok, a->ne, a->d);
   }
