@@ -142,6 +142,7 @@ typedef struct gb_moe_args {
   // seg_weight (device, [segments], may be NULL = 1) weights each segment's balance loss in aux_acc.  0 = one segment.
   int seg_tokens;
   const float* seg_weight;
+  int* status;                       // device status word for kernels with bounded waits (tensor-core router), or NULL
 } gb_moe_args;
 int gb_moe_seg_ok(int n_tok, int seg_tokens);   // 1 when seg_tokens is usable for a pass of n_tok tokens
 #define GB_ROUTER_WGRAD_CHUNKS 256

@@ -12,6 +12,7 @@
 // over experts with one cuBLAS call each.
 #include "sm100_common.cuh"
 #include <algorithm>
+#include <type_traits>
 
 #include "gb_api.h"
 
@@ -168,6 +169,173 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const gb_moe_args a) {
   }
   __syncthreads();
   for (int i = threadIdx.x; i <= ne; i += blockDim.x) a.block_hist[(size_t)blockIdx.x * (ne + 1) + i] = s_hist[i];
+}
+
+// ------------------------------------------------------------------------------------------------ router on tcgen05
+// The router logits are a GEMM with a tiny N: logits[n_tok, ne] = x16[n_tok, d] * router_w[ne, d]^T.  For at most 8
+// experts one CTA takes 128 tokens: warp 0 streams their activations through a 4-stage ring of [128 x 64] TMA tiles,
+// warp 1 issues M = 128, N = 16, K = 16 MMAs into 16 tensor-memory columns, and warps 2-5 then finish one token per
+// thread (thread = tensor-memory lane): soft-max, bias-steered top-k with the lowest index on ties, outputs, block
+// histograms - the same rules as moe_route_kernel, which stays for everything this kernel does not cover.  The fp32 router
+// rows are split into two 16-bit terms, hi = round16(w) in rows 0-7 of the B operand and lo = round16((w - hi) * S) in
+// rows 8-15 (S = 2048 for fp16, 256 for bf16), and the logit is D[e] + D[8 + e] / S: 22 (fp16) or 16 (bf16) mantissa
+// bits of the weight at the cost of columns the N = 16 instruction computes anyway.  (The CUDA-core kernel spent about
+// 400 warp instructions per token on FMAs and lane reductions; this one is bound by reading x16 once.)
+constexpr int RT_TOK = 128, RT_KC = 64, RT_ST = 4, RT_THREADS = 192;
+constexpr uint32_t RT_XTILE = RT_TOK * RT_KC * 2, RT_WPANEL = 16 * RT_KC * 2;
+__host__ __device__ inline size_t rt_smem_bytes(int d, int ne) {
+  return (size_t)RT_ST * RT_XTILE + (size_t)(d / RT_KC) * RT_WPANEL + 128 + (size_t)(RT_TOK / 8) * (ne + 1) * 4 + 1024;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RT_THREADS) moe_route_tc_kernel(const __grid_constant__ CUtensorMap tmX, const gb_moe_args a,
+                                                                  int* status) {
+  extern __shared__ __align__(1024) uint8_t rt_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(rt_raw) + 1023) & ~uintptr_t(1023));
+  const int ne = a.ne, K = a.top_k, d = a.d;
+  const int nkc = d / RT_KC;
+  uint8_t* sX = smem;
+  uint8_t* sW = sX + RT_ST * RT_XTILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sW + (size_t)nkc * RT_WPANEL);
+  uint64_t* full = bars;                   // RT_ST
+  uint64_t* empty = bars + RT_ST;          // RT_ST
+  uint64_t* d_full = bars + 2 * RT_ST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * RT_ST + 1);
+  int* s_hist = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 128);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bt = blk_tok(a.n_tok);                       // routing block (<= RT_TOK: checked by the launcher)
+  const int nsub = RT_TOK / bt;
+  const int t0 = blockIdx.x * RT_TOK;
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr float SPLIT = kBf16 ? 256.f : 2048.f;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RT_ST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(d_full, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 32); tmem_relinquish(); }
+  for (int i = threadIdx.x; i < nsub * (ne + 1); i += RT_THREADS) s_hist[i] = 0;
+  // the B operand: 16 rows (8 hi, 8 lo) x d columns, K-major, 128-byte swizzle, one 2 KB panel per 64 columns
+  for (int i = threadIdx.x; i < 8 * d; i += RT_THREADS) {
+    const int e = i / d, c = i - e * d;
+    const float w = e < ne ? a.router_w[(size_t)e * d + c] : 0.f;
+    const T hi = Cvt<T>::from_f(w);
+    const T lo = Cvt<T>::from_f((w - Cvt<T>::to_f(hi)) * SPLIT);
+    uint8_t* panel = sW + (size_t)(c >> 6) * RT_WPANEL;
+    const int cc = c & 63;
+    const uint32_t off_hi = (uint32_t)(e * 128 + ((((cc >> 3) ^ (e & 7)) << 4) | ((cc & 7) << 1)));
+    *reinterpret_cast<T*>(panel + off_hi) = hi;
+    *reinterpret_cast<T*>(panel + off_hi + 1024) = lo;        // row e + 8: the next 8-row group, same swizzle phase
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_D = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kc = 0; kc < nkc; ++kc) {
+        const int s = kc % RT_ST, ph = (kc / RT_ST) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1)) { atomicCAS(status, 0, ST_TIMEOUT_EMPTY); break; }
+        mbar_arrive_expect_tx(&full[s], RT_XTILE);
+        tma_load_2d(&tmX, &full[s], sX + s * RT_XTILE, kc * RT_KC, t0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(kBf16 ? 1 : 0, 0, 0, RT_TOK, 16);
+      bool ok = true;
+      for (int kc = 0; kc < nkc && ok; ++kc) {
+        const int s = kc % RT_ST, ph = (kc / RT_ST) & 1;
+        if (!mbar_wait(&full[s], ph)) { atomicCAS(status, 0, ST_TIMEOUT_FULL); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < RT_KC / 16; ++kk)
+          umma_f16(tmem_D, make_smem_desc_sw128(smem_u32(sX + s * RT_XTILE) + kk * 32, 16, 1024),
+                   make_smem_desc_sw128(smem_u32(sW + (size_t)kc * RT_WPANEL) + kk * 32, 16, 1024), idesc,
+                   (kc > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(d_full);
+    }
+    __syncwarp();
+  } else {
+    // one token per thread; a warp reads the tensor-memory lane quarter (warp % 4)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int t = t0 + r;
+    const bool got = mbar_wait(d_full, 0);
+    if (!got && lane == 0) atomicCAS(status, 0, ST_TIMEOUT_TMEM_FULL);
+    if (got) {
+      tc_fence_after();
+      uint32_t v[16];
+      tmem_ld_32x16(tmem_D + ((uint32_t)(q * 32) << 16), v);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (t < a.n_tok) {
+        const unsigned long long jseed = a.dyn_seed ? a.dyn_seed[0] : a.jitter_seed;
+        const int tj = a.seg_tokens > 0 ? t % a.seg_tokens : t;
+        float l[8], pr[8], sc[8];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          l[e] = __uint_as_float(v[e]) + __uint_as_float(v[8 + e]) * (1.f / SPLIT);
+          if (a.use_jitter) l[e] *= 1.0f + a.jitter * 2.0f * jitter_u(tj, e, jseed);
+          if (e >= ne) l[e] = -INFINITY;
+          mx = fmaxf(mx, l[e]);
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { pr[e] = e < ne ? __expf(l[e] - mx) : 0.f; sum += pr[e]; }
+        const float inv = 1.f / sum;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          pr[e] *= inv;
+          if (e < ne) a.probs[(size_t)t * ne + e] = pr[e];
+          sc[e] = e < ne ? pr[e] + (a.bias ? a.bias[e] : 0.f) : -INFINITY;
+        }
+        int esel[MAX_K];
+        float psel[MAX_K];
+        float psum = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_K; ++k)
+          if (k < K) {
+            float bv = sc[0];
+            int bi = 0;
+#pragma unroll
+            for (int e = 1; e < 8; ++e)
+              if (sc[e] > bv) { bv = sc[e]; bi = e; }       // strict: equal scores keep the lower index
+            float pw = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (e == bi) { pw = pr[e]; sc[e] = -INFINITY; }
+            esel[k] = bi;
+            psel[k] = pw;
+            psum += pw;
+          }
+        const float invs = psum > 1e-8f ? 1.f / psum : 0.f;
+        int* hist = s_hist + (r / bt) * (ne + 1);
+#pragma unroll
+        for (int k = 0; k < MAX_K; ++k)
+          if (k < K) {
+            a.idx[(size_t)t * K + k] = esel[k];
+            a.w[(size_t)t * K + k] = psel[k] * invs;
+            atomicAdd(&hist[esel[k]], 1);
+          }
+        if (a.shared) atomicAdd(&hist[ne], 1);
+      }
+    }
+  }
+  __syncthreads();
+  const int nb = (a.n_tok + bt - 1) / bt;
+  for (int i = threadIdx.x; i < nsub * (ne + 1); i += RT_THREADS) {
+    const int b = blockIdx.x * nsub + i / (ne + 1);
+    if (b < nb) a.block_hist[(size_t)b * (ne + 1) + i % (ne + 1)] = s_hist[i];
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_D, 32); }
 }
 
 // Single block.  Totals, padded offsets, per-block bases, tile map, balance statistics.
@@ -829,6 +997,32 @@ extern "C" int gb_moe_route(const gb_moe_args* a, cudaStream_t st) {
   int rc = moe_check(a);
   if (rc) return rc;
   const int nb = gb_moe_num_blocks(a->n_tok);
+  // tensor-core router: up to 8 experts, whole 64-column panels, routing blocks that divide the 128-token tile
+  const bool tc = a->status && a->ne <= 8 && a->d % RT_KC == 0 && a->d <= 4096 && a->n_tok >= 256 && blk_tok(a->n_tok) <= RT_TOK &&
+                  ((uintptr_t)a->x16 & 15) == 0;
+  if (tc) {
+    CUtensorMap tm;
+    if (gb_make_tmap_2d_16b(&tm, a->x16, (uint64_t)a->n_tok, (uint64_t)a->d, (uint64_t)a->d, RT_TOK, RT_KC, a->is_bf16)) return -20;
+    const size_t smem = rt_smem_bytes(a->d, a->ne);
+    const unsigned grid = (unsigned)((a->n_tok + RT_TOK - 1) / RT_TOK);
+    if (a->is_bf16) {
+      auto kern = moe_route_tc_kernel<__nv_bfloat16>;
+      static size_t set_b = 0;                   // the attribute only ever grows
+      if (smem > set_b) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -10;
+        set_b = smem;
+      }
+      kern<<<grid, RT_THREADS, smem, st>>>(tm, *a, a->status);
+    } else {
+      auto kern = moe_route_tc_kernel<__half>;
+      static size_t set_h = 0;
+      if (smem > set_h) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -10;
+        set_h = smem;
+      }
+      kern<<<grid, RT_THREADS, smem, st>>>(tm, *a, a->status);
+    }
+  }
   const bool vec = a->d % 256 == 0 && a->d <= 1024 && (((uintptr_t)a->x16 | (uintptr_t)a->router_w) & 15) == 0;
 #define GB_ROUTE(T)                                                           \
   switch (vec ? a->d / 256 : 0) {                                             \
@@ -838,7 +1032,9 @@ extern "C" int gb_moe_route(const gb_moe_args* a, cudaStream_t st) {
     case 4: moe_route_kernel<T, 4><<<nb, 256, 0, st>>>(*a); break;            \
     default: moe_route_kernel<T, 0><<<nb, 256, 0, st>>>(*a); break;           \
   }
-  if (a->is_bf16) { GB_ROUTE(__nv_bfloat16) } else { GB_ROUTE(__half) }
+  if (!tc) {
+    if (a->is_bf16) { GB_ROUTE(__nv_bfloat16) } else { GB_ROUTE(__half) }
+  }
 #undef GB_ROUTE
   if (a->aux_m) {
     const int seg_tok = a->seg_tokens > 0 ? a->seg_tokens : a->n_tok;

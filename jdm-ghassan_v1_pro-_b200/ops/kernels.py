@@ -47,7 +47,8 @@ class MoeArgs(ctypes.Structure):
                 ("dout", c_void_p), ("dy_perm", c_void_p), ("gdot", c_void_p), ("dx_perm", c_void_p),
                 ("aux_coef", c_float), ("f_frac", c_void_p), ("d_router_w", c_void_p), ("dx16", c_void_p),
                 ("aux_m", c_void_p), ("part", c_void_p), ("aux_acc", c_void_p), ("dyn_seed", c_void_p),
-                ("dyn_aux_coef", c_void_p), ("part2", c_void_p), ("seg_tokens", c_int), ("seg_weight", c_void_p)]
+                ("dyn_aux_coef", c_void_p), ("part2", c_void_p), ("seg_tokens", c_int), ("seg_weight", c_void_p),
+                ("status", c_void_p)]
 
 ROUTER_WGRAD_CHUNKS = 256
 
@@ -262,6 +263,7 @@ class MoeWorkspace:
         a.slot_pos, a.cap = _p(self.slot_pos), self.cap
         a.aux_m, a.f_frac = _p(self.aux_m), _p(self.f_frac)
         a.seg_tokens = self.seg_tokens
+        a.status = _p(_lib.status_word(self.probs.device))
         return a
 
 
