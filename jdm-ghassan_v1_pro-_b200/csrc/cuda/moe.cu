@@ -216,6 +216,14 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_tc_kernel(const __grid_c
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 32); tmem_relinquish(); }
   for (int i = threadIdx.x; i < nsub * (ne + 1); i += RT_THREADS) s_hist[i] = 0;
+  __syncthreads();
+  // the first activation tiles are asked for before the weights are prepared, so that they arrive meanwhile
+  const int pre = nkc < RT_ST ? nkc : RT_ST;
+  if (threadIdx.x == 0)
+    for (int kc = 0; kc < pre; ++kc) {
+      mbar_arrive_expect_tx(&full[kc], RT_XTILE);
+      tma_load_2d(&tmX, &full[kc], sX + kc * RT_XTILE, kc * RT_KC, t0);
+    }
   // the B operand: 16 rows (8 hi, 8 lo) x d columns, K-major, 128-byte swizzle, one 2 KB panel per 64 columns
   for (int i = threadIdx.x; i < 8 * d; i += RT_THREADS) {
     const int e = i / d, c = i - e * d;
@@ -236,7 +244,7 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_tc_kernel(const __grid_c
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kc = 0; kc < nkc; ++kc) {
+      for (int kc = pre; kc < nkc; ++kc) {
         const int s = kc % RT_ST, ph = (kc / RT_ST) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1)) { atomicCAS(status, 0, ST_TIMEOUT_EMPTY); break; }
         mbar_arrive_expect_tx(&full[s], RT_XTILE);
