@@ -846,7 +846,7 @@ __global__ void __launch_bounds__(RD_LANES * RD_GROUPS) moe_router_dx_kernel(con
 // d_router_w[e, c] += sum_t dlogit[t, e] * x16[t, c], in a fixed order (deterministic).
 // grid (column groups / 96, token chunks, expert groups of 8), 384 threads = 4 token groups x 96 lanes.  A lane owns 8
 // columns (one 16-byte load of the activations per token) and 8 experts, 64 sums in registers; token group g takes
-// tokens ta + g, ta + g + 4, ... of the chunk, two per trip, and the four groups are added in group order through
+// tokens ta + g, ta + g + 4, ... of the chunk, four per trip, and the four groups are added in group order through
 // shared memory.  With more than one token chunk `dw` is a partial buffer [chunks, ne, d] that
 // moe_router_wgrad_fold_kernel adds up in chunk order.  (One column per thread with eight scalar dlogit loads per token
 // ran at 0.14 of the copy bandwidth.)
@@ -891,14 +891,20 @@ __global__ void __launch_bounds__(RW_LANES * RW_GROUPS) moe_router_wgrad_kernel(
   };
   if (live) {
     int t = ta + g;
-    for (; t + RW_GROUPS < tb; t += 2 * RW_GROUPS) {      // two tokens' loads in flight; the additions keep token order
+    for (; t + 3 * RW_GROUPS < tb; t += 4 * RW_GROUPS) {  // four tokens' loads in flight; the additions keep token order
       const uint4 x0 = *reinterpret_cast<const uint4*>(x16 + (size_t)t * d + c0);
       const uint4 x1 = *reinterpret_cast<const uint4*>(x16 + (size_t)(t + RW_GROUPS) * d + c0);
-      float d0[8], d1[8];
+      const uint4 x2 = *reinterpret_cast<const uint4*>(x16 + (size_t)(t + 2 * RW_GROUPS) * d + c0);
+      const uint4 x3 = *reinterpret_cast<const uint4*>(x16 + (size_t)(t + 3 * RW_GROUPS) * d + c0);
+      float d0[8], d1[8], d2[8], d3[8];
       load_dl(t, d0);
       load_dl(t + RW_GROUPS, d1);
+      load_dl(t + 2 * RW_GROUPS, d2);
+      load_dl(t + 3 * RW_GROUPS, d3);
       fma_tok(x0, d0);
       fma_tok(x1, d1);
+      fma_tok(x2, d2);
+      fma_tok(x3, d3);
     }
     for (; t < tb; t += RW_GROUPS) {
       const uint4 x0 = *reinterpret_cast<const uint4*>(x16 + (size_t)t * d + c0);
