@@ -14,6 +14,7 @@ import itertools
 import sys
 from collections import Counter, defaultdict
 from typing import List, Optional
+from .common import add_common_flags, apply_common_flags
 
 from .. import _gb200_host as H
 from ..data import pipeline as P
@@ -29,7 +30,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--sample", type=int, default=0)
     for f in ("dedup", "pii", "quality"):
         ap.add_argument("--" + f, action="store_true")
+    add_common_flags(ap)
     a = ap.parse_args(argv)
+    apply_common_flags(a)
     if not a.input:
         log_error("--input is required")
         return 2

@@ -28,6 +28,8 @@ import os
 import sys
 from typing import Iterator, List, Optional
 
+from .common import add_common_flags, apply_common_flags
+
 from .. import _gb200_host as H
 from ..data import pipeline as P
 from ..data import retrieval as R
@@ -214,7 +216,10 @@ def cmd_jsons(a) -> int:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
-    a = _parser().parse_args(argv)
+    ap = _parser()
+    add_common_flags(ap)
+    a = ap.parse_args(argv)
+    apply_common_flags(a)
     a.n_given, a.seed_given = a.n is not None, a.seed is not None
     a.n = a.n if a.n_given else 50000
     a.seed = a.seed if a.seed_given else 1

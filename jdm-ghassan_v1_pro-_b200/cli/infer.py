@@ -27,6 +27,8 @@ from typing import List, Optional
 
 import numpy as np
 
+from .common import add_common_flags, apply_common_flags
+
 
 def _parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="ghassan-ai")
@@ -42,6 +44,7 @@ def _parser() -> argparse.ArgumentParser:
         ap.add_argument("--" + name, type=typ)
     for name in ("greedy", "no-adaptive", "no-stream", "retrieve-direct", "stats", "verbose", "measure"):
         ap.add_argument("--" + name, action="store_true")
+    add_common_flags(ap)
     return ap
 
 
@@ -113,6 +116,7 @@ def _load(a, batch=1, ctx=0):
 
 def main(argv: Optional[List[str]] = None) -> int:
     a = _parser().parse_args(argv)
+    apply_common_flags(a)
     cmd = a.command
     if cmd == "devices":
         import torch

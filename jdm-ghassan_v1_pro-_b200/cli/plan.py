@@ -25,6 +25,7 @@ from ..models.config import ModelConfig
 from ..training.config import TrainerConfig
 from ..utils.config import Config, ConfigError
 from ..utils.log import human_count, human_duration, log_error, log_info, log_warn
+from .common import add_common_flags, apply_common_flags
 
 HOUR_MARKS = (2, 4, 6, 8, 10)
 
@@ -141,7 +142,10 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
-    args = build_parser().parse_args(argv)
+    ap = build_parser()
+    add_common_flags(ap)
+    args = ap.parse_args(argv)
+    apply_common_flags(args)
     try:
         mcfg, tcfg = _load(args)
         mcfg.validate()

@@ -22,6 +22,7 @@ from ..training.config import TrainerConfig
 from ..training.memory_plan import memory_plan
 from ..utils.config import Config, ConfigError
 from ..utils.log import human_bytes, human_count, log_error, log_info, log_warn
+from .common import add_common_flags, apply_common_flags
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -38,6 +39,7 @@ def build_parser() -> argparse.ArgumentParser:
     for name in ("strict-config", "strict-args", "dry-run", "allow-recipe-drift", "verbose"):
         ap.add_argument("--" + name, action="store_true")
     ap.add_argument("--set", nargs=2, action="append", metavar=("KEY", "VALUE"))
+    add_common_flags(ap)
     return ap
 
 
@@ -56,6 +58,7 @@ def _num(args, name, strict, cast=int):
 
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
+    apply_common_flags(args)
     try:
         return _run(args)
     except (ConfigError, ValueError) as e:

@@ -14,6 +14,7 @@ import argparse
 import os
 import sys
 from typing import List, Optional
+from .common import add_common_flags, apply_common_flags
 
 from .. import _gb200_host as H
 from ..data import synth as S
@@ -70,7 +71,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--seed", type=int, default=1)
     for f in ("study", "keep-diacritics", "fold-letters", "keep-case"):
         ap.add_argument("--" + f, action="store_true")
+    add_common_flags(ap)
     a = ap.parse_args(argv)
+    apply_common_flags(a)
     if not (0 < a.vocab <= 10_000_000):
         log_error("--vocab is out of range")
         return 2

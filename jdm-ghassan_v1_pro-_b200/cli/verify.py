@@ -28,6 +28,8 @@ import sys
 import tempfile
 from typing import Callable, List, Optional, Tuple
 
+from .common import add_common_flags, apply_common_flags
+
 TINY = ["--vocab", "0", "--layers", "2", "--hidden", "128", "--heads", "4", "--kv-heads", "2"]
 
 RECIPE = """
@@ -384,7 +386,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--device", default="auto")
     ap.add_argument("--workdir", default="")
     ap.add_argument("--configs", default=os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "configs"))
+    add_common_flags(ap)
     a = ap.parse_args(argv)
+    apply_common_flags(a)
     dev = _device(a.device)
     ctx = tempfile.TemporaryDirectory(prefix="gb200_verify_") if not a.workdir else contextlib.nullcontext(a.workdir)
     with ctx as work:
