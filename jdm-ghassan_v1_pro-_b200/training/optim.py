@@ -73,6 +73,47 @@ def _lion_update(w, g, m, lr, b1, b2, wd, scale):
     m.mul_(b2).add_(gi, alpha=1.0 - b2)
 
 
+def _adamw_update_many(ws, gs, ms, vs, decay, lr, b1, b2, eps, wd, bc1, bc2, scale):
+    """``_adamw_update`` over lists of tensors: the same operations in the same order, one multi-tensor call per operation
+    instead of one call per tensor and operation (a step of a small model is mostly call overhead on a CPU)."""
+    if not ws:
+        return
+    gi = torch._foreach_mul(gs, scale)
+    torch._foreach_mul_(ms, b1)
+    torch._foreach_add_(ms, gi, alpha=1.0 - b1)
+    torch._foreach_mul_(vs, b2)
+    torch._foreach_addcmul_(vs, gi, gi, value=1.0 - b2)
+    den = torch._foreach_div(vs, bc2)
+    torch._foreach_sqrt_(den)
+    torch._foreach_add_(den, eps)
+    upd = list(torch._foreach_div(torch._foreach_div(ms, bc1), den))
+    if wd != 0.0:
+        idx = [i for i, d in enumerate(decay) if d]
+        if idx:
+            dec = torch._foreach_add([upd[i] for i in idx], torch._foreach_mul([ws[i] for i in idx], wd))
+            for i, t in zip(idx, dec):
+                upd[i] = t
+    torch._foreach_sub_(ws, upd, alpha=lr)
+
+
+def _lion_update_many(ws, gs, ms, decay, lr, b1, b2, wd, scale):
+    """``_lion_update`` over lists of tensors, operation by operation."""
+    if not ws:
+        return
+    gi = torch._foreach_mul(gs, scale)
+    c = torch._foreach_add(torch._foreach_mul(ms, b1), torch._foreach_mul(gi, 1.0 - b1))
+    upd = list(torch._foreach_sign(c))
+    if wd != 0.0:
+        idx = [i for i, d in enumerate(decay) if d]
+        if idx:
+            dec = torch._foreach_add([upd[i] for i in idx], torch._foreach_mul([ws[i] for i in idx], wd))
+            for i, t in zip(idx, dec):
+                upd[i] = t
+    torch._foreach_sub_(ws, upd, alpha=lr)
+    torch._foreach_mul_(ms, b2)
+    torch._foreach_add_(ms, gi, alpha=1.0 - b2)
+
+
 class Optimizer:
     kind = "none"
 
@@ -111,11 +152,10 @@ class AdamW(Optimizer):
         if eff is None:
             return gnorm
         bc1, bc2 = self._bias_corrections(self.beta1, self.beta2)
-        for i, p in enumerate(self.params):
-            if p.frozen or p.grad is None:
-                continue
-            wd = self.weight_decay if p.decay else 0.0
-            _adamw_update(p.w, p.grad, self.m[i], self.v[i], lr, self.beta1, self.beta2, self.eps, wd, bc1, bc2, eff)
+        live = [i for i, p in enumerate(self.params) if not p.frozen and p.grad is not None]
+        _adamw_update_many([self.params[i].w for i in live], [self.params[i].grad for i in live], [self.m[i] for i in live],
+                           [self.v[i] for i in live], [self.params[i].decay for i in live], lr, self.beta1, self.beta2,
+                           self.eps, self.weight_decay, bc1, bc2, eff)
         return gnorm
 
     def hyper(self):
@@ -138,11 +178,9 @@ class Lion(Optimizer):
         gnorm, eff = self._begin(grad_scale, self.grad_clip)
         if eff is None:
             return gnorm
-        for i, p in enumerate(self.params):
-            if p.frozen or p.grad is None:
-                continue
-            wd = self.weight_decay if p.decay else 0.0
-            _lion_update(p.w, p.grad, self.m[i], lr, self.beta1, self.beta2, wd, eff)
+        live = [i for i, p in enumerate(self.params) if not p.frozen and p.grad is not None]
+        _lion_update_many([self.params[i].w for i in live], [self.params[i].grad for i in live], [self.m[i] for i in live],
+                          [self.params[i].decay for i in live], lr, self.beta1, self.beta2, self.weight_decay, eff)
         return gnorm
 
     def hyper(self):
