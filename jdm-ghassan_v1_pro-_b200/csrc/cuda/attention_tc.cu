@@ -1330,44 +1330,52 @@ __global__ void __launch_bounds__(AT_DQ64_THREADS, 2) attn_tc_bwd_dkv64_kernel(c
   if (warp == W_MMA) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
 }
 
-// lo[i] = first position of the run of equal segment ids that contains i (per sequence); seg < 0 -> 0
+// lo[i] = first position of the run of equal segment ids that contains i (per sequence).  Rows with a negative id see
+// every earlier key (lo = 0) as long as no non-negative id has come before them in the sequence; after one they count
+// as a run of their own.  That keeps lo non-decreasing along a sequence, which the tensor-core kernels rely on (the
+// first row of a tile has its smallest lo, the last one its largest).
 // One block of 1024 threads per sequence: running maximum of the run-start positions (chunked inclusive scan).
 __global__ void __launch_bounds__(1024) attn_seg_lo_kernel(const int* __restrict__ seg, int* __restrict__ lo, int B, int T) {
-  __shared__ int s_warp[32];
-  __shared__ int s_carry;
+  __shared__ int s_warp[32], s_flag[32];
+  __shared__ int s_carry, s_carry_f;
   const long long base = (long long)blockIdx.x * T;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) s_carry = 0;
+  if (threadIdx.x == 0) { s_carry = 0; s_carry_f = 0; }
   __syncthreads();
   for (int c0 = 0; c0 < T; c0 += 1024) {
     const int i = c0 + threadIdx.x;
-    int s = 0, v = 0;
+    int s = 0, v = 0, f = 0;                 // f: a non-negative id at or before i
     if (i < T) {
       s = seg[base + i];
       if (i == 0 || seg[base + i - 1] != s) v = i;
+      f = s >= 0 ? 1 : 0;
     }
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int n = __shfl_up_sync(0xffffffffu, v, o);
-      if (lane >= o) v = max(v, n);
+      const int nf = __shfl_up_sync(0xffffffffu, f, o);
+      if (lane >= o) { v = max(v, n); f = max(f, nf); }
     }
-    if (lane == 31) s_warp[warp] = v;
+    if (lane == 31) { s_warp[warp] = v; s_flag[warp] = f; }
     __syncthreads();
     if (warp == 0) {
-      int w = s_warp[lane];
+      int w = s_warp[lane], wf = s_flag[lane];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int n = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w = max(w, n);
+        const int nf = __shfl_up_sync(0xffffffffu, wf, o);
+        if (lane >= o) { w = max(w, n); wf = max(wf, nf); }
       }
       s_warp[lane] = w;
+      s_flag[lane] = wf;
     }
     __syncthreads();
-    if (warp > 0) v = max(v, s_warp[warp - 1]);
+    if (warp > 0) { v = max(v, s_warp[warp - 1]); f = max(f, s_flag[warp - 1]); }
     v = max(v, s_carry);
-    if (i < T) lo[base + i] = s < 0 ? 0 : v;
+    f = max(f, s_carry_f);
+    if (i < T) lo[base + i] = (s < 0 && !f) ? 0 : v;
     __syncthreads();
-    if (threadIdx.x == 1023) s_carry = v;
+    if (threadIdx.x == 1023) { s_carry = v; s_carry_f = f; }
     __syncthreads();
   }
 }

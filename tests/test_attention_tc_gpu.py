@@ -125,3 +125,27 @@ def test_tc_attention_forward_rescales_when_the_row_maximum_jumps(dt, use_seg):
         want = torch.logsumexp(sc.masked_fill(~vis, float("-inf")), dim=-1).permute(0, 2, 1).reshape(n, H)
         ok, err, rule = near(lse, want, chain=False)
         assert ok, ("lse", variant, err, rule)
+
+
+def test_tc_attention_leading_negative_segment_ids():
+    """Rows with a negative segment id at the head of a sequence see every earlier key (the oracle's rule); the documents
+    after them see only themselves."""
+    from ghassan_b200.models import reference as R
+    from ghassan_b200.ops import _lib, kernels as K
+    B, T, H, KV, hd = 2, 300, 4, 2, 64
+    n = B * T
+    dt = torch.float16
+    scale = hd ** -0.5
+    q, k, v = rnd(n, H * hd, seed=21, dtype=dt), rnd(n, KV * hd, seed=22, dtype=dt), rnd(n, KV * hd, seed=23, dtype=dt)
+    one = torch.cat([torch.full((40,), -1, device="cuda"), torch.arange(T - 40, device="cuda") // 97])
+    seg = one.repeat(B).to(torch.int32)
+    lo = torch.empty(n, dtype=torch.int32, device="cuda")
+    o = torch.empty(n, H * hd, dtype=dt, device="cuda")
+    lse = torch.empty(n, H, device="cuda")
+    K.attn_tc_fwd(q, k, v, o, lse, seg, lo, B, T, H, KV, hd, 0, scale)
+    _lib.check_status(what="attn_tc_fwd")
+    assert int(lo.view(B, T)[:, :40].max()) == 0 and int(lo.view(B, T)[0, 40]) == 40
+    assert bool((lo.view(B, T)[:, 1:] >= lo.view(B, T)[:, :-1]).all())       # non-decreasing along a sequence
+    ref = R.attention(q.float().view(n, H, hd), k.float().view(n, KV, hd), v.float().view(n, KV, hd), B, T, scale, 0, seg)
+    ok, err, rule = near(o, ref)
+    assert ok, ("o", err, rule)
