@@ -76,7 +76,8 @@ typedef struct gb_attn_args {
   const void* v; long long ld_v;
   void* o; long long ld_o;
   float* lse;                        // [B*T, H]
-  const int* seg;                    // [B*T] segment ids or NULL
+  const int* seg;                    // [B*T] segment ids or NULL: contiguous runs per sequence (packed documents); rows with a
+                                     // negative id see every earlier key while no non-negative id has come before them
   int B, T, H, KV, hd, window, is_bf16;
   float scale;
   const void* d_o; long long ld_do;  // backward only
