@@ -42,7 +42,7 @@ def _parser() -> argparse.ArgumentParser:
                       ("ctx", int), ("batch", int), ("max-prompts", int), ("seq-len", int), ("batches", int),
                       ("batch-size", int), ("rope-scale", float), ("yarn-mscale", float)):
         ap.add_argument("--" + name, type=typ)
-    for name in ("greedy", "no-adaptive", "no-stream", "retrieve-direct", "stats", "verbose", "measure"):
+    for name in ("greedy", "no-adaptive", "no-stream", "retrieve-direct", "stats", "verbose", "measure", "pack", "raw"):
         ap.add_argument("--" + name, action="store_true")
     add_common_flags(ap)
     return ap
@@ -206,8 +206,33 @@ def main(argv: Optional[List[str]] = None) -> int:
     if cmd == "generate":
         if gen.tok is None:
             raise SystemExit("model has no tokenizer; pass --tokenizer")
+        if not a.prompt:
+            raise SystemExit("--prompt is required")
         cb = None if a.no_stream else (lambda b, s: print(s, end="", flush=True))
-        res = gen.generate(a.prompt or "", max_new_tokens=a.max_tokens or 256, sampling=sp, on_text=cb)
+        max_new = a.max_tokens or 256
+        prompt = a.prompt
+        if not a.raw:
+            # one chat turn, as the reference's `generate` does unless --raw (tools/inference_cli.cpp:cmd_generate,
+            # inference/generator.cpp:495-512 there): system prompt of the persona (default "en") or the given one plus
+            # the script directive, the prompt as the user message, the assistant header; when that does not fit the
+            # context next to the new tokens, tokens after the first are dropped from the front
+            from ..data import tokenizer as TK
+            from ..utils.log import log_warn
+            persona = a.persona or "en"
+            system = a.system or ""
+            if not system:
+                system = TK.system_for_persona(persona, TK.detect_script(prompt))
+            elif persona not in ("en", "english"):
+                system += "\n" + TK.script_directive(TK.detect_script(prompt))
+            ids, _ = TK.encode_chat(gen.tok, [TK.Message("system", system), TK.Message("user", prompt)], add_generation_prompt=True)
+            ids = [int(i) for i in ids]
+            budget = gen.engine.cap - max_new - 4
+            if budget > 0 and len(ids) > budget:
+                drop = len(ids) - budget
+                ids = ids[:1] + ids[1 + drop:]
+                log_warn("chat: history truncated by %d tokens" % drop)
+            prompt = ids
+        res = gen.generate([prompt] if not isinstance(prompt, str) else prompt, max_new_tokens=max_new, sampling=sp, on_text=cb)
         print("" if cb else res.text[0])
         if a.stats:
             print("  [prefill %.0f ms | decode %.1f tok/s | %s]" % (res.prefill_seconds * 1e3, res.decode_tokens_per_second, res.stopped[0]))
@@ -222,6 +247,20 @@ def main(argv: Optional[List[str]] = None) -> int:
     if cmd == "logits":
         ids = gen.encode_prompt(a.prompt or "", add_bos=True)
         import torch
+        if hasattr(gen.engine, "all_logits"):
+            # the reference's report (tools/inference_cli.cpp:748-812 there): every position's logits to --out as
+            # [tokens, vocab] fp32, and per position the arg-max with the five largest
+            if len(ids) > 512:
+                raise SystemExit("logits prompt too long (more than 512 tokens)")
+            print("  tokens: %d  ids: %s" % (len(ids), " ".join(str(int(i)) for i in ids)))
+            lg = gen.engine.all_logits(ids)
+            if a.out:
+                lg.astype(np.float32).tofile(a.out)
+            for t in range(lg.shape[0]):
+                row = lg[t]
+                top = np.argsort(-row, kind="stable")[:5]
+                print("  pos %3d argmax=%6d (%.4f) top5:%s" % (t, top[0], row[top[0]], "".join(" %d:%.3f" % (i, row[i]) for i in top)))
+            return 0
         gen.engine.reset(1)
         gen.engine.prefill(torch.from_numpy(np.asarray(ids, dtype=np.int32)[None, :]).repeat(gen.engine.B, 1))
         lg = gen.engine.logits[0].float().cpu().numpy()
@@ -239,6 +278,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             raise SystemExit("perplexity options must be positive")
         if a.text:
             r = E.perplexity_text(gen, a.text)
+        elif a.shards and hasattr(gen.engine, "score_batch"):
+            # the reference's rule: batches of its data loader, supervised positions, segment masks, z-loss included
+            r = E.perplexity_batches(gen, a.shards, a.prefix or "val", bs, seq_len, batches, bool(a.pack), a.seed if a.seed is not None else 42)
         elif a.shards:
             r = E.perplexity_shards(gen, a.shards, a.prefix or "val", max_tokens=batches * bs * seq_len, window=seq_len)
         else:
@@ -248,6 +290,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         print("  mean_nll    : %.8f" % r["nll"])
         print("  perplexity  : %.6f" % r["perplexity"])
         print("  tokens      : %d" % r["tokens"])
+        if "batches" in r:
+            print("  batches     : %d" % r["batches"])
         return 0
     if cmd == "eval":
         from ..data.tokenizer import SYSTEM_ENGLISH

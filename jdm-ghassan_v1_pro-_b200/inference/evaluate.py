@@ -36,6 +36,31 @@ def perplexity_text(gen: Generator, text: str) -> dict:
     return {"tokens": n, "nll": nll / max(1, n), "perplexity": float(np.exp(nll / max(1, n)))}
 
 
+def perplexity_batches(gen: Generator, directory: str, prefix: str = "val", batch_size: int = 1, seq_len: int = 512,
+                       max_batches: int = 20, pack: bool = False, seed: int = 42) -> dict:
+    """The reference's held-out measure (evaluation/perplexity.cpp:27-60 there): ``max_batches`` batches of its data
+    loader over ``<directory>/<prefix>*.gbin`` (same sampler, same seed, so the same windows), every row scored
+    teacher-forced on the supervised positions with its segment mask, z-loss included.  Needs an engine that scores a
+    row in one pass (``score_batch``)."""
+    from ..data.loader import DataLoader
+    dl = DataLoader(batch_size, seq_len, pack, seed, pin=False)
+    if not dl.open_glob(directory, prefix):
+        raise ValueError("no held-out shards found for perplexity: " + directory)
+    total, count, batches = 0.0, 0, 0
+    while batches < max_batches:
+        b = dl.next()
+        if b is None:
+            break
+        ids, tg, sg = b.ids.numpy(), b.targets.numpy(), b.segments.numpy()
+        # one call per batch, as the reference does: the rows of a batch are scored as ONE sequence of B * T positions
+        nll, n = gen.engine.score_batch(ids, tg, sg)
+        total += nll
+        count += n
+        batches += 1
+    mean = total / max(1, count)
+    return {"tokens": count, "nll": mean, "perplexity": float(np.exp(min(20.0, mean))), "batches": batches}
+
+
 def perplexity_shards(gen: Generator, directory: str, prefix: str = "val_", max_tokens: int = 20000, window: int = 512) -> dict:
     """Token-level NLL over validation shards, document by document, in windows of ``window`` tokens."""
     total, count = 0.0, 0

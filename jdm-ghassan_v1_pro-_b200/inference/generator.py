@@ -78,14 +78,17 @@ class Generator:
         eng.set_stop_tokens(sorted(stop_ids))
         max_new = min(max_new_tokens, eng.tok_log.shape[1])
         t0 = time.perf_counter()
+        host_only = getattr(eng, "host_only", False)          # the CPU engine: host sampler, no device to wait for
         eng.prefill(torch.from_numpy(np.stack(ids)).to(torch.int32))
-        torch.cuda.synchronize()
+        if not host_only:
+            torch.cuda.synchronize()
         t1 = time.perf_counter()
-        if sp.device_ok():
+        if sp.device_ok() and not host_only:
             toks, reasons = self._run_device(sp, max_new, stop_ids, stop_strings, on_text, poll, use_graph)
         else:
             toks, reasons = self._run_host(sp, ids, max_new, stop_ids, stop_strings, on_text)
-        torch.cuda.synchronize()
+        if not host_only:
+            torch.cuda.synchronize()
         t2 = time.perf_counter()
         res = GenerationResult(tokens=toks, prompt_tokens=n, prefill_seconds=t1 - t0, decode_seconds=t2 - t1,
                                stopped=reasons)
@@ -183,6 +186,8 @@ class Generator:
         ids = [int(i) for i in ids]
         if len(ids) < 2:
             return 0.0, 0
+        if hasattr(eng, "score_window"):                      # the CPU engine scores a window in one teacher-forced pass
+            return eng.score_window(ids)
         eng.reset(1)
         total, count = 0.0, 0
         row = torch.zeros(eng.B, dtype=torch.int32)
@@ -204,6 +209,8 @@ class Generator:
                   seed: int = 1234) -> dict:
         """Device-timed decode throughput after a synthetic uniform-random prompt (no host reads while decoding)."""
         eng = self.engine
+        if getattr(eng, "host_only", False):
+            return self._benchmark_host(prompt_len, new_tokens, sampling, seed)
         if new_tokens < 10:
             raise ValueError("benchmark needs at least 10 new tokens (the first 9 warm the graph up and are not timed)")
         sp = sampling or SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, seed=seed)
@@ -233,3 +240,26 @@ class Generator:
         return {"batch": eng.B, "prompt_len": prompt_len, "new_tokens": new_tokens, "decode_ms_per_token": dec_ms / (new_tokens - 9),
                 "decode_tokens_per_s": n_timed / (dec_ms / 1e3), "stored_weight_bytes": eng.weight_bytes,
                 "prefill_ms": e0.elapsed_time(e1_pre), "distinct_tokens": int(len(set(toks.reshape(-1).tolist())))}
+
+    def _benchmark_host(self, prompt_len, new_tokens, sampling, seed) -> dict:
+        """The same report for an engine without a device (the CPU engine): wall clock around the host-sampled loop."""
+        eng = self.engine
+        sp = sampling or SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, seed=seed)
+        rng = H.Rng(seed)
+        V = eng.cfg.vocab_size
+        prompt = np.empty((eng.B, prompt_len), dtype=np.int32)
+        for b in range(eng.B):
+            rng.fill_uniform_ids(prompt[b], V - 16)
+        prompt += 16
+        eng.reset(seed)
+        eng.set_stop_tokens([])
+        t0 = time.perf_counter()
+        eng.prefill(torch.from_numpy(prompt))
+        t1 = time.perf_counter()
+        toks, _ = self._run_host(sp, [list(map(int, p)) for p in prompt], new_tokens, set(), (), None)
+        t2 = time.perf_counter()
+        n = sum(len(t) for t in toks)
+        return {"batch": eng.B, "prompt_len": prompt_len, "new_tokens": new_tokens,
+                "decode_ms_per_token": (t2 - t1) * 1e3 / max(1, new_tokens), "decode_tokens_per_s": n / max(1e-9, t2 - t1),
+                "stored_weight_bytes": eng.weight_bytes, "prefill_ms": (t1 - t0) * 1e3,
+                "distinct_tokens": int(len({t for row in toks for t in row})), "device": "cpu"}

@@ -49,7 +49,12 @@ def quant_name(m: LoadedModel) -> str:
 
 
 def build_engine(m: LoadedModel, batch: int = 1, max_len: int = 2048, fmt: str = "auto", prefill_chunk: int = 1024):
-    """Engine whose decode weights keep the file's storage format where the kernels read it directly."""
+    """Engine whose decode weights keep the file's storage format where the kernels read it directly; on a host without
+    a CUDA device the fp32 CPU engine (`cpu_engine.CpuEngine`) over the expanded weights."""
+    import torch
+    if not torch.cuda.is_available():
+        from .cpu_engine import CpuEngine
+        return CpuEngine(m.cfg, m.named, batch=batch, max_len=min(max_len, max(64, m.cfg.max_seq_len)), moe_bias=m.moe_bias or None)
     from .engine import InferenceEngine
     raw = m.raw if (m.raw is not None and hasattr(m.raw, "tensor_raw")) else None
     if fmt == "auto" and raw is None:

@@ -1,0 +1,128 @@
+"""The inference command line on a host without a GPU (`inference/cpu_engine.py`), and, where a CPU build of the
+reference sits under baseline/_ref/bin, the same commands of both on the same GGUF file: held-out perplexity
+(evaluation/perplexity.cpp there), the per-position logits dump, and generation (one chat turn by default, --raw,
+greedy and seeded sampling) must agree."""
+import io
+import os
+import re
+import subprocess
+from contextlib import redirect_stdout
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref", "bin", "ghassan-ai")
+needs_ref = pytest.mark.skipif(not os.path.exists(REF), reason="no build of the reference command line here")
+pytestmark = pytest.mark.skipif(torch.cuda.is_available(), reason="with a GPU the command line uses the CUDA engine")
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    """A tiny trained model (context 1024) as GGUF, its tokenizer and its shards."""
+    from ghassan_b200.cli import data_pipeline as DP, infer as I, train as T, train_tokenizer as TT
+    w = str(tmp_path_factory.mktemp("cpuinf"))
+    sink = io.StringIO()
+    with redirect_stdout(sink):
+        assert DP.main(["synth", "--out", w + "/synth.jsonl", "--n", "300", "--seed", "11", "--silent"]) == 0
+        assert TT.main(["--input", w + "/synth.jsonl", "--output", w + "/tok.gtok", "--vocab", "600", "--silent"]) == 0
+        assert DP.main(["build", "--tokenizer", w + "/tok.gtok", "--out", w + "/shards", "--chat", w + "/synth.jsonl", "--val-ratio",
+                        "0.1", "--seq-len", "128", "--style-mode", "off", "--no-dedup", "--silent"]) == 0
+        assert T.main(["--config", os.path.join(ROOT, "configs", "cpu_smoke_test.yaml"), "--device", "cpu", "--max-steps", "30",
+                       "--data", w + "/shards", "--checkpoint-dir", w + "/ck", "--resume", "none", "--set", "model.max_seq_len",
+                       "1024", "--silent"]) == 0
+        assert I.main(["export", "--checkpoint", w + "/ck/last.ckpt", "--tokenizer", w + "/tok.gtok", "--out", w + "/m.gguf",
+                       "--profile", "fp16"]) == 0
+    from ghassan_b200.utils import log as LOG
+    LOG.set_log_level(LOG.INFO)
+    return w
+
+
+def ours(args):
+    from ghassan_b200.cli import infer as I
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert I.main(args) == 0
+    return buf.getvalue()
+
+
+def theirs(args):
+    p = subprocess.run([REF] + args, capture_output=True, cwd=ROOT, timeout=300)
+    assert p.returncode == 0, (p.stdout + p.stderr).decode("utf-8", "replace")[-600:]
+    return p.stdout.decode("utf-8", "replace")
+
+
+def test_engine_equals_the_oracle_model(model):
+    from ghassan_b200.inference import model_io as IO
+    from ghassan_b200.inference.cpu_engine import CpuEngine
+    m = IO.load_model(model + "/m.gguf")
+    eng = IO.build_engine(m, batch=1, max_len=256)
+    assert isinstance(eng, CpuEngine)
+    ids = [1, 40, 77, 120, 300, 9]
+    eng.reset(0)
+    eng.prefill(torch.tensor([ids], dtype=torch.int32))
+    want = eng.net.logits(torch.tensor(ids), 1, len(ids))[-1]
+    assert torch.equal(eng.logits[0], want)
+    eng.cur_tok[0] = 55
+    eng._forward_token()
+    want = eng.net.logits(torch.tensor(ids + [55]), 1, len(ids) + 1)[-1]
+    assert torch.equal(eng.logits[0], want)
+    # one teacher-forced pass scores what the token-by-token walk scores
+    nll, n = eng.score_window(ids)
+    lg = eng.net.logits(torch.tensor(ids), 1, len(ids)).double()
+    ref = -sum(float(torch.log_softmax(lg[j], -1)[ids[j + 1]]) for j in range(len(ids) - 1))
+    assert n == len(ids) - 1 and abs(nll - ref) < 1e-9
+
+
+def test_commands_run_without_a_gpu(model):
+    out = ours(["generate", "--model", model + "/m.gguf", "--prompt", "salam labas", "--max-tokens", "8", "--greedy", "--no-stream"])
+    again = ours(["generate", "--model", model + "/m.gguf", "--prompt", "salam labas", "--max-tokens", "8", "--greedy", "--no-stream"])
+    assert out == again                          # greedy decoding is repeatable (a model this small may well answer nothing)
+    raw = ours(["generate", "--model", model + "/m.gguf", "--prompt", "salam labas", "--max-tokens", "8", "--greedy", "--no-stream",
+                "--raw"])
+    assert raw.endswith("\n")
+    ppl = ours(["perplexity", "--model", model + "/m.gguf", "--shards", model + "/shards", "--prefix", "val_", "--batches", "5"])
+    assert re.search(r"batches +: 5", ppl) and float(re.search(r"perplexity +: ([0-9.]+)", ppl).group(1)) > 1.0
+    txt = ours(["perplexity", "--model", model + "/m.gguf", "--text", "salam labas 3lik, kif dayr"])
+    assert float(re.search(r"perplexity +: ([0-9.]+)", txt).group(1)) > 1.0
+    import json
+    rep = json.loads(ours(["bench", "--model", model + "/m.gguf", "--tokens", "12", "--prompt-tokens", "16"]).strip().splitlines()[-1])
+    assert rep["device"] == "cpu" and rep["new_tokens"] == 12 and rep["decode_tokens_per_s"] > 0
+    ev = ours(["eval", "--model", model + "/m.gguf", "--max-prompts", "2", "--max-tokens", "6"])
+    assert re.search(r"items 2 \| overall [0-9.]+", ev)
+
+
+@needs_ref
+def test_perplexity_equals_the_reference(model):
+    args = ["perplexity", "--model", model + "/m.gguf", "--shards", model + "/shards", "--prefix", "val_"]
+    a, b = theirs(args), ours(args)
+    for key in ("tokens", "batches"):
+        assert re.search(key + r" +: (\d+)", a).group(1) == re.search(key + r" +: (\d+)", b).group(1), key
+    na, nb = (float(re.search(r"mean_nll +: ([0-9.]+)", t).group(1)) for t in (a, b))
+    assert abs(na - nb) < 1e-4, (na, nb)
+
+
+@needs_ref
+def test_logits_dump_equals_the_reference(model, tmp_path):
+    fa, fb = str(tmp_path / "a.f32"), str(tmp_path / "b.f32")
+    a = theirs(["logits", "--model", model + "/m.gguf", "--prompt", "salam labas", "--out", fa])
+    b = ours(["logits", "--model", model + "/m.gguf", "--prompt", "salam labas", "--out", fb])
+    assert re.search(r"tokens: (\d+ +ids:.*)", a).group(1) == re.search(r"tokens: (\d+ +ids:.*)", b).group(1)
+    la, lb = np.fromfile(fa, dtype=np.float32), np.fromfile(fb, dtype=np.float32)
+    assert la.shape == lb.shape and la.size % 600 == 0
+    assert float(np.abs(la - lb).max()) < 2e-3
+    assert (la.reshape(-1, 600).argmax(1) == lb.reshape(-1, 600).argmax(1)).all()
+
+
+@needs_ref
+@pytest.mark.parametrize("extra", [["--greedy"], ["--seed", "7"], ["--greedy", "--raw"], ["--seed", "11", "--temp", "1.1", "--top-k", "20"]])
+def test_generation_equals_the_reference(model, extra):
+    args = ["generate", "--model", model + "/m.gguf", "--prompt", "salam labas", "--max-tokens", "16", "--no-stream"] + extra
+    def answer(out):          # the text is the last line of stdout; the reference also logs "[info ] ..." lines there
+        lines = [ln for ln in out.split("\n") if not ln.startswith("[")]
+        while lines and lines[-1] == "":
+            lines.pop()
+        return lines[-1] if lines else ""
+    a, b = answer(theirs(args)), answer(ours(args))
+    assert a == b, (a, b)
