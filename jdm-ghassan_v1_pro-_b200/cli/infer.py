@@ -300,7 +300,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         items = E.load_suite(a.suite) if (a.suite and os.path.isdir(a.suite)) else []
         if not items:
             items = E.builtin_suite_en() if english else E.builtin_suite()
-        rep = E.run_benchmark(gen, items, sp if not a.greedy else None, a.max_tokens or 128, a.categories or "", a.max_prompts or 0,
+        # the command line's sampling settings as they stand (with --greedy: arg-max under the default repetition penalty),
+        # as the reference's eval does
+        rep = E.run_benchmark(gen, items, sp, a.max_tokens or 128, a.categories or "", a.max_prompts or 0,
                               SYSTEM_ENGLISH if english else "")
         print(E.report_text(rep))
         if a.out:

@@ -113,11 +113,27 @@ const std::unordered_set<std::string>& lexicon(int which) {
   static const std::unordered_set<std::string> darija_ar = {
       "واش", "بزاف", "ديال", "دابا", "كيفاش", "علاش", "شنو", "فين", "غادي", "كنت", "كاين", "ماشي", "هادشي", "هاد", "ديالي",
       "ديالك", "بغيت", "كيف", "داير", "مزيان", "خويا", "صافي", "شحال", "عافاك", "بحال", "حيت", "راه", "باش", "كاع",
-      "والو", "شي", "هضر", "دير", "كندير", "كنهضر", "معاك", "ليا", "ليك", "لينا"};
+      "والو", "شي", "هضر", "دير", "كندير", "كنهضر", "معاك", "ليا", "ليك", "لينا",
+      // pronouns, demonstratives, connectives
+      "نتا", "نتي", "نتوما", "حنا", "هوما", "هادي", "هادو", "هاداك", "هاديك", "داك", "ديك", "داكشي", "ولا", "غير", "بلا", "بصح",
+      "زعما", "واقيلا", "فاش", "ملي", "منين", "عاد", "بعدا", "باقي", "واخا", "يالاه", "يلاه", "دبا", "دروك", "لبارح", "غدا", "شوية",
+      "بشوية", "دغيا", "بالزاف", "كولشي", "حتا", "معا", "معايا", "فيا", "فيك", "عندي", "عندك", "عندو", "عندنا",
+      // verbs and negated forms as they are written apart
+      "بغا", "بغينا", "بغيتي", "خاصني", "خاصك", "خاص", "مشيت", "مشا", "جيت", "جا", "شفت", "شوف", "عرفت", "كنعرف", "سير", "اجي",
+      "گلس", "نوض", "خدام", "خدامة", "عرفتش", "بغيتش", "كاينش", "قدرتش", "فهمتش", "والله", "عفاك", "سمح", "سمحلي",
+      // everyday nouns and adjectives
+      "زوين", "زوينة", "مزيانة", "خايب", "دار", "الدار", "خدمة", "فلوس", "دراهم", "اتاي", "طاجين", "صاحبي", "ختي", "ولد", "بنت", "الواليد",
+      "الواليدة", "بخير", "لاباس", "الحمدلله", "تبارك", "بسلامة"};
   static const std::unordered_set<std::string> darija_lat = {
       "wach", "bzaf", "bzzaf", "dyal", "daba", "kifach", "3lach", "chno", "fin", "ghadi", "kayn", "machi", "hadchi", "had",
       "dyali", "dyalk", "bghit", "kidayr", "mzyan", "khoya", "safi", "ch7al", "3afak", "b7al", "7it", "rah", "bach", "ga3",
-      "walo", "chi", "hder", "dir", "m3a", "m3ak", "lik", "salam", "labas", "wakha", "3la", "f", "l", "w", "ana", "nta", "nti"};
+      "walo", "chi", "hder", "dir", "m3a", "m3ak", "lik", "salam", "labas", "wakha", "3la", "ana", "nta", "nti",
+      "ntoma", "7na", "homa", "hadi", "hado", "hadak", "dak", "dik", "dakchi", "wla", "ghir", "bla", "bsa7", "z3ma", "fach", "mli", "mnin",
+      "3ad", "ba9i", "yallah", "db", "drok", "lbar7", "ghda", "chwiya", "bchwiya", "dghya", "kolchi", "7ta", "m3aya", "fia", "fik", "3ndi",
+      "3ndk", "3ndo", "3ndna", "bgha", "bghina", "bghiti", "khasni", "khask", "khass", "mchit", "mcha", "jit", "ja", "cheft", "chouf",
+      "3reft", "kan3ref", "sir", "aji", "gls", "nod", "khdam", "khdama", "ma3reftch", "mabghitch", "makaynch", "wallah", "sm7", "sm7li",
+      "zwin", "zwina", "mzyana", "khayb", "dar", "khdma", "flous", "drahm", "atay", "tajine", "sa7bi", "khti", "wld", "bnt", "lwalid",
+      "lwalida", "bikhir", "hamdollah", "hamdulillah", "tbarkllah", "bslama", "nhar", "lyoum", "souk", "bzef", "kifash", "3lash", "fin", "chkoun"};
   static const std::unordered_set<std::string> msa = {
       "الذي", "التي", "الذين", "هذا", "هذه", "ذلك", "لكن", "حيث", "ليس", "سوف", "لقد", "يجب", "يمكن", "كذلك", "ايضا",
       "بينما", "عندما", "لذلك", "حتي", "اذا", "ماذا", "لماذا", "كيف", "اين", "نحن", "انتم", "هؤلاء", "تلك", "الان", "جدا"};
@@ -170,49 +186,116 @@ const char* lang_name(LangTag t) {
   return names[static_cast<int>(t)];
 }
 
-LangScore classify_language(const std::string& text) {
+// Script first, word evidence second, with the reference classifier's decision procedure and thresholds
+// (dataset/langid.cpp:132-250 there), over this library's own word lists:
+//   * the text is letter-folded; a script "dominates" above 60 % of the letters;
+//   * words are runs of Arabic letters, Latin letters and the digits Arabizi uses as letters (2 3 5 6 7 8 9), ASCII
+//     lower-cased; a word counts as Arabic when its first letter is;
+//   * Arabic words: Darija list, Standard-Arabic list, and the verb shapes of Darija (a word of three or more letters that
+//     opens with ki- / ka- counts, and one that opens with ki- / ka- / ta- / gha- / ma- and ends in -sh counts);
+//     Latin words: Darija, French and English lists, and "Arabizi" = letters and such a digit in one word;
+//   * densities are taken over the words of the script; Arabic-dominant text is Darija from a density of 0.06 or two hits,
+//     otherwise Standard Arabic (confidently from a density of 0.10); Latin-dominant text goes through the
+//     Darija / French / English cascade below and is "other" without evidence; neither dominant = mixed.
+LangScore classify_language(const std::string& raw) {
   LangScore r;
+  if (raw.empty()) return r;
+  NormalizerConfig nc;
+  nc.fold_letters = true;
+  const std::string text = normalize(nc, raw);
   const uni::ScriptStats st = uni::script_stats(text);
   const double letters = static_cast<double>(st.arabic + st.latin);
   if (letters < 1) return r;
   r.arabic_ratio = st.arabic / letters;
   r.latin_ratio = st.latin / letters;
-  const std::vector<std::string> ws = words_of(canonical_text(text));
+
+  std::vector<std::string> ws;
+  {
+    std::string cur;
+    for (size_t i = 0; i < text.size();) {
+      u32 c = uni::decode(text, i);
+      if (uni::is_arabic_letter(c) || uni::is_latin_letter(c) || uni::is_arabizi_digit(c)) {
+        if (c >= 'A' && c <= 'Z') c += 32;
+        uni::encode(c, cur);
+      } else if (!cur.empty()) {
+        ws.push_back(std::move(cur));
+        cur.clear();
+      }
+    }
+    if (!cur.empty()) ws.push_back(std::move(cur));
+  }
   if (ws.empty()) return r;
-  double hit[5] = {0, 0, 0, 0, 0}, shaped = 0;
+
+  auto starts = [](const std::string& w, const char* pre) { return w.rfind(pre, 0) == 0; };
+  double dar_ar = 0, dar_lt = 0, msa = 0, fr = 0, en = 0, arabizi = 0, ar_words = 0, lt_words = 0;
   for (const auto& w : ws) {
-    for (int k = 0; k < 5; ++k) hit[k] += lexicon(k).count(w);
-    shaped += arabizi_shape(w);
+    size_t at = 0;
+    const bool is_ar = uni::is_arabic_letter(uni::decode(w, at));
+    if (is_ar) {
+      ++ar_words;
+      dar_ar += lexicon(0).count(w);
+      msa += lexicon(2).count(w);
+      if (w.size() >= 6) {                                  // three Arabic letters or more
+        const bool kik = starts(w, "كي") || starts(w, "كا");
+        if (kik || starts(w, "تا") || starts(w, "غا") || starts(w, "ما")) {
+          if (w.size() >= 4 && w.compare(w.size() - 2, 2, "ش") == 0) ++dar_ar;
+          else if (kik) ++dar_ar;
+        }
+      }
+    } else {
+      ++lt_words;
+      dar_lt += lexicon(1).count(w);
+      fr += lexicon(3).count(w);
+      en += lexicon(4).count(w);
+      bool letter = false, digit = false;
+      for (size_t q = 0; q < w.size();) {
+        const u32 c = uni::decode(w, q);
+        letter |= uni::is_latin_letter(c);
+        digit |= uni::is_arabizi_digit(c);
+      }
+      if (letter && digit) ++arabizi;
+    }
   }
   const double n = static_cast<double>(ws.size());
-  r.darija_score = hit[0] / n;
-  r.arabizi_score = (hit[1] + shaped) / n;
-  r.msa_score = hit[2] / n;
-  r.french_score = hit[3] / n;
-  r.english_score = hit[4] / n;
-  if (r.arabic_ratio >= 0.7) {
-    // Arabic script: Darija unless Standard-Arabic function words clearly dominate
-    const bool msa = r.msa_score > r.darija_score + 0.02 && r.msa_score >= 0.05;
-    r.tag = msa ? LangTag::MSA : LangTag::DarijaArab;
-    r.confidence = std::min(1.0, 0.4 + 2.0 * std::fabs(r.darija_score - r.msa_score) + (msa ? 0 : 0.1));
-  } else if (r.latin_ratio >= 0.7) {
-    const double best = std::max({r.arabizi_score, r.french_score, r.english_score});
-    if (best < 0.04) {
+  r.darija_score = (dar_ar + dar_lt) / n;
+  r.msa_score = msa / n;
+  r.french_score = fr / n;
+  r.english_score = en / n;
+  r.arabizi_score = arabizi / n;
+  const double arw = std::max(1.0, ar_words), ltw = std::max(1.0, lt_words);
+  const double d_ar = dar_ar / arw, d_lt = (dar_lt + arabizi) / ltw, d_msa = msa / arw, d_fr = fr / ltw, d_en = en / ltw;
+
+  if (r.arabic_ratio > 0.6) {
+    if (d_ar >= 0.06 || dar_ar >= 2) {
+      r.tag = LangTag::DarijaArab;
+      r.confidence = std::min(1.0, 0.4 + d_ar * 4.0);
+    } else {
+      r.tag = LangTag::MSA;
+      r.confidence = d_msa >= 0.10 ? std::min(1.0, 0.4 + d_msa * 3.0) : 0.3;
+    }
+  } else if (r.latin_ratio > 0.6) {
+    const bool dar_hit = d_lt >= 0.08 || dar_lt + arabizi >= 2;
+    const bool en_hit = d_en >= 0.08 || en >= 2;
+    const bool fr_hit = d_fr >= 0.15;
+    if (dar_hit && d_en <= d_lt) {
+      r.tag = LangTag::DarijaLatn;
+      r.confidence = std::min(1.0, 0.4 + d_lt * 4.0);
+    } else if (fr_hit && d_fr > d_en && d_fr >= d_lt) {
+      r.tag = LangTag::French;
+      r.confidence = std::min(1.0, 0.35 + d_fr * 2.0);
+    } else if (en_hit && d_en >= d_lt) {
+      r.tag = LangTag::English;
+      r.confidence = std::min(1.0, 0.35 + d_en * 2.0);
+    } else if (dar_hit) {
+      r.tag = LangTag::DarijaLatn;
+      r.confidence = std::min(1.0, 0.4 + d_lt * 4.0);
+    } else {
       r.tag = LangTag::Other;
       r.confidence = 0.2;
-    } else if (r.arabizi_score >= r.french_score && r.arabizi_score >= r.english_score * 0.8 && r.arabizi_score >= 0.08) {
-      r.tag = LangTag::DarijaLatn;
-      r.confidence = std::min(1.0, 0.35 + 2.0 * r.arabizi_score);
-    } else if (r.english_score >= r.french_score) {
-      r.tag = LangTag::English;
-      r.confidence = std::min(1.0, 0.35 + 2.0 * r.english_score);
-    } else {
-      r.tag = LangTag::French;
-      r.confidence = std::min(1.0, 0.35 + 2.0 * r.french_score);
     }
   } else {
     r.tag = LangTag::Mixed;
-    r.confidence = 0.5;
+    r.confidence = dar_ar + dar_lt + arabizi >= 1 ? 0.6 : 0.35;
   }
   return r;
 }

@@ -175,11 +175,13 @@ def load_suite(directory: str) -> List[EvalItem]:
 
 
 def write_suite(path: str, items: List[EvalItem]) -> None:
+    """One compact JSON object per line: the reference reads these files with a scanner that expects no space after
+    ``:`` and ``,`` (evaluation/benchmark.cpp:380-470 there)."""
     with open(path, "w", encoding="utf-8") as f:
         for it in items:
             f.write(json.dumps({"category": it.category, "id": it.id, "context": [{"role": m.role, "content": m.content} for m in it.context],
                                 "prompt": it.prompt, "expect_any": it.expect_any, "forbid": it.forbid, "expect_lang": it.expect_lang,
-                                "max_words": it.max_words, "note": it.note}, ensure_ascii=False) + "\n")
+                                "max_words": it.max_words, "note": it.note}, ensure_ascii=False, separators=(",", ":")) + "\n")
 
 
 def score_response(item: EvalItem, response: str, seconds: float = 0.0) -> dict:

@@ -87,7 +87,7 @@ def test_language_tags():
     h = H()
     want = {"واش نتا بخير؟ بغيت نمشي للسوق دابا حيت خاصني الخضرة": "ar-MA-arab",
             "wach nta bikhir? bghit nmchi l souk daba 7it khassni lkhodra": "ar-MA-latn",
-            "إن هذا الأمر يتطلب دراسة معمقة حيث أن النتائج التي تم الحصول عليها ليست كافية": "ar-MSA",
+            "إن هذا الأمر يتطلب دراسة معمقة لذلك يجب على الجميع أن يشاركوا في هذا العمل الذي بدأناه": "ar-MSA",
             "Je voudrais savoir comment aller à la gare, s'il vous plaît, parce que je suis en retard": "fr",
             "I would like to know how the weather is going to be tomorrow because we are travelling": "en"}
     for text, tag in want.items():
@@ -95,6 +95,13 @@ def test_language_tags():
         assert r["tag"] == tag, (text, r)
         assert 0.0 <= r["confidence"] <= 1.0
     assert h.msa_ratio(list(want)[2]) > h.msa_ratio(list(want)[0])
+    # without word evidence the script decides, as in the reference classifier (dataset/langid.cpp:196-237 there):
+    # Arabic script -> Standard Arabic at low confidence, Latin script -> other, no letters -> other at zero
+    assert h.classify_language("دددددددددددد")["tag"] == "ar-MSA" and h.classify_language("دددددددددددد")["confidence"] == 0.3
+    assert h.classify_language(" w w w w w w w w")["tag"] == "other"
+    assert h.classify_language("12345 !!!") == dict(h.classify_language(""), tag="other")
+    # the verb shapes of Darija count as evidence: a ka- word makes this otherwise formal sentence Darija there too
+    assert h.classify_language("إن هذا الأمر يتطلب دراسة معمقة حيث أن النتائج التي تم الحصول عليها ليست كافية")["tag"] == "ar-MA-arab"
 
 
 def test_dedup_exact_near_and_blocklist():
