@@ -73,7 +73,8 @@ def _load_tok(a) -> T.Tokenizer:
 
 
 def _build_cfg(a) -> P.BuildConfig:
-    style = a.style_mode or "darija"
+    # the reference's defaults: `build` works in the English style, the Parquet reader in the Darija one
+    style = a.style_mode or ("en" if getattr(a, "command", "") == "build" else "darija")
     if style not in ("darija", "en", "off"):
         raise SystemExit("--style-mode must be darija|en|off")
     block: List[str] = []

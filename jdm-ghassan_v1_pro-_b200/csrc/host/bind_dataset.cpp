@@ -68,6 +68,7 @@ void bind_dataset(py::module_& m) {
       .def_readwrite("max_digit_ratio", &QualityConfig::max_digit_ratio)
       .def_readwrite("max_upper_ratio", &QualityConfig::max_upper_ratio)
       .def_readwrite("max_word_repeat", &QualityConfig::max_word_repeat)
+      .def_readwrite("max_repeat_line", &QualityConfig::max_repeat_line)
       .def_readwrite("min_letter_ratio", &QualityConfig::min_letter_ratio)
       .def_readwrite("min_words", &QualityConfig::min_words)
       .def_readwrite("max_word_length", &QualityConfig::max_word_length)
@@ -77,6 +78,10 @@ void bind_dataset(py::module_& m) {
   m.def("english_quality_config", &english_quality_config);
   m.def("quality_check", [](const std::string& s, const QualityConfig& c) {
     const QualityVerdict v = quality_check(s, c);
+    return py::make_tuple(v.accept, v.reason);
+  }, py::arg("text"), py::arg("config") = QualityConfig{});
+  m.def("quality_check_english", [](const std::string& s, const QualityConfig& c) {
+    const QualityVerdict v = quality_check_english(s, c);
     return py::make_tuple(v.accept, v.reason);
   }, py::arg("text"), py::arg("config") = QualityConfig{});
   m.def("check_toxicity", [](const std::string& s) {

@@ -46,8 +46,8 @@ class Cleaner {
 };
 
 struct QualityConfig {
-  double max_symbol_ratio = 0.25, max_digit_ratio = 0.30, max_upper_ratio = 0.40, max_word_repeat = 0.15,
-         min_letter_ratio = 0.45;
+  double max_symbol_ratio = 0.25, max_digit_ratio = 0.30, max_upper_ratio = 0.40, max_repeat_line = 0.15,
+         max_word_repeat = 0.15, min_letter_ratio = 0.45;
   int min_words = 2, max_word_length = 60;
   bool require_arabic_or_latin = true, reject_ai_disclaimers = true, reject_placeholders = true;
 };
@@ -57,6 +57,8 @@ struct QualityVerdict {
 };
 QualityVerdict quality_check(const std::string& text, const QualityConfig& cfg = {});
 QualityConfig english_quality_config();
+// English text: the wider English limits when `cfg` is the default one, then the hard "I am a language model" phrases
+QualityVerdict quality_check_english(const std::string& text, const QualityConfig& cfg = {});
 
 struct ToxicityResult {
   bool toxic = false;

@@ -277,13 +277,27 @@ bool Cleaner::clean_line(const std::string& in, std::string& out, CleanStats& st
   return true;
 }
 
+// Limits for English chat text: code, tables and one-word replies are ordinary there (the reference's
+// english_quality_config, dataset/cleaner.cpp:459-474 there); AI disclaimers are left to quality_check_english.
 QualityConfig english_quality_config() {
   QualityConfig c;
-  c.max_upper_ratio = 0.5;
-  c.min_words = 3;
+  c.max_symbol_ratio = 0.35;
+  c.max_digit_ratio = 0.50;
+  c.max_upper_ratio = 0.60;
+  c.max_repeat_line = 0.30;
+  c.max_word_repeat = 0.40;
+  c.min_letter_ratio = 0.30;
+  c.min_words = 1;
+  c.max_word_length = 80;
+  c.reject_ai_disclaimers = false;
   return c;
 }
 
+// The reference's checks in its order, with its reasons (dataset/cleaner.cpp:351-457 there): AI disclaimers and
+// unresolved placeholders first; then the character mix over ALL characters of the text (white space included): no
+// content, no letters, letter / symbol / digit ratios, shouting (capitals among more than 20 Latin letters); then the
+// white-space separated words: their number, the longest one, and from 8 words on the share of the most frequent word;
+// last, from 5 non-empty lines on, the share of repeated lines.
 QualityVerdict quality_check(const std::string& text, const QualityConfig& cfg) {
   QualityVerdict v;
   auto reject = [&](const char* why) {
@@ -291,43 +305,90 @@ QualityVerdict quality_check(const std::string& text, const QualityConfig& cfg) 
     v.reason = why;
     return v;
   };
-  size_t total = 0, letters = 0, digits = 0, symbols = 0, upper = 0, latin = 0, arabic = 0;
+  if (text.empty()) return reject("empty");
+  if (cfg.reject_ai_disclaimers) {
+    const std::string low = lower_ascii(text);
+    for (const char* d : {"as an ai language model", "as a language model", "as an artificial intelligence",
+                          "i don't have personal opinions", "i cannot fulfill this request", "i am an ai", "i'm an ai",
+                          "i cannot provide", "i'm sorry, but i cannot", "i am a large language model"})
+      if (low.find(d) != std::string::npos) return reject("ai_disclaimer");
+  }
+  if (cfg.reject_placeholders) {
+    for (const char* ph : {"[insert ", "[Insert ", "<your_", "<YOUR_", "TODO:", "[Your Name]", "[your name]"})
+      if (text.find(ph) != std::string::npos) return reject("unresolved_placeholder");
+  }
+  const uni::ScriptStats st = uni::script_stats(text);
+  if (st.total == 0) return reject("no content");
+  const size_t letters = st.arabic + st.latin;
+  const double total = static_cast<double>(st.total);
+  if (cfg.require_arabic_or_latin && letters == 0) return reject("no letters");
+  if (letters / total < cfg.min_letter_ratio) return reject("low letter ratio");
+  if ((st.punct + st.other) / total > cfg.max_symbol_ratio) return reject("symbol spam");
+  if (st.digits / total > cfg.max_digit_ratio) return reject("digit spam");
+  size_t upper = 0;
   for (size_t i = 0; i < text.size();) {
     const u32 c = uni::decode(text, i);
-    if (uni::is_whitespace(c)) continue;
-    ++total;
-    if (uni::is_arabic_letter(c)) { ++letters; ++arabic; }
-    else if (uni::is_latin_letter(c)) { ++letters; ++latin; upper += c >= 'A' && c <= 'Z'; }
-    else if (uni::is_ascii_digit(c) || uni::is_arabic_digit(c)) ++digits;
-    else if (!uni::is_arabic_diacritic(c) && !uni::is_emoji(c)) ++symbols;
+    upper += c >= 'A' && c <= 'Z';
   }
-  if (total == 0) return reject("empty");
-  std::vector<std::string> words;
+  if (st.latin > 20 && static_cast<double>(upper) / st.latin > cfg.max_upper_ratio) return reject("shouting");
+
+  std::unordered_map<std::string, int> freq;
+  size_t n_words = 0, longest = 0;
   {
-    std::istringstream ss(text);
-    for (std::string w; ss >> w;) words.push_back(lower_ascii(w));
+    std::string cur;
+    auto flush = [&]() {
+      if (cur.empty()) return;
+      ++n_words;
+      longest = std::max(longest, uni::length(cur));
+      ++freq[cur];
+      cur.clear();
+    };
+    for (size_t i = 0; i < text.size();) {
+      const size_t at = i;
+      const u32 c = uni::decode(text, i);
+      if (uni::is_whitespace(c)) flush();
+      else cur.append(text, at, i - at);
+    }
+    flush();
   }
-  if (static_cast<int>(words.size()) < cfg.min_words) return reject("too-few-words");
-  for (const auto& w : words)
-    if (static_cast<int>(uni::length(w)) > cfg.max_word_length) return reject("overlong-word");
-  if (cfg.require_arabic_or_latin && arabic + latin == 0) return reject("no-letters");
-  if (static_cast<double>(letters) / total < cfg.min_letter_ratio) return reject("low-letter-ratio");
-  if (static_cast<double>(symbols) / total > cfg.max_symbol_ratio) return reject("symbol-heavy");
-  if (static_cast<double>(digits) / total > cfg.max_digit_ratio) return reject("digit-heavy");
-  if (latin >= 20 && static_cast<double>(upper) / latin > cfg.max_upper_ratio) return reject("shouting");
-  if (words.size() >= 8) {
-    std::unordered_map<std::string, int> freq;
+  if (static_cast<int>(n_words) < cfg.min_words) return reject("too few words");
+  if (static_cast<int>(longest) > cfg.max_word_length) return reject("absurd word length");
+  if (n_words >= 8) {
     int top = 0;
-    for (const auto& w : words) top = std::max(top, ++freq[w]);
-    const double allowed = std::max(cfg.max_word_repeat, 3.0 / words.size());
-    if (static_cast<double>(top) / words.size() > allowed + 0.15) return reject("repetitive");
+    for (const auto& kv : freq) top = std::max(top, kv.second);
+    if (static_cast<double>(top) / n_words > cfg.max_word_repeat) return reject("word repetition");
   }
+  {
+    std::unordered_map<std::string, int> lines;
+    std::istringstream ls(text);
+    int n_lines = 0;
+    for (std::string line; std::getline(ls, line);) {
+      if (line.empty()) continue;
+      ++lines[line];
+      ++n_lines;
+    }
+    if (n_lines >= 5) {
+      int dup = 0;
+      for (const auto& kv : lines) dup += kv.second > 1 ? kv.second - 1 : 0;
+      if (static_cast<double>(dup) / n_lines > cfg.max_repeat_line) return reject("duplicated lines");
+    }
+  }
+  return v;
+}
+
+QualityVerdict quality_check_english(const std::string& text, const QualityConfig& cfg) {
+  QualityConfig c = cfg;
+  if (c.min_words == 2 && c.min_letter_ratio == 0.45) c = english_quality_config();
+  QualityVerdict v = quality_check(text, c);
+  if (!v.accept) return v;
   const std::string low = lower_ascii(text);
-  if (cfg.reject_ai_disclaimers && has_hard_ai_boilerplate(low)) return reject("ai-disclaimer");
-  if (cfg.reject_placeholders) {
-    for (const char* p : {"lorem ipsum", "todo:", "insert text here", "[placeholder]", "xxx xxx", "{{", "}}"})
-      if (low.find(p) != std::string::npos) return reject("placeholder");
-  }
+  for (const char* ph : {"as an ai", "as a language model", "as an ai language model", "i am a large language model",
+                         "i cannot fulfill this request"})
+    if (low.find(ph) != std::string::npos) {
+      v.accept = false;
+      v.reason = "ai_disclosure_hard";
+      return v;
+    }
   return v;
 }
 

@@ -11,25 +11,40 @@ namespace gbh {
 Deduplicator::Deduplicator(const Config& cfg) : cfg_(cfg) {
   GBH_CHECK(cfg_.num_hashes > 0 && cfg_.bands > 0 && cfg_.num_hashes % cfg_.bands == 0, "dedup: bands must divide num_hashes");
   u64 s = cfg_.seed;
-  for (int i = 0; i < cfg_.num_hashes; ++i) seeds_.push_back(s = splitmix64(s));
+  for (int i = 0; i < cfg_.num_hashes; ++i) seeds_.push_back((s = splitmix64(s)) | 1ull);
   bands_.resize(static_cast<size_t>(cfg_.bands));
 }
 
 std::vector<u64> Deduplicator::signature(const std::string& canonical) const {
-  // character shingles of `shingle` code points, hashed once, then re-mixed per permutation
-  std::vector<size_t> starts;
-  for (size_t i = 0; i < canonical.size();) {
-    starts.push_back(i);
-    uni::decode(canonical, i);
+  // Shingles of `shingle` consecutive WORDS (single-space joined), one FNV hash each, re-mixed per permutation.
+  // Word shingles, not character ones: two template answers that differ in a few words share most character
+  // 5-grams but few word 5-grams, and only the second is a near-duplicate by the reference's measure
+  // (dataset/dedup.cpp:40-62).  A text shorter than one shingle hashes as a single short shingle.
+  std::vector<std::pair<size_t, size_t>> words;   // [lo, hi) byte ranges
+  for (size_t i = 0, lo = std::string::npos; i <= canonical.size();) {
+    const size_t at = i;
+    const bool end = i >= canonical.size();
+    const u32 c = end ? ' ' : uni::decode(canonical, i);
+    if (end) ++i;
+    if (uni::is_whitespace(c)) {
+      if (lo != std::string::npos) words.emplace_back(lo, at);
+      lo = std::string::npos;
+    } else if (lo == std::string::npos) {
+      lo = at;
+    }
   }
-  starts.push_back(canonical.size());
   std::vector<u64> sig(static_cast<size_t>(cfg_.num_hashes), ~0ull);
+  if (words.empty()) return sig;
   const size_t k = static_cast<size_t>(cfg_.shingle);
-  const size_t n_chars = starts.size() - 1;
-  const size_t n_sh = n_chars >= k ? n_chars - k + 1 : 1;
+  const size_t n_sh = words.size() >= k ? words.size() - k + 1 : 1;
+  std::string sh;
   for (size_t i = 0; i < n_sh; ++i) {
-    const size_t lo = starts[i], hi = starts[std::min(n_chars, i + k)];
-    const u64 h = fnv1a64(canonical.data() + lo, hi - lo);
+    sh.clear();
+    for (size_t j = i; j < std::min(words.size(), i + k); ++j) {
+      if (j > i) sh.push_back(' ');
+      sh.append(canonical, words[j].first, words[j].second - words[j].first);
+    }
+    const u64 h = fnv1a64(sh.data(), sh.size());
     for (size_t j = 0; j < sig.size(); ++j) sig[j] = std::min(sig[j], splitmix64(h ^ seeds_[j]));
   }
   return sig;

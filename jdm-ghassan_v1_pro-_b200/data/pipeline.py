@@ -159,6 +159,7 @@ class BuildReport:
     seen: int = 0
     kept_docs: int = 0
     kept_windows: int = 0
+    split_docs: int = 0
     train_windows: int = 0
     train_tokens: int = 0
     val_windows: int = 0
@@ -170,7 +171,8 @@ class BuildReport:
     dedup: Dict[str, int] = field(default_factory=dict)
 
     def summary(self) -> str:
-        lines = ["seen documents      : %d" % self.seen, "kept documents      : %d" % self.kept_docs,
+        lines = ["raw documents      : %d" % self.seen, "passed cleaning    : %d" % self.kept_docs,
+                 "split windows      : %d source docs exceeded seq_cap" % self.split_docs,
                  "kept windows        : %d" % self.kept_windows,
                  "train windows/tokens: %d / %d  (%d shards)" % (self.train_windows, self.train_tokens, self.train_shards),
                  "val   windows/tokens: %d / %d  (%d shards)" % (self.val_windows, self.val_tokens, self.val_shards)]
@@ -190,7 +192,7 @@ class _ShardSink:
         self.w, self.n_shards, self.in_shard, self.windows, self.tokens = None, 0, 0, 0, 0
 
     def add(self, ids: np.ndarray, mask: Optional[np.ndarray]):
-        if self.w is None or self.in_shard + len(ids) > self.cap:
+        if self.w is None or self.in_shard >= self.cap:
             self.close()
             path = os.path.join(self.dir, "%s%04d.gbin" % (self.prefix, self.n_shards))
             self.w = H.ShardWriter(path, self.vocab, self.with_mask)
@@ -208,100 +210,126 @@ class _ShardSink:
 
 
 def _windows(ids: np.ndarray, mask: Optional[np.ndarray], seq_len: int):
-    """Split one encoded document into windows of at most seq_len tokens (a tail shorter than 8 tokens joins the
-    previous window's fate: it is dropped rather than written as a stub)."""
-    n = len(ids)
-    if n <= seq_len:
-        yield ids, mask
-        return
-    for lo in range(0, n, seq_len):
-        hi = min(n, lo + seq_len)
-        if hi - lo < 8:
-            break
-        yield ids[lo:hi], (None if mask is None else mask[lo:hi])
+    """One encoded document as consecutive windows of at most ``seq_len`` tokens (no overlap; every window is kept)."""
+    for lo in range(0, len(ids), seq_len):
+        yield ids[lo:lo + seq_len], (None if mask is None else mask[lo:lo + seq_len])
 
 
 def build_shards(records: Iterable[Record], tok: T.Tokenizer, out_dir: str, cfg: BuildConfig) -> BuildReport:
+    """The reference builder's procedure (tools/data_pipeline_cli.cpp:1340-1620 there), so that both write the same shards
+    from the same input wherever their word lists agree:
+
+    * a text line: cleaned (PII lines dropped, or redacted for English), quality gate (the English limits for style
+      ``en``, the default ones otherwise: the gate is on in every style), toxicity, duplicate, then encoded with BOS / EOS
+      and supervised everywhere;
+    * a conversation: every message cleaned and passed through the quality gate on its own (one failure drops the
+      conversation), then toxicity and PII per message and, unless the style is ``off`` or robotic replies are kept, the
+      assistant-style check of each reply against the message before it; the duplicate key and the language are taken
+      from all messages joined by new lines; encoded with the chat template, assistant tokens supervised;
+    * a document goes to validation when the FNV-1a hash of its canonical key, modulo 10000, is below 10000 x
+      ``val_ratio``; all windows of a document follow it;
+    * shards always carry loss masks; a shard is closed once it holds ``shard_tokens`` tokens.
+    """
     os.makedirs(out_dir, exist_ok=True)
     rep = BuildReport()
-    cleaner = H.Cleaner()
-    qcfg = H.english_quality_config() if cfg.style_mode == "en" else H.QualityConfig()
+    english = cfg.style_mode == "en"
+    cc = H.CleanConfig()
+    cc.drop_pii_lines = not english
+    cc.redact_instead_drop = english
+    cleaner = H.Cleaner(cc)
+    quality = H.quality_check_english if english else H.quality_check
+    style_filter = cfg.style_mode != "off" and not cfg.keep_robotic
     dd = H.Deduplicator() if cfg.dedup else None
     if dd is not None:
         for t in cfg.blocklist:
             dd.add_blocklist_text(t)
     st = H.CleanStats()
-    staged: List[Tuple[np.ndarray, Optional[np.ndarray]]] = []
-    any_mask = False
+    dom = (cfg.domain + "_") if cfg.domain else ""
+    train = _ShardSink(out_dir, "train_" + dom, tok.vocab_size, True, cfg.shard_tokens)
+    val = _ShardSink(out_dir, "val_" + dom, tok.vocab_size, True, cfg.shard_tokens)
+    val_cut = int(cfg.val_ratio * 10000.0)
 
     def clean(text: str) -> Optional[str]:
         return cleaner.clean_line(text.encode("utf-8", errors="surrogateescape"), st)
 
+    def emit(ids: np.ndarray, mask: np.ndarray, key: str, lang: str):
+        if len(ids) == 0:
+            return
+        canon = H.canonical_text(key)
+        to_val = (H.fnv1a64((canon or key).encode("utf-8", errors="surrogateescape")) % 10000) < val_cut
+        if len(ids) > cfg.seq_len:
+            rep.split_docs += 1
+        for w_ids, w_mask in _windows(ids, mask, cfg.seq_len):
+            (val if to_val else train).add(np.ascontiguousarray(w_ids), np.ascontiguousarray(w_mask))
+            rep.kept_windows += 1
+            rep.languages[lang] += 1
+
     for rec in records:
         rep.seen += 1
         if rec.messages is not None:
-            msgs = []
+            if not rec.messages:
+                continue
+            msgs, bad = [], False
             for m in rec.messages:
                 c = clean(m.content)
-                if c is None:
-                    msgs = None
+                if c is None or len(c.encode("utf-8", errors="surrogateescape")) < 2 or not quality(c)[0]:
+                    bad = True
                     break
                 msgs.append(T.Message(m.role, c))
-            if not msgs or not any(m.role == "assistant" for m in msgs):
-                rep.dropped["clean"] += 1
+            if bad:
+                rep.dropped["quality"] += 1
                 continue
-            reply = " ".join(m.content for m in msgs if m.role == "assistant")
-            user = " ".join(m.content for m in msgs if m.role == "user")
-            if cfg.style_mode != "off" and not cfg.keep_robotic and H.check_assistant_style(reply, user)["robotic"]:
-                rep.dropped["robotic"] += 1
+            key = "".join(m.content + "\n" for m in msgs)
+            why = None
+            for i, m in enumerate(msgs):
+                if H.check_toxicity(m.content)["toxic"]:
+                    why = "toxicity"
+                elif H.scan_pii(m.content)["total"] > 0:
+                    why = "pii"
+                elif style_filter and m.role == "assistant":
+                    if english:
+                        robotic = H.has_hard_ai_boilerplate(m.content)
+                    else:
+                        robotic = H.check_assistant_style(m.content, msgs[i - 1].content if i > 0 else "")["robotic"]
+                    if robotic:
+                        why = "robotic"
+                if why:
+                    break
+            if why:
+                rep.dropped[why] += 1
                 continue
-            key_text = user + "\n" + reply
-            body = key_text
+            rep.kept_docs += 1
+            if dd is not None and not dd.add(key):
+                rep.dropped["duplicate"] += 1
+                continue
+            ids, mask = T.encode_chat(tok, msgs)
+            emit(np.asarray(ids, dtype=np.int32), np.asarray(mask, dtype=np.uint8), key, H.classify_language(key)["tag"])
         else:
             body = clean(rec.text)
             if body is None:
-                rep.dropped["clean"] += 1
                 continue
-            key_text = body
-            msgs = None
-        if cfg.style_mode != "off":
-            ok, why = H.quality_check(body, qcfg)
-            if not ok:
-                rep.dropped["quality:" + why] += 1
+            rep.kept_docs += 1
+            if not quality(body)[0]:
+                rep.dropped["quality"] += 1
                 continue
-        if dd is not None and not dd.add(key_text):
-            rep.dropped["duplicate"] += 1
-            continue
-        rep.languages[H.classify_language(body)["tag"]] += 1
-        if msgs is not None:
-            ids, mask = T.encode_chat(tok, msgs)
-            ids = np.concatenate([ids, np.array([T.EOS], dtype=np.int32)])
-            mask = np.concatenate([mask, np.array([0], dtype=np.uint8)])
-            any_mask = True
-        else:
-            ids, mask = tok.encode(body, add_bos=True, add_eos=True), None
-        rep.kept_docs += 1
-        for w_ids, w_mask in _windows(ids, mask, cfg.seq_len):
-            staged.append((np.ascontiguousarray(w_ids), w_mask))
+            if H.check_toxicity(body)["toxic"]:
+                rep.dropped["toxicity"] += 1
+                continue
+            if dd is not None and not dd.add(body):
+                rep.dropped["duplicate"] += 1
+                continue
+            ids = np.asarray(tok.encode(body, add_bos=True, add_eos=True), dtype=np.int32)
+            emit(ids, np.ones(len(ids), dtype=np.uint8), body, H.classify_language(body)["tag"])
     if dd is not None:
         rep.dedup = {"seen": dd.seen, "exact_dup": dd.exact_dups, "near_dup": dd.near_dups, "blocked": dd.blocked}
     rep.dropped["pii"] += int(st.dropped_pii)
     rep.dropped["encoding"] += int(st.dropped_encoding)
-    rep.kept_windows = len(staged)
-    if rep.kept_windows < cfg.min_keep:
-        raise ValueError("only %d windows kept (min_keep %d)" % (rep.kept_windows, cfg.min_keep))
-    dom = (cfg.domain + "_") if cfg.domain else ""
-    train = _ShardSink(out_dir, "train_" + dom, tok.vocab_size, any_mask, cfg.shard_tokens)
-    val = _ShardSink(out_dir, "val_" + dom, tok.vocab_size, any_mask, cfg.shard_tokens)
-    every = int(round(1.0 / cfg.val_ratio)) if cfg.val_ratio > 0 else 0
-    for i, (ids, mask) in enumerate(staged):
-        if any_mask and mask is None:
-            mask = np.ones(len(ids), dtype=np.uint8)        # plain text inside an SFT build: supervise everything
-        (val if (every and i % every == every - 1) else train).add(ids, mask)
     train.close()
     val.close()
     rep.train_windows, rep.train_tokens, rep.train_shards = train.windows, train.tokens, train.n_shards
     rep.val_windows, rep.val_tokens, rep.val_shards = val.windows, val.tokens, val.n_shards
+    if rep.kept_windows < cfg.min_keep:
+        raise ValueError("only %d windows kept (min_keep %d)" % (rep.kept_windows, cfg.min_keep))
     return rep
 
 

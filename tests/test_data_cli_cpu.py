@@ -48,7 +48,7 @@ def test_data_pipeline_build_inspect_tokinfo(tmp_path, capsys):
                   "--val-ratio", "0.1", "--style-mode", "off", "--domain", "mix", "--expect-vocab", "800"])
     text = (lambda o: o.out + o.err)(capsys.readouterr())
     assert rc == 0, text
-    assert "kept documents" in text and sorted(os.listdir(out)) == ["train_mix_0000.gbin", "val_mix_0000.gbin"]
+    assert "passed cleaning" in text and sorted(os.listdir(out)) == ["train_mix_0000.gbin", "val_mix_0000.gbin"]
     assert DP.main(["inspect", "--shards", out, "--tokenizer", TOK]) == 0
     assert "train_mix_0000.gbin:" in capsys.readouterr().out
     assert DP.main(["tok-info", "--tokenizer", TOK]) == 0
@@ -70,9 +70,9 @@ def test_data_pipeline_parquet_modes(tmp_path, capsys):
     lake = tmp_path / "lake"
     lake.mkdir()
     qs = ["chno hiya 3asimat lmaghrib nta li 3aref", "kifach n9der nt3ellem lprogrammation b zerba", "fin kayn a7san tajin f mrrakch had l3am"]
-    ans = ["l3asima hiya rbat, mdina zwina bzaf 3la lb7ar", "bda b python w dir tamarin kol nhar chwiya b chwiya", "kayn bzaf dyal lblayes zwinin f jam3 lfna w 7daha"]
+    ans = ["l3asima hiya rbat, mdina zwina bzaf 3la lb7ar", "bda b python w dir tamarin kol nhar chwiya bla zerba", "kayn bzaf dyal lblayes zwinin f jam3 lfna w 7daha"]
     pq.write_table(pa.table({"question": qs, "answer": ans}), str(lake / "darija_qa_part0.parquet"))
-    pq.write_table(pa.table({"text": ["had nhar zwin bzaf w ljow mzyan l tamchya f lb7ar m3a s7abi", "lbare7 mchit l souk w chrit lkhodra w lfawakih b taman mzyan"]}),
+    pq.write_table(pa.table({"text": ["had nhar zwin bzaf w ljow mzyan l tamchya f lb7ar m3a s7abi", "lbare7 mchit l souk w chrit lkhodra m3a lfawakih b taman mzyan"]}),
                    str(lake / "web_text_part0.parquet"))
     assert DP.main(["parquet", "--probe"]) == 0
     out = str(tmp_path / "o1")

@@ -77,9 +77,20 @@ def test_quality_and_toxicity_gates():
     ok, why = h.quality_check("$$$ ### @@@ !!! %%% ^^^ &&& *** ((( )))")
     assert not ok and why
     ok, why = h.quality_check("spam spam spam spam spam spam spam spam spam spam spam spam")
-    assert not ok and why == "repetitive"
-    ok, why = h.quality_check("As an AI language model, I cannot help with that request at all.", h.english_quality_config())
-    assert not ok
+    assert not ok and why == "word repetition"
+    ok, why = h.quality_check("wach nta bikhir a sahbi wach nta mzyan lyoum wla la")          # 2 of 11 words: above the 15 % limit
+    assert not ok and why == "word repetition"
+    ok, why = h.quality_check_english("wach nta bikhir a sahbi wach nta mzyan lyoum wla la")  # the English limit is 40 %
+    assert ok
+    ok, why = h.quality_check("As an AI language model, I cannot help with that request at all.")
+    assert not ok and why == "ai_disclaimer"
+    ok, why = h.quality_check_english("As an AI language model, I cannot help with that request at all.")
+    assert not ok and why == "ai_disclosure_hard"
+    ok, why = h.quality_check("ok")
+    assert not ok and why == "too few words"
+    assert h.quality_check_english("ok")[0]
+    ok, why = h.quality_check("\n".join(["nfs ster kol mera"] * 4 + ["ster akhor mkhtalf 3la lokhrin"]))
+    assert not ok and why in ("word repetition", "duplicated lines")
     assert not h.check_toxicity("nhar zwin had lyoum, nmchiw l b7ar")["toxic"]
 
 
@@ -133,10 +144,12 @@ def test_assistant_style_flags():
 def test_build_matches_reference_documents(tok, tmp_path):
     from ghassan_b200.data import pipeline as P
     ref, _ = _docs(os.path.join(GOLD, "probe_train_0000.gbin"))
-    rep = P.build_shards(P.iter_inputs(os.path.join(GOLD, "probe.txt")), tok, str(tmp_path), P.BuildConfig(val_ratio=0.0))
+    # the reference's `build` defaults: English style, 0.5 % validation by key hash, masks always written
+    rep = P.build_shards(P.iter_inputs(os.path.join(GOLD, "probe.txt")), tok, str(tmp_path), P.BuildConfig(val_ratio=0.005, style_mode="en"))
     mine, s = _docs(str(tmp_path / "train_0000.gbin"))
-    assert rep.kept_docs == 60 and rep.val_shards == 0 and not s.has_mask
-    assert set(ref) <= set(mine) and len(ref) == 59          # the reference held one document back for validation
+    assert rep.seen == 60 and rep.kept_docs == 60 and rep.dropped["quality"] == 1 and rep.val_shards == 0 and s.has_mask
+    assert mine == ref and len(ref) == 59                    # the same 59 documents in the same order (one fails the quality gate)
+    assert open(str(tmp_path / "train_0000.gbin"), "rb").read() == open(os.path.join(GOLD, "probe_train_0000.gbin"), "rb").read()
     assert all(d[0] == 1 and d[-1] == 2 for d in mine)
 
 
@@ -149,8 +162,8 @@ def test_build_chat_masks_val_split_and_windows(tok, tmp_path):
     recs = list(P.iter_inputs(str(src)))
     assert len(recs) == 60 and recs[0].messages and recs[0].messages[0].role == "user"
     rep = P.build_shards(recs, tok, str(tmp_path / "o"), P.BuildConfig(seq_len=48, val_ratio=0.1, style_mode="off"))
-    assert rep.dropped["duplicate"] > 0 and rep.kept_docs + rep.dropped["duplicate"] == 60
-    assert rep.val_windows == rep.kept_windows // 10 and rep.train_windows + rep.val_windows == rep.kept_windows
+    assert rep.dropped["duplicate"] == 4 and rep.kept_docs + rep.dropped["quality"] + rep.dropped["toxicity"] == 60
+    assert 0 < rep.val_windows < rep.kept_windows // 3 and rep.train_windows + rep.val_windows == rep.kept_windows   # split by key hash
     docs, s = _docs(str(tmp_path / "o" / "train_0000.gbin"))
     assert s.has_mask and max(len(d) for d in docs) <= 48
     m = np.asarray([s.mask(i) for i in range(s.n_tokens)])
@@ -161,12 +174,75 @@ def test_build_chat_masks_val_split_and_windows(tok, tmp_path):
         P.build_shards([], tok, str(tmp_path / "e"), P.BuildConfig())
 
 
+REF_DP = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "bin", "data_pipeline")
+
+
+def _windows_with_masks(folder, prefix):
+    h = H()
+    out = []
+    for name in sorted(n for n in os.listdir(folder) if n.startswith(prefix) and n.endswith(".gbin")):
+        s = h.ShardFile()
+        ok, why = s.open(os.path.join(folder, name))
+        assert ok, why
+        t = np.asarray(s.tokens(0, s.n_tokens)).tolist()
+        m = [int(s.mask(i)) for i in range(s.n_tokens)] if s.has_mask else [1] * s.n_tokens
+        st = 0
+        for _ in range(s.n_docs):
+            e = s.doc_end_after(st)
+            out.append((tuple(t[st:e]), tuple(m[st:e])))
+            st = e
+    return out
+
+
+def _is_subsequence(small, big):
+    it = iter(big)
+    return all(any(x == y for y in it) for x in small)
+
+
+@pytest.mark.skipif(not os.path.exists(REF_DP), reason="no build of the reference data tool here")
+def test_build_reproduces_the_reference_builder_live(tok, tmp_path):
+    """The reference's builder and this one on one chat corpus with the same settings (English style, 10 % validation,
+    48-token windows): every window the reference wrote appears here with the same tokens and loss mask, in the same
+    order and on the same side of the train/validation split.  This builder may keep more (its word lists differ),
+    never a different window.  Reference: tools/data_pipeline.cpp (build), src/data/shard_builder.cpp."""
+    import subprocess
+    from ghassan_b200.data import pipeline as P, synth as S
+    rows = list(S.darija_conversations(70, seed=11)) + list(S.english_conversations(50, seed=12))
+    rows += rows[:6]
+    src = tmp_path / "c.jsonl"
+    S.write_jsonl(str(src), rows)
+    r = subprocess.run([REF_DP, "build", "--tokenizer", os.path.join(GOLD, "ref_small.gtok"), "--out", str(tmp_path / "r"),
+                        "--chat", str(src), "--val-ratio", "0.1", "--seq-len", "48"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rep = P.build_shards(P.iter_inputs(str(src)), tok, str(tmp_path / "o"), P.BuildConfig(seq_len=48, val_ratio=0.1, style_mode="en"))
+    def conversations(ws):                     # a conversation's first window opens with <s>
+        out = []
+        for w in ws:
+            if w[0][0] == 1:
+                out.append([])
+            out[-1].append(w)
+        return [tuple(c) for c in out]
+
+    redacted = 0
+    for side in ("train_", "val_"):
+        ref = conversations(_windows_with_masks(str(tmp_path / "r"), side))
+        mine = conversations(_windows_with_masks(str(tmp_path / "o"), side))
+        # The reference's IBAN pattern (two letters, two digits, 15+ letters or digits with spaces between) also fires on
+        # lower-case Arabizi such as "mo93 riadi bash t3rf" and writes "[iban]" into the training text; this builder's
+        # pattern wants upper-case country letters, so those conversations differ and are set aside here.
+        clean = [c for c in ref if "[iban]" not in "".join(tok.decode(list(w[0])) for w in c)]
+        redacted += len(ref) - len(clean)
+        assert clean and _is_subsequence(clean, mine), side
+        assert len(mine) <= len(ref) * 1.1, (side, len(ref), len(mine))
+    assert redacted <= 6 and rep.dropped["duplicate"] == 6 and rep.dedup["near_dup"] == 0
+
+
 def test_blocklist_keeps_eval_prompts_out(tok, tmp_path):
     from ghassan_b200.data import pipeline as P
     secret = "what is the tallest mountain in north africa and where exactly is it located"
     recs = [P.Record(text=secret), P.Record(text="lyoum ljow zwin bzaf w bghit nmchi nt3awd m3a s7abi f lb7ar")]
     rep = P.build_shards(recs, tok, str(tmp_path), P.BuildConfig(val_ratio=0.0, style_mode="off", blocklist=[secret]))
-    assert rep.kept_docs == 1 and rep.dedup["blocked"] == 1
+    assert rep.kept_docs == 2 and rep.kept_windows == 1 and rep.dedup["blocked"] == 1
 
 
 def test_readers_accept_common_layouts(tmp_path):
