@@ -19,7 +19,7 @@ from .common import add_common_flags, apply_common_flags
 from .. import _gb200_host as H
 from ..data import pipeline as P
 from ..data import tokenizer as T
-from ..utils.log import human_count, log_error, log_info
+from ..utils.log import human_bytes, human_count, log_error, log_info
 
 
 def main(argv: Optional[List[str]] = None) -> int:
@@ -77,19 +77,43 @@ def main(argv: Optional[List[str]] = None) -> int:
     if st["documents"] == 0:
         log_error("no documents found under " + a.input)
         return 1
-    log_info("documents : %s" % human_count(st["documents"]))
-    log_info("words     : %s   characters: %s" % (human_count(st["words"]), human_count(st["characters"])))
-    log_info("words/doc : p50 %d  p90 %d  p99 %d" % (st["words_p50"], st["words_p90"], st["words_p99"]))
+    # the report goes to stdout as the reference's does (dataset/corpus_stats.cpp:92-140): totals, share of documents
+    # per language (by name), per script and style, lengths, vocabulary use
+    docs = st["documents"]
+    share = lambda k: 100.0 * k / docs
+    out = ["", "==================== corpus statistics ====================",
+           "  documents          : %s" % human_count(docs),
+           "  lines              : %s" % human_count(st["lines"]),
+           "  bytes              : %s" % human_bytes(st["bytes"]),
+           "  characters         : %s" % human_count(st["characters"]),
+           "  words              : %s" % human_count(st["words"])]
     if tok is not None:
-        log_info("tokens    : %s   tokens/word %.3f" % (human_count(st["tokens"]), st["tokens_per_word"] or 0.0))
-    log_info("---- language mix ----")
-    for k, v in st["languages"].items():
-        log_info("  %-12s %8d  %6.2f%%" % (k, v, 100.0 * v / st["documents"]))
+        out += ["  tokens             : %s" % human_count(st["tokens"]),
+                "  tokens / word      : %.3f" % (st["tokens_per_word"] or 0.0),
+                "  bytes / token      : %.3f" % (st["bytes_per_token"] or 0.0)]
+    out += ["", "  -- language distribution (share of documents) --"]
+    out += ["    %-14s %8s  %6.2f%%" % (k, human_count(v), share(v)) for k, v in sorted(st["languages"].items())]
+    sy = st["style"]
+    out += ["", "  -- script / style --",
+            "    arabic script    %6.2f%%" % share(sy["arabic_script"]), "    latin script     %6.2f%%" % share(sy["latin_script"]),
+            "    arabizi          %6.2f%%" % share(sy["arabizi"]), "    french-mixed     %6.2f%%" % share(sy["french_mixed"]),
+            "    contains emoji   %6.2f%%" % share(sy["emoji"])]
     sc = st["scripts"]
     total = max(1, sum(sc.values()))
-    log_info("---- script mix (letters) ----")
-    for k in ("arabic", "latin", "digits", "emoji"):
-        log_info("  %-8s %10d  %6.2f%%" % (k, sc[k], 100.0 * sc[k] / total))
+    out += ["    letters by script: " + "  ".join("%s %.2f%%" % (k, 100.0 * sc[k] / total) for k in ("arabic", "latin", "digits", "emoji"))]
+    out += ["", "  -- length --", "    avg chars/doc    %.1f" % st["avg_chars"], "    avg words/doc    %.1f" % st["avg_words"],
+            "    words p50/p90/p99  %d / %d / %d" % (st["words_p50"], st["words_p90"], st["words_p99"])]
+    if "avg_tokens" in st:
+        out += ["    avg tokens/doc   %.1f" % st["avg_tokens"], "    median tokens    %d" % st["median_tokens"],
+                "    p10/p50/p90/p99  %d / %d / %d / %d" % (st["tokens_p10"], st["tokens_p50"], st["tokens_p90"], st["tokens_p99"]),
+                "", "  -- vocabulary --",
+                "    distinct tokens  %s / %d  (%.1f%% coverage)" % (human_count(st["vocab_used"]), tok.vocab_size,
+                                                                      100.0 * st["vocab_used"] / max(1, tok.vocab_size)),
+                "    byte-fallback    %.2f%% of used vocab" % (100.0 * st["byte_fallback"])]
+    if dd is not None and dd.seen:
+        out += ["", "  duplicate ratio    : %.2f%%" % (100.0 * (dd.exact_dups + dd.near_dups) / dd.seen)]
+    out += ["==========================================================="]
+    print("\n".join(out))
     if dd is not None:
         log_info("duplicates: exact %d  near %d  (%.2f%% of %d)" % (dd.exact_dups, dd.near_dups,
                                                                     100.0 * (dd.exact_dups + dd.near_dups) / max(1, dd.seen), dd.seen))

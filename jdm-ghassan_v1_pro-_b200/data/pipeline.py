@@ -353,30 +353,57 @@ def inspect_shards(directory: str, tok: Optional[T.Tokenizer] = None, show: int 
 
 
 def corpus_stats(records: Iterable[Record], tok: Optional[T.Tokenizer] = None) -> dict:
-    """Counts for the ``corpus_stats`` command: documents, characters, words, language mix, script mix, fertility."""
-    n = chars = words = toks = 0
-    langs, scripts = Counter(), Counter()
-    lengths = []
+    """Counts for the ``corpus_stats`` command, by the reference analyser's definitions (dataset/corpus_stats.cpp:10-90):
+    a document's script is Arabic or Latin when more than 60 % of its letters are; it is Arabizi above an Arabizi score
+    of 0.02 and French-mixed when tagged Darija with a French score above 0.05; lines are newlines + 1; the median is
+    the upper middle element and a percentile p the element at floor(p * (n - 1)) of the sorted token counts; the
+    byte-fallback share is the part of the distinct tokens used that are raw byte tokens (ids 16..271)."""
+    n = chars = words = toks = nbytes = lines = 0
+    langs, scripts, style = Counter(), Counter(), Counter()
+    lengths, doc_tokens, used = [], [], set()
     for rec in records:
         text = rec.text if rec.messages is None else "\n".join(m.content for m in rec.messages)
         if not text:
             continue
         n += 1
-        chars += len(text)
+        nbytes += len(text.encode("utf-8", "surrogatepass"))
+        lines += 1 + text.count("\n")
         w = len(text.split())
         words += w
         lengths.append(w)
-        langs[H.classify_language(text)["tag"]] += 1
+        lang = H.classify_language(text)
+        langs[lang["tag"]] += 1
         st = H.script_stats(text)
-        scripts["arabic"] += st["arabic"]
-        scripts["latin"] += st["latin"]
-        scripts["digits"] += st["digits"]
-        scripts["emoji"] += st["emoji"]
+        chars += st["total"]
+        for k in ("arabic", "latin", "digits", "emoji"):
+            scripts[k] += st[k]
+        letters = st["arabic"] + st["latin"]
+        if letters and st["arabic"] / letters > 0.6:
+            style["arabic_script"] += 1
+        elif letters and st["latin"] / letters > 0.6:
+            style["latin_script"] += 1
+        style["emoji"] += st["emoji"] > 0
+        style["arabizi"] += lang["arabizi_score"] > 0.02
+        style["french_mixed"] += lang["french_score"] > 0.05 and lang["tag"] in ("ar-MA-arab", "ar-MA-latn")
         if tok is not None:
-            toks += len(tok.encode(text))
+            ids = tok.encode(text)
+            toks += len(ids)
+            doc_tokens.append(len(ids))
+            used.update(int(i) for i in ids)
     lengths.sort()
+    doc_tokens.sort()
     pct = lambda q: lengths[min(len(lengths) - 1, int(q * len(lengths)))] if lengths else 0
-    return {"documents": n, "characters": chars, "words": words, "tokens": toks,
-            "tokens_per_word": (toks / words) if (tok is not None and words) else None,
-            "words_p50": pct(0.5), "words_p90": pct(0.9), "words_p99": pct(0.99),
-            "languages": dict(langs.most_common()), "scripts": dict(scripts)}
+    tq = lambda q: doc_tokens[int(q * (len(doc_tokens) - 1))] if doc_tokens else 0
+    out = {"documents": n, "lines": lines, "bytes": nbytes, "characters": chars, "words": words, "tokens": toks,
+           "tokens_per_word": (toks / words) if (tok is not None and words) else None,
+           "bytes_per_token": (nbytes / toks) if toks else None,
+           "avg_chars": chars / n if n else 0.0, "avg_words": words / n if n else 0.0,
+           "words_p50": pct(0.5), "words_p90": pct(0.9), "words_p99": pct(0.99),
+           "languages": dict(langs.most_common()), "scripts": dict(scripts),
+           "style": {k: int(style[k]) for k in ("arabic_script", "latin_script", "arabizi", "french_mixed", "emoji")}}
+    if doc_tokens:
+        raw = sum(1 for i in used if 16 <= i < 272)
+        out.update({"avg_tokens": toks / len(doc_tokens), "median_tokens": doc_tokens[len(doc_tokens) // 2],
+                    "tokens_p10": tq(0.10), "tokens_p50": tq(0.50), "tokens_p90": tq(0.90), "tokens_p99": tq(0.99),
+                    "vocab_used": len(used), "byte_fallback": raw / len(used) if used else 0.0})
+    return out

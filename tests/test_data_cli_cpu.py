@@ -32,13 +32,49 @@ def test_corpus_stats_cli(capsys):
     from ghassan_b200.cli import corpus_stats as CS
     assert CS.main(["--input", os.path.join(GOLD, "probe.txt"), "--tokenizer", TOK, "--dedup", "--pii", "--quality", "--sample", "1"]) == 0
     text = (lambda o: o.out + o.err)(capsys.readouterr())
-    assert "documents : 60" in text and "tokens/word" in text and "ar-MA-latn" in text and "duplicates:" in text
+    assert "documents          : 60" in text and "tokens / word      : 1.114" in text and "ar-MA-latn" in text and "duplicates:" in text
+    assert "median tokens    13" in text and "p10/p50/p90/p99  5 / 12 / 19 / 21" in text and "distinct tokens  167 / 800" in text
     assert "personal data:" in text and "quality filter would reject" in text and "---- sample: en ----" in text
     assert CS.main(["--input", os.path.join(GOLD, "probe.txt"), "--limit", "7"]) == 0
-    assert "documents : 7" in (lambda o: o.out + o.err)(capsys.readouterr())
+    assert "documents          : 7\n" in (lambda o: o.out + o.err)(capsys.readouterr())
     assert CS.main([]) == 2 and CS.main(["--input", "/nonexistent/dir"]) == 1
     assert CS.main(["--input", os.path.join(GOLD, "probe.txt"), "--tokenizer", "/nonexistent.gtok"]) == 1
     capsys.readouterr()
+
+
+REF_CS = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "bin", "corpus_stats")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_CS), reason="no build of the reference corpus tool here")
+def test_corpus_stats_equals_the_reference_tool(capsys):
+    """Both tools on the fixture corpus: every figure outside the language table is the same (totals, fertility,
+    script and style shares, lengths, percentiles, vocabulary use); the language table may move one document between
+    neighbouring tags, since the word lists are each project's own."""
+    import re
+    import subprocess
+    from ghassan_b200.cli import corpus_stats as CS
+    args = ["--input", os.path.join(GOLD, "probe.txt"), "--tokenizer", TOK]
+    ref = subprocess.run([REF_CS] + args, capture_output=True, text=True, timeout=120)
+    assert ref.returncode == 0, ref.stdout + ref.stderr
+    assert CS.main(args) == 0
+    mine = capsys.readouterr().out
+
+    def figures(text):
+        rows, langs, in_lang = {}, {}, False
+        for ln in text.splitlines():
+            if ln.startswith("  -- "):
+                in_lang = "language distribution" in ln
+                continue
+            m = re.match(r"^\s+([a-zA-Z][a-zA-Z0-9/ \-]*?)\s*:?\s+([0-9].*)$", ln)
+            if not m:
+                continue
+            (langs if in_lang else rows)[m.group(1).strip()] = m.group(2).strip()
+        return rows, langs
+
+    (ra, la), (rb, lb) = figures(ref.stdout), figures(mine)
+    ra.pop("analysed in", None)
+    assert len(ra) >= 20 and all(rb.get(k) == v for k, v in ra.items()), {k: (v, rb.get(k)) for k, v in ra.items() if rb.get(k) != v}
+    assert set(la) == set(lb) and sum(abs(int(la[k].split()[0]) - int(lb[k].split()[0])) for k in la) <= 4
 
 
 def test_data_pipeline_build_inspect_tokinfo(tmp_path, capsys):
