@@ -20,7 +20,6 @@
 from __future__ import annotations
 
 import argparse
-import csv
 import glob
 import itertools
 import json
@@ -106,43 +105,133 @@ def _mode_filter(recs: Iterator[P.Record], mode: str) -> Iterator[P.Record]:
 def _csv_files(root: str) -> List[str]:
     if os.path.isfile(root):
         return [root]
-    return sorted(glob.glob(os.path.join(root, "**", "*.csv"), recursive=True))
+    return sorted(p for p in glob.glob(os.path.join(root, "**", "*"), recursive=True) if p.endswith(".csv") and os.path.isfile(p))
 
 
-_DARIJA_COLS = ("darija", "darija_ar", "darija_arabic", "darija_latin", "arabizi", "n1", "n2", "n3", "n4", "root", "masculine", "feminine", "plural")
-_ENGLISH_COLS = ("eng", "english", "en", "gloss")
-_Q_COLS = ("question", "prompt", "instruction", "input", "eng", "english")
-_A_COLS = ("answer", "response", "output", "darija", "darija_ar")
+# How the vocabulary and grammar tables are read (the reference's tools/data_pipeline_cli.cpp:894-926, 928-1030, 1099-1215):
+# a first row counts as a header only when it names one of the known columns; every column then has a role: bookkeeping
+# (skipped), Arabic script, English gloss, or a Darija variant (everything else).  A table without such a header has
+# variants only, its first row included.  Cells are flattened to one line and measured in bytes.
+_META_COLS = ("id", "source", "dataset_source", "metadata", "token_count", "word_count", "count", "freq")
+_HEADER_NAMES = ("darija", "darija_ar", "eng", "english", "root", "arabic")
+_SKIP, _VARIANT, _ARABIC, _ENGLISH = 0, 1, 2, 3
+_ASCII_LOWER = str.maketrans("ABCDEFGHIJKLMNOPQRSTUVWXYZ", "abcdefghijklmnopqrstuvwxyz")
 
 
-def _csv_rows(path: str):
-    with open(path, encoding="utf-8", errors="replace", newline="") as f:
-        rd = csv.DictReader(f)
-        for row in rd:
-            yield {(k or "").strip().lower(): (v or "").strip() for k, v in row.items()}
+def _flat(cell: str) -> str:
+    return cell.replace("\n", " ").replace("\r", " ").replace("\t", " ").strip(" \t\r\n")
+
+
+def _split_row(line: str) -> List[str]:
+    """One physical line into cells: commas split, double quotes group, a doubled quote inside quotes is a quote."""
+    cells, cur, quoted, i = [], [], False, 0
+    while i < len(line):
+        c = line[i]
+        if quoted:
+            if c == '"' and line[i + 1:i + 2] == '"':
+                cur.append('"')
+                i += 1
+            elif c == '"':
+                quoted = False
+            else:
+                cur.append(c)
+        elif c == '"':
+            quoted = True
+        elif c == ",":
+            cells.append("".join(cur))
+            cur = []
+        else:
+            cur.append(c)
+        i += 1
+    cells.append("".join(cur))
+    return cells
+
+
+def _role(name: str) -> int:
+    n = name.strip(" \t\r\n").translate(_ASCII_LOWER)
+    if n in _META_COLS:
+        return _SKIP
+    if n in ("arabic", "ar", "darija_ar") or (len(n) > 3 and n.endswith("_ar")):
+        return _ARABIC
+    if n.startswith("eng"):
+        return _ENGLISH
+    return _VARIANT
+
+
+def _table_rows(path: str, min_bytes: int):
+    """Yields (variants, arabic cells, english cells, cells in column order as (role, text)) per non-empty row."""
+    with open(path, "rb") as f:
+        data = f.read()
+    if data.startswith(b"\xef\xbb\xbf"):
+        data = data[3:]
+    lines = [ln[:-1] if ln.endswith("\r") else ln for ln in data.decode("utf-8", "surrogateescape").split("\n")]
+    if lines and lines[-1] == "":
+        lines.pop()
+    if not lines:
+        return
+    first = [c.strip(" \t\r\n").translate(_ASCII_LOWER) for c in _split_row(lines[0])]
+    roles = None
+    if any(n in _HEADER_NAMES or n.startswith("n1") for n in first):
+        roles = [_role(c) for c in _split_row(lines[0])]
+        lines = lines[1:]
+    for ln in lines:
+        if not ln:
+            continue
+        ordered = []
+        for i, cell in enumerate(_split_row(ln)):
+            r = _VARIANT if roles is None or i >= len(roles) else roles[i]
+            t = _flat(cell)
+            if r != _SKIP and len(t.encode("utf-8", "surrogateescape")) >= min_bytes:
+                ordered.append((r, t))
+        yield ordered
+
+
+def _write_text(f, t: str) -> None:
+    f.write(t.encode("utf-8", "surrogateescape") + b"\n")
 
 
 def cmd_csvs(a) -> int:
+    """Tables -> corpus lines for the tokenizer trainer: each distinct cell once (English glosses only with
+    --with-english), plus one alignment line "variant / [second variant /] arabic" per row that has both."""
     files = _csv_files(a.dir or ".")
     if not files:
         log_error("no .csv files found under: " + (a.dir or "."))
         return 1
     log_info("[csvs] found %d file(s) under %s" % (len(files), a.dir or "."))
     out_path = a.out or "corpus_csv.txt"
-    seen, kept = set(), 0
-    with open(out_path, "w", encoding="utf-8") as out:
+    if os.path.dirname(out_path):
+        os.makedirs(os.path.dirname(out_path), exist_ok=True)
+    seen, kept, aligned, rows_in = set(), 0, 0, 0
+    with open(out_path, "wb") as out:
+        def emit(t: str) -> bool:
+            nonlocal kept
+            t = _flat(t)
+            if len(t.encode("utf-8", "surrogateescape")) < a.min_chars or t in seen:
+                return False
+            seen.add(t)
+            _write_text(out, t)
+            kept += 1
+            return True
+
         for p in files:
-            for row in _csv_rows(p):
-                cols = [c for c in row if c in _DARIJA_COLS or (a.with_english and c in _ENGLISH_COLS)]
-                if not cols:                                   # unknown table: every text column that is not English
-                    cols = [c for c in row if a.with_english or c not in _ENGLISH_COLS]
-                for c in cols:
-                    v = row[c]
-                    if len(v) >= a.min_chars and v not in seen and not v.replace(".", "").isdigit():
-                        seen.add(v)
-                        out.write(v.replace("\n", " ") + "\n")
+            for cells in _table_rows(p, a.min_chars):
+                rows_in += 1
+                variants = [t for r, t in cells if r == _VARIANT]
+                arabic = next((t for r, t in cells if r == _ARABIC), "")
+                for r, t in cells:
+                    if r != _ENGLISH or a.with_english:
+                        emit(t)
+                if variants and arabic and variants[0] != arabic:
+                    parts = [variants[0]]
+                    if len(variants) > 1 and variants[1] not in (variants[0], arabic):
+                        parts.append(variants[1])
+                    t = _flat(" / ".join(parts + [arabic]))
+                    if t not in seen:
+                        seen.add(t)
+                        _write_text(out, t)
                         kept += 1
-    log_info("[csvs] wrote %s lines to %s" % (human_count(kept), out_path))
+                        aligned += 1
+    log_info("[csvs] %s rows in, %s corpus lines (alignment lines: %s) -> %s" % (human_count(rows_in), human_count(kept), human_count(aligned), out_path))
     if kept < a.min_keep:
         log_error("only %d lines kept (--min-keep %d)" % (kept, a.min_keep))
         return 1
@@ -150,6 +239,9 @@ def cmd_csvs(a) -> int:
 
 
 def cmd_csv2json(a) -> int:
+    """Tables -> id/question/answer files.  Per row: every variant against the Arabic cell; without Arabic the first
+    variant against the English gloss; without either the first variant against each other one.  Pairs with equal
+    sides, a side under --min-chars bytes or a question seen before are skipped."""
     files = _csv_files(a.dir or ".")
     if not files:
         log_error("no .csv files found under: " + (a.dir or "."))
@@ -158,41 +250,59 @@ def cmd_csv2json(a) -> int:
         raise SystemExit("--docs-per-file must be > 0 and --id-start >= 0")
     outdir = a.out or "json_shards"
     os.makedirs(outdir, exist_ok=True)
-    seen, batch, pairs, idx, next_id = set(), [], 0, 0, a.id_start
+    seen, pairs, idx, in_file, next_id, rows_in = set(), 0, 0, 0, a.id_start, 0
     skipped = {"same": 0, "empty": 0, "dup": 0}
+    jf = None
 
-    def flush():
-        nonlocal batch, idx
-        if batch:
-            p = os.path.join(outdir, "train-%05d.json" % idx)
-            with open(p, "w", encoding="utf-8") as f:
-                json.dump(batch, f, ensure_ascii=False, indent=1)
-            log_info("[json] wrote " + p)
-            idx += 1
-            batch = []
+    def close():
+        nonlocal jf
+        if jf is not None:
+            jf.write(b"\n]\n")
+            jf.close()
+            jf = None
+
+    def pair(q: str, ans: str) -> None:
+        nonlocal jf, idx, in_file, next_id, pairs
+        q, ans = _flat(q), _flat(ans)
+        if min(len(q.encode("utf-8", "surrogateescape")), len(ans.encode("utf-8", "surrogateescape"))) < a.min_chars:
+            skipped["empty"] += 1
+        elif q == ans:
+            skipped["same"] += 1
+        elif q in seen:
+            skipped["dup"] += 1
+        else:
+            seen.add(q)
+            if jf is None or in_file >= a.docs_per_file:
+                close()
+                path = os.path.join(outdir, "train-%05d.json" % idx)
+                jf = open(path, "wb")
+                jf.write(b"[\n")
+                idx, in_file = idx + 1, 0
+                log_info("[json] opened " + path)
+            # one key per line, no indentation: the layout the reference's own scanner of these files expects
+            rec = "{\n\"id\": %d,\n\"question\": %s,\n\"answer\": %s\n}" % (next_id, json.dumps(q, ensure_ascii=False), json.dumps(ans, ensure_ascii=False))
+            jf.write((b",\n" if in_file else b"") + rec.encode("utf-8", "surrogateescape"))
+            next_id, in_file, pairs = next_id + 1, in_file + 1, pairs + 1
 
     for p in files:
-        for row in _csv_rows(p):
-            q = next((row[c] for c in _Q_COLS if row.get(c)), "")
-            ans = next((row[c] for c in _A_COLS if row.get(c) and row[c] != q), "")
-            if len(q) < a.min_chars or len(ans) < a.min_chars:
+        for cells in _table_rows(p, a.min_chars):
+            rows_in += 1
+            variants = [t for r, t in cells if r == _VARIANT]
+            arabic = next((t for r, t in cells if r == _ARABIC), "")
+            english = next((t for r, t in cells if r == _ENGLISH), "")
+            if variants and arabic:
+                for v in variants:
+                    pair(v, arabic)
+            elif variants and english:
+                pair(variants[0], english)
+            elif len(variants) >= 2:
+                for v in variants[1:]:
+                    pair(variants[0], v)
+            elif variants:
                 skipped["empty"] += 1
-                continue
-            if R.normalize(q) == R.normalize(ans):
-                skipped["same"] += 1
-                continue
-            key = R.normalize(q)
-            if key in seen:
-                skipped["dup"] += 1
-                continue
-            seen.add(key)
-            batch.append({"id": next_id, "question": q, "answer": ans})
-            next_id += 1
-            pairs += 1
-            if len(batch) >= a.docs_per_file:
-                flush()
-    flush()
-    log_info("[json] %s pairs in %d file(s); skipped: %s" % (human_count(pairs), idx, " ".join("%s=%d" % kv for kv in skipped.items())))
+    close()
+    log_info("[json] %s rows in, %s pairs in %d file(s); skipped: %s" % (human_count(rows_in), human_count(pairs), idx,
+                                                                       " ".join("%s=%d" % kv for kv in skipped.items())))
     if pairs < a.min_keep:
         log_error("only %d pairs kept (--min-keep %d)" % (pairs, a.min_keep))
         return 1
@@ -200,14 +310,19 @@ def cmd_csv2json(a) -> int:
 
 
 def cmd_jsons(a) -> int:
+    """Question/answer files -> corpus lines: each distinct question and answer once, flattened to one line."""
     docs = R.load_qa_dir(a.dir) if os.path.isdir(a.dir or ".") else R.load_qa_json(a.dir)
     out_path = a.out or "corpus_json.txt"
-    kept = 0
-    with open(out_path, "w", encoding="utf-8") as out:
+    if os.path.dirname(out_path):
+        os.makedirs(os.path.dirname(out_path), exist_ok=True)
+    kept, seen = 0, set()
+    with open(out_path, "wb") as out:
         for d in docs:
             for v in (d.question, d.answer):
-                if len(v) >= a.min_chars:
-                    out.write(v.replace("\n", " ") + "\n")
+                t = _flat(v)
+                if len(t.encode("utf-8", "surrogateescape")) >= a.min_chars and t not in seen:
+                    seen.add(t)
+                    _write_text(out, t)
                     kept += 1
     log_info("[jsons] %s pairs -> %s lines in %s" % (human_count(len(docs)), human_count(kept), out_path))
     if kept < a.min_keep:

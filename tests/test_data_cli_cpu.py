@@ -153,7 +153,29 @@ def test_data_pipeline_csv_json_retrieve_synth(tmp_path, capsys):
     assert DP.main(["retrieve", "--index", js, "--query", "zzzzz"]) == 0
     assert DP.main(["retrieve", "--index", str(tmp_path / "nothing"), "--query", "x"]) == 1
     assert DP.main(["jsons", "--dir", js, "--out", corpus]) == 0
-    assert len(open(corpus, encoding="utf-8").read().splitlines()) == 2 * len(rows)
+    got = open(corpus, encoding="utf-8").read().splitlines()
+    assert len(got) == len(set(got)) == len({r["question"] for r in rows} | {r["answer"] for r in rows})   # each distinct side once
+    # a table without a known column name has no header: its first row is data, every column a variant
+    assert any(r["question"] == "question" and r["answer"] == "answer" for r in rows)
+    ref = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "bin", "data_pipeline")
+    if os.path.exists(ref):                     # the reference's converters on the same tables write the same bytes
+        import subprocess
+        (root / "verbs.csv").write_text('eng,darija,darija_ar,n1,id\nto eat,kla,\u0643\u0644\u0627,kayakol,7\n"big, large",kbir,\u0643\u0628\u064a\u0631,,8\n'
+                                        'to "go",mcha,,kaymchi,9\n', encoding="utf-8")
+        for extra in ([], ["--with-english"]):
+            a, b = str(tmp_path / "ca.txt"), str(tmp_path / "cb.txt")
+            assert subprocess.run([ref, "csvs", "--dir", str(root), "--out", a] + extra, capture_output=True, timeout=120).returncode == 0
+            assert DP.main(["csvs", "--dir", str(root), "--out", b] + extra) == 0
+            assert open(a, "rb").read() == open(b, "rb").read()
+        ja, jb = str(tmp_path / "ja"), str(tmp_path / "jb")
+        assert subprocess.run([ref, "csv2json", "--dir", str(root), "--out", ja, "--docs-per-file", "3"], capture_output=True, timeout=120).returncode == 0
+        assert DP.main(["csv2json", "--dir", str(root), "--out", jb, "--docs-per-file", "3"]) == 0
+        assert sorted(os.listdir(ja)) == sorted(os.listdir(jb)) and len(os.listdir(ja)) >= 2
+        assert all(open(os.path.join(ja, f), "rb").read() == open(os.path.join(jb, f), "rb").read() for f in os.listdir(ja))
+        a, b = str(tmp_path / "qa.txt"), str(tmp_path / "qb.txt")
+        assert subprocess.run([ref, "jsons", "--dir", ja, "--out", a], capture_output=True, timeout=120).returncode == 0
+        assert DP.main(["jsons", "--dir", ja, "--out", b]) == 0
+        assert open(a, "rb").read() == open(b, "rb").read()
     assert DP.main(["csvs", "--dir", str(tmp_path / "json")]) == 1
     sy = str(tmp_path / "s.jsonl")
     assert DP.main(["synth", "--out", sy, "--n", "25", "--seed", "5"]) == 0
