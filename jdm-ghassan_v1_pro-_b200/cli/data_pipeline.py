@@ -427,6 +427,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     if cmd == "tok-info":
         tok = _load_tok(a)
         n = H.NormalizerConfig.unpack(tok.normalizer_bits)
+        print("vocab_size=%d" % tok.vocab_size)          # the line shell scripts of the reference's tool read
         print("vocab        : %d (%d special)" % (tok.vocab_size, T.N_SPECIAL))
         print("fingerprint  : %s" % H.fingerprint_hex(H.fingerprint_file(a.tokenizer)))
         print("normalizer   : " + " ".join(k for k in ("strip_diacritics", "strip_tatweel", "fold_letters", "lowercase_latin",

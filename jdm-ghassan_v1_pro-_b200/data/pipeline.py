@@ -20,6 +20,7 @@ import numpy as np
 
 from .. import _gb200_host as H
 from . import tokenizer as T
+from ..utils.log import human_count
 
 
 # ---------------------------------------------------------------------------------------------- readers
@@ -334,13 +335,20 @@ def build_shards(records: Iterable[Record], tok: T.Tokenizer, out_dir: str, cfg:
 
 
 def inspect_shards(directory: str, tok: Optional[T.Tokenizer] = None, show: int = 2) -> str:
+    """One line per shard with its first documents decoded, then per split (train, val) the shard count and the
+    token total, as the reference's ``inspect`` sums them (tools/data_pipeline_cli.cpp:1654-1700)."""
     lines = []
+    totals = {"train": [0, 0, 0], "val": [0, 0, 0]}
     for p in sorted(glob.glob(os.path.join(directory, "*.gbin"))):
         s = H.ShardFile()
         ok, why = s.open(p)
         if not ok:
             lines.append("%s: INVALID (%s)" % (os.path.basename(p), why))
             continue
+        split = "val" if os.path.basename(p).startswith("val") else "train"
+        totals[split][0] += 1
+        totals[split][1] += s.n_tokens
+        totals[split][2] += s.n_docs
         lines.append("%s: %d docs, %d tokens%s" % (os.path.basename(p), s.n_docs, s.n_tokens, ", loss masks" if s.has_mask else ""))
         start = 0
         for d in range(min(show, s.n_docs)):
@@ -349,6 +357,10 @@ def inspect_shards(directory: str, tok: Optional[T.Tokenizer] = None, show: int 
             txt = tok.decode(ids, skip_special=True) if tok is not None else " ".join(map(str, ids[:24]))
             lines.append("    [%d] %s" % (d, txt[:160].replace("\n", " ")))
             start = end
+    for split in ("train", "val"):
+        n, t, d = totals[split]
+        if n:
+            lines.append("---- %s: %d shards, %d docs, total: %s tokens ----" % (split, n, d, human_count(t)))
     return "\n".join(lines)
 
 
