@@ -148,6 +148,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         ids = tok.encode(a.text or "")
         print("  input   : %s\n  tokens  : %d\n  pieces  : %s" % (a.text, len(ids), " | ".join(tok.token_bytes(i).decode("utf-8", "replace") for i in ids)))
         print("  ids     : %s" % " ".join(map(str, ids.tolist())))
+        words = max(1, len((a.text or "").split()))
+        print("  decoded : %s" % tok.decode(ids))
+        print("  fertility: %.3f tokens/word, %.2f bytes/token" % (len(ids) / words, len((a.text or "").encode("utf-8")) / max(1, len(ids))))
         return 0
     if cmd == "export":
         from ..formats.gguf import export_gguf

@@ -11,6 +11,7 @@ embeddings; norm gains always fp32.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
@@ -335,5 +336,9 @@ def describe(path: str) -> str:
              "config: " + cfg.summary(), "tensors: %d" % len(f.tensors)]
     for t, sizes in sorted(by_type.items()):
         lines.append("  %-5s %4d tensors %12d bytes" % (GGML_NAMES.get(t, str(t)), len(sizes), sum(sizes)))
-    lines.append("parameters: %d" % cfg.count_parameters())
+    n = cfg.count_parameters()
+    wbytes = sum(sum(v) for v in by_type.values())
+    lines.append("size: %d bytes" % os.path.getsize(path))
+    lines.append("parameters: %d (%.2f M)" % (n, n / 1e6))
+    lines.append("weight bytes: %d (%.2f bits/param)" % (wbytes, 8.0 * wbytes / max(1, n)))
     return "\n".join(lines)
