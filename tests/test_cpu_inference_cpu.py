@@ -166,3 +166,29 @@ def test_quality_benchmark_equals_the_reference(model, tmp_path):
             assert bool(x[key]) == bool(y[key]), (x["id"], key, x["response"])
         assert abs(x["score"] - y["score"]) < 1e-9, (x["id"], x["score"], y["score"])
         assert x["words"] == y["words"] and abs(x["distinct1"] - y["distinct1"]) < 1e-6 and x["max_ngram_repeat"] == y["max_ngram_repeat"]
+
+
+@needs_ref
+@pytest.mark.parametrize("profile", ["q4_0", "q8_k"])
+def test_quantize_writes_the_reference_payloads(model, tmp_path, profile):
+    """`quantize` of both tools on one fp16 file: every tensor's stored bytes and every metadata entry the reference
+    writes are the same; this tool also carries the training provenance (steps, val_loss) over, which the reference drops."""
+    from ghassan_b200 import _gb200_host as H
+    fa, fb = str(tmp_path / "a.gguf"), str(tmp_path / "b.gguf")
+    theirs(["quantize", "--model", model + "/m.gguf", "--out", fa, "--profile", profile])
+    ours(["quantize", "--model", model + "/m.gguf", "--out", fb, "--profile", profile])
+    a, b = H.GgufFile(fa), H.GgufFile(fb)
+    ma, mb = dict(a.metadata), dict(b.metadata)
+    assert set(mb) - set(ma) <= {"steps", "val_loss"} and not set(ma) - set(mb)
+    for k, v in ma.items():
+        assert np.array_equal(np.asarray(v), np.asarray(mb[k])) if not isinstance(v, (bytes, str)) else v == mb[k], k
+    assert [(t["name"], t["type"], tuple(t["shape"])) for t in a.tensors] == [(t["name"], t["type"], tuple(t["shape"])) for t in b.tensors]
+    # Same bytes, up to a handful of 8-bit codes one step apart: values that land within an ulp of a rounding tie
+    # (x / scale = +-0.5) fall either way with the compiler's floating-point contraction settings.
+    off = 0
+    for t in a.tensors:
+        x = np.frombuffer(bytes(a.tensor_raw(t["name"])), dtype=np.int8).astype(np.int32)
+        y = np.frombuffer(bytes(b.tensor_raw(t["name"])), dtype=np.int8).astype(np.int32)
+        assert x.shape == y.shape and int(np.abs(x - y).max(initial=0)) <= (1 if profile == "q8_k" else 0), t["name"]
+        off += int((x != y).sum())
+    assert off <= 8
